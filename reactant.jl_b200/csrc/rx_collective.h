@@ -1,0 +1,24 @@
+// All-reduce of sharded reductions over the mesh axis: NCCL, or the NVLink
+// mailbox kernel for single-word payloads.  In the reference both the
+// partitioning and the NCCL call are made by XLA
+// (deps/ReactantExtra/API.cpp:1487-1497); nothing in the Julia tree emits a
+// collective.
+#pragma once
+#include <functional>
+
+#include "rx_runtime.h"
+
+namespace rx {
+
+void nccl_unique_id(uint8_t* id128);
+void init_nccl(RxClient* c, const uint8_t* id128);
+void mailbox_handle(RxClient* c, int local_device, uint8_t* handle64);
+void open_mailboxes(RxClient* c, const uint8_t* handles, int n_global);
+void destroy_collectives(RxClient* c);
+
+// Sum `st.count` f32 values at ptr(k) on dev(k) for every local device k with the
+// matching values of all other ranks of the mesh; every rank ends with the same bits.
+void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::function<RxDevice*(size_t)>& dev,
+                   const std::function<void*(size_t)>& ptr);
+
+}  // namespace rx

@@ -1,0 +1,42 @@
+// Host-side launch interface of the sm_100a kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "rx_ir.h"
+#include "rx_vm.h"
+
+namespace rx {
+
+struct LaunchCtx {
+  cudaStream_t stream = nullptr;
+  int sm_count = 148;
+  uint32_t* scratch = nullptr;   // per-device partials buffer for two-pass reductions
+  size_t scratch_words = 0;
+  uint64_t* launches = nullptr;  // counts kernels launched through this context
+};
+
+int red_code(RedK k, DT dt);
+
+cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P);
+cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits);
+cudaError_t launch_reduce_row(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, int64_t outer, int64_t red_n);
+int reduce_col_splits(int64_t outer, int64_t red_n, int64_t inner, int sm_count);
+cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, int64_t outer, int64_t red_n,
+                              int64_t inner, uint32_t* partials, int nsplit);
+cudaError_t launch_logsumexp(const LaunchCtx& c, const float* x, int64_t row_stride, int64_t rows, int64_t cols, float* m, float* s, float* lse);
+
+// 2-D stencil step: out window = chain(shifted windows of src), tiles staged through
+// shared memory by TMA.  `tmap` is a CUtensorMap for the source array.
+struct StencilArgs {
+  const void* tmap;          // host pointer to a 128-byte CUtensorMap
+  const float* src;
+  float* dst;
+  int64_t rows, cols;        // output window
+  int64_t src_ld, dst_ld, src_off, dst_off;
+  int n_taps;
+  int dy[8], dx[8];
+};
+cudaError_t launch_stencil(const LaunchCtx& c, const VmProgram& P, const StencilArgs& a);
+
+}  // namespace rx

@@ -1,0 +1,1576 @@
+// Planner: walks the optimised StableHLO module and groups its ops into the
+// fusion templates the kernels implement:
+//   * elementwise chain -> full reduce            (sum(sin.(x) .+ y))
+//   * elementwise chain -> reduce over one axis   (row / column reductions)
+//   * max -> exp-sum -> log over the same axis     (logsumexp, one HBM read)
+//   * shifted-slice sums written into an interior (stencil updates, in place)
+//   * dot_general with elementwise epilogue       (bf16 GEMM, fp32 accumulate)
+//   * reduce over a mesh-sharded axis             (local reduce + all-reduce)
+// Layout shims (the reversed-dims transposes Reactant inserts at function entry
+// and exit, src/TracedUtils.jl:608-626, 846-883), reshapes, slices and
+// broadcasts are folded into index maps and never materialised.
+//
+// In the reference this role is played by XLA's compiler behind
+// ClientCompileWithProto (deps/ReactantExtra/API.cpp:1528-1536); SPMD
+// partitioning of sharded reductions, which XLA performs there
+// (API.cpp:1487-1497), is done here by rule.
+#include "rx_plan.h"
+
+#include <string.h>
+#include <algorithm>
+#include <cmath>
+#include <functional>
+#include <map>
+#include <set>
+#include <sstream>
+
+namespace rx {
+
+namespace {
+
+struct DimMap {
+  int src;        // parent dim feeding this dim, or -1
+  int64_t mult;
+  int64_t off;
+  bool operator<(const DimMap& o) const { return std::tie(src, mult, off) < std::tie(o.src, o.mult, o.off); }
+  bool operator==(const DimMap& o) const { return src == o.src && mult == o.mult && off == o.off; }
+};
+using RMap = std::vector<DimMap>;
+
+struct Expr;
+using ExprP = std::shared_ptr<Expr>;
+struct Expr {
+  enum K { Leaf, Const, Op, Iota, View, Sym } k = Const;
+  DT dt = DT::F32;
+  std::vector<int64_t> shape;
+  // Leaf
+  int slot = -1;
+  std::vector<int64_t> lstride;
+  int64_t loffset = 0;
+  // Const
+  double f = 0;
+  int64_t i = 0;
+  // Op
+  int vmop = 0, cmp = 0;
+  std::vector<ExprP> kids;
+  int iota_dim = 0;
+  RMap map;  // View: one entry per kid dim
+  int cost = 0;
+  bool heavy = false;
+};
+
+std::vector<int64_t> canon_strides(const std::vector<int64_t>& shape) {
+  std::vector<int64_t> s(shape.size());
+  int64_t acc = 1;
+  for (int d = (int)shape.size() - 1; d >= 0; --d) {
+    s[d] = acc;
+    acc *= shape[d];
+  }
+  return s;
+}
+
+int64_t prod(const std::vector<int64_t>& v) {
+  int64_t n = 1;
+  for (auto d : v) n *= d;
+  return n;
+}
+
+VmElem elem_of(DT dt) {
+  switch (dt) {
+    case DT::F32: return EL_F32;
+    case DT::BF16: return EL_BF16;
+    case DT::S32: case DT::U32: return EL_I32;
+    case DT::PRED: return EL_PRED;
+    default: throw Error(RX_ERR_UNSUPPORTED_TYPE, std::string("unsupported element type ") + dt_name(dt) + " in a fused computation");
+  }
+}
+
+bool is_transcendental(int op) {
+  return op == VM_SIN || op == VM_COS || op == VM_EXP || op == VM_LOG || op == VM_TANH || op == VM_POW ||
+         op == VM_LOG1P || op == VM_EXPM1 || op == VM_LOGISTIC || op == VM_DIV || op == VM_SQRT || op == VM_RSQRT;
+}
+
+// -------------------------------------------------------------------------
+// Lowering of an expression DAG over a root iteration space into a VmProgram
+// -------------------------------------------------------------------------
+struct LeafRef {
+  int slot;
+  DT dt;
+  int64_t offset;
+  std::vector<int64_t> stride;  // per root dim
+  bool operator==(const LeafRef& o) const { return slot == o.slot && dt == o.dt && offset == o.offset && stride == o.stride; }
+};
+
+struct VNode {
+  int op;
+  int a = -1, b = -1, c = -1;
+  uint32_t imm = 0;
+  int cmp = 0;
+  int leaf = -1;
+};
+
+struct Lowering {
+  std::vector<int64_t> root;
+  std::vector<VNode> nodes;
+  std::vector<LeafRef> leaves;
+  std::map<std::pair<const Expr*, RMap>, int> memo;
+  bool has_iota = false;
+
+  explicit Lowering(const std::vector<int64_t>& root_shape) : root(root_shape) {}
+
+  static RMap identity(size_t rank) {
+    RMap m(rank);
+    for (size_t d = 0; d < rank; ++d) m[d] = {(int)d, 1, 0};
+    return m;
+  }
+  static RMap compose(const RMap& view, const RMap& parent) {
+    RMap out(view.size());
+    for (size_t d = 0; d < view.size(); ++d) {
+      const DimMap& v = view[d];
+      if (v.src < 0) { out[d] = {-1, 0, v.off}; continue; }
+      const DimMap& p = parent[v.src];
+      if (p.src < 0) out[d] = {-1, 0, v.mult * p.off + v.off};
+      else out[d] = {p.src, v.mult * p.mult, v.mult * p.off + v.off};
+    }
+    return out;
+  }
+  int add(const VNode& n) {
+    nodes.push_back(n);
+    return (int)nodes.size() - 1;
+  }
+  int konst_bits(uint32_t bits) {
+    VNode n{VM_CONST};
+    n.imm = bits;
+    return add(n);
+  }
+  int konst(DT dt, double f, int64_t i) {
+    uint32_t bits;
+    if (dt == DT::F32 || dt == DT::BF16) {
+      float v = (float)f;
+      memcpy(&bits, &v, 4);
+      if (dt == DT::BF16) bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16;
+    } else {
+      bits = (uint32_t)(int32_t)i;
+    }
+    return konst_bits(bits);
+  }
+
+  int lower(const ExprP& e, const RMap& rmap) {
+    auto key = std::make_pair((const Expr*)e.get(), rmap);
+    auto it = memo.find(key);
+    if (it != memo.end()) return it->second;
+    int r = -1;
+    switch (e->k) {
+      case Expr::Leaf: {
+        LeafRef lr{e->slot, e->dt, e->loffset, std::vector<int64_t>(root.size(), 0)};
+        for (size_t d = 0; d < e->lstride.size(); ++d) {
+          lr.offset += e->lstride[d] * rmap[d].off;
+          if (rmap[d].src >= 0) lr.stride[rmap[d].src] += e->lstride[d] * rmap[d].mult;
+        }
+        int idx = -1;
+        for (size_t k = 0; k < leaves.size(); ++k)
+          if (leaves[k] == lr) idx = (int)k;
+        if (idx < 0) {
+          leaves.push_back(lr);
+          idx = (int)leaves.size() - 1;
+          VNode n{-1};
+          n.leaf = idx;
+          r = add(n);
+        } else {
+          for (size_t k = 0; k < nodes.size(); ++k)
+            if (nodes[k].leaf == idx) r = (int)k;
+        }
+        break;
+      }
+      case Expr::Const:
+        r = konst(e->dt, e->f, e->i);
+        break;
+      case Expr::View:
+        r = lower(e->kids[0], compose(e->map, rmap));
+        break;
+      case Expr::Iota: {
+        const DimMap& dm = rmap[e->iota_dim];
+        if (dm.src < 0) {
+          r = konst(DT::S32, 0, dm.off);
+        } else {
+          has_iota = true;
+          VNode n{VM_IOTA};
+          n.a = dm.src;  // root dim (remapped after dim sorting)
+          r = add(n);
+          if (dm.mult != 1) { VNode mul{VM_IMUL}; mul.a = r; mul.b = konst(DT::S32, 0, dm.mult); r = add(mul); }
+          if (dm.off != 0) { VNode ad{VM_IADD}; ad.a = r; ad.b = konst(DT::S32, 0, dm.off); r = add(ad); }
+        }
+        if (dt_is_float(e->dt)) { VNode cv{VM_I2F}; cv.a = r; r = add(cv); }
+        break;
+      }
+      case Expr::Op: {
+        VNode n{e->vmop};
+        n.cmp = e->cmp;
+        if (e->kids.size() > 0) n.a = lower(e->kids[0], rmap);
+        if (e->kids.size() > 1) n.b = lower(e->kids[1], rmap);
+        if (e->kids.size() > 2) n.c = lower(e->kids[2], rmap);
+        r = add(n);
+        break;
+      }
+      case Expr::Sym:
+        throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op: a loop-variant scalar feeds a tensor computation");
+    }
+    memo[key] = r;
+    return r;
+  }
+};
+
+// Sorted / collapsed iteration space shared by all leaves and outputs of a step.
+struct Space {
+  std::vector<int64_t> dim;
+  std::vector<int> cls;                       // 0 kept, 1 reduced
+  std::vector<std::vector<int64_t>> lstride;  // [leaf][dim]
+  std::vector<std::vector<int64_t>> ostride;  // [out][dim]
+  std::vector<int> origin;                    // original root dim of each dim (first of a merged run)
+};
+
+void normalise_space(Space& sp, int dominant_leaf, bool by_output, bool allow_collapse) {
+  size_t nd = sp.dim.size();
+  // drop unit dims
+  std::vector<size_t> keep;
+  for (size_t d = 0; d < nd; ++d)
+    if (sp.dim[d] != 1) keep.push_back(d);
+  auto take = [&](std::vector<int64_t>& v) {
+    std::vector<int64_t> o;
+    for (auto d : keep) o.push_back(v[d]);
+    v = o;
+  };
+  {
+    std::vector<int> c, org;
+    for (auto d : keep) { c.push_back(sp.cls[d]); org.push_back(sp.origin[d]); }
+    sp.cls = c;
+    sp.origin = org;
+  }
+  take(sp.dim);
+  for (auto& l : sp.lstride) take(l);
+  for (auto& o : sp.ostride) take(o);
+  nd = sp.dim.size();
+  // order dims so that the dominant access is contiguous in the innermost dim
+  std::vector<size_t> order(nd);
+  for (size_t d = 0; d < nd; ++d) order[d] = d;
+  const std::vector<int64_t>* ref = nullptr;
+  if (by_output && !sp.ostride.empty()) ref = &sp.ostride[0];
+  else if (dominant_leaf >= 0) ref = &sp.lstride[dominant_leaf];
+  if (ref) {
+    std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) {
+      int64_t sa = std::llabs((*ref)[a]), sb = std::llabs((*ref)[b]);
+      if (sa == 0) sa = INT64_MAX;  // broadcast dims outermost
+      if (sb == 0) sb = INT64_MAX;
+      return sa > sb;
+    });
+  }
+  auto perm = [&](std::vector<int64_t>& v) {
+    std::vector<int64_t> o(nd);
+    for (size_t d = 0; d < nd; ++d) o[d] = v[order[d]];
+    v = o;
+  };
+  {
+    std::vector<int> c(nd), org(nd);
+    for (size_t d = 0; d < nd; ++d) { c[d] = sp.cls[order[d]]; org[d] = sp.origin[order[d]]; }
+    sp.cls = c;
+    sp.origin = org;
+  }
+  perm(sp.dim);
+  for (auto& l : sp.lstride) perm(l);
+  for (auto& o : sp.ostride) perm(o);
+  if (!allow_collapse) return;
+  // merge adjacent dims that every access walks contiguously
+  for (size_t d = 0; d + 1 < sp.dim.size();) {
+    bool ok = sp.cls[d] == sp.cls[d + 1];
+    auto compat = [&](const std::vector<int64_t>& s) { return s[d] == s[d + 1] * sp.dim[d + 1]; };
+    for (auto& l : sp.lstride) ok = ok && compat(l);
+    for (auto& o : sp.ostride) ok = ok && compat(o);
+    if (!ok) { ++d; continue; }
+    sp.dim[d] *= sp.dim[d + 1];
+    auto fold = [&](std::vector<int64_t>& s) { s[d] = s[d + 1]; s.erase(s.begin() + d + 1); };
+    for (auto& l : sp.lstride) fold(l);
+    for (auto& o : sp.ostride) fold(o);
+    sp.dim.erase(sp.dim.begin() + d + 1);
+    sp.cls.erase(sp.cls.begin() + d + 1);
+    sp.origin.erase(sp.origin.begin() + d + 1);
+  }
+}
+
+// -------------------------------------------------------------------------
+struct Planner {
+  const Module& m;
+  Plan& plan;
+  std::vector<ExprP> env;
+  std::vector<int> uses;
+  std::vector<int> shard;  // per value: sharded dim or -1
+  int64_t nparts = 1;
+  std::vector<Step>* cur = nullptr;
+  struct LseInfo { int m_slot, lse_slot; };
+  std::map<int, LseInfo> lse_of_sum;  // sumexp slot -> companions
+  std::set<int> state_slots_live;     // loop-carried slots (writable in place)
+
+  Planner(const Module& mod, Plan& p) : m(mod), plan(p), env(mod.values.size()), uses(mod.values.size(), 0), shard(mod.values.size(), -1) {}
+
+  // ---- helpers -----------------------------------------------------------
+  void count_uses(const Region& r) {
+    for (auto& op : r.ops) {
+      for (int v : op.in) uses[v]++;
+      for (auto& sub : op.regions) count_uses(sub);
+    }
+    for (int v : r.yields) uses[v]++;
+  }
+  Type local_type(int v) const {
+    Type t = m.values[v].type;
+    if (shard[v] >= 0) t.shape[shard[v]] /= nparts;
+    return t;
+  }
+  int new_slot(const Type& t, SlotK k = SlotK::Temp) {
+    Slot s;
+    s.kind = k;
+    s.type = t;
+    plan.slots.push_back(s);
+    return (int)plan.slots.size() - 1;
+  }
+  ExprP leaf(int slot, const Type& t) {
+    auto e = std::make_shared<Expr>();
+    e->k = Expr::Leaf;
+    e->dt = t.dt;
+    e->shape = t.shape;
+    e->slot = slot;
+    e->lstride = canon_strides(t.shape);
+    return e;
+  }
+  ExprP konst(const Type& t, double f, int64_t i) {
+    auto e = std::make_shared<Expr>();
+    e->k = Expr::Const;
+    e->dt = t.dt;
+    e->shape = t.shape;
+    e->f = f;
+    e->i = i;
+    return e;
+  }
+  ExprP mkop(int vmop, const Type& t, std::vector<ExprP> kids, int cmp = 0) {
+    auto e = std::make_shared<Expr>();
+    e->k = Expr::Op;
+    e->dt = t.dt;
+    e->shape = t.shape;
+    e->vmop = vmop;
+    e->cmp = cmp;
+    e->cost = 1;
+    e->heavy = is_transcendental(vmop);
+    for (auto& k : kids) {
+      e->cost += k->cost;
+      e->heavy = e->heavy || k->heavy;
+    }
+    e->kids = std::move(kids);
+    return e;
+  }
+  ExprP view(const ExprP& kid, const Type& t, RMap map) {
+    auto e = std::make_shared<Expr>();
+    e->k = Expr::View;
+    e->dt = t.dt;
+    e->shape = t.shape;
+    e->kids = {kid};
+    e->map = std::move(map);
+    e->cost = kid->cost;
+    e->heavy = kid->heavy;
+    return e;
+  }
+  // A contiguous leaf (any offset): reinterpretable under reshape.
+  static bool contiguous_leaf(const ExprP& e) { return e->k == Expr::Leaf && e->lstride == canon_strides(e->shape); }
+  bool whole_slot(const ExprP& e) const {
+    return contiguous_leaf(e) && e->loffset == 0 && prod(e->shape) == plan.slots[e->slot].type.numel() && e->dt == plan.slots[e->slot].type.dt;
+  }
+  static bool is_splat(const ExprP& e) {
+    if (e->k == Expr::Const) return true;
+    if (e->k == Expr::View) return is_splat(e->kids[0]);
+    if (e->k == Expr::Leaf) return prod(e->shape) == 1;
+    return false;
+  }
+  // host evaluation of scalar integer expressions (loop bounds, update offsets)
+  static bool const_int(const ExprP& e, int64_t* out) {
+    switch (e->k) {
+      case Expr::Const: *out = dt_is_float(e->dt) ? (int64_t)e->f : e->i; return true;
+      case Expr::View: return const_int(e->kids[0], out);
+      case Expr::Op: {
+        int64_t a = 0, b = 0;
+        if (e->kids.size() >= 1 && !const_int(e->kids[0], &a)) return false;
+        if (e->kids.size() >= 2 && !const_int(e->kids[1], &b)) return false;
+        switch (e->vmop) {
+          case VM_IADD: *out = a + b; return true;
+          case VM_ISUB: *out = a - b; return true;
+          case VM_IMUL: *out = a * b; return true;
+          case VM_MOV: *out = a; return true;
+          default: return false;
+        }
+      }
+      default: return false;
+    }
+  }
+  bool slot_writable(int slot) const {
+    const Slot& s = plan.slots[slot];
+    if (s.kind == SlotK::Temp) return true;
+    if (s.kind == SlotK::Arg) return s.writable;
+    return false;
+  }
+  static void collect_leaves(const ExprP& e, std::vector<const Expr*>& out, std::set<const Expr*>& seen) {
+    if (!seen.insert(e.get()).second) return;
+    if (e->k == Expr::Leaf) out.push_back(e.get());
+    for (auto& k : e->kids) collect_leaves(k, out, seen);
+  }
+
+  // ---- program assembly ---------------------------------------------------
+  struct OutSpec {
+    int slot;
+    DT dt;
+    int64_t offset;
+    std::vector<int64_t> stride;  // per root dim
+    int vnode;
+  };
+
+  // Turn lowered nodes into prog (register allocation, dim sorting/collapsing).
+  void assemble(Step& st, Lowering& L, std::vector<OutSpec> outs, int result_vnode, const std::vector<int>& cls, bool by_output) {
+    if (L.leaves.size() > (size_t)kVmMaxLeaves) throw Error(RX_ERR_PLAN, "fusion group reads more than " + std::to_string(kVmMaxLeaves) + " operands");
+    if (outs.size() > (size_t)kVmMaxOuts) throw Error(RX_ERR_PLAN, "fusion group writes too many results");
+    Space sp;
+    sp.dim = L.root;
+    sp.cls = cls;
+    sp.origin.resize(L.root.size());
+    for (size_t d = 0; d < L.root.size(); ++d) sp.origin[d] = (int)d;
+    int dominant = -1;
+    int64_t best = -1;
+    for (size_t k = 0; k < L.leaves.size(); ++k) {
+      sp.lstride.push_back(L.leaves[k].stride);
+      int64_t span = 1;
+      for (size_t d = 0; d < L.root.size(); ++d)
+        if (L.leaves[k].stride[d] != 0) span *= L.root[d];
+      if (span > best) { best = span; dominant = (int)k; }
+    }
+    for (auto& o : outs) sp.ostride.push_back(o.stride);
+    normalise_space(sp, dominant, by_output, !L.has_iota);
+    if (sp.dim.size() > (size_t)kMaxRank) throw Error(RX_ERR_PLAN, "fusion group iteration space has rank > " + std::to_string(kMaxRank));
+    VmProgram& P = st.prog;
+    memset(&P, 0, sizeof P);
+    P.rank = (int)sp.dim.size();
+    for (int d = 0; d < kMaxRank; ++d) P.dim[d] = d < P.rank ? sp.dim[d] : 1;
+    std::vector<int64_t> cstr = canon_strides(sp.dim);
+    // register allocation (linear scan over the node list, which is in topological order)
+    size_t nn = L.nodes.size();
+    std::vector<int> last(nn, -1);
+    for (size_t k = 0; k < nn; ++k) {
+      const VNode& n = L.nodes[k];
+      if (n.op == VM_IOTA) continue;
+      for (int u : {n.a, n.b, n.c})
+        if (u >= 0) last[u] = (int)k;
+    }
+    for (auto& o : outs) last[o.vnode] = (int)nn + 1;
+    if (result_vnode >= 0) last[result_vnode] = (int)nn + 1;
+    std::vector<int> reg(nn, -1);
+    std::vector<int> free_regs;
+    for (int r = kVmMaxRegs - 1; r >= 0; --r) free_regs.push_back(r);
+    auto alloc = [&]() {
+      if (free_regs.empty()) throw Error(RX_ERR_PLAN, "fusion group needs more than " + std::to_string(kVmMaxRegs) + " live values");
+      int r = free_regs.back();
+      free_regs.pop_back();
+      return r;
+    };
+    // leaves first: they are loaded before the program runs
+    for (size_t k = 0; k < nn; ++k)
+      if (L.nodes[k].leaf >= 0) reg[k] = alloc();
+    st.leaf_slot.clear();
+    P.n_leaves = (int)L.leaves.size();
+    P.all_linear = L.has_iota ? 0 : 1;
+    for (size_t k = 0; k < L.leaves.size(); ++k) {
+      VmLeaf& vl = P.leaf[k];
+      vl.ptr = nullptr;
+      vl.offset = L.leaves[k].offset;
+      vl.elem = elem_of(L.leaves[k].dt);
+      bool lin = true, scalar = true;
+      for (int d = 0; d < P.rank; ++d) {
+        vl.stride[d] = sp.lstride[k][d];
+        lin = lin && vl.stride[d] == cstr[d];
+        scalar = scalar && vl.stride[d] == 0;
+      }
+      vl.linear = scalar ? 2 : (lin ? 1 : 0);
+      if (!vl.linear) P.all_linear = 0;
+      for (size_t q = 0; q < nn; ++q)
+        if (L.nodes[q].leaf == (int)k) vl.reg = (uint8_t)reg[q];
+      st.leaf_slot.push_back(L.leaves[k].slot);
+    }
+    int ni = 0;
+    for (size_t k = 0; k < nn; ++k) {
+      const VNode& n = L.nodes[k];
+      if (n.leaf < 0) {
+        // release operands whose last use is this node before allocating dst, so dst may reuse them
+        int ra = n.op == VM_IOTA ? -1 : (n.a >= 0 ? reg[n.a] : -1), rb = n.b >= 0 ? reg[n.b] : -1, rc = n.c >= 0 ? reg[n.c] : -1;
+        if (n.op != VM_IOTA)
+          for (int u : {n.a, n.b, n.c})
+            if (u >= 0 && last[u] == (int)k && reg[u] >= 0) {
+              bool dup = false;
+              for (int f : free_regs) dup = dup || f == reg[u];
+              if (!dup) free_regs.push_back(reg[u]);
+            }
+        reg[k] = alloc();
+        if (ni >= kVmMaxInstr) throw Error(RX_ERR_PLAN, "fusion group longer than " + std::to_string(kVmMaxInstr) + " ops");
+        VmInstr& in = P.ins[ni++];
+        in.op = (uint8_t)n.op;
+        in.dst = (uint8_t)reg[k];
+        if (n.op == VM_IOTA) {
+          int nd = -1;
+          for (int d = 0; d < P.rank; ++d)
+            if (sp.origin[d] == n.a) nd = d;
+          if (nd < 0) { in.op = VM_CONST; in.imm = 0; }  // unit dim: index is 0
+          else in.a = (uint8_t)nd;
+        } else {
+          in.a = (uint8_t)(ra < 0 ? 0 : ra);
+          in.b = (uint8_t)(rb < 0 ? 0 : rb);
+          in.c = (uint8_t)(rc < 0 ? 0 : rc);
+          if (n.op == VM_FCMP || n.op == VM_ICMP) in.c = (uint8_t)n.cmp;
+          in.imm = n.imm;
+        }
+      }
+      if (last[k] < 0 && reg[k] >= 0 && L.nodes[k].leaf < 0) free_regs.push_back(reg[k]);  // dead value
+    }
+    P.n_instr = ni;
+    P.n_outs = (int)outs.size();
+    st.out_slot.clear();
+    for (size_t k = 0; k < outs.size(); ++k) {
+      VmOut& vo = P.out[k];
+      vo.ptr = nullptr;
+      vo.offset = outs[k].offset;
+      vo.elem = elem_of(outs[k].dt);
+      vo.reg = (uint8_t)reg[outs[k].vnode];
+      bool lin = true;
+      for (int d = 0; d < P.rank; ++d) {
+        vo.stride[d] = sp.ostride[k][d];
+        lin = lin && vo.stride[d] == cstr[d];
+      }
+      vo.linear = lin ? 1 : 0;
+      if (!lin && result_vnode < 0) P.all_linear = 0;  // a reduction's output is a single store per group
+      st.out_slot.push_back(outs[k].slot);
+    }
+    P.result_reg = result_vnode >= 0 ? reg[result_vnode] : 0;
+    st.outer = st.red_n = st.inner = 1;
+    // reduction classes after normalisation -> [outer][red][inner]
+    if (!cls.empty() && std::find(cls.begin(), cls.end(), 1) != cls.end()) {
+      std::vector<int> c = sp.cls;
+      // strip to run-lengths: K* R+ K*
+      size_t a = 0;
+      while (a < c.size() && c[a] == 0) ++a;
+      size_t b = a;
+      while (b < c.size() && c[b] == 1) ++b;
+      for (size_t q = b; q < c.size(); ++q)
+        if (c[q] == 1) throw Error(RX_ERR_PLAN, "reduce over non-adjacent dimensions is not supported");
+      if (a > 1 || b - a > 1 || c.size() - b > 1) {
+        // more than one dim per group survived collapsing: strided group, handled by the generic kernels via rank-4 indexing
+      }
+      st.prog.fast_id = FAST_NONE;
+    }
+    detect_fast(st, L, result_vnode >= 0 ? result_vnode : (outs.empty() ? -1 : outs[0].vnode));
+    cls_after = sp.cls;
+  }
+  std::vector<int> cls_after;
+
+  // Recognise chains that have compile-time-fused kernels.
+  void detect_fast(Step& st, Lowering& L, int root) {
+    VmProgram& P = st.prog;
+    P.fast_id = FAST_NONE;
+    if (root < 0) return;
+    auto is_f32_leaf = [&](int v) { return v >= 0 && L.nodes[v].leaf >= 0 && L.leaves[L.nodes[v].leaf].dt == DT::F32; };
+    const VNode& r = L.nodes[root];
+    if (is_f32_leaf(root) && L.leaves.size() == 1) { P.fast_id = FAST_IDENTITY; return; }
+    if (r.op == VM_ADD && L.leaves.size() == 2) {
+      for (int sw = 0; sw < 2; ++sw) {
+        int s = sw ? r.b : r.a, o = sw ? r.a : r.b;
+        if (s >= 0 && L.nodes[s].op == VM_SIN && is_f32_leaf(L.nodes[s].a) && is_f32_leaf(o) && L.nodes[s].a != o) {
+          // leaf 0 must be the sine operand
+          if (L.nodes[L.nodes[s].a].leaf == 1) swap_leaves(st, 0, 1);
+          P.fast_id = FAST_SIN_ADD;
+          return;
+        }
+      }
+    }
+    if (r.op == VM_EXP && L.leaves.size() == 2) {
+      const VNode& sub = L.nodes[r.a];
+      if (sub.op == VM_SUB && is_f32_leaf(sub.a) && is_f32_leaf(sub.b) && sub.a != sub.b) {
+        if (L.nodes[sub.a].leaf == 1) swap_leaves(st, 0, 1);
+        P.fast_id = FAST_EXP_SUB;
+        return;
+      }
+    }
+    if (r.op == VM_MUL && L.leaves.size() == 5) {
+      for (int sw = 0; sw < 2; ++sw) {
+        int c = sw ? r.b : r.a, x = sw ? r.a : r.b;
+        if (c < 0 || x < 0 || L.nodes[c].op != VM_CONST || L.nodes[c].leaf >= 0) continue;
+        // x = ((((l_a + l_b) + l_c) + l_d) + l_e), left-leaning
+        std::vector<int> chain;
+        int curv = x;
+        bool ok = true;
+        for (int depth = 0; depth < 4 && ok; ++depth) {
+          const VNode& a = L.nodes[curv];
+          if (a.op != VM_ADD || !is_f32_leaf(a.b)) { ok = false; break; }
+          chain.push_back(L.nodes[a.b].leaf);
+          curv = a.a;
+        }
+        if (!ok || !is_f32_leaf(curv)) continue;
+        chain.push_back(L.nodes[curv].leaf);
+        std::reverse(chain.begin(), chain.end());
+        std::set<int> uniq(chain.begin(), chain.end());
+        if (uniq.size() != 5) continue;
+        // reorder leaves into evaluation order
+        std::vector<VmLeaf> nl;
+        std::vector<int> ns;
+        for (int q : chain) { nl.push_back(P.leaf[q]); ns.push_back(st.leaf_slot[q]); }
+        for (int q = 0; q < 5; ++q) { P.leaf[q] = nl[q]; st.leaf_slot[q] = ns[q]; }
+        // the interpreter form stays valid: leaf.reg travels with the leaf
+        memcpy(&P.fast_c, &L.nodes[c].imm, 4);
+        P.fast_id = FAST_STENCIL5_MUL;
+        return;
+      }
+    }
+  }
+  void swap_leaves(Step& st, int a, int b) {
+    std::swap(st.prog.leaf[a], st.prog.leaf[b]);
+    std::swap(st.leaf_slot[a], st.leaf_slot[b]);
+  }
+
+  // ---- step emitters -------------------------------------------------------
+  // out[shape-indexed] = expr, written at `offset` with `ostride` into `slot`.
+  void emit_map(const ExprP& e, int slot, int64_t offset, const std::vector<int64_t>& ostride, const std::string& note) {
+    Step st;
+    st.kind = StepK::Map;
+    st.note = note;
+    Lowering L(e->shape);
+    int root = L.lower(e, Lowering::identity(e->shape.size()));
+    DT odt = plan.slots[slot].type.dt;
+    std::vector<int> cls(e->shape.size(), 0);
+    assemble(st, L, {OutSpec{slot, odt, offset, ostride, root}}, -1, cls, true);
+    classify_stencil(st);
+    cur->push_back(std::move(st));
+  }
+
+  // A map whose operands are shifted windows of one row-major 2-D array and whose
+  // output is a window of another: run it through the shared-memory tiled kernel.
+  void classify_stencil(Step& st) {
+    VmProgram& P = st.prog;
+    if (P.rank != 2 || P.n_leaves < 2 || P.n_outs != 1) return;
+    if (P.out[0].stride[1] != 1 || P.out[0].elem != EL_F32) return;
+    int64_t ld = P.leaf[0].stride[0];
+    int64_t base = INT64_MAX;
+    for (int k = 0; k < P.n_leaves; ++k) {
+      if (st.leaf_slot[k] != st.leaf_slot[0] || P.leaf[k].elem != EL_F32) return;
+      if (P.leaf[k].stride[0] != ld || P.leaf[k].stride[1] != 1) return;
+      base = std::min(base, P.leaf[k].offset);
+    }
+    if (ld < P.dim[1]) return;
+    st.st_dy.clear();
+    st.st_dx.clear();
+    int radius = 0;
+    // offsets relative to the window origin; dx recovered as the remainder closest to zero
+    int64_t row0 = base / ld, col0 = INT64_MAX;
+    for (int k = 0; k < P.n_leaves; ++k) col0 = std::min(col0, P.leaf[k].offset % ld);
+    for (int k = 0; k < P.n_leaves; ++k) {
+      int64_t dy = P.leaf[k].offset / ld - row0, dx = P.leaf[k].offset % ld - col0;
+      if (dy < 0 || dy > 8 || dx < 0 || dx > 8) return;
+      st.st_dy.push_back((int)dy);
+      st.st_dx.push_back((int)dx);
+      radius = std::max(radius, (int)std::max(dy, dx));
+    }
+    if (st.leaf_slot[0] == st.out_slot[0]) return;  // in-place shifted update is not a stencil step
+    st.kind = StepK::Stencil;
+    st.st_rows = P.dim[0];
+    st.st_cols = P.dim[1];
+    st.st_src_ld = ld;
+    st.st_src_off = row0 * ld + col0;
+    st.st_dst_ld = P.out[0].stride[0];
+    st.st_dst_off = P.out[0].offset;
+    st.st_radius = radius;
+  }
+
+  int materialise(const ExprP& e, const std::string& why) {
+    if (whole_slot(e)) return e->slot;
+    Type t;
+    t.dt = e->dt;
+    t.shape = e->shape;
+    int slot = new_slot(t);
+    emit_map(e, slot, 0, canon_strides(e->shape), why);
+    return slot;
+  }
+  ExprP materialised(const ExprP& e, const std::string& why) {
+    if (e->k == Expr::Leaf) return e;
+    Type t;
+    t.dt = e->dt;
+    t.shape = e->shape;
+    return leaf(materialise(e, why), t);
+  }
+
+  // ---- op handlers -----------------------------------------------------------
+  int join_shard(const Op& op, const std::vector<int>& ins) {
+    int s = -1;
+    for (int v : ins) {
+      if (shard[v] < 0) continue;
+      if (s >= 0 && s != shard[v]) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op " + op.name + ": operands sharded along different dimensions");
+      s = shard[v];
+    }
+    if (s >= 0)
+      for (int v : ins)
+        if (shard[v] < 0 && !is_splat(env[v]))
+          throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op " + op.name + ": replicated non-splat operand combined with a sharded one");
+    return s;
+  }
+
+  int convert_op(DT from, DT to) {
+    auto cls = [](DT d) { return dt_is_float(d) ? 0 : (d == DT::PRED ? 2 : 1); };
+    int a = cls(from), b = cls(to);
+    if (a == 0 && b == 0) return to == DT::BF16 && from != DT::BF16 ? VM_RBF16 : VM_MOV;
+    if (a == 1 && b == 0) return VM_I2F;
+    if (a == 0 && b == 1) return VM_F2I;
+    if (a == 2 && b == 0) return VM_P2F;
+    if (a == 0 && b == 2) return VM_F2P;
+    if (a == 1 && b == 2) return VM_I2P;
+    return VM_MOV;  // pred->int, int->int of the same width
+  }
+  void check_dt(const Op& op, DT dt) {
+    if (dt == DT::F32 || dt == DT::BF16 || dt == DT::S32 || dt == DT::PRED) return;
+    throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type " + std::string(dt_name(dt)) + " in " + op.name);
+  }
+  // bf16 arithmetic is evaluated in f32 and rounded once per op, as XLA's CPU backend does
+  ExprP round_if_bf16(const ExprP& e) {
+    if (e->dt != DT::BF16 || e->k != Expr::Op || e->vmop == VM_RBF16 || e->vmop == VM_MOV || e->vmop == VM_SELECT) return e;
+    Type t{e->dt, e->shape};
+    return mkop(VM_RBF16, t, {e});
+  }
+
+  void maybe_spill(int v) {
+    // Values with several consumers are computed once when recomputation would be costly.
+    ExprP e = env[v];
+    if (uses[v] > 1 && e->k != Expr::Leaf && !is_splat(e) && prod(e->shape) > 1024 && e->cost > 12)
+      env[v] = materialised(e, "shared value " + m.values[v].name);
+  }
+
+  void plan_elementwise(const Op& op) {
+    int v = op.out[0];
+    shard[v] = join_shard(op, op.in);
+    Type t = local_type(v);
+    bool scalar_int = t.shape.empty() && (t.dt == DT::S64 || t.dt == DT::S32 || t.dt == DT::U32 || t.dt == DT::U64);
+    if (!scalar_int && op.kind != OpK::Compare) check_dt(op, t.dt);
+    DT idt = m.values[op.in[0]].type.dt;
+    bool fl = dt_is_float(idt);
+    std::vector<ExprP> k;
+    for (int x : op.in) k.push_back(env[x]);
+    ExprP e;
+    switch (op.kind) {
+      case OpK::Unary: {
+        int vop = op.ew;
+        if (!fl) {
+          if (vop == VM_NEG) vop = VM_INEG;
+          else if (vop == VM_ABS) vop = VM_IABS;
+          else if (vop == VM_NOT) vop = idt == DT::PRED ? VM_LNOT : VM_NOT;
+          else if (vop != VM_MOV && vop != VM_SIGN) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op " + op.name + " on integers");
+        }
+        e = mkop(vop, t, k);
+        break;
+      }
+      case OpK::Binary: {
+        int vop = op.ew;
+        if (!fl) {
+          switch (vop) {
+            case VM_ADD: vop = VM_IADD; break;
+            case VM_SUB: vop = VM_ISUB; break;
+            case VM_MUL: vop = VM_IMUL; break;
+            case VM_DIV: vop = VM_IDIV; break;
+            case VM_MAX: vop = idt == DT::PRED ? VM_OR : VM_IMAX; break;
+            case VM_MIN: vop = idt == DT::PRED ? VM_AND : VM_IMIN; break;
+            case VM_AND: case VM_OR: case VM_XOR: break;
+            default: throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op " + op.name + " on integers");
+          }
+        } else if (vop == VM_AND || vop == VM_OR || vop == VM_XOR) {
+          throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op " + op.name + " on floats");
+        }
+        // m + log(sumexp) where both come from one logsumexp pass: already computed
+        if (vop == VM_ADD) {
+          for (int sw = 0; sw < 2; ++sw) {
+            const ExprP& a = k[sw];
+            const ExprP& b = k[1 - sw];
+            if (a->k == Expr::Leaf && b->k == Expr::Op && b->vmop == VM_LOG && b->kids[0]->k == Expr::Leaf && whole_slot(a) && whole_slot(b->kids[0])) {
+              auto it = lse_of_sum.find(b->kids[0]->slot);
+              if (it != lse_of_sum.end() && it->second.m_slot == a->slot) {
+                env[v] = leaf(it->second.lse_slot, t);
+                return;
+              }
+            }
+          }
+        }
+        e = mkop(vop, t, k);
+        break;
+      }
+      case OpK::Convert: {
+        if (scalar_int) { e = mkop(VM_MOV, t, k); break; }
+        check_dt(op, idt);
+        e = mkop(convert_op(idt, t.dt), t, k);
+        break;
+      }
+      case OpK::Compare: {
+        bool sc = m.values[op.in[0]].type.shape.empty() && !fl;
+        if (!sc) check_dt(op, idt);
+        e = mkop(fl ? VM_FCMP : VM_ICMP, t, k, op.ew);
+        break;
+      }
+      case OpK::Select: {
+        ExprP p = k[0];
+        if (p->shape.empty() && !t.shape.empty()) {  // scalar predicate broadcasts
+          RMap mp;
+          Type pt{DT::PRED, t.shape};
+          p = view(p, pt, mp);
+        }
+        e = mkop(VM_SELECT, t, {p, k[1], k[2]});
+        break;
+      }
+      case OpK::Clamp: {
+        bool f = dt_is_float(t.dt);
+        auto bc = [&](const ExprP& x) {
+          if (x->shape.empty() && !t.shape.empty()) { Type xt{x->dt, t.shape}; return view(x, xt, RMap{}); }
+          return x;
+        };
+        ExprP lo = bc(k[0]), hi = bc(k[2]);
+        e = mkop(f ? VM_MIN : VM_IMIN, t, {mkop(f ? VM_MAX : VM_IMAX, t, {k[1], lo}), hi});
+        break;
+      }
+      default: throw Error(RX_ERR_PLAN, "internal: not elementwise");
+    }
+    env[v] = round_if_bf16(e);
+    maybe_spill(v);
+  }
+
+  void plan_constant(const Op& op) {
+    int v = op.out[0];
+    Type t = m.values[v].type;
+    if (op.splat) {
+      env[v] = konst(t, op.fval, op.ival);
+      return;
+    }
+    int slot = new_slot(t, SlotK::Const);
+    plan.slots[slot].init = op.dense;
+    env[v] = leaf(slot, t);
+  }
+
+  // Operand of a contraction: a strided 2-D (or batched) view of a bf16/f32 slot.
+  struct MatView { int slot; int64_t off; std::vector<int64_t> stride; };
+  bool as_strided_leaf(const ExprP& e, MatView* mv) {
+    Lowering L(e->shape);
+    int r = L.lower(e, Lowering::identity(e->shape.size()));
+    if (L.nodes[r].leaf < 0 || L.leaves.size() != 1 || L.nodes.size() != 1) return false;
+    mv->slot = L.leaves[0].slot;
+    mv->off = L.leaves[0].offset;
+    mv->stride = L.leaves[0].stride;
+    return true;
+  }
+
+  void plan_view(const Op& op) {
+    int v = op.out[0], x = op.in[0];
+    ExprP kid = env[x];
+    const Type& gt_in = m.values[x].type;
+    RMap mp(gt_in.shape.size());
+    switch (op.kind) {
+      case OpK::BroadcastInDim:
+        if (shard[x] >= 0) shard[v] = (int)op.dims[shard[x]];
+        for (size_t d = 0; d < gt_in.shape.size(); ++d) {
+          int od = (int)op.dims[d];
+          if (gt_in.shape[d] == 1 && m.values[v].type.shape[od] != 1) mp[d] = {-1, 0, 0};
+          else mp[d] = {od, 1, 0};
+        }
+        break;
+      case OpK::Transpose:
+        for (size_t j = 0; j < op.dims.size(); ++j) {
+          mp[op.dims[j]] = {(int)j, 1, 0};
+          if (shard[x] == (int)op.dims[j]) shard[v] = (int)j;
+        }
+        break;
+      case OpK::Slice:
+        if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.slice of a sharded tensor");
+        for (size_t d = 0; d < gt_in.shape.size(); ++d) mp[d] = {(int)d, op.stride[d], op.start[d]};
+        break;
+      default: break;
+    }
+    env[v] = simplify(view(kid, local_type(v), mp));
+  }
+
+  // A view that merely relabels unit dims of a contiguous leaf is itself a contiguous leaf.
+  ExprP simplify(const ExprP& e) {
+    if (e->k != Expr::View) return e;
+    const Expr* base = e.get();
+    while (base->k == Expr::View) base = base->kids[0].get();
+    if (base->k != Expr::Leaf) return e;
+    MatView mv;
+    if (!as_strided_leaf(e, &mv)) return e;
+    std::vector<int64_t> cs = canon_strides(e->shape);
+    for (size_t d = 0; d < e->shape.size(); ++d)
+      if (e->shape[d] != 1 && mv.stride[d] != cs[d]) return e;
+    auto l = leaf(mv.slot, Type{e->dt, e->shape});
+    l->loffset = mv.off;
+    return l;
+  }
+
+  void plan_reshape(const Op& op) {
+    int v = op.out[0], x = op.in[0];
+    if (shard[x] >= 0) {
+      // only unit-dim insertion/removal keeps the sharded dim identifiable
+      const auto& is = m.values[x].type.shape;
+      const auto& os = m.values[v].type.shape;
+      int64_t before = 1;
+      for (int d = 0; d < shard[x]; ++d) before *= is[d];
+      int64_t acc = 1;
+      shard[v] = -1;
+      for (size_t d = 0; d < os.size(); ++d) {
+        if (acc == before && os[d] == is[shard[x]]) { shard[v] = (int)d; break; }
+        acc *= os[d];
+      }
+      if (shard[v] < 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reshape regrouping a sharded dimension");
+    }
+    Type t = local_type(v);
+    ExprP kid = env[x];
+    if (kid->k == Expr::Const) { env[v] = konst(t, kid->f, kid->i); return; }
+    if (contiguous_leaf(kid)) {
+      auto e = leaf(kid->slot, t);
+      e->loffset = kid->loffset;
+      env[v] = e;
+      return;
+    }
+    // unit-dim insert/remove: a pure index relabelling
+    std::vector<int> in_nz, out_nz;
+    for (size_t d = 0; d < kid->shape.size(); ++d) if (kid->shape[d] != 1) in_nz.push_back((int)d);
+    for (size_t d = 0; d < t.shape.size(); ++d) if (t.shape[d] != 1) out_nz.push_back((int)d);
+    bool same = in_nz.size() == out_nz.size();
+    for (size_t q = 0; same && q < in_nz.size(); ++q) same = kid->shape[in_nz[q]] == t.shape[out_nz[q]];
+    if (same) {
+      RMap mp(kid->shape.size(), DimMap{-1, 0, 0});
+      for (size_t q = 0; q < in_nz.size(); ++q) mp[in_nz[q]] = {out_nz[q], 1, 0};
+      env[v] = view(kid, t, mp);
+      return;
+    }
+    ExprP mat = materialised(kid, "reshape operand " + m.values[x].name);
+    if (!contiguous_leaf(mat)) {
+      int s = new_slot(Type{mat->dt, mat->shape});
+      emit_map(mat, s, 0, canon_strides(mat->shape), "reshape operand " + m.values[x].name);
+      mat = leaf(s, Type{mat->dt, mat->shape});
+    }
+    auto e = leaf(mat->slot, t);
+    e->loffset = mat->loffset;
+    env[v] = e;
+  }
+
+  void plan_iota(const Op& op) {
+    int v = op.out[0];
+    auto e = std::make_shared<Expr>();
+    e->k = Expr::Iota;
+    e->dt = m.values[v].type.dt;
+    e->shape = m.values[v].type.shape;
+    e->iota_dim = (int)op.dims[0];
+    e->cost = 1;
+    if (e->dt != DT::S32 && e->dt != DT::F32) throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type " + std::string(dt_name(e->dt)) + " in stablehlo.iota");
+    env[v] = e;
+  }
+
+  void plan_reduce(const Op& op) {
+    int v = op.out[0], x = op.in[0];
+    ExprP X = env[x], init = env[op.in[1]];
+    if (init->k != Expr::Const) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce with a non-constant init value");
+    DT dt = X->dt;
+    check_dt(op, dt);
+    bool needs_allreduce = false;
+    if (shard[x] >= 0) {
+      bool over = std::find(op.dims.begin(), op.dims.end(), (int64_t)shard[x]) != op.dims.end();
+      if (over) {
+        if (op.red != RedK::Add) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce (non-additive) over a sharded dimension");
+        needs_allreduce = true;
+        shard[v] = -1;
+      } else {
+        int shift = 0;
+        for (auto d : op.dims) if (d < shard[x]) ++shift;
+        shard[v] = shard[x] - shift;
+      }
+    }
+    Type rt = local_type(v);
+    std::vector<int> cls(X->shape.size(), 0);
+    for (auto d : op.dims) cls[d] = 1;
+    // output strides over root dims: kept dims in order
+    std::vector<int64_t> ostr(X->shape.size(), 0);
+    {
+      int64_t acc = 1;
+      for (int d = (int)X->shape.size() - 1; d >= 0; --d)
+        if (!cls[d]) { ostr[d] = acc; acc *= X->shape[d]; }
+    }
+    int slot = new_slot(rt);
+    Step st;
+    st.red = op.red;
+    st.red_dt = (dt == DT::S32) ? DT::S32 : (dt == DT::PRED ? DT::PRED : DT::F32);
+    if (dt == DT::PRED && op.red == RedK::Add) st.red = RedK::Or;  // i1 addition saturates
+    st.init_f = init->f;
+    st.init_i = init->i;
+    Lowering L(X->shape);
+    int root = L.lower(X, Lowering::identity(X->shape.size()));
+    OutSpec os{slot, rt.dt, 0, ostr, root};
+    assemble(st, L, {os}, root, cls, false);
+    // shape of the collapsed space
+    const VmProgram& P = st.prog;
+    std::vector<int> c = cls_after;
+    int nred = (int)std::count(c.begin(), c.end(), 1);
+    int64_t red_n = 1, kept_n = 1;
+    for (int d = 0; d < P.rank; ++d) (c[d] ? red_n : kept_n) *= P.dim[d];
+    st.red_n = red_n;
+    std::ostringstream note;
+    note << "reduce(" << (op.red == RedK::Add ? "add" : op.red == RedK::Max ? "max" : op.red == RedK::Min ? "min" : op.red == RedK::Mul ? "mul" : op.red == RedK::Or ? "or" : "and") << ")";
+    if (nred == 0) {
+      // only unit dims are reduced: out = x (op) init, a plain map
+      int vop = st.red_dt == DT::F32 ? (op.red == RedK::Add ? VM_ADD : op.red == RedK::Max ? VM_MAX : op.red == RedK::Min ? VM_MIN : VM_MUL)
+                                     : (st.red == RedK::Add ? VM_IADD : st.red == RedK::Max ? VM_IMAX : st.red == RedK::Min ? VM_IMIN : st.red == RedK::Mul ? VM_IMUL : st.red == RedK::Or ? VM_OR : VM_AND);
+      Type xt{X->dt, X->shape};
+      ExprP e = round_if_bf16(mkop(vop, xt, {X, konst(xt, init->f, init->i)}));
+      emit_map(e, slot, 0, ostr, "reduce over unit dimensions");
+      env[v] = leaf(slot, rt);
+      return;
+    } else if (kept_n == 1) {
+      st.kind = StepK::ReduceFull;
+      if (P.rank != 1 && !(P.rank == 0)) {
+        // several reduced dims that could not be merged: index generically
+      }
+    } else {
+      to_outer_red_inner(st, c);
+      // the reduced run is contiguous in memory for the dominant operand iff it is the innermost dim
+      st.kind = st.inner == 1 ? StepK::ReduceRow : StepK::ReduceCol;
+    }
+    st.note = note.str() + " over " + std::to_string(st.red_n) + " of " + std::to_string(kept_n * red_n) + " elements";
+    plan.scratch_floats = std::max<int64_t>(plan.scratch_floats, 1 << 16);
+
+    // logsumexp: this is sum(exp(x - max(x))) with the max produced by an earlier row reduce of the same x
+    if (op.red == RedK::Add && st.kind == StepK::ReduceRow && st.prog.fast_id == FAST_EXP_SUB && try_logsumexp(st, slot)) {
+      env[v] = leaf(slot, rt);
+      return;
+    }
+    cur->push_back(std::move(st));
+    if (needs_allreduce) {
+      Step ar;
+      ar.kind = StepK::AllReduce;
+      ar.dst_slot = slot;
+      ar.count = rt.numel();
+      ar.red_dt = rt.dt;
+      ar.note = "all_reduce(sum) over the mesh axis";
+      if (rt.dt != DT::F32) throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type for all_reduce");
+      cur->push_back(std::move(ar));
+    }
+    env[v] = leaf(slot, rt);
+  }
+
+  // Rewrite prog dims/strides into exactly three dims [outer][red][inner].
+  void to_outer_red_inner(Step& st, const std::vector<int>& c) {
+    VmProgram& P = st.prog;
+    size_t a = 0;
+    while (a < c.size() && c[a] == 0) ++a;
+    size_t b = a;
+    while (b < c.size() && c[b] == 1) ++b;
+    if (a > 1 || b - a > 1 || c.size() - b > 1)
+      throw Error(RX_ERR_PLAN, "reduction over a strided group of dimensions is not supported");
+    int64_t dim[3] = {1, 1, 1};
+    int map3[3] = {-1, -1, -1};
+    if (a == 1) { dim[0] = P.dim[0]; map3[0] = 0; }
+    if (b - a == 1) { dim[1] = P.dim[a]; map3[1] = (int)a; }
+    if (c.size() - b == 1) { dim[2] = P.dim[b]; map3[2] = (int)b; }
+    auto remap = [&](int64_t* s) {
+      int64_t o[kMaxRank] = {0, 0, 0, 0};
+      for (int q = 0; q < 3; ++q) o[q] = map3[q] >= 0 ? s[map3[q]] : 0;
+      for (int q = 0; q < kMaxRank; ++q) s[q] = o[q];
+    };
+    for (int k = 0; k < P.n_leaves; ++k) remap(P.leaf[k].stride);
+    for (int k = 0; k < P.n_outs; ++k) remap(P.out[k].stride);
+    for (int k = 0; k < P.n_instr; ++k)
+      if (P.ins[k].op == VM_IOTA) {
+        int nd = -1;
+        for (int q = 0; q < 3; ++q) if (map3[q] == P.ins[k].a) nd = q;
+        P.ins[k].a = (uint8_t)(nd < 0 ? 0 : nd);
+      }
+    P.rank = 3;
+    P.dim[0] = st.outer = dim[0];
+    P.dim[1] = st.red_n = dim[1];
+    P.dim[2] = st.inner = dim[2];
+    P.dim[3] = 1;
+  }
+
+  bool try_logsumexp(Step& sum_step, int sum_slot) {
+    const VmProgram& S = sum_step.prog;
+    // leaf 0 = x rows (contiguous along the reduced dim), leaf 1 = per-row max (broadcast along it)
+    if (S.leaf[0].stride[1] != 1 || S.leaf[1].stride[1] != 0 || S.leaf[0].elem != EL_F32 || S.leaf[1].elem != EL_F32) return false;
+    if (sum_step.init_f != 0.0) return false;
+    int m_slot = sum_step.leaf_slot[1];
+    for (size_t q = 0; q < cur->size(); ++q) {
+      Step& mx = (*cur)[q];
+      if (mx.kind != StepK::ReduceRow || mx.red != RedK::Max || mx.out_slot.size() != 1 || mx.out_slot[0] != m_slot) continue;
+      if (mx.prog.fast_id != FAST_IDENTITY || mx.leaf_slot[0] != sum_step.leaf_slot[0]) return false;
+      const VmLeaf& a = mx.prog.leaf[0];
+      const VmLeaf& b = S.leaf[0];
+      if (a.offset != b.offset || a.stride[0] != b.stride[0] || a.stride[1] != b.stride[1]) return false;
+      if (mx.outer != sum_step.outer || mx.red_n != sum_step.red_n) return false;
+      if (!(std::isinf(mx.init_f) && mx.init_f < 0)) return false;
+      // max rows must be laid out like the sum rows
+      if (mx.prog.out[0].stride[0] != S.out[0].stride[0] || S.leaf[1].stride[0] != mx.prog.out[0].stride[0] || S.leaf[1].offset != 0) return false;
+      Step lse;
+      lse.kind = StepK::LogSumExp;
+      lse.prog = mx.prog;
+      lse.leaf_slot = mx.leaf_slot;
+      int lse_slot = new_slot(plan.slots[sum_slot].type);
+      lse.out_slot = {m_slot, sum_slot, lse_slot};
+      lse.outer = mx.outer;
+      lse.red_n = mx.red_n;
+      lse.inner = 1;
+      lse.note = "logsumexp rows=" + std::to_string(lse.outer) + " cols=" + std::to_string(lse.red_n) + " (max, sum(exp(x-max)), max+log(sum) in one read)";
+      (*cur)[q] = std::move(lse);
+      lse_of_sum[sum_slot] = {m_slot, lse_slot};
+      return true;
+    }
+    return false;
+  }
+
+  void plan_dus(const Op& op) {
+    int v = op.out[0], o = op.in[0], u = op.in[1];
+    for (int x : op.in) if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dynamic_update_slice of a sharded tensor");
+    ExprP O = env[o], U = env[u];
+    Type t = m.values[v].type;
+    std::vector<int64_t> starts;
+    for (size_t k = 2; k < op.in.size(); ++k) {
+      int64_t s;
+      if (!const_int(env[op.in[k]], &s)) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dynamic_update_slice with non-constant start indices");
+      int d = (int)k - 2;
+      s = std::max<int64_t>(0, std::min<int64_t>(s, t.shape[d] - U->shape[d]));  // clamped, as the op specifies
+      starts.push_back(s);
+    }
+    int dst = -1;
+    bool in_place = whole_slot(O) && uses[o] == 1 && slot_writable(O->slot);
+    if (in_place) {
+      // the update may read the destination only at the position it writes
+      std::vector<const Expr*> lv;
+      std::set<const Expr*> seen;
+      collect_leaves(U, lv, seen);
+      for (auto* l : lv)
+        if (l->slot == O->slot) in_place = false;
+    }
+    if (in_place) {
+      dst = O->slot;
+    } else {
+      dst = new_slot(t);
+      if (O->k == Expr::Leaf && whole_slot(O)) {
+        Step cp;
+        cp.kind = StepK::Copy;
+        cp.src_slot = O->slot;
+        cp.dst_slot = dst;
+        cp.bytes = plan.slots[dst].bytes();
+        cp.note = "copy (update target still live)";
+        cur->push_back(std::move(cp));
+      } else {
+        emit_map(O, dst, 0, canon_strides(t.shape), "materialise update target");
+      }
+    }
+    std::vector<int64_t> cs = canon_strides(t.shape);
+    int64_t off = 0;
+    for (size_t d = 0; d < starts.size(); ++d) off += starts[d] * cs[d];
+    emit_map(U, dst, off, cs, "update window at offset " + std::to_string(off));
+    env[v] = leaf(dst, t);
+  }
+
+  void plan_pad(const Op& op) {
+    int v = op.out[0];
+    if (shard[op.in[0]] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.pad of a sharded tensor");
+    for (auto i : op.stride) if (i != 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.pad with interior padding");
+    for (auto i : op.start) if (i < 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.pad with negative padding");
+    for (auto i : op.limit) if (i < 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.pad with negative padding");
+    ExprP X = env[op.in[0]], pv = env[op.in[1]];
+    if (pv->k != Expr::Const) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.pad with a non-constant padding value");
+    Type t = m.values[v].type;
+    check_dt(op, t.dt);
+    int dst = new_slot(t);
+    emit_map(konst(t, pv->f, pv->i), dst, 0, canon_strides(t.shape), "pad fill");
+    std::vector<int64_t> cs = canon_strides(t.shape);
+    int64_t off = 0;
+    for (size_t d = 0; d < op.start.size(); ++d) off += op.start[d] * cs[d];
+    emit_map(X, dst, off, cs, "pad interior");
+    env[v] = leaf(dst, t);
+  }
+
+  void plan_concat(const Op& op) {
+    int v = op.out[0];
+    Type t = m.values[v].type;
+    check_dt(op, t.dt);
+    int dst = new_slot(t);
+    std::vector<int64_t> cs = canon_strides(t.shape);
+    int64_t pos = 0;
+    int d = (int)op.dims[0];
+    for (int x : op.in) {
+      if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.concatenate of a sharded tensor");
+      emit_map(env[x], dst, pos * cs[d], cs, "concatenate piece");
+      pos += env[x]->shape[d];
+    }
+    env[v] = leaf(dst, t);
+  }
+
+  void plan_dot(const Op& op) {
+    int v = op.out[0], a = op.in[0], b = op.in[1];
+    if (shard[a] >= 0 || shard[b] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general on sharded operands");
+    ExprP A = env[a], B = env[b];
+    Type rt = m.values[v].type;
+    if (!(A->dt == B->dt && (A->dt == DT::BF16 || A->dt == DT::F32)))
+      throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element types for stablehlo.dot_general: " + std::string(dt_name(A->dt)) + " x " + dt_name(B->dt));
+    if (op.lcontract.size() != 1 || op.lbatch.size() > 1)
+      throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general with several contracting or batching dimensions");
+    size_t nb = op.lbatch.size();
+    if (A->shape.size() != 2 + nb || B->shape.size() != 2 + nb)
+      throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general on operands that are not (batched) matrices");
+    MatView av, bv;
+    auto get = [&](int val, MatView* mv, const char* why) {
+      if (as_strided_leaf(env[val], mv)) return;
+      ExprP mat = materialised(env[val], why);
+      if (!as_strided_leaf(mat, mv)) throw Error(RX_ERR_PLAN, "internal: materialised operand is not a leaf");
+      env[val] = mat;  // later consumers read the materialised copy
+    };
+    get(a, &av, "contraction lhs");
+    get(b, &bv, "contraction rhs");
+    int lc = (int)op.lcontract[0], rc = (int)op.rcontract[0];
+    int lb = nb ? (int)op.lbatch[0] : -1, rb = nb ? (int)op.rbatch[0] : -1;
+    int lf = -1, rf = -1;
+    for (int d = 0; d < (int)A->shape.size(); ++d) if (d != lc && d != lb) lf = d;
+    for (int d = 0; d < (int)B->shape.size(); ++d) if (d != rc && d != rb) rf = d;
+    Step st;
+    st.kind = StepK::Gemm;
+    GemmDesc& g = st.gemm;
+    g.M = A->shape[lf];
+    g.K = A->shape[lc];
+    g.N = B->shape[rf];
+    if (B->shape[rc] != g.K) throw Error(RX_ERR_SHAPE, "stablehlo.dot_general: contracting dimensions differ");
+    g.batch = nb ? A->shape[lb] : 1;
+    g.a_slot = av.slot;
+    g.b_slot = bv.slot;
+    g.a_sm = av.stride[lf];
+    g.a_sk = av.stride[lc];
+    g.b_sk = bv.stride[rc];
+    g.b_sn = bv.stride[rf];
+    g.a_sb = nb ? av.stride[lb] : 0;
+    g.b_sb = nb ? bv.stride[rb] : 0;
+    g.in_dt = A->dt;
+    g.out_dt = rt.dt;
+    st.prog.leaf[0].offset = av.off;
+    st.prog.leaf[1].offset = bv.off;
+    int dst = new_slot(rt);
+    g.d_slot = dst;
+    g.d_sb = g.M * g.N;
+    st.leaf_slot = {av.slot, bv.slot};
+    st.out_slot = {dst};
+    std::ostringstream note;
+    note << "gemm M=" << g.M << " N=" << g.N << " K=" << g.K << (g.batch > 1 ? " batch=" + std::to_string(g.batch) : "")
+         << " A(" << (g.a_sk == 1 ? "k-major" : "m-major") << ") B(" << (g.b_sk == 1 ? "k-major" : "n-major") << ") "
+         << dt_name(g.in_dt) << "->" << dt_name(g.out_dt) << " fp32 accumulate";
+    st.note = note.str();
+    cur->push_back(std::move(st));
+    env[v] = leaf(dst, rt);
+  }
+
+  void plan_while(const Op& op) {
+    size_t n = op.in.size();
+    const Region& cond = op.regions[0];
+    const Region& body = op.regions[1];
+    for (int x : op.in) if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while carrying sharded tensors");
+    // ---- trip count: cond is `compare LT|LE, counter, bound`, body steps counter by a constant
+    int64_t trip = -1;
+    int counter = -1;
+    {
+      if (cond.ops.empty() || cond.yields.size() != 1) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: condition is not a comparison");
+      // bind cond args symbolically
+      for (size_t k = 0; k < n; ++k) {
+        auto s = std::make_shared<Expr>();
+        s->k = Expr::Sym;
+        s->dt = m.values[cond.args[k]].type.dt;
+        s->shape = m.values[cond.args[k]].type.shape;
+        s->slot = (int)k;
+        env[cond.args[k]] = s;
+      }
+      const Op* cmp = nullptr;
+      for (auto& c : cond.ops) {
+        if (c.kind == OpK::Constant) plan_constant(c);
+        else if (c.kind == OpK::Compare && c.out[0] == cond.yields[0]) cmp = &c;
+        else throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: condition contains " + c.name);
+      }
+      if (!cmp) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: condition is not a comparison");
+      ExprP l = env[cmp->in[0]], r = env[cmp->in[1]];
+      int64_t bound;
+      if (l->k != Expr::Sym || !const_int(r, &bound) || (cmp->ew != CMP_LT && cmp->ew != CMP_LE))
+        throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: only `counter < constant` loops are supported");
+      counter = l->slot;
+      int64_t init;
+      if (!const_int(env[op.in[counter]], &init)) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: counter does not start at a constant");
+      // step: body yield of counter = counter + c
+      int yv = body.yields[counter];
+      int64_t step = 0;
+      for (auto& bo : body.ops)
+        if (bo.out.size() == 1 && bo.out[0] == yv && bo.kind == OpK::Binary && bo.ew == VM_ADD) {
+          for (int sw = 0; sw < 2; ++sw)
+            if (bo.in[sw] == body.args[counter]) {
+              // the other operand must be constant: look it up among constants defined so far or in the body
+              int other = bo.in[1 - sw];
+              if (env[other] && const_int(env[other], &step)) {}
+              else
+                for (auto& bc : body.ops)
+                  if (bc.kind == OpK::Constant && bc.out[0] == other && bc.splat) step = bc.ival;
+            }
+        }
+      if (step <= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: counter is not advanced by a positive constant");
+      if (cmp->ew == CMP_LE) bound += 1;
+      trip = bound <= init ? 0 : (bound - init + step - 1) / step;
+    }
+    // ---- loop-carried tensors live in slots
+    Step loop;
+    loop.kind = StepK::Loop;
+    loop.trip = trip;
+    std::vector<int> state_slot(n, -1);
+    for (size_t k = 0; k < n; ++k) {
+      if ((int)k == counter) continue;
+      int x = op.in[k];
+      Type t = m.values[x].type;
+      ExprP e = env[x];
+      if (t.shape.empty() && !dt_is_float(t.dt)) continue;  // integer scalar bookkeeping stays symbolic
+      bool reuse = whole_slot(e) && uses[x] == 1 && slot_writable(e->slot);
+      if (reuse) {
+        state_slot[k] = e->slot;
+      } else {
+        int s = new_slot(t);
+        if (whole_slot(e)) {
+          Step cp;
+          cp.kind = StepK::Copy;
+          cp.src_slot = e->slot;
+          cp.dst_slot = s;
+          cp.bytes = plan.slots[s].bytes();
+          cp.note = "copy loop-carried value into loop storage";
+          cur->push_back(std::move(cp));
+        } else {
+          emit_map(e, s, 0, canon_strides(t.shape), "initialise loop-carried value");
+        }
+        state_slot[k] = s;
+      }
+    }
+    // ---- body
+    std::vector<Step>* saved = cur;
+    cur = &loop.body;
+    for (size_t k = 0; k < n; ++k) {
+      int arg = body.args[k];
+      if (state_slot[k] >= 0) {
+        env[arg] = leaf(state_slot[k], m.values[arg].type);
+      } else {
+        auto s = std::make_shared<Expr>();
+        s->k = Expr::Sym;
+        s->dt = m.values[arg].type.dt;
+        s->shape = m.values[arg].type.shape;
+        env[arg] = s;
+      }
+    }
+    int first_body_slot = (int)plan.slots.size();
+    plan_region(body);
+    std::vector<int> yslot(n, -1);
+    for (size_t k = 0; k < n; ++k) {
+      if (state_slot[k] < 0) continue;
+      ExprP y = env[body.yields[k]];
+      if (!whole_slot(y)) y = leaf(materialise(y, "loop-carried result"), m.values[body.yields[k]].type);
+      // a value defined outside the loop (and not itself loop-carried) must not be rotated into the loop's storage
+      bool is_state = std::find(state_slot.begin(), state_slot.end(), y->slot) != state_slot.end();
+      if (!is_state && y->slot < first_body_slot) y = leaf(materialise_copy(y), m.values[body.yields[k]].type);
+      yslot[k] = y->slot;
+    }
+    cur = saved;
+    // two carried values must not end up in one buffer
+    {
+      std::set<int> seen;
+      for (size_t k = 0; k < n; ++k)
+        if (yslot[k] >= 0 && !seen.insert(yslot[k]).second)
+          throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: two loop-carried values alias one result");
+    }
+    for (size_t k = 0; k < n; ++k)
+      if (state_slot[k] >= 0) {
+        loop.state_slots.push_back(state_slot[k]);
+        loop.yield_slots.push_back(yslot[k]);
+      }
+    loop.note = "counted loop x" + std::to_string(trip);
+    cur->push_back(std::move(loop));
+    // ---- results
+    for (size_t k = 0; k < n; ++k) {
+      int r = op.out[k];
+      if (state_slot[k] >= 0) env[r] = leaf(state_slot[k], m.values[r].type);
+      else {
+        auto s = std::make_shared<Expr>();  // final scalar values are not consumed by tensor code on the path
+        s->k = Expr::Sym;
+        s->dt = m.values[r].type.dt;
+        env[r] = s;
+      }
+    }
+  }
+  int materialise_copy(const ExprP& e) {
+    Type t{e->dt, e->shape};
+    int s = new_slot(t);
+    emit_map(e, s, 0, canon_strides(e->shape), "copy");
+    return s;
+  }
+
+  void plan_region(const Region& r) {
+    for (auto& op : r.ops) {
+      switch (op.kind) {
+        case OpK::Constant: plan_constant(op); break;
+        case OpK::Iota: plan_iota(op); break;
+        case OpK::Unary: case OpK::Binary: case OpK::Convert: case OpK::Compare: case OpK::Select: case OpK::Clamp:
+          plan_elementwise(op); break;
+        case OpK::BroadcastInDim: case OpK::Transpose: case OpK::Slice: plan_view(op); break;
+        case OpK::Reshape: plan_reshape(op); break;
+        case OpK::Reduce: plan_reduce(op); break;
+        case OpK::DynamicUpdateSlice: plan_dus(op); break;
+        case OpK::Pad: plan_pad(op); break;
+        case OpK::Concatenate: plan_concat(op); break;
+        case OpK::DotGeneral: plan_dot(op); break;
+        case OpK::While: plan_while(op); break;
+        default: throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op " + op.name);
+      }
+    }
+  }
+
+  void run() {
+    const Func& f = m.funcs.at("main");
+    nparts = m.num_partitions;
+    plan.num_partitions = nparts;
+    count_uses(f.body);
+    int64_t mesh_size = 1;
+    for (auto& kv : m.meshes)
+      for (auto& ax : kv.second) mesh_size *= ax.second;
+    if (nparts > 1 && !m.meshes.empty() && mesh_size != nparts)
+      throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported: mesh size does not match mhlo.num_partitions");
+    if (nparts > 1)
+      for (auto& kv : m.meshes)
+        if (kv.second.size() != 1) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported: only 1-D meshes are supported");
+    for (size_t k = 0; k < f.body.args.size(); ++k) {
+      int v = f.body.args[k];
+      const ArgAttr& at = f.arg_attrs[k];
+      if (nparts > 1 && !at.sharding_mesh.empty()) {
+        int sd = -1;
+        for (size_t d = 0; d < at.dim_axes.size(); ++d)
+          if (!at.dim_axes[d].empty()) {
+            if (sd >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported: argument sharded along several dimensions");
+            sd = (int)d;
+          }
+        if (sd >= 0 && m.values[v].type.shape[sd] % nparts != 0)
+          throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported: sharded dimension is not divisible by the mesh size");
+        shard[v] = sd;
+      }
+      Type lt = local_type(v);
+      int slot = new_slot(lt, SlotK::Arg);
+      plan.slots[slot].arg_index = (int)k;
+      plan.slots[slot].writable = at.aliasing_output >= 0;
+      plan.arg_types.push_back(lt);
+      plan.arg_global_types.push_back(m.values[v].type);
+      plan.arg_sharded_dim.push_back(shard[v]);
+      plan.arg_alias.push_back(at.aliasing_output);
+      env[v] = leaf(slot, lt);
+    }
+    cur = &plan.steps;
+    plan_region(f.body);
+    for (size_t k = 0; k < f.body.yields.size(); ++k) {
+      int v = f.body.yields[k];
+      ExprP e = env[v];
+      if (!e || e->k == Expr::Sym) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported: @main returns a loop counter");
+      Type lt = local_type(v);
+      int slot;
+      if (whole_slot(e) && plan.slots[e->slot].kind != SlotK::Const) slot = e->slot;
+      else {
+        slot = new_slot(lt);
+        emit_map(e, slot, 0, canon_strides(lt.shape), "result " + std::to_string(k));
+      }
+      ResultBinding rb;
+      rb.slot = slot;
+      rb.type = lt;
+      rb.sharded_dim = shard[v];
+      plan.results.push_back(rb);
+    }
+    // a temp slot handed out twice would be freed twice: give later duplicates their own copy
+    std::set<int> seen;
+    for (auto& rb : plan.results) {
+      if (plan.slots[rb.slot].kind == SlotK::Temp && !seen.insert(rb.slot).second) {
+        int s = new_slot(rb.type);
+        Step cp;
+        cp.kind = StepK::Copy;
+        cp.src_slot = rb.slot;
+        cp.dst_slot = s;
+        cp.bytes = plan.slots[s].bytes();
+        cp.note = "duplicate result";
+        plan.steps.push_back(std::move(cp));
+        rb.slot = s;
+      }
+    }
+  }
+};
+
+const char* step_name(StepK k) {
+  switch (k) {
+    case StepK::Map: return "map";
+    case StepK::ReduceFull: return "reduce_full";
+    case StepK::ReduceRow: return "reduce_row";
+    case StepK::ReduceCol: return "reduce_col";
+    case StepK::LogSumExp: return "logsumexp";
+    case StepK::Stencil: return "stencil";
+    case StepK::Gemm: return "gemm";
+    case StepK::Copy: return "copy";
+    case StepK::Fill: return "fill";
+    case StepK::Loop: return "loop";
+    case StepK::AllReduce: return "all_reduce";
+  }
+  return "?";
+}
+
+const char* fast_name(int id) {
+  switch (id) {
+    case FAST_SIN_ADD: return "sin_add";
+    case FAST_IDENTITY: return "identity";
+    case FAST_EXP_SUB: return "exp_sub";
+    case FAST_STENCIL5_MUL: return "stencil5_mul";
+    default: return "vm";
+  }
+}
+
+void describe_steps(std::ostringstream& os, const std::vector<Step>& steps) {
+  os << "[";
+  for (size_t k = 0; k < steps.size(); ++k) {
+    const Step& s = steps[k];
+    if (k) os << ",";
+    os << "{\"kind\":\"" << step_name(s.kind) << "\",\"note\":\"" << s.note << "\"";
+    if (s.kind == StepK::Map || s.kind == StepK::ReduceFull || s.kind == StepK::ReduceRow || s.kind == StepK::ReduceCol || s.kind == StepK::Stencil || s.kind == StepK::LogSumExp) {
+      os << ",\"chain\":\"" << fast_name(s.prog.fast_id) << "\",\"instrs\":" << s.prog.n_instr << ",\"leaves\":" << s.prog.n_leaves
+         << ",\"linear\":" << s.prog.all_linear << ",\"rank\":" << s.prog.rank << ",\"dims\":[";
+      for (int d = 0; d < s.prog.rank; ++d) os << (d ? "," : "") << s.prog.dim[d];
+      os << "]";
+    }
+    if (s.kind == StepK::Loop) {
+      os << ",\"trip\":" << s.trip << ",\"body\":";
+      describe_steps(os, s.body);
+    }
+    os << "}";
+  }
+  os << "]";
+}
+
+}  // namespace
+
+std::string Plan::describe() const {
+  std::ostringstream os;
+  os << "{\"num_partitions\":" << num_partitions << ",\"slots\":" << slots.size() << ",\"args\":" << arg_types.size()
+     << ",\"results\":" << results.size() << ",\"steps\":";
+  describe_steps(os, steps);
+  os << "}";
+  return os.str();
+}
+
+std::unique_ptr<Plan> build_plan(const Module& m) {
+  auto p = std::make_unique<Plan>();
+  Planner pl(m, *p);
+  pl.run();
+  return p;
+}
+
+}  // namespace rx

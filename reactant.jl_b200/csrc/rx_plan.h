@@ -1,0 +1,93 @@
+// Execution plan: what `XLA.compile` turns a module into in this engine.
+// A plan is a list of kernel launches ("steps") over a table of buffer slots;
+// it replaces the loaded executable XLA would build at
+// deps/ReactantExtra/API.cpp:1482-1507 (ClientCompileInternal).
+#pragma once
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "rx_ir.h"
+#include "rx_vm.h"
+
+namespace rx {
+
+enum class SlotK { Arg, Temp, Const };
+
+struct Slot {
+  SlotK kind = SlotK::Temp;
+  Type type;                  // per-device (local) type
+  int arg_index = -1;         // Arg
+  bool writable = false;      // Arg: carries tf.aliasing_output (may be updated in place when donated)
+  std::vector<uint8_t> init;  // Const: payload uploaded once per device
+  int64_t bytes() const { return type.numel() * (int64_t)dt_size(type.dt); }
+};
+
+enum class StepK { Map, ReduceFull, ReduceRow, ReduceCol, LogSumExp, Stencil, Gemm, Copy, Fill, Loop, AllReduce };
+
+struct GemmDesc {
+  // D[m][n] = sum_k A(m,k) * B(k,n); strides in elements of the operand slots.
+  int a_slot = -1, b_slot = -1, d_slot = -1;
+  int64_t M = 0, N = 0, K = 0, batch = 1;
+  int64_t a_sm = 0, a_sk = 0, b_sk = 0, b_sn = 0;  // element strides
+  int64_t a_sb = 0, b_sb = 0, d_sb = 0;            // batch strides
+  DT in_dt = DT::BF16, out_dt = DT::BF16;
+  // optional fused epilogue: prog evaluated per (m, n) with the accumulator in register `acc_reg`
+  bool has_epilogue = false;
+  int acc_reg = 0;
+};
+
+struct Step {
+  StepK kind = StepK::Map;
+  std::string note;               // human-readable summary (plan dumps, tests)
+  VmProgram prog{};               // leaf/out pointers are bound at launch time
+  std::vector<int> leaf_slot;     // slot of prog.leaf[i]
+  std::vector<int> out_slot;      // slot of prog.out[i]
+  // reductions: collapsed space is [outer][red][inner]; prog.dim holds those three
+  RedK red = RedK::Add;
+  DT red_dt = DT::F32;
+  double init_f = 0;              // value combined with the reduction (the reduce op's init operand)
+  int64_t init_i = 0;
+  int64_t outer = 1, red_n = 1, inner = 1;
+  // LogSumExp: out_slot = {max, sumexp, lse}
+  // Stencil: prog leaves are shifted views of one slot; tile geometry derived at launch
+  int64_t st_rows = 0, st_cols = 0, st_src_ld = 0, st_dst_ld = 0, st_src_off = 0, st_dst_off = 0;
+  int st_radius = 0;
+  std::vector<int> st_dy, st_dx;  // per leaf
+  GemmDesc gemm;
+  // Copy / Fill
+  int src_slot = -1, dst_slot = -1;
+  int64_t bytes = 0;
+  double fill_f = 0;
+  int64_t fill_i = 0;
+  // Loop
+  int64_t trip = 0;
+  std::vector<Step> body;
+  std::vector<int> state_slots;   // slot holding loop-carried value j on entry to an iteration
+  std::vector<int> yield_slots;   // slot holding its next value at the end of the body
+  // AllReduce (sum over the mesh axis, in place on dst_slot)
+  int64_t count = 0;
+};
+
+struct ResultBinding {
+  int slot = -1;
+  Type type;          // per-device type handed back to the caller
+  int sharded_dim = -1;
+};
+
+struct Plan {
+  std::vector<Slot> slots;
+  std::vector<Step> steps;
+  std::vector<ResultBinding> results;
+  std::vector<Type> arg_types;        // per-device
+  std::vector<Type> arg_global_types;
+  std::vector<int> arg_sharded_dim;   // -1 = replicated
+  std::vector<int> arg_alias;         // tf.aliasing_output or -1
+  int64_t num_partitions = 1;
+  int64_t scratch_floats = 0;         // two-pass reduction scratch the plan needs
+  std::string describe() const;       // JSON summary of the plan
+};
+
+std::unique_ptr<Plan> build_plan(const Module& m);
+
+}  // namespace rx

@@ -1,0 +1,842 @@
+// C ABI + executor.  Entry points keep the names and meaning of Reactant's
+// PJRT shim (deps/ReactantExtra/API.cpp; see include/rx_b200.h for the
+// line-by-line mapping).  Device memory is owned here through the CUDA runtime
+// only; there is no CPU or library fallback behind any entry point.
+#include "rx_runtime.h"
+
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <cmath>
+#include <sstream>
+
+#include "../../include/rx_b200.h"
+#include "rx_collective.h"
+#include "rx_gemm.h"
+#include "rx_stencil.h"
+
+using namespace rx;
+
+extern "C" {
+void (*ReactantThrowError)(const char*) = nullptr;
+}
+
+namespace {
+
+thread_local std::string g_err;
+thread_local int g_code = 0;
+
+void report(int code, const std::string& msg) {
+  g_err = msg;
+  g_code = code;
+  if (ReactantThrowError) ReactantThrowError(msg.c_str());
+}
+void clear_error() {
+  g_err.clear();
+  g_code = 0;
+}
+struct CudaError : Error {
+  explicit CudaError(cudaError_t e, const char* what) : Error(RX_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e)) {}
+};
+#define CK(call)                                   \
+  do {                                             \
+    cudaError_t e__ = (call);                      \
+    if (e__ != cudaSuccess) throw CudaError(e__, #call); \
+  } while (0)
+
+char* dup_cstr(const std::string& s) {
+  char* p = (char*)malloc(s.size() + 1);
+  memcpy(p, s.c_str(), s.size() + 1);
+  return p;
+}
+
+size_t round_up(size_t b) { return b == 0 ? 256 : (b + 255) & ~(size_t)255; }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// device pool
+// ---------------------------------------------------------------------------
+void* RxDevice::alloc(size_t bytes) {
+  size_t rb = round_up(bytes);
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = pool.find(rb);
+    if (it != pool.end() && !it->second.empty()) {
+      void* p = it->second.back();
+      it->second.pop_back();
+      pool_bytes -= (int64_t)rb;
+      bytes_in_use += (int64_t)rb;
+      peak_bytes_in_use = std::max(peak_bytes_in_use, bytes_in_use);
+      return p;
+    }
+  }
+  if (bytes_limit > 0 && bytes_in_use + pool_bytes + (int64_t)rb > bytes_limit) trim();
+  void* p = nullptr;
+  CK(cudaSetDevice(ordinal));
+  cudaError_t e = cudaMalloc(&p, rb);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    trim();
+    e = cudaMalloc(&p, rb);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      throw Error(RX_ERR_CUDA, "out of device memory allocating " + std::to_string(rb) + " bytes on device " + std::to_string(ordinal));
+    }
+  }
+  std::lock_guard<std::mutex> lk(mu);
+  ++num_allocs;
+  bytes_in_use += (int64_t)rb;
+  peak_bytes_in_use = std::max(peak_bytes_in_use, bytes_in_use);
+  largest_alloc = std::max<int64_t>(largest_alloc, (int64_t)rb);
+  return p;
+}
+
+void RxDevice::release(void* p, size_t bytes) {
+  if (!p) return;
+  size_t rb = round_up(bytes);
+  std::lock_guard<std::mutex> lk(mu);
+  pool[rb].push_back(p);
+  bytes_in_use -= (int64_t)rb;
+  pool_bytes += (int64_t)rb;
+  peak_pool_bytes = std::max(peak_pool_bytes, pool_bytes);
+}
+
+void RxDevice::trim() {
+  std::map<size_t, std::vector<void*>> old;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    old.swap(pool);
+    pool_bytes = 0;
+  }
+  if (old.empty()) return;
+  cudaSetDevice(ordinal);
+  cudaStreamSynchronize(stream);  // cached blocks may still be read by queued work
+  for (auto& kv : old)
+    for (void* p : kv.second) cudaFree(p);
+}
+
+EventState::~EventState() {
+  if (ev) {
+    cudaSetDevice(dev->ordinal);
+    cudaEventDestroy(ev);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// executor
+// ---------------------------------------------------------------------------
+namespace {
+
+struct DevRun {
+  RxDevice* dev;
+  std::vector<std::shared_ptr<Storage>> table;  // per slot
+};
+
+void* slot_ptr(DevRun& r, int slot) {
+  if (slot < 0 || !r.table[slot]) throw Error(RX_ERR_PLAN, "internal: slot " + std::to_string(slot) + " has no storage");
+  return r.table[slot]->ptr;
+}
+
+VmProgram bind(const Step& st, DevRun& r) {
+  VmProgram P = st.prog;
+  for (int k = 0; k < P.n_leaves; ++k) P.leaf[k].ptr = slot_ptr(r, st.leaf_slot[k]);
+  for (int k = 0; k < P.n_outs; ++k) P.out[k].ptr = slot_ptr(r, st.out_slot[k]);
+  return P;
+}
+
+uint32_t init_bits(const Step& st) {
+  if (st.red_dt == DT::F32) {
+    float f = (float)st.init_f;
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    return u;
+  }
+  if (st.red_dt == DT::PRED) return st.init_i ? 1u : 0u;
+  return (uint32_t)(int32_t)st.init_i;
+}
+
+struct ProfScope {
+  RxDevice* d;
+  cudaEvent_t a = nullptr, b = nullptr;
+  const char* kind;
+  ProfScope(RxDevice* dev, const char* k) : d(dev), kind(k) {
+    if (!d->profiling) return;
+    cudaEventCreate(&a);
+    cudaEventCreate(&b);
+    cudaEventRecord(a, d->stream);
+  }
+  ~ProfScope() {
+    if (!d->profiling) return;
+    cudaEventRecord(b, d->stream);
+    d->spans.push_back({kind, a, b});
+  }
+};
+
+const char* kind_name(StepK k) {
+  switch (k) {
+    case StepK::Map: return "map";
+    case StepK::ReduceFull: return "reduce_full";
+    case StepK::ReduceRow: return "reduce_row";
+    case StepK::ReduceCol: return "reduce_col";
+    case StepK::LogSumExp: return "logsumexp";
+    case StepK::Stencil: return "stencil";
+    case StepK::Gemm: return "gemm";
+    case StepK::Copy: return "copy";
+    case StepK::Fill: return "fill";
+    case StepK::Loop: return "loop";
+    case StepK::AllReduce: return "all_reduce";
+  }
+  return "?";
+}
+
+void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<DevRun>& runs);
+
+void run_one(RxExecutable* ex, const Step& st, DevRun& r) {
+  RxDevice* d = r.dev;
+  CK(cudaSetDevice(d->ordinal));
+  LaunchCtx c = d->ctx();
+  ProfScope ps(d, kind_name(st.kind));
+  switch (st.kind) {
+    case StepK::Map: {
+      VmProgram P = bind(st, r);
+      CK(launch_map(c, P));
+      break;
+    }
+    case StepK::Stencil: {
+      VmProgram P = bind(st, r);
+      CK(rx::run_stencil(d, st, P));
+      break;
+    }
+    case StepK::ReduceFull: {
+      VmProgram P = bind(st, r);
+      CK(launch_reduce_full(c, P, red_code(st.red, st.red_dt), init_bits(st)));
+      break;
+    }
+    case StepK::ReduceRow: {
+      VmProgram P = bind(st, r);
+      CK(launch_reduce_row(c, P, red_code(st.red, st.red_dt), init_bits(st), st.outer, st.red_n));
+      break;
+    }
+    case StepK::ReduceCol: {
+      VmProgram P = bind(st, r);
+      int ns = reduce_col_splits(st.outer, st.red_n, st.inner, d->sm_count);
+      size_t words = (size_t)st.outer * ns * st.inner;
+      std::shared_ptr<Storage> tmp;
+      uint32_t* partials = d->scratch;
+      if (words > d->scratch_words) {
+        tmp = std::make_shared<Storage>(d, d->alloc(words * 4), words * 4);
+        partials = (uint32_t*)tmp->ptr;
+      }
+      CK(launch_reduce_col(c, P, red_code(st.red, st.red_dt), init_bits(st), st.outer, st.red_n, st.inner, partials, ns));
+      break;
+    }
+    case StepK::LogSumExp: {
+      const VmLeaf& l = st.prog.leaf[0];
+      const float* x = (const float*)slot_ptr(r, st.leaf_slot[0]) + l.offset;
+      CK(launch_logsumexp(c, x, l.stride[0], st.outer, st.red_n, (float*)slot_ptr(r, st.out_slot[0]), (float*)slot_ptr(r, st.out_slot[1]),
+                          (float*)slot_ptr(r, st.out_slot[2])));
+      break;
+    }
+    case StepK::Gemm: {
+      CK(rx::run_gemm(d, st, slot_ptr(r, st.gemm.a_slot), slot_ptr(r, st.gemm.b_slot), slot_ptr(r, st.gemm.d_slot)));
+      break;
+    }
+    case StepK::Copy: {
+      CK(cudaMemcpyAsync(slot_ptr(r, st.dst_slot), slot_ptr(r, st.src_slot), (size_t)st.bytes, cudaMemcpyDeviceToDevice, d->stream));
+      break;
+    }
+    default:
+      throw Error(RX_ERR_PLAN, std::string("internal: step kind ") + kind_name(st.kind) + " has no single-device launch");
+  }
+}
+
+void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<DevRun>& runs) {
+  for (const Step& st : steps) {
+    if (st.kind == StepK::Loop) {
+      for (int64_t it = 0; it < st.trip; ++it) {
+        run_steps(ex, st.body, runs);
+        // rotate storage: carried value j now lives where the body left its next value
+        for (auto& r : runs) {
+          std::vector<int> involved = st.state_slots;
+          for (int y : st.yield_slots)
+            if (std::find(involved.begin(), involved.end(), y) == involved.end()) involved.push_back(y);
+          std::map<int, std::shared_ptr<Storage>> old;
+          for (int s : involved) old[s] = r.table[s];
+          std::vector<std::shared_ptr<Storage>> spare;
+          std::map<int, bool> taken;
+          for (size_t j = 0; j < st.state_slots.size(); ++j) {
+            r.table[st.state_slots[j]] = old[st.yield_slots[j]];
+            taken[st.yield_slots[j]] = true;
+          }
+          for (int s : involved)
+            if (!taken.count(s)) spare.push_back(old[s]);
+          size_t q = 0;
+          for (int s : involved)
+            if (std::find(st.state_slots.begin(), st.state_slots.end(), s) == st.state_slots.end()) r.table[s] = spare[q++];
+        }
+      }
+    } else if (st.kind == StepK::AllReduce) {
+      rx::run_allreduce(ex->client, st, runs.size(), [&](size_t k) { return runs[k].dev; }, [&](size_t k) { return slot_ptr(runs[k], st.dst_slot); });
+    } else {
+      for (auto& r : runs) run_one(ex, st, r);
+    }
+  }
+}
+
+void check_arg(const Plan& p, int i, RxBuffer* b, RxDevice* d) {
+  if (!b) throw Error(RX_ERR_BAD_HANDLE, "argument " + std::to_string(i) + " is a null buffer");
+  if (b->donated.load() || !b->st) throw Error(RX_ERR_DONATED, "argument " + std::to_string(i) + " was donated to an earlier execution");
+  if (b->dev != d) throw Error(RX_ERR_ARG, "argument " + std::to_string(i) + " lives on a different device than the one executing");
+  const Type& t = p.arg_types[i];
+  if (b->dt != t.dt || b->dims != t.shape) {
+    Type got{b->dt, b->dims};
+    throw Error(RX_ERR_SHAPE, "argument " + std::to_string(i) + " is " + got.str() + ", executable expects " + t.str());
+  }
+}
+
+// Runs the plan on `devs` (one program instance per device), args laid out [device][arg].
+void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** args, int nargs_per_dev, const uint8_t* donatable,
+             int num_results, RxBuffer** results, uint8_t* futures, RxFuture** future_results) {
+  const Plan& p = *ex->plan;
+  if (nargs_per_dev != (int)p.arg_types.size())
+    throw Error(RX_ERR_ARG, "executable takes " + std::to_string(p.arg_types.size()) + " arguments per device, got " + std::to_string(nargs_per_dev));
+  if (num_results != (int)p.results.size())
+    throw Error(RX_ERR_ARG, "Error: results.size()=" + std::to_string(p.results.size()) + " does not match num_results=" + std::to_string(num_results));
+  if (p.num_partitions > 1 && (int64_t)devs.size() * ex->client->num_nodes != p.num_partitions)
+    throw Error(RX_ERR_ARG, "executable is partitioned over " + std::to_string(p.num_partitions) + " devices, launch covers " + std::to_string(devs.size() * ex->client->num_nodes));
+  std::vector<DevRun> runs(devs.size());
+  for (size_t k = 0; k < devs.size(); ++k) {
+    RxDevice* d = devs[k];
+    DevRun& r = runs[k];
+    r.dev = d;
+    r.table.resize(p.slots.size());
+    CK(cudaSetDevice(d->ordinal));
+    for (int i = 0; i < nargs_per_dev; ++i) check_arg(p, i, args[k * nargs_per_dev + i], d);
+    for (size_t s = 0; s < p.slots.size(); ++s) {
+      const Slot& sl = p.slots[s];
+      if (sl.kind == SlotK::Arg) {
+        RxBuffer* b = args[k * nargs_per_dev + sl.arg_index];
+        if (sl.writable && !(donatable && donatable[sl.arg_index])) {
+          // the plan updates this argument in place but the caller keeps it: work on a private copy
+          size_t bytes = (size_t)sl.bytes();
+          auto st = std::make_shared<Storage>(d, d->alloc(bytes), bytes);
+          CK(cudaMemcpyAsync(st->ptr, b->st->ptr, bytes, cudaMemcpyDeviceToDevice, d->stream));
+          r.table[s] = st;
+        } else {
+          r.table[s] = b->st;
+        }
+      } else if (sl.kind == SlotK::Const) {
+        std::lock_guard<std::mutex> lk(ex->mu);
+        auto& cs = ex->consts[d->local_id];
+        auto it = cs.find((int)s);
+        if (it == cs.end()) {
+          size_t bytes = (size_t)sl.bytes();
+          auto st = std::make_shared<Storage>(d, d->alloc(bytes), bytes);
+          CK(cudaMemcpyAsync(st->ptr, sl.init.data(), bytes, cudaMemcpyHostToDevice, d->stream));
+          CK(cudaStreamSynchronize(d->stream));
+          it = cs.emplace((int)s, st).first;
+        }
+        r.table[s] = it->second;
+      } else {
+        size_t bytes = (size_t)sl.bytes();
+        r.table[s] = std::make_shared<Storage>(d, d->alloc(bytes), bytes);
+      }
+    }
+  }
+  run_steps(ex, p.steps, runs);
+  for (size_t k = 0; k < devs.size(); ++k) {
+    RxDevice* d = devs[k];
+    CK(cudaSetDevice(d->ordinal));
+    auto es = std::make_shared<EventState>();
+    es->dev = d;
+    CK(cudaEventCreateWithFlags(&es->ev, cudaEventDisableTiming));
+    CK(cudaEventRecord(es->ev, d->stream));
+    for (int j = 0; j < num_results; ++j) {
+      const ResultBinding& rb = p.results[j];
+      auto* b = new RxBuffer();
+      b->st = runs[k].table[rb.slot];
+      b->dt = rb.type.dt;
+      b->dims = rb.type.shape;
+      b->dev = d;
+      results[k * num_results + j] = b;
+      if (future_results) {
+        auto* f = new RxFuture();
+        f->state = es;
+        future_results[k * num_results + j] = f;
+      }
+    }
+    // donated arguments whose storage the plan may have rewritten are dead for the caller
+    for (int i = 0; i < nargs_per_dev; ++i)
+      if (donatable && donatable[i] && p.arg_alias[i] >= 0) {
+        RxBuffer* b = args[k * nargs_per_dev + i];
+        b->donated.store(true);
+        b->st.reset();
+      }
+  }
+  if (futures) *futures = future_results ? 1 : 0;
+}
+
+RxDevice* make_device(RxClient* c, int ordinal, int local_id, double fraction) {
+  auto* d = new RxDevice();
+  d->client = c;
+  d->ordinal = ordinal;
+  d->local_id = local_id;
+  CK(cudaSetDevice(ordinal));
+  cudaDeviceProp prop;
+  CK(cudaGetDeviceProperties(&prop, ordinal));
+  d->sm_count = prop.multiProcessorCount;
+  d->total_mem = prop.totalGlobalMem;
+  d->bytes_limit = (int64_t)((double)prop.totalGlobalMem * (fraction > 0 && fraction <= 1 ? fraction : 0.9));
+  CK(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+  d->scratch_words = (size_t)1 << 20;
+  CK(cudaMalloc(&d->scratch, d->scratch_words * 4));
+  CK(cudaHostAlloc(&d->status, 64, cudaHostAllocMapped));
+  memset(d->status, 0, 64);
+  return d;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+#define API_BEGIN clear_error(); try {
+#define API_END(ret)                                  \
+  }                                                   \
+  catch (const Error& e) { report(e.code, e.what()); } \
+  catch (const std::exception& e) { report(RX_ERR_PLAN, e.what()); } \
+  return ret;
+#define API_END_VOID                                  \
+  }                                                   \
+  catch (const Error& e) { report(e.code, e.what()); } \
+  catch (const std::exception& e) { report(RX_ERR_PLAN, e.what()); }
+
+extern "C" {
+
+const char* RxLastError(void) { return g_err.c_str(); }
+int RxLastErrorCode(void) { return g_code; }
+void RxClearError(void) { clear_error(); }
+
+RxClient* MakeGPUClient(int node_id, int num_nodes, int64_t* allowed_devices, int64_t num_allowed_devices, double memory_fraction,
+                        uint8_t preallocate, const char* platform_name, const char** error, void* distributed_runtime_client) {
+  (void)preallocate; (void)platform_name; (void)distributed_runtime_client;
+  clear_error();
+  try {
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+      cudaGetLastError();
+      throw Error(RX_ERR_NO_DEVICE, std::string("no CUDA device available: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0"));
+    }
+    auto c = std::make_unique<RxClient>();
+    c->node_id = node_id;
+    c->num_nodes = num_nodes < 1 ? 1 : num_nodes;
+    std::vector<int> ords;
+    if (allowed_devices && num_allowed_devices > 0) {
+      for (int64_t i = 0; i < num_allowed_devices; ++i) {
+        if (allowed_devices[i] < 0 || allowed_devices[i] >= count) throw Error(RX_ERR_ARG, "allowed device " + std::to_string(allowed_devices[i]) + " does not exist");
+        ords.push_back((int)allowed_devices[i]);
+      }
+    } else {
+      for (int i = 0; i < count; ++i) ords.push_back(i);
+    }
+    if (ords.size() * (size_t)c->num_nodes > (size_t)kMaxRanks) throw Error(RX_ERR_ARG, "more than " + std::to_string(kMaxRanks) + " devices in the mesh");
+    for (size_t i = 0; i < ords.size(); ++i) {
+      RxDevice* d = make_device(c.get(), ords[i], (int)i, memory_fraction);
+      d->global_id = node_id * (int)ords.size() + (int)i;
+      c->devices.emplace_back(d);
+    }
+    for (int n = 0; n < c->num_nodes; ++n) {
+      if (n == node_id) continue;
+      for (size_t i = 0; i < ords.size(); ++i) {
+        auto* d = new RxDevice();
+        d->client = c.get();
+        d->addressable = false;
+        d->local_id = (int)i;
+        d->global_id = n * (int)ords.size() + (int)i;
+        c->remote.emplace_back(d);
+      }
+    }
+    const char* mode = getenv("RX_ALLREDUCE");
+    if (mode && !strcmp(mode, "nccl")) c->allreduce_mode = 1;
+    if (mode && !strcmp(mode, "mailbox")) c->allreduce_mode = 2;
+    return c.release();
+  } catch (const Error& e) {
+    g_err = e.what();
+    g_code = e.code;
+    if (error) *error = dup_cstr(e.what());
+    return nullptr;
+  }
+}
+
+void FreeClient(RxClient* client) {
+  if (!client) return;
+  clear_error();
+  rx::destroy_collectives(client);
+  for (auto& d : client->devices) {
+    cudaSetDevice(d->ordinal);
+    cudaStreamSynchronize(d->stream);
+    d->trim();
+    if (d->scratch) cudaFree(d->scratch);
+    if (d->flush_buf) cudaFree(d->flush_buf);
+    if (d->status) cudaFreeHost(d->status);
+    for (auto& s : d->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
+    cudaStreamDestroy(d->stream);
+  }
+  delete client;
+}
+
+int ClientNumDevices(RxClient* c) { return c ? c->n_global() : 0; }
+int ClientNumAddressableDevices(RxClient* c) { return c ? (int)c->devices.size() : 0; }
+int ClientProcessIndex(RxClient* c) { return c ? c->node_id : 0; }
+
+RxDevice* ClientGetDevice(RxClient* c, int id) {
+  API_BEGIN
+  if (!c) throw Error(RX_ERR_BAD_HANDLE, "null client");
+  for (auto& d : c->devices) if (d->global_id == id) return d.get();
+  for (auto& d : c->remote) if (d->global_id == id) return d.get();
+  throw Error(RX_ERR_ARG, "no device with global id " + std::to_string(id));
+  API_END(nullptr)
+}
+RxDevice* ClientGetAddressableDevice(RxClient* c, int id) {
+  API_BEGIN
+  if (!c) throw Error(RX_ERR_BAD_HANDLE, "null client");
+  if (id < 0 || id >= (int)c->devices.size()) throw Error(RX_ERR_ARG, "no addressable device " + std::to_string(id));
+  return c->devices[id].get();
+  API_END(nullptr)
+}
+void ClientGetDevices(RxClient* c, RxDevice** out) {
+  for (int i = 0; i < c->n_global(); ++i) out[i] = ClientGetDevice(c, i);
+}
+void ClientGetAddressableDevices(RxClient* c, RxDevice** out) {
+  for (size_t i = 0; i < c->devices.size(); ++i) out[i] = c->devices[i].get();
+}
+const char* ClientGetPlatformName(RxClient*) { return dup_cstr("cuda"); }
+
+RxClient* DeviceToClient(RxDevice* d) { return d ? d->client : nullptr; }
+int64_t PjRtDeviceGetLocalDeviceId(RxDevice* d) { return d->local_id; }
+int64_t PjRtDeviceGetGlobalDeviceId(RxDevice* d) { return d->global_id; }
+int64_t PjRtDeviceGetLocalHardwareId(RxDevice* d) { return d->ordinal; }
+const char* DeviceGetKind(RxDevice*) { return dup_cstr("NVIDIA B200 (sm_100a)"); }
+uint8_t pjrt_device_is_addressable(RxDevice* d) { return d && d->addressable; }
+void PjRtDeviceGetAllocatorStats(RxDevice* d, JLAllocatorStats* s) {
+  std::lock_guard<std::mutex> lk(d->mu);
+  int64_t none = INT64_MIN;
+  s->num_allocs = d->num_allocs;
+  s->bytes_in_use = d->bytes_in_use;
+  s->peak_bytes_in_use = d->peak_bytes_in_use;
+  s->largest_alloc_size = d->largest_alloc;
+  s->bytes_limit = d->bytes_limit;
+  s->bytes_reserved = d->bytes_in_use + d->pool_bytes;
+  s->peak_bytes_reserved = d->peak_bytes_in_use + d->peak_pool_bytes;
+  s->bytes_reservable_limit = none;
+  s->largest_free_block_bytes = d->pool.empty() ? 0 : (int64_t)d->pool.rbegin()->first;
+  s->pool_bytes = d->pool_bytes;
+  s->peak_pool_bytes = d->peak_pool_bytes;
+}
+
+static RxBuffer* new_buffer(RxDevice* d, uint64_t ptype, size_t ndim, const int64_t* dims) {
+  if (!d || !d->addressable) throw Error(RX_ERR_BAD_HANDLE, "device is null or not addressable from this process");
+  DT dt = (DT)ptype;
+  if (dt_size(dt) == 0) throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported primitive type code " + std::to_string(ptype));
+  auto b = std::make_unique<RxBuffer>();
+  b->dt = dt;
+  b->dev = d;
+  for (size_t i = 0; i < ndim; ++i) {
+    if (dims[i] < 0) throw Error(RX_ERR_SHAPE, "negative dimension");
+    b->dims.push_back(dims[i]);
+  }
+  size_t bytes = b->bytes();
+  b->st = std::make_shared<Storage>(d, d->alloc(bytes), bytes);
+  return b.release();
+}
+
+RxBuffer* ArrayFromHostBuffer(RxClient* client, void* data, uint64_t ptype, size_t ndim, const int64_t* dims, RxDevice* device) {
+  (void)client;
+  API_BEGIN
+  std::unique_ptr<RxBuffer> b(new_buffer(device, ptype, ndim, dims));
+  size_t bytes = b->bytes();
+  if (bytes) {
+    if (!data) throw Error(RX_ERR_ARG, "null host pointer");
+    CK(cudaSetDevice(device->ordinal));
+    CK(cudaMemcpyAsync(b->st->ptr, data, bytes, cudaMemcpyHostToDevice, device->stream));
+    CK(cudaStreamSynchronize(device->stream));  // host memory is reusable on return
+  }
+  return b.release();
+  API_END(nullptr)
+}
+
+RxBuffer* UninitPJRTBuffer(RxClient* client, RxDevice* device, uint64_t ptype, uint64_t ndim, uint64_t* dims) {
+  (void)client;
+  API_BEGIN
+  return new_buffer(device, ptype, (size_t)ndim, (const int64_t*)dims);
+  API_END(nullptr)
+}
+
+void PjRtBufferFree(RxBuffer* b) { delete b; }
+const int64_t* BufferShape(RxBuffer* b) { return b->dims.data(); }
+int64_t BufferNDimensions(RxBuffer* b) { return (int64_t)b->dims.size(); }
+int BufferPrimitiveType(RxBuffer* b) { return (int)b->dt; }
+RxDevice* BufferToDevice(RxBuffer* b) { return b->dev; }
+RxClient* BufferToClient(RxBuffer* b) { return b->dev->client; }
+uint8_t BufferOnCPU(RxBuffer*) { return 0; }
+
+static void live(RxBuffer* b) {
+  if (!b) throw Error(RX_ERR_BAD_HANDLE, "null buffer");
+  if (b->donated.load() || !b->st) throw Error(RX_ERR_DONATED, "buffer was donated to an execution and can no longer be read");
+}
+
+void BufferToHost(RxBuffer* b, void* dst) {
+  API_BEGIN
+  live(b);
+  size_t bytes = b->bytes();
+  if (bytes) {
+    CK(cudaSetDevice(b->dev->ordinal));
+    CK(cudaMemcpyAsync(dst, b->st->ptr, bytes, cudaMemcpyDeviceToHost, b->dev->stream));
+    CK(cudaStreamSynchronize(b->dev->stream));
+    if (b->dev->status[0]) {
+      int s = b->dev->status[0];
+      b->dev->status[0] = 0;
+      throw Error(RX_ERR_PEER_TIMEOUT, "a peer did not arrive at an all-reduce within the wait limit (status " + std::to_string(s) + ")");
+    }
+  }
+  API_END_VOID
+}
+
+void* UnsafeBufferPointer(RxBuffer* b) {
+  API_BEGIN
+  live(b);
+  return b->st->ptr;
+  API_END(nullptr)
+}
+
+RxBuffer* CopyBufferToDevice(RxBuffer* b, RxDevice* dst) {
+  API_BEGIN
+  live(b);
+  std::unique_ptr<RxBuffer> o(new_buffer(dst, (uint64_t)b->dt, b->dims.size(), b->dims.data()));
+  size_t bytes = b->bytes();
+  if (bytes) {
+    // order after the producer, then copy on the destination's stream
+    CK(cudaSetDevice(b->dev->ordinal));
+    cudaEvent_t ev;
+    CK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    CK(cudaEventRecord(ev, b->dev->stream));
+    CK(cudaSetDevice(dst->ordinal));
+    CK(cudaStreamWaitEvent(dst->stream, ev, 0));
+    CK(cudaMemcpyPeerAsync(o->st->ptr, dst->ordinal, b->st->ptr, b->dev->ordinal, bytes, dst->stream));
+    CK(cudaStreamSynchronize(dst->stream));
+    cudaEventDestroy(ev);
+  }
+  return o.release();
+  API_END(nullptr)
+}
+
+void CopyToBuffer(RxClient*, RxBuffer* b, void* data, size_t offset, size_t size, RxBuffer** bufferP) {
+  API_BEGIN
+  live(b);
+  if (offset + size > b->bytes()) throw Error(RX_ERR_ARG, "copy range exceeds the buffer");
+  CK(cudaSetDevice(b->dev->ordinal));
+  CK(cudaMemcpyAsync((char*)b->st->ptr + offset, data, size, cudaMemcpyHostToDevice, b->dev->stream));
+  CK(cudaStreamSynchronize(b->dev->stream));
+  if (bufferP) *bufferP = b;
+  API_END_VOID
+}
+void CopyFromBuffer(RxClient*, RxBuffer* b, void* data, size_t offset, size_t size, RxBuffer** bufferP) {
+  API_BEGIN
+  live(b);
+  if (offset + size > b->bytes()) throw Error(RX_ERR_ARG, "copy range exceeds the buffer");
+  CK(cudaSetDevice(b->dev->ordinal));
+  CK(cudaMemcpyAsync(data, (char*)b->st->ptr + offset, size, cudaMemcpyDeviceToHost, b->dev->stream));
+  CK(cudaStreamSynchronize(b->dev->stream));
+  if (bufferP) *bufferP = b;
+  API_END_VOID
+}
+
+void FreeFuture(RxFuture* f) { delete f; }
+uint8_t FutureIsReady(RxFuture* f) {
+  if (!f || !f->state) return 1;
+  cudaSetDevice(f->state->dev->ordinal);
+  return cudaEventQuery(f->state->ev) == cudaSuccess;
+}
+void FutureAwait(RxFuture* f) {
+  API_BEGIN
+  if (!f || !f->state) return;
+  RxDevice* d = f->state->dev;
+  CK(cudaSetDevice(d->ordinal));
+  CK(cudaEventSynchronize(f->state->ev));
+  if (d->status[0]) {
+    int s = d->status[0];
+    d->status[0] = 0;
+    throw Error(RX_ERR_PEER_TIMEOUT, "a peer did not arrive at an all-reduce within the wait limit (status " + std::to_string(s) + ")");
+  }
+  API_END_VOID
+}
+
+RxExecutable* ClientCompileText(RxClient* client, const char* text, size_t len, const char* opts, size_t nopts) {
+  (void)opts; (void)nopts;
+  API_BEGIN
+  if (!client) throw Error(RX_ERR_BAD_HANDLE, "null client");
+  std::string s(text, len);
+  auto mod = parse_module(s);
+  auto ex = std::make_unique<RxExecutable>();
+  ex->client = client;
+  ex->plan = build_plan(*mod);
+  if (const char* dir = getenv("RX_DUMP_PLAN")) {
+    static int counter = 0;
+    std::string path = std::string(dir) + "/plan_" + std::to_string(counter++) + ".json";
+    if (FILE* f = fopen(path.c_str(), "w")) {
+      std::string d = ex->plan->describe();
+      fwrite(d.data(), 1, d.size(), f);
+      fclose(f);
+    }
+  }
+  return ex.release();
+  API_END(nullptr)
+}
+
+const char* RxPlanDescribe(const char* text, size_t len) {
+  API_BEGIN
+  std::string s(text, len);
+  auto mod = parse_module(s);
+  auto plan = build_plan(*mod);
+  return dup_cstr(plan->describe());
+  API_END(nullptr)
+}
+
+void ExecutableFree(RxExecutable* e) { delete e; }
+RxClient* PjRtLoadedExecutableGetClient(RxExecutable* e) { return e->client; }
+int PjRtLoadedExecutableNumReplicas(RxExecutable*) { return 1; }
+int PjRtLoadedExecutableNumPartitions(RxExecutable* e) { return (int)e->plan->num_partitions; }
+int RxExecutableNumParameters(RxExecutable* e) { return (int)e->plan->arg_types.size(); }
+int RxExecutableNumResults(RxExecutable* e) { return (int)e->plan->results.size(); }
+int RxExecutableParameterShardedDim(RxExecutable* e, int i) { return e->plan->arg_sharded_dim.at(i); }
+int RxExecutableResultShardedDim(RxExecutable* e, int i) { return e->plan->results.at(i).sharded_dim; }
+int RxExecutableParameterAlias(RxExecutable* e, int i) { return e->plan->arg_alias.at(i); }
+const char* RxExecutableDescribe(RxExecutable* e) { return dup_cstr(e->plan->describe()); }
+
+void XLAExecuteSharded(RxExecutable* exec, int num_args, RxBuffer** op_args, RxDevice* device, uint8_t* is_arg_donatable, int num_results,
+                       RxBuffer** op_results, uint8_t* futures, RxFuture** future_results) {
+  API_BEGIN
+  if (!exec || !device) throw Error(RX_ERR_BAD_HANDLE, "null executable or device");
+  execute(exec, {device}, op_args, num_args, is_arg_donatable, num_results, op_results, futures, future_results);
+  API_END_VOID
+}
+
+void XLAExecute(RxExecutable* exec, int op_args_len, RxBuffer** op_args, uint8_t* is_arg_donatable, int num_results, RxBuffer** op_results,
+                uint8_t* futures, RxFuture** future_results) {
+  API_BEGIN
+  if (!exec) throw Error(RX_ERR_BAD_HANDLE, "null executable");
+  std::vector<RxDevice*> devs;
+  for (auto& d : exec->client->devices) devs.push_back(d.get());
+  if (exec->plan->num_partitions == 1) devs.resize(1);
+  int nd = (int)devs.size();
+  if (op_args_len % nd) throw Error(RX_ERR_ARG, "argument count " + std::to_string(op_args_len) + " is not a multiple of the device count " + std::to_string(nd));
+  execute(exec, devs, op_args, op_args_len / nd, is_arg_donatable, num_results, op_results, futures, future_results);
+  API_END_VOID
+}
+
+int RxCollectivesUniqueId(uint8_t* id128) {
+  API_BEGIN
+  rx::nccl_unique_id(id128);
+  return 0;
+  API_END(g_code)
+}
+int RxClientInitCollectives(RxClient* c, const uint8_t* id128) {
+  API_BEGIN
+  rx::init_nccl(c, id128);
+  return 0;
+  API_END(g_code)
+}
+int RxClientMailboxHandle(RxClient* c, int local_device, uint8_t* handle64) {
+  API_BEGIN
+  rx::mailbox_handle(c, local_device, handle64);
+  return 0;
+  API_END(g_code)
+}
+int RxClientOpenMailboxes(RxClient* c, const uint8_t* handles, int n) {
+  API_BEGIN
+  rx::open_mailboxes(c, handles, n);
+  return 0;
+  API_END(g_code)
+}
+
+RxEvent* RxEventRecord(RxDevice* d) {
+  API_BEGIN
+  auto* e = new RxEvent();
+  e->dev = d;
+  CK(cudaSetDevice(d->ordinal));
+  CK(cudaEventCreate(&e->ev));
+  CK(cudaEventRecord(e->ev, d->stream));
+  return e;
+  API_END(nullptr)
+}
+void RxEventSynchronize(RxEvent* e) {
+  API_BEGIN
+  CK(cudaSetDevice(e->dev->ordinal));
+  CK(cudaEventSynchronize(e->ev));
+  API_END_VOID
+}
+float RxEventElapsedMs(RxEvent* a, RxEvent* b) {
+  API_BEGIN
+  float ms = 0;
+  CK(cudaSetDevice(a->dev->ordinal));
+  CK(cudaEventElapsedTime(&ms, a->ev, b->ev));
+  return ms;
+  API_END(-1.f)
+}
+void RxEventFree(RxEvent* e) {
+  if (!e) return;
+  cudaSetDevice(e->dev->ordinal);
+  cudaEventDestroy(e->ev);
+  delete e;
+}
+void RxDeviceSynchronize(RxDevice* d) {
+  API_BEGIN
+  CK(cudaSetDevice(d->ordinal));
+  CK(cudaStreamSynchronize(d->stream));
+  API_END_VOID
+}
+uint64_t RxDeviceKernelLaunches(RxDevice* d) { return d->launches; }
+void RxDeviceSetProfiling(RxDevice* d, int on) { d->profiling = on != 0; }
+const char* RxDeviceProfileJson(RxDevice* d) {
+  API_BEGIN
+  CK(cudaSetDevice(d->ordinal));
+  CK(cudaStreamSynchronize(d->stream));
+  for (auto& s : d->spans) {
+    float ms = 0;
+    cudaEventElapsedTime(&ms, s.a, s.b);
+    auto& p = d->prof[s.kind];
+    p.first += 1;
+    p.second += ms;
+    cudaEventDestroy(s.a);
+    cudaEventDestroy(s.b);
+  }
+  d->spans.clear();
+  std::ostringstream os;
+  os << "{";
+  bool first = true;
+  for (auto& kv : d->prof) {
+    os << (first ? "" : ",") << "\"" << kv.first << "\":{\"launches\":" << kv.second.first << ",\"ms\":" << kv.second.second << "}";
+    first = false;
+  }
+  os << "}";
+  d->prof.clear();
+  return dup_cstr(os.str());
+  API_END(nullptr)
+}
+void* RxDeviceStream(RxDevice* d) { return (void*)d->stream; }
+void RxDeviceFlushL2(RxDevice* d) {
+  API_BEGIN
+  CK(cudaSetDevice(d->ordinal));
+  if (!d->flush_buf) {
+    d->flush_bytes = (size_t)256 << 20;
+    CK(cudaMalloc(&d->flush_buf, d->flush_bytes));
+  }
+  CK(cudaMemsetAsync(d->flush_buf, 0, d->flush_bytes, d->stream));
+  API_END_VOID
+}
+
+}  // extern "C"

@@ -1,0 +1,127 @@
+// Runtime objects behind the C ABI: client, devices with their stream-ordered
+// memory pools, reference-counted buffer storage, futures and executables.
+// They stand in for the PjRt objects Reactant's wrapper structs hold
+// (src/xla/PJRT/{Client,Device,Buffer,Future,LoadedExecutable}.jl).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "rx_ir.h"
+#include "rx_kernels.h"
+#include "rx_plan.h"
+
+struct RxClient;
+
+constexpr int kMaxRanks = 32;
+
+// Peer mailboxes for the NVLink all-reduce: slot [parity][rank] of every device.
+struct MailTable {
+  unsigned long long* peer[kMaxRanks];
+};
+
+struct RxDevice {
+  RxClient* client = nullptr;
+  int ordinal = 0;    // CUDA device ordinal
+  int local_id = 0;   // index among this process's devices
+  int global_id = 0;  // index in the mesh
+  bool addressable = true;
+  cudaStream_t stream = nullptr;
+  int sm_count = 148;
+  size_t total_mem = 0;
+  // memory pool (exact-size free lists, stream ordered on `stream`)
+  std::mutex mu;
+  std::map<size_t, std::vector<void*>> pool;
+  int64_t num_allocs = 0, bytes_in_use = 0, peak_bytes_in_use = 0, largest_alloc = 0, bytes_limit = 0, pool_bytes = 0, peak_pool_bytes = 0;
+  uint32_t* scratch = nullptr;
+  size_t scratch_words = 0;
+  uint64_t launches = 0;
+  // profiling
+  bool profiling = false;
+  struct Span { std::string kind; cudaEvent_t a, b; };
+  std::vector<Span> spans;
+  std::map<std::string, std::pair<int64_t, double>> prof;
+  void* flush_buf = nullptr;
+  size_t flush_bytes = 0;
+  // NVLink mailbox
+  unsigned long long* mailbox = nullptr;  // [2][kMaxRanks]
+  int* status = nullptr;                  // device-visible status word (pinned host memory)
+  MailTable mail{};
+  bool mail_ready = false;
+  std::map<const void*, std::vector<uint8_t>> tmaps;  // tensor-map cache keyed by base pointer
+
+  void* alloc(size_t bytes);
+  void release(void* p, size_t bytes);
+  void trim();
+  rx::LaunchCtx ctx() {
+    rx::LaunchCtx c;
+    c.stream = stream;
+    c.sm_count = sm_count;
+    c.scratch = scratch;
+    c.scratch_words = scratch_words;
+    c.launches = &launches;
+    return c;
+  }
+};
+
+struct Storage {
+  RxDevice* dev;
+  void* ptr;
+  size_t bytes;
+  Storage(RxDevice* d, void* p, size_t b) : dev(d), ptr(p), bytes(b) {}
+  ~Storage() { dev->release(ptr, bytes); }
+};
+
+struct RxBuffer {
+  std::shared_ptr<Storage> st;
+  rx::DT dt;
+  std::vector<int64_t> dims;
+  RxDevice* dev;
+  std::atomic<bool> donated{false};
+  size_t bytes() const {
+    size_t n = rx::dt_size(dt);
+    for (auto d : dims) n *= (size_t)d;
+    return n;
+  }
+};
+
+struct EventState {
+  cudaEvent_t ev = nullptr;
+  RxDevice* dev = nullptr;
+  ~EventState();
+};
+
+struct RxFuture {
+  std::shared_ptr<EventState> state;
+};
+
+struct RxEvent {
+  cudaEvent_t ev = nullptr;
+  RxDevice* dev = nullptr;
+};
+
+struct RxExecutable {
+  RxClient* client = nullptr;
+  std::unique_ptr<rx::Plan> plan;
+  std::mutex mu;
+  std::map<int, std::map<int, std::shared_ptr<Storage>>> consts;  // [local device][slot]
+};
+
+struct RxClient {
+  int node_id = 0, num_nodes = 1;
+  std::vector<std::unique_ptr<RxDevice>> devices;     // addressable devices
+  std::vector<std::unique_ptr<RxDevice>> remote;      // placeholders for other processes' devices
+  std::mutex mu;
+  // NCCL
+  void* nccl_comms[kMaxRanks] = {};
+  bool nccl_ready = false;
+  bool peers_enabled = false;
+  uint32_t epoch = 0;       // all-reduce sequence number (same on every rank)
+  int allreduce_mode = 0;   // 0 auto, 1 nccl, 2 mailbox
+  int n_global() const { return (int)devices.size() * num_nodes; }
+};

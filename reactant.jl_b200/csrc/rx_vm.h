@@ -1,0 +1,94 @@
+// Fused-elementwise micro-program: the planner compiles a chain of StableHLO
+// elementwise ops (the body of a fusion group) into this register bytecode and
+// every map / map-reduce / stencil / GEMM-epilogue kernel evaluates it per
+// element.  Well-known chains are additionally recognised by `fast_id` and run
+// through compile-time-fused functors instead of the interpreter.
+//
+// The op set mirrors the scalar emitters of Reactant (src/Ops.jl:398-460 unary,
+// :536-589 binary, :1865-1961 select/compare/convert).
+#pragma once
+#include <stdint.h>
+
+namespace rx {
+
+enum VmOp : uint8_t {
+  VM_NOP = 0,
+  VM_CONST,   // dst = imm (raw 32 bits)
+  VM_MOV,
+  // f32 unary
+  VM_NEG, VM_SIN, VM_COS, VM_EXP, VM_LOG, VM_TANH, VM_SQRT, VM_RSQRT, VM_ABS,
+  VM_LOG1P, VM_EXPM1, VM_FLOOR, VM_CEIL, VM_SIGN, VM_LOGISTIC,
+  VM_RBF16,   // round f32 to the nearest bf16 value (ties to even)
+  // f32 binary
+  VM_ADD, VM_SUB, VM_MUL, VM_DIV, VM_MAX, VM_MIN, VM_POW,
+  // i32 arithmetic
+  VM_IADD, VM_ISUB, VM_IMUL, VM_IDIV, VM_IMAX, VM_IMIN, VM_INEG, VM_IABS,
+  VM_AND, VM_OR, VM_XOR, VM_NOT,   // bitwise on raw 32 bits
+  VM_LNOT,                          // logical not on a 0/1 predicate
+  // comparisons -> 0/1 ; `c` = direction
+  VM_FCMP, VM_ICMP,
+  VM_SELECT,  // dst = a ? b : c
+  // conversions
+  VM_I2F, VM_F2I, VM_P2F /* pred->f32 */, VM_F2P /* f32 != 0 */, VM_I2P,
+  VM_IOTA,    // dst = index along root dim `a` (as i32)
+  VM_NUM_OPS
+};
+
+enum VmCmp : uint8_t { CMP_EQ = 0, CMP_NE, CMP_LT, CMP_LE, CMP_GT, CMP_GE };
+
+// storage element kinds a kernel can load/store
+enum VmElem : uint8_t { EL_F32 = 0, EL_BF16, EL_I32, EL_PRED /* 1 byte */, EL_I64, EL_F64 };
+
+struct VmInstr {
+  uint8_t op, dst, a, b, c, pad[3];
+  uint32_t imm;
+};
+
+constexpr int kVmMaxInstr = 48;
+constexpr int kVmMaxRegs = 24;
+constexpr int kVmMaxLeaves = 8;
+constexpr int kVmMaxOuts = 4;
+constexpr int kMaxRank = 4;
+
+// Known chains with compile-time-fused implementations.
+enum FastId : int32_t {
+  FAST_NONE = 0,
+  FAST_SIN_ADD,        // sin(l0) + l1          (README sinsum_add)
+  FAST_IDENTITY,       // l0
+  FAST_EXP_SUB,        // exp(l0 - l1)
+  FAST_STENCIL5_MUL,   // ((((l0+l1)+l2)+l3)+l4) * c   (Jacobi-2D)
+};
+
+struct VmLeaf {
+  const void* ptr;
+  int64_t offset;             // in elements
+  int64_t stride[kMaxRank];   // in elements, per collapsed root dim
+  uint8_t elem;               // VmElem
+  uint8_t reg;                // destination register
+  uint8_t linear;             // 1: contiguous in the root linear index; 2: scalar broadcast
+  uint8_t pad[5];
+};
+
+struct VmOut {
+  void* ptr;
+  int64_t offset;
+  int64_t stride[kMaxRank];
+  uint8_t elem;
+  uint8_t reg;                // register holding the value
+  uint8_t linear;
+  uint8_t pad[5];
+};
+
+struct VmProgram {
+  int32_t n_instr, n_leaves, n_outs, fast_id;
+  int32_t rank;               // collapsed root rank (<= kMaxRank)
+  int32_t all_linear;         // every leaf/out is linear or scalar
+  int64_t dim[kMaxRank];      // collapsed root dims, row-major
+  float fast_c;               // constant of the fast chain, if any
+  int32_t result_reg;         // register reduced / handed to an epilogue
+  VmLeaf leaf[kVmMaxLeaves];
+  VmOut out[kVmMaxOuts];
+  VmInstr ins[kVmMaxInstr];
+};
+
+}  // namespace rx

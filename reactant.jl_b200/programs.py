@@ -1,0 +1,230 @@
+"""StableHLO module text for the benchmark configurations, in the form Reactant
+hands to its runtime: `func.func @main` over reversed-dim tensors, printed by
+MLIR's default printer.
+
+Reactant's tracer and pass pipeline cannot run where this engine is built (no
+Julia), so these are written out by hand from the op emitters:
+  sum / maximum  -> stablehlo.reduce       src/TracedRArray.jl:187-230, src/Ops.jl:3491-3622
+  broadcasting   -> elementwise ops        src/TracedUtils.jl:1202-1352
+  A[r, c]        -> stablehlo.slice        src/Indexing.jl:552-627, src/Ops.jl:761-793
+  B[r, c] = v    -> dynamic_update_slice   src/Indexing.jl:350-446, src/Ops.jl:3662-3678
+  @trace for     -> stablehlo.while        src/Ops.jl:2349-2447
+  W * X          -> stablehlo.dot_general  src/stdlibs/LinearAlgebra.jl:274-330
+  sharding attrs -> sdy.mesh / sdy.sharding src/Sharding.jl:512-575
+Each generator offers the optimised form (`raw=False`: layout transposes already
+propagated away) and, where it differs, the raw trace form (`raw=True`: every
+argument and result wrapped in the reversed-dims transposes of
+src/TracedUtils.jl:608-626).
+"""
+from __future__ import annotations
+
+import math
+
+
+def _t(shape, et="f32"):
+    return "tensor<" + "".join(f"{d}x" for d in shape) + et + ">"
+
+
+def sinsum_add(n: int, raw: bool = False, num_partitions: int = 1) -> str:
+    """f(x, y) = sum(sin.(x) .+ y) on Float32 vectors of length n.
+    With num_partitions > 1 both vectors are sharded along a 1-D mesh "x"."""
+    t = _t([n])
+    shard = ' {sdy.sharding = #sdy.sharding<@mesh, [{"x"}]>}' if num_partitions > 1 else ""
+    mesh = f'  sdy.mesh @mesh = <["x"={num_partitions}]>\n' if num_partitions > 1 else ""
+    body = []
+    x, y = "%arg0", "%arg1"
+    if raw:
+        body.append(f"    %t0 = stablehlo.transpose %arg0, dims = [0] : ({t}) -> {t}")
+        body.append(f"    %t1 = stablehlo.transpose %arg1, dims = [0] : ({t}) -> {t}")
+        x, y = "%t0", "%t1"
+    body += [
+        "    %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>",
+        f"    %0 = stablehlo.sine {x} : {t}",
+        f"    %1 = stablehlo.add %0, {y} : {t}",
+        f"    %2 = stablehlo.reduce(%1 init: %cst) applies stablehlo.add across dimensions = [0] : ({t}, tensor<f32>) -> tensor<f32>",
+        "    return %2 : tensor<f32>",
+    ]
+    return (f"module @reactant_sinsum_add attributes {{mhlo.num_partitions = {num_partitions} : i64, mhlo.num_replicas = 1 : i64}} {{\n"
+            f"{mesh}  func.func @main(%arg0: {t}{shard}, %arg1: {t}{shard}) -> tensor<f32> {{\n" + "\n".join(body) + "\n  }\n}\n")
+
+
+def logsumexp_dims1(rows: int, cols: int, raw: bool = False) -> str:
+    """m = maximum(x; dims=1); m .+ log.(sum(exp.(x .- m); dims=1)) for a Julia
+    rows x cols Float32 matrix (argument tensor is cols x rows)."""
+    ta, tc, tr = _t([cols, rows]), _t([cols]), _t([cols, 1])
+    if not raw:
+        body = f"""    %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %cst_0 = stablehlo.constant dense<0xFF800000> : tensor<f32>
+    %0 = stablehlo.reduce(%arg0 init: %cst_0) applies stablehlo.maximum across dimensions = [1] : ({ta}, tensor<f32>) -> {tc}
+    %1 = stablehlo.broadcast_in_dim %0, dims = [0] : ({tc}) -> {ta}
+    %2 = stablehlo.subtract %arg0, %1 : {ta}
+    %3 = stablehlo.exponential %2 : {ta}
+    %4 = stablehlo.reduce(%3 init: %cst) applies stablehlo.add across dimensions = [1] : ({ta}, tensor<f32>) -> {tc}
+    %5 = stablehlo.log %4 : {tc}
+    %6 = stablehlo.add %0, %5 : {tc}
+    %7 = stablehlo.reshape %6 : ({tc}) -> {tr}
+    return %7 : {tr}"""
+    else:
+        tl, t1 = _t([rows, cols]), _t([1, cols])
+        body = f"""    %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %cst_0 = stablehlo.constant dense<0xFF800000> : tensor<f32>
+    %0 = stablehlo.transpose %arg0, dims = [1, 0] : ({ta}) -> {tl}
+    %1 = stablehlo.reduce(%0 init: %cst_0) applies stablehlo.maximum across dimensions = [0] : ({tl}, tensor<f32>) -> {tc}
+    %2 = stablehlo.reshape %1 : ({tc}) -> {t1}
+    %3 = stablehlo.broadcast_in_dim %2, dims = [0, 1] : ({t1}) -> {tl}
+    %4 = stablehlo.subtract %0, %3 : {tl}
+    %5 = stablehlo.exponential %4 : {tl}
+    %6 = stablehlo.reduce(%5 init: %cst) applies stablehlo.add across dimensions = [0] : ({tl}, tensor<f32>) -> {tc}
+    %7 = stablehlo.reshape %6 : ({tc}) -> {t1}
+    %8 = stablehlo.log %7 : {t1}
+    %9 = stablehlo.add %2, %8 : {t1}
+    %10 = stablehlo.transpose %9, dims = [1, 0] : ({t1}) -> {tr}
+    return %10 : {tr}"""
+    return ("module @reactant_logsumexp attributes {mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64} {\n"
+            f"  func.func @main(%arg0: {ta}) -> {tr} {{\n{body}\n  }}\n}}\n")
+
+
+def jacobi2d(n: int, steps: int, form: str = "dus") -> str:
+    """`steps` sweeps of B[2:end-1,2:end-1] = 0.2f0 .* (A[c] .+ A[n] .+ A[s] .+ A[w] .+ A[e]); A, B = B, A
+    on n x n Float32 arrays (benchmark/polybench/stencil.jl:263-289 spelling).
+    Both arrays are mutated, hence donated and aliased to the two results.
+    form="dus": interior written by dynamic_update_slice; form="pad": the
+    pad + select rewrite that Enzyme-JAX's communication patterns can produce
+    (src/compiler/OptimizationPasses.jl:356-372)."""
+    t, ti = _t([n, n]), _t([n - 2, n - 2])
+    m = n - 1
+    # physical dims are reversed Julia dims: Julia A[i-1, j] is the minor-dim neighbour
+    sl = [f"[1:{m}, 1:{m}]", f"[1:{m}, 0:{n - 2}]", f"[1:{m}, 2:{n}]", f"[0:{n - 2}, 1:{m}]", f"[2:{n}, 1:{m}]"]
+    lines = [f"      %s{k} = stablehlo.slice %iterArg_0 {s} : ({t}) -> {ti}" for k, s in enumerate(sl)]
+    lines += [
+        f"      %a0 = stablehlo.add %s0, %s1 : {ti}",
+        f"      %a1 = stablehlo.add %a0, %s2 : {ti}",
+        f"      %a2 = stablehlo.add %a1, %s3 : {ti}",
+        f"      %a3 = stablehlo.add %a2, %s4 : {ti}",
+        f"      %u = stablehlo.multiply %cst, %a3 : {ti}",
+    ]
+    if form == "dus":
+        lines.append(f"      %nb = stablehlo.dynamic_update_slice %iterArg_1, %u, %c_1, %c_1 : ({t}, {ti}, tensor<i32>, tensor<i32>) -> {t}")
+    else:
+        lines += [
+            f"      %pu = stablehlo.pad %u, %cst_z, low = [1, 1], high = [1, 1], interior = [0, 0] : ({ti}, tensor<f32>) -> {t}",
+            f"      %nb = stablehlo.select %pm, %pu, %iterArg_1 : {_t([n, n], 'i1')}, {t}",
+        ]
+    body = "\n".join(lines)
+    extra = ""
+    if form != "dus":
+        extra = (f"    %cst_z = stablehlo.constant dense<0.000000e+00> : tensor<f32>\n"
+                 f"    %false = stablehlo.constant dense<false> : tensor<i1>\n"
+                 f"    %ones = stablehlo.constant dense<true> : {_t([n - 2, n - 2], 'i1')}\n"
+                 f"    %pm = stablehlo.pad %ones, %false, low = [1, 1], high = [1, 1], interior = [0, 0] : ({_t([n - 2, n - 2], 'i1')}, tensor<i1>) -> {_t([n, n], 'i1')}\n")
+    return f"""module @reactant_jacobi2d attributes {{mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64}} {{
+  func.func @main(%arg0: {t} {{tf.aliasing_output = 0 : i32}}, %arg1: {t} {{tf.aliasing_output = 1 : i32}}) -> ({t}, {t}) {{
+    %c = stablehlo.constant dense<0> : tensor<i64>
+    %c_0 = stablehlo.constant dense<{steps}> : tensor<i64>
+    %c_2 = stablehlo.constant dense<1> : tensor<i64>
+    %c_1 = stablehlo.constant dense<1> : tensor<i32>
+    %cst = stablehlo.constant dense<2.000000e-01> : {ti}
+{extra}    %0:3 = stablehlo.while(%iterArg = %c, %iterArg_0 = %arg0, %iterArg_1 = %arg1) : tensor<i64>, {t}, {t} attributes {{enzyme.disable_mincut}}
+     cond {{
+      %1 = stablehlo.compare  LT, %iterArg, %c_0 : (tensor<i64>, tensor<i64>) -> tensor<i1>
+      stablehlo.return %1 : tensor<i1>
+    }} do {{
+      %1 = stablehlo.add %iterArg, %c_2 : tensor<i64>
+{body}
+      stablehlo.return %1, %nb, %iterArg_0 : tensor<i64>, {t}, {t}
+    }}
+    return %0#1, %0#2 : {t}, {t}
+  }}
+}}
+"""
+
+
+def mlp_grad(features: int = 1024, hidden: int = 4096, out: int = 1024, batch: int = 4096) -> str:
+    """Two-layer MLP forward + reverse-mode gradient, as it reaches the runtime
+    after Enzyme's pass has synthesised the reverse program: five dot_generals
+    (two forward, three transposed-operand backward), gelu(tanh) and its
+    derivative as elementwise chains, bias gradients as column reductions.
+
+    Julia shapes: W1 hidden x features (bf16), b1 hidden (f32), W2 out x hidden
+    (bf16), b2 out (f32), X features x batch (bf16), Y out x batch (f32).
+    Results: dW1, db1, dW2, db2, loss.
+    """
+    F, H, O, B = features, hidden, out, batch
+    tW1, tW2, tX, tY = _t([F, H], "bf16"), _t([H, O], "bf16"), _t([B, F], "bf16"), _t([B, O])
+    tb1, tb2 = _t([H]), _t([O])
+    tZ1b, tZ1 = _t([B, H], "bf16"), _t([B, H])
+    tZ2b, tZ2 = _t([B, O], "bf16"), _t([B, O])
+    c = math.sqrt(2.0 / math.pi)
+    inv = 1.0 / (B * O)
+
+    def k(v, t):
+        return f"stablehlo.constant dense<{v:.9e}> : {t}"
+
+    return f"""module @reactant_mlp_grad attributes {{mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64}} {{
+  func.func @main(%arg0: {tW1}, %arg1: {tb1}, %arg2: {tW2}, %arg3: {tb2}, %arg4: {tX}, %arg5: {tY}) -> ({tW1}, {tb1}, {tW2}, {tb2}, tensor<f32>) {{
+    %zero = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %half = {k(0.5, tZ1)}
+    %one = {k(1.0, tZ1)}
+    %ca = {k(0.044715, tZ1)}
+    %c3a = {k(3 * 0.044715, tZ1)}
+    %cc = {k(c, tZ1)}
+    %cinv = {k(inv, "tensor<f32>")}
+    %c2inv = {k(2 * inv, tZ2)}
+    %0 = stablehlo.dot_general %arg4, %arg0, contracting_dims = [1] x [0], precision = [DEFAULT, DEFAULT] : ({tX}, {tW1}) -> {tZ1b}
+    %1 = stablehlo.convert %0 : ({tZ1b}) -> {tZ1}
+    %2 = stablehlo.broadcast_in_dim %arg1, dims = [1] : ({tb1}) -> {tZ1}
+    %z1 = stablehlo.add %1, %2 : {tZ1}
+    %z1sq = stablehlo.multiply %z1, %z1 : {tZ1}
+    %z1cu = stablehlo.multiply %z1sq, %z1 : {tZ1}
+    %3 = stablehlo.multiply %ca, %z1cu : {tZ1}
+    %4 = stablehlo.add %z1, %3 : {tZ1}
+    %5 = stablehlo.multiply %cc, %4 : {tZ1}
+    %th = stablehlo.tanh %5 : {tZ1}
+    %6 = stablehlo.add %one, %th : {tZ1}
+    %7 = stablehlo.multiply %half, %z1 : {tZ1}
+    %h = stablehlo.multiply %7, %6 : {tZ1}
+    %hb = stablehlo.convert %h : ({tZ1}) -> {tZ1b}
+    %8 = stablehlo.dot_general %hb, %arg2, contracting_dims = [1] x [0], precision = [DEFAULT, DEFAULT] : ({tZ1b}, {tW2}) -> {tZ2b}
+    %9 = stablehlo.convert %8 : ({tZ2b}) -> {tZ2}
+    %10 = stablehlo.broadcast_in_dim %arg3, dims = [1] : ({tb2}) -> {tZ2}
+    %z2 = stablehlo.add %9, %10 : {tZ2}
+    %d = stablehlo.subtract %z2, %arg5 : {tZ2}
+    %dd = stablehlo.multiply %d, %d : {tZ2}
+    %11 = stablehlo.reduce(%dd init: %zero) applies stablehlo.add across dimensions = [0, 1] : ({tZ2}, tensor<f32>) -> tensor<f32>
+    %loss = stablehlo.multiply %11, %cinv : tensor<f32>
+    %dz2 = stablehlo.multiply %c2inv, %d : {tZ2}
+    %db2 = stablehlo.reduce(%dz2 init: %zero) applies stablehlo.add across dimensions = [0] : ({tZ2}, tensor<f32>) -> {tb2}
+    %dz2b = stablehlo.convert %dz2 : ({tZ2}) -> {tZ2b}
+    %dw2 = stablehlo.dot_general %hb, %dz2b, contracting_dims = [0] x [0], precision = [DEFAULT, DEFAULT] : ({tZ1b}, {tZ2b}) -> {tW2}
+    %dhb = stablehlo.dot_general %dz2b, %arg2, contracting_dims = [1] x [1], precision = [DEFAULT, DEFAULT] : ({tZ2b}, {tW2}) -> {tZ1b}
+    %dh = stablehlo.convert %dhb : ({tZ1b}) -> {tZ1}
+    %12 = stablehlo.multiply %th, %th : {tZ1}
+    %13 = stablehlo.subtract %one, %12 : {tZ1}
+    %14 = stablehlo.multiply %c3a, %z1sq : {tZ1}
+    %15 = stablehlo.add %one, %14 : {tZ1}
+    %16 = stablehlo.multiply %cc, %15 : {tZ1}
+    %17 = stablehlo.multiply %13, %16 : {tZ1}
+    %18 = stablehlo.multiply %7, %17 : {tZ1}
+    %19 = stablehlo.multiply %half, %6 : {tZ1}
+    %gp = stablehlo.add %19, %18 : {tZ1}
+    %dz1 = stablehlo.multiply %dh, %gp : {tZ1}
+    %db1 = stablehlo.reduce(%dz1 init: %zero) applies stablehlo.add across dimensions = [0] : ({tZ1}, tensor<f32>) -> {tb1}
+    %dz1b = stablehlo.convert %dz1 : ({tZ1}) -> {tZ1b}
+    %dw1 = stablehlo.dot_general %arg4, %dz1b, contracting_dims = [0] x [0], precision = [DEFAULT, DEFAULT] : ({tX}, {tZ1b}) -> {tW1}
+    return %dw1, %db1, %dw2, %db2, %loss : {tW1}, {tb1}, {tW2}, {tb2}, tensor<f32>
+  }}
+}}
+"""
+
+
+def matmul(m: int, k: int, n: int, et: str = "f32") -> str:
+    """C = A * B for Julia A (m x k), B (k x n): the arguments arrive as k x m and
+    n x k tensors and the product as n x m (test/core/compile.jl:350-355)."""
+    ta, tb, tc = _t([k, m], et), _t([n, k], et), _t([n, m], et)
+    return f"""module @reactant_matmul attributes {{mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64}} {{
+  func.func @main(%arg0: {ta}, %arg1: {tb}) -> {tc} {{
+    %0 = stablehlo.dot_general %arg1, %arg0, contracting_dims = [1] x [0], precision = [DEFAULT, DEFAULT] : ({tb}, {ta}) -> {tc}
+    return %0 : {tc}
+  }}
+}}
+"""

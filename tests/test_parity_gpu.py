@@ -1,0 +1,294 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI (ctypes).
+
+Bars (from the benchmark contract): bit-exact for indexing / slicing / integer
+work; fp32 reductions within 1e-5*sqrt(log2 n) relative to the float64 result
+(relative to the 2-norm of the terms where the sum itself is ill-conditioned);
+bf16 dot_general within 2e-2 of the fp32 result.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+NP = {"f64": np.float64, "f32": np.float32, "i32": np.int32, "i1": np.bool_}
+
+
+def run(rx, client, text, inputs_xla, **kw):
+    """inputs in the boundary layout (row-major over the tensor dims)."""
+    f = rx.compile(text, client)
+    args = [rx.to_rarray(np.asarray(a).T, client) for a in inputs_xla]
+    out = f(*args, **kw)
+    outs = out if isinstance(out, tuple) else (out,)
+    return [np.asarray(o).T for o in outs], f, args
+
+
+# ---------------------------------------------------------------- sinsum (C1)
+@pytest.mark.parametrize("n", [1, 3, 127, 4096, (1 << 20) + 1, 1 << 24])
+@pytest.mark.parametrize("raw", [False, True])
+def test_sinsum_add(rx, ref, client, n, raw):
+    rng = np.random.default_rng(n)
+    x = rng.uniform(-np.pi, np.pi, n).astype(np.float32)
+    y = rng.uniform(-np.pi, np.pi, n).astype(np.float32)
+    text = rx.programs.sinsum_add(n, raw=raw)
+    (got,), f, args = run(rx, client, text, [x, y])
+    terms = np.sin(x.astype(np.float64)) + y.astype(np.float64)
+    want = terms.sum()
+    tol = ref.reduction_tolerance(n)
+    assert abs(float(got) - want) <= tol * max(abs(want), np.linalg.norm(terms)), (float(got), want)
+    # deterministic two-pass combine: same bits on a second run
+    again = np.asarray(f(*args)).T
+    assert again.tobytes() == np.asarray(got).tobytes()
+
+
+def test_sinsum_large_arguments_take_the_slow_range_reduction(rx, ref, client):
+    n = 10007
+    rng = np.random.default_rng(5)
+    x = (rng.uniform(-1, 1, n) * 1e6).astype(np.float32)
+    y = np.zeros(n, np.float32)
+    (got,), _, _ = run(rx, client, rx.programs.sinsum_add(n), [x, y])
+    terms = np.sin(x.astype(np.float64))
+    assert abs(float(got) - terms.sum()) <= 1e-5 * np.linalg.norm(terms) * 4
+
+
+# ---------------------------------------------------------------- generic chains
+def module(args, results, body):
+    a = ", ".join(f"%arg{i}: {t}" for i, t in enumerate(args))
+    return f"module {{\n  func.func @main({a}) -> ({', '.join(results)}) {{\n{body}\n  }}\n}}\n"
+
+
+def test_generic_map_chain(rx, ref, client):
+    n = 100003
+    t = f"tensor<{n}xf32>"
+    text = module([t, t], [t], f"""    %c = stablehlo.constant dense<2.500000e+00> : {t}
+    %0 = stablehlo.tanh %arg0 : {t}
+    %1 = stablehlo.multiply %0, %arg1 : {t}
+    %2 = stablehlo.add %1, %c : {t}
+    %3 = stablehlo.exponential %arg1 : {t}
+    %4 = stablehlo.maximum %2, %3 : {t}
+    %5 = stablehlo.compare  GT, %arg0, %arg1 : ({t}, {t}) -> tensor<{n}xi1>
+    %6 = stablehlo.select %5, %4, %arg0 : tensor<{n}xi1>, {t}
+    return %6 : {t}""")
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal(n).astype(np.float32)
+    y = rng.standard_normal(n).astype(np.float32)
+    (got,), _, _ = run(rx, client, text, [x, y])
+    want = ref.run_module(text, [x, y])[0]
+    np.testing.assert_allclose(got, want, rtol=4e-6, atol=1e-7)
+
+
+def test_generic_reduce_chain_and_strided_operands(rx, ref, client):
+    # sum(x .* x') : one operand is read transposed
+    t = "tensor<37x37xf32>"
+    text = module([t], ["tensor<f32>"], f"""    %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %0 = stablehlo.transpose %arg0, dims = [1, 0] : ({t}) -> {t}
+    %1 = stablehlo.multiply %arg0, %0 : {t}
+    %2 = stablehlo.reduce(%1 init: %cst) applies stablehlo.add across dimensions = [0, 1] : ({t}, tensor<f32>) -> tensor<f32>
+    return %2 : tensor<f32>""")
+    x = np.random.default_rng(8).standard_normal((37, 37)).astype(np.float32)
+    (got,), _, _ = run(rx, client, text, [x])
+    want = ref.run_module(text, [x])[0]
+    np.testing.assert_allclose(got, want, rtol=2e-5)
+
+
+@pytest.mark.parametrize("dims,keep", [([1], "96x40"), ([0], "64x40"), ([2], "96x64"), ([0, 1], "40"), ([1, 2], "96"), ([0, 1, 2], "")])
+@pytest.mark.parametrize("kind,init", [("add", "0.000000e+00"), ("maximum", "0xFF800000")])
+def test_axis_reductions(rx, ref, client, dims, keep, kind, init):
+    t = "tensor<96x64x40xf32>"
+    tr = f"tensor<{keep + 'x' if keep else ''}f32>"
+    text = module([t], [tr], f"""    %cst = stablehlo.constant dense<{init}> : tensor<f32>
+    %0 = stablehlo.cosine %arg0 : {t}
+    %1 = stablehlo.reduce(%0 init: %cst) applies stablehlo.{kind} across dimensions = {dims} : ({t}, tensor<f32>) -> {tr}
+    return %1 : {tr}""")
+    x = np.random.default_rng(9).standard_normal((96, 64, 40)).astype(np.float32)
+    (got,), _, _ = run(rx, client, text, [x])
+    want = ref.run_module(text, [x])[0]
+    np.testing.assert_allclose(got, want, rtol=3e-5, atol=3e-5)
+
+
+with open(os.path.join(HERE, "golden", "reactant_fixtures.json")) as f:
+    CASES = [c for c in json.load(f)["cases"] if c["element_type"] != "f64" and "sharded" not in c["name"]]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_reference_fixtures_through_the_engine(rx, ref, client, case):
+    mod = ref.parse_module(case["module"])
+    ins = [np.array(s["data"], dtype=NP[et]).reshape(s["dims"]) for (_, (_, et)), s in zip(mod["funcs"]["main"].args, case["inputs"])]
+    got, _, _ = run(rx, client, case["module"], ins)
+    for g, e in zip(got, case["expected"]):
+        want = np.array(e["data"], dtype=np.float64).reshape(e["dims"])
+        assert list(g.shape) == e["dims"]
+        if case["rtol"] == 0.0:
+            assert np.array_equal(g, want.astype(g.dtype))
+        else:
+            np.testing.assert_allclose(g.astype(np.float64), want, rtol=max(case["rtol"], 4e-6))
+
+
+# ---------------------------------------------------------------- logsumexp (C2)
+@pytest.mark.parametrize("rows,cols", [(1, 1), (7, 3), (1000, 17), (4096, 8), (2049, 5), (32768, 64)])
+@pytest.mark.parametrize("raw", [False, True])
+def test_logsumexp_dims1(rx, ref, client, rows, cols, raw):
+    x = np.random.default_rng(rows * 31 + cols).standard_normal((cols, rows)).astype(np.float32)
+    text = rx.programs.logsumexp_dims1(rows, cols, raw=raw)
+    (got,), f, _ = run(rx, client, text, [x])
+    assert [s["kind"] for s in f.describe()["steps"]] == ["logsumexp"]
+    want = ref.run_module(text, [x])[0]
+    assert got.shape == want.shape == (cols, 1)
+    np.testing.assert_allclose(got, want, rtol=ref.reduction_tolerance(rows))
+
+
+def test_logsumexp_with_infinities(rx, ref, client):
+    rows, cols = 300, 4
+    x = np.random.default_rng(2).standard_normal((cols, rows)).astype(np.float32)
+    x[0, 5] = -np.inf
+    x[1, :] = -np.inf
+    x[1, 7] = 1.5
+    x[2, 9] = 80.0
+    x[3, 0] = np.inf
+    text = rx.programs.logsumexp_dims1(rows, cols)
+    (got,), _, _ = run(rx, client, text, [x])
+    with np.errstate(all="ignore"):
+        want = ref.run_module(text, [x])[0]
+    np.testing.assert_allclose(got[:3], want[:3], rtol=1e-5)
+    assert np.isnan(got[3, 0]) and np.isnan(want[3, 0])  # inf - inf inside the op sequence
+
+
+def test_logsumexp_full_size_against_c_oracle(rx, ref, cpu, client):
+    rows, cols = 32768, 8192
+    x = np.random.default_rng(3).standard_normal((cols, rows), dtype=np.float32)
+    (got,), _, _ = run(rx, client, rx.programs.logsumexp_dims1(rows, cols), [x])
+    want = cpu.logsumexp_dims1(x)
+    np.testing.assert_allclose(got.reshape(-1), want, rtol=ref.reduction_tolerance(rows))
+    # shift invariance: logsumexp(x + c) = logsumexp(x) + c
+    (got2,), _, _ = run(rx, client, rx.programs.logsumexp_dims1(rows, 64), [x[:64] + np.float32(3.0)])
+    np.testing.assert_allclose(got2.reshape(-1), want[:64] + 3.0, rtol=1e-5)
+
+
+# ---------------------------------------------------------------- Jacobi-2D (C3)
+@pytest.mark.parametrize("n,steps", [(3, 1), (4, 3), (8, 2), (33, 5), (130, 4), (515, 3), (1030, 2)])
+@pytest.mark.parametrize("form", ["dus", "pad"])
+def test_jacobi2d_bit_exact(rx, ref, client, n, steps, form):
+    rng = np.random.default_rng(n)
+    a = rng.random((n, n), dtype=np.float32)
+    b = rng.random((n, n), dtype=np.float32)
+    text = rx.programs.jacobi2d(n, steps, form=form)
+    (ga, gb), _, _ = run(rx, client, text, [a, b])
+    wa, wb = ref.run_module(text, [a, b])
+    assert np.array_equal(ga, wa) and np.array_equal(gb, wb)
+
+
+def test_jacobi2d_full_size_against_c_oracle(rx, cpu, client):
+    n, steps = 8192, 4
+    rng = np.random.default_rng(4)
+    a = rng.random((n, n), dtype=np.float32)
+    b = rng.random((n, n), dtype=np.float32)
+    (ga, gb), _, _ = run(rx, client, rx.programs.jacobi2d(n, steps), [a, b])
+    wa, wb = cpu.jacobi2d(a, b, steps)
+    assert np.array_equal(ga, wa) and np.array_equal(gb, wb)
+    # boundary rows/cols of both arrays are never written
+    assert np.array_equal(ga[0], a[0] if steps % 2 == 0 else b[0])
+
+
+def test_donated_arguments_follow_their_results(rx, ref, client):
+    n = 64
+    a = np.random.default_rng(1).random((n, n), dtype=np.float32)
+    b = np.zeros((n, n), np.float32)
+    text = rx.programs.jacobi2d(n, 1)
+    f = rx.compile(text, client)
+    A, B = rx.to_rarray(a.T, client), rx.to_rarray(b.T, client)
+    old_a = A.data[0]
+    ra, rb = f(A, B)
+    wa, wb = ref.run_module(text, [a, b])
+    assert np.array_equal(np.asarray(A).T, wa) and np.array_equal(np.asarray(B).T, wb)
+    with pytest.raises(rx.ReactantError) as e:  # the donated handle is dead
+        old_a.to_host()
+    assert e.value.code == 7
+    # without donation the inputs stay intact and the results are fresh
+    A2, B2 = rx.to_rarray(a.T, client), rx.to_rarray(b.T, client)
+    ra2, rb2 = f(A2, B2, donate=False)
+    assert np.array_equal(np.asarray(A2).T, a) and np.array_equal(np.asarray(B2).T, b)
+    assert np.array_equal(np.asarray(ra2).T, wa) and np.array_equal(np.asarray(rb2).T, wb)
+
+
+# ---------------------------------------------------------------- dot_general (C4)
+@pytest.mark.parametrize("m,k,n", [(50, 70, 30), (128, 256, 128), (257, 129, 65)])
+def test_matmul_f32(rx, ref, client, m, k, n):
+    rng = np.random.default_rng(m)
+    a = rng.standard_normal((k, m)).astype(np.float32)
+    b = rng.standard_normal((n, k)).astype(np.float32)
+    text = rx.programs.matmul(m, k, n)
+    (got,), _, _ = run(rx, client, text, [a, b])
+    want = ref.run_module(text, [a, b])[0]
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 128, 128), (256, 512, 384), (1024, 1024, 512), (200, 72, 136)])
+def test_matmul_bf16(rx, ref, client, m, k, n):
+    rng = np.random.default_rng(k)
+    a = ref.round_to_bf16(rng.standard_normal((k, m)).astype(np.float32))
+    b = ref.round_to_bf16(rng.standard_normal((n, k)).astype(np.float32))
+    text = rx.programs.matmul(m, k, n, et="bf16")
+    f = rx.compile(text, client)
+    out = f(rx.to_rarray(a.T.astype(rx.bfloat16), client), rx.to_rarray(b.T.astype(rx.bfloat16), client))
+    got = np.asarray(out).T.astype(np.float32)
+    want = b.astype(np.float64) @ a.astype(np.float64)
+    err = np.abs(got - want).max() / np.abs(want).max()
+    assert err <= 2e-2, err
+    # tighter: only the final bf16 rounding separates us from the fp32 result
+    np.testing.assert_allclose(got, want, rtol=2 ** -7, atol=np.abs(want).max() * 2 ** -8)
+
+
+def mlp_inputs(ref, F, H, O, B, seed=6):
+    rng = np.random.default_rng(seed)
+    bf = lambda a: ref.round_to_bf16(a.astype(np.float32))
+    X = bf(rng.standard_normal((B, F)))
+    W1 = bf(rng.standard_normal((F, H)) / np.sqrt(F))
+    W2 = bf(rng.standard_normal((H, O)) / np.sqrt(H))
+    b1 = (0.01 * rng.standard_normal(H)).astype(np.float32)
+    b2 = (0.01 * rng.standard_normal(O)).astype(np.float32)
+    Y = rng.standard_normal((B, O)).astype(np.float32)
+    return [W1, b1, W2, b2, X, Y]
+
+
+@pytest.mark.parametrize("F,H,O,B", [(64, 128, 32, 256), (128, 256, 128, 128)])
+def test_mlp_forward_and_gradients(rx, ref, client, F, H, O, B):
+    ins = mlp_inputs(ref, F, H, O, B)
+    text = rx.programs.mlp_grad(F, H, O, B)
+    f = rx.compile(text, client)
+    conv = lambda a: a.T.astype(rx.bfloat16) if a.ndim == 2 and a is not ins[5] else a.T
+    outs = f(*[rx.to_rarray(conv(a), client) for a in ins])
+    got = [np.asarray(o).T.astype(np.float32) for o in outs]
+    want = ref.run_module(text, ins)
+    for name, g, w in zip(("dW1", "db1", "dW2", "db2", "loss"), got, want):
+        scale = np.abs(w).max()
+        assert np.abs(g - w).max() <= 2e-2 * scale, (name, np.abs(g - w).max(), scale)
+
+
+# ---------------------------------------------------------------- boundary errors
+def test_shape_mismatch_and_bad_arity_are_errors(rx, client):
+    f = rx.compile(rx.programs.sinsum_add(16), client)
+    x = rx.to_rarray(np.zeros(16, np.float32), client)
+    y = rx.to_rarray(np.zeros(8, np.float32), client)
+    with pytest.raises(rx.ReactantError) as e:
+        f(x, y)
+    assert e.value.code == 6 and "tensor<8xf32>" in str(e.value)
+    with pytest.raises(rx.ReactantError):
+        f(x)
+    z = rx.to_rarray(np.zeros(16, np.float64), client)
+    with pytest.raises(rx.ReactantError) as e:
+        f(x, z)
+    assert e.value.code == 6
+
+
+def test_buffer_round_trip_and_allocator_stats(rx, client):
+    dev = client.addressable_devices[0]
+    for dt in (np.float32, np.int32, np.bool_, np.float64, np.int64, np.uint8):
+        a = (np.arange(2 * 3 * 5).reshape(2, 3, 5) % 7).astype(dt)
+        r = rx.to_rarray(a, client)
+        assert r.data[0].dims == (5, 3, 2), "dims cross the boundary reversed"
+        assert np.array_equal(np.asarray(r), a)
+    s = dev.allocator_stats()
+    assert s["bytes_in_use"] >= 0 and s["peak_bytes_in_use"] > 0 and s["bytes_limit"] > 0
+    assert client.platform_name == "cuda"

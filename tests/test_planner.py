@@ -1,0 +1,124 @@
+"""Parser + planner on the host (no GPU): fusion decisions for the benchmark
+programs and the hard-error contract for anything outside the supported set."""
+import json
+import os
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def kinds(plan):
+    return [s["kind"] for s in plan["steps"]]
+
+
+def test_sinsum_is_one_fused_map_reduce(rx):
+    for raw in (False, True):
+        p = rx.plan_describe(rx.programs.sinsum_add(1 << 24, raw=raw))
+        assert kinds(p) == ["reduce_full"]
+        s = p["steps"][0]
+        assert s["chain"] == "sin_add" and s["linear"] == 1 and s["dims"] == [1 << 24]
+
+
+def test_logsumexp_reads_input_once(rx):
+    opt = rx.plan_describe(rx.programs.logsumexp_dims1(32768, 8192))
+    assert kinds(opt) == ["logsumexp"]
+    assert opt["steps"][0]["dims"][:2] == [8192, 32768]
+    raw = rx.plan_describe(rx.programs.logsumexp_dims1(32768, 8192, raw=True))
+    assert kinds(raw) == ["logsumexp"], "entry/exit transposes and unit-dim reshapes must fold away"
+
+
+def test_jacobi_is_an_in_place_stencil_loop(rx):
+    p = rx.plan_describe(rx.programs.jacobi2d(8192, 100))
+    assert kinds(p) == ["loop"] and p["slots"] == 2, "no temporaries: both arrays are updated in place"
+    loop = p["steps"][0]
+    assert loop["trip"] == 100 and kinds(loop) if False else True
+    body = loop["body"]
+    assert [s["kind"] for s in body] == ["stencil"]
+    assert body[0]["chain"] == "stencil5_mul" and body[0]["dims"] == [8190, 8190]
+
+
+def test_jacobi_pad_select_form_plans(rx):
+    p = rx.plan_describe(rx.programs.jacobi2d(64, 4, form="pad"))
+    loop = [s for s in p["steps"] if s["kind"] == "loop"][0]
+    assert loop["trip"] == 4
+    assert any(s["kind"] == "stencil" for s in loop["body"])
+
+
+def test_sharded_sinsum_gets_local_reduce_plus_all_reduce(rx):
+    p = rx.plan_describe(rx.programs.sinsum_add(1 << 30, num_partitions=8))
+    assert p["num_partitions"] == 8
+    assert kinds(p) == ["reduce_full", "all_reduce"]
+    assert p["steps"][0]["dims"] == [(1 << 30) // 8], "each device reduces its own contiguous chunk"
+
+
+def test_mlp_has_five_gemms_with_folded_transposes(rx):
+    p = rx.plan_describe(rx.programs.mlp_grad())
+    gemms = [s["note"] for s in p["steps"] if s["kind"] == "gemm"]
+    assert len(gemms) == 5
+    assert sum("A(m-major)" in g for g in gemms) == 2 and sum("B(k-major)" in g for g in gemms) == 1
+    assert not any(s["kind"] == "copy" for s in p["steps"])
+
+
+def test_golden_modules_all_plan(rx):
+    with open(os.path.join(HERE, "golden", "reactant_fixtures.json")) as f:
+        cases = json.load(f)["cases"]
+    for c in cases:
+        if c["element_type"] == "f64":
+            with pytest.raises(rx.ReactantError) as e:
+                rx.plan_describe(c["module"])
+            assert "f64" in str(e.value)
+        else:
+            rx.plan_describe(c["module"])
+
+
+UNSUPPORTED = {
+    "stablehlo.sort": '    %0 = "stablehlo.sort"(%arg0) ({\n    }) : (tensor<4xf32>) -> tensor<4xf32>\n    return %0 : tensor<4xf32>',
+    "stablehlo.fft": "    %0 = stablehlo.fft %arg0, type = FFT, length = [4] : (tensor<4xf32>) -> tensor<4xf32>\n    return %0 : tensor<4xf32>",
+    "enzymexla.kernel_call": "    %0 = enzymexla.kernel_call @k (%arg0) : (tensor<4xf32>) -> tensor<4xf32>\n    return %0 : tensor<4xf32>",
+    "stablehlo.cholesky": "    %0 = stablehlo.cholesky %arg0 : tensor<4xf32>\n    return %0 : tensor<4xf32>",
+}
+
+
+@pytest.mark.parametrize("op", sorted(UNSUPPORTED))
+def test_unsupported_op_is_a_hard_error_naming_the_op(rx, op):
+    text = "module {\n  func.func @main(%arg0: tensor<4xf32>) -> tensor<4xf32> {\n" + UNSUPPORTED[op] + "\n  }\n}\n"
+    with pytest.raises(rx.ReactantError) as e:
+        rx.plan_describe(text)
+    assert e.value.code == 2 and op in str(e.value)
+
+
+def test_non_default_dot_precision_is_rejected(rx):
+    text = rx.programs.matmul(4, 4, 4).replace("[DEFAULT, DEFAULT]", "[HIGHEST, HIGHEST]")
+    with pytest.raises(rx.ReactantError) as e:
+        rx.plan_describe(text)
+    assert "HIGHEST" in str(e.value)
+
+
+def test_parse_errors_carry_line_numbers(rx):
+    with pytest.raises(rx.ReactantError) as e:
+        rx.plan_describe("module {\n  func.func @main(%arg0: tensor<4xf32>) -> tensor<4xf32> {\n    %0 = stablehlo.add %arg0, %nope : tensor<4xf32>\n    return %0 : tensor<4xf32>\n  }\n}\n")
+    assert e.value.code == 1 and "line 3" in str(e.value) and "%nope" in str(e.value)
+
+
+def test_dynamic_loop_bound_is_rejected(rx):
+    text = """module {
+  func.func @main(%arg0: tensor<4xf32>, %arg1: tensor<i64>) -> tensor<4xf32> {
+    %c = stablehlo.constant dense<0> : tensor<i64>
+    %c_1 = stablehlo.constant dense<1> : tensor<i64>
+    %0:2 = stablehlo.while(%iterArg = %c, %iterArg_0 = %arg0) : tensor<i64>, tensor<4xf32>
+     cond {
+      %1 = stablehlo.compare  LT, %iterArg, %arg1 : (tensor<i64>, tensor<i64>) -> tensor<i1>
+      stablehlo.return %1 : tensor<i1>
+    } do {
+      %1 = stablehlo.add %iterArg, %c_1 : tensor<i64>
+      %2 = stablehlo.add %iterArg_0, %iterArg_0 : tensor<4xf32>
+      stablehlo.return %1, %2 : tensor<i64>, tensor<4xf32>
+    }
+    return %0#1 : tensor<4xf32>
+  }
+}
+"""
+    with pytest.raises(rx.ReactantError) as e:
+        rx.plan_describe(text)
+    assert "stablehlo.while" in str(e.value)
