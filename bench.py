@@ -71,6 +71,9 @@ class ClockSampler:
 
     def __exit__(self, *a):
         if self.proc:
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 3.0:  # short regions: wait for the first sample
+                time.sleep(0.05)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -393,7 +396,7 @@ def main():
     wl = WORKLOADS[args.workload](rx, client, dist.rank, world)
     flush = args.workload in SMALL_INPUT
     peaks = measured_peaks()
-    with ClockSampler(dist.local_rank) as clk:
+    with ClockSampler(dist.local_rank) as clk:  # sampling covers warm-up and the timed region
         ms, launches, prof, result = time_resident(rx, client, wl, args.steps, args.warmup, flush, dist)
     ms = dist.reduce(ms, "max")
     launches = int(dist.reduce(launches, "sum"))

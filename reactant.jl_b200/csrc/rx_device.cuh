@@ -177,6 +177,21 @@ __device__ __forceinline__ void unravel(const VmProgram& P, int64_t lin, int64_t
   }
 }
 
+// same for spaces of fewer than 2^31 points: 32-bit divisions
+__device__ __forceinline__ void unravel32(const VmProgram& P, uint32_t lin, int64_t* idx) {
+#pragma unroll
+  for (int d = kMaxRank - 1; d >= 0; --d) {
+    if (d < P.rank) {
+      uint32_t dm = (uint32_t)P.dim[d];
+      uint32_t q = lin / dm;
+      idx[d] = lin - q * dm;
+      lin = q;
+    } else {
+      idx[d] = 0;
+    }
+  }
+}
+
 __device__ __forceinline__ int64_t leaf_offset(const VmLeaf& l, const int64_t* idx, int rank) {
   int64_t o = l.offset;
 #pragma unroll

@@ -23,6 +23,39 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// Second pass of the cross-CTA combine, run by whichever CTA finishes last: it adds
+// the per-CTA partials in index order, so the result does not depend on which CTA
+// that is.  `ticket` counts finished CTAs and is reset for the next launch.
+__device__ __forceinline__ void finish_in_last_block(uint32_t mine, uint32_t* partials, unsigned* ticket, int code, uint32_t init_bits, const VmOut& out,
+                                                     uint32_t* sm) {
+  __shared__ bool is_last;
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = mine;
+    __threadfence();
+    unsigned t = atomicAdd(ticket, 1u);
+    is_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  uint32_t acc = red_identity(code);
+  for (int i = threadIdx.x; i < (int)gridDim.x; i += kThreads) acc = red_combine(code, acc, __ldcg(partials + i));
+  // block_red<kThreads>, inlined here because this branch is taken by one whole CTA only
+  acc = warp_red(code, acc);
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) sm[w] = acc;
+  __syncthreads();
+  if (w == 0) {
+    uint32_t x = lane < kThreads / 32 ? sm[lane] : red_identity(code);
+    x = warp_red(code, x);
+    if (lane == 0) {
+      store_elem(out.ptr, out.offset, out.elem, red_combine(code, init_bits, x));
+      *ticket = 0;
+    }
+  }
+}
+
 // ---- vector leaf access (4 consecutive elements, 4-element aligned) ----------
 __device__ __forceinline__ void load4(const VmLeaf& l, int64_t i, uint32_t* d) {
   if (l.linear == 2) {
@@ -93,11 +126,13 @@ __global__ void __launch_bounds__(kThreads) k_map_linear(const __grid_constant__
   }
 }
 
+template <bool SMALL>
 __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant__ VmProgram P, int64_t n) {
   int64_t stride = (int64_t)gridDim.x * kThreads;
   for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
     int64_t idx[kMaxRank];
-    unravel(P, i, idx);
+    if (SMALL) unravel32(P, (uint32_t)i, idx);
+    else unravel(P, i, idx);
     uint32_t R[kVmMaxRegs][1];
     for (int k = 0; k < P.n_leaves; ++k) R[P.leaf[k].reg][0] = load_elem(P.leaf[k].ptr, leaf_offset(P.leaf[k], idx, P.rank), P.leaf[k].elem);
     vm_exec<1>(P, R, idx);
@@ -107,7 +142,8 @@ __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant_
 
 // ---- full reduce: pass 1 ---------------------------------------------------------
 // FAST_SIN_ADD: sum(sin(x) + y) with x = leaf 0, y = leaf 1, both contiguous f32.
-__global__ void __launch_bounds__(kThreads) k_reduce_full_sinadd(const float* __restrict__ x, const float* __restrict__ y, int64_t n, float* __restrict__ partials) {
+__global__ void __launch_bounds__(kThreads) k_reduce_full_sinadd(const float* __restrict__ x, const float* __restrict__ y, int64_t n, uint32_t* __restrict__ partials,
+                                                                 unsigned* ticket, uint32_t init_bits, VmOut out) {
   __shared__ uint32_t sm[kThreads / 32];
   const float4* x4 = (const float4*)x;
   const float4* y4 = (const float4*)y;
@@ -133,11 +169,12 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_sinadd(const float* __
   }
   float v = (a0 + a1) + (a2 + a3);
   uint32_t r = block_red<kThreads>(R_FADD, f2u(v), sm);
-  if (threadIdx.x == 0) partials[blockIdx.x] = u2f(r);
+  finish_in_last_block(r, partials, ticket, R_FADD, init_bits, out, sm);
 }
 
 // Generic chain, all operands contiguous: interpreter on 4 lanes.
-__global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_constant__ VmProgram P, int64_t n, int code, uint32_t* __restrict__ partials) {
+__global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_constant__ VmProgram P, int64_t n, int code, uint32_t* __restrict__ partials,
+                                                                 unsigned* ticket, uint32_t init_bits) {
   __shared__ uint32_t sm[kThreads / 32];
   int64_t n4 = n >> 2;
   int64_t stride = (int64_t)gridDim.x * kThreads;
@@ -161,30 +198,24 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_co
   }
   uint32_t v = red_combine(code, red_combine(code, acc[0], acc[1]), red_combine(code, acc[2], acc[3]));
   v = block_red<kThreads>(code, v, sm);
-  if (threadIdx.x == 0) partials[blockIdx.x] = v;
+  finish_in_last_block(v, partials, ticket, code, init_bits, P.out[0], sm);
 }
 
 // Generic chain, strided operands.
-__global__ void __launch_bounds__(kThreads) k_reduce_full_generic(const __grid_constant__ VmProgram P, int64_t n, int code, uint32_t* __restrict__ partials) {
+__global__ void __launch_bounds__(kThreads) k_reduce_full_generic(const __grid_constant__ VmProgram P, int64_t n, int code, uint32_t* __restrict__ partials,
+                                                                  unsigned* ticket, uint32_t init_bits) {
   __shared__ uint32_t sm[kThreads / 32];
   int64_t stride = (int64_t)gridDim.x * kThreads;
   uint32_t acc = red_identity(code);
+  const bool small = n < ((int64_t)1 << 31);
   for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
     int64_t idx[kMaxRank];
-    unravel(P, i, idx);
+    if (small) unravel32(P, (uint32_t)i, idx);
+    else unravel(P, i, idx);
     acc = red_combine(code, acc, vm_eval_at(P, idx));
   }
   acc = block_red<kThreads>(code, acc, sm);
-  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
-}
-
-// pass 2: one CTA, fixed order
-__global__ void __launch_bounds__(kThreads) k_reduce_finish(const uint32_t* __restrict__ partials, int nparts, int code, uint32_t init_bits, VmOut out) {
-  __shared__ uint32_t sm[kThreads / 32];
-  uint32_t acc = red_identity(code);
-  for (int i = threadIdx.x; i < nparts; i += kThreads) acc = red_combine(code, acc, partials[i]);
-  acc = block_red<kThreads>(code, acc, sm);
-  if (threadIdx.x == 0) store_elem(out.ptr, out.offset, out.elem, red_combine(code, init_bits, acc));
+  finish_in_last_block(acc, partials, ticket, code, init_bits, P.out[0], sm);
 }
 
 // ---- reduce along one axis: [outer][red] with TPR threads per row --------------------
@@ -241,7 +272,8 @@ __device__ __forceinline__ void lse_push4(float4 v, float& m, float& s) {
     s *= expf(m - cm);
     m = cm;
   }
-  s += (expf(v.x - m) + expf(v.y - m)) + (expf(v.z - m) + expf(v.w - m));
+  // while only -inf has been seen there is nothing to add (exp(-inf - finite max) = 0 once the max is known)
+  if (m > -INFINITY) s += (expf(v.x - m) + expf(v.y - m)) + (expf(v.z - m) + expf(v.w - m));
 }
 __device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2) {
   float M = fmaxf(m, m2);
@@ -281,7 +313,7 @@ __global__ void __launch_bounds__(kThreads) k_logsumexp(const float* __restrict_
       for (int64_t c = lane; c < cols; c += TPR) {
         float v = __ldg(xr + c);
         if (v > m) { s *= expf(m - v); m = v; }
-        s += expf(v - m);
+        if (m > -INFINITY) s += expf(v - m);
       }
     }
   }
@@ -308,6 +340,7 @@ __global__ void __launch_bounds__(kThreads) k_logsumexp(const float* __restrict_
     }
   }
   if (threadIdx.x % TPR == 0 && row < rows && (TPR != kThreads || threadIdx.x == 0)) {
+    if (m == -INFINITY) s = NAN;  // every element was -inf: x - max is inf - inf in the op sequence
     m_out[row] = m;
     s_out[row] = s;
     lse_out[row] = m + logf(s);
@@ -362,7 +395,8 @@ cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
   if (P.all_linear && vec_aligned(P)) {
     k_map_linear<<<grid_for((n + 3) / 4, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
   } else {
-    k_map_generic<<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
+    if (n < ((int64_t)1 << 31)) k_map_generic<true><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
+    else k_map_generic<false><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
   }
   ++*c.launches;
   return cudaGetLastError();
@@ -372,20 +406,20 @@ cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code,
   int64_t n = total_of(P);
   // 16 elements per thread per trip keeps four 128-bit loads in flight per operand
   int blocks = grid_for((n + 15) / 16, c.sm_count, 8);
-  if ((size_t)blocks > c.scratch_words) return cudaErrorInvalidValue;
+  if ((size_t)blocks + 1 > c.scratch_words) return cudaErrorInvalidValue;
   uint32_t* partials = c.scratch;
+  unsigned* ticket = (unsigned*)(c.scratch + c.scratch_words - 1);  // zeroed at device creation, reset by each launch
   bool vec = P.all_linear && vec_aligned(P);
   if (vec && P.fast_id == FAST_SIN_ADD && code == R_FADD) {
     const float* x = (const float*)P.leaf[0].ptr + P.leaf[0].offset;
     const float* y = (const float*)P.leaf[1].ptr + P.leaf[1].offset;
-    k_reduce_full_sinadd<<<blocks, kThreads, 0, c.stream>>>(x, y, n, (float*)partials);
+    k_reduce_full_sinadd<<<blocks, kThreads, 0, c.stream>>>(x, y, n, partials, ticket, init_bits, P.out[0]);
   } else if (vec) {
-    k_reduce_full_linear<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials);
+    k_reduce_full_linear<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits);
   } else {
-    k_reduce_full_generic<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials);
+    k_reduce_full_generic<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits);
   }
-  k_reduce_finish<<<1, kThreads, 0, c.stream>>>(partials, blocks, code, init_bits, P.out[0]);
-  *c.launches += 2;
+  *c.launches += 1;
   return cudaGetLastError();
 }
 

@@ -60,6 +60,7 @@ size_t round_up(size_t b) { return b == 0 ? 256 : (b + 255) & ~(size_t)255; }
 // device pool
 // ---------------------------------------------------------------------------
 void* RxDevice::alloc(size_t bytes) {
+  if (closed.load()) throw Error(RX_ERR_BAD_HANDLE, "the client that owns this device was freed");
   size_t rb = round_up(bytes);
   {
     std::lock_guard<std::mutex> lk(mu);
@@ -96,6 +97,12 @@ void* RxDevice::alloc(size_t bytes) {
 
 void RxDevice::release(void* p, size_t bytes) {
   if (!p) return;
+  if (closed.load()) {  // pool and stream are gone: hand the block back to the driver
+    cudaSetDevice(ordinal);
+    cudaFree(p);
+    cudaGetLastError();
+    return;
+  }
   size_t rb = round_up(bytes);
   std::lock_guard<std::mutex> lk(mu);
   pool[rb].push_back(p);
@@ -226,7 +233,7 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r) {
       size_t words = (size_t)st.outer * ns * st.inner;
       std::shared_ptr<Storage> tmp;
       uint32_t* partials = d->scratch;
-      if (words > d->scratch_words) {
+      if (words + 1 > d->scratch_words) {
         tmp = std::make_shared<Storage>(d, d->alloc(words * 4), words * 4);
         partials = (uint32_t*)tmp->ptr;
       }
@@ -352,6 +359,7 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
     CK(cudaSetDevice(d->ordinal));
     auto es = std::make_shared<EventState>();
     es->dev = d;
+    es->keep = d->shared_from_this();
     CK(cudaEventCreateWithFlags(&es->ev, cudaEventDisableTiming));
     CK(cudaEventRecord(es->ev, d->stream));
     for (int j = 0; j < num_results; ++j) {
@@ -379,8 +387,8 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
   if (futures) *futures = future_results ? 1 : 0;
 }
 
-RxDevice* make_device(RxClient* c, int ordinal, int local_id, double fraction) {
-  auto* d = new RxDevice();
+std::shared_ptr<RxDevice> make_device(RxClient* c, int ordinal, int local_id, double fraction) {
+  auto d = std::make_shared<RxDevice>();
   d->client = c;
   d->ordinal = ordinal;
   d->local_id = local_id;
@@ -393,6 +401,7 @@ RxDevice* make_device(RxClient* c, int ordinal, int local_id, double fraction) {
   CK(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
   d->scratch_words = (size_t)1 << 20;
   CK(cudaMalloc(&d->scratch, d->scratch_words * 4));
+  CK(cudaMemset(d->scratch, 0, d->scratch_words * 4));  // the last word is the finished-CTA ticket of the reductions
   CK(cudaHostAlloc(&d->status, 64, cudaHostAllocMapped));
   memset(d->status, 0, 64);
   return d;
@@ -445,19 +454,19 @@ RxClient* MakeGPUClient(int node_id, int num_nodes, int64_t* allowed_devices, in
     }
     if (ords.size() * (size_t)c->num_nodes > (size_t)kMaxRanks) throw Error(RX_ERR_ARG, "more than " + std::to_string(kMaxRanks) + " devices in the mesh");
     for (size_t i = 0; i < ords.size(); ++i) {
-      RxDevice* d = make_device(c.get(), ords[i], (int)i, memory_fraction);
+      std::shared_ptr<RxDevice> d = make_device(c.get(), ords[i], (int)i, memory_fraction);
       d->global_id = node_id * (int)ords.size() + (int)i;
-      c->devices.emplace_back(d);
+      c->devices.push_back(d);
     }
     for (int n = 0; n < c->num_nodes; ++n) {
       if (n == node_id) continue;
       for (size_t i = 0; i < ords.size(); ++i) {
-        auto* d = new RxDevice();
+        auto d = std::make_shared<RxDevice>();
         d->client = c.get();
         d->addressable = false;
         d->local_id = (int)i;
         d->global_id = n * (int)ords.size() + (int)i;
-        c->remote.emplace_back(d);
+        c->remote.push_back(d);
       }
     }
     const char* mode = getenv("RX_ALLREDUCE");
@@ -484,7 +493,13 @@ void FreeClient(RxClient* client) {
     if (d->flush_buf) cudaFree(d->flush_buf);
     if (d->status) cudaFreeHost(d->status);
     for (auto& s : d->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
+    d->spans.clear();
+    d->closed.store(true);
     cudaStreamDestroy(d->stream);
+    d->stream = nullptr;
+    d->scratch = nullptr;
+    d->flush_buf = nullptr;
+    d->client = nullptr;
   }
   delete client;
 }
@@ -767,6 +782,7 @@ RxEvent* RxEventRecord(RxDevice* d) {
   API_BEGIN
   auto* e = new RxEvent();
   e->dev = d;
+  e->keep = d->shared_from_this();
   CK(cudaSetDevice(d->ordinal));
   CK(cudaEventCreate(&e->ev));
   CK(cudaEventRecord(e->ev, d->stream));

@@ -25,8 +25,9 @@ struct MailTable {
   unsigned long long* peer[kMaxRanks];
 };
 
-struct RxDevice {
+struct RxDevice : std::enable_shared_from_this<RxDevice> {
   RxClient* client = nullptr;
+  std::atomic<bool> closed{false};  // client freed: late buffer finalizers free straight to the driver
   int ordinal = 0;    // CUDA device ordinal
   int local_id = 0;   // index among this process's devices
   int global_id = 0;  // index in the mesh
@@ -69,11 +70,14 @@ struct RxDevice {
   }
 };
 
+// Device memory block.  Keeps its device object alive: handles may be finalized
+// (from a garbage collector, on any thread) after the client itself was freed.
 struct Storage {
   RxDevice* dev;
+  std::shared_ptr<RxDevice> keep;
   void* ptr;
   size_t bytes;
-  Storage(RxDevice* d, void* p, size_t b) : dev(d), ptr(p), bytes(b) {}
+  Storage(RxDevice* d, void* p, size_t b) : dev(d), keep(d->shared_from_this()), ptr(p), bytes(b) {}
   ~Storage() { dev->release(ptr, bytes); }
 };
 
@@ -93,6 +97,7 @@ struct RxBuffer {
 struct EventState {
   cudaEvent_t ev = nullptr;
   RxDevice* dev = nullptr;
+  std::shared_ptr<RxDevice> keep;
   ~EventState();
 };
 
@@ -103,6 +108,7 @@ struct RxFuture {
 struct RxEvent {
   cudaEvent_t ev = nullptr;
   RxDevice* dev = nullptr;
+  std::shared_ptr<RxDevice> keep;
 };
 
 struct RxExecutable {
@@ -114,8 +120,8 @@ struct RxExecutable {
 
 struct RxClient {
   int node_id = 0, num_nodes = 1;
-  std::vector<std::unique_ptr<RxDevice>> devices;     // addressable devices
-  std::vector<std::unique_ptr<RxDevice>> remote;      // placeholders for other processes' devices
+  std::vector<std::shared_ptr<RxDevice>> devices;     // addressable devices
+  std::vector<std::shared_ptr<RxDevice>> remote;      // placeholders for other processes' devices
   std::mutex mu;
   // NCCL
   void* nccl_comms[kMaxRanks] = {};

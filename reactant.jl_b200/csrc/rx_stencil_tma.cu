@@ -1,0 +1,265 @@
+// 2-D stencil step with TMA-staged tiles.
+//
+// out[r][c] = chain(src[r + dy_k][c + dx_k], k = 0..taps)   for a window of a
+// row-major f32 array -- the fused form of the slice / add / multiply /
+// dynamic_update_slice sequence Reactant traces for
+//     B[2:end-1, 2:end-1] = 0.2f0 .* (A[2:end-1, 2:end-1] .+ A[1:end-2, 2:end-1] .+ ...)
+// (src/Indexing.jl:552-627 getindex -> stablehlo.slice, :350-446 setindex! ->
+// dynamic_update_slice; benchmark/polybench/stencil.jl:263-289).
+//
+// Each CTA walks a strided list of 32 x 252 (or 248) output tiles.  One elected thread
+// issues a cp.async.bulk.tensor.2d (TMA) load of the tile plus its halo into a
+// two-stage shared-memory ring, signalled through an mbarrier; the other threads
+// compute the previous tile meanwhile.  Halo rows/columns are re-read from L2,
+// not HBM (neighbouring tiles are in flight at the same time), so DRAM traffic
+// stays at one read and one write per element.  The adds are evaluated in the
+// traced order and nothing is contracted into an FMA, so results are bit-exact
+// with the CPU evaluation.  TMA loads start on 16-byte boundaries (x is rounded
+// down to a multiple of 4 floats and the box is widened); no multicast is used.
+#include <cuda.h>
+
+#include "rx_device.cuh"
+#include "rx_stencil.h"
+
+namespace rx {
+
+namespace {
+
+constexpr int TH = 32, HALO_H = 8;
+constexpr int BOX_W = 256;                  // TMA boxes are at most 256 elements wide; a tile is BOX_W - halo columns
+constexpr int STAGES = 2;
+constexpr int kMaxTaps = 8;
+constexpr long long kWaitLimit = 2000000;  // bounded mbarrier polling
+
+struct StencilParams {
+  float* dst;
+  int64_t rows, cols, dst_ld, dst_off;
+  int x_base, y_base, x_shift;  // tensor coordinates of window column/row 0; columns skipped inside the box
+  int box_h;
+  int tw;       // output columns per tile
+  int n_taps;
+  int dy[kMaxTaps], dx[kMaxTaps];
+  int tiles_x, tiles_y;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: returns false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (long long i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(smem_dst)),
+               "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+               : "memory");
+}
+
+template <bool FAST5>
+__global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ StencilParams p,
+                                                     const __grid_constant__ VmProgram P) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[STAGES];
+  float* tile[STAGES];
+  const int stage_floats = BOX_W * (TH + HALO_H);
+  // 128-byte aligned stages
+  uintptr_t base = ((uintptr_t)smem_raw + 127) & ~(uintptr_t)127;
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s) tile[s] = (float*)base + (size_t)s * stage_floats;
+  const uint32_t bytes = (uint32_t)(BOX_W * p.box_h * sizeof(float));
+  const int ntiles = p.tiles_x * p.tiles_y;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](int t, int s) {
+    int ty = t / p.tiles_x, tx = t - ty * p.tiles_x;
+    mbar_expect_tx(&bars[s], bytes);
+    tma_load_2d(tile[s], &tmap, p.x_base + tx * p.tw, p.y_base + ty * TH, &bars[s]);
+  };
+
+  int first = blockIdx.x;
+  if (threadIdx.x == 0 && first < ntiles) issue(first, 0);
+  int it = 0;
+  bool failed = false;
+  for (int t = first; t < ntiles; t += gridDim.x, ++it) {
+    int s = it % STAGES;
+    uint32_t parity = (it / STAGES) & 1;
+    int next = t + gridDim.x;
+    if (threadIdx.x == 0 && next < ntiles) issue(next, (it + 1) % STAGES);  // that stage was drained before the last barrier
+    if (!mbar_wait(&bars[s], parity)) {
+      failed = true;
+      break;
+    }
+    int ty = t / p.tiles_x, tx = t - ty * p.tiles_x;
+    int64_t c = (int64_t)tx * p.tw + threadIdx.x;
+    int64_t r0 = (int64_t)ty * TH;
+    const float* sm = tile[s] + p.x_shift + threadIdx.x;
+    if ((int)threadIdx.x < p.tw && c < p.cols) {
+      float* out = p.dst + p.dst_off + r0 * p.dst_ld + c;
+      int rmax = (int)min((int64_t)TH, p.rows - r0);
+      if (FAST5) {
+        const int o0 = p.dy[0] * BOX_W + p.dx[0], o1 = p.dy[1] * BOX_W + p.dx[1], o2 = p.dy[2] * BOX_W + p.dx[2], o3 = p.dy[3] * BOX_W + p.dx[3],
+                  o4 = p.dy[4] * BOX_W + p.dx[4];
+        const float k = P.fast_c;
+#pragma unroll 4
+        for (int r = 0; r < rmax; ++r) {
+          const float* q = sm + r * BOX_W;
+          float v = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(q[o0], q[o1]), q[o2]), q[o3]), q[o4]);
+          out[(int64_t)r * p.dst_ld] = __fmul_rn(k, v);
+        }
+      } else {
+        int64_t idx0[kMaxRank] = {0, 0, 0, 0};
+        for (int r = 0; r < rmax; ++r) {
+          const float* q = sm + r * BOX_W;
+          uint32_t R[kVmMaxRegs][1];
+          for (int k = 0; k < P.n_leaves; ++k) R[P.leaf[k].reg][0] = f2u(q[p.dy[k] * BOX_W + p.dx[k]]);
+          vm_exec<1>(P, R, idx0);
+          out[(int64_t)r * p.dst_ld] = u2f(R[P.out[0].reg][0]);
+        }
+      }
+    }
+    __syncthreads();  // every thread is done with stage s before it is refilled
+  }
+  if (failed) {
+    if (threadIdx.x == 0) *p.status = 2;
+    // a load may still be in flight into this CTA's shared memory: give it a bounded chance to land
+    __syncthreads();
+    if (threadIdx.x == 0)
+      for (int s = 0; s < STAGES; ++s) mbar_wait(&bars[s], 0) || mbar_wait(&bars[s], 1);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)p;
+    cudaGetLastError();
+  }
+  return fn;
+}
+
+}  // namespace
+
+cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, bool* handled) {
+  *handled = false;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return cudaSuccess;
+  if ((int)st.st_dy.size() > kMaxTaps || st.st_dy.size() != (size_t)P.n_leaves) return cudaSuccess;
+  int max_dy = 0, max_dx = 0;
+  for (size_t k = 0; k < st.st_dy.size(); ++k) {
+    max_dy = std::max(max_dy, st.st_dy[k]);
+    max_dx = std::max(max_dx, st.st_dx[k]);
+  }
+  const float* src = (const float*)P.leaf[0].ptr;
+  int64_t ld = st.st_src_ld;
+  int64_t slot_elems = 0;
+  // the source slot is a dense [rows_total][ld] array
+  {
+    int64_t last = st.st_src_off + (st.st_rows - 1 + max_dy) * ld + (st.st_cols - 1 + max_dx);
+    slot_elems = ((last / ld) + 1) * ld;
+  }
+  int64_t rows_total = slot_elems / ld;
+  int64_t col0 = st.st_src_off % ld, row0 = st.st_src_off / ld;
+  int x_shift = (int)(col0 % 4);
+  int halo_w = (max_dx + x_shift + 3) & ~3;  // box start and tile width stay multiples of 4 floats (16 B)
+  if (halo_w > 16 || max_dy > HALO_H) return cudaSuccess;
+  int tw = BOX_W - halo_w;
+  if (((uintptr_t)src % 16) || (ld % 4) || ld > (int64_t)INT32_MAX || rows_total > (int64_t)INT32_MAX) return cudaSuccess;
+  if (st.st_rows <= 0 || st.st_cols <= 0) { *handled = true; return cudaSuccess; }
+
+  int box_h = TH + max_dy;
+  // tensor map cache: (base pointer, ld, rows, box height)
+  struct Key { const void* p; int64_t ld, rows; int bh; };
+  Key key{src, ld, rows_total, box_h};
+  std::vector<uint8_t>* blob = nullptr;
+  for (auto& kv : d->tmaps)
+    if (kv.first == src && kv.second.size() == sizeof(CUtensorMap) + sizeof(Key) && !memcmp(kv.second.data() + sizeof(CUtensorMap), &key, sizeof(Key))) blob = &kv.second;
+  if (!blob) {
+    CUtensorMap m;
+    cuuint64_t gdim[2] = {(cuuint64_t)ld, (cuuint64_t)rows_total};
+    cuuint64_t gstride[1] = {(cuuint64_t)ld * sizeof(float)};
+    cuuint32_t box[2] = {(cuuint32_t)BOX_W, (cuuint32_t)box_h};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)src, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaSuccess;  // decline: the generic kernel handles it
+    std::vector<uint8_t> v(sizeof(CUtensorMap) + sizeof(Key));
+    memcpy(v.data(), &m, sizeof(CUtensorMap));
+    memcpy(v.data() + sizeof(CUtensorMap), &key, sizeof(Key));
+    if (d->tmaps.size() > 64) d->tmaps.clear();
+    d->tmaps[src] = std::move(v);
+    blob = &d->tmaps[src];
+  }
+  CUtensorMap tmap;
+  memcpy(&tmap, blob->data(), sizeof(CUtensorMap));
+
+  StencilParams sp{};
+  sp.dst = (float*)P.out[0].ptr;
+  sp.rows = st.st_rows;
+  sp.cols = st.st_cols;
+  sp.dst_ld = st.st_dst_ld;
+  sp.dst_off = st.st_dst_off;
+  sp.x_base = (int)(col0 - x_shift);
+  sp.y_base = (int)row0;
+  sp.x_shift = x_shift;
+  sp.box_h = box_h;
+  sp.tw = tw;
+  sp.n_taps = (int)st.st_dy.size();
+  for (int k = 0; k < sp.n_taps; ++k) { sp.dy[k] = st.st_dy[k]; sp.dx[k] = st.st_dx[k]; }
+  sp.tiles_x = (int)((st.st_cols + tw - 1) / tw);
+  sp.tiles_y = (int)((st.st_rows + TH - 1) / TH);
+  int* dstatus = nullptr;
+  cudaHostGetDevicePointer(&dstatus, d->status, 0);
+  sp.status = dstatus + 1;
+
+  size_t smem = (size_t)STAGES * BOX_W * (TH + HALO_H) * sizeof(float) + 128;
+  bool fast = P.fast_id == FAST_STENCIL5_MUL && sp.n_taps == 5;
+  auto kern = fast ? k_stencil_tma<true> : k_stencil_tma<false>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[fast]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_set[fast] = true;
+  }
+  int ntiles = sp.tiles_x * sp.tiles_y;
+  int grid = std::min(ntiles, d->sm_count * 2);
+  kern<<<grid, 256, smem, d->stream>>>(tmap, sp, P);
+  ++d->launches;
+  *handled = true;
+  return cudaGetLastError();
+}
+
+}  // namespace rx

@@ -133,7 +133,8 @@ def test_logsumexp_dims1(rx, ref, client, rows, cols, raw):
     x = np.random.default_rng(rows * 31 + cols).standard_normal((cols, rows)).astype(np.float32)
     text = rx.programs.logsumexp_dims1(rows, cols, raw=raw)
     (got,), f, _ = run(rx, client, text, [x])
-    assert [s["kind"] for s in f.describe()["steps"]] == ["logsumexp"]
+    if rows > 1 and cols > 1:  # degenerate shapes collapse to plain maps
+        assert [s["kind"] for s in f.describe()["steps"]] == ["logsumexp"]
     want = ref.run_module(text, [x])[0]
     assert got.shape == want.shape == (cols, 1)
     np.testing.assert_allclose(got, want, rtol=ref.reduction_tolerance(rows))
