@@ -240,7 +240,7 @@ def _upload(client: Client, device: Device, a: np.ndarray) -> _Buffer:
     """Julia array -> device buffer with reversed dims and unchanged (column-major) bytes."""
     if a.dtype not in _PTYPE:
         raise ReactantError(3, f"unsupported element type {a.dtype}")
-    rm = np.ascontiguousarray(a.T)
+    rm = np.ascontiguousarray(a.T).reshape(a.T.shape)  # (ascontiguousarray promotes 0-d to 1-d)
     dims = (C.c_int64 * rm.ndim)(*rm.shape)
     h = lib().ArrayFromHostBuffer(client.handle, rm.ctypes.data_as(C.c_void_p), _PTYPE[a.dtype], rm.ndim, dims, device.handle)
     check()
