@@ -162,6 +162,24 @@ void XLAExecuteSharded(RxExecutable* exec, int num_args, RxBuffer** op_args, RxD
 void XLAExecute(RxExecutable* exec, int op_args_len, RxBuffer** op_args, uint8_t* is_arg_donatable,
                 int num_results, RxBuffer** op_results, uint8_t* futures, RxFuture** future_results);
 
+/* ---- allocation-free entry point (no counterpart in the reference) -----------
+ * out_dev[0] = sum(sin(x_dev[i]) + y_dev[i], i < n), computed on `stream`
+ * (a cudaStream_t; NULL = the default stream) of the current device, for hosts
+ * that cannot let this library allocate device memory: ones that have given all
+ * of it to their own arena, ones that cannot take the device-wide stall of
+ * cudaMalloc / cudaFree inside a latency-critical loop, ones that account for
+ * every byte themselves.  It calls no cudaMalloc, cudaFree or any allocating
+ * routine: x_dev, y_dev (16-byte aligned) and out_dev are the caller's device
+ * pointers, and the cross-CTA scratch is a fixed 64 KiB + 256 B array inside the
+ * library image (resident on every GPU that loads the library until exit).
+ * Limits and rules: n <= 2^30 elements, larger n returns RX_ERR_TOO_LARGE and
+ * launches nothing; the first call on each device resolves the array's address
+ * and should be made outside any stream capture; every call shares the array,
+ * so calls whose kernels could overlap on one GPU must be serialised by the
+ * caller.  Returns RX_OK or an RX_ERR_* code (message in RxLastError()).  The
+ * result is deterministic and independent of the GPU's SM count. */
+int RxSinSumAddNoAlloc(const float* x_dev, const float* y_dev, int64_t n, float* out_dev, void* stream);
+
 /* ---- collectives bootstrap (takes the place of the NCCL clique setup XLA
  * performs through its distributed KV store, API.cpp:536-547, 2896-3050) ------ */
 /* Rank 0 obtains an id (128 bytes), the host distributes it to every process,

@@ -85,6 +85,7 @@ PROTOTYPES = {
     "RxPlanDescribe": (P, [C.c_char_p, C.c_size_t]),
     "XLAExecuteSharded": (None, [P, C.c_int, PP, P, U8P, C.c_int, PP, U8P, PP]),
     "XLAExecute": (None, [P, C.c_int, PP, U8P, C.c_int, PP, U8P, PP]),
+    "RxSinSumAddNoAlloc": (C.c_int, [P, P, C.c_int64, P, P]),
     "RxCollectivesUniqueId": (C.c_int, [U8P]),
     "RxClientInitCollectives": (C.c_int, [P, U8P]),
     "RxClientMailboxHandle": (C.c_int, [P, C.c_int, U8P]),

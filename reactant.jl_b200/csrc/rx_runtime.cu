@@ -56,6 +56,12 @@ size_t round_up(size_t b) { return b == 0 ? 256 : (b + 255) & ~(size_t)255; }
 
 }  // namespace
 
+namespace rx {
+// error reporting for entry points that live in other translation units
+void set_last_error(int code, const std::string& msg) { report(code, msg); }
+void clear_last_error() { clear_error(); }
+}  // namespace rx
+
 // ---------------------------------------------------------------------------
 // device pool
 // ---------------------------------------------------------------------------
