@@ -254,51 +254,6 @@ def time_e2e(rx, client, wl, steps, warmup, dist):
     return ms, out
 
 
-class Dist:
-    """torch.distributed plumbing (NCCL): barrier, max/sum over ranks, byte exchange."""
-
-    def __init__(self, world):
-        self.world = world
-        self.rank = int(os.environ.get("RANK", "0"))
-        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-        if world > 1:
-            import torch
-            import torch.distributed as dist
-            torch.cuda.set_device(self.local_rank)
-            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
-            self.dist, self.torch = dist, torch
-
-    def barrier(self):
-        if self.world > 1:
-            self.dist.barrier()
-            self.torch.cuda.synchronize()
-
-    def reduce(self, v, op="max"):
-        if self.world == 1:
-            return v
-        t = self.torch.tensor([float(v)], dtype=self.torch.float64, device="cuda")
-        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX if op == "max" else self.dist.ReduceOp.SUM)
-        return float(t.item())
-
-    def all_gather_bytes(self, b: bytes):
-        if self.world == 1:
-            return [b]
-        out = [None] * self.world
-        self.dist.all_gather_object(out, b)
-        return out
-
-    def broadcast_bytes(self, b):
-        if self.world == 1:
-            return b
-        box = [b]
-        self.dist.broadcast_object_list(box, src=0)
-        return box[0]
-
-    def close(self):
-        if self.world > 1:
-            self.dist.destroy_process_group()
-
-
 def cpu_baseline(name, seconds_budget=20.0):
     """The C/OpenMP oracle timed on this host's cores on a bounded sample of the workload."""
     _, cpu = entry.load_oracle()
@@ -377,22 +332,14 @@ def main():
     if world != args.gpus:
         if args.gpus > 1:
             raise SystemExit(f"--gpus {args.gpus} needs torch.distributed.run with {args.gpus} processes (WORLD_SIZE={world})")
-    dist = Dist(world)
     rx = entry.load_package()
+    dist = rx.dist.Dist(world)
     client = rx.Client(node_id=dist.rank, num_nodes=world, allowed_devices=[dist.local_rank])
     allreduce = "none"
     if world > 1:
         if args.workload not in ("c5_sharded_sinsum_2p30", "c1_sinsum_2p24"):
             raise SystemExit("only the sinsum workloads shard; the others run as single-GPU configurations")
-        mode = os.environ.get("RX_ALLREDUCE", "mailbox")
-        if mode == "nccl":
-            uid = rx.collectives_unique_id() if dist.rank == 0 else None
-            client.init_collectives(dist.broadcast_bytes(uid))
-            allreduce = "nccl"
-        else:
-            handles = dist.all_gather_bytes(client.mailbox_handles())
-            client.open_mailboxes(b"".join(handles))
-            allreduce = "nvlink-mailbox"
+        allreduce = rx.dist.connect_collectives(rx, client, dist, os.environ.get("RX_ALLREDUCE", "mailbox"))
     wl = WORKLOADS[args.workload](rx, client, dist.rank, world)
     flush = args.workload in SMALL_INPUT
     peaks = measured_peaks()

@@ -28,7 +28,7 @@ import weakref
 
 import numpy as np
 
-from . import _lib
+from . import _lib, dist
 from ._lib import ReactantError, lib, check, take_string
 
 try:
@@ -313,11 +313,12 @@ def to_rarray(x, client: Client | None = None, device: Device | None = None, sha
         if d is None:
             piece = a
         else:
-            if a.shape[d] % n:
-                raise ReactantError(2, "sharded dimension is not divisible by the mesh size")
-            step = a.shape[d] // n
+            try:
+                lo, hi = dist.shard_bounds(a.shape[d], n, i)
+            except ValueError as e:
+                raise ReactantError(2, str(e))
             sl = [slice(None)] * a.ndim
-            sl[d] = slice(i * step, (i + 1) * step)
+            sl[d] = slice(lo, hi)
             piece = a[tuple(sl)]
         bufs.append(_upload(client, dev, piece))
     return ConcreteRArray(bufs, a.shape, a.dtype, sharding=sharding, replicated=d is None)

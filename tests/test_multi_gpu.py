@@ -1,0 +1,63 @@
+"""Sharded execution on several GPUs of one process (the shape a Julia session
+has): XLAExecute with [device][arg] buffers, local reduce + all-reduce, every
+device ends with the same bits.  Skipped when the box has fewer GPUs."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpu():
+    try:
+        import torch
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+@pytest.mark.parametrize("ndev", [2, 4, 8])
+@pytest.mark.parametrize("transport", ["mailbox", "nccl"])
+def test_sharded_sinsum_matches_unsharded(rx, ref, ndev, transport, monkeypatch):
+    if _ngpu() < ndev:
+        pytest.skip(f"needs {ndev} GPUs")
+    monkeypatch.setenv("RX_ALLREDUCE", transport)
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    client = rx.Client(allowed_devices=list(range(ndev)))
+    try:
+        n = ndev * ((1 << 18) + 4)
+        rng = np.random.default_rng(ndev)
+        x = rng.uniform(-np.pi, np.pi, n).astype(np.float32)
+        y = rng.uniform(-np.pi, np.pi, n).astype(np.float32)
+        mesh = rx.Mesh(client.devices, ("x",))
+        sh = rx.NamedSharding(mesh, ("x",))
+        X, Y = rx.to_rarray(x, client, sharding=sh), rx.to_rarray(y, client, sharding=sh)
+        assert len(X.data) == ndev and X.data[1].dims == (n // ndev,)
+        assert np.array_equal(np.asarray(X), x), "gathering the shards restores the array"
+        f = rx.compile(rx.programs.sinsum_add(n, num_partitions=ndev), client)
+        r = f(X, Y)
+        assert len(r.data) == ndev, "the scalar result is replicated on every device"
+        vals = [b.to_host().item() for b in r.data]
+        assert len(set(np.float32(v).tobytes() for v in vals)) == 1, vals
+        terms = np.sin(x.astype(np.float64)) + y
+        assert abs(vals[0] - terms.sum()) <= ref.reduction_tolerance(n) * max(abs(terms.sum()), np.linalg.norm(terms))
+        # a second call (next all-reduce epoch) gives the same bits
+        r2 = f(X, Y)
+        assert r2.data[0].to_host().tobytes() == r.data[0].to_host().tobytes()
+    finally:
+        client.close()
+
+
+def test_sharded_executable_refuses_a_partial_mesh(rx):
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    client = rx.Client(allowed_devices=[0, 1])
+    try:
+        f = rx.compile(rx.programs.sinsum_add(1 << 12, num_partitions=4), client)
+        mesh = rx.Mesh(client.devices, ("x",))
+        sh = rx.NamedSharding(mesh, ("x",))
+        x = np.zeros(1 << 11, np.float32)  # wrong on purpose: 2 devices for a 4-way program
+        X = rx.to_rarray(x, client, sharding=sh)
+        with pytest.raises(rx.ReactantError):
+            f(X, X)
+    finally:
+        client.close()
