@@ -153,7 +153,7 @@ def setup_jacobi(rx, client, n=8192, steps=100):
     per_sweep = 4 * n * n + 4 * (n - 2) * (n - 2)
     return dict(thunk=thunk, upload=lambda: (rx.to_rarray(a.T, client), rx.to_rarray(b.T, client)), host=(a, b),
                 read=lambda r: (np.asarray(r[0]), np.asarray(r[1])), bytes_per_step=per_sweep * steps, h2d=8 * n * n, d2h=8 * n * n,
-                unit="GB/s", kind="stencil", dtype="f32", bound="hbm", kernel="k_stencil", launches_per_step=steps, donates=True)
+                unit="GB/s", kind="stencil_tma", dtype="f32", bound="hbm", kernel="k_stencil", launches_per_step=steps, donates=True)
 
 
 def setup_mlp(rx, client, F=1024, H=4096, O=1024, B=4096):
@@ -171,7 +171,7 @@ def setup_mlp(rx, client, F=1024, H=4096, O=1024, B=4096):
     flops = 2 * B * H * F * 2 + 2 * B * O * H * 3
     nbytes = sum(a.nbytes for a in ins)
     return dict(thunk=thunk, upload=lambda: tuple(rx.to_rarray(a.T, client) for a in ins), host=ins, read=lambda r: float(r[4]),
-                flops_per_step=flops, h2d=nbytes, d2h=W1.nbytes + W2.nbytes + b1.nbytes + b2.nbytes + 4, unit="TFLOP/s", kind="gemm", dtype="bf16",
+                flops_per_step=flops, h2d=nbytes, d2h=W1.nbytes + W2.nbytes + b1.nbytes + b2.nbytes + 4, unit="TFLOP/s", kind="gemm_tc", dtype="bf16",
                 bound="tensor", kernel="k_gemm", launches_per_step=5)
 
 

@@ -220,6 +220,38 @@ void destroy_collectives(RxClient* c) {
   }
 }
 
+namespace {
+bool mailboxes_ready(RxClient* c) {
+  std::lock_guard<std::mutex> lk(c->mu);
+  bool ready = true;
+  for (auto& d : c->devices) ready = ready && d->mail_ready;
+  if (!ready && c->num_nodes == 1) ready = setup_local_mailboxes(c);
+  return ready;
+}
+}  // namespace
+
+bool prepare_fused_allreduce(RxClient* c, const Step& st, const std::vector<RxDevice*>& devs, std::vector<FusedAllReduce>* out) {
+  int world = c->n_global();
+  if (world <= 1 || c->allreduce_mode == 1 || st.count != 1 || devs.size() != c->devices.size()) return false;
+  if (getenv("RX_NO_FUSED_ALLREDUCE")) return false;
+  if (!mailboxes_ready(c)) return false;
+  unsigned epoch = ++c->epoch;
+  out->clear();
+  for (RxDevice* d : devs) {
+    FusedAllReduce ar{};
+    for (int r = 0; r < kMailRanks && r < kMaxRanks; ++r) ar.peer[r] = d->mail.peer[r];
+    ar.rank = d->global_id;
+    ar.n = world;
+    ar.epoch = epoch;
+    int* dstatus = nullptr;
+    cudaSetDevice(d->ordinal);
+    cudaHostGetDevicePointer(&dstatus, d->status, 0);
+    ar.status = dstatus;
+    out->push_back(ar);
+  }
+  return true;
+}
+
 void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::function<RxDevice*(size_t)>& dev, const std::function<void*(size_t)>& ptr) {
   int world = c->n_global();
   if (world <= 1) return;

@@ -5,6 +5,7 @@
 // collective.
 #pragma once
 #include <functional>
+#include <vector>
 
 #include "rx_runtime.h"
 
@@ -20,5 +21,9 @@ void destroy_collectives(RxClient* c);
 // matching values of all other ranks of the mesh; every rank ends with the same bits.
 void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::function<RxDevice*(size_t)>& dev,
                    const std::function<void*(size_t)>& ptr);
+
+// If a single-word all-reduce can go through the mailboxes, advance the epoch and fill
+// one FusedAllReduce per local device (to be handed to the producing reduce kernel).
+bool prepare_fused_allreduce(RxClient* c, const Step& ar_step, const std::vector<RxDevice*>& devs, std::vector<FusedAllReduce>* out);
 
 }  // namespace rx

@@ -244,4 +244,42 @@ __device__ __forceinline__ uint32_t block_red(int code, uint32_t v, uint32_t* sm
   return smem[0];
 }
 
+// All-reduce(sum) of one f32 across the mesh through peer mailboxes, executed by one
+// warp (lane r talks to rank r).  Every rank stores {epoch, value} as a single 64-bit
+// word into its slot of every peer's mailbox, then polls its own mailbox -- bounded --
+// and adds the words in rank order, so all ranks return the same bits.  Returns false
+// (and sets *status) if a peer's word did not arrive within the limit.
+__device__ __forceinline__ bool mailbox_allreduce_warp(const FusedAllReduce& ar, float mine, float* result) {
+  const int lane = threadIdx.x & 31;
+  const unsigned long long word = ((unsigned long long)ar.epoch << 32) | (unsigned long long)__float_as_uint(mine);
+  const int set = (ar.epoch & 1) * kMailRanks;
+  if (lane < ar.n) {
+    volatile unsigned long long* dst = ar.peer[lane] + set + ar.rank;
+    *dst = word;
+  }
+  __threadfence_system();
+  float got = 0.f;
+  int failed = 0;
+  if (lane < ar.n) {
+    volatile unsigned long long* src = ar.peer[ar.rank] + set + lane;
+    unsigned long long w = *src;
+    long long spins = 0;
+    while ((unsigned)(w >> 32) != ar.epoch) {
+      if (++spins > 4000000) { failed = 1; break; }
+      __nanosleep(100);
+      w = *src;
+    }
+    got = __uint_as_float((unsigned)w);
+  }
+  failed = __any_sync(0xFFFFFFFFu, failed);
+  float sum = 0.f;
+  for (int r = 0; r < ar.n; ++r) sum += __shfl_sync(0xFFFFFFFFu, got, r);
+  if (failed) {
+    if (lane == 0) *ar.status = 1;
+    return false;
+  }
+  *result = sum;
+  return true;
+}
+
 }  // namespace rx

@@ -82,6 +82,7 @@ cudaError_t run_gemm(RxDevice* d, const Step& st, const void* a, const void* b, 
   const GemmDesc& g = st.gemm;
   bool handled = false;
   cudaError_t e = run_gemm_tc(d, st, a, b, out, &handled);
+  d->last_gemm_tc = handled;
   if (handled) return e;
   dim3 grid((unsigned)((g.N + TN - 1) / TN), (unsigned)((g.M + TM - 1) / TM), (unsigned)g.batch);
   int64_t ao = st.prog.leaf[0].offset, bo = st.prog.leaf[1].offset;

@@ -1,0 +1,304 @@
+// bf16 dot_general on the 5th-generation tensor cores (tcgen05 + TMEM), fp32
+// accumulation -- the contraction Reactant emits for `W * X`
+// (src/stdlibs/LinearAlgebra.jl:274-330 -> src/Ops.jl:1075-1200) and the three
+// transposed-operand contractions Enzyme's reverse pass adds for its gradient.
+//
+// Persistent kernel, one CTA per SM, 128 x 256 output tiles:
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte
+//               swizzle) of the A (128 x 64) and B (256 x 64) k-slabs into a
+//               4-stage shared-memory ring, completion on `full` mbarriers;
+//   warp 1      allocates TMEM (512 columns = two 128 x 256 fp32 accumulators);
+//               one lane issues tcgen05.mma (M128 N256 K16, cta_group::1) four
+//               times per slab, releases the slab with tcgen05.commit -> `empty`,
+//               and hands a finished accumulator over with tcgen05.commit ->
+//               `acc_full`;
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (32 lanes x 32 columns per
+//               instruction), round once to the output type, store; then free the
+//               accumulator (`acc_empty`) so the next tile's MMAs overlap it.
+// Operands may be K-major or MN-major in memory (any of the four combinations):
+// the transposes of the reverse pass are expressed in the shared-memory and
+// instruction descriptors, never materialised.  No multicast, one CTA per tile.
+// Every mbarrier wait is bounded; a wait that runs out sets a status word and
+// all roles drain, TMEM is released and the kernel returns.
+#include <cuda_bf16.h>
+
+#include "rx_gemm.h"
+#include "rx_tma.h"
+
+namespace rx {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;   // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int kThreads = 192;
+constexpr int kEpiWarps = 4;
+constexpr long long kWaitLimit = 4000000;
+
+struct GemmParams {
+  int M, N, K;
+  int a_mn, b_mn;        // 1: operand is MN-major in memory (contiguous along M resp. N)
+  void* D;
+  long long ldd;
+  int out_bf16;
+  int tiles_m, tiles_n;
+  int* status;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+      "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]),
+        "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
+        "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (SWIZZLE_128B): start address, leading / stride
+// byte offsets in 16-byte units, descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                                                         const __grid_constant__ GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms are 1 KiB aligned
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ntiles = p.tiles_m * p.tiles_n;
+  const int kblocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kEpiWarps); }
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_p = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < ntiles && !*abort_p; t += gridDim.x) {
+        const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, kWaitLimit, abort_p)) { *abort_p = 1; *p.status = 3; break; }
+          unsigned char* sa = smem + stage * STAGE_BYTES;
+          unsigned char* sb = sa + A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (p.a_mn) {
+            tma_load_2d(sa, &tmA, m0, k0, &full[stage]);
+            tma_load_2d(sa + 8192, &tmA, m0 + 64, k0, &full[stage]);
+          } else {
+            tma_load_2d(sa, &tmA, k0, m0, &full[stage]);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tma_load_2d(sb + j * 8192, &tmB, n0 + 64 * j, k0, &full[stage]);
+          } else {
+            tma_load_2d(sb, &tmB, k0, n0, &full[stage]);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: D=f32, A=B=bf16, majors, N>>3, M>>4
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < ntiles && !*abort_p; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, kWaitLimit, abort_p)) { *abort_p = 1; *p.status = 4; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, kWaitLimit, abort_p)) { *abort_p = 1; *p.status = 5; ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+          // K-major: rows of 128 B, 8-row groups 1 KiB apart; a K=16 step is 32 B inside the row.
+          // MN-major: 64-element blocks of 8 KiB (LBO), 8-k groups 1 KiB apart (SBO); a K=16 step is 2 KiB.
+          const uint64_t adesc0 = p.a_mn ? smem_desc(sa, 8192, 1024) : smem_desc(sa, 16, 1024);
+          const uint64_t bdesc0 = p.b_mn ? smem_desc(sb, 8192, 1024) : smem_desc(sb, 16, 1024);
+          const uint64_t astep = p.a_mn ? (2048 >> 4) : (32 >> 4);
+          const uint64_t bstep = p.b_mn ? (2048 >> 4) : (32 >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) tc_mma(tmem_d, adesc0 + k * astep, bdesc0 + k * bstep, idesc, (kb | k) ? 1u : 0u);
+          tc_commit(&empty[stage]);  // slab may be refilled once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // epilogue warps: TMEM lane quadrant is warp % 4
+    const int quad = warp & 3;
+    int it = 0;
+    for (int t = blockIdx.x; t < ntiles && !*abort_p; t += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&acc_full[buf], acc_phase, kWaitLimit, abort_p)) { *abort_p = 1; *p.status = 6; break; }
+      tc_fence_after();
+      const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+      const long long m = (long long)tm * BM + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c, v);
+        tmem_ld_wait();
+        const long long n = (long long)tn * BN + c;
+        if (m < p.M) {
+          if (p.out_bf16) {
+            __nv_bfloat16* row = (__nv_bfloat16*)p.D + m * p.ldd + n;
+            if (n + 32 <= p.N && (((uintptr_t)row & 15) == 0)) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
+                __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+                __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+                o.x = *(uint32_t*)&b0; o.y = *(uint32_t*)&b1; o.z = *(uint32_t*)&b2; o.w = *(uint32_t*)&b3;
+                *(uint4*)(row + 8 * q) = o;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (n + j < p.N) row[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            }
+          } else {
+            float* row = (float*)p.D + m * p.ldd + n;
+            if (n + 32 <= p.N && (((uintptr_t)row & 15) == 0)) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) *(uint4*)(row + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (n + j < p.N) row[j] = __uint_as_float(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+bool make_operand_map(CUtensorMap* m, const __nv_bfloat16* base, bool mn_major, long long mn_extent, long long k_extent, long long pitch_elems, int box_mn) {
+  // K-major: inner dim = K (contiguous), rows = MN with pitch; box 64 (K) x box_mn
+  // MN-major: inner dim = MN (contiguous), rows = K with pitch; box 64 (MN) x 64 (K)
+  if (mn_major) return tma_make_2d(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, (uint64_t)mn_extent, (uint64_t)k_extent, (uint64_t)pitch_elems * 2, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  return tma_make_2d(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, (uint64_t)k_extent, (uint64_t)mn_extent, (uint64_t)pitch_elems * 2, 64, (uint32_t)box_mn, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+
+cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* b, void* out, bool* handled) {
+  *handled = false;
+  const GemmDesc& g = st.gemm;
+  if (getenv("RX_GEMM_SIMT")) return cudaSuccess;
+  if (g.in_dt != DT::BF16 || g.batch != 1) return cudaSuccess;
+  if (!(g.out_dt == DT::BF16 || g.out_dt == DT::F32)) return cudaSuccess;
+  const bool a_k = g.a_sk == 1, a_m = g.a_sm == 1, b_k = g.b_sk == 1, b_n = g.b_sn == 1;
+  if (!(a_k || a_m) || !(b_k || b_n)) return cudaSuccess;
+  const bool a_mn = !a_k, b_mn = !b_k;  // prefer K-major when a dimension has extent 1
+  const long long a_pitch = a_mn ? g.a_sk : g.a_sm, b_pitch = b_mn ? g.b_sk : g.b_sn;
+  const __nv_bfloat16* A = (const __nv_bfloat16*)a + st.prog.leaf[0].offset;
+  const __nv_bfloat16* B = (const __nv_bfloat16*)b + st.prog.leaf[1].offset;
+  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || (a_pitch % 8) || (b_pitch % 8) || a_pitch <= 0 || b_pitch <= 0) return cudaSuccess;
+  if (g.M < 1 || g.N < 1 || g.K < 1 || g.M > INT32_MAX || g.N > INT32_MAX || g.K > INT32_MAX) return cudaSuccess;
+  CUtensorMap tmA, tmB;
+  if (!make_operand_map(&tmA, A, a_mn, g.M, g.K, a_pitch, BM)) return cudaSuccess;
+  if (!make_operand_map(&tmB, B, b_mn, g.N, g.K, b_pitch, BN)) return cudaSuccess;
+  GemmParams p{};
+  p.M = (int)g.M;
+  p.N = (int)g.N;
+  p.K = (int)g.K;
+  p.a_mn = a_mn;
+  p.b_mn = b_mn;
+  p.D = out;
+  p.ldd = g.N;
+  p.out_bf16 = g.out_dt == DT::BF16;
+  p.tiles_m = (int)((g.M + BM - 1) / BM);
+  p.tiles_n = (int)((g.N + BN - 1) / BN);
+  int* dstatus = nullptr;
+  cudaHostGetDevicePointer(&dstatus, d->status, 0);
+  p.status = dstatus + 2;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr = true;
+  }
+  int grid = std::min(p.tiles_m * p.tiles_n, d->sm_count);
+  k_gemm_tc<<<grid, kThreads, smem, d->stream>>>(tmA, tmB, p);
+  ++d->launches;
+  *handled = true;
+  return cudaGetLastError();
+}
+
+}  // namespace rx

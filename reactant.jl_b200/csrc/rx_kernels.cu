@@ -27,7 +27,7 @@ constexpr int kThreads = 256;
 // the per-CTA partials in index order, so the result does not depend on which CTA
 // that is.  `ticket` counts finished CTAs and is reset for the next launch.
 __device__ __forceinline__ void finish_in_last_block(uint32_t mine, uint32_t* partials, unsigned* ticket, int code, uint32_t init_bits, const VmOut& out,
-                                                     uint32_t* sm) {
+                                                     uint32_t* sm, const FusedAllReduce& ar) {
   __shared__ bool is_last;
   if (threadIdx.x == 0) {
     partials[blockIdx.x] = mine;
@@ -49,8 +49,15 @@ __device__ __forceinline__ void finish_in_last_block(uint32_t mine, uint32_t* pa
   if (w == 0) {
     uint32_t x = lane < kThreads / 32 ? sm[lane] : red_identity(code);
     x = warp_red(code, x);
+    x = red_combine(code, init_bits, x);
+    if (ar.n > 1) {
+      // sharded reduce: exchange this device's partial with the mesh before storing (f32 sum only)
+      float total;
+      if (!mailbox_allreduce_warp(ar, u2f(x), &total)) total = u2f(x);
+      x = f2u(total);
+    }
     if (lane == 0) {
-      store_elem(out.ptr, out.offset, out.elem, red_combine(code, init_bits, x));
+      store_elem(out.ptr, out.offset, out.elem, x);
       *ticket = 0;
     }
   }
@@ -143,7 +150,7 @@ __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant_
 // ---- full reduce: pass 1 ---------------------------------------------------------
 // FAST_SIN_ADD: sum(sin(x) + y) with x = leaf 0, y = leaf 1, both contiguous f32.
 __global__ void __launch_bounds__(kThreads) k_reduce_full_sinadd(const float* __restrict__ x, const float* __restrict__ y, int64_t n, uint32_t* __restrict__ partials,
-                                                                 unsigned* ticket, uint32_t init_bits, VmOut out) {
+                                                                 unsigned* ticket, uint32_t init_bits, VmOut out, const __grid_constant__ FusedAllReduce ar) {
   __shared__ uint32_t sm[kThreads / 32];
   const float4* x4 = (const float4*)x;
   const float4* y4 = (const float4*)y;
@@ -169,12 +176,12 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_sinadd(const float* __
   }
   float v = (a0 + a1) + (a2 + a3);
   uint32_t r = block_red<kThreads>(R_FADD, f2u(v), sm);
-  finish_in_last_block(r, partials, ticket, R_FADD, init_bits, out, sm);
+  finish_in_last_block(r, partials, ticket, R_FADD, init_bits, out, sm, ar);
 }
 
 // Generic chain, all operands contiguous: interpreter on 4 lanes.
 __global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_constant__ VmProgram P, int64_t n, int code, uint32_t* __restrict__ partials,
-                                                                 unsigned* ticket, uint32_t init_bits) {
+                                                                 unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar) {
   __shared__ uint32_t sm[kThreads / 32];
   int64_t n4 = n >> 2;
   int64_t stride = (int64_t)gridDim.x * kThreads;
@@ -198,12 +205,12 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_co
   }
   uint32_t v = red_combine(code, red_combine(code, acc[0], acc[1]), red_combine(code, acc[2], acc[3]));
   v = block_red<kThreads>(code, v, sm);
-  finish_in_last_block(v, partials, ticket, code, init_bits, P.out[0], sm);
+  finish_in_last_block(v, partials, ticket, code, init_bits, P.out[0], sm, ar);
 }
 
 // Generic chain, strided operands.
 __global__ void __launch_bounds__(kThreads) k_reduce_full_generic(const __grid_constant__ VmProgram P, int64_t n, int code, uint32_t* __restrict__ partials,
-                                                                  unsigned* ticket, uint32_t init_bits) {
+                                                                  unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar) {
   __shared__ uint32_t sm[kThreads / 32];
   int64_t stride = (int64_t)gridDim.x * kThreads;
   uint32_t acc = red_identity(code);
@@ -215,7 +222,7 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_generic(const __grid_c
     acc = red_combine(code, acc, vm_eval_at(P, idx));
   }
   acc = block_red<kThreads>(code, acc, sm);
-  finish_in_last_block(acc, partials, ticket, code, init_bits, P.out[0], sm);
+  finish_in_last_block(acc, partials, ticket, code, init_bits, P.out[0], sm, ar);
 }
 
 // ---- reduce along one axis: [outer][red] with TPR threads per row --------------------
@@ -402,7 +409,9 @@ cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits) {
+cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, const FusedAllReduce* fused) {
+  FusedAllReduce ar{};
+  if (fused) ar = *fused;
   int64_t n = total_of(P);
   // 16 elements per thread per trip keeps four 128-bit loads in flight per operand
   int blocks = grid_for((n + 15) / 16, c.sm_count, 8);
@@ -413,11 +422,11 @@ cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code,
   if (vec && P.fast_id == FAST_SIN_ADD && code == R_FADD) {
     const float* x = (const float*)P.leaf[0].ptr + P.leaf[0].offset;
     const float* y = (const float*)P.leaf[1].ptr + P.leaf[1].offset;
-    k_reduce_full_sinadd<<<blocks, kThreads, 0, c.stream>>>(x, y, n, partials, ticket, init_bits, P.out[0]);
+    k_reduce_full_sinadd<<<blocks, kThreads, 0, c.stream>>>(x, y, n, partials, ticket, init_bits, P.out[0], ar);
   } else if (vec) {
-    k_reduce_full_linear<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits);
+    k_reduce_full_linear<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
   } else {
-    k_reduce_full_generic<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits);
+    k_reduce_full_generic<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
   }
   *c.launches += 1;
   return cudaGetLastError();

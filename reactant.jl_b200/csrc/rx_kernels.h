@@ -19,7 +19,8 @@ struct LaunchCtx {
 int red_code(RedK k, DT dt);
 
 cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P);
-cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits);
+// `fused` (optional): all-reduce the scalar over the mesh in the tail of the same kernel.
+cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, const FusedAllReduce* fused = nullptr);
 cudaError_t launch_reduce_row(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, int64_t outer, int64_t red_n);
 int reduce_col_splits(int64_t outer, int64_t red_n, int64_t inner, int sm_count);
 cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, int64_t outer, int64_t red_n,

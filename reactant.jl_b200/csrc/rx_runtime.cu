@@ -207,7 +207,7 @@ const char* kind_name(StepK k) {
 
 void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<DevRun>& runs);
 
-void run_one(RxExecutable* ex, const Step& st, DevRun& r) {
+void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* fused = nullptr) {
   RxDevice* d = r.dev;
   CK(cudaSetDevice(d->ordinal));
   LaunchCtx c = d->ctx();
@@ -221,11 +221,12 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r) {
     case StepK::Stencil: {
       VmProgram P = bind(st, r);
       CK(rx::run_stencil(d, st, P));
+      ps.kind = d->last_stencil_tma ? "stencil_tma" : "stencil_generic";
       break;
     }
     case StepK::ReduceFull: {
       VmProgram P = bind(st, r);
-      CK(launch_reduce_full(c, P, red_code(st.red, st.red_dt), init_bits(st)));
+      CK(launch_reduce_full(c, P, red_code(st.red, st.red_dt), init_bits(st), fused));
       break;
     }
     case StepK::ReduceRow: {
@@ -255,6 +256,7 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r) {
     }
     case StepK::Gemm: {
       CK(rx::run_gemm(d, st, slot_ptr(r, st.gemm.a_slot), slot_ptr(r, st.gemm.b_slot), slot_ptr(r, st.gemm.d_slot)));
+      ps.kind = d->last_gemm_tc ? "gemm_tc" : "gemm_simt";
       break;
     }
     case StepK::Copy: {
@@ -267,7 +269,20 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r) {
 }
 
 void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<DevRun>& runs) {
-  for (const Step& st : steps) {
+  for (size_t si = 0; si < steps.size(); ++si) {
+    const Step& st = steps[si];
+    // a full reduce of f32 followed by the all-reduce of its scalar: one kernel does both
+    if (st.kind == StepK::ReduceFull && si + 1 < steps.size() && steps[si + 1].kind == StepK::AllReduce && st.out_slot.size() == 1 &&
+        steps[si + 1].dst_slot == st.out_slot[0] && st.red == RedK::Add && st.red_dt == DT::F32 && st.prog.out[0].elem == EL_F32) {
+      std::vector<RxDevice*> devs;
+      for (auto& r : runs) devs.push_back(r.dev);
+      std::vector<FusedAllReduce> fused;
+      if (rx::prepare_fused_allreduce(ex->client, steps[si + 1], devs, &fused)) {
+        for (size_t k = 0; k < runs.size(); ++k) run_one(ex, st, runs[k], &fused[k]);
+        ++si;
+        continue;
+      }
+    }
     if (st.kind == StepK::Loop) {
       for (int64_t it = 0; it < st.trip; ++it) {
         run_steps(ex, st.body, runs);
@@ -559,6 +574,21 @@ void PjRtDeviceGetAllocatorStats(RxDevice* d, JLAllocatorStats* s) {
   s->peak_pool_bytes = d->peak_pool_bytes;
 }
 
+// Device-side waits are bounded; one that ran out leaves a code in the host-mapped status words.
+static void check_device_status(RxDevice* d) {
+  if (d->status[0]) {
+    int s = d->status[0];
+    d->status[0] = 0;
+    throw Error(RX_ERR_PEER_TIMEOUT, "a peer did not arrive at an all-reduce within the wait limit (status " + std::to_string(s) + ")");
+  }
+  for (int w = 1; w <= 2; ++w)
+    if (d->status[w]) {
+      int s = d->status[w];
+      d->status[w] = 0;
+      throw Error(RX_ERR_CUDA, std::string(w == 1 ? "stencil" : "gemm") + " kernel: an on-chip copy did not complete within the wait limit (status " + std::to_string(s) + "); results are invalid");
+    }
+}
+
 static RxBuffer* new_buffer(RxDevice* d, uint64_t ptype, size_t ndim, const int64_t* dims) {
   if (!d || !d->addressable) throw Error(RX_ERR_BAD_HANDLE, "device is null or not addressable from this process");
   DT dt = (DT)ptype;
@@ -618,11 +648,7 @@ void BufferToHost(RxBuffer* b, void* dst) {
     CK(cudaSetDevice(b->dev->ordinal));
     CK(cudaMemcpyAsync(dst, b->st->ptr, bytes, cudaMemcpyDeviceToHost, b->dev->stream));
     CK(cudaStreamSynchronize(b->dev->stream));
-    if (b->dev->status[0]) {
-      int s = b->dev->status[0];
-      b->dev->status[0] = 0;
-      throw Error(RX_ERR_PEER_TIMEOUT, "a peer did not arrive at an all-reduce within the wait limit (status " + std::to_string(s) + ")");
-    }
+    check_device_status(b->dev);
   }
   API_END_VOID
 }
@@ -688,11 +714,7 @@ void FutureAwait(RxFuture* f) {
   RxDevice* d = f->state->dev;
   CK(cudaSetDevice(d->ordinal));
   CK(cudaEventSynchronize(f->state->ev));
-  if (d->status[0]) {
-    int s = d->status[0];
-    d->status[0] = 0;
-    throw Error(RX_ERR_PEER_TIMEOUT, "a peer did not arrive at an all-reduce within the wait limit (status " + std::to_string(s) + ")");
-  }
+  check_device_status(d);
   API_END_VOID
 }
 

@@ -42,6 +42,7 @@ struct RxDevice : std::enable_shared_from_this<RxDevice> {
   uint32_t* scratch = nullptr;
   size_t scratch_words = 0;
   uint64_t launches = 0;
+  bool last_gemm_tc = false, last_stencil_tma = false;  // which kernel family the last such step used
   // profiling
   bool profiling = false;
   struct Span { std::string kind; cudaEvent_t a, b; };

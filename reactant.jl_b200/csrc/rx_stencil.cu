@@ -10,6 +10,7 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
 cudaError_t run_stencil(RxDevice* d, const Step& st, const VmProgram& P) {
   bool handled = false;
   cudaError_t e = run_stencil_tma(d, st, P, &handled);
+  d->last_stencil_tma = handled;
   if (handled) return e;
   return launch_map(d->ctx(), P);
 }

@@ -16,10 +16,9 @@
 // traced order and nothing is contracted into an FMA, so results are bit-exact
 // with the CPU evaluation.  TMA loads start on 16-byte boundaries (x is rounded
 // down to a multiple of 4 floats and the box is widened); no multicast is used.
-#include <cuda.h>
-
 #include "rx_device.cuh"
 #include "rx_stencil.h"
+#include "rx_tma.h"
 
 namespace rx {
 
@@ -43,39 +42,6 @@ struct StencilParams {
   int* status;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: returns false if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (long long i = 0; i < kWaitLimit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(smem_dst)),
-               "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
-               : "memory");
-}
-
 template <bool FAST5>
 __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ StencilParams p,
                                                      const __grid_constant__ VmProgram P) {
@@ -92,8 +58,7 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_fence_init();
   }
   __syncthreads();
 
@@ -112,7 +77,7 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
     uint32_t parity = (it / STAGES) & 1;
     int next = t + gridDim.x;
     if (threadIdx.x == 0 && next < ntiles) issue(next, (it + 1) % STAGES);  // that stage was drained before the last barrier
-    if (!mbar_wait(&bars[s], parity)) {
+    if (!mbar_wait(&bars[s], parity, kWaitLimit)) {
       failed = true;
       break;
     }
@@ -151,31 +116,15 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
     // a load may still be in flight into this CTA's shared memory: give it a bounded chance to land
     __syncthreads();
     if (threadIdx.x == 0)
-      for (int s = 0; s < STAGES; ++s) mbar_wait(&bars[s], 0) || mbar_wait(&bars[s], 1);
+      for (int s = 0; s < STAGES; ++s) mbar_wait(&bars[s], 0, kWaitLimit) || mbar_wait(&bars[s], 1, kWaitLimit);
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)p;
-    cudaGetLastError();
-  }
-  return fn;
 }
 
 }  // namespace
 
 cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, bool* handled) {
   *handled = false;
-  EncodeTiledFn enc = encode_fn();
+  EncodeTiledFn enc = tma_encode_fn();
   if (!enc) return cudaSuccess;
   if ((int)st.st_dy.size() > kMaxTaps || st.st_dy.size() != (size_t)P.n_leaves) return cudaSuccess;
   int max_dy = 0, max_dx = 0;

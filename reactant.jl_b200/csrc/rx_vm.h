@@ -91,4 +91,15 @@ struct VmProgram {
   VmInstr ins[kVmMaxInstr];
 };
 
+// Arguments of the NVLink mailbox all-reduce when it is fused into the tail of a
+// full reduce (n == 0: no all-reduce).  peer[r] points at rank r's mailbox:
+// 2 x kMailRanks 64-bit slots, indexed [epoch parity][sender rank].
+constexpr int kMailRanks = 32;
+struct FusedAllReduce {
+  unsigned long long* peer[kMailRanks];
+  int rank, n;
+  unsigned epoch;
+  int* status;
+};
+
 }  // namespace rx

@@ -241,6 +241,27 @@ def test_matmul_bf16(rx, ref, client, m, k, n):
     np.testing.assert_allclose(got, want, rtol=2 ** -7, atol=np.abs(want).max() * 2 ** -8)
 
 
+def test_native_kernel_families_are_the_ones_that_run(rx, ref, client):
+    """bf16 contractions must run on the tcgen05 kernel and stencil steps on the TMA kernel
+    (the CUDA-core / generic kernels exist only for shapes those cannot take)."""
+    dev = client.addressable_devices[0]
+    dev.profile()
+    dev.set_profiling(True)
+    try:
+        a = np.ones((256, 128), np.float32).astype(rx.bfloat16)
+        f = rx.compile(rx.programs.matmul(128, 256, 256, et="bf16"), client)
+        f(rx.to_rarray(a.T, client), rx.to_rarray(np.ones((256, 256), np.float32).astype(rx.bfloat16), client))
+        g = rx.compile(rx.programs.jacobi2d(300, 2), client)
+        z = np.zeros((300, 300), np.float32)
+        g(rx.to_rarray(z, client), rx.to_rarray(z, client))
+        dev.synchronize()
+    finally:
+        dev.set_profiling(False)
+    prof = dev.profile()
+    assert prof.get("gemm_tc", {}).get("launches") == 1 and "gemm_simt" not in prof, prof
+    assert prof.get("stencil_tma", {}).get("launches") == 2 and "stencil_generic" not in prof, prof
+
+
 def mlp_inputs(ref, F, H, O, B, seed=6):
     rng = np.random.default_rng(seed)
     bf = lambda a: ref.round_to_bf16(a.astype(np.float32))
