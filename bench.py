@@ -182,6 +182,12 @@ WORKLOADS = {
     "c3_jacobi2d_8192_100": lambda rx, c, r, w: setup_jacobi(rx, c),
     "c4_mlp_grad_bf16": lambda rx, c, r, w: setup_mlp(rx, c),
 }
+# reduced sizes of the same programs for profiler captures (a few hundred MB on the device, still larger than L2)
+WORKLOADS.update({
+    "prof_sinsum_2p27": lambda rx, c, r, w: setup_sinsum(rx, c, 1 << 27, r, w, seeds=(1, 2)),
+    "prof_logsumexp_32768x2048": lambda rx, c, r, w: setup_logsumexp(rx, c, 32768, 2048),
+    "prof_jacobi2d_8192_4": lambda rx, c, r, w: setup_jacobi(rx, c, 8192, 4),
+})
 SMALL_INPUT = {"c1_sinsum_2p24", "c4_mlp_grad_bf16"}  # working set near or below the 126 MB L2: flush between steps
 
 

@@ -147,6 +147,104 @@ __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant_
   }
 }
 
+
+// ---- 2-D "row-vector" access: 4 consecutive elements of the innermost dim, operands either
+// contiguous along it (stride 1) or broadcast along it (stride 0); any stride along the row dim.
+__device__ __forceinline__ void load4_rowvec(const VmLeaf& l, int64_t row, int64_t col, int drow, int dcol, uint32_t* d) {
+  int64_t off = l.offset + row * l.stride[drow];
+  if (l.stride[dcol] == 0) {
+    uint32_t u = load_elem(l.ptr, off, l.elem);
+    d[0] = d[1] = d[2] = d[3] = u;
+    return;
+  }
+  off += col;
+  switch (l.elem) {
+    case EL_F32:
+    case EL_I32: {
+      uint4 v = __ldg((const uint4*)((const uint32_t*)l.ptr + off));
+      d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+      break;
+    }
+    case EL_BF16: {
+      uint2 v = __ldg((const uint2*)((const uint16_t*)l.ptr + off));
+      d[0] = v.x << 16; d[1] = v.x & 0xFFFF0000u; d[2] = v.y << 16; d[3] = v.y & 0xFFFF0000u;
+      break;
+    }
+    default: {
+      uchar4 v = __ldg((const uchar4*)((const uint8_t*)l.ptr + off));
+      d[0] = v.x != 0; d[1] = v.y != 0; d[2] = v.z != 0; d[3] = v.w != 0;
+      break;
+    }
+  }
+}
+
+__device__ __forceinline__ void store4_rowvec(const VmOut& o, int64_t row, int64_t col, int drow, const uint32_t* s) {
+  VmOut t = o;
+  t.offset = o.offset + row * o.stride[drow] + col;
+  store4(t, 0, s);
+}
+
+// map over [rows][cols], 4 columns per thread
+__global__ void __launch_bounds__(kThreads) k_map_rows(const __grid_constant__ VmProgram P, int64_t rows, int64_t cols) {
+  const int64_t c4 = cols >> 2, total = rows * c4;
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  int64_t idx0[kMaxRank] = {0, 0, 0, 0};
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
+    int64_t row, col;
+    if (total < ((int64_t)1 << 31)) { uint32_t r = (uint32_t)i / (uint32_t)c4; row = r; col = ((uint32_t)i - r * (uint32_t)c4) * 4; }
+    else { row = i / c4; col = (i - row * c4) * 4; }
+    uint32_t R[kVmMaxRegs][4];
+    for (int k = 0; k < P.n_leaves; ++k) load4_rowvec(P.leaf[k], row, col, 0, 1, R[P.leaf[k].reg]);
+    vm_exec<4>(P, R, idx0);
+    for (int k = 0; k < P.n_outs; ++k) store4_rowvec(P.out[k], row, col, 0, R[P.out[k].reg]);
+  }
+}
+
+// full reduce over [rows][cols], 4 columns per thread
+__global__ void __launch_bounds__(kThreads) k_reduce_full_rows(const __grid_constant__ VmProgram P, int64_t rows, int64_t cols, int code, uint32_t* __restrict__ partials,
+                                                               unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar) {
+  __shared__ uint32_t sm[kThreads / 32];
+  const int64_t c4 = cols >> 2, total = rows * c4;
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  int64_t idx0[kMaxRank] = {0, 0, 0, 0};
+  uint32_t acc[4];
+  for (int v = 0; v < 4; ++v) acc[v] = red_identity(code);
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
+    int64_t row, col;
+    if (total < ((int64_t)1 << 31)) { uint32_t r = (uint32_t)i / (uint32_t)c4; row = r; col = ((uint32_t)i - r * (uint32_t)c4) * 4; }
+    else { row = i / c4; col = (i - row * c4) * 4; }
+    uint32_t R[kVmMaxRegs][4];
+    for (int k = 0; k < P.n_leaves; ++k) load4_rowvec(P.leaf[k], row, col, 0, 1, R[P.leaf[k].reg]);
+    vm_exec<4>(P, R, idx0);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) acc[v] = red_combine(code, acc[v], R[P.result_reg][v]);
+  }
+  uint32_t v = red_combine(code, red_combine(code, acc[0], acc[1]), red_combine(code, acc[2], acc[3]));
+  v = block_red<kThreads>(code, v, sm);
+  finish_in_last_block(v, partials, ticket, code, init_bits, P.out[0], sm, ar);
+}
+
+// column reduce over [red][inner] (outer == 1): each thread owns 4 adjacent columns and a slice of rows
+__global__ void __launch_bounds__(kThreads) k_reduce_col_vec(const __grid_constant__ VmProgram P, int code, int64_t red_n, int64_t inner, int nsplit,
+                                                             uint32_t* __restrict__ partials) {
+  const int64_t b4 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) * 4;
+  if (b4 >= inner) return;
+  const int split = blockIdx.y;
+  const int64_t chunk = (red_n + nsplit - 1) / nsplit;
+  const int64_t r0 = split * chunk, r1 = min(red_n, r0 + chunk);
+  int64_t idx0[kMaxRank] = {0, 0, 0, 0};
+  uint32_t acc[4];
+  for (int v = 0; v < 4; ++v) acc[v] = red_identity(code);
+  for (int64_t r = r0; r < r1; ++r) {
+    uint32_t R[kVmMaxRegs][4];
+    for (int k = 0; k < P.n_leaves; ++k) load4_rowvec(P.leaf[k], r, b4, 1, 2, R[P.leaf[k].reg]);
+    vm_exec<4>(P, R, idx0);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) acc[v] = red_combine(code, acc[v], R[P.result_reg][v]);
+  }
+  *(uint4*)(partials + (int64_t)split * inner + b4) = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+}
+
 // ---- full reduce: pass 1 ---------------------------------------------------------
 // FAST_SIN_ADD: sum(sin(x) + y) with x = leaf 0, y = leaf 1, both contiguous f32.
 __global__ void __launch_bounds__(kThreads) k_reduce_full_sinadd(const float* __restrict__ x, const float* __restrict__ y, int64_t n, uint32_t* __restrict__ partials,
@@ -376,6 +474,27 @@ bool vec_aligned(const VmProgram& P) {
   return true;
 }
 
+// Can [P.dim[drow]][P.dim[dcol]] be walked 4 columns at a time with aligned vector accesses?
+bool rowvec_ok(const VmProgram& P, int drow, int dcol, bool check_outs) {
+  auto esz = [](int e) { return e == EL_F32 || e == EL_I32 ? 4 : (e == EL_BF16 ? 2 : 1); };
+  if (P.dim[dcol] % 4) return false;
+  for (int k = 0; k < P.n_instr; ++k)
+    if (P.ins[k].op == VM_IOTA) return false;
+  for (int k = 0; k < P.n_leaves; ++k) {
+    const VmLeaf& l = P.leaf[k];
+    if (l.stride[dcol] == 0) continue;
+    int es = esz(l.elem);
+    if (l.stride[dcol] != 1 || (l.offset % 4) || (l.stride[drow] % 4) || ((uintptr_t)l.ptr % (4 * es))) return false;
+  }
+  if (check_outs)
+    for (int k = 0; k < P.n_outs; ++k) {
+      const VmOut& o = P.out[k];
+      int es = esz(o.elem);
+      if (o.stride[dcol] != 1 || (o.offset % 4) || (o.stride[drow] % 4) || ((uintptr_t)o.ptr % (4 * es))) return false;
+    }
+  return true;
+}
+
 int64_t total_of(const VmProgram& P) {
   int64_t n = 1;
   for (int d = 0; d < P.rank; ++d) n *= P.dim[d];
@@ -401,6 +520,8 @@ cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
   if (n == 0) return cudaSuccess;
   if (P.all_linear && vec_aligned(P)) {
     k_map_linear<<<grid_for((n + 3) / 4, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
+  } else if (P.rank == 2 && rowvec_ok(P, 0, 1, true)) {
+    k_map_rows<<<grid_for(n / 4, c.sm_count, 8), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
   } else {
     if (n < ((int64_t)1 << 31)) k_map_generic<true><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
     else k_map_generic<false><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
@@ -425,6 +546,8 @@ cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code,
     k_reduce_full_sinadd<<<blocks, kThreads, 0, c.stream>>>(x, y, n, partials, ticket, init_bits, P.out[0], ar);
   } else if (vec) {
     k_reduce_full_linear<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
+  } else if (P.rank == 2 && rowvec_ok(P, 0, 1, false)) {
+    k_reduce_full_rows<<<blocks, kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1], code, partials, ticket, init_bits, ar);
   } else {
     k_reduce_full_generic<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
   }
@@ -446,16 +569,22 @@ cudaError_t launch_reduce_row(const LaunchCtx& c, const VmProgram& P, int code, 
 }
 
 int reduce_col_splits(int64_t outer, int64_t red_n, int64_t inner, int sm_count) {
-  int64_t col_blocks = (inner + kThreads - 1) / kThreads;
+  int64_t col_blocks = (inner / 4 + kThreads - 1) / kThreads;
+  if (col_blocks < 1) col_blocks = 1;
   int64_t want = ((int64_t)sm_count * 8 + col_blocks * outer - 1) / (col_blocks * outer);
-  int64_t ns = std::max<int64_t>(1, std::min<int64_t>(want, std::min<int64_t>(64, (red_n + 15) / 16)));
+  int64_t ns = std::max<int64_t>(1, std::min<int64_t>(want, std::min<int64_t>(256, (red_n + 15) / 16)));
   return (int)ns;
 }
 
 cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, int64_t outer, int64_t red_n, int64_t inner, uint32_t* partials, int nsplit) {
   if (outer * inner == 0) return cudaSuccess;
-  dim3 grid((unsigned)((inner + kThreads - 1) / kThreads), (unsigned)nsplit, (unsigned)std::min<int64_t>(outer, 65535));
-  k_reduce_col<<<grid, kThreads, 0, c.stream>>>(P, code, outer, red_n, inner, nsplit, partials);
+  if (outer == 1 && rowvec_ok(P, 1, 2, false)) {
+    dim3 grid((unsigned)((inner / 4 + kThreads - 1) / kThreads), (unsigned)nsplit, 1);
+    k_reduce_col_vec<<<grid, kThreads, 0, c.stream>>>(P, code, red_n, inner, nsplit, partials);
+  } else {
+    dim3 grid((unsigned)((inner + kThreads - 1) / kThreads), (unsigned)nsplit, (unsigned)std::min<int64_t>(outer, 65535));
+    k_reduce_col<<<grid, kThreads, 0, c.stream>>>(P, code, outer, red_n, inner, nsplit, partials);
+  }
   k_reduce_col_finish<<<(unsigned)((outer * inner + kThreads - 1) / kThreads), kThreads, 0, c.stream>>>(partials, code, init_bits, outer, nsplit, inner, P.out[0]);
   *c.launches += 2;
   return cudaGetLastError();
