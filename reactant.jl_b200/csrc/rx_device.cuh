@@ -95,71 +95,104 @@ __device__ __forceinline__ uint32_t vm_cmp_i(int dir, int32_t a, int32_t b) {
 // lane 0 (only read by VM_IOTA, which the planner never vectorises).
 template <int V>
 __device__ __forceinline__ void vm_exec(const VmProgram& P, uint32_t (*R)[V], const int64_t* idx) {
+  uint32_t acc[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) acc[v] = 0;
   for (int pc = 0; pc < P.n_instr; ++pc) {
     const VmInstr in = P.ins[pc];
-    const uint32_t* A = R[in.a];
-    const uint32_t* B = R[in.b];
-    const uint32_t* C = R[in.c];
-    uint32_t out[V];
+    uint32_t A[V], B[V];
+    if (in.flags & VMF_A_ACC) {
 #pragma unroll
-    for (int v = 0; v < V; ++v) {
-      float a = u2f(A[v]), b = u2f(B[v]);
-      int32_t ia = (int32_t)A[v], ib = (int32_t)B[v];
-      uint32_t r;
-      switch (in.op) {
-        case VM_CONST: r = in.imm; break;
-        case VM_MOV: r = A[v]; break;
-        case VM_NEG: r = f2u(-a); break;
-        case VM_SIN: r = f2u(sinf(a)); break;
-        case VM_COS: r = f2u(cosf(a)); break;
-        case VM_EXP: r = f2u(expf(a)); break;
-        case VM_LOG: r = f2u(logf(a)); break;
-        case VM_TANH: r = f2u(tanhf(a)); break;
-        case VM_SQRT: r = f2u(sqrtf(a)); break;
-        case VM_RSQRT: r = f2u(1.0f / sqrtf(a)); break;
-        case VM_ABS: r = f2u(fabsf(a)); break;
-        case VM_LOG1P: r = f2u(log1pf(a)); break;
-        case VM_EXPM1: r = f2u(expm1f(a)); break;
-        case VM_FLOOR: r = f2u(floorf(a)); break;
-        case VM_CEIL: r = f2u(ceilf(a)); break;
-        case VM_SIGN: r = f2u((a != a) ? a : (float)((a > 0.f) - (a < 0.f))); break;
-        case VM_LOGISTIC: r = f2u(1.0f / (1.0f + expf(-a))); break;
-        case VM_RBF16: r = f2u(round_bf16(a)); break;
-        case VM_ADD: r = f2u(a + b); break;
-        case VM_SUB: r = f2u(a - b); break;
-        case VM_MUL: r = f2u(a * b); break;
-        case VM_DIV: r = f2u(a / b); break;
-        case VM_MAX: r = f2u(nan_max(a, b)); break;
-        case VM_MIN: r = f2u(nan_min(a, b)); break;
-        case VM_POW: r = f2u(powf(a, b)); break;
-        case VM_IADD: r = (uint32_t)(ia + ib); break;
-        case VM_ISUB: r = (uint32_t)(ia - ib); break;
-        case VM_IMUL: r = (uint32_t)(ia * ib); break;
-        case VM_IDIV: r = ib == 0 ? 0xFFFFFFFFu : ((ia == INT32_MIN && ib == -1) ? (uint32_t)INT32_MIN : (uint32_t)(ia / ib)); break;
-        case VM_IMAX: r = (uint32_t)max(ia, ib); break;
-        case VM_IMIN: r = (uint32_t)min(ia, ib); break;
-        case VM_INEG: r = (uint32_t)(-ia); break;
-        case VM_IABS: r = (uint32_t)abs(ia); break;
-        case VM_AND: r = A[v] & B[v]; break;
-        case VM_OR: r = A[v] | B[v]; break;
-        case VM_XOR: r = A[v] ^ B[v]; break;
-        case VM_NOT: r = ~A[v]; break;
-        case VM_LNOT: r = A[v] ? 0u : 1u; break;
-        case VM_FCMP: r = vm_cmp_f(in.c, a, b); break;
-        case VM_ICMP: r = vm_cmp_i(in.c, ia, ib); break;
-        case VM_SELECT: r = A[v] ? B[v] : C[v]; break;
-        case VM_I2F: r = f2u((float)ia); break;
-        case VM_F2I: r = (a != a) ? 0u : (uint32_t)(int32_t)fminf(fmaxf(truncf(a), -2147483648.f), 2147483520.f); break;
-        case VM_P2F: r = f2u(A[v] ? 1.f : 0.f); break;
-        case VM_F2P: r = a != 0.f; break;
-        case VM_I2P: r = ia != 0; break;
-        case VM_IOTA: r = (uint32_t)(int32_t)(idx[in.a] + (in.a == P.rank - 1 ? v : 0)); break;
-        default: r = 0; break;
-      }
-      out[v] = r;
+      for (int v = 0; v < V; ++v) A[v] = acc[v];
+    } else {
+#pragma unroll
+      for (int v = 0; v < V; ++v) A[v] = R[in.a][v];
     }
+    if (in.flags & VMF_B_ACC) {
 #pragma unroll
-    for (int v = 0; v < V; ++v) R[in.dst][v] = out[v];
+      for (int v = 0; v < V; ++v) B[v] = acc[v];
+    } else {
+#pragma unroll
+      for (int v = 0; v < V; ++v) B[v] = R[in.b][v];
+    }
+    // one dispatch per instruction; the lane loop lives inside each case
+#define RX_LANES(expr)                 \
+  {                                    \
+    _Pragma("unroll") for (int v = 0; v < V; ++v) { \
+      const float a = u2f(A[v]), b = u2f(B[v]);     \
+      const int32_t ia = (int32_t)A[v], ib = (int32_t)B[v]; \
+      (void)a; (void)b; (void)ia; (void)ib;         \
+      acc[v] = (expr);                 \
+    }                                  \
+  }                                    \
+  break
+    switch (in.op) {
+      case VM_CONST: RX_LANES(in.imm);
+      case VM_MOV: RX_LANES(A[v]);
+      case VM_NEG: RX_LANES(f2u(-a));
+      case VM_SIN: RX_LANES(f2u(sinf(a)));
+      case VM_COS: RX_LANES(f2u(cosf(a)));
+      case VM_EXP: RX_LANES(f2u(expf(a)));
+      case VM_LOG: RX_LANES(f2u(logf(a)));
+      case VM_TANH: RX_LANES(f2u(tanhf(a)));
+      case VM_SQRT: RX_LANES(f2u(sqrtf(a)));
+      case VM_RSQRT: RX_LANES(f2u(1.0f / sqrtf(a)));
+      case VM_ABS: RX_LANES(f2u(fabsf(a)));
+      case VM_LOG1P: RX_LANES(f2u(log1pf(a)));
+      case VM_EXPM1: RX_LANES(f2u(expm1f(a)));
+      case VM_FLOOR: RX_LANES(f2u(floorf(a)));
+      case VM_CEIL: RX_LANES(f2u(ceilf(a)));
+      case VM_SIGN: RX_LANES(f2u((a != a) ? a : (float)((a > 0.f) - (a < 0.f))));
+      case VM_LOGISTIC: RX_LANES(f2u(1.0f / (1.0f + expf(-a))));
+      case VM_RBF16: RX_LANES(f2u(round_bf16(a)));
+      case VM_ADD: RX_LANES(f2u(__fadd_rn(a, b)));
+      case VM_SUB: RX_LANES(f2u(__fsub_rn(a, b)));
+      case VM_MUL: RX_LANES(f2u(__fmul_rn(a, b)));
+      case VM_DIV: RX_LANES(f2u(a / b));
+      case VM_MAX: RX_LANES(f2u(nan_max(a, b)));
+      case VM_MIN: RX_LANES(f2u(nan_min(a, b)));
+      case VM_POW: RX_LANES(f2u(powf(a, b)));
+      case VM_IADD: RX_LANES((uint32_t)(ia + ib));
+      case VM_ISUB: RX_LANES((uint32_t)(ia - ib));
+      case VM_IMUL: RX_LANES((uint32_t)(ia * ib));
+      case VM_IDIV: RX_LANES(ib == 0 ? 0xFFFFFFFFu : ((ia == INT32_MIN && ib == -1) ? (uint32_t)INT32_MIN : (uint32_t)(ia / ib)));
+      case VM_IMAX: RX_LANES((uint32_t)max(ia, ib));
+      case VM_IMIN: RX_LANES((uint32_t)min(ia, ib));
+      case VM_INEG: RX_LANES((uint32_t)(-ia));
+      case VM_IABS: RX_LANES((uint32_t)abs(ia));
+      case VM_AND: RX_LANES(A[v] & B[v]);
+      case VM_OR: RX_LANES(A[v] | B[v]);
+      case VM_XOR: RX_LANES(A[v] ^ B[v]);
+      case VM_NOT: RX_LANES(~A[v]);
+      case VM_LNOT: RX_LANES(A[v] ? 0u : 1u);
+      case VM_FCMP: RX_LANES(vm_cmp_f(in.c, a, b));
+      case VM_ICMP: RX_LANES(vm_cmp_i(in.c, ia, ib));
+      case VM_SELECT: {
+        uint32_t C[V];
+        if (in.flags & VMF_C_ACC) {
+#pragma unroll
+          for (int v = 0; v < V; ++v) C[v] = acc[v];
+        } else {
+#pragma unroll
+          for (int v = 0; v < V; ++v) C[v] = R[in.c][v];
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = A[v] ? B[v] : C[v];
+        break;
+      }
+      case VM_I2F: RX_LANES(f2u((float)ia));
+      case VM_F2I: RX_LANES((a != a) ? 0u : (uint32_t)(int32_t)fminf(fmaxf(truncf(a), -2147483648.f), 2147483520.f));
+      case VM_P2F: RX_LANES(f2u(A[v] ? 1.f : 0.f));
+      case VM_F2P: RX_LANES((uint32_t)(a != 0.f));
+      case VM_I2P: RX_LANES((uint32_t)(ia != 0));
+      case VM_IOTA: RX_LANES((uint32_t)(int32_t)(idx[in.a] + (in.a == P.rank - 1 ? v : 0)));
+      default: RX_LANES(0u);
+    }
+#undef RX_LANES
+    if (in.flags & VMF_STORE) {
+#pragma unroll
+      for (int v = 0; v < V; ++v) R[in.dst][v] = acc[v];
+    }
   }
 }
 

@@ -46,6 +46,7 @@ struct GemmParams {
   int out_bf16;
   int tiles_m, tiles_n;
   int* status;
+  int exp_flags;  // experiment switches (0 in production)
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------
@@ -93,6 +94,39 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;
   return d;
+}
+
+
+// One epilogue step: 32 consecutive columns of row m, rounded once to the output type.
+__device__ __forceinline__ void store_row32(const GemmParams& p, long long m, long long n, const uint32_t* v) {
+  if (m >= p.M) return;
+  if (p.out_bf16) {
+    __nv_bfloat16* row = (__nv_bfloat16*)p.D + m * p.ldd + n;
+    if (n + 32 <= p.N && (((uintptr_t)row & 15) == 0)) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
+        __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+        __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+        o.x = *(uint32_t*)&b0; o.y = *(uint32_t*)&b1; o.z = *(uint32_t*)&b2; o.w = *(uint32_t*)&b3;
+        *(uint4*)(row + 8 * q) = o;
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (n + j < p.N) row[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+    }
+  } else {
+    float* row = (float*)p.D + m * p.ldd + n;
+    if (n + 32 <= p.N && (((uintptr_t)row & 15) == 0)) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) *(uint4*)(row + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (n + j < p.N) row[j] = __uint_as_float(v[j]);
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -203,36 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         uint32_t v[32];
         tmem_ld32(taddr + c, v);
         tmem_ld_wait();
-        const long long n = (long long)tn * BN + c;
-        if (m < p.M) {
-          if (p.out_bf16) {
-            __nv_bfloat16* row = (__nv_bfloat16*)p.D + m * p.ldd + n;
-            if (n + 32 <= p.N && (((uintptr_t)row & 15) == 0)) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 o;
-                __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
-                __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
-                __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
-                o.x = *(uint32_t*)&b0; o.y = *(uint32_t*)&b1; o.z = *(uint32_t*)&b2; o.w = *(uint32_t*)&b3;
-                *(uint4*)(row + 8 * q) = o;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (n + j < p.N) row[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
-            }
-          } else {
-            float* row = (float*)p.D + m * p.ldd + n;
-            if (n + 32 <= p.N && (((uintptr_t)row & 15) == 0)) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) *(uint4*)(row + 4 * q) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (n + j < p.N) row[j] = __uint_as_float(v[j]);
-            }
-          }
-        }
+        store_row32(p, m, (long long)tn * BN + c, v);
       }
       tc_fence_before();
       __syncwarp();
@@ -244,6 +249,201 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+
+// =======================================================================================
+// Two-CTA variant: a cluster of two CTAs (two SMs) computes one 256 x 256 tile with
+// tcgen05.mma.cta_group::2 (M256 N256 K16).  Each CTA stages its own 128 rows of A and
+// *half* of the B slab (128 of the 256 N rows), so per SM the shared-memory fill and the
+// L2->SM traffic per FLOP drop by a third against the one-CTA kernel, which is what its
+// mainloop is bound by.  The leader CTA (cluster rank 0) issues every MMA; the TMA loads of
+// both CTAs complete on the leader's `full` barrier (cta_group::2 loads, no multicast);
+// tcgen05.commit with a two-CTA mask releases slabs / publishes accumulators in both CTAs;
+// both CTAs' epilogue warps arrive on the leader's `acc_empty` barrier.  Each CTA's TMEM
+// holds its 128 accumulator rows x 256 columns, double buffered.
+// =======================================================================================
+constexpr int STAGES2 = 6;
+constexpr int A2_BYTES = 128 * BK * 2;      // 16 KiB: this CTA's rows of A
+constexpr int B2_BYTES = 128 * BK * 2;      // 16 KiB: this CTA's half of B
+constexpr int STAGE2_BYTES = A2_BYTES + B2_BYTES;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc2(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// commit -> the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void tc_commit2(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma2(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// TMA load of this CTA's box whose completion is counted on the *leader's* barrier
+// (same offset, CTA-rank bit of the shared::cluster address cleared).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(smem_dst)),
+               "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar) & 0xFEFFFFFFu)
+               : "memory");
+}
+// arrive on the barrier at this offset in the leader CTA
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  asm volatile(
+      "{\n"
+      ".reg .b32 ra;\n"
+      "mapa.shared::cluster.u32 ra, %0, 0;\n"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n"
+      "}\n" ::"r"(smem_u32(bar))
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1) k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                                                          const __grid_constant__ GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full[STAGES2], empty[STAGES2], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();      // 0 = leader
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int ntiles = p.tiles_m * p.tiles_n;     // 256 x 256 tiles
+  const int kblocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * kEpiWarps); }
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc2(&tmem_base_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_p = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = pair; t < ntiles && !*abort_p; t += npairs) {
+        const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+        const int m0 = tm * 256 + (int)rank * 128, n0 = tn * 256 + (int)rank * 128;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, kWaitLimit, abort_p)) { *abort_p = 1; *p.status = 13; break; }
+          unsigned char* sa = smem + stage * STAGE2_BYTES;
+          unsigned char* sb = sa + A2_BYTES;
+          if (p.exp_flags & 1) {  // experiment: no loads, MMAs run on whatever is in shared memory
+            if (rank == 0) mbar_arrive(&full[stage]);
+            if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+            continue;
+          }
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * STAGE2_BYTES);  // both CTAs' boxes land on the leader's barrier
+          const int k0 = kb * BK;
+          if (p.a_mn) {
+            tma_load_2d_pair(sa, &tmA, m0, k0, &full[stage]);
+            tma_load_2d_pair(sa + 8192, &tmA, m0 + 64, k0, &full[stage]);
+          } else {
+            tma_load_2d_pair(sa, &tmA, k0, m0, &full[stage]);
+          }
+          if (p.b_mn) {
+            tma_load_2d_pair(sb, &tmB, n0, k0, &full[stage]);
+            tma_load_2d_pair(sb + 8192, &tmB, n0 + 64, k0, &full[stage]);
+          } else {
+            tma_load_2d_pair(sb, &tmB, k0, n0, &full[stage]);
+          }
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) | ((uint32_t)(256 >> 3) << 17) |
+                             ((uint32_t)(256 >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int t = pair; t < ntiles && !*abort_p; t += npairs, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, kWaitLimit, abort_p)) { *abort_p = 1; *p.status = 14; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * 256;
+        bool ok = true;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, kWaitLimit, abort_p)) { *abort_p = 1; *p.status = 15; ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE2_BYTES);
+          const uint32_t sb = sa + A2_BYTES;
+          const uint64_t adesc0 = p.a_mn ? smem_desc(sa, 8192, 1024) : smem_desc(sa, 16, 1024);
+          const uint64_t bdesc0 = p.b_mn ? smem_desc(sb, 8192, 1024) : smem_desc(sb, 16, 1024);
+          const uint64_t astep = p.a_mn ? (2048 >> 4) : (32 >> 4);
+          const uint64_t bstep = p.b_mn ? (2048 >> 4) : (32 >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) tc_mma2(tmem_d, adesc0 + k * astep, bdesc0 + k * bstep, idesc, (kb | k) ? 1u : 0u);
+          tc_commit2(&empty[stage]);
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit2(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    int it = 0;
+    for (int t = pair; t < ntiles && !*abort_p; t += npairs, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&acc_full[buf], acc_phase, kWaitLimit, abort_p)) { *abort_p = 1; *p.status = 16; break; }
+      tc_fence_after();
+      const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+      const long long m = (long long)tm * 256 + rank * 128 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * 256;
+#pragma unroll 1
+      for (int c = 0; c < 256; c += 32) {
+        uint32_t v[32];
+        if (p.exp_flags & 2) break;  // experiment: skip the epilogue's TMEM reads and stores
+        tmem_ld32(taddr + c, v);
+        tmem_ld_wait();
+        if (!(p.exp_flags & 4)) store_row32(p, m, (long long)tn * 256 + c, v);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&acc_empty[buf]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees TMEM or exits while its peer may still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, 512);
   }
 }
 
@@ -270,9 +470,11 @@ cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* 
   const __nv_bfloat16* B = (const __nv_bfloat16*)b + st.prog.leaf[1].offset;
   if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || (a_pitch % 8) || (b_pitch % 8) || a_pitch <= 0 || b_pitch <= 0) return cudaSuccess;
   if (g.M < 1 || g.N < 1 || g.K < 1 || g.M > INT32_MAX || g.N > INT32_MAX || g.K > INT32_MAX) return cudaSuccess;
+  // two-CTA tiles (256 x 256 per SM pair) when the problem is large enough to fill them
+  const bool two_cta = !getenv("RX_GEMM_1CTA") && g.M >= 256 && g.N >= 256;
   CUtensorMap tmA, tmB;
   if (!make_operand_map(&tmA, A, a_mn, g.M, g.K, a_pitch, BM)) return cudaSuccess;
-  if (!make_operand_map(&tmB, B, b_mn, g.N, g.K, b_pitch, BN)) return cudaSuccess;
+  if (!make_operand_map(&tmB, B, b_mn, g.N, g.K, b_pitch, two_cta ? 128 : BN)) return cudaSuccess;
   GemmParams p{};
   p.M = (int)g.M;
   p.N = (int)g.N;
@@ -287,6 +489,41 @@ cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* 
   int* dstatus = nullptr;
   cudaHostGetDevicePointer(&dstatus, d->status, 0);
   p.status = dstatus + 2;
+  p.exp_flags = getenv("RX_GEMM_EXP") ? atoi(getenv("RX_GEMM_EXP")) : 0;
+  if (two_cta) {
+    p.tiles_m = (int)((g.M + 255) / 256);
+    p.tiles_n = (int)((g.N + 255) / 256);
+    const size_t smem2 = (size_t)STAGES2 * STAGE2_BYTES + 1024;
+    static bool attr2 = false;
+    static int max_clusters = 0;
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem2;
+    cfg.stream = d->stream;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    if (!attr2) {
+      cudaError_t e = cudaFuncSetAttribute(k_gemm_tc2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+      if (e != cudaSuccess) return e;
+      cfg.gridDim = dim3(d->sm_count & ~1);
+      if (cudaOccupancyMaxActiveClusters(&max_clusters, k_gemm_tc2, &cfg) != cudaSuccess || max_clusters < 1) {
+        cudaGetLastError();
+        max_clusters = d->sm_count / 2;
+      }
+      attr2 = true;
+    }
+    int pairs = std::min(p.tiles_m * p.tiles_n, std::min(max_clusters, d->sm_count / 2));
+    cfg.gridDim = dim3(2 * pairs);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k_gemm_tc2, tmA, tmB, p);
+    ++d->launches;
+    *handled = true;
+    return e != cudaSuccess ? e : cudaGetLastError();
+  }
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
   static bool attr = false;
   if (!attr) {

@@ -530,12 +530,28 @@ cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
   return cudaGetLastError();
 }
 
+// Resident CTAs per SM of a kernel (registers decide): grids are sized to exactly one
+// resident wave so that no CTA starts late and the partial count stays fixed per device.
+template <typename K>
+int resident_per_sm(K kernel) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kThreads, 0) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    n = 4;
+  }
+  return n;
+}
+
 cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, const FusedAllReduce* fused) {
   FusedAllReduce ar{};
   if (fused) ar = *fused;
   int64_t n = total_of(P);
+  static const int occ_sinadd = resident_per_sm(k_reduce_full_sinadd), occ_linear = resident_per_sm(k_reduce_full_linear),
+                   occ_rows = resident_per_sm(k_reduce_full_rows), occ_generic = resident_per_sm(k_reduce_full_generic);
+  const bool vec0 = P.all_linear && vec_aligned(P);
+  const int occ = (vec0 && P.fast_id == FAST_SIN_ADD && code == R_FADD) ? occ_sinadd : vec0 ? occ_linear : (P.rank == 2 && rowvec_ok(P, 0, 1, false)) ? occ_rows : occ_generic;
   // 16 elements per thread per trip keeps four 128-bit loads in flight per operand
-  int blocks = grid_for((n + 15) / 16, c.sm_count, 8);
+  int blocks = grid_for((n + 15) / 16, c.sm_count, occ);
   if ((size_t)blocks + 1 > c.scratch_words) return cudaErrorInvalidValue;
   uint32_t* partials = c.scratch;
   unsigned* ticket = (unsigned*)(c.scratch + c.scratch_words - 1);  // zeroed at device creation, reset by each launch

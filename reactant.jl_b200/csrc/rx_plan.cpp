@@ -497,6 +497,19 @@ struct Planner {
         if (L.nodes[q].leaf == (int)k) vl.reg = (uint8_t)reg[q];
       st.leaf_slot.push_back(L.leaves[k].slot);
     }
+    // uses of each value, to decide which results must reach the register file
+    std::vector<int> nuses(nn, 0);
+    for (size_t k = 0; k < nn; ++k) {
+      const VNode& n = L.nodes[k];
+      if (n.leaf >= 0 || n.op == VM_IOTA) continue;
+      for (int u : {n.a, n.b, n.c})
+        if (u >= 0) nuses[u]++;
+    }
+    std::vector<bool> is_output(nn, false);
+    for (auto& o : outs) is_output[o.vnode] = true;
+    if (result_vnode >= 0) is_output[result_vnode] = true;
+    int prev_instr_node = -1;  // node emitted as the previous instruction (its value sits in the accumulator)
+    int prev_instr_index = -1;
     int ni = 0;
     for (size_t k = 0; k < nn; ++k) {
       const VNode& n = L.nodes[k];
@@ -527,7 +540,19 @@ struct Planner {
           in.c = (uint8_t)(rc < 0 ? 0 : rc);
           if (n.op == VM_FCMP || n.op == VM_ICMP) in.c = (uint8_t)n.cmp;
           in.imm = n.imm;
+          // operands produced by the instruction just before this one are read from the accumulator
+          int acc_uses = 0;
+          if (prev_instr_node >= 0) {
+            if (n.a == prev_instr_node) { in.flags |= VMF_A_ACC; ++acc_uses; }
+            if (n.b == prev_instr_node) { in.flags |= VMF_B_ACC; ++acc_uses; }
+            if (n.c == prev_instr_node && n.op == VM_SELECT) { in.flags |= VMF_C_ACC; ++acc_uses; }
+            // the previous result needs no register-file copy if this instruction is its only consumer
+            if (acc_uses > 0 && acc_uses == nuses[prev_instr_node] && !is_output[prev_instr_node]) P.ins[prev_instr_index].flags &= (uint8_t)~VMF_STORE;
+          }
         }
+        in.flags |= VMF_STORE;  // cleared above by the next instruction when it is the sole, adjacent consumer
+        prev_instr_node = (int)k;
+        prev_instr_index = ni - 1;
       }
       if (last[k] < 0 && reg[k] >= 0 && L.nodes[k].leaf < 0) free_regs.push_back(reg[k]);  // dead value
     }

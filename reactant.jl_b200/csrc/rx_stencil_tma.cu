@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[STAGES];
   float* tile[STAGES];
-  const int stage_floats = BOX_W * (TH + HALO_H);
+  const int stage_floats = BOX_W * p.box_h;
   // 128-byte aligned stages
   uintptr_t base = ((uintptr_t)smem_raw + 127) & ~(uintptr_t)127;
 #pragma unroll
@@ -194,17 +194,18 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
   cudaHostGetDevicePointer(&dstatus, d->status, 0);
   sp.status = dstatus + 1;
 
-  size_t smem = (size_t)STAGES * BOX_W * (TH + HALO_H) * sizeof(float) + 128;
+  size_t smem = (size_t)STAGES * BOX_W * box_h * sizeof(float) + 128;  // 2 x 34 KiB for a radius-1 stencil; two CTAs per SM measured fastest
   bool fast = P.fast_id == FAST_STENCIL5_MUL && sp.n_taps == 5;
   auto kern = fast ? k_stencil_tma<true> : k_stencil_tma<false>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[fast]) {
+  static size_t attr_set[2] = {0, 0};
+  if (attr_set[fast] < smem) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attr_set[fast] = true;
+    attr_set[fast] = smem;
   }
   int ntiles = sp.tiles_x * sp.tiles_y;
-  int grid = std::min(ntiles, d->sm_count * 2);
+  int per_sm = (int)std::max<size_t>(1, std::min<size_t>(2, (size_t)(220 * 1024) / smem));
+  int grid = std::min(ntiles, d->sm_count * per_sm);
   kern<<<grid, 256, smem, d->stream>>>(tmap, sp, P);
   ++d->launches;
   *handled = true;

@@ -39,8 +39,15 @@ enum VmCmp : uint8_t { CMP_EQ = 0, CMP_NE, CMP_LT, CMP_LE, CMP_GT, CMP_GE };
 // storage element kinds a kernel can load/store
 enum VmElem : uint8_t { EL_F32 = 0, EL_BF16, EL_I32, EL_PRED /* 1 byte */, EL_I64, EL_F64 };
 
+// Operands normally come from the register file; when the matching VMF_*_ACC flag is
+// set the operand is the previous instruction's result, which the interpreter keeps in
+// machine registers ("accumulator").  A result is written back to the register file
+// only when VMF_STORE is set (it has a later, non-adjacent use or is an output).  For
+// the chain-shaped programs fusion produces this removes most register-file traffic.
+enum VmFlags : uint8_t { VMF_A_ACC = 1, VMF_B_ACC = 2, VMF_C_ACC = 4, VMF_STORE = 8 };
+
 struct VmInstr {
-  uint8_t op, dst, a, b, c, pad[3];
+  uint8_t op, dst, a, b, c, flags, pad[2];
   uint32_t imm;
 };
 

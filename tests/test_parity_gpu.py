@@ -225,7 +225,7 @@ def test_matmul_f32(rx, ref, client, m, k, n):
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("m,k,n", [(128, 128, 128), (256, 512, 384), (1024, 1024, 512), (200, 72, 136)])
+@pytest.mark.parametrize("m,k,n", [(128, 128, 128), (256, 512, 384), (1024, 1024, 512), (200, 72, 136), (520, 200, 392), (2048, 4096, 1024)])
 def test_matmul_bf16(rx, ref, client, m, k, n):
     rng = np.random.default_rng(k)
     a = ref.round_to_bf16(rng.standard_normal((k, m)).astype(np.float32))
@@ -274,7 +274,7 @@ def mlp_inputs(ref, F, H, O, B, seed=6):
     return [W1, b1, W2, b2, X, Y]
 
 
-@pytest.mark.parametrize("F,H,O,B", [(64, 128, 32, 256), (128, 256, 128, 128)])
+@pytest.mark.parametrize("F,H,O,B", [(64, 128, 32, 256), (128, 256, 128, 128), (256, 512, 256, 512), (320, 768, 264, 384)])
 def test_mlp_forward_and_gradients(rx, ref, client, F, H, O, B):
     ins = mlp_inputs(ref, F, H, O, B)
     text = rx.programs.mlp_grad(F, H, O, B)
