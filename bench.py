@@ -188,7 +188,17 @@ WORKLOADS.update({
     "prof_logsumexp_32768x2048": lambda rx, c, r, w: setup_logsumexp(rx, c, 32768, 2048),
     "prof_jacobi2d_8192_4": lambda rx, c, r, w: setup_jacobi(rx, c, 8192, 4),
 })
-SMALL_INPUT = {"c1_sinsum_2p24", "c4_mlp_grad_bf16"}  # working set near or below the 126 MB L2: flush between steps
+SMALL_INPUT = {"c1_sinsum_2p24", "c4_mlp_grad_bf16"}  # working set near or below the 126 MB L2: rotate input copies
+
+
+# DRAM traffic per algorithmic byte of the dominant kernel, from the ncu captures summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured launch; traffic grows in
+# proportion to the units processed, so the ratio carries over to the full-size launch).
+TRAFFIC_RATIO = {
+    "reduce_full": (1.073795e9 + 3.84e6) / (8 * (1 << 27)),          # profiles/k_reduce_full_sinadd__sinsum_2p27.md
+    "logsumexp": (268.457728e6 + 3.685e6) / (4 * 32768 * 2048 + 12 * 2048),  # profiles/k_logsumexp__32768x2048.md
+    "stencil_tma": (269.39392e6 + 219.197184e6) / (4 * 8192 * 8192 + 4 * 8190 * 8190),  # profiles/k_stencil_tma__jacobi2d_8192*.md
+}
 
 
 def work_per_step(wl):
@@ -199,46 +209,31 @@ def to_metric(wl, work, ms):
     return work / (ms * 1e-3) / (1e9 if wl["unit"] == "GB/s" else 1e12)
 
 
-def time_resident(rx, client, wl, steps, warmup, flush, dist):
-    """K steps with inputs resident in HBM, timed with CUDA events on the engine's stream."""
+def time_resident(rx, client, wl, steps, warmup, rotate, dist):
+    """K steps with inputs resident in HBM, timed with CUDA events on the engine's stream.
+    Workloads whose inputs would fit in L2 rotate over several resident copies of the inputs so that
+    the set touched between two uses of the same copy is larger than L2."""
     dev = client.addressable_devices[0]
     thunk = wl["thunk"]
-    donates = wl.get("donates", False)
-    args = wl["upload"]()
-    for _ in range(warmup):
-        if flush:
-            dev.flush_l2()
-        r = thunk(*args)
+    sets = [wl["upload"]() for _ in range(rotate)]
+    for k in range(warmup):
+        r = thunk(*sets[k % rotate])
     dev.synchronize()
     dev.profile()  # drop spans recorded so far
     launches0 = dev.kernel_launches()
     dist.barrier()
     dev.set_profiling(True)
-    spans_ms = []
-    if flush:
-        # events per step so that the flush is outside the measured time
-        total = 0.0
-        for _ in range(steps):
-            dev.flush_l2()
-            e0 = dev.record_event()
-            r = thunk(*args)
-            e1 = dev.record_event()
-            e1.synchronize()
-            total += e0.elapsed_ms(e1)
-        ms = total
-    else:
-        e0 = dev.record_event()
-        for _ in range(steps):
-            r = thunk(*args)
-        e1 = dev.record_event()
-        e1.synchronize()
-        ms = e0.elapsed_ms(e1)
+    e0 = dev.record_event()
+    for k in range(steps):
+        r = thunk(*sets[(warmup + k) % rotate])
+    e1 = dev.record_event()
+    e1.synchronize()
+    ms = e0.elapsed_ms(e1)
     dev.synchronize()
     dev.set_profiling(False)
     launches = dev.kernel_launches() - launches0
     prof = dev.profile()
     dist.barrier()
-    del spans_ms
     return ms, launches, prof, wl["read"](r)
 
 
@@ -347,10 +342,10 @@ def main():
             raise SystemExit("only the sinsum workloads shard; the others run as single-GPU configurations")
         allreduce = rx.dist.connect_collectives(rx, client, dist, os.environ.get("RX_ALLREDUCE", "mailbox"))
     wl = WORKLOADS[args.workload](rx, client, dist.rank, world)
-    flush = args.workload in SMALL_INPUT
+    rotate = 4 if args.workload in SMALL_INPUT else 1
     peaks = measured_peaks()
     with ClockSampler(dist.local_rank) as clk:  # sampling covers warm-up and the timed region
-        ms, launches, prof, result = time_resident(rx, client, wl, args.steps, args.warmup, flush, dist)
+        ms, launches, prof, result = time_resident(rx, client, wl, args.steps, args.warmup, rotate, dist)
     ms = dist.reduce(ms, "max")
     launches = int(dist.reduce(launches, "sum"))
     work = work_per_step(wl)
@@ -364,7 +359,10 @@ def main():
         per_launch_work = work / wl.get("launches_per_step", 1)
         achieved = to_metric(wl, per_launch_work, per_launch_ms)
         peak = peaks["hbm_gbs"] * world if wl["bound"] == "hbm" else peaks["bf16_tflops"]
-        roof = {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": wl["unit"], "frac": achieved / peak, "traffic": None,
+        traffic = None
+        if kind in TRAFFIC_RATIO:
+            traffic = TRAFFIC_RATIO[kind] * per_launch_work / world  # bytes per launch on one GPU
+        roof = {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": wl["unit"], "frac": achieved / peak, "traffic": traffic,
                 "kernel": wl["kernel"], "peak_source": f"of {peaks['source']}" + (f" x{world} GPUs" if world > 1 else ""),
                 "ms_per_launch": per_launch_ms}
     e2e = None
@@ -381,7 +379,7 @@ def main():
         line = {"metric": "fused map-reduce HBM GB/s" if wl["unit"] == "GB/s" else "dot_general TFLOP/s", "value": value, "unit": wl["unit"], "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 or "c5" in args.workload else "weak",
                 "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-                "config": {"workload": args.workload, "l2": "flushed between steps (256 MiB memset)" if flush else "inputs larger than L2", "all_reduce": allreduce,
+                "config": {"workload": args.workload, "l2": f"{rotate} rotating resident input sets, together larger than L2" if rotate > 1 else "inputs larger than L2", "all_reduce": allreduce,
                            "result": result if isinstance(result, float) else None},
                 "clocks": clk.summary(), "e2e": e2e, "gpu_launches": launches, "roofline": roof, "cpu_baseline": cpu, "profile_ms": prof}
         print(json.dumps(line), flush=True)

@@ -167,6 +167,15 @@ __device__ __forceinline__ void vm_exec(const VmProgram& P, uint32_t (*R)[V], co
       case VM_LNOT: RX_LANES(A[v] ? 0u : 1u);
       case VM_FCMP: RX_LANES(vm_cmp_f(in.c, a, b));
       case VM_ICMP: RX_LANES(vm_cmp_i(in.c, ia, ib));
+      case VM_ADDI: RX_LANES(f2u(__fadd_rn(a, u2f(in.imm))));
+      case VM_SUBI: RX_LANES(f2u(__fsub_rn(a, u2f(in.imm))));
+      case VM_RSUBI: RX_LANES(f2u(__fsub_rn(u2f(in.imm), a)));
+      case VM_MULI: RX_LANES(f2u(__fmul_rn(a, u2f(in.imm))));
+      case VM_DIVI: RX_LANES(f2u(a / u2f(in.imm)));
+      case VM_RDIVI: RX_LANES(f2u(u2f(in.imm) / a));
+      case VM_MAXI: RX_LANES(f2u(nan_max(a, u2f(in.imm))));
+      case VM_MINI: RX_LANES(f2u(nan_min(a, u2f(in.imm))));
+      case VM_MULADD:
       case VM_SELECT: {
         uint32_t C[V];
         if (in.flags & VMF_C_ACC) {
@@ -176,8 +185,13 @@ __device__ __forceinline__ void vm_exec(const VmProgram& P, uint32_t (*R)[V], co
 #pragma unroll
           for (int v = 0; v < V; ++v) C[v] = R[in.c][v];
         }
+        if (in.op == VM_SELECT) {
 #pragma unroll
-        for (int v = 0; v < V; ++v) acc[v] = A[v] ? B[v] : C[v];
+          for (int v = 0; v < V; ++v) acc[v] = A[v] ? B[v] : C[v];
+        } else {
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[v] = f2u(__fadd_rn(__fmul_rn(u2f(A[v]), u2f(B[v])), u2f(C[v])));
+        }
         break;
       }
       case VM_I2F: RX_LANES(f2u((float)ia));

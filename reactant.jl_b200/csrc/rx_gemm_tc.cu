@@ -46,7 +46,6 @@ struct GemmParams {
   int out_bf16;
   int tiles_m, tiles_n;
   int* status;
-  int exp_flags;  // experiment switches (0 in production)
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------
@@ -359,11 +358,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc2(const __grid_constant_
           if (!mbar_wait(&empty[stage], phase ^ 1, kWaitLimit, abort_p)) { *abort_p = 1; *p.status = 13; break; }
           unsigned char* sa = smem + stage * STAGE2_BYTES;
           unsigned char* sb = sa + A2_BYTES;
-          if (p.exp_flags & 1) {  // experiment: no loads, MMAs run on whatever is in shared memory
-            if (rank == 0) mbar_arrive(&full[stage]);
-            if (++stage == STAGES2) { stage = 0; phase ^= 1; }
-            continue;
-          }
           if (rank == 0) mbar_expect_tx(&full[stage], 2 * STAGE2_BYTES);  // both CTAs' boxes land on the leader's barrier
           const int k0 = kb * BK;
           if (p.a_mn) {
@@ -428,10 +422,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc2(const __grid_constant_
 #pragma unroll 1
       for (int c = 0; c < 256; c += 32) {
         uint32_t v[32];
-        if (p.exp_flags & 2) break;  // experiment: skip the epilogue's TMEM reads and stores
         tmem_ld32(taddr + c, v);
         tmem_ld_wait();
-        if (!(p.exp_flags & 4)) store_row32(p, m, (long long)tn * 256 + c, v);
+        store_row32(p, m, (long long)tn * 256 + c, v);
       }
       tc_fence_before();
       __syncwarp();
@@ -489,7 +482,6 @@ cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* 
   int* dstatus = nullptr;
   cudaHostGetDevicePointer(&dstatus, d->status, 0);
   p.status = dstatus + 2;
-  p.exp_flags = getenv("RX_GEMM_EXP") ? atoi(getenv("RX_GEMM_EXP")) : 0;
   if (two_cta) {
     p.tiles_m = (int)((g.M + 255) / 256);
     p.tiles_n = (int)((g.N + 255) / 256);

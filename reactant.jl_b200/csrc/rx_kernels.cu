@@ -184,19 +184,25 @@ __device__ __forceinline__ void store4_rowvec(const VmOut& o, int64_t row, int64
   store4(t, 0, s);
 }
 
-// map over [rows][cols], 4 columns per thread
+// map over [rows][cols], 4*U columns per thread (U = 2 halves the interpreter's per-lane dispatch cost)
+template <int U>
 __global__ void __launch_bounds__(kThreads) k_map_rows(const __grid_constant__ VmProgram P, int64_t rows, int64_t cols) {
-  const int64_t c4 = cols >> 2, total = rows * c4;
+  constexpr int V = 4 * U;
+  const int64_t cv = cols / V, total = rows * cv;
   const int64_t stride = (int64_t)gridDim.x * kThreads;
   int64_t idx0[kMaxRank] = {0, 0, 0, 0};
   for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
     int64_t row, col;
-    if (total < ((int64_t)1 << 31)) { uint32_t r = (uint32_t)i / (uint32_t)c4; row = r; col = ((uint32_t)i - r * (uint32_t)c4) * 4; }
-    else { row = i / c4; col = (i - row * c4) * 4; }
-    uint32_t R[kVmMaxRegs][4];
-    for (int k = 0; k < P.n_leaves; ++k) load4_rowvec(P.leaf[k], row, col, 0, 1, R[P.leaf[k].reg]);
-    vm_exec<4>(P, R, idx0);
-    for (int k = 0; k < P.n_outs; ++k) store4_rowvec(P.out[k], row, col, 0, R[P.out[k].reg]);
+    if (total < ((int64_t)1 << 31)) { uint32_t r = (uint32_t)i / (uint32_t)cv; row = r; col = (int64_t)((uint32_t)i - r * (uint32_t)cv) * V; }
+    else { row = i / cv; col = (i - row * cv) * V; }
+    uint32_t R[kVmMaxRegs][V];
+    for (int k = 0; k < P.n_leaves; ++k)
+#pragma unroll
+      for (int u = 0; u < U; ++u) load4_rowvec(P.leaf[k], row, col + 4 * u, 0, 1, R[P.leaf[k].reg] + 4 * u);
+    vm_exec<V>(P, R, idx0);
+    for (int k = 0; k < P.n_outs; ++k)
+#pragma unroll
+      for (int u = 0; u < U; ++u) store4_rowvec(P.out[k], row, col + 4 * u, 0, R[P.out[k].reg] + 4 * u);
   }
 }
 
@@ -521,7 +527,8 @@ cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
   if (P.all_linear && vec_aligned(P)) {
     k_map_linear<<<grid_for((n + 3) / 4, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
   } else if (P.rank == 2 && rowvec_ok(P, 0, 1, true)) {
-    k_map_rows<<<grid_for(n / 4, c.sm_count, 8), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
+    if (P.dim[1] % 8 == 0) k_map_rows<2><<<grid_for(n / 8, c.sm_count, 8), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
+    else k_map_rows<1><<<grid_for(n / 4, c.sm_count, 8), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
   } else {
     if (n < ((int64_t)1 << 31)) k_map_generic<true><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
     else k_map_generic<false><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);

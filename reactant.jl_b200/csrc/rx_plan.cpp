@@ -204,6 +204,10 @@ struct Lowering {
         break;
       }
       case Expr::Op: {
+        if (e->vmop == VM_MOV && e->kids.size() == 1) {  // widening converts and identities cost nothing
+          r = lower(e->kids[0], rmap);
+          break;
+        }
         VNode n{e->vmop};
         n.cmp = e->cmp;
         if (e->kids.size() > 0) n.a = lower(e->kids[0], rmap);
@@ -428,6 +432,64 @@ struct Planner {
     int vnode;
   };
 
+  // Strength-reduce the node list: constants become immediates of their consumer, and a
+  // multiply whose only consumer is an add merges into one multiply-add instruction (still
+  // two roundings, so results are unchanged).  Returns which nodes are no longer needed.
+  std::vector<bool> peephole(Lowering& L, const std::vector<OutSpec>& outs, int result_vnode) {
+    size_t nn = L.nodes.size();
+    std::vector<int> nuses(nn, 0);
+    std::vector<bool> pinned(nn, false), dead(nn, false);
+    for (auto& o : outs) pinned[o.vnode] = true;
+    if (result_vnode >= 0) pinned[result_vnode] = true;
+    auto count = [&]() {
+      std::fill(nuses.begin(), nuses.end(), 0);
+      for (size_t k = 0; k < nn; ++k) {
+        const VNode& n = L.nodes[k];
+        if (dead[k] || n.leaf >= 0 || n.op == VM_IOTA) continue;
+        for (int u : {n.a, n.b, n.c})
+          if (u >= 0) nuses[u]++;
+      }
+    };
+    auto is_const = [&](int v) { return v >= 0 && L.nodes[v].leaf < 0 && L.nodes[v].op == VM_CONST; };
+    for (size_t k = 0; k < nn; ++k) {
+      VNode& n = L.nodes[k];
+      if (n.leaf >= 0) continue;
+      int imm_op = -1, rimm_op = -1;
+      switch (n.op) {
+        case VM_ADD: imm_op = rimm_op = VM_ADDI; break;
+        case VM_MUL: imm_op = rimm_op = VM_MULI; break;
+        case VM_MAX: imm_op = rimm_op = VM_MAXI; break;
+        case VM_MIN: imm_op = rimm_op = VM_MINI; break;
+        case VM_SUB: imm_op = VM_SUBI; rimm_op = VM_RSUBI; break;
+        case VM_DIV: imm_op = VM_DIVI; rimm_op = VM_RDIVI; break;
+        default: break;
+      }
+      if (imm_op < 0) continue;
+      if (is_const(n.b)) { n.imm = L.nodes[n.b].imm; n.op = imm_op; n.b = -1; }
+      else if (is_const(n.a)) { n.imm = L.nodes[n.a].imm; n.op = rimm_op; n.a = n.b; n.b = -1; }
+    }
+    count();
+    for (size_t k = 0; k < nn; ++k) {
+      VNode& n = L.nodes[k];
+      if (n.leaf >= 0 || n.op != VM_ADD) continue;
+      for (int sw = 0; sw < 2; ++sw) {
+        int m = sw ? n.b : n.a, other = sw ? n.a : n.b;
+        if (m >= 0 && L.nodes[m].leaf < 0 && L.nodes[m].op == VM_MUL && nuses[m] == 1 && !pinned[m]) {
+          n.op = VM_MULADD;
+          n.a = L.nodes[m].a;
+          n.b = L.nodes[m].b;
+          n.c = other;
+          dead[m] = true;
+          break;
+        }
+      }
+    }
+    count();
+    for (size_t k = 0; k < nn; ++k)
+      if (L.nodes[k].leaf < 0 && nuses[k] == 0 && !pinned[k]) dead[k] = true;
+    return dead;
+  }
+
   // Turn lowered nodes into prog (register allocation, dim sorting/collapsing).
   void assemble(Step& st, Lowering& L, std::vector<OutSpec> outs, int result_vnode, const std::vector<int>& cls, bool by_output) {
     if (L.leaves.size() > (size_t)kVmMaxLeaves) throw Error(RX_ERR_PLAN, "fusion group reads more than " + std::to_string(kVmMaxLeaves) + " operands");
@@ -454,12 +516,14 @@ struct Planner {
     P.rank = (int)sp.dim.size();
     for (int d = 0; d < kMaxRank; ++d) P.dim[d] = d < P.rank ? sp.dim[d] : 1;
     std::vector<int64_t> cstr = canon_strides(sp.dim);
+    const std::vector<VNode> original_nodes = L.nodes;  // chain recognition below looks at the unreduced form
+    const std::vector<bool> dead = peephole(L, outs, result_vnode);
     // register allocation (linear scan over the node list, which is in topological order)
     size_t nn = L.nodes.size();
     std::vector<int> last(nn, -1);
     for (size_t k = 0; k < nn; ++k) {
       const VNode& n = L.nodes[k];
-      if (n.op == VM_IOTA) continue;
+      if (n.op == VM_IOTA || dead[k]) continue;
       for (int u : {n.a, n.b, n.c})
         if (u >= 0) last[u] = (int)k;
     }
@@ -501,7 +565,7 @@ struct Planner {
     std::vector<int> nuses(nn, 0);
     for (size_t k = 0; k < nn; ++k) {
       const VNode& n = L.nodes[k];
-      if (n.leaf >= 0 || n.op == VM_IOTA) continue;
+      if (n.leaf >= 0 || n.op == VM_IOTA || dead[k]) continue;
       for (int u : {n.a, n.b, n.c})
         if (u >= 0) nuses[u]++;
     }
@@ -513,7 +577,7 @@ struct Planner {
     int ni = 0;
     for (size_t k = 0; k < nn; ++k) {
       const VNode& n = L.nodes[k];
-      if (n.leaf < 0) {
+      if (n.leaf < 0 && !dead[k]) {
         // release operands whose last use is this node before allocating dst, so dst may reuse them
         int ra = n.op == VM_IOTA ? -1 : (n.a >= 0 ? reg[n.a] : -1), rb = n.b >= 0 ? reg[n.b] : -1, rc = n.c >= 0 ? reg[n.c] : -1;
         if (n.op != VM_IOTA)
@@ -545,7 +609,7 @@ struct Planner {
           if (prev_instr_node >= 0) {
             if (n.a == prev_instr_node) { in.flags |= VMF_A_ACC; ++acc_uses; }
             if (n.b == prev_instr_node) { in.flags |= VMF_B_ACC; ++acc_uses; }
-            if (n.c == prev_instr_node && n.op == VM_SELECT) { in.flags |= VMF_C_ACC; ++acc_uses; }
+            if (n.c == prev_instr_node && (n.op == VM_SELECT || n.op == VM_MULADD)) { in.flags |= VMF_C_ACC; ++acc_uses; }
             // the previous result needs no register-file copy if this instruction is its only consumer
             if (acc_uses > 0 && acc_uses == nuses[prev_instr_node] && !is_output[prev_instr_node]) P.ins[prev_instr_index].flags &= (uint8_t)~VMF_STORE;
           }
@@ -591,6 +655,7 @@ struct Planner {
       }
       st.prog.fast_id = FAST_NONE;
     }
+    L.nodes = original_nodes;
     detect_fast(st, L, result_vnode >= 0 ? result_vnode : (outs.empty() ? -1 : outs[0].vnode));
     cls_after = sp.cls;
   }

@@ -9,7 +9,7 @@
 //
 // Each CTA walks a strided list of 32 x 252 (or 248) output tiles.  One elected thread
 // issues a cp.async.bulk.tensor.2d (TMA) load of the tile plus its halo into a
-// two-stage shared-memory ring, signalled through an mbarrier; the other threads
+// two-stage shared-memory ring, signalled through mbarriers; the other threads
 // compute the previous tile meanwhile.  Halo rows/columns are re-read from L2,
 // not HBM (neighbouring tiles are in flight at the same time), so DRAM traffic
 // stays at one read and one write per element.  The adds are evaluated in the
@@ -24,9 +24,9 @@ namespace rx {
 
 namespace {
 
-constexpr int TH = 32, HALO_H = 8;
+constexpr int HALO_H = 8;
 constexpr int BOX_W = 256;                  // TMA boxes are at most 256 elements wide; a tile is BOX_W - halo columns
-constexpr int STAGES = 2;
+constexpr int STAGES = 2;                   // a deeper ring measured slower (more tiles in flight hurt DRAM locality)
 constexpr int kMaxTaps = 8;
 constexpr long long kWaitLimit = 2000000;  // bounded mbarrier polling
 
@@ -36,13 +36,14 @@ struct StencilParams {
   int x_base, y_base, x_shift;  // tensor coordinates of window column/row 0; columns skipped inside the box
   int box_h;
   int tw;       // output columns per tile
+  int cross;    // taps are (centre, left, right, up, down) of a radius-1 cross, in that order
   int n_taps;
   int dy[kMaxTaps], dx[kMaxTaps];
   int tiles_x, tiles_y;
   int* status;
 };
 
-template <bool FAST5>
+template <bool FAST5, int TH>
 __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ StencilParams p,
                                                      const __grid_constant__ VmProgram P) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -69,14 +70,16 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
   };
 
   int first = blockIdx.x;
-  if (threadIdx.x == 0 && first < ntiles) issue(first, 0);
+  if (threadIdx.x == 0)
+    for (int q = 0; q < STAGES - 1; ++q)
+      if (first + q * (int)gridDim.x < ntiles) issue(first + q * (int)gridDim.x, q);
   int it = 0;
   bool failed = false;
   for (int t = first; t < ntiles; t += gridDim.x, ++it) {
     int s = it % STAGES;
     uint32_t parity = (it / STAGES) & 1;
-    int next = t + gridDim.x;
-    if (threadIdx.x == 0 && next < ntiles) issue(next, (it + 1) % STAGES);  // that stage was drained before the last barrier
+    int next = t + (STAGES - 1) * (int)gridDim.x;
+    if (threadIdx.x == 0 && next < ntiles) issue(next, (it + STAGES - 1) % STAGES);  // that stage was drained before the last barrier
     if (!mbar_wait(&bars[s], parity, kWaitLimit)) {
       failed = true;
       break;
@@ -89,14 +92,30 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
       float* out = p.dst + p.dst_off + r0 * p.dst_ld + c;
       int rmax = (int)min((int64_t)TH, p.rows - r0);
       if (FAST5) {
-        const int o0 = p.dy[0] * BOX_W + p.dx[0], o1 = p.dy[1] * BOX_W + p.dx[1], o2 = p.dy[2] * BOX_W + p.dx[2], o3 = p.dy[3] * BOX_W + p.dx[3],
-                  o4 = p.dy[4] * BOX_W + p.dx[4];
         const float k = P.fast_c;
+        if (p.cross) {
+          // taps are centre, left, right, up, down in that evaluation order: slide a three-row window
+          // down the column so that each output costs three shared-memory reads instead of five
+          const float* q = sm + p.dx[0];  // column of the centre tap
+          float up = q[(p.dy[3]) * BOX_W], mid = q[p.dy[0] * BOX_W];
 #pragma unroll 4
-        for (int r = 0; r < rmax; ++r) {
-          const float* q = sm + r * BOX_W;
-          float v = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(q[o0], q[o1]), q[o2]), q[o3]), q[o4]);
-          out[(int64_t)r * p.dst_ld] = __fmul_rn(k, v);
+          for (int r = 0; r < rmax; ++r) {
+            const float* row = q + (r + p.dy[0]) * BOX_W;
+            const float left = row[-1], right = row[1], down = row[BOX_W];
+            float v = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(mid, left), right), up), down);
+            out[(int64_t)r * p.dst_ld] = __fmul_rn(k, v);
+            up = mid;
+            mid = down;
+          }
+        } else {
+          const int o0 = p.dy[0] * BOX_W + p.dx[0], o1 = p.dy[1] * BOX_W + p.dx[1], o2 = p.dy[2] * BOX_W + p.dx[2], o3 = p.dy[3] * BOX_W + p.dx[3],
+                    o4 = p.dy[4] * BOX_W + p.dx[4];
+#pragma unroll 4
+          for (int r = 0; r < rmax; ++r) {
+            const float* q = sm + r * BOX_W;
+            float v = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(q[o0], q[o1]), q[o2]), q[o3]), q[o4]);
+            out[(int64_t)r * p.dst_ld] = __fmul_rn(k, v);
+          }
         }
       } else {
         int64_t idx0[kMaxRank] = {0, 0, 0, 0};
@@ -149,6 +168,7 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
   if (((uintptr_t)src % 16) || (ld % 4) || ld > (int64_t)INT32_MAX || rows_total > (int64_t)INT32_MAX) return cudaSuccess;
   if (st.st_rows <= 0 || st.st_cols <= 0) { *handled = true; return cudaSuccess; }
 
+  const int TH = 32;  // 16 x 3 CTAs/SM and 64 x 1 CTA/SM measured within 2% of 32 x 2
   int box_h = TH + max_dy;
   // tensor map cache: (base pointer, ld, rows, box height)
   struct Key { const void* p; int64_t ld, rows; int bh; };
@@ -188,6 +208,11 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
   sp.tw = tw;
   sp.n_taps = (int)st.st_dy.size();
   for (int k = 0; k < sp.n_taps; ++k) { sp.dy[k] = st.st_dy[k]; sp.dx[k] = st.st_dx[k]; }
+  if (sp.n_taps == 5) {
+    const int cy = sp.dy[0], cx = sp.dx[0];
+    sp.cross = cy >= 1 && cx >= 1 && sp.dy[1] == cy && sp.dx[1] == cx - 1 && sp.dy[2] == cy && sp.dx[2] == cx + 1 && sp.dy[3] == cy - 1 && sp.dx[3] == cx &&
+               sp.dy[4] == cy + 1 && sp.dx[4] == cx;
+  }
   sp.tiles_x = (int)((st.st_cols + tw - 1) / tw);
   sp.tiles_y = (int)((st.st_rows + TH - 1) / TH);
   int* dstatus = nullptr;
@@ -196,15 +221,16 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
 
   size_t smem = (size_t)STAGES * BOX_W * box_h * sizeof(float) + 128;  // 2 x 34 KiB for a radius-1 stencil; two CTAs per SM measured fastest
   bool fast = P.fast_id == FAST_STENCIL5_MUL && sp.n_taps == 5;
-  auto kern = fast ? k_stencil_tma<true> : k_stencil_tma<false>;
+  auto kern = fast ? k_stencil_tma<true, 32> : k_stencil_tma<false, 32>;
   static size_t attr_set[2] = {0, 0};
   if (attr_set[fast] < smem) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     attr_set[fast] = smem;
   }
+  const int per_sm_env = 2;
   int ntiles = sp.tiles_x * sp.tiles_y;
-  int per_sm = (int)std::max<size_t>(1, std::min<size_t>(2, (size_t)(220 * 1024) / smem));
+  int per_sm = (int)std::max<size_t>(1, std::min<size_t>((size_t)per_sm_env, (size_t)(220 * 1024) / smem));
   int grid = std::min(ntiles, d->sm_count * per_sm);
   kern<<<grid, 256, smem, d->stream>>>(tmap, sp, P);
   ++d->launches;

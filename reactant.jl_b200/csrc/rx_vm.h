@@ -31,6 +31,10 @@ enum VmOp : uint8_t {
   // conversions
   VM_I2F, VM_F2I, VM_P2F /* pred->f32 */, VM_F2P /* f32 != 0 */, VM_I2P,
   VM_IOTA,    // dst = index along root dim `a` (as i32)
+  // f32 forms with an immediate operand (imm = raw bits) and the two-rounding multiply-add;
+  // produced by the planner's peephole pass, never by the parser
+  VM_ADDI, VM_SUBI /* a - imm */, VM_RSUBI /* imm - a */, VM_MULI, VM_DIVI /* a / imm */, VM_RDIVI /* imm / a */, VM_MAXI, VM_MINI,
+  VM_MULADD,  // dst = round(round(a * b) + c): same roundings as separate multiply and add
   VM_NUM_OPS
 };
 
