@@ -191,9 +191,24 @@ void open_mailboxes(RxClient* c, const uint8_t* handles, int n_global) {
       } else {
         cudaIpcMemHandle_t h;
         memcpy(&h, handles + (size_t)g * 64, 64);
-        void* p = nullptr;
-        cck(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
-        d->mail.peer[g] = (unsigned long long*)p;
+        // a handle exported by this very process cannot be opened through IPC: map it directly
+        unsigned long long* own = nullptr;
+        for (auto& o : c->devices) {
+          if (!o->mailbox) continue;
+          cudaIpcMemHandle_t mine;
+          cudaSetDevice(o->ordinal);
+          if (cudaIpcGetMemHandle(&mine, o->mailbox) == cudaSuccess && !memcmp(&mine, &h, 64)) own = o->mailbox;
+          cudaGetLastError();
+        }
+        cck(cudaSetDevice(d->ordinal), "cudaSetDevice");
+        if (own) {
+          d->mail.peer[g] = own;
+          d->mail_own[g] = true;
+        } else {
+          void* p = nullptr;
+          cck(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+          d->mail.peer[g] = (unsigned long long*)p;
+        }
       }
     }
     d->mail_ready = true;
@@ -213,7 +228,7 @@ void destroy_collectives(RxClient* c) {
       for (int g = 0; g < c->n_global(); ++g) {
         bool local = false;
         for (auto& o : c->devices) local = local || o->global_id == g;
-        if (!local && d->mail.peer[g]) cudaIpcCloseMemHandle(d->mail.peer[g]);
+        if (!local && d->mail.peer[g] && !d->mail_own[g]) cudaIpcCloseMemHandle(d->mail.peer[g]);
       }
     cudaFree(d->mailbox);
     d->mailbox = nullptr;

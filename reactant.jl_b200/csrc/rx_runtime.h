@@ -54,6 +54,7 @@ struct RxDevice : std::enable_shared_from_this<RxDevice> {
   unsigned long long* mailbox = nullptr;  // [2][kMaxRanks]
   int* status = nullptr;                  // device-visible status word (pinned host memory)
   MailTable mail{};
+  bool mail_own[kMaxRanks] = {};          // entry maps one of this process's own mailboxes (no IPC mapping to close)
   bool mail_ready = false;
   std::map<const void*, std::vector<uint8_t>> tmaps;  // tensor-map cache keyed by base pointer
 

@@ -61,3 +61,31 @@ def test_sharded_executable_refuses_a_partial_mesh(rx):
             f(X, X)
     finally:
         client.close()
+
+
+def test_column_sharded_logsumexp_needs_no_collective(rx, ref):
+    """logsumexp(x; dims=1) with the columns split over the mesh: every device reduces its own
+    columns, the result stays sharded, and no all-reduce is planned."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    ndev = 2
+    rows, cols = 4096, 64
+    text = rx.programs.logsumexp_dims1(rows, cols)
+    shard = ' {sdy.sharding = #sdy.sharding<@mesh, [{"x"}, {}]>}'
+    text = text.replace("mhlo.num_partitions = 1", f"mhlo.num_partitions = {ndev}")
+    text = text.replace("  func.func @main(%arg0: tensor<64x4096xf32>", f'  sdy.mesh @mesh = <["x"={ndev}]>\n  func.func @main(%arg0: tensor<64x4096xf32>{shard}')
+    plan = rx.plan_describe(text)
+    assert [s["kind"] for s in plan["steps"]] == ["logsumexp"], plan
+    client = rx.Client(allowed_devices=list(range(ndev)))
+    try:
+        a = np.random.default_rng(5).standard_normal((rows, cols)).astype(np.float32)  # Julia rows x cols
+        mesh = rx.Mesh(client.devices, ("x",))
+        X = rx.to_rarray(a, client, sharding=rx.NamedSharding(mesh, (None, "x")))     # columns (Julia dim 2) sharded
+        f = rx.compile(text, client)
+        r = f(X)
+        got = np.asarray(r)
+        want = ref.run_module(rx.programs.logsumexp_dims1(rows, cols), [ref.julia_to_xla(a)])[0].T
+        assert got.shape == want.shape == (1, cols)
+        np.testing.assert_allclose(got, want, rtol=ref.reduction_tolerance(rows))
+    finally:
+        client.close()
