@@ -302,7 +302,11 @@ void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::funct
   for (size_t k = 0; k < n_local; ++k) {
     RxDevice* d = dev(k);
     cck(cudaSetDevice(d->ordinal), "cudaSetDevice");
-    nck(nccl().AllReduce(ptr(k), ptr(k), (size_t)st.count, ncclFloat32, ncclSum, (ncclComm_t)c->nccl_comms[d->local_id], d->stream), "ncclAllReduce");
+    const ncclDataType_t ty = st.red_dt == DT::BF16 ? ncclBfloat16 : ncclFloat32;
+    cudaEvent_t ea = nullptr, eb = nullptr;
+    if (d->profiling) { cudaEventCreate(&ea); cudaEventCreate(&eb); cudaEventRecord(ea, d->stream); }
+    nck(nccl().AllReduce(ptr(k), ptr(k), (size_t)st.count, ty, ncclSum, (ncclComm_t)c->nccl_comms[d->local_id], d->stream), "ncclAllReduce");
+    if (d->profiling) { cudaEventRecord(eb, d->stream); d->spans.push_back({"all_reduce_nccl", ea, eb}); }
     ++d->launches;
   }
   nck(nccl().GroupEnd(), "ncclGroupEnd");

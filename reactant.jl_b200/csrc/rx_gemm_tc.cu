@@ -486,8 +486,10 @@ cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* 
     p.tiles_m = (int)((g.M + 255) / 256);
     p.tiles_n = (int)((g.N + 255) / 256);
     const size_t smem2 = (size_t)STAGES2 * STAGE2_BYTES + 1024;
-    static bool attr2 = false;
-    static int max_clusters = 0;
+    static bool attr2_dev[64] = {};          // function attributes are per device
+    static int max_clusters_dev[64] = {};
+    bool& attr2 = attr2_dev[d->ordinal & 63];
+    int& max_clusters = max_clusters_dev[d->ordinal & 63];
     cudaLaunchConfig_t cfg{};
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
@@ -517,7 +519,8 @@ cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* 
     return e != cudaSuccess ? e : cudaGetLastError();
   }
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
-  static bool attr = false;
+  static bool attr_dev[64] = {};
+  bool& attr = attr_dev[d->ordinal & 63];
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

@@ -391,6 +391,26 @@ struct Planner {
     if (e->k == Expr::Leaf) return prod(e->shape) == 1;
     return false;
   }
+  // Does the value of `e` not depend on its index along dim `dim`?  (Such a replicated value can be
+  // combined with a tensor sharded along that dim: every device evaluates it on its own index range.)
+  static bool invariant_along(const ExprP& e, int dim) {
+    switch (e->k) {
+      case Expr::Const: return true;
+      case Expr::Leaf: return dim < (int)e->shape.size() && e->shape[dim] == 1;
+      case Expr::Iota: return e->iota_dim != dim;
+      case Expr::Sym: return false;
+      case Expr::Op:
+        for (auto& k : e->kids)
+          if (!invariant_along(k, dim)) return false;
+        return true;
+      case Expr::View:
+        for (size_t d = 0; d < e->map.size(); ++d)
+          if (e->map[d].src == dim && !invariant_along(e->kids[0], (int)d)) return false;
+        return true;
+    }
+    return false;
+  }
+
   // host evaluation of scalar integer expressions (loop bounds, update offsets)
   static bool const_int(const ExprP& e, int64_t* out) {
     switch (e->k) {
@@ -804,8 +824,8 @@ struct Planner {
     }
     if (s >= 0)
       for (int v : ins)
-        if (shard[v] < 0 && !is_splat(env[v]))
-          throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op " + op.name + ": replicated non-splat operand combined with a sharded one");
+        if (shard[v] < 0 && !is_splat(env[v]) && !invariant_along(env[v], s))
+          throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op " + op.name + ": a replicated operand that varies along the sharded dimension is combined with a sharded one");
     return s;
   }
 
@@ -1302,9 +1322,23 @@ struct Planner {
 
   void plan_dot(const Op& op) {
     int v = op.out[0], a = op.in[0], b = op.in[1];
-    if (shard[a] >= 0 || shard[b] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general on sharded operands");
     ExprP A = env[a], B = env[b];
-    Type rt = m.values[v].type;
+    // SPMD rule for contractions on a 1-D mesh: a sharded free dimension stays sharded in the result;
+    // a contraction over a dimension sharded in both operands gives per-device partial products that
+    // are summed with an all-reduce; anything else is not expressible without resharding.
+    bool partial_sum = false;
+    shard[v] = -1;
+    if (shard[a] >= 0 || shard[b] >= 0) {
+      if (op.lcontract.size() != 1 || !op.lbatch.empty()) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general: sharded batched contraction");
+      int lc0 = (int)op.lcontract[0], rc0 = (int)op.rcontract[0];
+      bool a_c = shard[a] == lc0, b_c = shard[b] == rc0;
+      if (a_c && b_c) partial_sum = true;
+      else if (a_c || b_c) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general: contraction dimension sharded in only one operand");
+      else if (shard[a] >= 0 && shard[b] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general: both operands sharded along free dimensions");
+      else if (shard[a] >= 0) shard[v] = 0;                                  // result dims are (lhs free, rhs free)
+      else shard[v] = (int)A->shape.size() - 1;
+    }
+    Type rt = local_type(v);
     if (!(A->dt == B->dt && (A->dt == DT::BF16 || A->dt == DT::F32)))
       throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element types for stablehlo.dot_general: " + std::string(dt_name(A->dt)) + " x " + dt_name(B->dt));
     if (op.lcontract.size() != 1 || op.lbatch.size() > 1)
@@ -1357,6 +1391,16 @@ struct Planner {
          << dt_name(g.in_dt) << "->" << dt_name(g.out_dt) << " fp32 accumulate";
     st.note = note.str();
     cur->push_back(std::move(st));
+    if (partial_sum) {
+      if (rt.dt != DT::F32 && rt.dt != DT::BF16) throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type for all_reduce");
+      Step ar;
+      ar.kind = StepK::AllReduce;
+      ar.dst_slot = dst;
+      ar.count = rt.numel();
+      ar.red_dt = rt.dt;
+      ar.note = "all_reduce(sum) of per-device partial products";
+      cur->push_back(std::move(ar));
+    }
     env[v] = leaf(dst, rt);
   }
 

@@ -222,11 +222,12 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
   size_t smem = (size_t)STAGES * BOX_W * box_h * sizeof(float) + 128;  // 2 x 34 KiB for a radius-1 stencil; two CTAs per SM measured fastest
   bool fast = P.fast_id == FAST_STENCIL5_MUL && sp.n_taps == 5;
   auto kern = fast ? k_stencil_tma<true, 32> : k_stencil_tma<false, 32>;
-  static size_t attr_set[2] = {0, 0};
-  if (attr_set[fast] < smem) {
+  static size_t attr_set[64][2] = {};  // function attributes are per device
+  size_t& have = attr_set[d->ordinal & 63][fast];
+  if (have < smem) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    attr_set[fast] = smem;
+    have = smem;
   }
   const int per_sm_env = 2;
   int ntiles = sp.tiles_x * sp.tiles_y;

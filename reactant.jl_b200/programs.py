@@ -139,7 +139,7 @@ def jacobi2d(n: int, steps: int, form: str = "dus") -> str:
 """
 
 
-def mlp_grad(features: int = 1024, hidden: int = 4096, out: int = 1024, batch: int = 4096) -> str:
+def mlp_grad(features: int = 1024, hidden: int = 4096, out: int = 1024, batch: int = 4096, num_partitions: int = 1) -> str:
     """Two-layer MLP forward + reverse-mode gradient, as it reaches the runtime
     after Enzyme's pass has synthesised the reverse program: five dot_generals
     (two forward, three transposed-operand backward), gelu(tanh) and its
@@ -148,6 +148,10 @@ def mlp_grad(features: int = 1024, hidden: int = 4096, out: int = 1024, batch: i
     Julia shapes: W1 hidden x features (bf16), b1 hidden (f32), W2 out x hidden
     (bf16), b2 out (f32), X features x batch (bf16), Y out x batch (f32).
     Results: dW1, db1, dW2, db2, loss.
+
+    With num_partitions > 1 the batch is split over a 1-D mesh (data parallelism): X and Y carry
+    `sdy.sharding` on their batch dimension, the weights are replicated, and every gradient is a
+    sum over devices, so the runtime has to all-reduce them.
     """
     F, H, O, B = features, hidden, out, batch
     tW1, tW2, tX, tY = _t([F, H], "bf16"), _t([H, O], "bf16"), _t([B, F], "bf16"), _t([B, O])
@@ -160,8 +164,10 @@ def mlp_grad(features: int = 1024, hidden: int = 4096, out: int = 1024, batch: i
     def k(v, t):
         return f"stablehlo.constant dense<{v:.9e}> : {t}"
 
-    return f"""module @reactant_mlp_grad attributes {{mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64}} {{
-  func.func @main(%arg0: {tW1}, %arg1: {tb1}, %arg2: {tW2}, %arg3: {tb2}, %arg4: {tX}, %arg5: {tY}) -> ({tW1}, {tb1}, {tW2}, {tb2}, tensor<f32>) {{
+    sh = ' {sdy.sharding = #sdy.sharding<@mesh, [{"x"}, {}]>}' if num_partitions > 1 else ""
+    mesh = f'  sdy.mesh @mesh = <["x"={num_partitions}]>\n' if num_partitions > 1 else ""
+    return f"""module @reactant_mlp_grad attributes {{mhlo.num_partitions = {num_partitions} : i64, mhlo.num_replicas = 1 : i64}} {{
+{mesh}  func.func @main(%arg0: {tW1}, %arg1: {tb1}, %arg2: {tW2}, %arg3: {tb2}, %arg4: {tX}{sh}, %arg5: {tY}{sh}) -> ({tW1}, {tb1}, {tW2}, {tb2}, tensor<f32>) {{
     %zero = stablehlo.constant dense<0.000000e+00> : tensor<f32>
     %half = {k(0.5, tZ1)}
     %one = {k(1.0, tZ1)}

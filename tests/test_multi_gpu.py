@@ -89,3 +89,45 @@ def test_column_sharded_logsumexp_needs_no_collective(rx, ref):
         np.testing.assert_allclose(got, want, rtol=ref.reduction_tolerance(rows))
     finally:
         client.close()
+
+
+@pytest.mark.parametrize("transport", ["mailbox", "nccl"])
+def test_data_parallel_mlp_gradients(rx, ref, transport, monkeypatch):
+    """Batch-sharded MLP forward + gradients: local GEMMs, then all-reduce of every gradient and of
+    the loss (vector payloads go through NCCL, the scalar through the fused mailbox path unless
+    NCCL is forced).  Must match the unsharded oracle."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    ndev = 2
+    monkeypatch.setenv("RX_ALLREDUCE", transport)
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    F, H, O, B = 64, 128, 32, 512
+    rng = np.random.default_rng(6)
+    bf = lambda a: ref.round_to_bf16(a.astype(np.float32))
+    X = bf(rng.standard_normal((B, F)))
+    W1 = bf(rng.standard_normal((F, H)) / np.sqrt(F))
+    W2 = bf(rng.standard_normal((H, O)) / np.sqrt(H))
+    b1 = (0.01 * rng.standard_normal(H)).astype(np.float32)
+    b2 = (0.01 * rng.standard_normal(O)).astype(np.float32)
+    Y = rng.standard_normal((B, O)).astype(np.float32)
+    want = ref.run_module(rx.programs.mlp_grad(F, H, O, B), [W1, b1, W2, b2, X, Y])
+    client = rx.Client(allowed_devices=list(range(ndev)))
+    try:
+        mesh = rx.Mesh(client.devices, ("x",))
+        rep2, rep1 = rx.NamedSharding(mesh, (None, None)), rx.NamedSharding(mesh, (None,))
+        batch = rx.NamedSharding(mesh, (None, "x"))          # Julia (features, batch): batch is dim 2
+        up = lambda a, sh, bf16=False: rx.to_rarray(a.T.astype(rx.bfloat16) if bf16 else a.T, client, sharding=sh)
+        args = [up(W1, rep2, True), up(b1, rep1), up(W2, rep2, True), up(b2, rep1), up(X, batch, True), up(Y, batch)]
+        f = rx.compile(rx.programs.mlp_grad(F, H, O, B, num_partitions=ndev), client)
+        kinds = [s["kind"] for s in f.describe()["steps"]]
+        assert kinds.count("all_reduce") == 5 and kinds.count("gemm") == 5
+        outs = f(*args)
+        for name, o, w in zip(("dW1", "db1", "dW2", "db2", "loss"), outs, want):
+            assert len(o.data) == ndev
+            per_dev = [np.asarray(b.to_host()).astype(np.float32) for b in o.data]
+            assert all(np.array_equal(per_dev[0], p) for p in per_dev[1:]), f"{name} differs between devices"
+            g = per_dev[0]
+            scale = np.abs(w).max()
+            assert np.abs(g - w).max() <= 2e-2 * scale, (name, np.abs(g - w).max(), scale)
+    finally:
+        client.close()
