@@ -367,13 +367,27 @@ __global__ void __launch_bounds__(kThreads) k_reduce_col(const __grid_constant__
   }
 }
 
+// Second pass of the strided-axis reduce: one CTA per 32 adjacent columns of one outer index.  Warp w
+// adds the partials of splits w, w+8, ... (lane = column, so every read is a coalesced 128-byte row);
+// the eight warp results are then combined in warp order.  The order is fixed, so the result is
+// deterministic.
 __global__ void __launch_bounds__(kThreads) k_reduce_col_finish(const uint32_t* __restrict__ partials, int code, uint32_t init_bits, int64_t outer, int nsplit, int64_t inner, VmOut out) {
-  int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-  if (t >= outer * inner) return;
-  int64_t o = t / inner, b = t - o * inner;
+  __shared__ uint32_t sm[kThreads / 32][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int64_t col_blocks = (inner + 31) / 32;
+  const int64_t o = blockIdx.x / col_blocks;
+  const int64_t b = (blockIdx.x - o * col_blocks) * 32 + lane;
   uint32_t acc = red_identity(code);
-  for (int s = 0; s < nsplit; ++s) acc = red_combine(code, acc, partials[(o * nsplit + s) * inner + b]);
-  store_elem(out.ptr, out.offset + o * out.stride[0] + b * out.stride[2], out.elem, red_combine(code, init_bits, acc));
+  if (b < inner)
+    for (int s = w; s < nsplit; s += kThreads / 32) acc = red_combine(code, acc, partials[(o * nsplit + s) * inner + b]);
+  sm[w][lane] = acc;
+  __syncthreads();
+  if (w == 0 && b < inner) {
+    uint32_t t = sm[0][lane];
+#pragma unroll
+    for (int q = 1; q < kThreads / 32; ++q) t = red_combine(code, t, sm[q][lane]);
+    store_elem(out.ptr, out.offset + o * out.stride[0] + b * out.stride[2], out.elem, red_combine(code, init_bits, t));
+  }
 }
 
 // ---- logsumexp over rows ----------------------------------------------------------------
@@ -608,7 +622,7 @@ cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, 
     dim3 grid((unsigned)((inner + kThreads - 1) / kThreads), (unsigned)nsplit, (unsigned)std::min<int64_t>(outer, 65535));
     k_reduce_col<<<grid, kThreads, 0, c.stream>>>(P, code, outer, red_n, inner, nsplit, partials);
   }
-  k_reduce_col_finish<<<(unsigned)((outer * inner + kThreads - 1) / kThreads), kThreads, 0, c.stream>>>(partials, code, init_bits, outer, nsplit, inner, P.out[0]);
+  k_reduce_col_finish<<<(unsigned)(outer * ((inner + 31) / 32)), kThreads, 0, c.stream>>>(partials, code, init_bits, outer, nsplit, inner, P.out[0]);
   *c.launches += 2;
   return cudaGetLastError();
 }
