@@ -93,6 +93,31 @@ __device__ __forceinline__ uint32_t vm_cmp_i(int dir, int32_t a, int32_t b) {
 // Evaluate the instruction list on V lanes.  R holds the registers; leaves have
 // already been loaded into their registers.  `idx` is the root multi-index of
 // lane 0 (only read by VM_IOTA, which the planner never vectorises).
+// Register-file rows are moved 128 bits at a time (the rows are 16-byte aligned local memory).
+template <int V>
+__device__ __forceinline__ void vm_ldrow(const uint32_t* src, uint32_t* dst) {
+  if constexpr (V % 4 == 0) {
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q) {
+      const uint4 t = *reinterpret_cast<const uint4*>(src + 4 * q);
+      dst[4 * q] = t.x; dst[4 * q + 1] = t.y; dst[4 * q + 2] = t.z; dst[4 * q + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < V; ++v) dst[v] = src[v];
+  }
+}
+template <int V>
+__device__ __forceinline__ void vm_strow(uint32_t* dst, const uint32_t* src) {
+  if constexpr (V % 4 == 0) {
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q) *reinterpret_cast<uint4*>(dst + 4 * q) = make_uint4(src[4 * q], src[4 * q + 1], src[4 * q + 2], src[4 * q + 3]);
+  } else {
+#pragma unroll
+    for (int v = 0; v < V; ++v) dst[v] = src[v];
+  }
+}
+
 template <int V>
 __device__ __forceinline__ void vm_exec(const VmProgram& P, uint32_t (*R)[V], const int64_t* idx) {
   uint32_t acc[V];
@@ -100,113 +125,111 @@ __device__ __forceinline__ void vm_exec(const VmProgram& P, uint32_t (*R)[V], co
   for (int v = 0; v < V; ++v) acc[v] = 0;
   for (int pc = 0; pc < P.n_instr; ++pc) {
     const VmInstr in = P.ins[pc];
-    uint32_t A[V], B[V];
-    if (in.flags & VMF_A_ACC) {
-#pragma unroll
-      for (int v = 0; v < V; ++v) A[v] = acc[v];
-    } else {
-#pragma unroll
-      for (int v = 0; v < V; ++v) A[v] = R[in.a][v];
-    }
-    if (in.flags & VMF_B_ACC) {
-#pragma unroll
-      for (int v = 0; v < V; ++v) B[v] = acc[v];
-    } else {
-#pragma unroll
-      for (int v = 0; v < V; ++v) B[v] = R[in.b][v];
-    }
     // one dispatch per instruction; the lane loop lives inside each case
-#define RX_LANES(expr)                 \
-  {                                    \
-    _Pragma("unroll") for (int v = 0; v < V; ++v) { \
-      const float a = u2f(A[v]), b = u2f(B[v]);     \
-      const int32_t ia = (int32_t)A[v], ib = (int32_t)B[v]; \
-      (void)a; (void)b; (void)ia; (void)ib;         \
-      acc[v] = (expr);                 \
-    }                                  \
-  }                                    \
+#define RX_UN(expr)                                  \
+  {                                                  \
+    _Pragma("unroll") for (int v = 0; v < V; ++v) {  \
+      const float a = u2f(acc[v]);                   \
+      const int32_t ia = (int32_t)acc[v];            \
+      (void)a; (void)ia;                             \
+      acc[v] = (expr);                               \
+    }                                                \
+  }                                                  \
+  break
+#define RX_BIN(expr)                                 \
+  {                                                  \
+    uint32_t B[V];                                   \
+    vm_ldrow<V>(R[in.b], B);                         \
+    _Pragma("unroll") for (int v = 0; v < V; ++v) {  \
+      const float a = u2f(acc[v]), b = u2f(B[v]);    \
+      const int32_t ia = (int32_t)acc[v], ib = (int32_t)B[v]; \
+      (void)a; (void)b; (void)ia; (void)ib;          \
+      acc[v] = (expr);                               \
+    }                                                \
+  }                                                  \
   break
     switch (in.op) {
-      case VM_CONST: RX_LANES(in.imm);
-      case VM_MOV: RX_LANES(A[v]);
-      case VM_NEG: RX_LANES(f2u(-a));
-      case VM_SIN: RX_LANES(f2u(sinf(a)));
-      case VM_COS: RX_LANES(f2u(cosf(a)));
-      case VM_EXP: RX_LANES(f2u(expf(a)));
-      case VM_LOG: RX_LANES(f2u(logf(a)));
-      case VM_TANH: RX_LANES(f2u(tanhf(a)));
-      case VM_SQRT: RX_LANES(f2u(sqrtf(a)));
-      case VM_RSQRT: RX_LANES(f2u(1.0f / sqrtf(a)));
-      case VM_ABS: RX_LANES(f2u(fabsf(a)));
-      case VM_LOG1P: RX_LANES(f2u(log1pf(a)));
-      case VM_EXPM1: RX_LANES(f2u(expm1f(a)));
-      case VM_FLOOR: RX_LANES(f2u(floorf(a)));
-      case VM_CEIL: RX_LANES(f2u(ceilf(a)));
-      case VM_SIGN: RX_LANES(f2u((a != a) ? a : (float)((a > 0.f) - (a < 0.f))));
-      case VM_LOGISTIC: RX_LANES(f2u(1.0f / (1.0f + expf(-a))));
-      case VM_RBF16: RX_LANES(f2u(round_bf16(a)));
-      case VM_ADD: RX_LANES(f2u(__fadd_rn(a, b)));
-      case VM_SUB: RX_LANES(f2u(__fsub_rn(a, b)));
-      case VM_MUL: RX_LANES(f2u(__fmul_rn(a, b)));
-      case VM_DIV: RX_LANES(f2u(a / b));
-      case VM_MAX: RX_LANES(f2u(nan_max(a, b)));
-      case VM_MIN: RX_LANES(f2u(nan_min(a, b)));
-      case VM_POW: RX_LANES(f2u(powf(a, b)));
-      case VM_IADD: RX_LANES((uint32_t)(ia + ib));
-      case VM_ISUB: RX_LANES((uint32_t)(ia - ib));
-      case VM_IMUL: RX_LANES((uint32_t)(ia * ib));
-      case VM_IDIV: RX_LANES(ib == 0 ? 0xFFFFFFFFu : ((ia == INT32_MIN && ib == -1) ? (uint32_t)INT32_MIN : (uint32_t)(ia / ib)));
-      case VM_IMAX: RX_LANES((uint32_t)max(ia, ib));
-      case VM_IMIN: RX_LANES((uint32_t)min(ia, ib));
-      case VM_INEG: RX_LANES((uint32_t)(-ia));
-      case VM_IABS: RX_LANES((uint32_t)abs(ia));
-      case VM_AND: RX_LANES(A[v] & B[v]);
-      case VM_OR: RX_LANES(A[v] | B[v]);
-      case VM_XOR: RX_LANES(A[v] ^ B[v]);
-      case VM_NOT: RX_LANES(~A[v]);
-      case VM_LNOT: RX_LANES(A[v] ? 0u : 1u);
-      case VM_FCMP: RX_LANES(vm_cmp_f(in.c, a, b));
-      case VM_ICMP: RX_LANES(vm_cmp_i(in.c, ia, ib));
-      case VM_ADDI: RX_LANES(f2u(__fadd_rn(a, u2f(in.imm))));
-      case VM_SUBI: RX_LANES(f2u(__fsub_rn(a, u2f(in.imm))));
-      case VM_RSUBI: RX_LANES(f2u(__fsub_rn(u2f(in.imm), a)));
-      case VM_MULI: RX_LANES(f2u(__fmul_rn(a, u2f(in.imm))));
-      case VM_DIVI: RX_LANES(f2u(a / u2f(in.imm)));
-      case VM_RDIVI: RX_LANES(f2u(u2f(in.imm) / a));
-      case VM_MAXI: RX_LANES(f2u(nan_max(a, u2f(in.imm))));
-      case VM_MINI: RX_LANES(f2u(nan_min(a, u2f(in.imm))));
+      case VM_LD: vm_ldrow<V>(R[in.b], acc); break;
+      case VM_CONST: RX_UN(in.imm);
+      case VM_MOV: break;
+      case VM_NEG: RX_UN(f2u(-a));
+      case VM_SIN: RX_UN(f2u(sinf(a)));
+      case VM_COS: RX_UN(f2u(cosf(a)));
+      case VM_EXP: RX_UN(f2u(expf(a)));
+      case VM_LOG: RX_UN(f2u(logf(a)));
+      case VM_TANH: RX_UN(f2u(tanhf(a)));
+      case VM_SQRT: RX_UN(f2u(sqrtf(a)));
+      case VM_RSQRT: RX_UN(f2u(1.0f / sqrtf(a)));
+      case VM_ABS: RX_UN(f2u(fabsf(a)));
+      case VM_LOG1P: RX_UN(f2u(log1pf(a)));
+      case VM_EXPM1: RX_UN(f2u(expm1f(a)));
+      case VM_FLOOR: RX_UN(f2u(floorf(a)));
+      case VM_CEIL: RX_UN(f2u(ceilf(a)));
+      case VM_SIGN: RX_UN(f2u((a != a) ? a : (float)((a > 0.f) - (a < 0.f))));
+      case VM_LOGISTIC: RX_UN(f2u(1.0f / (1.0f + expf(-a))));
+      case VM_RBF16: RX_UN(f2u(round_bf16(a)));
+      case VM_SQR: RX_UN(f2u(__fmul_rn(a, a)));
+      case VM_ADDI: RX_UN(f2u(__fadd_rn(a, u2f(in.imm))));
+      case VM_SUBI: RX_UN(f2u(__fsub_rn(a, u2f(in.imm))));
+      case VM_RSUBI: RX_UN(f2u(__fsub_rn(u2f(in.imm), a)));
+      case VM_MULI: RX_UN(f2u(__fmul_rn(a, u2f(in.imm))));
+      case VM_DIVI: RX_UN(f2u(a / u2f(in.imm)));
+      case VM_RDIVI: RX_UN(f2u(u2f(in.imm) / a));
+      case VM_MAXI: RX_UN(f2u(nan_max(a, u2f(in.imm))));
+      case VM_MINI: RX_UN(f2u(nan_min(a, u2f(in.imm))));
+      case VM_INEG: RX_UN((uint32_t)(-ia));
+      case VM_IABS: RX_UN((uint32_t)abs(ia));
+      case VM_NOT: RX_UN(~acc[v]);
+      case VM_LNOT: RX_UN(acc[v] ? 0u : 1u);
+      case VM_I2F: RX_UN(f2u((float)ia));
+      case VM_F2I: RX_UN((a != a) ? 0u : (uint32_t)(int32_t)fminf(fmaxf(truncf(a), -2147483648.f), 2147483520.f));
+      case VM_P2F: RX_UN(f2u(acc[v] ? 1.f : 0.f));
+      case VM_F2P: RX_UN((uint32_t)(a != 0.f));
+      case VM_I2P: RX_UN((uint32_t)(ia != 0));
+      case VM_IOTA: RX_UN((uint32_t)(int32_t)(idx[in.a] + (in.a == P.rank - 1 ? v : 0)));
+      case VM_ADD: RX_BIN(f2u(__fadd_rn(a, b)));
+      case VM_SUB: RX_BIN(f2u(__fsub_rn(a, b)));
+      case VM_RSUB: RX_BIN(f2u(__fsub_rn(b, a)));
+      case VM_MUL: RX_BIN(f2u(__fmul_rn(a, b)));
+      case VM_DIV: RX_BIN(f2u(a / b));
+      case VM_RDIV: RX_BIN(f2u(b / a));
+      case VM_MAX: RX_BIN(f2u(nan_max(a, b)));
+      case VM_MIN: RX_BIN(f2u(nan_min(a, b)));
+      case VM_POW: RX_BIN(f2u(powf(a, b)));
+      case VM_IADD: RX_BIN((uint32_t)(ia + ib));
+      case VM_ISUB: RX_BIN((uint32_t)(ia - ib));
+      case VM_IMUL: RX_BIN((uint32_t)(ia * ib));
+      case VM_IDIV: RX_BIN(ib == 0 ? 0xFFFFFFFFu : ((ia == INT32_MIN && ib == -1) ? (uint32_t)INT32_MIN : (uint32_t)(ia / ib)));
+      case VM_IMAX: RX_BIN((uint32_t)max(ia, ib));
+      case VM_IMIN: RX_BIN((uint32_t)min(ia, ib));
+      case VM_AND: RX_BIN(acc[v] & B[v]);
+      case VM_OR: RX_BIN(acc[v] | B[v]);
+      case VM_XOR: RX_BIN(acc[v] ^ B[v]);
+      case VM_FCMP: RX_BIN(vm_cmp_f(in.c, a, b));
+      case VM_ICMP: RX_BIN(vm_cmp_i(in.c, ia, ib));
+      case VM_SELECT:
       case VM_MULADD:
-      case VM_SELECT: {
-        uint32_t C[V];
-        if (in.flags & VMF_C_ACC) {
-#pragma unroll
-          for (int v = 0; v < V; ++v) C[v] = acc[v];
-        } else {
-#pragma unroll
-          for (int v = 0; v < V; ++v) C[v] = R[in.c][v];
-        }
+      case VM_MULADD_C: {
+        uint32_t B[V], C[V];
+        vm_ldrow<V>(R[in.b], B);
+        vm_ldrow<V>(R[in.c], C);
         if (in.op == VM_SELECT) {
 #pragma unroll
-          for (int v = 0; v < V; ++v) acc[v] = A[v] ? B[v] : C[v];
+          for (int v = 0; v < V; ++v) acc[v] = acc[v] ? B[v] : C[v];
+        } else if (in.op == VM_MULADD) {
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[v] = f2u(__fadd_rn(__fmul_rn(u2f(acc[v]), u2f(B[v])), u2f(C[v])));
         } else {
 #pragma unroll
-          for (int v = 0; v < V; ++v) acc[v] = f2u(__fadd_rn(__fmul_rn(u2f(A[v]), u2f(B[v])), u2f(C[v])));
+          for (int v = 0; v < V; ++v) acc[v] = f2u(__fadd_rn(__fmul_rn(u2f(B[v]), u2f(C[v])), u2f(acc[v])));
         }
         break;
       }
-      case VM_I2F: RX_LANES(f2u((float)ia));
-      case VM_F2I: RX_LANES((a != a) ? 0u : (uint32_t)(int32_t)fminf(fmaxf(truncf(a), -2147483648.f), 2147483520.f));
-      case VM_P2F: RX_LANES(f2u(A[v] ? 1.f : 0.f));
-      case VM_F2P: RX_LANES((uint32_t)(a != 0.f));
-      case VM_I2P: RX_LANES((uint32_t)(ia != 0));
-      case VM_IOTA: RX_LANES((uint32_t)(int32_t)(idx[in.a] + (in.a == P.rank - 1 ? v : 0)));
-      default: RX_LANES(0u);
+      default: break;
     }
-#undef RX_LANES
-    if (in.flags & VMF_STORE) {
-#pragma unroll
-      for (int v = 0; v < V; ++v) R[in.dst][v] = acc[v];
-    }
+#undef RX_UN
+#undef RX_BIN
+    if (in.flags & VMF_STORE) vm_strow<V>(R[in.dst], acc);
   }
 }
 
@@ -256,7 +279,7 @@ __device__ __forceinline__ int64_t out_offset(const VmOut& l, const int64_t* idx
 
 // one element through the interpreter, leaves addressed by multi-index
 __device__ __forceinline__ uint32_t vm_eval_at(const VmProgram& P, const int64_t* idx) {
-  uint32_t R[kVmMaxRegs][1];
+  __align__(16) uint32_t R[kVmMaxRegs][1];
   for (int k = 0; k < P.n_leaves; ++k) R[P.leaf[k].reg][0] = load_elem(P.leaf[k].ptr, leaf_offset(P.leaf[k], idx, P.rank), P.leaf[k].elem);
   vm_exec<1>(P, R, idx);
   return R[P.result_reg][0];

@@ -67,24 +67,23 @@ __device__ __forceinline__ void finish_in_last_block(uint32_t mine, uint32_t* pa
 __device__ __forceinline__ void load4(const VmLeaf& l, int64_t i, uint32_t* d) {
   if (l.linear == 2) {
     uint32_t u = load_elem(l.ptr, l.offset, l.elem);
-    d[0] = d[1] = d[2] = d[3] = u;
+    *(uint4*)d = make_uint4(u, u, u, u);
     return;
   }
   switch (l.elem) {
     case EL_F32:
     case EL_I32: {
-      uint4 v = __ldg((const uint4*)((const uint32_t*)l.ptr + l.offset + i));
-      d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+      *(uint4*)d = __ldg((const uint4*)((const uint32_t*)l.ptr + l.offset + i));
       break;
     }
     case EL_BF16: {
       uint2 v = __ldg((const uint2*)((const uint16_t*)l.ptr + l.offset + i));
-      d[0] = v.x << 16; d[1] = v.x & 0xFFFF0000u; d[2] = v.y << 16; d[3] = v.y & 0xFFFF0000u;
+      *(uint4*)d = make_uint4(v.x << 16, v.x & 0xFFFF0000u, v.y << 16, v.y & 0xFFFF0000u);
       break;
     }
     default: {
       uchar4 v = __ldg((const uchar4*)((const uint8_t*)l.ptr + l.offset + i));
-      d[0] = v.x != 0; d[1] = v.y != 0; d[2] = v.z != 0; d[3] = v.w != 0;
+      *(uint4*)d = make_uint4(v.x != 0, v.y != 0, v.z != 0, v.w != 0);
       break;
     }
   }
@@ -117,7 +116,7 @@ __global__ void __launch_bounds__(kThreads) k_map_linear(const __grid_constant__
   int64_t stride = (int64_t)gridDim.x * kThreads;
   int64_t idx0[kMaxRank] = {0, 0, 0, 0};
   for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += stride) {
-    uint32_t R[kVmMaxRegs][4];
+    __align__(16) uint32_t R[kVmMaxRegs][4];
     for (int k = 0; k < P.n_leaves; ++k) load4(P.leaf[k], i * 4, R[P.leaf[k].reg]);
     vm_exec<4>(P, R, idx0);
     for (int k = 0; k < P.n_outs; ++k) store4(P.out[k], i * 4, R[P.out[k].reg]);
@@ -125,7 +124,7 @@ __global__ void __launch_bounds__(kThreads) k_map_linear(const __grid_constant__
   // tail
   if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
     int64_t i = n4 * 4 + threadIdx.x;
-    uint32_t R[kVmMaxRegs][1];
+    __align__(16) uint32_t R[kVmMaxRegs][1];
     for (int k = 0; k < P.n_leaves; ++k)
       R[P.leaf[k].reg][0] = load_elem(P.leaf[k].ptr, P.leaf[k].offset + (P.leaf[k].linear == 2 ? 0 : i), P.leaf[k].elem);
     vm_exec<1>(P, R, idx0);
@@ -140,7 +139,7 @@ __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant_
     int64_t idx[kMaxRank];
     if (SMALL) unravel32(P, (uint32_t)i, idx);
     else unravel(P, i, idx);
-    uint32_t R[kVmMaxRegs][1];
+    __align__(16) uint32_t R[kVmMaxRegs][1];
     for (int k = 0; k < P.n_leaves; ++k) R[P.leaf[k].reg][0] = load_elem(P.leaf[k].ptr, leaf_offset(P.leaf[k], idx, P.rank), P.leaf[k].elem);
     vm_exec<1>(P, R, idx);
     for (int k = 0; k < P.n_outs; ++k) store_elem(P.out[k].ptr, out_offset(P.out[k], idx, P.rank), P.out[k].elem, R[P.out[k].reg][0]);
@@ -154,25 +153,24 @@ __device__ __forceinline__ void load4_rowvec(const VmLeaf& l, int64_t row, int64
   int64_t off = l.offset + row * l.stride[drow];
   if (l.stride[dcol] == 0) {
     uint32_t u = load_elem(l.ptr, off, l.elem);
-    d[0] = d[1] = d[2] = d[3] = u;
+    *(uint4*)d = make_uint4(u, u, u, u);
     return;
   }
   off += col;
   switch (l.elem) {
     case EL_F32:
     case EL_I32: {
-      uint4 v = __ldg((const uint4*)((const uint32_t*)l.ptr + off));
-      d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+      *(uint4*)d = __ldg((const uint4*)((const uint32_t*)l.ptr + off));
       break;
     }
     case EL_BF16: {
       uint2 v = __ldg((const uint2*)((const uint16_t*)l.ptr + off));
-      d[0] = v.x << 16; d[1] = v.x & 0xFFFF0000u; d[2] = v.y << 16; d[3] = v.y & 0xFFFF0000u;
+      *(uint4*)d = make_uint4(v.x << 16, v.x & 0xFFFF0000u, v.y << 16, v.y & 0xFFFF0000u);
       break;
     }
     default: {
       uchar4 v = __ldg((const uchar4*)((const uint8_t*)l.ptr + off));
-      d[0] = v.x != 0; d[1] = v.y != 0; d[2] = v.z != 0; d[3] = v.w != 0;
+      *(uint4*)d = make_uint4(v.x != 0, v.y != 0, v.z != 0, v.w != 0);
       break;
     }
   }
@@ -195,7 +193,7 @@ __global__ void __launch_bounds__(kThreads) k_map_rows(const __grid_constant__ V
     int64_t row, col;
     if (total < ((int64_t)1 << 31)) { uint32_t r = (uint32_t)i / (uint32_t)cv; row = r; col = (int64_t)((uint32_t)i - r * (uint32_t)cv) * V; }
     else { row = i / cv; col = (i - row * cv) * V; }
-    uint32_t R[kVmMaxRegs][V];
+    __align__(16) uint32_t R[kVmMaxRegs][V];
     for (int k = 0; k < P.n_leaves; ++k)
 #pragma unroll
       for (int u = 0; u < U; ++u) load4_rowvec(P.leaf[k], row, col + 4 * u, 0, 1, R[P.leaf[k].reg] + 4 * u);
@@ -219,7 +217,7 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_rows(const __grid_cons
     int64_t row, col;
     if (total < ((int64_t)1 << 31)) { uint32_t r = (uint32_t)i / (uint32_t)c4; row = r; col = ((uint32_t)i - r * (uint32_t)c4) * 4; }
     else { row = i / c4; col = (i - row * c4) * 4; }
-    uint32_t R[kVmMaxRegs][4];
+    __align__(16) uint32_t R[kVmMaxRegs][4];
     for (int k = 0; k < P.n_leaves; ++k) load4_rowvec(P.leaf[k], row, col, 0, 1, R[P.leaf[k].reg]);
     vm_exec<4>(P, R, idx0);
 #pragma unroll
@@ -242,7 +240,7 @@ __global__ void __launch_bounds__(kThreads) k_reduce_col_vec(const __grid_consta
   uint32_t acc[4];
   for (int v = 0; v < 4; ++v) acc[v] = red_identity(code);
   for (int64_t r = r0; r < r1; ++r) {
-    uint32_t R[kVmMaxRegs][4];
+    __align__(16) uint32_t R[kVmMaxRegs][4];
     for (int k = 0; k < P.n_leaves; ++k) load4_rowvec(P.leaf[k], r, b4, 1, 2, R[P.leaf[k].reg]);
     vm_exec<4>(P, R, idx0);
 #pragma unroll
@@ -293,7 +291,7 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_co
   uint32_t acc[4];
   for (int v = 0; v < 4; ++v) acc[v] = red_identity(code);
   for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += stride) {
-    uint32_t R[kVmMaxRegs][4];
+    __align__(16) uint32_t R[kVmMaxRegs][4];
     for (int k = 0; k < P.n_leaves; ++k) load4(P.leaf[k], i * 4, R[P.leaf[k].reg]);
     vm_exec<4>(P, R, idx0);
 #pragma unroll
@@ -301,7 +299,7 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_co
   }
   if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
     int64_t i = n4 * 4 + threadIdx.x;
-    uint32_t R[kVmMaxRegs][1];
+    __align__(16) uint32_t R[kVmMaxRegs][1];
     for (int k = 0; k < P.n_leaves; ++k)
       R[P.leaf[k].reg][0] = load_elem(P.leaf[k].ptr, P.leaf[k].offset + (P.leaf[k].linear == 2 ? 0 : i), P.leaf[k].elem);
     vm_exec<1>(P, R, idx0);
@@ -541,8 +539,10 @@ cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
   if (P.all_linear && vec_aligned(P)) {
     k_map_linear<<<grid_for((n + 3) / 4, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
   } else if (P.rank == 2 && rowvec_ok(P, 0, 1, true)) {
-    if (P.dim[1] % 8 == 0) k_map_rows<2><<<grid_for(n / 8, c.sm_count, 8), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
-    else k_map_rows<1><<<grid_for(n / 4, c.sm_count, 8), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
+    static const int per_sm = getenv("RX_MAP_CTAS") ? atoi(getenv("RX_MAP_CTAS")) : 8;
+    static const int lanes = getenv("RX_MAP_LANES") ? atoi(getenv("RX_MAP_LANES")) : 8;
+    if (P.dim[1] % 8 == 0 && lanes == 8) k_map_rows<2><<<grid_for(n / 8, c.sm_count, per_sm), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
+    else k_map_rows<1><<<grid_for(n / 4, c.sm_count, per_sm), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
   } else {
     if (n < ((int64_t)1 << 31)) k_map_generic<true><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
     else k_map_generic<false><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);

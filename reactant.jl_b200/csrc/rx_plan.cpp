@@ -592,14 +592,41 @@ struct Planner {
     std::vector<bool> is_output(nn, false);
     for (auto& o : outs) is_output[o.vnode] = true;
     if (result_vnode >= 0) is_output[result_vnode] = true;
-    int prev_instr_node = -1;  // node emitted as the previous instruction (its value sits in the accumulator)
-    int prev_instr_index = -1;
+    // ---- emission for the accumulator machine: acc = f(acc, R[b], R[c] | imm) --------------------
+    int prev = -1;  // node whose value is in the accumulator
     int ni = 0;
+    std::vector<int> instr_of(nn, -1);
+    auto mark_store = [&](int vnode) {
+      if (vnode >= 0 && L.nodes[vnode].leaf < 0 && instr_of[vnode] >= 0) P.ins[instr_of[vnode]].flags |= VMF_STORE;
+    };
+    auto push = [&](int op) -> VmInstr& {
+      if (ni >= kVmMaxInstr) throw Error(RX_ERR_PLAN, "fusion group longer than " + std::to_string(kVmMaxInstr) + " ops");
+      VmInstr& in = P.ins[ni++];
+      in = VmInstr{};
+      in.op = (uint8_t)op;
+      return in;
+    };
+    auto rg = [&](int vnode) {  // operand read from the register file
+      mark_store(vnode);
+      return (uint8_t)reg[vnode];
+    };
+    auto load_acc = [&](int vnode) {
+      if (vnode == prev) return;
+      uint8_t r = rg(vnode);
+      VmInstr& in = push(VM_LD);
+      in.b = r;
+    };
+    auto commutative = [](int op) {
+      return op == VM_ADD || op == VM_MUL || op == VM_MAX || op == VM_MIN || op == VM_IADD || op == VM_IMUL || op == VM_IMAX || op == VM_IMIN ||
+             op == VM_AND || op == VM_OR || op == VM_XOR;
+    };
+    auto is_binary = [](int op) {
+      return (op >= VM_ADD && op <= VM_POW) || (op >= VM_IADD && op <= VM_IMIN) || op == VM_AND || op == VM_OR || op == VM_XOR || op == VM_FCMP || op == VM_ICMP;
+    };
     for (size_t k = 0; k < nn; ++k) {
       const VNode& n = L.nodes[k];
       if (n.leaf < 0 && !dead[k]) {
         // release operands whose last use is this node before allocating dst, so dst may reuse them
-        int ra = n.op == VM_IOTA ? -1 : (n.a >= 0 ? reg[n.a] : -1), rb = n.b >= 0 ? reg[n.b] : -1, rc = n.c >= 0 ? reg[n.c] : -1;
         if (n.op != VM_IOTA)
           for (int u : {n.a, n.b, n.c})
             if (u >= 0 && last[u] == (int)k && reg[u] >= 0) {
@@ -608,35 +635,69 @@ struct Planner {
               if (!dup) free_regs.push_back(reg[u]);
             }
         reg[k] = alloc();
-        if (ni >= kVmMaxInstr) throw Error(RX_ERR_PLAN, "fusion group longer than " + std::to_string(kVmMaxInstr) + " ops");
-        VmInstr& in = P.ins[ni++];
-        in.op = (uint8_t)n.op;
-        in.dst = (uint8_t)reg[k];
-        if (n.op == VM_IOTA) {
+        int op = n.op;
+        if (op == VM_IOTA) {
           int nd = -1;
           for (int d = 0; d < P.rank; ++d)
             if (sp.origin[d] == n.a) nd = d;
-          if (nd < 0) { in.op = VM_CONST; in.imm = 0; }  // unit dim: index is 0
-          else in.a = (uint8_t)nd;
-        } else {
-          in.a = (uint8_t)(ra < 0 ? 0 : ra);
-          in.b = (uint8_t)(rb < 0 ? 0 : rb);
-          in.c = (uint8_t)(rc < 0 ? 0 : rc);
-          if (n.op == VM_FCMP || n.op == VM_ICMP) in.c = (uint8_t)n.cmp;
+          VmInstr& in = push(nd < 0 ? VM_CONST : VM_IOTA);  // unit dim: index is 0
+          in.a = (uint8_t)(nd < 0 ? 0 : nd);
+        } else if (op == VM_CONST) {
+          VmInstr& in = push(VM_CONST);
           in.imm = n.imm;
-          // operands produced by the instruction just before this one are read from the accumulator
-          int acc_uses = 0;
-          if (prev_instr_node >= 0) {
-            if (n.a == prev_instr_node) { in.flags |= VMF_A_ACC; ++acc_uses; }
-            if (n.b == prev_instr_node) { in.flags |= VMF_B_ACC; ++acc_uses; }
-            if (n.c == prev_instr_node && (n.op == VM_SELECT || n.op == VM_MULADD)) { in.flags |= VMF_C_ACC; ++acc_uses; }
-            // the previous result needs no register-file copy if this instruction is its only consumer
-            if (acc_uses > 0 && acc_uses == nuses[prev_instr_node] && !is_output[prev_instr_node]) P.ins[prev_instr_index].flags &= (uint8_t)~VMF_STORE;
+        } else if (op == VM_SELECT) {
+          load_acc(n.a);
+          uint8_t rb = rg(n.b), rc = rg(n.c);
+          VmInstr& in = push(VM_SELECT);
+          in.b = rb;
+          in.c = rc;
+        } else if (op == VM_MULADD) {
+          int a = n.a, b = n.b, c = n.c;
+          if (b == prev && a != prev) std::swap(a, b);
+          if (a != prev && c == prev) {
+            uint8_t rb = rg(a), rc = rg(b);
+            VmInstr& in = push(VM_MULADD_C);
+            in.b = rb;
+            in.c = rc;
+          } else {
+            load_acc(a);
+            uint8_t rb = rg(b), rc = rg(c);
+            VmInstr& in = push(VM_MULADD);
+            in.b = rb;
+            in.c = rc;
           }
+        } else if (is_binary(op)) {
+          int a = n.a, b = n.b, cmp = n.cmp;
+          if (op == VM_MUL && a == b) {
+            load_acc(a);
+            push(VM_SQR);
+          } else {
+            if (b == prev && a != prev) {
+              // the accumulator holds the right operand: swap, reversing the op where it matters
+              if (commutative(op)) std::swap(a, b);
+              else if (op == VM_SUB) { op = VM_RSUB; std::swap(a, b); }
+              else if (op == VM_DIV) { op = VM_RDIV; std::swap(a, b); }
+              else if (op == VM_FCMP || op == VM_ICMP) {
+                cmp = cmp == CMP_LT ? CMP_GT : cmp == CMP_GT ? CMP_LT : cmp == CMP_LE ? CMP_GE : cmp == CMP_GE ? CMP_LE : cmp;
+                std::swap(a, b);
+              }
+            }
+            load_acc(a);
+            uint8_t rb = rg(b);
+            VmInstr& in = push(op);
+            in.b = rb;
+            if (op == VM_FCMP || op == VM_ICMP) in.c = (uint8_t)cmp;
+          }
+        } else {
+          // unary forms (including immediates)
+          load_acc(n.a);
+          VmInstr& in = push(op);  // VM_MOV: the accumulator already holds the value
+          in.imm = n.imm;
         }
-        in.flags |= VMF_STORE;  // cleared above by the next instruction when it is the sole, adjacent consumer
-        prev_instr_node = (int)k;
-        prev_instr_index = ni - 1;
+        P.ins[ni - 1].dst = (uint8_t)reg[k];
+        instr_of[k] = ni - 1;
+        if (is_output[k]) P.ins[ni - 1].flags |= VMF_STORE;
+        prev = (int)k;
       }
       if (last[k] < 0 && reg[k] >= 0 && L.nodes[k].leaf < 0) free_regs.push_back(reg[k]);  // dead value
     }

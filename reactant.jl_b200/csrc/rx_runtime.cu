@@ -211,7 +211,8 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
   RxDevice* d = r.dev;
   CK(cudaSetDevice(d->ordinal));
   LaunchCtx c = d->ctx();
-  ProfScope ps(d, kind_name(st.kind));
+  static const bool by_note = getenv("RX_PROFILE_NOTES") != nullptr;  // finer spans: one per plan step description
+  ProfScope ps(d, by_note ? st.note.c_str() : kind_name(st.kind));
   switch (st.kind) {
     case StepK::Map: {
       VmProgram P = bind(st, r);

@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
         int64_t idx0[kMaxRank] = {0, 0, 0, 0};
         for (int r = 0; r < rmax; ++r) {
           const float* q = sm + r * BOX_W;
-          uint32_t R[kVmMaxRegs][1];
+          __align__(16) uint32_t R[kVmMaxRegs][1];
           for (int k = 0; k < P.n_leaves; ++k) R[P.leaf[k].reg][0] = f2u(q[p.dy[k] * BOX_W + p.dx[k]]);
           vm_exec<1>(P, R, idx0);
           out[(int64_t)r * p.dst_ld] = u2f(R[P.out[0].reg][0]);

@@ -34,7 +34,12 @@ enum VmOp : uint8_t {
   // f32 forms with an immediate operand (imm = raw bits) and the two-rounding multiply-add;
   // produced by the planner's peephole pass, never by the parser
   VM_ADDI, VM_SUBI /* a - imm */, VM_RSUBI /* imm - a */, VM_MULI, VM_DIVI /* a / imm */, VM_RDIVI /* imm / a */, VM_MAXI, VM_MINI,
-  VM_MULADD,  // dst = round(round(a * b) + c): same roundings as separate multiply and add
+  VM_MULADD,  // acc = round(round(acc * R[b]) + R[c]): same roundings as separate multiply and add
+  VM_MULADD_C,  // acc = round(round(R[b] * R[c]) + acc)
+  VM_LD,      // acc = R[b]
+  VM_SQR,     // acc = acc * acc
+  VM_RSUB,    // acc = R[b] - acc
+  VM_RDIV,    // acc = R[b] / acc
   VM_NUM_OPS
 };
 
@@ -43,15 +48,15 @@ enum VmCmp : uint8_t { CMP_EQ = 0, CMP_NE, CMP_LT, CMP_LE, CMP_GT, CMP_GE };
 // storage element kinds a kernel can load/store
 enum VmElem : uint8_t { EL_F32 = 0, EL_BF16, EL_I32, EL_PRED /* 1 byte */, EL_I64, EL_F64 };
 
-// Operands normally come from the register file; when the matching VMF_*_ACC flag is
-// set the operand is the previous instruction's result, which the interpreter keeps in
-// machine registers ("accumulator").  A result is written back to the register file
-// only when VMF_STORE is set (it has a later, non-adjacent use or is an output).  For
-// the chain-shaped programs fusion produces this removes most register-file traffic.
-enum VmFlags : uint8_t { VMF_A_ACC = 1, VMF_B_ACC = 2, VMF_C_ACC = 4, VMF_STORE = 8 };
+// Accumulator machine: every instruction computes acc = f(acc, R[b], R[c] | imm), where acc
+// (the previous instruction's result) lives in machine registers and R is the per-thread
+// register file in local memory.  The result is copied to R[dst] only when VMF_STORE is set
+// (it has a later, non-adjacent use or is an output).  For the chain-shaped programs that
+// fusion produces, most instructions touch the register file once or not at all.
+enum VmFlags : uint8_t { VMF_STORE = 8 };
 
 struct VmInstr {
-  uint8_t op, dst, a, b, c, flags, pad[2];
+  uint8_t op, dst, a /* root dim for VM_IOTA */, b, c /* register, or comparison direction */, flags, pad[2];
   uint32_t imm;
 };
 
