@@ -149,6 +149,24 @@ const char* RxExecutableDescribe(RxExecutable* exec);
  * device. */
 const char* RxPlanDescribe(const char* mlir_text, size_t text_len);
 
+/* ---- run-time specialisation of fused chains ---------------------------------
+ * Fusion groups whose launch covers at least `min_elems` elements (default 2^20)
+ * run a kernel compiled for that chain with NVRTC on first use (cached for the
+ * life of the process); smaller launches, and every launch when NVRTC cannot be
+ * loaded, run the same kernel skeleton over a bytecode interpreter on the GPU.
+ * Both produce the same bits.  The counterpart in the reference is XLA's own
+ * code generation inside ClientCompile (API.cpp:1482-1507); these three entry
+ * points have no counterpart of their own.
+ * RxChainSpecialiser: set the threshold; a negative value switches it off.
+ * RxChainSpecialiserStats: out4 = {kernels compiled, cache hits, compile
+ *   failures, 1 if NVRTC or the driver entry points are unavailable}.
+ * RxPlanSpecialiseCheck: plan a module and compile every chain in it for each
+ *   kernel family it could run in, without a device; returns a JSON list
+ *   (caller frees) or NULL with the error set to the compiler log. */
+void RxChainSpecialiser(int64_t min_elems);
+void RxChainSpecialiserStats(int64_t* out4);
+const char* RxPlanSpecialiseCheck(const char* mlir_text, size_t text_len);
+
 /* ---- execute (API.cpp:1585-1630, 1653-1728) --------------------------------- */
 /* Single-device launch.  `is_arg_donatable[i]` != 0 allows argument i's storage
  * to be reused for the output it aliases.  Writes `num_results` fresh buffer

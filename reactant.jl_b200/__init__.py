@@ -444,4 +444,27 @@ def plan_describe(module_text: str) -> dict:
     return json.loads(take_string(p))
 
 
+def specialise_check(module_text: str) -> list:
+    """Plan a module and compile each of its fused chains with NVRTC for every kernel family it could run in.
+    Needs no device.  Raises with the compiler log if a chain does not compile."""
+    t = module_text.encode()
+    p = lib().RxPlanSpecialiseCheck(t, len(t))
+    if not p:
+        check()
+    return json.loads(take_string(p))
+
+
+def chain_specialiser(min_elems: int) -> None:
+    """Launches covering at least `min_elems` elements run kernels compiled for their chain (default 2^20);
+    a negative value switches specialisation off and everything runs the on-GPU interpreter."""
+    lib().RxChainSpecialiser(int(min_elems))
+
+
+def chain_specialiser_stats() -> dict:
+    import ctypes
+    out = (ctypes.c_int64 * 4)()
+    lib().RxChainSpecialiserStats(out)
+    return {"compiled": out[0], "cache_hits": out[1], "failed": out[2], "unavailable": bool(out[3])}
+
+
 from . import programs  # noqa: E402,F401

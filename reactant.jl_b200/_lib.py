@@ -83,6 +83,9 @@ PROTOTYPES = {
     "RxExecutableParameterAlias": (C.c_int, [P, C.c_int]),
     "RxExecutableDescribe": (P, [P]),
     "RxPlanDescribe": (P, [C.c_char_p, C.c_size_t]),
+    "RxChainSpecialiser": (None, [C.c_int64]),
+    "RxChainSpecialiserStats": (None, [C.POINTER(C.c_int64)]),
+    "RxPlanSpecialiseCheck": (P, [C.c_char_p, C.c_size_t]),
     "XLAExecuteSharded": (None, [P, C.c_int, PP, P, U8P, C.c_int, PP, U8P, PP]),
     "XLAExecute": (None, [P, C.c_int, PP, U8P, C.c_int, PP, U8P, PP]),
     "RxSinSumAddNoAlloc": (C.c_int, [P, P, C.c_int64, P, P]),

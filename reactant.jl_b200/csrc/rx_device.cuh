@@ -1,9 +1,10 @@
 // Device-side helpers shared by the kernels: element loads/stores, the
 // fused-chain interpreter, and warp/block combine primitives.
 #pragma once
-#include <cuda_bf16.h>
+#ifndef __CUDACC_RTC__
 #include <cuda_runtime.h>
 #include <stdint.h>
+#endif
 
 #include "rx_vm.h"
 
@@ -49,6 +50,19 @@ __host__ __device__ __forceinline__ uint32_t red_identity(int code) {
   }
 }
 
+// f32 -> bf16, round to nearest even (cvt.rn), as a 16-bit pattern; two at once packed lo | hi << 16
+__device__ __forceinline__ uint16_t bf16_bits(float x) {
+  uint16_t r;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf16x2_bits(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float round_bf16(float x) { return __uint_as_float((uint32_t)bf16_bits(x) << 16); }
+
 __device__ __forceinline__ uint32_t load_elem(const void* p, int64_t i, int elem) {
   switch (elem) {
     case EL_F32: return __ldg((const uint32_t*)p + i);
@@ -61,13 +75,12 @@ __device__ __forceinline__ uint32_t load_elem(const void* p, int64_t i, int elem
 __device__ __forceinline__ void store_elem(void* p, int64_t i, int elem, uint32_t v) {
   switch (elem) {
     case EL_F32: ((uint32_t*)p)[i] = v; break;
-    case EL_BF16: ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(u2f(v)); break;
+    case EL_BF16: ((uint16_t*)p)[i] = bf16_bits(u2f(v)); break;
     case EL_I32: ((uint32_t*)p)[i] = v; break;
     default: ((uint8_t*)p)[i] = v ? 1 : 0; break;
   }
 }
 
-__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 __device__ __forceinline__ uint32_t vm_cmp_f(int dir, float a, float b) {
   switch (dir) {
@@ -125,12 +138,17 @@ __device__ __forceinline__ void vm_exec(const VmProgram& P, uint32_t (*R)[V], co
   for (int v = 0; v < V; ++v) acc[v] = 0;
   for (int pc = 0; pc < P.n_instr; ++pc) {
     const VmInstr in = P.ins[pc];
+    const uint32_t imm = in.imm;
+    const float fimm = u2f(imm);
+    const int cdir = in.c;
+    (void)fimm; (void)cdir;
     // one dispatch per instruction; the lane loop lives inside each case
 #define RX_UN(expr)                                  \
   {                                                  \
     _Pragma("unroll") for (int v = 0; v < V; ++v) {  \
-      const float a = u2f(acc[v]);                   \
-      const int32_t ia = (int32_t)acc[v];            \
+      const uint32_t ua = acc[v];                    \
+      const float a = u2f(ua);                       \
+      const int32_t ia = (int32_t)ua;                \
       (void)a; (void)ia;                             \
       acc[v] = (expr);                               \
     }                                                \
@@ -141,8 +159,9 @@ __device__ __forceinline__ void vm_exec(const VmProgram& P, uint32_t (*R)[V], co
     uint32_t B[V];                                   \
     vm_ldrow<V>(R[in.b], B);                         \
     _Pragma("unroll") for (int v = 0; v < V; ++v) {  \
-      const float a = u2f(acc[v]), b = u2f(B[v]);    \
-      const int32_t ia = (int32_t)acc[v], ib = (int32_t)B[v]; \
+      const uint32_t ua = acc[v], ub = B[v];         \
+      const float a = u2f(ua), b = u2f(ub);          \
+      const int32_t ia = (int32_t)ua, ib = (int32_t)ub; \
       (void)a; (void)b; (void)ia; (void)ib;          \
       acc[v] = (expr);                               \
     }                                                \
@@ -150,63 +169,17 @@ __device__ __forceinline__ void vm_exec(const VmProgram& P, uint32_t (*R)[V], co
   break
     switch (in.op) {
       case VM_LD: vm_ldrow<V>(R[in.b], acc); break;
-      case VM_CONST: RX_UN(in.imm);
-      case VM_MOV: break;
-      case VM_NEG: RX_UN(f2u(-a));
-      case VM_SIN: RX_UN(f2u(sinf(a)));
-      case VM_COS: RX_UN(f2u(cosf(a)));
-      case VM_EXP: RX_UN(f2u(expf(a)));
-      case VM_LOG: RX_UN(f2u(logf(a)));
-      case VM_TANH: RX_UN(f2u(tanhf(a)));
-      case VM_SQRT: RX_UN(f2u(sqrtf(a)));
-      case VM_RSQRT: RX_UN(f2u(1.0f / sqrtf(a)));
-      case VM_ABS: RX_UN(f2u(fabsf(a)));
-      case VM_LOG1P: RX_UN(f2u(log1pf(a)));
-      case VM_EXPM1: RX_UN(f2u(expm1f(a)));
-      case VM_FLOOR: RX_UN(f2u(floorf(a)));
-      case VM_CEIL: RX_UN(f2u(ceilf(a)));
-      case VM_SIGN: RX_UN(f2u((a != a) ? a : (float)((a > 0.f) - (a < 0.f))));
-      case VM_LOGISTIC: RX_UN(f2u(1.0f / (1.0f + expf(-a))));
-      case VM_RBF16: RX_UN(f2u(round_bf16(a)));
-      case VM_SQR: RX_UN(f2u(__fmul_rn(a, a)));
-      case VM_ADDI: RX_UN(f2u(__fadd_rn(a, u2f(in.imm))));
-      case VM_SUBI: RX_UN(f2u(__fsub_rn(a, u2f(in.imm))));
-      case VM_RSUBI: RX_UN(f2u(__fsub_rn(u2f(in.imm), a)));
-      case VM_MULI: RX_UN(f2u(__fmul_rn(a, u2f(in.imm))));
-      case VM_DIVI: RX_UN(f2u(a / u2f(in.imm)));
-      case VM_RDIVI: RX_UN(f2u(u2f(in.imm) / a));
-      case VM_MAXI: RX_UN(f2u(nan_max(a, u2f(in.imm))));
-      case VM_MINI: RX_UN(f2u(nan_min(a, u2f(in.imm))));
-      case VM_INEG: RX_UN((uint32_t)(-ia));
-      case VM_IABS: RX_UN((uint32_t)abs(ia));
-      case VM_NOT: RX_UN(~acc[v]);
-      case VM_LNOT: RX_UN(acc[v] ? 0u : 1u);
-      case VM_I2F: RX_UN(f2u((float)ia));
-      case VM_F2I: RX_UN((a != a) ? 0u : (uint32_t)(int32_t)fminf(fmaxf(truncf(a), -2147483648.f), 2147483520.f));
-      case VM_P2F: RX_UN(f2u(acc[v] ? 1.f : 0.f));
-      case VM_F2P: RX_UN((uint32_t)(a != 0.f));
-      case VM_I2P: RX_UN((uint32_t)(ia != 0));
-      case VM_IOTA: RX_UN((uint32_t)(int32_t)(idx[in.a] + (in.a == P.rank - 1 ? v : 0)));
-      case VM_ADD: RX_BIN(f2u(__fadd_rn(a, b)));
-      case VM_SUB: RX_BIN(f2u(__fsub_rn(a, b)));
-      case VM_RSUB: RX_BIN(f2u(__fsub_rn(b, a)));
-      case VM_MUL: RX_BIN(f2u(__fmul_rn(a, b)));
-      case VM_DIV: RX_BIN(f2u(a / b));
-      case VM_RDIV: RX_BIN(f2u(b / a));
-      case VM_MAX: RX_BIN(f2u(nan_max(a, b)));
-      case VM_MIN: RX_BIN(f2u(nan_min(a, b)));
-      case VM_POW: RX_BIN(f2u(powf(a, b)));
-      case VM_IADD: RX_BIN((uint32_t)(ia + ib));
-      case VM_ISUB: RX_BIN((uint32_t)(ia - ib));
-      case VM_IMUL: RX_BIN((uint32_t)(ia * ib));
-      case VM_IDIV: RX_BIN(ib == 0 ? 0xFFFFFFFFu : ((ia == INT32_MIN && ib == -1) ? (uint32_t)INT32_MIN : (uint32_t)(ia / ib)));
-      case VM_IMAX: RX_BIN((uint32_t)max(ia, ib));
-      case VM_IMIN: RX_BIN((uint32_t)min(ia, ib));
-      case VM_AND: RX_BIN(acc[v] & B[v]);
-      case VM_OR: RX_BIN(acc[v] | B[v]);
-      case VM_XOR: RX_BIN(acc[v] ^ B[v]);
-      case VM_FCMP: RX_BIN(vm_cmp_f(in.c, a, b));
-      case VM_ICMP: RX_BIN(vm_cmp_i(in.c, ia, ib));
+#define RX_X(op, expr) case op: RX_UN(expr);
+      RX_VM_UNARY_OPS(RX_X)
+#undef RX_X
+#define RX_X(op, expr) case op: RX_BIN(expr);
+      RX_VM_BINARY_OPS(RX_X)
+#undef RX_X
+      case VM_IOTA: {
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = (uint32_t)(int32_t)(idx[in.a] + (in.a == P.rank - 1 ? v : 0));
+        break;
+      }
       case VM_SELECT:
       case VM_MULADD:
       case VM_MULADD_C: {
@@ -275,14 +248,6 @@ __device__ __forceinline__ int64_t out_offset(const VmOut& l, const int64_t* idx
   for (int d = 0; d < kMaxRank; ++d)
     if (d < rank) o += idx[d] * l.stride[d];
   return o;
-}
-
-// one element through the interpreter, leaves addressed by multi-index
-__device__ __forceinline__ uint32_t vm_eval_at(const VmProgram& P, const int64_t* idx) {
-  __align__(16) uint32_t R[kVmMaxRegs][1];
-  for (int k = 0; k < P.n_leaves; ++k) R[P.leaf[k].reg][0] = load_elem(P.leaf[k].ptr, leaf_offset(P.leaf[k], idx, P.rank), P.leaf[k].elem);
-  vm_exec<1>(P, R, idx);
-  return R[P.result_reg][0];
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -1,0 +1,296 @@
+// Chain specialiser: VmProgram -> CUDA source -> NVRTC (sm_100a cubin) -> driver module.
+#include "rx_jit.h"
+
+#include <cuda.h>
+#include <dlfcn.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include "rx_b200.h"
+
+namespace rx {
+
+void set_last_error(int code, const std::string& msg);
+
+namespace {
+
+// The device headers, embedded at build time (build.py writes this file from the sources
+// beside it) so that run-time compilation needs no file system access and no CUDA headers.
+#include "rx_jit_embed.inc"
+
+// ---- NVRTC, loaded on first use ---------------------------------------------------------
+struct Nvrtc {
+  void* lib = nullptr;
+  int (*CreateProgram)(void**, const char*, const char*, int, const char* const*, const char* const*) = nullptr;
+  int (*DestroyProgram)(void**) = nullptr;
+  int (*CompileProgram)(void*, int, const char* const*) = nullptr;
+  int (*GetProgramLogSize)(void*, size_t*) = nullptr;
+  int (*GetProgramLog)(void*, char*) = nullptr;
+  int (*GetCUBINSize)(void*, size_t*) = nullptr;
+  int (*GetCUBIN)(void*, char*) = nullptr;
+  int (*AddNameExpression)(void*, const char*) = nullptr;
+  int (*GetLoweredName)(void*, const char*, const char**) = nullptr;
+  bool ok = false;
+};
+
+const Nvrtc& nvrtc() {
+  static Nvrtc n;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* names[] = {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so"};
+    for (const char* nm : names) {
+      n.lib = dlopen(nm, RTLD_NOW | RTLD_LOCAL);
+      if (n.lib) break;
+    }
+    if (!n.lib) return;
+    auto sym = [&](const char* s) { return dlsym(n.lib, s); };
+    n.CreateProgram = (decltype(n.CreateProgram))sym("nvrtcCreateProgram");
+    n.DestroyProgram = (decltype(n.DestroyProgram))sym("nvrtcDestroyProgram");
+    n.CompileProgram = (decltype(n.CompileProgram))sym("nvrtcCompileProgram");
+    n.GetProgramLogSize = (decltype(n.GetProgramLogSize))sym("nvrtcGetProgramLogSize");
+    n.GetProgramLog = (decltype(n.GetProgramLog))sym("nvrtcGetProgramLog");
+    n.GetCUBINSize = (decltype(n.GetCUBINSize))sym("nvrtcGetCUBINSize");
+    n.GetCUBIN = (decltype(n.GetCUBIN))sym("nvrtcGetCUBIN");
+    n.AddNameExpression = (decltype(n.AddNameExpression))sym("nvrtcAddNameExpression");
+    n.GetLoweredName = (decltype(n.GetLoweredName))sym("nvrtcGetLoweredName");
+    n.ok = n.CreateProgram && n.DestroyProgram && n.CompileProgram && n.GetProgramLogSize && n.GetProgramLog && n.GetCUBINSize && n.GetCUBIN &&
+           n.AddNameExpression && n.GetLoweredName;
+  });
+  return n;
+}
+
+// ---- driver entry points (the library links the CUDA runtime only) --------------------------
+struct Driver {
+  CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+  CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**) = nullptr;
+  CUresult (*Occupancy)(int*, CUfunction, int, size_t) = nullptr;
+  bool ok = false;
+};
+
+const Driver& driver() {
+  static Driver d;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    auto get = [](const char* s) -> void* {
+      void* p = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint(s, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+      cudaGetLastError();
+      return p;
+    };
+    d.ModuleLoadData = (decltype(d.ModuleLoadData))get("cuModuleLoadData");
+    d.ModuleGetFunction = (decltype(d.ModuleGetFunction))get("cuModuleGetFunction");
+    d.LaunchKernel = (decltype(d.LaunchKernel))get("cuLaunchKernel");
+    d.Occupancy = (decltype(d.Occupancy))get("cuOccupancyMaxActiveBlocksPerMultiprocessor");
+    d.ok = d.ModuleLoadData && d.ModuleGetFunction && d.LaunchKernel && d.Occupancy;
+  });
+  return d;
+}
+
+// ---- op expression text, from the same tables the interpreter expands ----------------------
+struct OpText {
+  const char* unary[VM_NUM_OPS] = {};
+  const char* binary[VM_NUM_OPS] = {};
+  OpText() {
+#define RX_X(op, expr) unary[op] = #expr;
+    RX_VM_UNARY_OPS(RX_X)
+#undef RX_X
+#define RX_X(op, expr) binary[op] = #expr;
+    RX_VM_BINARY_OPS(RX_X)
+#undef RX_X
+  }
+};
+const OpText& op_text() {
+  static OpText t;
+  return t;
+}
+
+std::string hex32(uint32_t v) {
+  char b[16];
+  snprintf(b, sizeof b, "0x%08xu", v);
+  return b;
+}
+
+std::mutex g_mu;
+// RX_JIT_MIN_ELEMS overrides the default threshold (e.g. 0 to specialise every launch, -1 for none)
+int64_t g_min_elems = getenv("RX_JIT_MIN_ELEMS") ? atoll(getenv("RX_JIT_MIN_ELEMS")) : (int64_t)1 << 20;
+int64_t g_compiled = 0, g_hits = 0, g_failed = 0;
+std::map<std::string, std::vector<char>> g_cubins;              // source -> cubin
+std::map<std::string, std::string> g_lowered;                   // source -> lowered kernel name
+std::map<std::pair<int, std::string>, JitKernel> g_kernels;     // (device, source) -> loaded kernel
+
+bool compile(const std::string& src, const std::string& name_expr, std::vector<char>* cubin, std::string* lowered, std::string* log) {
+  const Nvrtc& n = nvrtc();
+  void* prog = nullptr;
+  if (n.CreateProgram(&prog, src.c_str(), "rx_chain.cu", kEmbedCount, kEmbedSrc, kEmbedNames) != 0) {
+    *log = "nvrtcCreateProgram failed";
+    return false;
+  }
+  n.AddNameExpression(prog, name_expr.c_str());
+  // RX_JIT_VERBOSE=1 prints each generated source and ptxas' resource summary to stderr
+  static const bool verbose = getenv("RX_JIT_VERBOSE") && atoi(getenv("RX_JIT_VERBOSE")) > 0;
+  const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "--ptxas-options=-v"};
+  int rc = n.CompileProgram(prog, verbose ? 3 : 2, opts);
+  size_t ls = 0;
+  n.GetProgramLogSize(prog, &ls);
+  if (ls > 1) {
+    log->resize(ls);
+    n.GetProgramLog(prog, &(*log)[0]);
+  }
+  if (verbose) fprintf(stderr, "---- %s\n%s\n%s\n", name_expr.c_str(), src.c_str(), log->c_str());
+  bool ok = rc == 0;
+  if (ok) {
+    size_t cs = 0;
+    const char* lname = nullptr;
+    ok = n.GetCUBINSize(prog, &cs) == 0 && cs > 0;
+    if (ok) {
+      cubin->resize(cs);
+      ok = n.GetCUBIN(prog, cubin->data()) == 0 && n.GetLoweredName(prog, name_expr.c_str(), &lname) == 0 && lname;
+      if (ok) *lowered = lname;
+    }
+  }
+  n.DestroyProgram(&prog);
+  return ok;
+}
+
+}  // namespace
+
+std::string jit_chain_source(const VmProgram& P, int red_code, const char* family) {
+  const OpText& T = op_text();
+  std::string s;
+  s.reserve(4096);
+  s += "// family: ";
+  s += family;
+  s += "\n#define RX_CHAIN_SPECIALISED 1\n#include \"rx_chain_kernels.cuh\"\nnamespace rx {\nstruct SpecChain {\n";
+  int max_reg = P.result_reg;
+  for (int k = 0; k < P.n_leaves; ++k) max_reg = std::max<int>(max_reg, P.leaf[k].reg);
+  for (int k = 0; k < P.n_outs; ++k) max_reg = std::max<int>(max_reg, P.out[k].reg);
+  for (int k = 0; k < P.n_instr; ++k) {
+    const VmInstr& in = P.ins[k];
+    if (in.flags & VMF_STORE) max_reg = std::max<int>(max_reg, in.dst);
+  }
+  auto I = [](int v) { return std::to_string(v); };
+  s += "  static constexpr int kRegs = " + I(max_reg + 1) + ";\n";
+  s += "  static __device__ __forceinline__ int n_leaves(const VmProgram&) { return " + I(P.n_leaves) + "; }\n";
+  s += "  static __device__ __forceinline__ int n_outs(const VmProgram&) { return " + I(P.n_outs) + "; }\n";
+  s += "  static __device__ __forceinline__ int result_reg(const VmProgram&) { return " + I(P.result_reg) + "; }\n";
+  s += "  static __device__ __forceinline__ int red_code(int c) { return " + (red_code >= 0 ? I(red_code) : std::string("c")) + "; }\n";
+  s += "  static __device__ __forceinline__ int leaf_reg(const VmProgram&, int k) {\n    switch (k) {\n";
+  for (int k = 0; k < P.n_leaves; ++k) s += "      case " + I(k) + ": return " + I(P.leaf[k].reg) + ";\n";
+  s += "    }\n    return 0;\n  }\n";
+  s += "  static __device__ __forceinline__ int out_reg(const VmProgram&, int k) {\n    switch (k) {\n";
+  for (int k = 0; k < P.n_outs; ++k) s += "      case " + I(k) + ": return " + I(P.out[k].reg) + ";\n";
+  s += "    }\n    return 0;\n  }\n";
+  s += "  static __device__ __forceinline__ VmLeaf leaf(const VmProgram& P, int k) {\n    VmLeaf l = P.leaf[k];\n    switch (k) {\n";
+  for (int k = 0; k < P.n_leaves; ++k)
+    s += "      case " + I(k) + ": l.elem = " + I(P.leaf[k].elem) + "; l.linear = " + I(P.leaf[k].linear) + "; break;\n";
+  s += "    }\n    return l;\n  }\n";
+  s += "  static __device__ __forceinline__ VmOut out(const VmProgram& P, int k) {\n    VmOut o = P.out[k];\n    switch (k) {\n";
+  for (int k = 0; k < P.n_outs; ++k) s += "      case " + I(k) + ": o.elem = " + I(P.out[k].elem) + "; break;\n";
+  s += "    }\n    return o;\n  }\n";
+  s += "  template <int V>\n  static __device__ __forceinline__ void exec(const VmProgram& P, uint32_t (*R)[V], const int64_t* idx) {\n";
+  s += "#pragma unroll\n    for (int v = 0; v < V; ++v) {\n      uint32_t acc = 0;\n";
+  for (int k = 0; k < P.n_instr; ++k) {
+    const VmInstr& in = P.ins[k];
+    const std::string rb = "R[" + I(in.b) + "][v]", rc = "R[" + I(in.c) + "][v]";
+    if (in.op == VM_LD) {
+      s += "      acc = " + rb + ";\n";
+    } else if (in.op == VM_IOTA) {
+      s += "      acc = (uint32_t)(int32_t)(idx[" + I(in.a) + "] + (" + I(in.a) + " == P.rank - 1 ? v : 0));\n";
+    } else if (in.op == VM_SELECT) {
+      s += "      acc = acc ? " + rb + " : " + rc + ";\n";
+    } else if (in.op == VM_MULADD) {
+      s += "      acc = f2u(__fadd_rn(__fmul_rn(u2f(acc), u2f(" + rb + ")), u2f(" + rc + ")));\n";
+    } else if (in.op == VM_MULADD_C) {
+      s += "      acc = f2u(__fadd_rn(__fmul_rn(u2f(" + rb + "), u2f(" + rc + ")), u2f(acc)));\n";
+    } else if (T.unary[in.op]) {
+      s += "      { const uint32_t ua = acc, imm = " + hex32(in.imm) + "; const float a = u2f(ua), fimm = u2f(imm); const int32_t ia = (int32_t)ua; acc = (" +
+           T.unary[in.op] + "); }\n";
+    } else if (T.binary[in.op]) {
+      s += "      { const uint32_t ua = acc, ub = " + rb + "; const float a = u2f(ua), b = u2f(ub); const int32_t ia = (int32_t)ua, ib = (int32_t)ub; const int cdir = " +
+           I(in.c) + "; acc = (" + T.binary[in.op] + "); }\n";
+    } else {
+      s += "      // op " + I(in.op) + " has no effect\n";
+    }
+    if (in.flags & VMF_STORE) s += "      R[" + I(in.dst) + "][v] = acc;\n";
+  }
+  s += "    }\n  }\n};\n}  // namespace rx\n";
+  return s;
+}
+
+int64_t jit_compile_only(const VmProgram& P, int red_code, const char* family, std::string* log) {
+  if (!nvrtc().ok) {
+    *log = "NVRTC library not found";
+    return -1;
+  }
+  std::vector<char> cubin;
+  std::string lowered;
+  if (!compile(jit_chain_source(P, red_code, family), std::string("rx::") + family, &cubin, &lowered, log)) return -1;
+  return (int64_t)cubin.size();
+}
+
+void jit_set_min_elems(int64_t n) {
+  std::lock_guard<std::mutex> g(g_mu);
+  g_min_elems = n;
+}
+
+void jit_stats(int64_t out[4]) {
+  std::lock_guard<std::mutex> g(g_mu);
+  out[0] = g_compiled;
+  out[1] = g_hits;
+  out[2] = g_failed;
+  out[3] = (nvrtc().ok && driver().ok) ? 0 : 1;
+}
+
+const JitKernel* jit_chain_kernel(int device, const VmProgram& P, const char* family, int red_code, int64_t work_elems, bool* failed) {
+  *failed = false;
+  std::lock_guard<std::mutex> g(g_mu);
+  if (g_min_elems < 0 || work_elems < g_min_elems) return nullptr;
+  if (!nvrtc().ok || !driver().ok) return nullptr;
+  const std::string src = jit_chain_source(P, red_code, family);
+  auto key = std::make_pair(device, src);
+  auto it = g_kernels.find(key);
+  if (it != g_kernels.end()) {
+    ++g_hits;
+    return &it->second;
+  }
+  auto fail = [&](const std::string& msg) -> const JitKernel* {
+    ++g_failed;
+    *failed = true;
+    set_last_error(RX_ERR_CUDA, "chain specialisation (" + std::string(family) + "): " + msg);
+    return nullptr;
+  };
+  if (!g_cubins.count(src)) {
+    std::vector<char> cubin;
+    std::string lowered, log;
+    if (!compile(src, std::string("rx::") + family, &cubin, &lowered, &log)) return fail("NVRTC: " + log);
+    g_cubins[src] = std::move(cubin);
+    g_lowered[src] = lowered;
+    ++g_compiled;
+  }
+  const Driver& d = driver();
+  CUmodule mod = nullptr;
+  CUfunction fn = nullptr;
+  CUresult r = d.ModuleLoadData(&mod, g_cubins[src].data());
+  if (r != CUDA_SUCCESS) return fail("cuModuleLoadData returned " + std::to_string((int)r));
+  r = d.ModuleGetFunction(&fn, mod, g_lowered[src].c_str());
+  if (r != CUDA_SUCCESS) return fail("cuModuleGetFunction(" + g_lowered[src] + ") returned " + std::to_string((int)r));
+  JitKernel k;
+  k.fn = (void*)fn;
+  int occ = 0;
+  if (d.Occupancy(&occ, fn, 256, 0) != CUDA_SUCCESS || occ < 1) occ = 4;
+  k.occupancy = occ;
+  return &(g_kernels[key] = k);
+}
+
+cudaError_t jit_launch(const JitKernel* k, dim3 grid, dim3 block, void** args, cudaStream_t stream) {
+  CUresult r = driver().LaunchKernel((CUfunction)k->fn, grid.x, grid.y, grid.z, block.x, block.y, block.z, 0, (CUstream)stream, args, nullptr);
+  return r == CUDA_SUCCESS ? cudaSuccess : (cudaError_t)r;
+}
+
+}  // namespace rx

@@ -1,0 +1,46 @@
+// Run-time specialisation of fused chains.
+//
+// The ahead-of-time kernels evaluate a fusion group's elementwise chain with a bytecode
+// interpreter, which costs tens of machine instructions per chain op.  For launches large
+// enough to be bandwidth-bound, the same kernel skeleton (rx_chain_kernels.cuh) is compiled
+// once per distinct chain with NVRTC for sm_100a, with the chain as straight-line code and
+// the leaf kinds, register numbers and reduction kind as constants; the cubin is loaded
+// through the driver API and cached per device.  XLA plays this role for Reactant
+// (src/Compiler.jl:1402-1480 hands the module to XLA.compile, which emits PTX per fusion).
+//
+// Specialisation never changes results: generated code pastes the op expressions of
+// RX_VM_UNARY_OPS / RX_VM_BINARY_OPS (rx_vm.h) that the interpreter itself is built from.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "rx_vm.h"
+
+namespace rx {
+
+struct JitKernel {
+  void* fn = nullptr;  // CUfunction
+  int occupancy = 1;   // resident CTAs per SM at 256 threads
+};
+
+// A kernel of `family` (e.g. "k_map_rows<rx::SpecChain, 2>") specialised for P's chain.
+// nullptr when specialisation is switched off, the work is below the threshold, or NVRTC /
+// the driver entry points are not available (the caller then runs the interpreter kernel).
+// A chain that fails to compile is an error: *failed is set and the message goes to the
+// library's last-error slot.
+const JitKernel* jit_chain_kernel(int device, const VmProgram& P, const char* family, int red_code, int64_t work_elems, bool* failed);
+
+cudaError_t jit_launch(const JitKernel* k, dim3 grid, dim3 block, void** args, cudaStream_t stream);
+
+// Threshold in elements per launch (default 2^20); negative switches specialisation off.
+void jit_set_min_elems(int64_t n);
+// {kernels compiled, cache hits, compile failures, 1 if NVRTC or the driver API is unavailable}
+void jit_stats(int64_t out[4]);
+// Compile only (needs NVRTC but no device): size of the cubin, or -1 with the compiler log in *log.
+int64_t jit_compile_only(const VmProgram& P, int red_code, const char* family, std::string* log);
+// Generated source for P (exposed for tests and for reading).
+std::string jit_chain_source(const VmProgram& P, int red_code, const char* family);
+
+}  // namespace rx

@@ -15,239 +15,29 @@
 #include <stdio.h>
 #include <algorithm>
 
-#include "rx_device.cuh"
+#include "rx_chain_kernels.cuh"
+#include "rx_jit.h"
 
 namespace rx {
 
 namespace {
 
-constexpr int kThreads = 256;
-
-// Second pass of the cross-CTA combine, run by whichever CTA finishes last: it adds
-// the per-CTA partials in index order, so the result does not depend on which CTA
-// that is.  `ticket` counts finished CTAs and is reset for the next launch.
-__device__ __forceinline__ void finish_in_last_block(uint32_t mine, uint32_t* partials, unsigned* ticket, int code, uint32_t init_bits, const VmOut& out,
-                                                     uint32_t* sm, const FusedAllReduce& ar) {
-  __shared__ bool is_last;
-  if (threadIdx.x == 0) {
-    partials[blockIdx.x] = mine;
-    __threadfence();
-    unsigned t = atomicAdd(ticket, 1u);
-    is_last = (t == gridDim.x - 1);
+// Chain policy of the ahead-of-time kernels: the bytecode interpreter, everything read from P.
+struct InterpChain {
+  static constexpr int kRegs = kVmMaxRegs;
+  static __device__ __forceinline__ int n_leaves(const VmProgram& P) { return P.n_leaves; }
+  static __device__ __forceinline__ int n_outs(const VmProgram& P) { return P.n_outs; }
+  static __device__ __forceinline__ int result_reg(const VmProgram& P) { return P.result_reg; }
+  static __device__ __forceinline__ int red_code(int c) { return c; }
+  static __device__ __forceinline__ int leaf_reg(const VmProgram& P, int k) { return P.leaf[k].reg; }
+  static __device__ __forceinline__ int out_reg(const VmProgram& P, int k) { return P.out[k].reg; }
+  static __device__ __forceinline__ const VmLeaf& leaf(const VmProgram& P, int k) { return P.leaf[k]; }
+  static __device__ __forceinline__ const VmOut& out(const VmProgram& P, int k) { return P.out[k]; }
+  template <int V>
+  static __device__ __forceinline__ void exec(const VmProgram& P, uint32_t (*R)[V], const int64_t* idx) {
+    vm_exec<V>(P, R, idx);
   }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  uint32_t acc = red_identity(code);
-  for (int i = threadIdx.x; i < (int)gridDim.x; i += kThreads) acc = red_combine(code, acc, __ldcg(partials + i));
-  // block_red<kThreads>, inlined here because this branch is taken by one whole CTA only
-  acc = warp_red(code, acc);
-  int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  __syncthreads();
-  if (lane == 0) sm[w] = acc;
-  __syncthreads();
-  if (w == 0) {
-    uint32_t x = lane < kThreads / 32 ? sm[lane] : red_identity(code);
-    x = warp_red(code, x);
-    x = red_combine(code, init_bits, x);
-    if (ar.n > 1) {
-      // sharded reduce: exchange this device's partial with the mesh before storing (f32 sum only)
-      float total;
-      if (!mailbox_allreduce_warp(ar, u2f(x), &total)) total = u2f(x);
-      x = f2u(total);
-    }
-    if (lane == 0) {
-      store_elem(out.ptr, out.offset, out.elem, x);
-      *ticket = 0;
-    }
-  }
-}
-
-// ---- vector leaf access (4 consecutive elements, 4-element aligned) ----------
-__device__ __forceinline__ void load4(const VmLeaf& l, int64_t i, uint32_t* d) {
-  if (l.linear == 2) {
-    uint32_t u = load_elem(l.ptr, l.offset, l.elem);
-    *(uint4*)d = make_uint4(u, u, u, u);
-    return;
-  }
-  switch (l.elem) {
-    case EL_F32:
-    case EL_I32: {
-      *(uint4*)d = __ldg((const uint4*)((const uint32_t*)l.ptr + l.offset + i));
-      break;
-    }
-    case EL_BF16: {
-      uint2 v = __ldg((const uint2*)((const uint16_t*)l.ptr + l.offset + i));
-      *(uint4*)d = make_uint4(v.x << 16, v.x & 0xFFFF0000u, v.y << 16, v.y & 0xFFFF0000u);
-      break;
-    }
-    default: {
-      uchar4 v = __ldg((const uchar4*)((const uint8_t*)l.ptr + l.offset + i));
-      *(uint4*)d = make_uint4(v.x != 0, v.y != 0, v.z != 0, v.w != 0);
-      break;
-    }
-  }
-}
-
-__device__ __forceinline__ void store4(const VmOut& o, int64_t i, const uint32_t* s) {
-  switch (o.elem) {
-    case EL_F32:
-    case EL_I32:
-      *(uint4*)((uint32_t*)o.ptr + o.offset + i) = make_uint4(s[0], s[1], s[2], s[3]);
-      break;
-    case EL_BF16: {
-      __nv_bfloat162 a = __floats2bfloat162_rn(u2f(s[0]), u2f(s[1]));
-      __nv_bfloat162 b = __floats2bfloat162_rn(u2f(s[2]), u2f(s[3]));
-      uint2 v;
-      v.x = *(uint32_t*)&a;
-      v.y = *(uint32_t*)&b;
-      *(uint2*)((uint16_t*)o.ptr + o.offset + i) = v;
-      break;
-    }
-    default:
-      *(uchar4*)((uint8_t*)o.ptr + o.offset + i) = make_uchar4(s[0] != 0, s[1] != 0, s[2] != 0, s[3] != 0);
-      break;
-  }
-}
-
-// ---- map ----------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads) k_map_linear(const __grid_constant__ VmProgram P, int64_t n) {
-  int64_t n4 = n >> 2;
-  int64_t stride = (int64_t)gridDim.x * kThreads;
-  int64_t idx0[kMaxRank] = {0, 0, 0, 0};
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += stride) {
-    __align__(16) uint32_t R[kVmMaxRegs][4];
-    for (int k = 0; k < P.n_leaves; ++k) load4(P.leaf[k], i * 4, R[P.leaf[k].reg]);
-    vm_exec<4>(P, R, idx0);
-    for (int k = 0; k < P.n_outs; ++k) store4(P.out[k], i * 4, R[P.out[k].reg]);
-  }
-  // tail
-  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
-    int64_t i = n4 * 4 + threadIdx.x;
-    __align__(16) uint32_t R[kVmMaxRegs][1];
-    for (int k = 0; k < P.n_leaves; ++k)
-      R[P.leaf[k].reg][0] = load_elem(P.leaf[k].ptr, P.leaf[k].offset + (P.leaf[k].linear == 2 ? 0 : i), P.leaf[k].elem);
-    vm_exec<1>(P, R, idx0);
-    for (int k = 0; k < P.n_outs; ++k) store_elem(P.out[k].ptr, P.out[k].offset + i, P.out[k].elem, R[P.out[k].reg][0]);
-  }
-}
-
-template <bool SMALL>
-__global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant__ VmProgram P, int64_t n) {
-  int64_t stride = (int64_t)gridDim.x * kThreads;
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
-    int64_t idx[kMaxRank];
-    if (SMALL) unravel32(P, (uint32_t)i, idx);
-    else unravel(P, i, idx);
-    __align__(16) uint32_t R[kVmMaxRegs][1];
-    for (int k = 0; k < P.n_leaves; ++k) R[P.leaf[k].reg][0] = load_elem(P.leaf[k].ptr, leaf_offset(P.leaf[k], idx, P.rank), P.leaf[k].elem);
-    vm_exec<1>(P, R, idx);
-    for (int k = 0; k < P.n_outs; ++k) store_elem(P.out[k].ptr, out_offset(P.out[k], idx, P.rank), P.out[k].elem, R[P.out[k].reg][0]);
-  }
-}
-
-
-// ---- 2-D "row-vector" access: 4 consecutive elements of the innermost dim, operands either
-// contiguous along it (stride 1) or broadcast along it (stride 0); any stride along the row dim.
-__device__ __forceinline__ void load4_rowvec(const VmLeaf& l, int64_t row, int64_t col, int drow, int dcol, uint32_t* d) {
-  int64_t off = l.offset + row * l.stride[drow];
-  if (l.stride[dcol] == 0) {
-    uint32_t u = load_elem(l.ptr, off, l.elem);
-    *(uint4*)d = make_uint4(u, u, u, u);
-    return;
-  }
-  off += col;
-  switch (l.elem) {
-    case EL_F32:
-    case EL_I32: {
-      *(uint4*)d = __ldg((const uint4*)((const uint32_t*)l.ptr + off));
-      break;
-    }
-    case EL_BF16: {
-      uint2 v = __ldg((const uint2*)((const uint16_t*)l.ptr + off));
-      *(uint4*)d = make_uint4(v.x << 16, v.x & 0xFFFF0000u, v.y << 16, v.y & 0xFFFF0000u);
-      break;
-    }
-    default: {
-      uchar4 v = __ldg((const uchar4*)((const uint8_t*)l.ptr + off));
-      *(uint4*)d = make_uint4(v.x != 0, v.y != 0, v.z != 0, v.w != 0);
-      break;
-    }
-  }
-}
-
-__device__ __forceinline__ void store4_rowvec(const VmOut& o, int64_t row, int64_t col, int drow, const uint32_t* s) {
-  VmOut t = o;
-  t.offset = o.offset + row * o.stride[drow] + col;
-  store4(t, 0, s);
-}
-
-// map over [rows][cols], 4*U columns per thread (U = 2 halves the interpreter's per-lane dispatch cost)
-template <int U>
-__global__ void __launch_bounds__(kThreads) k_map_rows(const __grid_constant__ VmProgram P, int64_t rows, int64_t cols) {
-  constexpr int V = 4 * U;
-  const int64_t cv = cols / V, total = rows * cv;
-  const int64_t stride = (int64_t)gridDim.x * kThreads;
-  int64_t idx0[kMaxRank] = {0, 0, 0, 0};
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
-    int64_t row, col;
-    if (total < ((int64_t)1 << 31)) { uint32_t r = (uint32_t)i / (uint32_t)cv; row = r; col = (int64_t)((uint32_t)i - r * (uint32_t)cv) * V; }
-    else { row = i / cv; col = (i - row * cv) * V; }
-    __align__(16) uint32_t R[kVmMaxRegs][V];
-    for (int k = 0; k < P.n_leaves; ++k)
-#pragma unroll
-      for (int u = 0; u < U; ++u) load4_rowvec(P.leaf[k], row, col + 4 * u, 0, 1, R[P.leaf[k].reg] + 4 * u);
-    vm_exec<V>(P, R, idx0);
-    for (int k = 0; k < P.n_outs; ++k)
-#pragma unroll
-      for (int u = 0; u < U; ++u) store4_rowvec(P.out[k], row, col + 4 * u, 0, R[P.out[k].reg] + 4 * u);
-  }
-}
-
-// full reduce over [rows][cols], 4 columns per thread
-__global__ void __launch_bounds__(kThreads) k_reduce_full_rows(const __grid_constant__ VmProgram P, int64_t rows, int64_t cols, int code, uint32_t* __restrict__ partials,
-                                                               unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar) {
-  __shared__ uint32_t sm[kThreads / 32];
-  const int64_t c4 = cols >> 2, total = rows * c4;
-  const int64_t stride = (int64_t)gridDim.x * kThreads;
-  int64_t idx0[kMaxRank] = {0, 0, 0, 0};
-  uint32_t acc[4];
-  for (int v = 0; v < 4; ++v) acc[v] = red_identity(code);
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
-    int64_t row, col;
-    if (total < ((int64_t)1 << 31)) { uint32_t r = (uint32_t)i / (uint32_t)c4; row = r; col = ((uint32_t)i - r * (uint32_t)c4) * 4; }
-    else { row = i / c4; col = (i - row * c4) * 4; }
-    __align__(16) uint32_t R[kVmMaxRegs][4];
-    for (int k = 0; k < P.n_leaves; ++k) load4_rowvec(P.leaf[k], row, col, 0, 1, R[P.leaf[k].reg]);
-    vm_exec<4>(P, R, idx0);
-#pragma unroll
-    for (int v = 0; v < 4; ++v) acc[v] = red_combine(code, acc[v], R[P.result_reg][v]);
-  }
-  uint32_t v = red_combine(code, red_combine(code, acc[0], acc[1]), red_combine(code, acc[2], acc[3]));
-  v = block_red<kThreads>(code, v, sm);
-  finish_in_last_block(v, partials, ticket, code, init_bits, P.out[0], sm, ar);
-}
-
-// column reduce over [red][inner] (outer == 1): each thread owns 4 adjacent columns and a slice of rows
-__global__ void __launch_bounds__(kThreads) k_reduce_col_vec(const __grid_constant__ VmProgram P, int code, int64_t red_n, int64_t inner, int nsplit,
-                                                             uint32_t* __restrict__ partials) {
-  const int64_t b4 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) * 4;
-  if (b4 >= inner) return;
-  const int split = blockIdx.y;
-  const int64_t chunk = (red_n + nsplit - 1) / nsplit;
-  const int64_t r0 = split * chunk, r1 = min(red_n, r0 + chunk);
-  int64_t idx0[kMaxRank] = {0, 0, 0, 0};
-  uint32_t acc[4];
-  for (int v = 0; v < 4; ++v) acc[v] = red_identity(code);
-  for (int64_t r = r0; r < r1; ++r) {
-    __align__(16) uint32_t R[kVmMaxRegs][4];
-    for (int k = 0; k < P.n_leaves; ++k) load4_rowvec(P.leaf[k], r, b4, 1, 2, R[P.leaf[k].reg]);
-    vm_exec<4>(P, R, idx0);
-#pragma unroll
-    for (int v = 0; v < 4; ++v) acc[v] = red_combine(code, acc[v], R[P.result_reg][v]);
-  }
-  *(uint4*)(partials + (int64_t)split * inner + b4) = make_uint4(acc[0], acc[1], acc[2], acc[3]);
-}
+};
 
 // ---- full reduce: pass 1 ---------------------------------------------------------
 // FAST_SIN_ADD: sum(sin(x) + y) with x = leaf 0, y = leaf 1, both contiguous f32.
@@ -279,90 +69,6 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_sinadd(const float* __
   float v = (a0 + a1) + (a2 + a3);
   uint32_t r = block_red<kThreads>(R_FADD, f2u(v), sm);
   finish_in_last_block(r, partials, ticket, R_FADD, init_bits, out, sm, ar);
-}
-
-// Generic chain, all operands contiguous: interpreter on 4 lanes.
-__global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_constant__ VmProgram P, int64_t n, int code, uint32_t* __restrict__ partials,
-                                                                 unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar) {
-  __shared__ uint32_t sm[kThreads / 32];
-  int64_t n4 = n >> 2;
-  int64_t stride = (int64_t)gridDim.x * kThreads;
-  int64_t idx0[kMaxRank] = {0, 0, 0, 0};
-  uint32_t acc[4];
-  for (int v = 0; v < 4; ++v) acc[v] = red_identity(code);
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += stride) {
-    __align__(16) uint32_t R[kVmMaxRegs][4];
-    for (int k = 0; k < P.n_leaves; ++k) load4(P.leaf[k], i * 4, R[P.leaf[k].reg]);
-    vm_exec<4>(P, R, idx0);
-#pragma unroll
-    for (int v = 0; v < 4; ++v) acc[v] = red_combine(code, acc[v], R[P.result_reg][v]);
-  }
-  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
-    int64_t i = n4 * 4 + threadIdx.x;
-    __align__(16) uint32_t R[kVmMaxRegs][1];
-    for (int k = 0; k < P.n_leaves; ++k)
-      R[P.leaf[k].reg][0] = load_elem(P.leaf[k].ptr, P.leaf[k].offset + (P.leaf[k].linear == 2 ? 0 : i), P.leaf[k].elem);
-    vm_exec<1>(P, R, idx0);
-    acc[0] = red_combine(code, acc[0], R[P.result_reg][0]);
-  }
-  uint32_t v = red_combine(code, red_combine(code, acc[0], acc[1]), red_combine(code, acc[2], acc[3]));
-  v = block_red<kThreads>(code, v, sm);
-  finish_in_last_block(v, partials, ticket, code, init_bits, P.out[0], sm, ar);
-}
-
-// Generic chain, strided operands.
-__global__ void __launch_bounds__(kThreads) k_reduce_full_generic(const __grid_constant__ VmProgram P, int64_t n, int code, uint32_t* __restrict__ partials,
-                                                                  unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar) {
-  __shared__ uint32_t sm[kThreads / 32];
-  int64_t stride = (int64_t)gridDim.x * kThreads;
-  uint32_t acc = red_identity(code);
-  const bool small = n < ((int64_t)1 << 31);
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
-    int64_t idx[kMaxRank];
-    if (small) unravel32(P, (uint32_t)i, idx);
-    else unravel(P, i, idx);
-    acc = red_combine(code, acc, vm_eval_at(P, idx));
-  }
-  acc = block_red<kThreads>(code, acc, sm);
-  finish_in_last_block(acc, partials, ticket, code, init_bits, P.out[0], sm, ar);
-}
-
-// ---- reduce along one axis: [outer][red] with TPR threads per row --------------------
-template <int TPR>
-__global__ void __launch_bounds__(kThreads) k_reduce_row(const __grid_constant__ VmProgram P, int code, uint32_t init_bits, int64_t outer, int64_t red_n) {
-  __shared__ uint32_t sm[kThreads / 32];
-  constexpr int RPB = kThreads / TPR;
-  int64_t row = (int64_t)blockIdx.x * RPB + threadIdx.x / TPR;
-  int lane = threadIdx.x % TPR;
-  uint32_t acc = red_identity(code);
-  if (row < outer) {
-    int64_t idx[kMaxRank] = {row, 0, 0, 0};
-    for (int64_t r = lane; r < red_n; r += TPR) {
-      idx[1] = r;
-      acc = red_combine(code, acc, vm_eval_at(P, idx));
-    }
-  }
-  if (TPR == kThreads) acc = block_red<kThreads>(code, acc, sm);
-  else if (TPR == 32) acc = warp_red(code, acc);
-  if (lane == 0 && row < outer) store_elem(P.out[0].ptr, P.out[0].offset + row * P.out[0].stride[0], P.out[0].elem, red_combine(code, init_bits, acc));
-}
-
-// ---- reduce along a strided axis: [outer][red][inner], threads along inner -----------
-__global__ void __launch_bounds__(kThreads) k_reduce_col(const __grid_constant__ VmProgram P, int code, int64_t outer, int64_t red_n, int64_t inner, int nsplit, uint32_t* __restrict__ partials) {
-  int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-  if (b >= inner) return;
-  int split = blockIdx.y;
-  int64_t chunk = (red_n + nsplit - 1) / nsplit;
-  int64_t r0 = split * chunk, r1 = min(red_n, r0 + chunk);
-  for (int64_t o = blockIdx.z; o < outer; o += gridDim.z) {
-    int64_t idx[kMaxRank] = {o, 0, b, 0};
-    uint32_t acc = red_identity(code);
-    for (int64_t r = r0; r < r1; ++r) {
-      idx[1] = r;
-      acc = red_combine(code, acc, vm_eval_at(P, idx));
-    }
-    partials[(o * nsplit + split) * inner + b] = acc;
-  }
 }
 
 // Second pass of the strided-axis reduce: one CTA per 32 adjacent columns of one outer index.  Warp w
@@ -533,20 +239,56 @@ int red_code(RedK k, DT dt) {
   }
 }
 
+// Launch `family` specialised for P's chain when that is worthwhile and possible; otherwise (*ran == false)
+// the caller launches the interpreter kernel.
+cudaError_t try_specialised(const LaunchCtx& c, const VmProgram& P, const char* family, int code, int64_t work, dim3 grid, void** args, bool* ran,
+                            int* occupancy = nullptr) {
+  *ran = false;
+  bool failed = false;
+  const JitKernel* k = jit_chain_kernel(c.device, P, family, code, work, &failed);
+  if (failed) return cudaErrorUnknown;
+  if (!k) return cudaSuccess;
+  if (occupancy) {  // the caller only wanted to size its grid
+    *occupancy = k->occupancy;
+    return cudaSuccess;
+  }
+  *ran = true;
+  return jit_launch(k, grid, dim3(kThreads), args, c.stream);
+}
+
 cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
   int64_t n = total_of(P);
   if (n == 0) return cudaSuccess;
+  bool ran = false;
+  cudaError_t e = cudaSuccess;
   if (P.all_linear && vec_aligned(P)) {
-    k_map_linear<<<grid_for((n + 3) / 4, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
+    dim3 grid(grid_for((n + 3) / 4, c.sm_count, 8));
+    void* args[] = {(void*)&P, (void*)&n};
+    e = try_specialised(c, P, "k_map_linear<rx::SpecChain>", -1, n, grid, args, &ran);
+    if (!ran && e == cudaSuccess) k_map_linear<InterpChain><<<grid, kThreads, 0, c.stream>>>(P, n);
   } else if (P.rank == 2 && rowvec_ok(P, 0, 1, true)) {
-    static const int per_sm = getenv("RX_MAP_CTAS") ? atoi(getenv("RX_MAP_CTAS")) : 8;
-    static const int lanes = getenv("RX_MAP_LANES") ? atoi(getenv("RX_MAP_LANES")) : 8;
-    if (P.dim[1] % 8 == 0 && lanes == 8) k_map_rows<2><<<grid_for(n / 8, c.sm_count, per_sm), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
-    else k_map_rows<1><<<grid_for(n / 4, c.sm_count, per_sm), kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1]);
+    int64_t rows = P.dim[0], cols = P.dim[1];
+    void* args[] = {(void*)&P, (void*)&rows, (void*)&cols};
+    if (cols % 8 == 0) {
+      dim3 grid(grid_for(n / 8, c.sm_count, 8));
+      e = try_specialised(c, P, "k_map_rows<rx::SpecChain, 2>", -1, n, grid, args, &ran);
+      if (!ran && e == cudaSuccess) k_map_rows<InterpChain, 2><<<grid, kThreads, 0, c.stream>>>(P, rows, cols);
+    } else {
+      dim3 grid(grid_for(n / 4, c.sm_count, 8));
+      e = try_specialised(c, P, "k_map_rows<rx::SpecChain, 1>", -1, n, grid, args, &ran);
+      if (!ran && e == cudaSuccess) k_map_rows<InterpChain, 1><<<grid, kThreads, 0, c.stream>>>(P, rows, cols);
+    }
   } else {
-    if (n < ((int64_t)1 << 31)) k_map_generic<true><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
-    else k_map_generic<false><<<grid_for(n, c.sm_count, 8), kThreads, 0, c.stream>>>(P, n);
+    dim3 grid(grid_for(n, c.sm_count, 8));
+    void* args[] = {(void*)&P, (void*)&n};
+    const bool small = n < ((int64_t)1 << 31);
+    e = try_specialised(c, P, small ? "k_map_generic<rx::SpecChain, true>" : "k_map_generic<rx::SpecChain, false>", -1, n, grid, args, &ran);
+    if (!ran && e == cudaSuccess) {
+      if (small) k_map_generic<InterpChain, true><<<grid, kThreads, 0, c.stream>>>(P, n);
+      else k_map_generic<InterpChain, false><<<grid, kThreads, 0, c.stream>>>(P, n);
+    }
   }
+  if (e != cudaSuccess) return e;
   ++*c.launches;
   return cudaGetLastError();
 }
@@ -567,40 +309,67 @@ cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code,
   FusedAllReduce ar{};
   if (fused) ar = *fused;
   int64_t n = total_of(P);
-  static const int occ_sinadd = resident_per_sm(k_reduce_full_sinadd), occ_linear = resident_per_sm(k_reduce_full_linear),
-                   occ_rows = resident_per_sm(k_reduce_full_rows), occ_generic = resident_per_sm(k_reduce_full_generic);
-  const bool vec0 = P.all_linear && vec_aligned(P);
-  const int occ = (vec0 && P.fast_id == FAST_SIN_ADD && code == R_FADD) ? occ_sinadd : vec0 ? occ_linear : (P.rank == 2 && rowvec_ok(P, 0, 1, false)) ? occ_rows : occ_generic;
+  static const int occ_sinadd = resident_per_sm(k_reduce_full_sinadd), occ_linear = resident_per_sm(k_reduce_full_linear<InterpChain>),
+                   occ_rows = resident_per_sm(k_reduce_full_rows<InterpChain>), occ_generic = resident_per_sm(k_reduce_full_generic<InterpChain>);
+  const bool vec = P.all_linear && vec_aligned(P);
+  const bool sinadd = vec && P.fast_id == FAST_SIN_ADD && code == R_FADD;
+  const bool rows2 = !vec && P.rank == 2 && rowvec_ok(P, 0, 1, false);
+  const char* family = vec ? "k_reduce_full_linear<rx::SpecChain>" : rows2 ? "k_reduce_full_rows<rx::SpecChain>" : "k_reduce_full_generic<rx::SpecChain>";
+  int occ = sinadd ? occ_sinadd : vec ? occ_linear : rows2 ? occ_rows : occ_generic;
+  bool ran = false;
+  if (!sinadd) {  // a specialised kernel has its own register count, hence its own resident wave
+    cudaError_t e = try_specialised(c, P, family, code, n, dim3(1), nullptr, &ran, &occ);
+    if (e != cudaSuccess) return e;
+  }
   // 16 elements per thread per trip keeps four 128-bit loads in flight per operand
   int blocks = grid_for((n + 15) / 16, c.sm_count, occ);
   if ((size_t)blocks + 1 > c.scratch_words) return cudaErrorInvalidValue;
   uint32_t* partials = c.scratch;
   unsigned* ticket = (unsigned*)(c.scratch + c.scratch_words - 1);  // zeroed at device creation, reset by each launch
-  bool vec = P.all_linear && vec_aligned(P);
-  if (vec && P.fast_id == FAST_SIN_ADD && code == R_FADD) {
+  cudaError_t e = cudaSuccess;
+  if (sinadd) {
     const float* x = (const float*)P.leaf[0].ptr + P.leaf[0].offset;
     const float* y = (const float*)P.leaf[1].ptr + P.leaf[1].offset;
     k_reduce_full_sinadd<<<blocks, kThreads, 0, c.stream>>>(x, y, n, partials, ticket, init_bits, P.out[0], ar);
   } else if (vec) {
-    k_reduce_full_linear<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
-  } else if (P.rank == 2 && rowvec_ok(P, 0, 1, false)) {
-    k_reduce_full_rows<<<blocks, kThreads, 0, c.stream>>>(P, P.dim[0], P.dim[1], code, partials, ticket, init_bits, ar);
+    void* args[] = {(void*)&P, (void*)&n, (void*)&code, (void*)&partials, (void*)&ticket, (void*)&init_bits, (void*)&ar};
+    e = try_specialised(c, P, family, code, n, dim3(blocks), args, &ran);
+    if (!ran && e == cudaSuccess) k_reduce_full_linear<InterpChain><<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
+  } else if (rows2) {
+    int64_t rows = P.dim[0], cols = P.dim[1];
+    void* args[] = {(void*)&P, (void*)&rows, (void*)&cols, (void*)&code, (void*)&partials, (void*)&ticket, (void*)&init_bits, (void*)&ar};
+    e = try_specialised(c, P, family, code, n, dim3(blocks), args, &ran);
+    if (!ran && e == cudaSuccess) k_reduce_full_rows<InterpChain><<<blocks, kThreads, 0, c.stream>>>(P, rows, cols, code, partials, ticket, init_bits, ar);
   } else {
-    k_reduce_full_generic<<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
+    void* args[] = {(void*)&P, (void*)&n, (void*)&code, (void*)&partials, (void*)&ticket, (void*)&init_bits, (void*)&ar};
+    e = try_specialised(c, P, family, code, n, dim3(blocks), args, &ran);
+    if (!ran && e == cudaSuccess) k_reduce_full_generic<InterpChain><<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
   }
+  if (e != cudaSuccess) return e;
   *c.launches += 1;
   return cudaGetLastError();
 }
 
 cudaError_t launch_reduce_row(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, int64_t outer, int64_t red_n) {
   if (outer == 0) return cudaSuccess;
+  void* args[] = {(void*)&P, (void*)&code, (void*)&init_bits, (void*)&outer, (void*)&red_n};
+  bool ran = false;
+  cudaError_t e;
+  const int64_t work = outer * red_n;
   if (red_n >= 2048) {
-    k_reduce_row<kThreads><<<(unsigned)outer, kThreads, 0, c.stream>>>(P, code, init_bits, outer, red_n);
+    dim3 grid((unsigned)outer);
+    e = try_specialised(c, P, "k_reduce_row<rx::SpecChain, 256>", code, work, grid, args, &ran);
+    if (!ran && e == cudaSuccess) k_reduce_row<InterpChain, kThreads><<<grid, kThreads, 0, c.stream>>>(P, code, init_bits, outer, red_n);
   } else if (red_n >= 16) {
-    k_reduce_row<32><<<(unsigned)((outer + 7) / 8), kThreads, 0, c.stream>>>(P, code, init_bits, outer, red_n);
+    dim3 grid((unsigned)((outer + 7) / 8));
+    e = try_specialised(c, P, "k_reduce_row<rx::SpecChain, 32>", code, work, grid, args, &ran);
+    if (!ran && e == cudaSuccess) k_reduce_row<InterpChain, 32><<<grid, kThreads, 0, c.stream>>>(P, code, init_bits, outer, red_n);
   } else {
-    k_reduce_row<1><<<(unsigned)((outer + kThreads - 1) / kThreads), kThreads, 0, c.stream>>>(P, code, init_bits, outer, red_n);
+    dim3 grid((unsigned)((outer + kThreads - 1) / kThreads));
+    e = try_specialised(c, P, "k_reduce_row<rx::SpecChain, 1>", code, work, grid, args, &ran);
+    if (!ran && e == cudaSuccess) k_reduce_row<InterpChain, 1><<<grid, kThreads, 0, c.stream>>>(P, code, init_bits, outer, red_n);
   }
+  if (e != cudaSuccess) return e;
   ++*c.launches;
   return cudaGetLastError();
 }
@@ -615,13 +384,21 @@ int reduce_col_splits(int64_t outer, int64_t red_n, int64_t inner, int sm_count)
 
 cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, int64_t outer, int64_t red_n, int64_t inner, uint32_t* partials, int nsplit) {
   if (outer * inner == 0) return cudaSuccess;
+  bool ran = false;
+  cudaError_t e;
+  const int64_t work = outer * red_n * inner;
   if (outer == 1 && rowvec_ok(P, 1, 2, false)) {
     dim3 grid((unsigned)((inner / 4 + kThreads - 1) / kThreads), (unsigned)nsplit, 1);
-    k_reduce_col_vec<<<grid, kThreads, 0, c.stream>>>(P, code, red_n, inner, nsplit, partials);
+    void* args[] = {(void*)&P, (void*)&code, (void*)&red_n, (void*)&inner, (void*)&nsplit, (void*)&partials};
+    e = try_specialised(c, P, "k_reduce_col_vec<rx::SpecChain>", code, work, grid, args, &ran);
+    if (!ran && e == cudaSuccess) k_reduce_col_vec<InterpChain><<<grid, kThreads, 0, c.stream>>>(P, code, red_n, inner, nsplit, partials);
   } else {
     dim3 grid((unsigned)((inner + kThreads - 1) / kThreads), (unsigned)nsplit, (unsigned)std::min<int64_t>(outer, 65535));
-    k_reduce_col<<<grid, kThreads, 0, c.stream>>>(P, code, outer, red_n, inner, nsplit, partials);
+    void* args[] = {(void*)&P, (void*)&code, (void*)&outer, (void*)&red_n, (void*)&inner, (void*)&nsplit, (void*)&partials};
+    e = try_specialised(c, P, "k_reduce_col<rx::SpecChain>", code, work, grid, args, &ran);
+    if (!ran && e == cudaSuccess) k_reduce_col<InterpChain><<<grid, kThreads, 0, c.stream>>>(P, code, outer, red_n, inner, nsplit, partials);
   }
+  if (e != cudaSuccess) return e;
   k_reduce_col_finish<<<(unsigned)(outer * ((inner + 31) / 32)), kThreads, 0, c.stream>>>(partials, code, init_bits, outer, nsplit, inner, P.out[0]);
   *c.launches += 2;
   return cudaGetLastError();

@@ -11,6 +11,7 @@ namespace rx {
 struct LaunchCtx {
   cudaStream_t stream = nullptr;
   int sm_count = 148;
+  int device = 0;                // CUDA ordinal: specialised kernels are loaded per device
   uint32_t* scratch = nullptr;   // per-device partials buffer for two-pass reductions
   size_t scratch_words = 0;
   uint64_t* launches = nullptr;  // counts kernels launched through this context

@@ -15,6 +15,7 @@
 #include "../../include/rx_b200.h"
 #include "rx_collective.h"
 #include "rx_gemm.h"
+#include "rx_jit.h"
 #include "rx_stencil.h"
 
 using namespace rx;
@@ -748,6 +749,49 @@ const char* RxPlanDescribe(const char* text, size_t len) {
   auto plan = build_plan(*mod);
   return dup_cstr(plan->describe());
   API_END(nullptr)
+}
+
+static void specialise_check_steps(const std::vector<Step>& steps, std::string& out, bool& first) {
+  for (const Step& st : steps) {
+    if (st.kind == StepK::Loop) {
+      specialise_check_steps(st.body, out, first);
+      continue;
+    }
+    std::vector<const char*> families;
+    int code = -1;
+    if (st.kind == StepK::Map) families = {"k_map_linear<rx::SpecChain>", "k_map_rows<rx::SpecChain, 2>", "k_map_generic<rx::SpecChain, true>"};
+    else if (st.kind == StepK::ReduceFull) families = {"k_reduce_full_linear<rx::SpecChain>", "k_reduce_full_rows<rx::SpecChain>", "k_reduce_full_generic<rx::SpecChain>"};
+    else if (st.kind == StepK::ReduceRow) families = {"k_reduce_row<rx::SpecChain, 256>", "k_reduce_row<rx::SpecChain, 32>"};
+    else if (st.kind == StepK::ReduceCol) families = {"k_reduce_col_vec<rx::SpecChain>", "k_reduce_col<rx::SpecChain>"};
+    else continue;
+    if (st.kind != StepK::Map) code = red_code(st.red, st.red_dt);
+    for (const char* fam : families) {
+      std::string log;
+      int64_t bytes = jit_compile_only(st.prog, code, fam, &log);
+      if (bytes < 0) throw Error(RX_ERR_CUDA, std::string("chain of step '") + st.note + "' does not compile as " + fam + ": " + log);
+      out += first ? "" : ",";
+      first = false;
+      out += "{\"step\":\"" + st.note + "\",\"kernel\":\"" + fam + "\",\"cubin_bytes\":" + std::to_string(bytes) + "}";
+    }
+  }
+}
+
+const char* RxPlanSpecialiseCheck(const char* text, size_t len) {
+  API_BEGIN
+  std::string s(text, len);
+  auto mod = parse_module(s);
+  auto plan = build_plan(*mod);
+  std::string out = "[";
+  bool first = true;
+  specialise_check_steps(plan->steps, out, first);
+  out += "]";
+  return dup_cstr(out);
+  API_END(nullptr)
+}
+
+void RxChainSpecialiser(int64_t min_elems) { rx::jit_set_min_elems(min_elems); }
+void RxChainSpecialiserStats(int64_t* out4) {
+  if (out4) rx::jit_stats(out4);
 }
 
 void ExecutableFree(RxExecutable* e) { delete e; }

@@ -65,6 +65,7 @@ struct RxDevice : std::enable_shared_from_this<RxDevice> {
     rx::LaunchCtx c;
     c.stream = stream;
     c.sm_count = sm_count;
+    c.device = ordinal;
     c.scratch = scratch;
     c.scratch_words = scratch_words;
     c.launches = &launches;

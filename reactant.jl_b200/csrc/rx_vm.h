@@ -7,7 +7,18 @@
 // The op set mirrors the scalar emitters of Reactant (src/Ops.jl:398-460 unary,
 // :536-589 binary, :1865-1961 select/compare/convert).
 #pragma once
+#ifdef __CUDACC_RTC__
+// run-time compilation of specialised chains: no host headers are available
+typedef unsigned char uint8_t;
+typedef unsigned short uint16_t;
+typedef unsigned int uint32_t;
+typedef int int32_t;
+typedef long long int64_t;
+typedef unsigned long long uint64_t;
+#define INT32_MIN (-2147483647 - 1)
+#else
 #include <stdint.h>
+#endif
 
 namespace rx {
 
@@ -42,6 +53,70 @@ enum VmOp : uint8_t {
   VM_RDIV,    // acc = R[b] / acc
   VM_NUM_OPS
 };
+
+// Scalar semantics of the ops, written once: the interpreter expands the tables into its
+// switch, and the chain specialiser pastes the same expression text into generated code.
+// Names available to an expression: ua / a / ia = the accumulator as raw bits / f32 / i32,
+// ub / b / ib = the register operand, imm / fimm = the immediate as raw bits / f32,
+// cdir = comparison direction.
+#define RX_VM_UNARY_OPS(X)                                                                     \
+  X(VM_CONST, imm)                                                                             \
+  X(VM_MOV, ua)                                                                                \
+  X(VM_NEG, f2u(-a))                                                                           \
+  X(VM_SIN, f2u(sinf(a)))                                                                      \
+  X(VM_COS, f2u(cosf(a)))                                                                      \
+  X(VM_EXP, f2u(expf(a)))                                                                      \
+  X(VM_LOG, f2u(logf(a)))                                                                      \
+  X(VM_TANH, f2u(tanhf(a)))                                                                    \
+  X(VM_SQRT, f2u(sqrtf(a)))                                                                    \
+  X(VM_RSQRT, f2u(1.0f / sqrtf(a)))                                                            \
+  X(VM_ABS, f2u(fabsf(a)))                                                                     \
+  X(VM_LOG1P, f2u(log1pf(a)))                                                                  \
+  X(VM_EXPM1, f2u(expm1f(a)))                                                                  \
+  X(VM_FLOOR, f2u(floorf(a)))                                                                  \
+  X(VM_CEIL, f2u(ceilf(a)))                                                                    \
+  X(VM_SIGN, f2u((a != a) ? a : (float)((a > 0.f) - (a < 0.f))))                               \
+  X(VM_LOGISTIC, f2u(1.0f / (1.0f + expf(-a))))                                                \
+  X(VM_RBF16, f2u(round_bf16(a)))                                                              \
+  X(VM_SQR, f2u(__fmul_rn(a, a)))                                                              \
+  X(VM_ADDI, f2u(__fadd_rn(a, fimm)))                                                          \
+  X(VM_SUBI, f2u(__fsub_rn(a, fimm)))                                                          \
+  X(VM_RSUBI, f2u(__fsub_rn(fimm, a)))                                                         \
+  X(VM_MULI, f2u(__fmul_rn(a, fimm)))                                                          \
+  X(VM_DIVI, f2u(a / fimm))                                                                    \
+  X(VM_RDIVI, f2u(fimm / a))                                                                   \
+  X(VM_MAXI, f2u(nan_max(a, fimm)))                                                            \
+  X(VM_MINI, f2u(nan_min(a, fimm)))                                                            \
+  X(VM_INEG, (uint32_t)(-ia))                                                                  \
+  X(VM_IABS, (uint32_t)abs(ia))                                                                \
+  X(VM_NOT, ~ua)                                                                               \
+  X(VM_LNOT, ua ? 0u : 1u)                                                                     \
+  X(VM_I2F, f2u((float)ia))                                                                    \
+  X(VM_F2I, (a != a) ? 0u : (uint32_t)(int32_t)fminf(fmaxf(truncf(a), -2147483648.f), 2147483520.f)) \
+  X(VM_P2F, f2u(ua ? 1.f : 0.f))                                                               \
+  X(VM_F2P, (uint32_t)(a != 0.f))                                                              \
+  X(VM_I2P, (uint32_t)(ia != 0))
+#define RX_VM_BINARY_OPS(X)                                                                    \
+  X(VM_ADD, f2u(__fadd_rn(a, b)))                                                              \
+  X(VM_SUB, f2u(__fsub_rn(a, b)))                                                              \
+  X(VM_RSUB, f2u(__fsub_rn(b, a)))                                                             \
+  X(VM_MUL, f2u(__fmul_rn(a, b)))                                                              \
+  X(VM_DIV, f2u(a / b))                                                                        \
+  X(VM_RDIV, f2u(b / a))                                                                       \
+  X(VM_MAX, f2u(nan_max(a, b)))                                                                \
+  X(VM_MIN, f2u(nan_min(a, b)))                                                                \
+  X(VM_POW, f2u(powf(a, b)))                                                                   \
+  X(VM_IADD, (uint32_t)(ia + ib))                                                              \
+  X(VM_ISUB, (uint32_t)(ia - ib))                                                              \
+  X(VM_IMUL, (uint32_t)(ia * ib))                                                              \
+  X(VM_IDIV, ib == 0 ? 0xFFFFFFFFu : ((ia == INT32_MIN && ib == -1) ? (uint32_t)INT32_MIN : (uint32_t)(ia / ib))) \
+  X(VM_IMAX, (uint32_t)max(ia, ib))                                                            \
+  X(VM_IMIN, (uint32_t)min(ia, ib))                                                            \
+  X(VM_AND, ua & ub)                                                                           \
+  X(VM_OR, ua | ub)                                                                            \
+  X(VM_XOR, ua ^ ub)                                                                           \
+  X(VM_FCMP, vm_cmp_f(cdir, a, b))                                                             \
+  X(VM_ICMP, vm_cmp_i(cdir, ia, ib))
 
 enum VmCmp : uint8_t { CMP_EQ = 0, CMP_NE, CMP_LT, CMP_LE, CMP_GT, CMP_GE };
 

@@ -1,0 +1,116 @@
+"""Run-time specialisation of fused chains: the generated kernels must compile for sm_100a (checked without a
+device, NVRTC only) and must produce the same bits as the on-GPU interpreter they replace."""
+import numpy as np
+import pytest
+
+import __graft_entry__ as entry
+
+rx = entry.load_package()
+P = rx.programs
+
+
+CHAIN_MODULE = """
+module {
+  func.func @main(%x: tensor<1024x2048xf32>, %y: tensor<1024x2048xf32>, %s: tensor<2048xf32>) -> (tensor<1024x2048xf32>, tensor<2048xf32>, tensor<f32>) {
+    %c = stablehlo.constant dense<5.000000e-01> : tensor<1024x2048xf32>
+    %z = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %sb = stablehlo.broadcast_in_dim %s, dims = [1] : (tensor<2048xf32>) -> tensor<1024x2048xf32>
+    %0 = stablehlo.tanh %x : tensor<1024x2048xf32>
+    %1 = stablehlo.multiply %0, %sb : tensor<1024x2048xf32>
+    %2 = stablehlo.subtract %y, %1 : tensor<1024x2048xf32>
+    %3 = stablehlo.multiply %2, %2 : tensor<1024x2048xf32>
+    %4 = stablehlo.compare GT, %3, %c : (tensor<1024x2048xf32>, tensor<1024x2048xf32>) -> tensor<1024x2048xi1>
+    %5 = stablehlo.select %4, %3, %1 : tensor<1024x2048xi1>, tensor<1024x2048xf32>
+    %6 = stablehlo.divide %c, %5 : tensor<1024x2048xf32>
+    %7 = stablehlo.maximum %6, %2 : tensor<1024x2048xf32>
+    %col = stablehlo.reduce(%7 init: %z) applies stablehlo.add across dimensions = [0] : (tensor<1024x2048xf32>, tensor<f32>) -> tensor<2048xf32>
+    %all = stablehlo.reduce(%3 init: %z) applies stablehlo.add across dimensions = [0, 1] : (tensor<1024x2048xf32>, tensor<f32>) -> tensor<f32>
+    return %7, %col, %all : tensor<1024x2048xf32>, tensor<2048xf32>, tensor<f32>
+  }
+}
+"""
+
+
+def _programs():
+    return {
+        "sinsum_add": P.sinsum_add(1 << 12),
+        "logsumexp_raw": P.logsumexp_dims1(64, 256, raw=True),
+        "jacobi_dus": P.jacobi2d(64, 3),
+        "mlp_grad": P.mlp_grad(128, 256, 128, 128),
+        "chain": CHAIN_MODULE,
+    }
+
+
+@pytest.mark.parametrize("name", list(_programs()))
+def test_every_chain_compiles_for_sm100a(name):
+    built = rx.specialise_check(_programs()[name])
+    if name not in ("jacobi_dus", "logsumexp_raw"):  # these plan into the dedicated stencil / logsumexp kernels
+        assert built, "no chain kernels were generated"
+    for k in built:
+        assert k["cubin_bytes"] > 0, k
+
+
+def test_generated_code_is_built_from_the_interpreter_tables():
+    # comparison directions, immediates and the reversed forms all reach the generated source
+    built = rx.specialise_check(CHAIN_MODULE)
+    families = {k["kernel"] for k in built}
+    assert "k_map_rows<rx::SpecChain, 2>" in families
+    assert "k_reduce_col_vec<rx::SpecChain>" in families
+    assert "k_reduce_full_rows<rx::SpecChain>" in families
+
+
+@pytest.mark.gpu
+def test_specialised_kernels_match_the_interpreter_bit_for_bit():
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((1024, 2048), dtype=np.float32)
+    y = rng.standard_normal((1024, 2048), dtype=np.float32)
+    s = rng.standard_normal((2048,), dtype=np.float32)
+    oracle, _ = entry.load_oracle()
+    want = oracle.run_module(CHAIN_MODULE, [x, y, s])
+    outs = {}
+    try:
+        for mode, threshold in (("interpreter", -1), ("specialised", 0)):
+            rx.chain_specialiser(threshold)
+            before = rx.chain_specialiser_stats()
+            f = rx.compile(CHAIN_MODULE)
+            r = f(rx.to_rarray(x), rx.to_rarray(y), rx.to_rarray(s))
+            outs[mode] = [np.asarray(t) for t in r]
+            after = rx.chain_specialiser_stats()
+            if mode == "specialised":
+                assert not after["unavailable"], "NVRTC or the driver entry points could not be loaded on a GPU machine"
+                assert after["compiled"] + after["cache_hits"] > before["compiled"] + before["cache_hits"]
+                assert after["failed"] == 0
+            else:
+                assert after["compiled"] == before["compiled"] and after["cache_hits"] == before["cache_hits"]
+    finally:
+        rx.chain_specialiser(1 << 20)
+    for a, b in zip(outs["interpreter"], outs["specialised"]):
+        assert a.dtype == b.dtype and a.shape == b.shape
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    # and both agree with the oracle: elementwise exact up to libm differences, reductions within the stated bound
+    np.testing.assert_allclose(outs["specialised"][0], want[0], rtol=2e-6, atol=1e-6)
+    tol = oracle.reduction_tolerance(1024)
+    np.testing.assert_allclose(outs["specialised"][1], want[1], rtol=tol, atol=tol * np.abs(want[0]).sum(axis=0).max())
+    tol = oracle.reduction_tolerance(1024 * 2048)
+    np.testing.assert_allclose(outs["specialised"][2], want[2], rtol=tol)
+
+
+@pytest.mark.gpu
+def test_default_threshold_keeps_small_launches_on_the_interpreter():
+    rx.chain_specialiser(1 << 20)
+    before = rx.chain_specialiser_stats()
+    n = 1 << 12
+    x = np.linspace(0, 1, n, dtype=np.float32)
+    f = rx.compile("""
+module {
+  func.func @main(%x: tensor<4096xf32>) -> tensor<4096xf32> {
+    %0 = stablehlo.cosine %x : tensor<4096xf32>
+    %1 = stablehlo.multiply %0, %x : tensor<4096xf32>
+    return %1 : tensor<4096xf32>
+  }
+}
+""")
+    got = np.asarray(f(rx.to_rarray(x)))
+    after = rx.chain_specialiser_stats()
+    assert after["compiled"] == before["compiled"] and after["cache_hits"] == before["cache_hits"]
+    np.testing.assert_allclose(got, np.cos(x) * x, rtol=2e-6, atol=1e-7)
