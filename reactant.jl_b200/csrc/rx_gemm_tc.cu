@@ -263,10 +263,21 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
 // both CTAs' epilogue warps arrive on the leader's `acc_empty` barrier.  Each CTA's TMEM
 // holds its 128 accumulator rows x 256 columns, double buffered.
 // =======================================================================================
-constexpr int STAGES2 = 6;
-constexpr int A2_BYTES = 128 * BK * 2;      // 16 KiB: this CTA's rows of A
-constexpr int B2_BYTES = 128 * BK * 2;      // 16 KiB: this CTA's half of B
-constexpr int STAGE2_BYTES = A2_BYTES + B2_BYTES;
+// Two slab geometries with the same 192 KiB ring.  WIDE (operand extents that are multiples of 64 along their
+// contiguous dimension): 128-deep k-slabs, three stages, each operand half fetched by ONE 32 KiB copy through a
+// 3-D "grouped" tensor map.  Otherwise: 64-deep slabs, six stages, 2-D maps (one 16 KiB copy for a K-major half,
+// two 8 KiB copies for an MN-major half) with zero fill past the edges.  Measured on B200, the per-SM copy engine
+// moves 56 / 68 / 78 bytes per clock with 8 / 16 / 32 KiB copies whatever the ring depth or the number of busy SMs,
+// and the MMAs of a 256 x 256 pair tile consume 64 bytes per clock per SM -- so only the wide form keeps ahead.
+template <bool WIDE>
+struct Slab2 {
+  static constexpr int kBK = WIDE ? 128 : 64;
+  static constexpr int kStages = WIDE ? 3 : 6;
+  static constexpr int kABytes = 128 * kBK * 2;   // this CTA's rows of A
+  static constexpr int kBBytes = 128 * kBK * 2;   // this CTA's half of B
+  static constexpr int kStageBytes = kABytes + kBBytes;
+};
+constexpr int kRing2Bytes = 6 * 32768;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -307,6 +318,11 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
                : "memory");
 }
 // arrive on the barrier at this offset in the leader CTA
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* tmap, int x, int y, int z, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(smem_dst)),
+               "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar) & 0xFEFFFFFFu)
+               : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
   asm volatile(
       "{\n"
@@ -317,8 +333,11 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
       : "memory");
 }
 
+template <bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                                           const __grid_constant__ GemmParams p) {
+  using S = Slab2<WIDE>;
+  constexpr int STAGES2 = S::kStages, STAGE2_BYTES = S::kStageBytes, A2_BYTES = S::kABytes, BK = S::kBK;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full[STAGES2], empty[STAGES2], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
@@ -360,17 +379,25 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc2(const __grid_constant_
           unsigned char* sb = sa + A2_BYTES;
           if (rank == 0) mbar_expect_tx(&full[stage], 2 * STAGE2_BYTES);  // both CTAs' boxes land on the leader's barrier
           const int k0 = kb * BK;
-          if (p.a_mn) {
-            tma_load_2d_pair(sa, &tmA, m0, k0, &full[stage]);
-            tma_load_2d_pair(sa + 8192, &tmA, m0 + 64, k0, &full[stage]);
+          if (WIDE) {
+            // one 32 KiB copy per operand half: {64, 128 rows, 2 groups}
+            if (p.a_mn) tma_load_3d_pair(sa, &tmA, 0, k0, m0 >> 6, &full[stage]);
+            else tma_load_3d_pair(sa, &tmA, 0, m0, k0 >> 6, &full[stage]);
+            if (p.b_mn) tma_load_3d_pair(sb, &tmB, 0, k0, n0 >> 6, &full[stage]);
+            else tma_load_3d_pair(sb, &tmB, 0, n0, k0 >> 6, &full[stage]);
           } else {
-            tma_load_2d_pair(sa, &tmA, k0, m0, &full[stage]);
-          }
-          if (p.b_mn) {
-            tma_load_2d_pair(sb, &tmB, n0, k0, &full[stage]);
-            tma_load_2d_pair(sb + 8192, &tmB, n0 + 64, k0, &full[stage]);
-          } else {
-            tma_load_2d_pair(sb, &tmB, k0, n0, &full[stage]);
+            if (p.a_mn) {
+              tma_load_2d_pair(sa, &tmA, m0, k0, &full[stage]);
+              tma_load_2d_pair(sa + 8192, &tmA, m0 + 64, k0, &full[stage]);
+            } else {
+              tma_load_2d_pair(sa, &tmA, k0, m0, &full[stage]);
+            }
+            if (p.b_mn) {
+              tma_load_2d_pair(sb, &tmB, n0, k0, &full[stage]);
+              tma_load_2d_pair(sb + 8192, &tmB, n0 + 64, k0, &full[stage]);
+            } else {
+              tma_load_2d_pair(sb, &tmB, k0, n0, &full[stage]);
+            }
           }
           if (++stage == STAGES2) { stage = 0; phase ^= 1; }
         }
@@ -395,12 +422,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc2(const __grid_constant_
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE2_BYTES);
           const uint32_t sb = sa + A2_BYTES;
-          const uint64_t adesc0 = p.a_mn ? smem_desc(sa, 8192, 1024) : smem_desc(sa, 16, 1024);
-          const uint64_t bdesc0 = p.b_mn ? smem_desc(sb, 8192, 1024) : smem_desc(sb, 16, 1024);
-          const uint64_t astep = p.a_mn ? (2048 >> 4) : (32 >> 4);
-          const uint64_t bstep = p.b_mn ? (2048 >> 4) : (32 >> 4);
+          // MN-major: the two 64-wide groups of the 128 rows are one slab-height apart (8 KiB for 64 k-rows,
+          // 16 KiB for 128), and 16 k-rows are 2 KiB.  K-major: 16 k-columns are 32 bytes inside a 64-column
+          // group; the wide slab's second group starts 16 KiB further on.
+          constexpr uint32_t kGroupBytes = 128 * BK;
+          const uint64_t adesc0 = p.a_mn ? smem_desc(sa, kGroupBytes, 1024) : smem_desc(sa, 16, 1024);
+          const uint64_t bdesc0 = p.b_mn ? smem_desc(sb, kGroupBytes, 1024) : smem_desc(sb, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) tc_mma2(tmem_d, adesc0 + k * astep, bdesc0 + k * bstep, idesc, (kb | k) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t aoff = p.a_mn ? k * 2048 : ((k >> 2) * 16384 + (k & 3) * 32);
+            const uint32_t boff = p.b_mn ? k * 2048 : ((k >> 2) * 16384 + (k & 3) * 32);
+            tc_mma2(tmem_d, adesc0 + (aoff >> 4), bdesc0 + (boff >> 4), idesc, (kb | k) ? 1u : 0u);
+          }
           tc_commit2(&empty[stage]);
           if (++stage == STAGES2) { stage = 0; phase ^= 1; }
         }
@@ -447,6 +480,40 @@ bool make_operand_map(CUtensorMap* m, const __nv_bfloat16* base, bool mn_major, 
   return tma_make_2d(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, (uint64_t)k_extent, (uint64_t)mn_extent, (uint64_t)pitch_elems * 2, 64, (uint32_t)box_mn, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+template <bool WIDE>
+cudaError_t launch_pair_kernel(RxDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p) {
+  const size_t smem2 = (size_t)Slab2<WIDE>::kStages * Slab2<WIDE>::kStageBytes + 1024;
+  static_assert(Slab2<WIDE>::kStages * Slab2<WIDE>::kStageBytes == kRing2Bytes, "both slab geometries use the same ring");
+  static bool attr2_dev[64] = {};          // function attributes are per device
+  static int max_clusters_dev[64] = {};
+  bool& attr2 = attr2_dev[d->ordinal & 63];
+  int& max_clusters = max_clusters_dev[d->ordinal & 63];
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem2;
+  cfg.stream = d->stream;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  if (!attr2) {
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_tc2<WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    if (e != cudaSuccess) return e;
+    cfg.gridDim = dim3(d->sm_count & ~1);
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, k_gemm_tc2<WIDE>, &cfg) != cudaSuccess || max_clusters < 1) {
+      cudaGetLastError();
+      max_clusters = d->sm_count / 2;
+    }
+    attr2 = true;
+  }
+  int pairs = std::min(p.tiles_m * p.tiles_n, std::min(max_clusters, d->sm_count / 2));
+  cfg.gridDim = dim3(2 * pairs);
+  return cudaLaunchKernelEx(&cfg, k_gemm_tc2<WIDE>, tmA, tmB, p);
+}
+
 }  // namespace
 
 cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* b, void* out, bool* handled) {
@@ -485,35 +552,18 @@ cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* 
   if (two_cta) {
     p.tiles_m = (int)((g.M + 255) / 256);
     p.tiles_n = (int)((g.N + 255) / 256);
-    const size_t smem2 = (size_t)STAGES2 * STAGE2_BYTES + 1024;
-    static bool attr2_dev[64] = {};          // function attributes are per device
-    static int max_clusters_dev[64] = {};
-    bool& attr2 = attr2_dev[d->ordinal & 63];
-    int& max_clusters = max_clusters_dev[d->ordinal & 63];
-    cudaLaunchConfig_t cfg{};
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = 2;
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem2;
-    cfg.stream = d->stream;
-    cfg.attrs = at;
-    cfg.numAttrs = 1;
-    if (!attr2) {
-      cudaError_t e = cudaFuncSetAttribute(k_gemm_tc2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-      if (e != cudaSuccess) return e;
-      cfg.gridDim = dim3(d->sm_count & ~1);
-      if (cudaOccupancyMaxActiveClusters(&max_clusters, k_gemm_tc2, &cfg) != cudaSuccess || max_clusters < 1) {
-        cudaGetLastError();
-        max_clusters = d->sm_count / 2;
+    // wide slabs need whole 64-element groups along each operand's contiguous dimension
+    bool wide = !getenv("RX_GEMM_NARROW") && ((a_mn ? g.M : g.K) % 64 == 0) && ((b_mn ? g.N : g.K) % 64 == 0);
+    if (wide) {
+      CUtensorMap wa, wb;
+      wide = tma_make_grouped(&wa, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, a_mn ? g.M : g.K, a_mn ? g.K : g.M, (uint64_t)a_pitch * 2, 128, 2) &&
+             tma_make_grouped(&wb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, b_mn ? g.N : g.K, b_mn ? g.K : g.N, (uint64_t)b_pitch * 2, 128, 2);
+      if (wide) {
+        tmA = wa;
+        tmB = wb;
       }
-      attr2 = true;
     }
-    int pairs = std::min(p.tiles_m * p.tiles_n, std::min(max_clusters, d->sm_count / 2));
-    cfg.gridDim = dim3(2 * pairs);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, k_gemm_tc2, tmA, tmB, p);
+    cudaError_t e = wide ? launch_pair_kernel<true>(d, tmA, tmB, p) : launch_pair_kernel<false>(d, tmA, tmB, p);
     ++d->launches;
     *handled = true;
     return e != cudaSuccess ? e : cudaGetLastError();

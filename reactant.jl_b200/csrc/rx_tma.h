@@ -38,6 +38,23 @@ inline bool tma_make_2d(CUtensorMap* m, CUtensorMapDataType dt, const void* base
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 3-D map that fetches `groups` adjacent 64-element (128-byte) column groups of a row-major 16-bit matrix with ONE
+// copy: dim0 = the 64 elements of a group, dim1 = the rows (pitch), dim2 = the groups (128 bytes apart).  A box
+// {64, box_rows, box_groups} lands in shared memory as box_groups consecutive [box_rows][128 B] blocks -- the layout
+// the 128-byte-swizzled UMMA descriptors expect -- and a copy of 32 KiB moves more bytes per clock than two of
+// 16 KiB or four of 8 KiB (the copy engine has a fixed cost per copy).  `cols` must be a multiple of 64.
+inline bool tma_make_grouped(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows,
+                             uint32_t box_groups) {
+  EncodeTiledFn enc = tma_encode_fn();
+  if (!enc || cols % 64) return false;
+  cuuint64_t gdim[3] = {64, rows, cols / 64};
+  cuuint64_t gstride[2] = {pitch_bytes, 128};
+  cuuint32_t box[3] = {64, box_rows, box_groups};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(m, dt, 3, (void*)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 #ifdef __CUDACC__
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -73,8 +73,9 @@ def test_specialised_kernels_match_the_interpreter_bit_for_bit():
             rx.chain_specialiser(threshold)
             before = rx.chain_specialiser_stats()
             f = rx.compile(CHAIN_MODULE)
-            r = f(rx.to_rarray(x), rx.to_rarray(y), rx.to_rarray(s))
-            outs[mode] = [np.asarray(t) for t in r]
+            # host arrays follow the reversed-dimension (column-major) convention of the boundary
+            r = f(rx.to_rarray(x.T), rx.to_rarray(y.T), rx.to_rarray(s))
+            outs[mode] = [np.ascontiguousarray(np.asarray(t).T) for t in r]
             after = rx.chain_specialiser_stats()
             if mode == "specialised":
                 assert not after["unavailable"], "NVRTC or the driver entry points could not be loaded on a GPU machine"
@@ -87,10 +88,16 @@ def test_specialised_kernels_match_the_interpreter_bit_for_bit():
     for a, b in zip(outs["interpreter"], outs["specialised"]):
         assert a.dtype == b.dtype and a.shape == b.shape
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
-    # and both agree with the oracle: elementwise exact up to libm differences, reductions within the stated bound
-    np.testing.assert_allclose(outs["specialised"][0], want[0], rtol=2e-6, atol=1e-6)
+    # and both agree with the oracle.  The select is discontinuous where %3 crosses 0.5: elements within a few ulp
+    # of the threshold may legitimately take the other branch (tanh differs in the last bit between libraries).
+    t = np.tanh(x.astype(np.float64)) * s.astype(np.float64)
+    margin = np.abs((y - t) ** 2 - 0.5)
+    safe = margin > 1e-5
+    assert safe.mean() > 0.9999
+    np.testing.assert_allclose(outs["specialised"][0][safe], want[0][safe], rtol=2e-6, atol=1e-6)
+    cols_ok = safe.all(axis=0)
     tol = oracle.reduction_tolerance(1024)
-    np.testing.assert_allclose(outs["specialised"][1], want[1], rtol=tol, atol=tol * np.abs(want[0]).sum(axis=0).max())
+    np.testing.assert_allclose(outs["specialised"][1][cols_ok], want[1][cols_ok], rtol=tol, atol=tol * np.abs(want[0]).sum(axis=0).max())
     tol = oracle.reduction_tolerance(1024 * 2048)
     np.testing.assert_allclose(outs["specialised"][2], want[2], rtol=tol)
 
