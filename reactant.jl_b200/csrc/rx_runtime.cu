@@ -184,6 +184,11 @@ struct ProfScope {
   }
   ~ProfScope() {
     if (!d->profiling) return;
+    if (!kind) {  // the step was not taken after all
+      cudaEventDestroy(a);
+      cudaEventDestroy(b);
+      return;
+    }
     cudaEventRecord(b, d->stream);
     d->spans.push_back({kind, a, b});
   }
@@ -207,6 +212,64 @@ const char* kind_name(StepK k) {
 }
 
 void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<DevRun>& runs);
+
+// End of a loop iteration: carried value j now lives where the body left its next value; the storage it
+// vacated goes to the slots the body writes next time.
+void rotate_loop_state(const Step& st, DevRun& r) {
+  std::vector<int> involved = st.state_slots;
+  for (int y : st.yield_slots)
+    if (std::find(involved.begin(), involved.end(), y) == involved.end()) involved.push_back(y);
+  std::map<int, std::shared_ptr<Storage>> old;
+  for (int s : involved) old[s] = r.table[s];
+  std::vector<std::shared_ptr<Storage>> spare;
+  std::map<int, bool> taken;
+  for (size_t j = 0; j < st.state_slots.size(); ++j) {
+    r.table[st.state_slots[j]] = old[st.yield_slots[j]];
+    taken[st.yield_slots[j]] = true;
+  }
+  for (int s : involved)
+    if (!taken.count(s)) spare.push_back(old[s]);
+  size_t q = 0;
+  for (int s : involved)
+    if (std::find(st.state_slots.begin(), st.state_slots.end(), s) == st.state_slots.end()) r.table[s] = spare[q++];
+}
+
+// A counted loop whose body is only stencil updates runs as one cooperative launch (rx_stencil_tma.cu).  The
+// buffer bindings of the body repeat with the period of the storage rotation (2 for the Jacobi swap); they are
+// found by rotating a copy of the slot table until it returns to where it started.
+bool try_stencil_loop(const Step& st, DevRun& r) {
+  static const bool off = getenv("RX_STENCIL_LOOP") && atoi(getenv("RX_STENCIL_LOOP")) == 0;
+  if (off || st.trip < 2 || st.body.empty() || st.body.size() > 4) return false;
+  for (const Step& b : st.body)
+    if (b.kind != StepK::Stencil) return false;
+  RxDevice* d = r.dev;
+  CK(cudaSetDevice(d->ordinal));
+  const auto saved = r.table;
+  std::vector<const Step*> steps;
+  std::vector<VmProgram> bound;
+  int period = 0;
+  for (int p = 1; p <= 4 && !period; ++p) {
+    if (steps.size() + st.body.size() > 4) break;
+    for (const Step& b : st.body) {
+      steps.push_back(&b);
+      bound.push_back(bind(b, r));
+    }
+    rotate_loop_state(st, r);
+    if (r.table == saved) period = p;
+  }
+  r.table = saved;
+  if (!period) return false;
+  bool handled = false;
+  {
+    ProfScope ps(d, "stencil_tma_loop");
+    CK(rx::run_stencil_loop(d, steps, bound, st.trip * (int64_t)st.body.size(), &handled));
+    if (!handled) ps.kind = nullptr;
+  }
+  if (!handled) return false;
+  d->last_stencil_tma = true;
+  for (int64_t i = 0; i < st.trip % period; ++i) rotate_loop_state(st, r);
+  return true;
+}
 
 void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* fused = nullptr) {
   RxDevice* d = r.dev;
@@ -286,27 +349,12 @@ void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<Dev
       }
     }
     if (st.kind == StepK::Loop) {
+      bool whole = true;
+      for (auto& r : runs) whole = try_stencil_loop(st, r) && whole;  // all devices take the same decision: same plan, same shapes
+      if (whole) continue;
       for (int64_t it = 0; it < st.trip; ++it) {
         run_steps(ex, st.body, runs);
-        // rotate storage: carried value j now lives where the body left its next value
-        for (auto& r : runs) {
-          std::vector<int> involved = st.state_slots;
-          for (int y : st.yield_slots)
-            if (std::find(involved.begin(), involved.end(), y) == involved.end()) involved.push_back(y);
-          std::map<int, std::shared_ptr<Storage>> old;
-          for (int s : involved) old[s] = r.table[s];
-          std::vector<std::shared_ptr<Storage>> spare;
-          std::map<int, bool> taken;
-          for (size_t j = 0; j < st.state_slots.size(); ++j) {
-            r.table[st.state_slots[j]] = old[st.yield_slots[j]];
-            taken[st.yield_slots[j]] = true;
-          }
-          for (int s : involved)
-            if (!taken.count(s)) spare.push_back(old[s]);
-          size_t q = 0;
-          for (int s : involved)
-            if (std::find(st.state_slots.begin(), st.state_slots.end(), s) == st.state_slots.end()) r.table[s] = spare[q++];
-        }
+        for (auto& r : runs) rotate_loop_state(st, r);
       }
     } else if (st.kind == StepK::AllReduce) {
       rx::run_allreduce(ex->client, st, runs.size(), [&](size_t k) { return runs[k].dev; }, [&](size_t k) { return slot_ptr(runs[k], st.dst_slot); });

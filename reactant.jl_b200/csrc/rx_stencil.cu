@@ -15,6 +15,11 @@ cudaError_t run_stencil(RxDevice* d, const Step& st, const VmProgram& P) {
   return launch_map(d->ctx(), P);
 }
 
+__attribute__((weak)) cudaError_t run_stencil_loop(RxDevice*, const std::vector<const Step*>&, const std::vector<VmProgram>&, int64_t, bool* handled) {
+  *handled = false;
+  return cudaSuccess;
+}
+
 __attribute__((weak)) cudaError_t run_stencil_tma(RxDevice*, const Step&, const VmProgram&, bool* handled) {
   *handled = false;
   return cudaSuccess;

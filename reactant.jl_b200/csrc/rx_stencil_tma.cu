@@ -43,47 +43,29 @@ struct StencilParams {
   int* status;
 };
 
+// One sweep of this CTA's tiles.  `it` counts the tiles this CTA has processed since the kernel started: it
+// selects the ring stage and the mbarrier parity, so that several sweeps can share one ring.  On entry every
+// stage is drained.  Returns false if a load did not arrive within the wait limit.
 template <bool FAST5, int TH>
-__global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ StencilParams p,
-                                                     const __grid_constant__ VmProgram P) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bars[STAGES];
-  float* tile[STAGES];
-  const int stage_floats = BOX_W * p.box_h;
-  // 128-byte aligned stages
-  uintptr_t base = ((uintptr_t)smem_raw + 127) & ~(uintptr_t)127;
-#pragma unroll
-  for (int s = 0; s < STAGES; ++s) tile[s] = (float*)base + (size_t)s * stage_floats;
+__device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const StencilParams& p, const VmProgram* P, float fast_c, float* const* tile, uint64_t* bars,
+                                              int& it) {
   const uint32_t bytes = (uint32_t)(BOX_W * p.box_h * sizeof(float));
   const int ntiles = p.tiles_x * p.tiles_y;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
-    mbar_fence_init();
-  }
-  __syncthreads();
-
   auto issue = [&](int t, int s) {
     int ty = t / p.tiles_x, tx = t - ty * p.tiles_x;
     mbar_expect_tx(&bars[s], bytes);
-    tma_load_2d(tile[s], &tmap, p.x_base + tx * p.tw, p.y_base + ty * TH, &bars[s]);
+    tma_load_2d(tile[s], tmap, p.x_base + tx * p.tw, p.y_base + ty * TH, &bars[s]);
   };
-
   int first = blockIdx.x;
   if (threadIdx.x == 0)
     for (int q = 0; q < STAGES - 1; ++q)
-      if (first + q * (int)gridDim.x < ntiles) issue(first + q * (int)gridDim.x, q);
-  int it = 0;
-  bool failed = false;
+      if (first + q * (int)gridDim.x < ntiles) issue(first + q * (int)gridDim.x, (it + q) % STAGES);
   for (int t = first; t < ntiles; t += gridDim.x, ++it) {
     int s = it % STAGES;
     uint32_t parity = (it / STAGES) & 1;
     int next = t + (STAGES - 1) * (int)gridDim.x;
     if (threadIdx.x == 0 && next < ntiles) issue(next, (it + STAGES - 1) % STAGES);  // that stage was drained before the last barrier
-    if (!mbar_wait(&bars[s], parity, kWaitLimit)) {
-      failed = true;
-      break;
-    }
+    if (!mbar_wait(&bars[s], parity, kWaitLimit)) return false;
     int ty = t / p.tiles_x, tx = t - ty * p.tiles_x;
     int64_t c = (int64_t)tx * p.tw + threadIdx.x;
     int64_t r0 = (int64_t)ty * TH;
@@ -92,7 +74,7 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
       float* out = p.dst + p.dst_off + r0 * p.dst_ld + c;
       int rmax = (int)min((int64_t)TH, p.rows - r0);
       if (FAST5) {
-        const float k = P.fast_c;
+        const float k = fast_c;
         if (p.cross) {
           // taps are centre, left, right, up, down in that evaluation order: slide a three-row window
           // down the column so that each output costs three shared-memory reads instead of five
@@ -122,30 +104,129 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
         for (int r = 0; r < rmax; ++r) {
           const float* q = sm + r * BOX_W;
           __align__(16) uint32_t R[kVmMaxRegs][1];
-          for (int k = 0; k < P.n_leaves; ++k) R[P.leaf[k].reg][0] = f2u(q[p.dy[k] * BOX_W + p.dx[k]]);
-          vm_exec<1>(P, R, idx0);
-          out[(int64_t)r * p.dst_ld] = u2f(R[P.out[0].reg][0]);
+          for (int k = 0; k < P->n_leaves; ++k) R[P->leaf[k].reg][0] = f2u(q[p.dy[k] * BOX_W + p.dx[k]]);
+          vm_exec<1>(*P, R, idx0);
+          out[(int64_t)r * p.dst_ld] = u2f(R[P->out[0].reg][0]);
         }
       }
     }
     __syncthreads();  // every thread is done with stage s before it is refilled
   }
-  if (failed) {
+  return true;
+}
+
+// a load may still be in flight into this CTA's shared memory after a failed wait: give it a bounded chance to land
+__device__ __forceinline__ void stencil_drain(uint64_t* bars) {
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int s = 0; s < STAGES; ++s) mbar_wait(&bars[s], 0, kWaitLimit) || mbar_wait(&bars[s], 1, kWaitLimit);
+}
+
+template <bool FAST5, int TH>
+__global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ StencilParams p,
+                                                     const __grid_constant__ VmProgram P) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[STAGES];
+  float* tile[STAGES];
+  const int stage_floats = BOX_W * p.box_h;
+  uintptr_t base = ((uintptr_t)smem_raw + 127) & ~(uintptr_t)127;  // 128-byte aligned stages
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s) tile[s] = (float*)base + (size_t)s * stage_floats;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  int it = 0;
+  if (!stencil_sweep<FAST5, TH>(&tmap, p, &P, P.fast_c, tile, bars, it)) {
     if (threadIdx.x == 0) *p.status = 2;
-    // a load may still be in flight into this CTA's shared memory: give it a bounded chance to land
+    stencil_drain(bars);
+  }
+}
+
+// ---- whole counted loop in one launch ------------------------------------------------------------------
+// A `stablehlo.while` whose body is nothing but 5-point stencil updates (Jacobi: A -> B, B -> A, ...) runs as ONE
+// cooperative launch: every CTA keeps its tile list and its shared-memory ring, sweeps follow each other
+// separated by a grid-wide barrier instead of a kernel boundary (about 6 us per sweep on B200).  `phase` i uses
+// tensor map and destination i mod n_phases.  The barrier is a monotonic counter in device memory: arrive with a
+// release (after making this CTA's stores visible to the async proxy that serves the next sweep's TMA loads),
+// poll with acquire loads and a limit; a CTA that gives up reports through the status word and returns.  The
+// launch is cooperative, so all CTAs are resident and the barrier cannot wait for a CTA that never started.
+constexpr int kMaxPhases = 4;
+struct alignas(64) PhaseMaps { CUtensorMap m[kMaxPhases]; };
+struct LoopParams {
+  StencilParams ph[kMaxPhases];
+  float k[kMaxPhases];
+  int n_phases;
+  int total;          // sweeps to run = loop trip count x stencil steps per iteration
+  unsigned* counter;  // zero at launch
+};
+
+template <int TH>
+__global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ PhaseMaps maps, const __grid_constant__ LoopParams lp) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[STAGES];
+  float* tile[STAGES];
+  const int stage_floats = BOX_W * lp.ph[0].box_h;  // all phases share the ring geometry
+  uintptr_t base = ((uintptr_t)smem_raw + 127) & ~(uintptr_t)127;
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s) tile[s] = (float*)base + (size_t)s * stage_floats;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  int it = 0;
+  for (int sweep = 0; sweep < lp.total; ++sweep) {
+    const int ph = sweep % lp.n_phases;
+    if (!stencil_sweep<true, TH>(&maps.m[ph], lp.ph[ph], nullptr, lp.k[ph], tile, bars, it)) {
+      if (threadIdx.x == 0) *lp.ph[0].status = 2;
+      stencil_drain(bars);
+      return;
+    }
+    if (sweep + 1 == lp.total) break;
+    // grid-wide barrier between sweeps
     __syncthreads();
-    if (threadIdx.x == 0)
-      for (int s = 0; s < STAGES; ++s) mbar_wait(&bars[s], 0, kWaitLimit) || mbar_wait(&bars[s], 1, kWaitLimit);
+    int ok = 1;
+    if (threadIdx.x == 0) {
+      __threadfence();
+      asm volatile("fence.proxy.async;" ::: "memory");
+      atomicAdd(lp.counter, 1u);
+      const unsigned target = (unsigned)(sweep + 1) * gridDim.x;
+      long long spins = 0;
+      for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(lp.counter) : "memory");
+        if (v >= target) break;
+        if (++spins > kWaitLimit) { ok = 0; break; }
+      }
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
+    ok = __syncthreads_and(ok);
+    if (!ok) {
+      if (threadIdx.x == 0) *lp.ph[0].status = 3;
+      return;  // nothing of this CTA is in flight: the sweep above drained its ring
+    }
   }
 }
 
 }  // namespace
 
-cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, bool* handled) {
-  *handled = false;
+namespace {
+
+struct Prepared {
+  CUtensorMap tmap;
+  StencilParams sp;
+  size_t smem = 0;
+  bool fast = false;
+  bool empty = false;
+};
+
+// Tile geometry, tensor map and parameters of one stencil step; false = this path declines the step.
+bool prepare_stencil(RxDevice* d, const Step& st, const VmProgram& P, Prepared* out) {
   EncodeTiledFn enc = tma_encode_fn();
-  if (!enc) return cudaSuccess;
-  if ((int)st.st_dy.size() > kMaxTaps || st.st_dy.size() != (size_t)P.n_leaves) return cudaSuccess;
+  if (!enc) return false;
+  if ((int)st.st_dy.size() > kMaxTaps || st.st_dy.size() != (size_t)P.n_leaves) return false;
   int max_dy = 0, max_dx = 0;
   for (size_t k = 0; k < st.st_dy.size(); ++k) {
     max_dy = std::max(max_dy, st.st_dy[k]);
@@ -163,10 +244,13 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
   int64_t col0 = st.st_src_off % ld, row0 = st.st_src_off / ld;
   int x_shift = (int)(col0 % 4);
   int halo_w = (max_dx + x_shift + 3) & ~3;  // box start and tile width stay multiples of 4 floats (16 B)
-  if (halo_w > 16 || max_dy > HALO_H) return cudaSuccess;
+  if (halo_w > 16 || max_dy > HALO_H) return false;
   int tw = BOX_W - halo_w;
-  if (((uintptr_t)src % 16) || (ld % 4) || ld > (int64_t)INT32_MAX || rows_total > (int64_t)INT32_MAX) return cudaSuccess;
-  if (st.st_rows <= 0 || st.st_cols <= 0) { *handled = true; return cudaSuccess; }
+  if (((uintptr_t)src % 16) || (ld % 4) || ld > (int64_t)INT32_MAX || rows_total > (int64_t)INT32_MAX) return false;
+  if (st.st_rows <= 0 || st.st_cols <= 0) {
+    out->empty = true;
+    return true;
+  }
 
   const int TH = 32;  // 16 x 3 CTAs/SM and 64 x 1 CTA/SM measured within 2% of 32 x 2
   int box_h = TH + max_dy;
@@ -184,7 +268,7 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)src, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return cudaSuccess;  // decline: the generic kernel handles it
+    if (r != CUDA_SUCCESS) return false;  // decline: the generic kernel handles it
     std::vector<uint8_t> v(sizeof(CUtensorMap) + sizeof(Key));
     memcpy(v.data(), &m, sizeof(CUtensorMap));
     memcpy(v.data() + sizeof(CUtensorMap), &key, sizeof(Key));
@@ -192,10 +276,10 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
     d->tmaps[src] = std::move(v);
     blob = &d->tmaps[src];
   }
-  CUtensorMap tmap;
-  memcpy(&tmap, blob->data(), sizeof(CUtensorMap));
+  memcpy(&out->tmap, blob->data(), sizeof(CUtensorMap));
 
-  StencilParams sp{};
+  StencilParams& sp = out->sp;
+  sp = StencilParams{};
   sp.dst = (float*)P.out[0].ptr;
   sp.rows = st.st_rows;
   sp.cols = st.st_cols;
@@ -218,9 +302,24 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
   int* dstatus = nullptr;
   cudaHostGetDevicePointer(&dstatus, d->status, 0);
   sp.status = dstatus + 1;
+  out->smem = (size_t)STAGES * BOX_W * box_h * sizeof(float) + 128;  // 2 x 34 KiB for a radius-1 stencil; two CTAs per SM measured fastest
+  out->fast = P.fast_id == FAST_STENCIL5_MUL && sp.n_taps == 5;
+  return true;
+}
 
-  size_t smem = (size_t)STAGES * BOX_W * box_h * sizeof(float) + 128;  // 2 x 34 KiB for a radius-1 stencil; two CTAs per SM measured fastest
-  bool fast = P.fast_id == FAST_STENCIL5_MUL && sp.n_taps == 5;
+}  // namespace
+
+cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, bool* handled) {
+  *handled = false;
+  Prepared pr;
+  if (!prepare_stencil(d, st, P, &pr)) return cudaSuccess;
+  if (pr.empty) {
+    *handled = true;
+    return cudaSuccess;
+  }
+  const StencilParams& sp = pr.sp;
+  const size_t smem = pr.smem;
+  const bool fast = pr.fast;
   auto kern = fast ? k_stencil_tma<true, 32> : k_stencil_tma<false, 32>;
   static size_t attr_set[64][2] = {};  // function attributes are per device
   size_t& have = attr_set[d->ordinal & 63][fast];
@@ -229,14 +328,68 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
     if (e != cudaSuccess) return e;
     have = smem;
   }
-  const int per_sm_env = 2;
   int ntiles = sp.tiles_x * sp.tiles_y;
-  int per_sm = (int)std::max<size_t>(1, std::min<size_t>((size_t)per_sm_env, (size_t)(220 * 1024) / smem));
+  int per_sm = (int)std::max<size_t>(1, std::min<size_t>((size_t)2, (size_t)(220 * 1024) / smem));
   int grid = std::min(ntiles, d->sm_count * per_sm);
-  kern<<<grid, 256, smem, d->stream>>>(tmap, sp, P);
+  kern<<<grid, 256, smem, d->stream>>>(pr.tmap, sp, P);
   ++d->launches;
   *handled = true;
   return cudaGetLastError();
+}
+
+// `total` sweeps cycling through the given stencil steps (already bound to their buffers) in one cooperative
+// launch.  Declines (handled = false) unless every step is the 5-point fast chain on the same tile geometry.
+cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps, const std::vector<VmProgram>& bound, int64_t total, bool* handled) {
+  *handled = false;
+  const int n = (int)steps.size();
+  if (n < 1 || n > kMaxPhases || total < 2 || total > INT32_MAX) return cudaSuccess;
+  PhaseMaps maps{};
+  LoopParams lp{};
+  size_t smem = 0;
+  for (int i = 0; i < n; ++i) {
+    Prepared pr;
+    if (!prepare_stencil(d, *steps[i], bound[i], &pr) || pr.empty || !pr.fast) return cudaSuccess;
+    if (i && (pr.smem != smem || pr.sp.box_h != lp.ph[0].box_h)) return cudaSuccess;
+    smem = pr.smem;
+    maps.m[i] = pr.tmap;
+    lp.ph[i] = pr.sp;
+    lp.k[i] = bound[i].fast_c;
+  }
+  lp.n_phases = n;
+  lp.total = (int)total;
+  lp.counter = (unsigned*)(d->scratch + d->scratch_words - 2);  // the word before the reductions' ticket
+  auto kern = k_stencil_loop<32>;
+  static size_t attr_set[64] = {};
+  static int resident[64] = {};
+  size_t& have = attr_set[d->ordinal & 63];
+  int& occ = resident[d->ordinal & 63];
+  if (have < smem) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    have = smem;
+    occ = 0;
+  }
+  if (!occ) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, 256, smem) != cudaSuccess || occ < 1) {
+      cudaGetLastError();
+      occ = 0;
+      return cudaSuccess;
+    }
+  }
+  int ntiles = 0;
+  for (int i = 0; i < n; ++i) ntiles = std::max(ntiles, lp.ph[i].tiles_x * lp.ph[i].tiles_y);
+  int grid = std::min(ntiles, d->sm_count * std::min(occ, 2));
+  cudaError_t e = cudaMemsetAsync(lp.counter, 0, sizeof(unsigned), d->stream);
+  if (e != cudaSuccess) return e;
+  void* args[] = {(void*)&maps, (void*)&lp};
+  e = cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(256), args, smem, d->stream);
+  if (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorNotSupported) {
+    cudaGetLastError();
+    return cudaSuccess;  // the caller launches sweep by sweep
+  }
+  ++d->launches;
+  *handled = true;
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace rx

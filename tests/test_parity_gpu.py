@@ -180,6 +180,26 @@ def test_jacobi2d_bit_exact(rx, ref, client, n, steps, form):
     assert np.array_equal(ga, wa) and np.array_equal(gb, wb)
 
 
+@pytest.mark.parametrize("steps", [2, 3, 7])
+def test_counted_stencil_loop_is_one_launch_and_bit_exact(rx, ref, client, steps):
+    """A loop whose body is only 5-point updates runs as one cooperative launch with grid barriers between the
+    sweeps; an odd trip count leaves the arrays swapped exactly as sweep-by-sweep execution does."""
+    n = 1030
+    rng = np.random.default_rng(steps)
+    a = rng.random((n, n), dtype=np.float32)
+    b = rng.random((n, n), dtype=np.float32)
+    text = rx.programs.jacobi2d(n, steps)
+    dev = client.addressable_devices[0]
+    f = rx.compile(text, client)
+    A, B = rx.to_rarray(a.T, client), rx.to_rarray(b.T, client)
+    before = dev.kernel_launches
+    out = f(A, B)
+    assert dev.kernel_launches - before == 1
+    ga, gb = [np.asarray(o).T for o in out]
+    wa, wb = ref.run_module(text, [a, b])
+    assert np.array_equal(ga, wa) and np.array_equal(gb, wb)
+
+
 def test_jacobi2d_full_size_against_c_oracle(rx, cpu, client):
     n, steps = 8192, 4
     rng = np.random.default_rng(4)
