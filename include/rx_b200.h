@@ -148,6 +148,11 @@ const char* RxExecutableDescribe(RxExecutable* exec);
  * or NULL with the error set.  Used to validate modules on machines without a
  * device. */
 const char* RxPlanDescribe(const char* mlir_text, size_t text_len);
+/* ClientCompileText keeps the plan of every module it has seen (keyed by the
+ * module text) and hands it out again when the same module is compiled once
+ * more -- what src/PersistentCompileCache.jl does for XLA executables, in
+ * memory.  This returns how many compilations were served from that cache. */
+int64_t RxPlanCacheHits(void);
 
 /* ---- run-time specialisation of fused chains ---------------------------------
  * Fusion groups whose launch covers at least `min_elems` elements (default 2^20)

@@ -83,6 +83,7 @@ PROTOTYPES = {
     "RxExecutableParameterAlias": (C.c_int, [P, C.c_int]),
     "RxExecutableDescribe": (P, [P]),
     "RxPlanDescribe": (P, [C.c_char_p, C.c_size_t]),
+    "RxPlanCacheHits": (C.c_int64, []),
     "RxChainSpecialiser": (None, [C.c_int64]),
     "RxChainSpecialiserStats": (None, [C.POINTER(C.c_int64)]),
     "RxPlanSpecialiseCheck": (P, [C.c_char_p, C.c_size_t]),

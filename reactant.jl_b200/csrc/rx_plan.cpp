@@ -1162,8 +1162,51 @@ struct Planner {
       }
     }
     Type rt = local_type(v);
+    std::vector<int64_t> dims = op.dims;
+    std::sort(dims.begin(), dims.end());
+    env[v] = reduce_any(op, X, dims, rt, init->f, init->i, needs_allreduce);
+  }
+
+  // One step when the reduced dims form a single run of the (normalised) iteration space and the kept dims on
+  // either side merge.  Otherwise (a) several reduced dims: reduce the innermost one on its own, with the
+  // operation's identity as init, and go on with the rest -- valid for every supported combiner (associative and
+  // commutative), each stage a streaming pass; (b) one reduced dim whose neighbours do not merge (a broadcast
+  // operand along one of them): evaluate the chain into a dense temporary first, then reduce that.
+  ExprP reduce_any(const Op& op, ExprP X, std::vector<int64_t> dims, const Type& rt, double init_f, int64_t init_i, bool needs_allreduce) {
+    const size_t n_slots = plan.slots.size(), n_steps = cur->size();
+    try {
+      return reduce_core(op, X, dims, rt, init_f, init_i, needs_allreduce);
+    } catch (const Error& e) {
+      if (e.code != RX_ERR_PLAN) throw;
+      plan.slots.resize(n_slots);
+      cur->resize(n_steps);
+      if (dims.size() < 2 && whole_slot(X)) throw;
+    }
+    if (dims.size() < 2) {
+      Type xt{X->dt, X->shape};
+      return reduce_core(op, leaf(materialise(X, "reduce operand (kept dims do not merge)"), xt), dims, rt, init_f, init_i, needs_allreduce);
+    }
+    const int64_t d = dims.back();
+    dims.pop_back();
+    Type mid{X->dt, X->shape};
+    mid.shape.erase(mid.shape.begin() + d);
+    double idf = 0;
+    int64_t idi = 0;
+    switch (op.red) {
+      case RedK::Add: case RedK::Or: break;
+      case RedK::Max: idf = -INFINITY; idi = INT32_MIN; break;
+      case RedK::Min: idf = INFINITY; idi = INT32_MAX; break;
+      case RedK::Mul: case RedK::And: idf = 1; idi = 1; break;
+    }
+    ExprP M = reduce_any(op, X, {d}, mid, idf, idi, false);
+    return reduce_any(op, M, dims, rt, init_f, init_i, needs_allreduce);
+  }
+
+  // chain X -> reduce over `dims` -> a fresh slot of type rt; returns the result as a leaf
+  ExprP reduce_core(const Op& op, ExprP X, const std::vector<int64_t>& dims, const Type& rt, double init_f, int64_t init_i, bool needs_allreduce) {
+    const DT dt = X->dt;
     std::vector<int> cls(X->shape.size(), 0);
-    for (auto d : op.dims) cls[d] = 1;
+    for (auto d : dims) cls[d] = 1;
     // output strides over root dims: kept dims in order
     std::vector<int64_t> ostr(X->shape.size(), 0);
     {
@@ -1176,8 +1219,8 @@ struct Planner {
     st.red = op.red;
     st.red_dt = (dt == DT::S32) ? DT::S32 : (dt == DT::PRED ? DT::PRED : DT::F32);
     if (dt == DT::PRED && op.red == RedK::Add) st.red = RedK::Or;  // i1 addition saturates
-    st.init_f = init->f;
-    st.init_i = init->i;
+    st.init_f = init_f;
+    st.init_i = init_i;
     Lowering L(X->shape);
     int root = L.lower(X, Lowering::identity(X->shape.size()));
     OutSpec os{slot, rt.dt, 0, ostr, root};
@@ -1196,10 +1239,9 @@ struct Planner {
       int vop = st.red_dt == DT::F32 ? (op.red == RedK::Add ? VM_ADD : op.red == RedK::Max ? VM_MAX : op.red == RedK::Min ? VM_MIN : VM_MUL)
                                      : (st.red == RedK::Add ? VM_IADD : st.red == RedK::Max ? VM_IMAX : st.red == RedK::Min ? VM_IMIN : st.red == RedK::Mul ? VM_IMUL : st.red == RedK::Or ? VM_OR : VM_AND);
       Type xt{X->dt, X->shape};
-      ExprP e = round_if_bf16(mkop(vop, xt, {X, konst(xt, init->f, init->i)}));
+      ExprP e = round_if_bf16(mkop(vop, xt, {X, konst(xt, init_f, init_i)}));
       emit_map(e, slot, 0, ostr, "reduce over unit dimensions");
-      env[v] = leaf(slot, rt);
-      return;
+      return leaf(slot, rt);
     } else if (kept_n == 1) {
       st.kind = StepK::ReduceFull;
       if (P.rank != 1 && !(P.rank == 0)) {
@@ -1215,8 +1257,7 @@ struct Planner {
 
     // logsumexp: this is sum(exp(x - max(x))) with the max produced by an earlier row reduce of the same x
     if (op.red == RedK::Add && st.kind == StepK::ReduceRow && st.prog.fast_id == FAST_EXP_SUB && try_logsumexp(st, slot)) {
-      env[v] = leaf(slot, rt);
-      return;
+      return leaf(slot, rt);
     }
     cur->push_back(std::move(st));
     if (needs_allreduce) {
@@ -1229,7 +1270,7 @@ struct Planner {
       if (rt.dt != DT::F32) throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type for all_reduce");
       cur->push_back(std::move(ar));
     }
-    env[v] = leaf(slot, rt);
+    return leaf(slot, rt);
   }
 
   // Rewrite prog dims/strides into exactly three dims [outer][red][inner].

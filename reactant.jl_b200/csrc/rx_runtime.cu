@@ -768,15 +768,39 @@ void FutureAwait(RxFuture* f) {
   API_END_VOID
 }
 
+static std::atomic<int64_t> g_plan_cache_hits{0};
+int64_t RxPlanCacheHits() { return g_plan_cache_hits.load(); }
+
 RxExecutable* ClientCompileText(RxClient* client, const char* text, size_t len, const char* opts, size_t nopts) {
   (void)opts; (void)nopts;
   API_BEGIN
   if (!client) throw Error(RX_ERR_BAD_HANDLE, "null client");
   std::string s(text, len);
-  auto mod = parse_module(s);
   auto ex = std::make_unique<RxExecutable>();
   ex->client = client;
-  ex->plan = build_plan(*mod);
+  // Plan cache keyed by the module text (the in-memory analogue of Reactant's persistent compile cache,
+  // src/PersistentCompileCache.jl): compiling the same module again, on any client, reuses the plan.  A plan
+  // holds no device state (buffers are bound at launch), so sharing it is safe.
+  static std::mutex cache_mu;
+  static std::map<std::string, std::shared_ptr<const Plan>> cache;
+  static int64_t hits = 0;
+  {
+    std::lock_guard<std::mutex> g(cache_mu);
+    auto it = cache.find(s);
+    if (it != cache.end()) {
+      ex->plan = it->second;
+      ++hits;
+      g_plan_cache_hits.store(hits);
+    }
+  }
+  if (!ex->plan) {
+    auto mod = parse_module(s);
+    std::shared_ptr<const Plan> plan(build_plan(*mod).release());
+    std::lock_guard<std::mutex> g(cache_mu);
+    if (cache.size() >= 256) cache.clear();
+    cache[s] = plan;
+    ex->plan = plan;
+  }
   if (const char* dir = getenv("RX_DUMP_PLAN")) {
     static int counter = 0;
     std::string path = std::string(dir) + "/plan_" + std::to_string(counter++) + ".json";

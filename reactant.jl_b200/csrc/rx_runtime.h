@@ -116,7 +116,7 @@ struct RxEvent {
 
 struct RxExecutable {
   RxClient* client = nullptr;
-  std::unique_ptr<rx::Plan> plan;
+  std::shared_ptr<const rx::Plan> plan;  // shared with the process-wide plan cache
   std::mutex mu;
   std::map<int, std::map<int, std::shared_ptr<Storage>>> consts;  // [local device][slot]
 };

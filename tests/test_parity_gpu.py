@@ -336,3 +336,15 @@ def test_buffer_round_trip_and_allocator_stats(rx, client):
     s = dev.allocator_stats()
     assert s["bytes_in_use"] >= 0 and s["peak_bytes_in_use"] > 0 and s["bytes_limit"] > 0
     assert client.platform_name == "cuda"
+
+
+def test_compiling_a_module_again_reuses_its_plan(rx, client):
+    from reactant_jl_b200 import _lib
+    text = rx.programs.sinsum_add(12345)
+    before = _lib.lib().RxPlanCacheHits()
+    f = rx.compile(text, client)
+    g = rx.compile(text, client)
+    assert _lib.lib().RxPlanCacheHits() >= before + 1
+    x = np.linspace(-1, 1, 12345, dtype=np.float32)
+    a, b = float(f(rx.to_rarray(x, client), rx.to_rarray(x, client))), float(g(rx.to_rarray(x, client), rx.to_rarray(x, client)))
+    assert a == b
