@@ -350,6 +350,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc2(const __grid_constant_
   const int kblocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");  // the first copies wait for the descriptors otherwise
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
     for (int s = 0; s < STAGES2; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * kEpiWarps); }
     abort_flag = 0;
