@@ -156,21 +156,34 @@ def setup_jacobi(rx, client, n=8192, steps=100):
                 unit="GB/s", kind="stencil_tma", dtype="f32", bound="hbm", kernel="k_stencil", launches_per_step=steps, donates=True)
 
 
-def setup_mlp(rx, client, F=1024, H=4096, O=1024, B=4096):
+def setup_mlp(rx, client, rank=0, world=1, F=1024, H=4096, O=1024, B=4096):
+    """MLP forward + gradients.  With N > 1 ranks the batch is sharded (weak scaling: B rows per GPU, global batch
+    B * N), the weights are replicated, and every gradient is all-reduced (NCCL over NVLink) -- data-parallel training."""
     import ml_dtypes
     rng = np.random.default_rng(6)
     bf = lambda a: a.astype(np.float32).astype(ml_dtypes.bfloat16)
-    X = bf(rng.standard_normal((B, F)))
     W1 = bf(rng.standard_normal((F, H)) / np.sqrt(F))
     W2 = bf(rng.standard_normal((H, O)) / np.sqrt(H))
     b1 = (0.01 * rng.standard_normal(H)).astype(np.float32)
     b2 = (0.01 * rng.standard_normal(O)).astype(np.float32)
+    rng = np.random.default_rng(600 + rank)  # this rank's rows of the global batch
+    X = bf(rng.standard_normal((B, F)))
     Y = rng.standard_normal((B, O)).astype(np.float32)
     ins = [W1, b1, W2, b2, X, Y]
-    thunk = rx.compile(rx.programs.mlp_grad(F, H, O, B), client)
-    flops = 2 * B * H * F * 2 + 2 * B * O * H * 3
+    thunk = rx.compile(rx.programs.mlp_grad(F, H, O, B * world, num_partitions=world), client)
+    flops = (2 * B * H * F * 2 + 2 * B * O * H * 3) * world
     nbytes = sum(a.nbytes for a in ins)
-    return dict(thunk=thunk, upload=lambda: tuple(rx.to_rarray(a.T, client) for a in ins), host=ins, read=lambda r: float(r[4]),
+    if world > 1:
+        mesh = rx.Mesh(client.devices, ("x",))
+        rep2, rep1, batch = rx.NamedSharding(mesh, (None, None)), rx.NamedSharding(mesh, (None,)), rx.NamedSharding(mesh, (None, "x"))
+        spec = [(rep2, (H, F)), (rep1, (H,)), (rep2, (O, H)), (rep1, (O,)), (batch, (F, B * world)), (batch, (O, B * world))]
+
+        def upload():
+            return tuple(rx.from_local_shards([a.T], shape, sh, client) for a, (sh, shape) in zip(ins, spec))
+    else:
+        def upload():
+            return tuple(rx.to_rarray(a.T, client) for a in ins)
+    return dict(thunk=thunk, upload=upload, host=ins, read=lambda r: float(r[4]),
                 flops_per_step=flops, h2d=nbytes, d2h=W1.nbytes + W2.nbytes + b1.nbytes + b2.nbytes + 4, unit="TFLOP/s", kind="gemm_tc", dtype="bf16",
                 bound="tensor", kernel="k_gemm", launches_per_step=5)
 
@@ -180,7 +193,7 @@ WORKLOADS = {
     "c1_sinsum_2p24": lambda rx, c, r, w: setup_sinsum(rx, c, 1 << 24, r, w, seeds=(1, 2)),
     "c2_logsumexp_32768x8192": lambda rx, c, r, w: setup_logsumexp(rx, c),
     "c3_jacobi2d_8192_100": lambda rx, c, r, w: setup_jacobi(rx, c),
-    "c4_mlp_grad_bf16": lambda rx, c, r, w: setup_mlp(rx, c),
+    "c4_mlp_grad_bf16": lambda rx, c, r, w: setup_mlp(rx, c, r, w),
 }
 # reduced sizes of the same programs for profiler captures (a few hundred MB on the device, still larger than L2)
 WORKLOADS.update({
@@ -341,9 +354,10 @@ def main():
     client = rx.Client(node_id=dist.rank, num_nodes=world, allowed_devices=[dist.local_rank])
     allreduce = "none"
     if world > 1:
-        if args.workload not in ("c5_sharded_sinsum_2p30", "c1_sinsum_2p24"):
-            raise SystemExit("only the sinsum workloads shard; the others run as single-GPU configurations")
-        allreduce = rx.dist.connect_collectives(rx, client, dist, os.environ.get("RX_ALLREDUCE", "mailbox"))
+        if args.workload not in ("c5_sharded_sinsum_2p30", "c1_sinsum_2p24", "c4_mlp_grad_bf16"):
+            raise SystemExit("the sinsum workloads and the data-parallel MLP step shard; the others run as single-GPU configurations")
+        default_mode = "mailbox+nccl" if args.workload == "c4_mlp_grad_bf16" else "mailbox"
+        allreduce = rx.dist.connect_collectives(rx, client, dist, os.environ.get("RX_ALLREDUCE", default_mode))
     wl = WORKLOADS[args.workload](rx, client, dist.rank, world)
     rotate = 4 if args.workload in SMALL_INPUT else 1
     peaks = measured_peaks()
@@ -371,7 +385,7 @@ def main():
         per_launch_ms = dist.reduce(per_launch_ms, "max")
         per_launch_work = work / launches_per_step
         achieved = to_metric(wl, per_launch_work, per_launch_ms)
-        peak = peaks["hbm_gbs"] * world if wl["bound"] == "hbm" else peaks["bf16_tflops"]
+        peak = (peaks["hbm_gbs"] if wl["bound"] == "hbm" else peaks["bf16_tflops"]) * world
         traffic = None
         if kind in TRAFFIC_RATIO:
             traffic = TRAFFIC_RATIO[kind] * per_launch_work / world  # bytes per launch on one GPU
@@ -390,7 +404,7 @@ def main():
         cpu = cpu_baseline(args.workload)
     if dist.rank == 0:
         line = {"metric": "fused map-reduce HBM GB/s" if wl["unit"] == "GB/s" else "dot_general TFLOP/s", "value": value, "unit": wl["unit"], "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if world > 1 or "c5" in args.workload else "weak",
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if "sinsum" in args.workload and (world > 1 or "c5" in args.workload) else "weak",
                 "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
                 "config": {"workload": args.workload, "l2": f"{rotate} rotating resident input sets, together larger than L2" if rotate > 1 else "inputs larger than L2", "all_reduce": allreduce,
                            "result": result if isinstance(result, float) else None},

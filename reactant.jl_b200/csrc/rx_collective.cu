@@ -267,7 +267,8 @@ bool prepare_fused_allreduce(RxClient* c, const Step& st, const std::vector<RxDe
   return true;
 }
 
-void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::function<RxDevice*(size_t)>& dev, const std::function<void*(size_t)>& ptr) {
+void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::function<RxDevice*(size_t)>& dev, const std::function<void*(size_t)>& ptr,
+                   bool on_comm_stream) {
   int world = c->n_global();
   if (world <= 1) return;
   if (n_local != c->devices.size()) throw Error(RX_ERR_ARG, "all_reduce must run on every addressable device of the client");
@@ -303,10 +304,8 @@ void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::funct
     RxDevice* d = dev(k);
     cck(cudaSetDevice(d->ordinal), "cudaSetDevice");
     const ncclDataType_t ty = st.red_dt == DT::BF16 ? ncclBfloat16 : ncclFloat32;
-    cudaEvent_t ea = nullptr, eb = nullptr;
-    if (d->profiling) { cudaEventCreate(&ea); cudaEventCreate(&eb); cudaEventRecord(ea, d->stream); }
-    nck(nccl().AllReduce(ptr(k), ptr(k), (size_t)st.count, ty, ncclSum, (ncclComm_t)c->nccl_comms[d->local_id], d->stream), "ncclAllReduce");
-    if (d->profiling) { cudaEventRecord(eb, d->stream); d->spans.push_back({"all_reduce_nccl", ea, eb}); }
+    cudaStream_t s = (on_comm_stream && d->comm_stream) ? d->comm_stream : d->stream;
+    nck(nccl().AllReduce(ptr(k), ptr(k), (size_t)st.count, ty, ncclSum, (ncclComm_t)c->nccl_comms[d->local_id], s), "ncclAllReduce");
     ++d->launches;
   }
   nck(nccl().GroupEnd(), "ncclGroupEnd");

@@ -19,8 +19,10 @@ void destroy_collectives(RxClient* c);
 
 // Sum `st.count` f32 values at ptr(k) on dev(k) for every local device k with the
 // matching values of all other ranks of the mesh; every rank ends with the same bits.
+// on_comm_stream: enqueue on each device's communication stream instead of its compute stream (the caller
+// orders the two with events); only the NCCL path honours it.
 void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::function<RxDevice*(size_t)>& dev,
-                   const std::function<void*(size_t)>& ptr);
+                   const std::function<void*(size_t)>& ptr, bool on_comm_stream = false);
 
 // If a single-word all-reduce can go through the mailboxes, advance the epoch and fill
 // one FusedAllReduce per local device (to be handed to the producing reduce kernel).

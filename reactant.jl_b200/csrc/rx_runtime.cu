@@ -147,7 +147,34 @@ namespace {
 struct DevRun {
   RxDevice* dev;
   std::vector<std::shared_ptr<Storage>> table;  // per slot
+  // slots with an all-reduce still running on the device's communication stream, and the event that ends it
+  std::map<int, cudaEvent_t> pending;
 };
+
+// Before a step touches a slot whose all-reduce is still in flight on the communication stream, the compute
+// stream waits for it (and only then): gradient all-reduces overlap the GEMMs that follow them.
+void join_pending(DevRun& r, int slot) {
+  auto it = r.pending.find(slot);
+  if (it == r.pending.end()) return;
+  cudaStreamWaitEvent(r.dev->stream, it->second, 0);
+  cudaEventDestroy(it->second);  // destruction is deferred until the wait has been satisfied
+  r.pending.erase(it);
+}
+void join_pending_of(DevRun& r, const Step& st) {
+  if (r.pending.empty()) return;
+  for (int s : st.leaf_slot) join_pending(r, s);
+  for (int s : st.out_slot) join_pending(r, s);
+  for (int s : {st.gemm.a_slot, st.gemm.b_slot, st.gemm.d_slot, st.src_slot, st.dst_slot})
+    if (s >= 0) join_pending(r, s);
+  for (int s : st.state_slots) join_pending(r, s);
+  for (int s : st.yield_slots) join_pending(r, s);
+  if (st.kind == StepK::Loop) {  // a loop body may touch anything: simplest to drain
+    while (!r.pending.empty()) join_pending(r, r.pending.begin()->first);
+  }
+}
+void join_all_pending(DevRun& r) {
+  while (!r.pending.empty()) join_pending(r, r.pending.begin()->first);
+}
 
 void* slot_ptr(DevRun& r, int slot) {
   if (slot < 0 || !r.table[slot]) throw Error(RX_ERR_PLAN, "internal: slot " + std::to_string(slot) + " has no storage");
@@ -336,6 +363,7 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
 void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<DevRun>& runs) {
   for (size_t si = 0; si < steps.size(); ++si) {
     const Step& st = steps[si];
+    for (auto& r : runs) join_pending_of(r, st);
     // a full reduce of f32 followed by the all-reduce of its scalar: one kernel does both
     if (st.kind == StepK::ReduceFull && si + 1 < steps.size() && steps[si + 1].kind == StepK::AllReduce && st.out_slot.size() == 1 &&
         steps[si + 1].dst_slot == st.out_slot[0] && st.red == RedK::Add && st.red_dt == DT::F32 && st.prog.out[0].elem == EL_F32) {
@@ -357,7 +385,32 @@ void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<Dev
         for (auto& r : runs) rotate_loop_state(st, r);
       }
     } else if (st.kind == StepK::AllReduce) {
-      rx::run_allreduce(ex->client, st, runs.size(), [&](size_t k) { return runs[k].dev; }, [&](size_t k) { return slot_ptr(runs[k], st.dst_slot); });
+      // vectors (gradients) go to the communication stream so that the steps after them keep the SMs busy;
+      // single words stay on the compute stream (mailbox kernel, a few microseconds)
+      static const bool overlap_off = getenv("RX_ALLREDUCE_OVERLAP") && atoi(getenv("RX_ALLREDUCE_OVERLAP")) == 0;
+      const bool side = st.count > 1 && !overlap_off && ex->client->n_global() > 1;
+      if (side) {
+        for (auto& r : runs) {
+          RxDevice* d = r.dev;
+          CK(cudaSetDevice(d->ordinal));
+          if (!d->comm_stream) CK(cudaStreamCreateWithFlags(&d->comm_stream, cudaStreamNonBlocking));
+          cudaEvent_t ready;
+          CK(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
+          CK(cudaEventRecord(ready, d->stream));
+          CK(cudaStreamWaitEvent(d->comm_stream, ready, 0));
+          cudaEventDestroy(ready);
+        }
+      }
+      rx::run_allreduce(ex->client, st, runs.size(), [&](size_t k) { return runs[k].dev; }, [&](size_t k) { return slot_ptr(runs[k], st.dst_slot); }, side);
+      if (side) {
+        for (auto& r : runs) {
+          CK(cudaSetDevice(r.dev->ordinal));
+          cudaEvent_t done;
+          CK(cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
+          CK(cudaEventRecord(done, r.dev->comm_stream));
+          r.pending[st.dst_slot] = done;
+        }
+      }
     } else {
       for (auto& r : runs) run_one(ex, st, r);
     }
@@ -425,6 +478,10 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
     }
   }
   run_steps(ex, p.steps, runs);
+  for (auto& r : runs) {
+    CK(cudaSetDevice(r.dev->ordinal));
+    join_all_pending(r);  // results are complete on the compute stream
+  }
   for (size_t k = 0; k < devs.size(); ++k) {
     RxDevice* d = devs[k];
     CK(cudaSetDevice(d->ordinal));
@@ -567,6 +624,8 @@ void FreeClient(RxClient* client) {
     d->spans.clear();
     d->closed.store(true);
     cudaStreamDestroy(d->stream);
+    if (d->comm_stream) cudaStreamDestroy(d->comm_stream);  // joined into `stream` at the end of every execution
+    d->comm_stream = nullptr;
     d->stream = nullptr;
     d->scratch = nullptr;
     d->flush_buf = nullptr;

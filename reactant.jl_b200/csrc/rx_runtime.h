@@ -33,6 +33,7 @@ struct RxDevice : std::enable_shared_from_this<RxDevice> {
   int global_id = 0;  // index in the mesh
   bool addressable = true;
   cudaStream_t stream = nullptr;
+  cudaStream_t comm_stream = nullptr;  // vector all-reduces run here, ordered against `stream` by events
   int sm_count = 148;
   size_t total_mem = 0;
   // memory pool (exact-size free lists, stream ordered on `stream`)

@@ -78,10 +78,12 @@ def connect_collectives(rx, client, dist: Dist, mode: str = "mailbox") -> str:
     the NVLink mailbox table (default) or the NCCL unique id."""
     if dist.world == 1:
         return "none"
-    if mode == "nccl":
+    if mode in ("nccl", "mailbox+nccl"):
         uid = rx.collectives_unique_id() if dist.rank == 0 else None
         client.init_collectives(dist.broadcast_bytes(uid))
-        return "nccl"
+        if mode == "nccl":
+            return "nccl"
     handles = dist.all_gather_bytes(client.mailbox_handles())
     client.open_mailboxes(b"".join(handles))
-    return "nvlink-mailbox"
+    # "mailbox+nccl": single words (loss, sharded sums) over the NVLink mailbox, vectors (gradients) over NCCL
+    return "nvlink-mailbox" if mode == "mailbox" else "nvlink-mailbox + nccl"
