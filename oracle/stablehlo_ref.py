@@ -183,6 +183,12 @@ def _parse_block(lines, i):
             body, i = _parse_block(lines, i + 1)
             op.regions = [cond, body]
             i += 1
+        elif name == "stablehlo.reduce_window":
+            # generic form: '"stablehlo.reduce_window"(%x, %init) <{attrs}> ({', a block label, the body, '}) : (types) -> type'
+            body, i = _parse_block(lines, i)
+            op.regions = [body]
+            op.text = rest + " " + lines[i].strip()
+            i += 1
         elif name == "stablehlo.reduce" and "applies" not in rest:
             # long form: next line is "reducer(%a: t, %b: t) {"
             hdr = lines[i].strip()
@@ -473,6 +479,8 @@ class Interpreter:
             return make(res.reshape(shape), et)
         if short == "reduce":
             return self._reduce(op, env)
+        if short == "reduce_window":
+            return self._reduce_window(op, env)
         if short == "while":
             return self._while(op, env)
         if short == "all_reduce":
@@ -511,6 +519,38 @@ class Interpreter:
         else:
             raise NotImplementedError(f"oracle: reducer {kind}")
         return make(np.asarray(r).reshape(shape), et)
+
+    def _reduce_window(self, op, env):
+        """Cumulative form only (Reactant's scan_impl!, src/TracedRArray.jl:1049-1107): the window spans one whole
+        dimension, padded low by its extent minus one, unit strides and dilations -- an inclusive scan."""
+        text = op.text
+        names = re.findall(r"%[\w#.$-]+", text[text.index("("):text.index(")")])
+        x, init = env[names[0]], env[names[1]]
+        win = [int(v) for v in re.search(r"window_dimensions\s*=\s*array<i64:\s*([^>]*)>", text).group(1).split(",")]
+        pm = re.search(r"padding\s*=\s*dense<(.*?)>\s*:\s*tensor<(\d+)x2xi64>", text)
+        nums = [int(v) for v in re.findall(r"-?\d+", pm.group(1))]
+        rank = len(win)
+        pad = [(nums[2 * d], nums[2 * d + 1]) for d in range(rank)] if len(nums) == 2 * rank else [(nums[0], nums[0])] * rank
+        for attr in ("window_strides", "base_dilations", "window_dilations"):
+            m = re.search(attr + r"\s*=\s*array<i64:\s*([^>]*)>", text)
+            assert m is None or all(int(v) == 1 for v in m.group(1).split(",")), f"oracle: {attr} other than 1"
+        shape = list(x.a.shape)
+        axes = [d for d in range(rank) if win[d] != 1 or pad[d] != (0, 0)]
+        assert len(axes) <= 1, "oracle: only cumulative windows along one dimension"
+        kinds = [o.name.split(".", 1)[1] for o in op.regions[0] if o.name != "stablehlo.return"]
+        assert len(kinds) == 1, "only single-op reducers are on the path"
+        kind = kinds[0]
+        X, i0 = _wide(x), _wide(init)
+        ufunc = {"add": np.add, "maximum": np.maximum, "minimum": np.minimum, "multiply": np.multiply}[kind]
+        if axes:
+            d = axes[0]
+            assert win[d] == shape[d] and pad[d] == (shape[d] - 1, 0), "oracle: only cumulative windows"
+            r = ufunc.accumulate(X, axis=d)
+        else:
+            r = X
+        r = ufunc(r, i0)
+        (oshape, et), = _types_after_colon(text)[-1:]
+        return make(np.asarray(r).reshape(oshape), et)
 
     def _while(self, op, env):
         text = op.text

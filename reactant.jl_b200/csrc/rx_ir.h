@@ -46,7 +46,7 @@ struct Type {
 enum class OpK {
   Constant, Iota, Unary, Binary, Convert, Compare, Select, Clamp,
   BroadcastInDim, Transpose, Reshape, Slice, DynamicUpdateSlice, Pad, Concatenate,
-  DotGeneral, Reduce, While, AllReduce, Return
+  DotGeneral, Reduce, ReduceWindow, While, AllReduce, Return
 };
 
 enum class RedK { Add, Max, Min, Mul, Or, And };
@@ -64,7 +64,7 @@ struct Op {
   int ew = 0;                 // VmOp for Unary/Binary; VmCmp for Compare
   std::vector<int> in, out;   // value ids
   std::vector<int64_t> dims;  // broadcast dims / permutation / reduce dims / concat dim / iota dim
-  std::vector<int64_t> start, limit, stride;  // slice; pad: low/high/interior
+  std::vector<int64_t> start, limit, stride;  // slice; pad: low/high/interior; reduce_window: padding low/high (dims = window)
   // constant payload
   bool splat = true;
   double fval = 0;            // splat value as double (floats)

@@ -176,6 +176,82 @@ __global__ void __launch_bounds__(kThreads) k_logsumexp(const float* __restrict_
   }
 }
 
+
+// ---- inclusive scan along the middle dim of [outer][n][inner] (stablehlo.reduce_window in its cumulative form) ------
+// Lines that are strided in memory (inner > 1): one thread per line, sequential along n, coalesced across lines.
+__global__ void __launch_bounds__(kThreads) k_scan_lines(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, int code, int64_t outer, int64_t n, int64_t inner) {
+  const int64_t line = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (line >= outer * inner) return;
+  const int64_t o = line / inner, i = line - o * inner;
+  const int64_t base = o * n * inner + i;
+  uint32_t acc = red_identity(code);
+  for (int64_t r = 0; r < n; ++r) {
+    acc = red_combine(code, acc, __ldg(x + base + r * inner));
+    y[base + r * inner] = acc;
+  }
+}
+
+// Contiguous rows (inner == 1), each row cut into `nseg` segments of `seg` elements (a multiple of 1024).
+// Pass 1: the combined value of every segment.  Pass 2: every CTA folds the values of the segments before its own
+// (in order), then scans its segment 1024 elements at a time: four per thread, warp shuffles, one shared-memory hop
+// across the eight warps, and a running carry.  The order of combination is fixed, so results are deterministic.
+__global__ void __launch_bounds__(kThreads) k_scan_row_partials(const uint32_t* __restrict__ x, uint32_t* __restrict__ partial, int code, int64_t n, int64_t seg,
+                                                               int nseg) {
+  __shared__ uint32_t sm[kThreads / 32];
+  const int64_t row = blockIdx.y, s0 = (int64_t)blockIdx.x * seg, s1 = min(n, s0 + seg);
+  const uint32_t* xr = x + row * n;
+  uint32_t acc = red_identity(code);
+  for (int64_t c = s0 + threadIdx.x; c < s1; c += kThreads) acc = red_combine(code, acc, __ldg(xr + c));
+  acc = block_red<kThreads>(code, acc, sm);
+  if (threadIdx.x == 0) partial[row * nseg + blockIdx.x] = acc;
+}
+
+__global__ void __launch_bounds__(kThreads) k_scan_row_apply(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, const uint32_t* __restrict__ partial, int code, int64_t n,
+                                                            int64_t seg, int nseg) {
+  __shared__ uint32_t warp_tot[kThreads / 32];
+  __shared__ uint32_t carry_s;
+  const int64_t row = blockIdx.y, s0 = (int64_t)blockIdx.x * seg, s1 = min(n, s0 + seg);
+  const uint32_t* xr = x + row * n;
+  uint32_t* yr = y + row * n;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    uint32_t c = red_identity(code);
+    for (int q = 0; q < (int)blockIdx.x; ++q) c = red_combine(code, c, partial[row * nseg + q]);
+    carry_s = c;
+  }
+  __syncthreads();
+  uint32_t carry = carry_s;
+  for (int64_t c0 = s0; c0 < s1; c0 += 4 * kThreads) {
+    const int64_t c = c0 + 4 * threadIdx.x;
+    uint32_t v[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) v[q] = (c + q < s1) ? __ldg(xr + c + q) : red_identity(code);
+    v[1] = red_combine(code, v[0], v[1]);
+    v[2] = red_combine(code, v[1], v[2]);
+    v[3] = red_combine(code, v[2], v[3]);
+    // inclusive scan of the thread totals across the warp, then across the warps
+    uint32_t t = v[3];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t u = __shfl_up_sync(0xFFFFFFFFu, t, o);
+      if (lane >= o) t = red_combine(code, u, t);
+    }
+    if (lane == 31) warp_tot[w] = t;
+    __syncthreads();
+    uint32_t before = carry;  // everything left of this thread: carry, earlier warps, earlier lanes
+    for (int q = 0; q < w; ++q) before = red_combine(code, before, warp_tot[q]);
+    uint32_t lane_excl = __shfl_up_sync(0xFFFFFFFFu, t, 1);
+    if (lane > 0) before = red_combine(code, before, lane_excl);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (c + q < s1) yr[c + q] = red_combine(code, before, v[q]);
+    uint32_t total = carry;
+    for (int q = 0; q < kThreads / 32; ++q) total = red_combine(code, total, warp_tot[q]);
+    carry = total;
+    __syncthreads();  // warp_tot is rewritten by the next chunk
+  }
+}
+
 int grid_for(int64_t work_items, int sm_count, int per_sm) {
   int64_t blocks = (work_items + kThreads - 1) / kThreads;
   int64_t cap = (int64_t)sm_count * per_sm;
@@ -401,6 +477,37 @@ cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, 
   if (e != cudaSuccess) return e;
   k_reduce_col_finish<<<(unsigned)(outer * ((inner + 31) / 32)), kThreads, 0, c.stream>>>(partials, code, init_bits, outer, nsplit, inner, P.out[0]);
   *c.launches += 2;
+  return cudaGetLastError();
+}
+
+
+cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code, int64_t outer, int64_t n, int64_t inner) {
+  if (outer * n * inner == 0) return cudaSuccess;
+  const uint32_t* x = (const uint32_t*)src;
+  uint32_t* y = (uint32_t*)dst;
+  if (inner > 1 || n <= 32) {
+    // (for very short contiguous rows a thread per row is as good as anything)
+    const int64_t lines = outer * inner;
+    k_scan_lines<<<(unsigned)((lines + kThreads - 1) / kThreads), kThreads, 0, c.stream>>>(x, y, code, outer, n, inner);
+    ++*c.launches;
+    return cudaGetLastError();
+  }
+  if (outer > 65535) return cudaErrorInvalidValue;
+  // enough CTAs to fill the GPU, at least four 1024-element chunks per segment
+  int64_t want = std::max<int64_t>(1, (4 * (int64_t)c.sm_count + outer - 1) / outer);
+  int64_t max_seg = std::max<int64_t>(1, n / 4096);
+  int nseg = (int)std::min<int64_t>(std::min(want, max_seg), 1024);
+  int64_t seg = ((n + nseg - 1) / nseg + 1023) / 1024 * 1024;
+  nseg = (int)((n + seg - 1) / seg);
+  if ((size_t)(outer * nseg) + 2 > c.scratch_words) return cudaErrorInvalidValue;
+  uint32_t* partial = c.scratch;
+  dim3 grid((unsigned)nseg, (unsigned)outer);
+  if (nseg > 1) {
+    k_scan_row_partials<<<grid, kThreads, 0, c.stream>>>(x, partial, code, n, seg, nseg);
+    ++*c.launches;
+  }
+  k_scan_row_apply<<<grid, kThreads, 0, c.stream>>>(x, y, partial, code, n, seg, nseg);
+  ++*c.launches;
   return cudaGetLastError();
 }
 

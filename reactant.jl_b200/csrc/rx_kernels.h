@@ -26,6 +26,8 @@ cudaError_t launch_reduce_row(const LaunchCtx& c, const VmProgram& P, int code, 
 int reduce_col_splits(int64_t outer, int64_t red_n, int64_t inner, int sm_count);
 cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, int64_t outer, int64_t red_n,
                               int64_t inner, uint32_t* partials, int nsplit);
+// inclusive scan along the middle dim of a dense [outer][n][inner] array of 32-bit elements
+cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code, int64_t outer, int64_t n, int64_t inner);
 cudaError_t launch_logsumexp(const LaunchCtx& c, const float* x, int64_t row_stride, int64_t rows, int64_t cols, float* m, float* s, float* lse);
 
 // 2-D stencil step: out window = chain(shifted windows of src), tiles staged through

@@ -419,6 +419,105 @@ struct Parser {
     }
   }
 
+  // "stablehlo.reduce_window"(%x, %init) <{padding = dense<..> : tensor<Rx2xi64>, window_dimensions = array<i64: ..>, ..}> ({
+  //   ^bb0(%a: tensor<T>, %b: tensor<T>):  %s = stablehlo.add %a, %b : tensor<T>  stablehlo.return %s : tensor<T>
+  // }) : (tensor<..>, tensor<T>) -> tensor<..>
+  // -- the generic form MLIR prints for the op Reactant's scans emit (src/Ops.jl:3967-4010).
+  void parse_reduce_window(Region& region, const std::vector<std::string>& res, int line) {
+    Op op;
+    op.name = "stablehlo.reduce_window";
+    op.kind = OpK::ReduceWindow;
+    op.line = line;
+    expect("(");
+    op.in.push_back(use());
+    expect(",");
+    op.in.push_back(use());
+    if (accept(",")) fail(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window with several operands");
+    expect(")");
+    ws();
+    size_t a0 = p;
+    skip_balanced('<', '>');
+    const std::string attrs = s.substr(a0, p - a0);
+    auto ints_after = [&](const std::string& key, bool required) {
+      std::vector<int64_t> v;
+      size_t k = attrs.find(key);
+      if (k == std::string::npos) {
+        if (required) fail(RX_ERR_PARSE, "stablehlo.reduce_window without " + key);
+        return v;
+      }
+      size_t b = attrs.find('<', k);  // dense<...> or array<i64: ...>
+      if (b == std::string::npos) fail(RX_ERR_PARSE, "stablehlo.reduce_window: malformed " + key);
+      ++b;
+      size_t e2 = b;
+      for (int depth = 0; e2 < attrs.size() && !(attrs[e2] == '>' && depth == 0); ++e2) {
+        if (attrs[e2] == '<') ++depth;
+        if (attrs[e2] == '>') --depth;
+      }
+      if (key != "padding") {  // skip the element type of array<i64: ...>
+        size_t colon = attrs.find(':', b);
+        if (colon == std::string::npos || colon > e2) fail(RX_ERR_PARSE, "stablehlo.reduce_window: malformed " + key);
+        b = colon + 1;
+      }
+      const std::string body = attrs.substr(b, e2 - b);
+      for (size_t q = 0; q < body.size();) {
+        if (isdigit((unsigned char)body[q]) || (body[q] == '-' && q + 1 < body.size() && isdigit((unsigned char)body[q + 1]))) {
+          size_t used = 0;
+          v.push_back(std::stoll(body.substr(q), &used));
+          q += used;
+        } else {
+          ++q;
+        }
+      }
+      return v;
+    };
+    op.dims = ints_after("window_dimensions", true);
+    const size_t rank = op.dims.size();
+    std::vector<int64_t> pad = ints_after("padding", false);
+    if (pad.empty()) pad.assign(2 * rank, 0);
+    if (pad.size() == 1) pad.assign(2 * rank, pad[0]);  // splat
+    if (pad.size() != 2 * rank) fail(RX_ERR_PARSE, "stablehlo.reduce_window: padding does not match the window rank");
+    for (size_t d = 0; d < rank; ++d) {
+      op.start.push_back(pad[2 * d]);
+      op.limit.push_back(pad[2 * d + 1]);
+    }
+    for (const char* key : {"window_strides", "base_dilations", "window_dilations"})
+      for (int64_t v : ints_after(key, false))
+        if (v != 1) fail(RX_ERR_UNSUPPORTED_OP, std::string("unsupported op stablehlo.reduce_window with ") + key + " other than 1");
+    expect("(");
+    expect("{");
+    scopes.emplace_back();
+    ws();
+    if (peek("^")) {
+      while (p < s.size() && s[p] != '(') ++p;
+      expect("(");
+      do {
+        std::string n = value_name();
+        expect(":");
+        define(n, type());
+      } while (accept(","));
+      expect(")");
+      expect(":");
+    }
+    Region body;
+    bool ret;
+    parse_region_body(body, &ret);
+    scopes.pop_back();
+    expect(")");
+    if (body.ops.size() != 1 || body.yields.size() != 1 || body.ops[0].out[0] != body.yields[0])
+      fail(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window with a multi-op body");
+    static const std::pair<const char*, RedK> reds[] = {
+        {"stablehlo.add", RedK::Add}, {"stablehlo.maximum", RedK::Max}, {"stablehlo.minimum", RedK::Min}, {"stablehlo.multiply", RedK::Mul}};
+    bool ok = false;
+    for (auto& r : reds)
+      if (body.ops[0].name == r.first) { op.red = r.second; ok = true; }
+    if (!ok) fail(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window applying " + body.ops[0].name);
+    std::vector<Type> ins, outs;
+    signature(&ins, &outs);
+    if (rank != m->values[op.in[0]].type.shape.size()) fail(RX_ERR_PARSE, "stablehlo.reduce_window: window rank does not match the operand");
+    finish(op, res, outs);
+    region.ops.push_back(std::move(op));
+  }
+
   void parse_op(Region& region, bool* saw_return) {
     ws();
     int line = line_at(p);
@@ -438,7 +537,11 @@ struct Parser {
     ws();
     if (peek("\"")) {
       size_t e = s.find('"', p + 1);
-      fail(RX_ERR_UNSUPPORTED_OP, "unsupported op (generic form) " + s.substr(p, e - p + 1));
+      std::string quoted = s.substr(p, e - p + 1);
+      if (quoted != "\"stablehlo.reduce_window\"") fail(RX_ERR_UNSUPPORTED_OP, "unsupported op (generic form) " + quoted);
+      p = e + 1;
+      parse_reduce_window(region, res, line);
+      return;
     }
     std::string name = ident();
     Op op;

@@ -1167,6 +1167,70 @@ struct Planner {
     env[v] = reduce_any(op, X, dims, rt, init->f, init->i, needs_allreduce);
   }
 
+  // stablehlo.reduce_window in the cumulative form Reactant's accumulate / cumsum / cumprod emit
+  // (src/TracedRArray.jl:1049-1107): the window covers one whole dimension, padded low by its extent minus one,
+  // unit strides and dilations -- an inclusive scan along that dimension, combined with the init value.
+  void plan_reduce_window(const Op& op) {
+    int v = op.out[0], x = op.in[0];
+    ExprP X = env[x], init = env[op.in[1]];
+    if (init->k != Expr::Const) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window with a non-constant init value");
+    if (X->dt != DT::F32 && X->dt != DT::S32)
+      throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type " + std::string(dt_name(X->dt)) + " in " + op.name);
+    {
+      // the padding is filled with the init value, so anything but the combiner's identity would be counted once
+      // per padded position; Reactant passes the identity (src/TracedRArray.jl:1063-1070)
+      const bool f = X->dt == DT::F32;
+      bool identity = false;
+      switch (op.red) {
+        case RedK::Add: identity = f ? init->f == 0.0 : init->i == 0; break;
+        case RedK::Mul: identity = f ? init->f == 1.0 : init->i == 1; break;
+        case RedK::Max: identity = f ? (std::isinf(init->f) && init->f < 0) : init->i == INT32_MIN; break;
+        case RedK::Min: identity = f ? (std::isinf(init->f) && init->f > 0) : init->i == INT32_MAX; break;
+        default: break;
+      }
+      if (!identity) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window with an init value that is not the identity of its combiner");
+    }
+    const int rank = (int)X->shape.size();
+    int axis = -1;
+    for (int d = 0; d < rank; ++d) {
+      const bool trivial = op.dims[d] == 1 && op.start[d] == 0 && op.limit[d] == 0;
+      if (trivial) continue;
+      // the window and padding are written for the global shape
+      const int64_t extent = m.values[x].type.shape[d];
+      if (axis >= 0 || op.dims[d] != extent || op.start[d] != extent - 1 || op.limit[d] != 0)
+        throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window: only cumulative windows along one dimension (scans) are supported");
+      axis = d;
+    }
+    if (axis >= 0 && shard[x] == axis) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window scanning along a sharded dimension");
+    shard[v] = shard[x];
+    Type t = local_type(v);
+    const bool flt = X->dt == DT::F32;
+    if (axis < 0) {  // windows of one element: out = x (op) init
+      int vop = flt ? (op.red == RedK::Add ? VM_ADD : op.red == RedK::Max ? VM_MAX : op.red == RedK::Min ? VM_MIN : VM_MUL)
+                    : (op.red == RedK::Add ? VM_IADD : op.red == RedK::Max ? VM_IMAX : op.red == RedK::Min ? VM_IMIN : VM_IMUL);
+      env[v] = mkop(vop, t, {X, konst(t, init->f, init->i)});
+      return;
+    }
+    Step st;
+    st.kind = StepK::Scan;
+    st.src_slot = materialise(X, "scan operand");
+    st.dst_slot = new_slot(t);
+    st.red = op.red;
+    st.red_dt = flt ? DT::F32 : DT::S32;
+    st.init_f = init->f;
+    st.init_i = init->i;
+    st.outer = st.inner = 1;
+    for (int d = 0; d < axis; ++d) st.outer *= X->shape[d];
+    st.red_n = X->shape[axis];
+    for (int d = axis + 1; d < rank; ++d) st.inner *= X->shape[d];
+    st.note = std::string("inclusive scan(") + (op.red == RedK::Add ? "add" : op.red == RedK::Max ? "max" : op.red == RedK::Min ? "min" : "mul") + ") over " +
+              std::to_string(st.red_n) + " x " + std::to_string(st.outer * st.inner) + " lines";
+    plan.scratch_floats = std::max<int64_t>(plan.scratch_floats, 1 << 16);
+    const int dst = st.dst_slot;
+    cur->push_back(std::move(st));
+    env[v] = leaf(dst, t);
+  }
+
   // One step when the reduced dims form a single run of the (normalised) iteration space and the kept dims on
   // either side merge.  Otherwise (a) several reduced dims: reduce the innermost one on its own, with the
   // operation's identity as init, and go on with the rest -- valid for every supported combiner (associative and
@@ -1659,6 +1723,7 @@ struct Planner {
         case OpK::BroadcastInDim: case OpK::Transpose: case OpK::Slice: plan_view(op); break;
         case OpK::Reshape: plan_reshape(op); break;
         case OpK::Reduce: plan_reduce(op); break;
+        case OpK::ReduceWindow: plan_reduce_window(op); break;
         case OpK::DynamicUpdateSlice: plan_dus(op); break;
         case OpK::Pad: plan_pad(op); break;
         case OpK::Concatenate: plan_concat(op); break;
@@ -1756,6 +1821,7 @@ const char* step_name(StepK k) {
     case StepK::Fill: return "fill";
     case StepK::Loop: return "loop";
     case StepK::AllReduce: return "all_reduce";
+    case StepK::Scan: return "scan";
   }
   return "?";
 }

@@ -23,7 +23,7 @@ struct Slot {
   int64_t bytes() const { return type.numel() * (int64_t)dt_size(type.dt); }
 };
 
-enum class StepK { Map, ReduceFull, ReduceRow, ReduceCol, LogSumExp, Stencil, Gemm, Copy, Fill, Loop, AllReduce };
+enum class StepK { Map, ReduceFull, ReduceRow, ReduceCol, LogSumExp, Stencil, Gemm, Copy, Fill, Loop, AllReduce, Scan };
 
 struct GemmDesc {
   // D[m][n] = sum_k A(m,k) * B(k,n); strides in elements of the operand slots.
@@ -65,6 +65,7 @@ struct Step {
   std::vector<Step> body;
   std::vector<int> state_slots;   // slot holding loop-carried value j on entry to an iteration
   std::vector<int> yield_slots;   // slot holding its next value at the end of the body
+  // Scan: inclusive prefix (red) of src_slot along the middle dim of [outer][red_n][inner] into dst_slot, combined with init
   // AllReduce (sum over the mesh axis, in place on dst_slot)
   int64_t count = 0;
 };

@@ -234,6 +234,7 @@ const char* kind_name(StepK k) {
     case StepK::Fill: return "fill";
     case StepK::Loop: return "loop";
     case StepK::AllReduce: return "all_reduce";
+    case StepK::Scan: return "scan";
   }
   return "?";
 }
@@ -344,6 +345,10 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
       const float* x = (const float*)slot_ptr(r, st.leaf_slot[0]) + l.offset;
       CK(launch_logsumexp(c, x, l.stride[0], st.outer, st.red_n, (float*)slot_ptr(r, st.out_slot[0]), (float*)slot_ptr(r, st.out_slot[1]),
                           (float*)slot_ptr(r, st.out_slot[2])));
+      break;
+    }
+    case StepK::Scan: {
+      CK(launch_scan(c, slot_ptr(r, st.src_slot), slot_ptr(r, st.dst_slot), red_code(st.red, st.red_dt), st.outer, st.red_n, st.inner));
       break;
     }
     case StepK::Gemm: {

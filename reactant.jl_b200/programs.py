@@ -234,3 +234,31 @@ def matmul(m: int, k: int, n: int, et: str = "f32") -> str:
   }}
 }}
 """
+
+
+def scan(xla_dims, xla_axis: int, kind: str = "add", et: str = "f32") -> str:
+    """cumsum / cumprod / accumulate(max|min) along one dimension, as Reactant's scan_impl! lowers it
+    (src/TracedRArray.jl:1049-1107): stablehlo.reduce_window whose window is the whole dimension, padded low by
+    its extent minus one, with the combiner's identity as init value.  `xla_dims` are the boundary (reversed)
+    dims; Julia `dims = d` of an N-d array is boundary dim N - d."""
+    rank = len(xla_dims)
+    win = [1] * rank
+    win[xla_axis] = xla_dims[xla_axis]
+    pads = "[" + ", ".join(f"[{xla_dims[d] - 1 if d == xla_axis else 0}, 0]" for d in range(rank)) + "]"
+    ones = ", ".join(["1"] * rank)
+    flt = et in ("f32", "bf16")
+    init = {"add": "0.000000e+00" if flt else "0", "multiply": "1.000000e+00" if flt else "1",
+            "maximum": "0xFF800000" if flt else "-2147483648", "minimum": "0x7F800000" if flt else "2147483647"}[kind]
+    ty, sc = _t(list(xla_dims), et), _t([], et)
+    return f"""module @reactant_scan attributes {{mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64}} {{
+  func.func @main(%arg0: {ty}) -> {ty} {{
+    %cst = stablehlo.constant dense<{init}> : {sc}
+    %0 = "stablehlo.reduce_window"(%arg0, %cst) <{{base_dilations = array<i64: {ones}>, padding = dense<{pads}> : tensor<{rank}x2xi64>, window_dilations = array<i64: {ones}>, window_dimensions = array<i64: {', '.join(map(str, win))}>, window_strides = array<i64: {ones}>}}> ({{
+    ^bb0(%arg1: {sc}, %arg2: {sc}):
+      %1 = stablehlo.{kind} %arg1, %arg2 : {sc}
+      stablehlo.return %1 : {sc}
+    }}) : ({ty}, {sc}) -> {ty}
+    return %0 : {ty}
+  }}
+}}
+"""

@@ -261,6 +261,56 @@ add("sharded_sum_768_f32", "test/core/sharding/sharding.jl:26-63 (collect(1:768)
     "    return %0 : tensor<f32>\n  }\n}\n",
     [{"dims": [768], "data": [float(v) for v in xsh]}], [{"dims": [], "data": [float(sum(xsh))]}], "f32", 2e-6)
 
+# ---- test/core/map_reduction.jl:163-200 "accumulate" / "cumsum": a = (1:10)/10; b = reshape(1:60, 3,4,5)/60, dims = 1, 2, 3 ----
+# Reactant lowers cumsum to stablehlo.reduce_window over the whole dimension, padded low by its extent minus one
+# (scan_impl!, src/TracedRArray.jl:1049-1107); MLIR prints that op in the generic form.
+def reduce_window_module(xla_dims, xla_axis, et, kind="add", init="0.000000e+00"):
+    rank = len(xla_dims)
+    win = [1] * rank
+    win[xla_axis] = xla_dims[xla_axis]
+    pad = [[0, 0] for _ in range(rank)]
+    pad[xla_axis] = [xla_dims[xla_axis] - 1, 0]
+    ones = ", ".join(["1"] * rank)
+    ty = t(xla_dims, et)
+    pads = "[" + ", ".join(f"[{lo}, {hi}]" for lo, hi in pad) + "]"
+    return wrap([ty], [ty],
+                f"    %cst = stablehlo.constant dense<{init}> : {t([], et)}\n"
+                f"    %0 = \"stablehlo.reduce_window\"(%arg0, %cst) <{{base_dilations = array<i64: {ones}>, padding = dense<{pads}> : tensor<{rank}x2xi64>, "
+                f"window_dilations = array<i64: {ones}>, window_dimensions = array<i64: {', '.join(map(str, win))}>, window_strides = array<i64: {ones}>}}> ({{\n"
+                f"    ^bb0(%arg1: {t([], et)}, %arg2: {t([], et)}):\n"
+                f"      %1 = stablehlo.{kind} %arg1, %arg2 : {t([], et)}\n"
+                f"      stablehlo.return %1 : {t([], et)}\n"
+                f"    }}) : ({ty}, {t([], et)}) -> {ty}\n"
+                f"    return %0 : {ty}")
+
+
+for et in ("f64", "f32"):
+    tol = 1e-12 if et == "f64" else 2e-6
+    a10 = [Fraction(k, 10) for k in range(1, 11)]
+    run, acc = [], Fraction(0)
+    for v in a10:
+        acc += v
+        run.append(float(acc))
+    add(f"cumsum_vector_{et}", "test/core/map_reduction.jl:163-173 (cumsum(a), a = (1:10)/10)",
+        reduce_window_module([10], 0, et), [{"dims": [10], "data": [float(v) for v in a10]}], [{"dims": [10], "data": run}], et, tol)
+    b60 = [Fraction(k, 60) for k in range(1, 61)]
+    jd = (3, 4, 5)
+    for jdim in (1, 2, 3):
+        out = [None] * 60
+        for i in range(3):
+            for j in range(4):
+                for k in range(5):
+                    ix = [i, j, k]
+                    acc = Fraction(0)
+                    for q in range(ix[jdim - 1] + 1):
+                        jx = list(ix)
+                        jx[jdim - 1] = q
+                        acc += b60[idx_cm(jd, *jx)]
+                    out[idx_cm(jd, i, j, k)] = float(acc)
+        add(f"cumsum_3d_dims{jdim}_{et}", f"test/core/map_reduction.jl:175-177 (cumsum(b; dims={jdim}), b = reshape(1:60, 3, 4, 5)/60)",
+            reduce_window_module([5, 4, 3], 3 - jdim, et), [{"dims": [5, 4, 3], "data": [float(v) for v in b60]}],
+            [{"dims": [5, 4, 3], "data": out}], et, tol)
+
 with open(os.path.join(HERE, "reactant_fixtures.json"), "w") as f:
     json.dump({"generator": "tests/golden/make_fixtures.py", "cases": cases}, f, indent=1)
 print(f"wrote {len(cases)} cases")

@@ -348,3 +348,31 @@ def test_compiling_a_module_again_reuses_its_plan(rx, client):
     x = np.linspace(-1, 1, 12345, dtype=np.float32)
     a, b = float(f(rx.to_rarray(x, client), rx.to_rarray(x, client))), float(g(rx.to_rarray(x, client), rx.to_rarray(x, client)))
     assert a == b
+
+
+# ---------------------------------------------------------------- scans (cumsum and friends)
+@pytest.mark.parametrize("dims,axis", [((1,), 0), ((33,), 0), ((5000,), 0), (((1 << 20) + 3,), 0), ((700, 5000), 1), ((3, 300000), 1),
+                                        ((257, 129), 0), ((6, 1000, 7), 1), ((4, 5, 2049), 2), ((70000, 3), 1)])
+@pytest.mark.parametrize("kind", ["add", "maximum"])
+def test_scans_along_one_dimension(rx, ref, client, dims, axis, kind):
+    rng = np.random.default_rng(len(dims) * 100 + axis)
+    x = rng.standard_normal(dims).astype(np.float32)
+    text = rx.programs.scan(dims, axis, kind)
+    (got,), _, _ = run(rx, client, text, [x])
+    want = ref.run_module(text, [x])[0]
+    if kind == "maximum":
+        assert np.array_equal(got, want)
+    else:
+        n = dims[axis]
+        # a prefix of k terms carries the reduction bound for k terms, relative to the 2-norm of the terms seen so far
+        norm = np.sqrt(np.cumsum(x.astype(np.float64) ** 2, axis=axis))
+        assert np.all(np.abs(got - want) <= ref.reduction_tolerance(max(n, 2)) * np.maximum(np.abs(want), norm) + 1e-30)
+
+
+def test_integer_scans_are_exact(rx, ref, client):
+    x = np.random.default_rng(0).integers(-1000, 1000, size=(37, 4099)).astype(np.int32)
+    for axis in (0, 1):
+        for kind in ("add", "minimum"):
+            text = rx.programs.scan(x.shape, axis, kind, et="i32")
+            (got,), _, _ = run(rx, client, text, [x])
+            assert np.array_equal(got, ref.run_module(text, [x])[0])
