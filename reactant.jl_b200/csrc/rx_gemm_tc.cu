@@ -46,6 +46,7 @@ struct GemmParams {
   int out_bf16;
   int tiles_m, tiles_n;
   int* status;
+  int tma_store;         // pair kernel: epilogue goes through shared memory and tiled bulk stores
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------
@@ -333,9 +334,15 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
       : "memory");
 }
 
+// Epilogue staging of the pair kernel: per epilogue warp two 4 KiB buffers (32 rows x 128 bytes, 128-byte swizzle).
+// Each lane owns an accumulator row after tcgen05.ld, so direct global stores touch 32 different lines per
+// instruction (the last tile's epilogue, which nothing overlaps, took 3.4 us that way); through shared memory the
+// copy engine writes whole 128-byte row pieces and the warp only issues conflict-free 16-byte shared stores.
+constexpr int kOutStageBytes = kEpiWarps * 2 * 4096;
+
 template <bool WIDE>
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc2(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                                                          const __grid_constant__ GemmParams p) {
+                                                          const __grid_constant__ CUtensorMap tmD, const __grid_constant__ GemmParams p) {
   using S = Slab2<WIDE>;
   constexpr int STAGES2 = S::kStages, STAGE2_BYTES = S::kStageBytes, A2_BYTES = S::kABytes, BK = S::kBK;
   extern __shared__ unsigned char smem_raw[];
@@ -454,17 +461,71 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc2(const __grid_constant_
       const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
       const long long m = (long long)tm * 256 + rank * 128 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * 256;
+      if (p.tma_store) {
+        unsigned char* ob = smem + kRing2Bytes + (warp - 2) * 8192;
+        const int row0 = tm * 256 + (int)rank * 128 + quad * 32;   // row of lane 0
+        const int sw = lane & 7;
+        if (p.out_bf16) {
 #pragma unroll 1
-      for (int c = 0; c < 256; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c, v);
-        tmem_ld_wait();
-        store_row32(p, m, (long long)tn * 256 + c, v);
+          for (int c = 0; c < 256; c += 64) {   // 64 bf16 columns = 128 bytes per row
+            uint32_t v[32], w[32];
+            tmem_ld32(taddr + c, v);
+            tmem_ld32(taddr + c + 32, w);
+            if (lane == 0) tma_store_wait_read<1>();  // the buffer written two chunks ago has been read
+            __syncwarp();
+            tmem_ld_wait();
+            unsigned char* dst = ob + ((c >> 6) & 1) * 4096 + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t* q = j < 4 ? v + 8 * j : w + 8 * (j - 4);
+              uint4 o;
+              __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(q[0]), __uint_as_float(q[1]));
+              __nv_bfloat162 b1 = __floats2bfloat162_rn(__uint_as_float(q[2]), __uint_as_float(q[3]));
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(q[4]), __uint_as_float(q[5]));
+              __nv_bfloat162 b3 = __floats2bfloat162_rn(__uint_as_float(q[6]), __uint_as_float(q[7]));
+              o.x = *(uint32_t*)&b0; o.y = *(uint32_t*)&b1; o.z = *(uint32_t*)&b2; o.w = *(uint32_t*)&b3;
+              *(uint4*)(dst + ((j ^ sw) << 4)) = o;
+            }
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmD, ob + ((c >> 6) & 1) * 4096, tn * 256 + c, row0);
+              tma_store_commit();
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < 256; c += 32) {   // 32 f32 columns = 128 bytes per row
+            uint32_t v[32];
+            tmem_ld32(taddr + c, v);
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+            tmem_ld_wait();
+            unsigned char* dst = ob + ((c >> 5) & 1) * 4096 + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) *(uint4*)(dst + ((j ^ sw) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmD, ob + ((c >> 5) & 1) * 4096, tn * 256 + c, row0);
+              tma_store_commit();
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 256; c += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c, v);
+          tmem_ld_wait();
+          store_row32(p, m, (long long)tn * 256 + c, v);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&acc_empty[buf]);
     }
+    if (p.tma_store && lane == 0) tma_store_wait<0>();  // this thread's bulk stores have been written
   }
   tc_fence_before();
   __syncthreads();
@@ -483,8 +544,8 @@ bool make_operand_map(CUtensorMap* m, const __nv_bfloat16* base, bool mn_major, 
 }
 
 template <bool WIDE>
-cudaError_t launch_pair_kernel(RxDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p) {
-  const size_t smem2 = (size_t)Slab2<WIDE>::kStages * Slab2<WIDE>::kStageBytes + 1024;
+cudaError_t launch_pair_kernel(RxDevice* d, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const GemmParams& p) {
+  const size_t smem2 = (size_t)Slab2<WIDE>::kStages * Slab2<WIDE>::kStageBytes + kOutStageBytes + 1024;
   static_assert(Slab2<WIDE>::kStages * Slab2<WIDE>::kStageBytes == kRing2Bytes, "both slab geometries use the same ring");
   static bool attr2_dev[64] = {};          // function attributes are per device
   static int max_clusters_dev[64] = {};
@@ -513,7 +574,7 @@ cudaError_t launch_pair_kernel(RxDevice* d, const CUtensorMap& tmA, const CUtens
   }
   int pairs = std::min(p.tiles_m * p.tiles_n, std::min(max_clusters, d->sm_count / 2));
   cfg.gridDim = dim3(2 * pairs);
-  return cudaLaunchKernelEx(&cfg, k_gemm_tc2<WIDE>, tmA, tmB, p);
+  return cudaLaunchKernelEx(&cfg, k_gemm_tc2<WIDE>, tmA, tmB, tmD, p);
 }
 
 }  // namespace
@@ -565,7 +626,13 @@ cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* 
         tmB = wb;
       }
     }
-    cudaError_t e = wide ? launch_pair_kernel<true>(d, tmA, tmB, p) : launch_pair_kernel<false>(d, tmA, tmB, p);
+    // output tensor map for the staged epilogue: boxes of 32 rows x 128 bytes, 128-byte swizzle
+    CUtensorMap tmD{};
+    const size_t esz = p.out_bf16 ? 2 : 4;
+    p.tma_store = !getenv("RX_GEMM_DIRECT_STORE") && ((uintptr_t)out % 16 == 0) && ((size_t)p.ldd * esz % 16 == 0) &&
+                  tma_make_2d(&tmD, p.out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, out, (uint64_t)g.N, (uint64_t)g.M,
+                              (uint64_t)p.ldd * esz, (uint32_t)(128 / esz), 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    cudaError_t e = wide ? launch_pair_kernel<true>(d, tmA, tmB, tmD, p) : launch_pair_kernel<false>(d, tmA, tmB, tmD, p);
     ++d->launches;
     *handled = true;
     return e != cudaSuccess ? e : cudaGetLastError();
