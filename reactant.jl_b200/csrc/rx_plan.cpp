@@ -807,7 +807,105 @@ struct Planner {
 
   // ---- step emitters -------------------------------------------------------
   // out[shape-indexed] = expr, written at `offset` with `ostride` into `slot`.
+  // What the most recently emitted Map step computes, kept so that the next map can be merged into it.
+  struct LastMap {
+    std::vector<Step>* where = nullptr;
+    size_t index = 0;
+    struct Out { int slot; ExprP expr; int64_t offset; std::vector<int64_t> stride; };
+    std::vector<Out> outs;
+  } last_map;
+
+  // Replace every whole-slot read of `slot` in `e` by `repl`.  *blocked is set if `slot` is also read in a way that
+  // cannot be replaced (a window of it): the reader must then stay a separate launch after the writer.
+  ExprP subst_slot(const ExprP& e, int slot, const ExprP& repl, std::map<const Expr*, ExprP>& memo, bool* found, bool* blocked) {
+    auto it = memo.find(e.get());
+    if (it != memo.end()) return it->second;
+    ExprP r = e;
+    if (e->k == Expr::Leaf) {
+      if (e->slot == slot) {
+        if (whole_slot(e) && e->shape == repl->shape && e->dt == repl->dt) { r = repl; *found = true; }
+        else *blocked = true;
+      }
+    } else if (e->k == Expr::Op || e->k == Expr::View) {
+      std::vector<ExprP> kids;
+      bool changed = false;
+      for (auto& k : e->kids) {
+        kids.push_back(subst_slot(k, slot, repl, memo, found, blocked));
+        changed = changed || kids.back() != k;
+      }
+      if (changed) {
+        auto c = std::make_shared<Expr>(*e);
+        c->kids = kids;
+        r = c;
+      }
+    }
+    memo[e.get()] = r;
+    return r;
+  }
+  bool reads_slot(const ExprP& e, int slot, std::set<const Expr*>& seen) {
+    if (!seen.insert(e.get()).second) return false;
+    if (e->k == Expr::Leaf) return e->slot == slot;
+    for (auto& k : e->kids)
+      if (reads_slot(k, slot, seen)) return true;
+    return false;
+  }
+
+  // ---- step emitters -------------------------------------------------------
+  // out[shape-indexed] = expr, written at `offset` with `ostride` into `slot`.
+  //
+  // Merging: when this map reads, element for element, what the map emitted just before it wrote (a value that
+  // was materialised because it has several consumers, e.g. the activation that both the next layer and the
+  // backward pass need), the two become ONE launch with both outputs: the shared value is computed once in
+  // registers, stored, and used -- it is not written and read back, and the operands the two chains have in common
+  // are loaded once.  Results are identical: the register holds exactly the value that is stored.
   void emit_map(const ExprP& e, int slot, int64_t offset, const std::vector<int64_t>& ostride, const std::string& note) {
+    static const bool merge_off = getenv("RX_NO_MAP_MERGE") != nullptr;
+    if (!merge_off && last_map.where == cur && last_map.index < cur->size() && (*cur)[last_map.index].kind == StepK::Map &&
+        last_map.outs.size() + 1 <= (size_t)kVmMaxOuts && !last_map.outs.empty() && last_map.outs[0].expr->shape == e->shape) {
+      ExprP merged = e;
+      bool found = false, blocked = false;
+      for (auto& o : last_map.outs) {
+        std::map<const Expr*, ExprP> memo;
+        merged = subst_slot(merged, o.slot, o.expr, memo, &found, &blocked);
+        std::set<const Expr*> seen;
+        blocked = blocked || reads_slot(o.expr, slot, seen) || o.slot == slot;  // the earlier chain must not read what this one writes
+      }
+      // steps emitted since that map (reductions of its result, say) stay where they are; this map moves up in front
+      // of them, which is fine as long as none of them writes anything it reads
+      if (found && !blocked) {
+        std::set<int> written;
+        for (size_t q = last_map.index + 1; q < cur->size(); ++q) {
+          const Step& t = (*cur)[q];
+          if (t.kind == StepK::Loop || t.kind == StepK::Stencil) blocked = true;
+          for (int w : t.out_slot) written.insert(w);
+          for (int w : {t.dst_slot, t.gemm.d_slot})
+            if (w >= 0) written.insert(w);
+        }
+        for (int w : written) {
+          std::set<const Expr*> seen;
+          blocked = blocked || w == slot || reads_slot(merged, w, seen);
+        }
+      }
+      if (found && !blocked) {
+        Step st;
+        st.kind = StepK::Map;
+        st.note = (*cur)[last_map.index].note + " + " + note;
+        try {
+          Lowering L(e->shape);
+          std::vector<OutSpec> outs;
+          for (auto& o : last_map.outs)
+            outs.push_back(OutSpec{o.slot, plan.slots[o.slot].type.dt, o.offset, o.stride, L.lower(o.expr, Lowering::identity(e->shape.size()))});
+          outs.push_back(OutSpec{slot, plan.slots[slot].type.dt, offset, ostride, L.lower(merged, Lowering::identity(e->shape.size()))});
+          std::vector<int> cls(e->shape.size(), 0);
+          assemble(st, L, outs, -1, cls, true);
+          (*cur)[last_map.index] = std::move(st);
+          last_map.outs.push_back({slot, merged, offset, ostride});
+          return;
+        } catch (const Error& err) {
+          if (err.code != RX_ERR_PLAN) throw;  // too many operands / instructions / registers for one group: keep two launches
+        }
+      }
+    }
     Step st;
     st.kind = StepK::Map;
     st.note = note;
@@ -817,7 +915,15 @@ struct Planner {
     std::vector<int> cls(e->shape.size(), 0);
     assemble(st, L, {OutSpec{slot, odt, offset, ostride, root}}, -1, cls, true);
     classify_stencil(st);
+    const bool plain = st.kind == StepK::Map;
     cur->push_back(std::move(st));
+    last_map.where = nullptr;
+    if (plain && offset == 0 && ostride == canon_strides(e->shape) && prod(e->shape) == plan.slots[slot].type.numel()) {
+      last_map.where = cur;
+      last_map.index = cur->size() - 1;
+      last_map.outs.clear();
+      last_map.outs.push_back({slot, e, offset, ostride});
+    }
   }
 
   // A map whose operands are shifted windows of one row-major 2-D array and whose
@@ -1244,6 +1350,7 @@ struct Planner {
       if (e.code != RX_ERR_PLAN) throw;
       plan.slots.resize(n_slots);
       cur->resize(n_steps);
+      last_map.where = nullptr;
       if (dims.size() < 2 && whole_slot(X)) throw;
     }
     if (dims.size() < 2) {
