@@ -122,3 +122,44 @@ def test_dynamic_loop_bound_is_rejected(rx):
     with pytest.raises(rx.ReactantError) as e:
         rx.plan_describe(text)
     assert "stablehlo.while" in str(e.value)
+
+
+def test_maps_that_consume_a_materialised_value_join_its_producer(rx):
+    """gelu activation + the bf16 operand of the next GEMM, and gelu' + its bf16 copy, are one launch each: the
+    second chain reads what the first one materialised, element for element."""
+    steps = rx.plan_describe(rx.programs.mlp_grad(64, 128, 32, 256))["steps"]
+    notes = [s["note"] for s in steps]
+    assert any("shared value %th + contraction lhs" in n for n in notes), notes
+    assert any(n.startswith("shared value %dz1 + ") for n in notes), notes
+    assert sum(s["kind"] == "gemm" for s in steps) == 5
+    assert len(steps) == 12
+
+
+def test_cumulative_reduce_window_plans_as_a_scan_and_other_windows_are_refused(rx):
+    d = rx.plan_describe(rx.programs.scan((5, 4, 3), 1, "add"))
+    assert [s["kind"] for s in d["steps"]] == ["scan"]
+    pooling = rx.programs.scan((8, 8), 1, "maximum").replace("window_dimensions = array<i64: 1, 8>", "window_dimensions = array<i64: 1, 2>").replace(
+        "[7, 0]", "[0, 0]")
+    with pytest.raises(rx.ReactantError) as e:
+        rx.plan_describe(pooling)
+    assert "reduce_window" in str(e.value)
+    with pytest.raises(rx.ReactantError) as e:  # the padding is filled with the init value: only the identity is accepted
+        rx.plan_describe(rx.programs.scan((16,), 0, "add").replace("dense<0.000000e+00>", "dense<1.000000e+00>"))
+    assert "identity" in str(e.value)
+
+
+def test_reductions_over_non_adjacent_or_non_mergeable_dims_are_staged(rx):
+    t = "tensor<17x3x17xf32>"
+    text = f"""module {{
+  func.func @main(%arg0: {t}, %arg1: tensor<3xf32>) -> (tensor<3xf32>, tensor<17x3xf32>) {{
+    %z = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %b = stablehlo.broadcast_in_dim %arg1, dims = [1] : (tensor<3xf32>) -> {t}
+    %0 = stablehlo.multiply %arg0, %b : {t}
+    %1 = stablehlo.reduce(%0 init: %z) applies stablehlo.add across dimensions = [0, 2] : ({t}, tensor<f32>) -> tensor<3xf32>
+    %2 = stablehlo.reduce(%0 init: %z) applies stablehlo.add across dimensions = [2] : ({t}, tensor<f32>) -> tensor<17x3xf32>
+    return %1, %2 : tensor<3xf32>, tensor<17x3xf32>
+  }}
+}}
+"""
+    kinds = [s["kind"] for s in rx.plan_describe(text)["steps"]]
+    assert kinds.count("reduce_row") + kinds.count("reduce_col") + kinds.count("reduce_full") >= 3, kinds
