@@ -163,13 +163,17 @@ int64_t RxPlanCacheHits(void);
  * code generation inside ClientCompile (API.cpp:1482-1507); these three entry
  * points have no counterpart of their own.
  * RxChainSpecialiser: set the threshold; a negative value switches it off.
- * RxChainSpecialiserStats: out4 = {kernels compiled, cache hits, compile
- *   failures, 1 if NVRTC or the driver entry points are unavailable}.
+ * RxChainSpecialiserStats: out5 = {kernels compiled, in-memory cache hits,
+ *   compile failures, 1 if NVRTC or the driver entry points are unavailable,
+ *   kernels read from the on-disk cache}.  With RX_JIT_CACHE_DIR set to an
+ *   existing directory compiled chains are kept there across processes (the
+ *   counterpart of src/PersistentCompileCache.jl for this engine's only
+ *   compiled artefact).
  * RxPlanSpecialiseCheck: plan a module and compile every chain in it for each
  *   kernel family it could run in, without a device; returns a JSON list
  *   (caller frees) or NULL with the error set to the compiler log. */
 void RxChainSpecialiser(int64_t min_elems);
-void RxChainSpecialiserStats(int64_t* out4);
+void RxChainSpecialiserStats(int64_t* out5);
 const char* RxPlanSpecialiseCheck(const char* mlir_text, size_t text_len);
 
 /* ---- execute (API.cpp:1585-1630, 1653-1728) --------------------------------- */

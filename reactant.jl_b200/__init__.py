@@ -462,9 +462,9 @@ def chain_specialiser(min_elems: int) -> None:
 
 def chain_specialiser_stats() -> dict:
     import ctypes
-    out = (ctypes.c_int64 * 4)()
+    out = (ctypes.c_int64 * 5)()
     lib().RxChainSpecialiserStats(out)
-    return {"compiled": out[0], "cache_hits": out[1], "failed": out[2], "unavailable": bool(out[3])}
+    return {"compiled": out[0], "cache_hits": out[1], "failed": out[2], "unavailable": bool(out[3]), "disk_hits": out[4]}
 
 
 from . import programs  # noqa: E402,F401

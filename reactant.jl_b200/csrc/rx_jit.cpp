@@ -5,6 +5,8 @@
 #include <dlfcn.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
+#include <unistd.h>
 
 #include <map>
 #include <mutex>
@@ -119,7 +121,7 @@ std::string hex32(uint32_t v) {
 std::mutex g_mu;
 // RX_JIT_MIN_ELEMS overrides the default threshold (e.g. 0 to specialise every launch, -1 for none)
 int64_t g_min_elems = getenv("RX_JIT_MIN_ELEMS") ? atoll(getenv("RX_JIT_MIN_ELEMS")) : (int64_t)1 << 20;
-int64_t g_compiled = 0, g_hits = 0, g_failed = 0;
+int64_t g_compiled = 0, g_hits = 0, g_failed = 0, g_disk_hits = 0;
 std::map<std::string, std::vector<char>> g_cubins;              // source -> cubin
 std::map<std::string, std::string> g_lowered;                   // source -> lowered kernel name
 std::map<std::pair<int, std::string>, JitKernel> g_kernels;     // (device, source) -> loaded kernel
@@ -156,6 +158,54 @@ bool compile(const std::string& src, const std::string& name_expr, std::vector<c
   }
   n.DestroyProgram(&prog);
   return ok;
+}
+
+// Optional on-disk cache of compiled chains (RX_JIT_CACHE_DIR=<existing directory>): the analogue, for this
+// engine's only compiled artefact, of Reactant's persistent compile cache (src/PersistentCompileCache.jl).
+// A file holds the lowered kernel name, a newline, and the cubin; its name is a 64-bit FNV-1a hash of the
+// generated source together with the source length, and the source itself is stored and compared on load.
+std::string cache_path(const std::string& src) {
+  const char* dir = getenv("RX_JIT_CACHE_DIR");
+  if (!dir || !*dir) return "";
+  uint64_t h = 1469598103934665603ull;
+  for (unsigned char c : src) h = (h ^ c) * 1099511628211ull;
+  char name[64];
+  snprintf(name, sizeof name, "/rx_chain_%016llx_%zu.bin", (unsigned long long)h, src.size());
+  return std::string(dir) + name;
+}
+bool cache_load(const std::string& src, std::vector<char>* cubin, std::string* lowered) {
+  const std::string path = cache_path(src);
+  if (path.empty()) return false;
+  FILE* f = fopen(path.c_str(), "rb");
+  if (!f) return false;
+  std::string blob;
+  char buf[65536];
+  size_t n;
+  while ((n = fread(buf, 1, sizeof buf, f)) > 0) blob.append(buf, n);
+  fclose(f);
+  // layout: source length (decimal) '\n' source lowered-name '\n' cubin
+  size_t nl = blob.find('\n');
+  if (nl == std::string::npos) return false;
+  size_t slen = strtoull(blob.substr(0, nl).c_str(), nullptr, 10);
+  if (slen != src.size() || blob.size() < nl + 1 + slen || blob.compare(nl + 1, slen, src) != 0) return false;
+  size_t p = nl + 1 + slen, nl2 = blob.find('\n', p);
+  if (nl2 == std::string::npos) return false;
+  *lowered = blob.substr(p, nl2 - p);
+  cubin->assign(blob.begin() + nl2 + 1, blob.end());
+  return !cubin->empty();
+}
+void cache_store(const std::string& src, const std::vector<char>& cubin, const std::string& lowered) {
+  const std::string path = cache_path(src);
+  if (path.empty()) return;
+  const std::string tmp = path + ".tmp" + std::to_string((long long)getpid());
+  FILE* f = fopen(tmp.c_str(), "wb");
+  if (!f) return;
+  const std::string head = std::to_string(src.size()) + "\n";
+  bool ok = fwrite(head.data(), 1, head.size(), f) == head.size() && fwrite(src.data(), 1, src.size(), f) == src.size() &&
+            fwrite(lowered.data(), 1, lowered.size(), f) == lowered.size() && fputc('\n', f) != EOF && fwrite(cubin.data(), 1, cubin.size(), f) == cubin.size();
+  ok = fclose(f) == 0 && ok;
+  if (ok) rename(tmp.c_str(), path.c_str());  // atomic: readers see a whole file or none
+  else remove(tmp.c_str());
 }
 
 }  // namespace
@@ -239,47 +289,73 @@ void jit_set_min_elems(int64_t n) {
   g_min_elems = n;
 }
 
-void jit_stats(int64_t out[4]) {
+void jit_stats(int64_t out[5]) {
   std::lock_guard<std::mutex> g(g_mu);
   out[0] = g_compiled;
   out[1] = g_hits;
   out[2] = g_failed;
   out[3] = (nvrtc().ok && driver().ok) ? 0 : 1;
+  out[4] = g_disk_hits;
 }
 
 const JitKernel* jit_chain_kernel(int device, const VmProgram& P, const char* family, int red_code, int64_t work_elems, bool* failed) {
   *failed = false;
-  std::lock_guard<std::mutex> g(g_mu);
-  if (g_min_elems < 0 || work_elems < g_min_elems) return nullptr;
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    if (g_min_elems < 0 || work_elems < g_min_elems) return nullptr;
+  }
   if (!nvrtc().ok || !driver().ok) return nullptr;
   const std::string src = jit_chain_source(P, red_code, family);
   auto key = std::make_pair(device, src);
-  auto it = g_kernels.find(key);
-  if (it != g_kernels.end()) {
-    ++g_hits;
-    return &it->second;
+  bool have_cubin = false;
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    auto it = g_kernels.find(key);
+    if (it != g_kernels.end()) {
+      ++g_hits;
+      return &it->second;  // entries are never erased: the pointer stays valid
+    }
+    have_cubin = g_cubins.count(src) != 0;
   }
   auto fail = [&](const std::string& msg) -> const JitKernel* {
+    std::lock_guard<std::mutex> g(g_mu);
     ++g_failed;
     *failed = true;
     set_last_error(RX_ERR_CUDA, "chain specialisation (" + std::string(family) + "): " + msg);
     return nullptr;
   };
-  if (!g_cubins.count(src)) {
+  if (!have_cubin) {
+    // compile without holding the lock (a tenth of a second or more); two threads may compile the same chain at the
+    // same time, the second result is dropped
     std::vector<char> cubin;
     std::string lowered, log;
-    if (!compile(src, std::string("rx::") + family, &cubin, &lowered, &log)) return fail("NVRTC: " + log);
-    g_cubins[src] = std::move(cubin);
-    g_lowered[src] = lowered;
-    ++g_compiled;
+    const bool from_disk = cache_load(src, &cubin, &lowered);
+    if (!from_disk) {
+      if (!compile(src, std::string("rx::") + family, &cubin, &lowered, &log)) return fail("NVRTC: " + log);
+      cache_store(src, cubin, lowered);
+    }
+    std::lock_guard<std::mutex> g(g_mu);
+    if (!g_cubins.count(src)) {
+      g_cubins[src] = std::move(cubin);
+      g_lowered[src] = lowered;
+      if (from_disk) ++g_disk_hits;
+      else ++g_compiled;
+    }
   }
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_kernels.find(key);
+  if (it != g_kernels.end()) return &it->second;
   const Driver& d = driver();
   CUmodule mod = nullptr;
   CUfunction fn = nullptr;
   CUresult r = d.ModuleLoadData(&mod, g_cubins[src].data());
-  if (r != CUDA_SUCCESS) return fail("cuModuleLoadData returned " + std::to_string((int)r));
-  r = d.ModuleGetFunction(&fn, mod, g_lowered[src].c_str());
-  if (r != CUDA_SUCCESS) return fail("cuModuleGetFunction(" + g_lowered[src] + ") returned " + std::to_string((int)r));
+  if (r == CUDA_SUCCESS) r = d.ModuleGetFunction(&fn, mod, g_lowered[src].c_str());
+  if (r != CUDA_SUCCESS) {
+    ++g_failed;
+    *failed = true;
+    set_last_error(RX_ERR_CUDA, "chain specialisation (" + std::string(family) + "): loading " + g_lowered[src] + " returned " + std::to_string((int)r));
+    return nullptr;
+  }
   JitKernel k;
   k.fn = (void*)fn;
   int occ = 0;

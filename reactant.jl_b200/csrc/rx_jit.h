@@ -36,8 +36,9 @@ cudaError_t jit_launch(const JitKernel* k, dim3 grid, dim3 block, void** args, c
 
 // Threshold in elements per launch (default 2^20); negative switches specialisation off.
 void jit_set_min_elems(int64_t n);
-// {kernels compiled, cache hits, compile failures, 1 if NVRTC or the driver API is unavailable}
-void jit_stats(int64_t out[4]);
+// {kernels compiled, in-memory cache hits, compile failures, 1 if NVRTC or the driver API is unavailable,
+//  kernels taken from the on-disk cache (RX_JIT_CACHE_DIR)}
+void jit_stats(int64_t out[5]);
 // Compile only (needs NVRTC but no device): size of the cubin, or -1 with the compiler log in *log.
 int64_t jit_compile_only(const VmProgram& P, int red_code, const char* family, std::string* log);
 // Generated source for P (exposed for tests and for reading).

@@ -926,8 +926,8 @@ const char* RxPlanSpecialiseCheck(const char* text, size_t len) {
 }
 
 void RxChainSpecialiser(int64_t min_elems) { rx::jit_set_min_elems(min_elems); }
-void RxChainSpecialiserStats(int64_t* out4) {
-  if (out4) rx::jit_stats(out4);
+void RxChainSpecialiserStats(int64_t* out5) {
+  if (out5) rx::jit_stats(out5);
 }
 
 void ExecutableFree(RxExecutable* e) { delete e; }

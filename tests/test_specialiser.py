@@ -121,3 +121,37 @@ module {
     after = rx.chain_specialiser_stats()
     assert after["compiled"] == before["compiled"] and after["cache_hits"] == before["cache_hits"]
     np.testing.assert_allclose(got, np.cos(x) * x, rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.gpu
+def test_compiled_chains_persist_across_processes(tmp_path):
+    """With RX_JIT_CACHE_DIR set, a second process loads the cubin of a chain instead of compiling it, and computes
+    the same bits."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = (
+        "import sys, json, numpy as np\\n"
+        f"sys.path.insert(0, {root!r})\\n"
+        "import __graft_entry__ as entry\\n"
+        "rx = entry.load_package()\\n"
+        "rx.chain_specialiser(0)\\n"
+        "t = 'tensor<4096xf32>'\\n"
+        "text = 'module {\\\\n  func.func @main(%x: ' + t + ') -> ' + t + ' {\\\\n    %0 = stablehlo.tanh %x : ' + t + '\\\\n    %1 = stablehlo.multiply %0, %x : ' + t + '\\\\n    return %1 : ' + t + '\\\\n  }\\\\n}\\\\n'\\n"
+        "x = np.linspace(-2, 2, 4096, dtype=np.float32)\\n"
+        "y = np.asarray(rx.compile(text)(rx.to_rarray(x)))\\n"
+        "print(json.dumps({'stats': rx.chain_specialiser_stats(), 'sum': float(y.astype(np.float64).sum()), 'bits': int(y.view(np.uint32).astype(np.uint64).sum())}))\\n"
+    )
+    env = dict(os.environ, RX_JIT_CACHE_DIR=str(tmp_path))
+    outs = []
+    for _ in range(2):
+        r = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs.append(json.loads(r.stdout.strip().splitlines()[-1]))
+    first, second = outs
+    assert first["stats"]["compiled"] >= 1 and first["stats"]["disk_hits"] == 0
+    assert second["stats"]["compiled"] == 0 and second["stats"]["disk_hits"] >= 1
+    assert first["bits"] == second["bits"]
+    assert any(f.startswith("rx_chain_") for f in os.listdir(tmp_path))
