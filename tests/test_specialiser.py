@@ -132,26 +132,30 @@ def test_compiled_chains_persist_across_processes(tmp_path):
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    script = (
-        "import sys, json, numpy as np\\n"
-        f"sys.path.insert(0, {root!r})\\n"
-        "import __graft_entry__ as entry\\n"
-        "rx = entry.load_package()\\n"
-        "rx.chain_specialiser(0)\\n"
-        "t = 'tensor<4096xf32>'\\n"
-        "text = 'module {\\\\n  func.func @main(%x: ' + t + ') -> ' + t + ' {\\\\n    %0 = stablehlo.tanh %x : ' + t + '\\\\n    %1 = stablehlo.multiply %0, %x : ' + t + '\\\\n    return %1 : ' + t + '\\\\n  }\\\\n}\\\\n'\\n"
-        "x = np.linspace(-2, 2, 4096, dtype=np.float32)\\n"
-        "y = np.asarray(rx.compile(text)(rx.to_rarray(x)))\\n"
-        "print(json.dumps({'stats': rx.chain_specialiser_stats(), 'sum': float(y.astype(np.float64).sum()), 'bits': int(y.view(np.uint32).astype(np.uint64).sum())}))\\n"
-    )
-    env = dict(os.environ, RX_JIT_CACHE_DIR=str(tmp_path))
+    script = tmp_path / "chain_once.py"
+    script.write_text(f"""
+import sys, json, numpy as np
+sys.path.insert(0, {root!r})
+import __graft_entry__ as entry
+rx = entry.load_package()
+rx.chain_specialiser(0)
+t = "tensor<4096xf32>"
+text = ("module {{\\n  func.func @main(%x: " + t + ") -> " + t + " {{\\n    %0 = stablehlo.tanh %x : " + t +
+        "\\n    %1 = stablehlo.multiply %0, %x : " + t + "\\n    return %1 : " + t + "\\n  }}\\n}}\\n")
+x = np.linspace(-2, 2, 4096, dtype=np.float32)
+y = np.asarray(rx.compile(text)(rx.to_rarray(x)))
+print(json.dumps({{"stats": rx.chain_specialiser_stats(), "bits": int(y.view(np.uint32).astype(np.uint64).sum())}}))
+""")
+    cache = tmp_path / "cache"
+    cache.mkdir()
+    env = dict(os.environ, RX_JIT_CACHE_DIR=str(cache))
     outs = []
     for _ in range(2):
-        r = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=600)
+        r = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=600)
         assert r.returncode == 0, r.stderr[-2000:]
         outs.append(json.loads(r.stdout.strip().splitlines()[-1]))
     first, second = outs
     assert first["stats"]["compiled"] >= 1 and first["stats"]["disk_hits"] == 0
     assert second["stats"]["compiled"] == 0 and second["stats"]["disk_hits"] >= 1
     assert first["bits"] == second["bits"]
-    assert any(f.startswith("rx_chain_") for f in os.listdir(tmp_path))
+    assert any(f.startswith("rx_chain_") for f in os.listdir(cache))
