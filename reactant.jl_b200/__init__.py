@@ -468,3 +468,29 @@ def chain_specialiser_stats() -> dict:
 
 
 from . import programs  # noqa: E402,F401
+
+
+def load_export(directory: str, function_name: str, index: int = 0, client: Client | None = None):
+    """Open a bundle written by Reactant.Serialization.export_to_enzymejax (src/serialization/EnzymeJAX.jl:94-190):
+    `{function_name}_{index}.mlir` holds the StableHLO module, `{function_name}_{index}_inputs.npz` the example
+    inputs as `arr_1 .. arr_n`, already permuted to the row-major layout of the module's argument types
+    (ext/ReactantNPZExt.jl:6-19).  Returns `(thunk, inputs)`: the compiled module and the inputs uploaded as
+    ConcreteRArrays, so that `thunk(*inputs)` runs the exported function on the GPU."""
+    import os
+    client = client or default_client()
+    base = os.path.join(directory, f"{function_name}_{index}")
+    with open(base + ".mlir") as f:
+        text = f.read()
+    thunk = compile(text, client)
+    inputs = []
+    path = base + "_inputs.npz"
+    if os.path.exists(path):
+        with np.load(path) as data:
+            keys = sorted((k for k in data.files if k.startswith("arr_")), key=lambda k: int(k.split("_")[1]))
+            if len(keys) != thunk.num_parameters:
+                raise ReactantError(12, f"{path} holds {len(keys)} arrays, the module takes {thunk.num_parameters} arguments")
+            for k in keys:
+                a = np.asarray(data[k])
+                # the file holds the boundary (row-major, reversed dims) layout; host arrays here are column-major
+                inputs.append(to_rarray(a.T if a.ndim else a, client))
+    return thunk, inputs

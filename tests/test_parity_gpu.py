@@ -376,3 +376,17 @@ def test_integer_scans_are_exact(rx, ref, client):
             text = rx.programs.scan(x.shape, axis, kind, et="i32")
             (got,), _, _ = run(rx, client, text, [x])
             assert np.array_equal(got, ref.run_module(text, [x])[0])
+
+
+def test_an_exported_bundle_runs_from_its_files(rx, ref, client, tmp_path):
+    """The file layout of Reactant.Serialization.export_to_enzymejax: <name>_0.mlir + <name>_0_inputs.npz with
+    arr_1..arr_n in the row-major layout of the module's argument types."""
+    rows, cols = 96, 40
+    text = rx.programs.logsumexp_dims1(rows, cols)
+    x = np.random.default_rng(5).standard_normal((cols, rows)).astype(np.float32)   # boundary layout of the argument
+    (tmp_path / "lse_0.mlir").write_text(text)
+    np.savez_compressed(tmp_path / "lse_0_inputs.npz", arr_1=x)
+    thunk, inputs = rx.load_export(str(tmp_path), "lse", client=client)
+    got = np.asarray(thunk(*inputs)).T
+    want = ref.run_module(text, [x])[0]
+    np.testing.assert_allclose(got, want, rtol=ref.reduction_tolerance(rows))
