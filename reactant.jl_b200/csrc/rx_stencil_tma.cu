@@ -46,12 +46,15 @@ struct StencilParams {
 // One sweep of this CTA's tiles.  `it` counts the tiles this CTA has processed since the kernel started: it
 // selects the ring stage and the mbarrier parity, so that several sweeps can share one ring.  On entry every
 // stage is drained.  Returns false if a load did not arrive within the wait limit.
+// `reverse` walks the tile list from its far end: consecutive sweeps of one launch alternate direction, so that a
+// sweep starts on the part of the arrays the previous sweep touched last, which is still in L2.
 template <bool FAST5, int TH>
 __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const StencilParams& p, const VmProgram* P, float fast_c, float* const* tile, uint64_t* bars,
-                                              int& it) {
+                                              int& it, bool reverse = false) {
   const uint32_t bytes = (uint32_t)(BOX_W * p.box_h * sizeof(float));
   const int ntiles = p.tiles_x * p.tiles_y;
   auto issue = [&](int t, int s) {
+    if (reverse) t = ntiles - 1 - t;
     int ty = t / p.tiles_x, tx = t - ty * p.tiles_x;
     mbar_expect_tx(&bars[s], bytes);
     tma_load_2d(tile[s], tmap, p.x_base + tx * p.tw, p.y_base + ty * TH, &bars[s]);
@@ -66,7 +69,8 @@ __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const Ste
     int next = t + (STAGES - 1) * (int)gridDim.x;
     if (threadIdx.x == 0 && next < ntiles) issue(next, (it + STAGES - 1) % STAGES);  // that stage was drained before the last barrier
     if (!mbar_wait(&bars[s], parity, kWaitLimit)) return false;
-    int ty = t / p.tiles_x, tx = t - ty * p.tiles_x;
+    const int tt = reverse ? ntiles - 1 - t : t;
+    int ty = tt / p.tiles_x, tx = tt - ty * p.tiles_x;
     int64_t c = (int64_t)tx * p.tw + threadIdx.x;
     int64_t r0 = (int64_t)ty * TH;
     const float* sm = tile[s] + p.x_shift + threadIdx.x;
@@ -159,6 +163,7 @@ struct LoopParams {
   float k[kMaxPhases];
   int n_phases;
   int total;          // sweeps to run = loop trip count x stencil steps per iteration
+  int alternate;      // odd sweeps walk the tiles backwards
   unsigned* counter;  // zero at launch
 };
 
@@ -179,7 +184,7 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
   int it = 0;
   for (int sweep = 0; sweep < lp.total; ++sweep) {
     const int ph = sweep % lp.n_phases;
-    if (!stencil_sweep<true, TH>(&maps.m[ph], lp.ph[ph], nullptr, lp.k[ph], tile, bars, it)) {
+    if (!stencil_sweep<true, TH>(&maps.m[ph], lp.ph[ph], nullptr, lp.k[ph], tile, bars, it, lp.alternate && (sweep & 1))) {
       if (threadIdx.x == 0) *lp.ph[0].status = 2;
       stencil_drain(bars);
       return;
@@ -357,6 +362,7 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
   }
   lp.n_phases = n;
   lp.total = (int)total;
+  lp.alternate = getenv("RX_STENCIL_ONE_WAY") ? 0 : 1;
   lp.counter = (unsigned*)(d->scratch + d->scratch_words - 2);  // the word before the reductions' ticket
   auto kern = k_stencil_loop<32>;
   static size_t attr_set[64] = {};
