@@ -311,6 +311,57 @@ for et in ("f64", "f32"):
             reduce_window_module([5, 4, 3], 3 - jdim, et), [{"dims": [5, 4, 3], "data": [float(v) for v in b60]}],
             [{"dims": [5, 4, 3], "data": out}], et, tol)
 
+# ---- test/nn/activations.jl:3-33 "Activation Functions": sumabs2(act, x) = sum(abs2, act.(x)) on
+# x = construct_test_array(Float32, 10, 10) .- 0.5f0, for act in (tanh, sigmoid, gelu).  gelu is NNlib's tanh form,
+# which Reactant emits as enzymexla.math_gelu {TANH} and lowers to tanh / multiply / add
+# (ext/ReactantNNlibExt/Implementations.jl:12-25, src/Ops.jl:4153-4175).
+import struct
+
+
+def f32(v):
+    return struct.unpack("f", struct.pack("f", float(v)))[0]
+
+
+x_act = [f32(f32(float(Fraction(k, 100))) - 0.5) for k in range(1, 101)]
+T100 = t([10, 10], "f32")
+
+
+def sumabs2_module(body_lines, last):
+    return wrap([T100], [t([], "f32")],
+                "\n".join(body_lines) + "\n"
+                f"    %sq = stablehlo.multiply {last}, {last} : {T100}\n"
+                f"    %cst = stablehlo.constant dense<0.000000e+00> : tensor<f32>\n"
+                f"    %r = stablehlo.reduce(%sq init: %cst) applies stablehlo.add across dimensions = [0, 1] : ({T100}, tensor<f32>) -> tensor<f32>\n"
+                f"    return %r : tensor<f32>")
+
+
+add("sumabs2_tanh_f32", "test/nn/activations.jl:3-33 (act = tanh)",
+    sumabs2_module([f"    %0 = stablehlo.tanh %arg0 : {T100}"], "%0"),
+    [{"dims": [10, 10], "data": x_act}], [{"dims": [], "data": [sum(math.tanh(v) ** 2 for v in x_act)]}], "f32", 5e-6)
+add("sumabs2_sigmoid_f32", "test/nn/activations.jl:3-33 (act = sigmoid)",
+    sumabs2_module([f"    %0 = stablehlo.logistic %arg0 : {T100}"], "%0"),
+    [{"dims": [10, 10], "data": x_act}], [{"dims": [], "data": [sum((1.0 / (1.0 + math.exp(-v))) ** 2 for v in x_act)]}], "f32", 5e-6)
+c0, c1 = f32(math.sqrt(2.0 / math.pi)), f32(0.044715)
+gelu_lines = [
+    f"    %k0 = stablehlo.constant dense<{c0!r}> : {T100}",
+    f"    %k1 = stablehlo.constant dense<{c1!r}> : {T100}",
+    f"    %half = stablehlo.constant dense<5.000000e-01> : {T100}",
+    f"    %one = stablehlo.constant dense<1.000000e+00> : {T100}",
+    f"    %x2 = stablehlo.multiply %arg0, %arg0 : {T100}",
+    f"    %x3 = stablehlo.multiply %x2, %arg0 : {T100}",
+    f"    %a = stablehlo.multiply %k1, %x3 : {T100}",
+    f"    %b = stablehlo.add %arg0, %a : {T100}",
+    f"    %c = stablehlo.multiply %k0, %b : {T100}",
+    f"    %th = stablehlo.tanh %c : {T100}",
+    f"    %d = stablehlo.add %one, %th : {T100}",
+    f"    %e = stablehlo.multiply %half, %arg0 : {T100}",
+    f"    %g = stablehlo.multiply %e, %d : {T100}",
+]
+add("sumabs2_gelu_tanh_f32", "test/nn/activations.jl:3-33 (act = gelu, the tanh form)",
+    sumabs2_module(gelu_lines, "%g"),
+    [{"dims": [10, 10], "data": x_act}],
+    [{"dims": [], "data": [sum((0.5 * v * (1.0 + math.tanh(c0 * (v + c1 * v ** 3)))) ** 2 for v in x_act)]}], "f32", 5e-6)
+
 with open(os.path.join(HERE, "reactant_fixtures.json"), "w") as f:
     json.dump({"generator": "tests/golden/make_fixtures.py", "cases": cases}, f, indent=1)
 print(f"wrote {len(cases)} cases")
