@@ -283,11 +283,15 @@ _UNARY = {
     "rsqrt": lambda x: 1.0 / np.sqrt(x),
     "logistic": lambda x: 1.0 / (1.0 + np.exp(-x)),
     "not": lambda x: ~x,
+    "tan": np.tan, "cbrt": np.cbrt, "round_nearest_even": np.rint,
+    "round_nearest_afz": lambda x: np.sign(x) * np.floor(np.abs(x) + 0.5),
+    "is_finite": np.isfinite,
 }
 _BINARY = {
     "add": np.add, "subtract": np.subtract, "multiply": np.multiply,
     "maximum": np.maximum, "minimum": np.minimum, "power": np.power,
     "and": np.bitwise_and, "or": np.bitwise_or, "xor": np.bitwise_xor,
+    "atan2": np.arctan2, "remainder": np.fmod,
 }
 _CMP = {"LT": np.less, "LE": np.less_equal, "GT": np.greater, "GE": np.greater_equal,
         "EQ": np.equal, "NE": np.not_equal}

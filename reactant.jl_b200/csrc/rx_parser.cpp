@@ -53,11 +53,12 @@ const UnaryName kUnary[] = {
     {"tanh", VM_TANH}, {"sqrt", VM_SQRT}, {"rsqrt", VM_RSQRT}, {"negate", VM_NEG},
     {"abs", VM_ABS}, {"log_plus_one", VM_LOG1P}, {"exponential_minus_one", VM_EXPM1},
     {"floor", VM_FLOOR}, {"ceil", VM_CEIL}, {"sign", VM_SIGN}, {"logistic", VM_LOGISTIC},
-    {"not", VM_NOT}};
+    {"not", VM_NOT}, {"tan", VM_TAN}, {"cbrt", VM_CBRT}, {"round_nearest_even", VM_RINT}, {"round_nearest_afz", VM_ROUND},
+    {"is_finite", VM_ISFINITE}};
 const UnaryName kBinary[] = {
     {"add", VM_ADD}, {"subtract", VM_SUB}, {"multiply", VM_MUL}, {"divide", VM_DIV},
     {"maximum", VM_MAX}, {"minimum", VM_MIN}, {"power", VM_POW},
-    {"and", VM_AND}, {"or", VM_OR}, {"xor", VM_XOR}};
+    {"and", VM_AND}, {"or", VM_OR}, {"xor", VM_XOR}, {"atan2", VM_ATAN2}, {"remainder", VM_REM}};
 
 struct Parser {
   const std::string& s;

@@ -87,7 +87,8 @@ VmElem elem_of(DT dt) {
 
 bool is_transcendental(int op) {
   return op == VM_SIN || op == VM_COS || op == VM_EXP || op == VM_LOG || op == VM_TANH || op == VM_POW ||
-         op == VM_LOG1P || op == VM_EXPM1 || op == VM_LOGISTIC || op == VM_DIV || op == VM_SQRT || op == VM_RSQRT;
+         op == VM_LOG1P || op == VM_EXPM1 || op == VM_LOGISTIC || op == VM_DIV || op == VM_SQRT || op == VM_RSQRT || op == VM_TAN || op == VM_CBRT ||
+         op == VM_ATAN2 || op == VM_REM;
 }
 
 // -------------------------------------------------------------------------
@@ -621,7 +622,8 @@ struct Planner {
              op == VM_AND || op == VM_OR || op == VM_XOR;
     };
     auto is_binary = [](int op) {
-      return (op >= VM_ADD && op <= VM_POW) || (op >= VM_IADD && op <= VM_IMIN) || op == VM_AND || op == VM_OR || op == VM_XOR || op == VM_FCMP || op == VM_ICMP;
+      return (op >= VM_ADD && op <= VM_POW) || (op >= VM_IADD && op <= VM_IMIN) || op == VM_AND || op == VM_OR || op == VM_XOR || op == VM_FCMP || op == VM_ICMP ||
+             op == VM_ATAN2 || op == VM_REM;
     };
     for (size_t k = 0; k < nn; ++k) {
       const VNode& n = L.nodes[k];

@@ -51,6 +51,9 @@ enum VmOp : uint8_t {
   VM_SQR,     // acc = acc * acc
   VM_RSUB,    // acc = R[b] - acc
   VM_RDIV,    // acc = R[b] / acc
+  // more f32 ops (src/Ops.jl:398-460, 536-589 emitters for tan, cbrt, round, isfinite, atan, rem)
+  VM_TAN, VM_CBRT, VM_RINT /* ties to even */, VM_ROUND /* ties away from zero */, VM_ISFINITE /* -> 0/1 */,
+  VM_ATAN2, VM_REM,
   VM_NUM_OPS
 };
 
@@ -95,7 +98,12 @@ enum VmOp : uint8_t {
   X(VM_F2I, (a != a) ? 0u : (uint32_t)(int32_t)fminf(fmaxf(truncf(a), -2147483648.f), 2147483520.f)) \
   X(VM_P2F, f2u(ua ? 1.f : 0.f))                                                               \
   X(VM_F2P, (uint32_t)(a != 0.f))                                                              \
-  X(VM_I2P, (uint32_t)(ia != 0))
+  X(VM_I2P, (uint32_t)(ia != 0))                                                              \
+  X(VM_TAN, f2u(tanf(a)))                                                                      \
+  X(VM_CBRT, f2u(cbrtf(a)))                                                                    \
+  X(VM_RINT, f2u(rintf(a)))                                                                    \
+  X(VM_ROUND, f2u(roundf(a)))                                                                  \
+  X(VM_ISFINITE, (uint32_t)(fabsf(a) <= 3.402823466e+38f))
 #define RX_VM_BINARY_OPS(X)                                                                    \
   X(VM_ADD, f2u(__fadd_rn(a, b)))                                                              \
   X(VM_SUB, f2u(__fsub_rn(a, b)))                                                              \
@@ -116,7 +124,9 @@ enum VmOp : uint8_t {
   X(VM_OR, ua | ub)                                                                            \
   X(VM_XOR, ua ^ ub)                                                                           \
   X(VM_FCMP, vm_cmp_f(cdir, a, b))                                                             \
-  X(VM_ICMP, vm_cmp_i(cdir, ia, ib))
+  X(VM_ICMP, vm_cmp_i(cdir, ia, ib))                                                          \
+  X(VM_ATAN2, f2u(atan2f(a, b)))                                                               \
+  X(VM_REM, f2u(fmodf(a, b)))
 
 enum VmCmp : uint8_t { CMP_EQ = 0, CMP_NE, CMP_LT, CMP_LE, CMP_GT, CMP_GE };
 

@@ -390,3 +390,30 @@ def test_an_exported_bundle_runs_from_its_files(rx, ref, client, tmp_path):
     got = np.asarray(thunk(*inputs)).T
     want = ref.run_module(text, [x])[0]
     np.testing.assert_allclose(got, want, rtol=ref.reduction_tolerance(rows))
+
+
+def test_more_elementwise_ops(rx, ref, client):
+    """tan, cbrt, both roundings, is_finite, atan2, remainder (src/Ops.jl:398-460, 536-589)."""
+    n = 4099
+    t, ti = f"tensor<{n}xf32>", f"tensor<{n}xi1>"
+    text = module([t, t], [t, t, ti], f"""    %0 = stablehlo.tan %arg0 : {t}
+    %1 = stablehlo.cbrt %arg1 : {t}
+    %2 = stablehlo.add %0, %1 : {t}
+    %3 = stablehlo.round_nearest_even %arg1 : {t}
+    %4 = stablehlo.round_nearest_afz %arg1 : {t}
+    %5 = stablehlo.subtract %3, %4 : {t}
+    %6 = stablehlo.atan2 %arg0, %arg1 : {t}
+    %7 = stablehlo.remainder %arg1, %arg0 : {t}
+    %8 = stablehlo.add %6, %7 : {t}
+    %9 = stablehlo.add %8, %5 : {t}
+    %10 = stablehlo.divide %arg0, %5 : {t}
+    %11 = stablehlo.is_finite %10 : ({t}) -> {ti}
+    return %2, %9, %11 : {t}, {t}, {ti}""")
+    rng = np.random.default_rng(3)
+    x = rng.uniform(-1.4, 1.4, n).astype(np.float32)
+    y = (rng.integers(-40, 40, n) * 0.25).astype(np.float32)   # quarters: exercises both tie rules exactly
+    got, _, _ = run(rx, client, text, [x, y])
+    want = ref.run_module(text, [x, y])
+    np.testing.assert_allclose(got[0], want[0], rtol=4e-6, atol=1e-6)
+    np.testing.assert_allclose(got[1], want[1], rtol=4e-6, atol=2e-6)
+    assert np.array_equal(got[2], want[2])
