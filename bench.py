@@ -257,6 +257,7 @@ def time_resident(rx, client, wl, steps, warmup, rotate, dist, spans=False):
     e0 = dev.record_event()
     for k in range(steps):
         r = thunk(*sets[(warmup + k) % rotate])
+    dev.join_streams()  # gradient all-reduces of the last step (communication stream) end inside the timed region
     e1 = dev.record_event()
     e1.synchronize()
     ms = e0.elapsed_ms(e1)

@@ -228,6 +228,10 @@ void RxEventSynchronize(RxEvent* ev);
 float RxEventElapsedMs(RxEvent* start, RxEvent* stop);
 void RxEventFree(RxEvent* ev);
 void RxDeviceSynchronize(RxDevice* device);
+/* Gradient all-reduces run on a second stream per device and may still be in flight when an execution
+ * returns (its futures and the next user of each result wait for them).  This makes the device's compute
+ * stream wait for everything queued on that stream so far, so that an event recorded afterwards covers it. */
+void RxDeviceJoinStreams(RxDevice* device);
 uint64_t RxDeviceKernelLaunches(RxDevice* device);   /* kernels launched so far on this device */
 /* When enabled, every step of every execute on this device is bracketed by
  * events; RxDeviceProfileJson returns {"<step kind>": {"launches": n, "ms": t}, ...}

@@ -70,6 +70,11 @@ class Device:
         lib().RxDeviceSynchronize(self.handle)
         check()
 
+    def join_streams(self):
+        """Make the compute stream wait for the all-reduces queued on the communication stream so far."""
+        lib().RxDeviceJoinStreams(self.handle)
+        check()
+
     def kernel_launches(self) -> int:
         return int(lib().RxDeviceKernelLaunches(self.handle))
 

@@ -99,6 +99,7 @@ PROTOTYPES = {
     "RxEventElapsedMs": (C.c_float, [P, P]),
     "RxEventFree": (None, [P]),
     "RxDeviceSynchronize": (None, [P]),
+    "RxDeviceJoinStreams": (None, [P]),
     "RxDeviceKernelLaunches": (C.c_uint64, [P]),
     "RxDeviceSetProfiling": (None, [P, C.c_int]),
     "RxDeviceProfileJson": (P, [P]),

@@ -455,6 +455,7 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
       const Slot& sl = p.slots[s];
       if (sl.kind == SlotK::Arg) {
         RxBuffer* b = args[k * nargs_per_dev + sl.arg_index];
+        b->st->make_ready();
         if (sl.writable && !(donatable && donatable[sl.arg_index])) {
           // the plan updates this argument in place but the caller keeps it: work on a private copy
           size_t bytes = (size_t)sl.bytes();
@@ -483,9 +484,32 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
     }
   }
   run_steps(ex, p.steps, runs);
-  for (auto& r : runs) {
+  // All-reduces still in flight on the communication stream: a result keeps the event (its future and its next user
+  // wait for it), so the compute stream is free to start the next execution; anything else is joined now.
+  std::vector<std::map<int, std::shared_ptr<EventState>>> late(devs.size());  // [device][slot] -> completion of a result's all-reduce
+  for (size_t k = 0; k < devs.size(); ++k) {
+    DevRun& r = runs[k];
     CK(cudaSetDevice(r.dev->ordinal));
-    join_all_pending(r);  // results are complete on the compute stream
+    for (const ResultBinding& rb : p.results) {
+      auto it = r.pending.find(rb.slot);
+      if (it == r.pending.end() || late[k].count(rb.slot)) continue;
+      auto es = std::make_shared<EventState>();
+      es->dev = r.dev;
+      es->keep = r.dev->shared_from_this();
+      es->ev = it->second;              // recorded on the communication stream after the all-reduce
+      late[k][rb.slot] = es;
+      cudaEvent_t again;               // a second event for the storage itself (the future may be freed first)
+      CK(cudaEventCreateWithFlags(&again, cudaEventDisableTiming));
+      CK(cudaEventRecord(again, r.dev->comm_stream));
+      {
+        Storage& st = *r.table[rb.slot];
+        std::lock_guard<std::mutex> g(st.pending_mu);
+        if (st.pending) cudaEventDestroy(st.pending);
+        st.pending = again;
+      }
+      r.pending.erase(it);
+    }
+    join_all_pending(r);
   }
   for (size_t k = 0; k < devs.size(); ++k) {
     RxDevice* d = devs[k];
@@ -505,7 +529,8 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
       results[k * num_results + j] = b;
       if (future_results) {
         auto* f = new RxFuture();
-        f->state = es;
+        auto lt = late[k].find(rb.slot);
+        f->state = lt != late[k].end() ? lt->second : es;
         future_results[k * num_results + j] = f;
       }
     }
@@ -621,6 +646,7 @@ void FreeClient(RxClient* client) {
   for (auto& d : client->devices) {
     cudaSetDevice(d->ordinal);
     cudaStreamSynchronize(d->stream);
+    if (d->comm_stream) cudaStreamSynchronize(d->comm_stream);
     d->trim();
     if (d->scratch) cudaFree(d->scratch);
     if (d->flush_buf) cudaFree(d->flush_buf);
@@ -760,6 +786,7 @@ void BufferToHost(RxBuffer* b, void* dst) {
   size_t bytes = b->bytes();
   if (bytes) {
     CK(cudaSetDevice(b->dev->ordinal));
+    b->st->make_ready();
     CK(cudaMemcpyAsync(dst, b->st->ptr, bytes, cudaMemcpyDeviceToHost, b->dev->stream));
     CK(cudaStreamSynchronize(b->dev->stream));
     check_device_status(b->dev);
@@ -770,6 +797,11 @@ void BufferToHost(RxBuffer* b, void* dst) {
 void* UnsafeBufferPointer(RxBuffer* b) {
   API_BEGIN
   live(b);
+  if (b->st->pending) {  // the caller will use the pointer outside this library's streams
+    CK(cudaSetDevice(b->dev->ordinal));
+    b->st->make_ready();
+    CK(cudaStreamSynchronize(b->dev->stream));
+  }
   return b->st->ptr;
   API_END(nullptr)
 }
@@ -782,6 +814,7 @@ RxBuffer* CopyBufferToDevice(RxBuffer* b, RxDevice* dst) {
   if (bytes) {
     // order after the producer, then copy on the destination's stream
     CK(cudaSetDevice(b->dev->ordinal));
+    b->st->make_ready();
     cudaEvent_t ev;
     CK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
     CK(cudaEventRecord(ev, b->dev->stream));
@@ -800,6 +833,7 @@ void CopyToBuffer(RxClient*, RxBuffer* b, void* data, size_t offset, size_t size
   live(b);
   if (offset + size > b->bytes()) throw Error(RX_ERR_ARG, "copy range exceeds the buffer");
   CK(cudaSetDevice(b->dev->ordinal));
+  b->st->make_ready();
   CK(cudaMemcpyAsync((char*)b->st->ptr + offset, data, size, cudaMemcpyHostToDevice, b->dev->stream));
   CK(cudaStreamSynchronize(b->dev->stream));
   if (bufferP) *bufferP = b;
@@ -810,6 +844,7 @@ void CopyFromBuffer(RxClient*, RxBuffer* b, void* data, size_t offset, size_t si
   live(b);
   if (offset + size > b->bytes()) throw Error(RX_ERR_ARG, "copy range exceeds the buffer");
   CK(cudaSetDevice(b->dev->ordinal));
+  b->st->make_ready();
   CK(cudaMemcpyAsync(data, (char*)b->st->ptr + offset, size, cudaMemcpyDeviceToHost, b->dev->stream));
   CK(cudaStreamSynchronize(b->dev->stream));
   if (bufferP) *bufferP = b;
@@ -1022,6 +1057,19 @@ void RxDeviceSynchronize(RxDevice* d) {
   API_BEGIN
   CK(cudaSetDevice(d->ordinal));
   CK(cudaStreamSynchronize(d->stream));
+  if (d->comm_stream) CK(cudaStreamSynchronize(d->comm_stream));
+  API_END_VOID
+}
+void RxDeviceJoinStreams(RxDevice* d) {
+  API_BEGIN
+  if (d->comm_stream) {
+    CK(cudaSetDevice(d->ordinal));
+    cudaEvent_t ev;
+    CK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    CK(cudaEventRecord(ev, d->comm_stream));
+    CK(cudaStreamWaitEvent(d->stream, ev, 0));
+    cudaEventDestroy(ev);
+  }
   API_END_VOID
 }
 uint64_t RxDeviceKernelLaunches(RxDevice* d) { return d->launches; }

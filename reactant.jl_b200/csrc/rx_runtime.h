@@ -81,8 +81,29 @@ struct Storage {
   std::shared_ptr<RxDevice> keep;
   void* ptr;
   size_t bytes;
+  // Set when the last writer of this block ran on the device's communication stream (an all-reduce that was still
+  // in flight when the execution that produced it returned): whoever touches the block next on the compute stream
+  // -- the next execution, a copy to the host, or the release of the memory -- waits for this event first.
+  std::mutex pending_mu;
+  cudaEvent_t pending = nullptr;
   Storage(RxDevice* d, void* p, size_t b) : dev(d), keep(d->shared_from_this()), ptr(p), bytes(b) {}
-  ~Storage() { dev->release(ptr, bytes); }
+  void make_ready() {  // call with the owning device current
+    std::lock_guard<std::mutex> g(pending_mu);
+    if (!pending) return;
+    if (dev->stream) cudaStreamWaitEvent(dev->stream, pending, 0);
+    cudaEventDestroy(pending);
+    pending = nullptr;
+  }
+  ~Storage() {
+    if (pending) {
+      int cur = 0;
+      cudaGetDevice(&cur);
+      cudaSetDevice(dev->ordinal);
+      make_ready();  // the pool hands the block out again in compute-stream order
+      cudaSetDevice(cur);
+    }
+    dev->release(ptr, bytes);
+  }
 };
 
 struct RxBuffer {
