@@ -17,10 +17,8 @@
 
 #ifdef RX_CHAIN_SPECIALISED
 #define RX_CHAIN_UNROLL _Pragma("unroll")
-#define RX_CHAIN_UNROLL4 _Pragma("unroll 4")  // row loops: several rows' loads in flight per thread
 #else
 #define RX_CHAIN_UNROLL
-#define RX_CHAIN_UNROLL4
 #endif
 
 namespace rx {
@@ -269,7 +267,7 @@ __global__ void __launch_bounds__(kThreads) k_reduce_col_vec(const __grid_consta
   int64_t idx0[kMaxRank] = {0, 0, 0, 0};
   uint32_t acc[4];
   for (int v = 0; v < 4; ++v) acc[v] = red_identity(code);
-  RX_CHAIN_UNROLL4 for (int64_t r = r0; r < r1; ++r) {
+  for (int64_t r = r0; r < r1; ++r) {
     __align__(16) uint32_t R[C::kRegs][4];
     RX_CHAIN_UNROLL for (int k = 0; k < C::n_leaves(P); ++k) load4_rowvec(C::leaf(P, k), r, b4, 1, 2, R[C::leaf_reg(P, k)]);
     C::template exec<4>(P, R, idx0);

@@ -82,11 +82,8 @@ __global__ void __launch_bounds__(kThreads) k_reduce_col_finish(const uint32_t* 
   const int64_t o = blockIdx.x / col_blocks;
   const int64_t b = (blockIdx.x - o * col_blocks) * 32 + lane;
   uint32_t acc = red_identity(code);
-  if (b < inner) {
-    // the additions stay in split order; unrolling lets the (independent) loads of several splits be in flight together
-#pragma unroll 8
-    for (int s = w; s < nsplit; s += kThreads / 32) acc = red_combine(code, acc, __ldg(partials + (o * nsplit + s) * inner + b));
-  }
+  if (b < inner)
+    for (int s = w; s < nsplit; s += kThreads / 32) acc = red_combine(code, acc, partials[(o * nsplit + s) * inner + b]);
   sm[w][lane] = acc;
   __syncthreads();
   if (w == 0 && b < inner) {
