@@ -443,6 +443,13 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
     throw Error(RX_ERR_ARG, "Error: results.size()=" + std::to_string(p.results.size()) + " does not match num_results=" + std::to_string(num_results));
   if (p.num_partitions > 1 && (int64_t)devs.size() * ex->client->num_nodes != p.num_partitions)
     throw Error(RX_ERR_ARG, "executable is partitioned over " + std::to_string(p.num_partitions) + " devices, launch covers " + std::to_string(devs.size() * ex->client->num_nodes));
+  // Thunks may be called from any host thread (Julia tasks): serialise the enqueueing per device, taking the
+  // devices in a fixed order so that two multi-device executions cannot deadlock.
+  std::vector<RxDevice*> order(devs.begin(), devs.end());
+  std::sort(order.begin(), order.end(), [](RxDevice* a, RxDevice* b) { return a->ordinal < b->ordinal; });
+  order.erase(std::unique(order.begin(), order.end()), order.end());
+  std::vector<std::unique_lock<std::mutex>> held;
+  for (RxDevice* d : order) held.emplace_back(d->exec_mu);
   std::vector<DevRun> runs(devs.size());
   for (size_t k = 0; k < devs.size(); ++k) {
     RxDevice* d = devs[k];

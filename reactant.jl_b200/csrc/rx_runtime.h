@@ -36,6 +36,9 @@ struct RxDevice : std::enable_shared_from_this<RxDevice> {
   cudaStream_t comm_stream = nullptr;  // vector all-reduces run here, ordered against `stream` by events
   int sm_count = 148;
   size_t total_mem = 0;
+  // One execution at a time enqueues on a device: launches of different host threads must not interleave (they
+  // share the reduction scratch in stream order) and the launch-side tables below are not otherwise protected.
+  std::mutex exec_mu;
   // memory pool (exact-size free lists, stream ordered on `stream`)
   std::mutex mu;
   std::map<size_t, std::vector<void*>> pool;

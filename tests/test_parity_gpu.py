@@ -417,3 +417,39 @@ def test_more_elementwise_ops(rx, ref, client):
     np.testing.assert_allclose(got[0], want[0], rtol=4e-6, atol=1e-6)
     np.testing.assert_allclose(got[1], want[1], rtol=4e-6, atol=2e-6)
     assert np.array_equal(got[2], want[2])
+
+
+def test_thunks_called_from_several_host_threads(rx, ref, client):
+    """Julia tasks may call compiled functions from any OS thread (different Thunks concurrently, and finalizers at any
+    time): executions on one device are serialised inside the library and every call returns its own result."""
+    import threading
+    n = 1 << 16
+    rng = np.random.default_rng(11)
+    x = rng.uniform(-3, 3, n).astype(np.float32)
+    y = rng.uniform(-3, 3, n).astype(np.float32)
+    f_sum = rx.compile(rx.programs.sinsum_add(n), client)
+    rows, cols = 512, 96
+    a = rng.standard_normal((rows, cols)).astype(np.float32)
+    f_lse = rx.compile(rx.programs.logsumexp_dims1(rows, cols), client)
+    want_sum = float(f_sum(rx.to_rarray(x, client), rx.to_rarray(y, client)))
+    want_lse = np.asarray(f_lse(rx.to_rarray(a, client)))
+    errors = []
+
+    def worker(kind):
+        try:
+            for _ in range(40):
+                if kind == 0:
+                    got = float(f_sum(rx.to_rarray(x, client), rx.to_rarray(y, client)))
+                    assert got == want_sum, (got, want_sum)       # deterministic reduction: same bits every time
+                else:
+                    got = np.asarray(f_lse(rx.to_rarray(a, client)))
+                    assert np.array_equal(got, want_lse)
+        except Exception as e:  # noqa: BLE001
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(k % 2,)) for k in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors[:3]
