@@ -162,8 +162,9 @@ bool compile(const std::string& src, const std::string& name_expr, std::vector<c
 
 // Optional on-disk cache of compiled chains (RX_JIT_CACHE_DIR=<existing directory>): the analogue, for this
 // engine's only compiled artefact, of Reactant's persistent compile cache (src/PersistentCompileCache.jl).
-// A file holds the lowered kernel name, a newline, and the cubin; its name is a 64-bit FNV-1a hash of the
-// generated source together with the source length, and the source itself is stored and compared on load.
+// A file holds the source length, a newline, the generated source, the lowered kernel name, a newline, and the
+// cubin; its name is a 64-bit FNV-1a hash of the source together with its length, and the stored source is
+// compared on load, so a hash collision cannot hand out the wrong kernel.
 std::string cache_path(const std::string& src) {
   const char* dir = getenv("RX_JIT_CACHE_DIR");
   if (!dir || !*dir) return "";
