@@ -16,9 +16,19 @@ enum RedCode : int { R_FADD = 0, R_FMAX, R_FMIN, R_FMUL, R_IADD, R_IMAX, R_IMIN,
 __device__ __forceinline__ float u2f(uint32_t u) { return __uint_as_float(u); }
 __device__ __forceinline__ uint32_t f2u(float f) { return __float_as_uint(f); }
 
-// StableHLO maximum/minimum propagate NaN.
-__device__ __forceinline__ float nan_max(float a, float b) { return (a != a) ? a : ((b != b) ? b : fmaxf(a, b)); }
-__device__ __forceinline__ float nan_min(float a, float b) { return (a != a) ? a : ((b != b) ? b : fminf(a, b)); }
+// NaN-propagating maximum / minimum (stablehlo.maximum / minimum semantics) as the single hardware instruction.
+// Written as PTX rather than as selects around fmaxf: nested select forms of min(min(x, c), x * c) crashed the
+// run-time compiler's optimiser, and the instruction is what the selects should become anyway.
+__device__ __forceinline__ float nan_max(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float nan_min(float a, float b) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
 
 __device__ __forceinline__ uint32_t red_combine(int code, uint32_t a, uint32_t b) {
   switch (code) {

@@ -137,6 +137,7 @@ bool compile(const std::string& src, const std::string& name_expr, std::vector<c
   // RX_JIT_VERBOSE=1 prints each generated source and ptxas' resource summary to stderr
   static const bool verbose = getenv("RX_JIT_VERBOSE") && atoi(getenv("RX_JIT_VERBOSE")) > 0;
   const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "--ptxas-options=-v"};
+  if (verbose) fprintf(stderr, "---- %s\n%s\n", name_expr.c_str(), src.c_str());
   int rc = n.CompileProgram(prog, verbose ? 3 : 2, opts);
   size_t ls = 0;
   n.GetProgramLogSize(prog, &ls);
@@ -144,7 +145,7 @@ bool compile(const std::string& src, const std::string& name_expr, std::vector<c
     log->resize(ls);
     n.GetProgramLog(prog, &(*log)[0]);
   }
-  if (verbose) fprintf(stderr, "---- %s\n%s\n%s\n", name_expr.c_str(), src.c_str(), log->c_str());
+  if (verbose) fprintf(stderr, "%s\n", log->c_str());
   bool ok = rc == 0;
   if (ok) {
     size_t cs = 0;

@@ -133,7 +133,7 @@ def gen_case(seed):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("seed", range(int(os.environ.get("RX_FUZZ_CASES", "60"))))
+@pytest.mark.parametrize("seed", range(int(os.environ.get("RX_FUZZ_FIRST", "0")), int(os.environ.get("RX_FUZZ_FIRST", "0")) + int(os.environ.get("RX_FUZZ_CASES", "60"))))
 def test_random_fusion_groups(seed):
     oracle, _ = entry.load_oracle()
     text, inputs, kinds, scale, n_ops = gen_case(seed)

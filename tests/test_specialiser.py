@@ -31,8 +31,26 @@ module {
 """
 
 
+# minimum of a minimum and a product of the same operand: as nested selects around fminf this shape crashed the
+# run-time compiler, which took the calling process with it
+NESTED_MIN_MODULE = """
+module {
+  func.func @main(%v: tensor<64xf32>) -> tensor<64x130x3xf32> {
+    %bc = stablehlo.broadcast_in_dim %v, dims = [0] : (tensor<64xf32>) -> tensor<64x130x3xf32>
+    %k = stablehlo.constant dense<1.5845897197723389> : tensor<64x130x3xf32>
+    %0 = stablehlo.multiply %bc, %k : tensor<64x130x3xf32>
+    %1 = stablehlo.minimum %k, %bc : tensor<64x130x3xf32>
+    %2 = stablehlo.minimum %0, %1 : tensor<64x130x3xf32>
+    %3 = stablehlo.abs %2 : tensor<64x130x3xf32>
+    return %3 : tensor<64x130x3xf32>
+  }
+}
+"""
+
+
 def _programs():
     return {
+        "nested_min": NESTED_MIN_MODULE,
         "sinsum_add": P.sinsum_add(1 << 12),
         "logsumexp_raw": P.logsumexp_dims1(64, 256, raw=True),
         "jacobi_dus": P.jacobi2d(64, 3),
