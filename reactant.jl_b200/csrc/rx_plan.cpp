@@ -1023,6 +1023,12 @@ struct Planner {
   void maybe_spill(int v) {
     // Values with several consumers are computed once when recomputation would be costly.
     ExprP e = env[v];
+    // A replicated value that does not vary along some dim may later meet a tensor sharded along that dim, where
+    // each device evaluates it on its own index range; a materialised copy would no longer show that it is
+    // invariant, so such values stay expressions and are recomputed.
+    if (nparts > 1 && shard[v] < 0)
+      for (size_t d = 0; d < e->shape.size(); ++d)
+        if (e->shape[d] > 1 && invariant_along(e, (int)d)) return;
     if (uses[v] > 1 && e->k != Expr::Leaf && !is_splat(e) && prod(e->shape) > 1024 && e->cost > 12)
       env[v] = materialised(e, "shared value " + m.values[v].name);
   }

@@ -80,7 +80,7 @@ def gen_case(seed):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("seed", range(int(os.environ.get("RX_FUZZ_CASES", "40"))))
+@pytest.mark.parametrize("seed", range(int(os.environ.get("RX_FUZZ_FIRST", "0")), int(os.environ.get("RX_FUZZ_FIRST", "0")) + int(os.environ.get("RX_FUZZ_CASES", "40"))))
 def test_random_sharded_fusion_groups(seed):
     if _ngpu() < NDEV:
         pytest.skip("needs 2 GPUs")

@@ -163,3 +163,29 @@ def test_reductions_over_non_adjacent_or_non_mergeable_dims_are_staged(rx):
 """
     kinds = [s["kind"] for s in rx.plan_describe(text)["steps"]]
     assert kinds.count("reduce_row") + kinds.count("reduce_col") + kinds.count("reduce_full") >= 3, kinds
+
+
+def test_replicated_broadcast_chain_with_several_consumers_still_meets_a_sharded_operand(rx):
+    # %v2 is long and used three times; materialising it would hide that it does not vary along the sharded dim
+    text = """
+module attributes {mhlo.num_partitions = 2 : i64, mhlo.num_replicas = 1 : i64} {
+  sdy.mesh @mesh = <["x"=2]>
+  func.func @main(%arg0: tensor<516x260xf32> {sdy.sharding = #sdy.sharding<@mesh, [{"x"}, {}]>}, %arg1: tensor<260xf32> {sdy.sharding = #sdy.sharding<@mesh, [{}]>}) -> (tensor<516x260xf32> {sdy.sharding = #sdy.sharding<@mesh, [{"x"}, {}]>}) {
+    %bc = stablehlo.broadcast_in_dim %arg1, dims = [1] : (tensor<260xf32>) -> tensor<516x260xf32>
+    %t0 = stablehlo.tanh %bc : tensor<516x260xf32>
+    %v0 = stablehlo.multiply %bc, %t0 : tensor<516x260xf32>
+    %v1 = stablehlo.maximum %v0, %bc : tensor<516x260xf32>
+    %t2 = stablehlo.tanh %bc : tensor<516x260xf32>
+    %v2 = stablehlo.multiply %v1, %t2 : tensor<516x260xf32>
+    %t3 = stablehlo.tanh %v2 : tensor<516x260xf32>
+    %v3 = stablehlo.multiply %v2, %t3 : tensor<516x260xf32>
+    %t5 = stablehlo.tanh %arg0 : tensor<516x260xf32>
+    %v5 = stablehlo.multiply %v3, %t5 : tensor<516x260xf32>
+    %v6 = stablehlo.subtract %v5, %v2 : tensor<516x260xf32>
+    return %v6 : tensor<516x260xf32>
+  }
+}
+"""
+    d = rx.plan_describe(text)
+    assert [s["kind"] for s in d["steps"]] == ["map"], d["steps"]
+    assert d["steps"][0]["dims"] == [258, 260] or d["steps"][0]["dims"] == [258 * 260], d["steps"]
