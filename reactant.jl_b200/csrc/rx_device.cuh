@@ -36,10 +36,10 @@ __device__ __forceinline__ uint32_t red_combine(int code, uint32_t a, uint32_t b
     case R_FMAX: return f2u(nan_max(u2f(a), u2f(b)));
     case R_FMIN: return f2u(nan_min(u2f(a), u2f(b)));
     case R_FMUL: return f2u(u2f(a) * u2f(b));
-    case R_IADD: return (uint32_t)((int32_t)a + (int32_t)b);
+    case R_IADD: return a + b;  // two's-complement wrap-around
     case R_IMAX: return (uint32_t)max((int32_t)a, (int32_t)b);
     case R_IMIN: return (uint32_t)min((int32_t)a, (int32_t)b);
-    case R_IMUL: return (uint32_t)((int32_t)a * (int32_t)b);
+    case R_IMUL: return a * b;
     case R_OR: return a | b;
     default: return a & b;
   }

@@ -90,8 +90,8 @@ enum VmOp : uint8_t {
   X(VM_RDIVI, f2u(fimm / a))                                                                   \
   X(VM_MAXI, f2u(nan_max(a, fimm)))                                                            \
   X(VM_MINI, f2u(nan_min(a, fimm)))                                                            \
-  X(VM_INEG, (uint32_t)(-ia))                                                                  \
-  X(VM_IABS, (uint32_t)abs(ia))                                                                \
+  X(VM_INEG, 0u - ua)                                                                  \
+  X(VM_IABS, ia < 0 ? 0u - ua : ua)                                                                \
   X(VM_NOT, ~ua)                                                                               \
   X(VM_LNOT, ua ? 0u : 1u)                                                                     \
   X(VM_I2F, f2u((float)ia))                                                                    \
@@ -114,9 +114,9 @@ enum VmOp : uint8_t {
   X(VM_MAX, f2u(nan_max(a, b)))                                                                \
   X(VM_MIN, f2u(nan_min(a, b)))                                                                \
   X(VM_POW, f2u(powf(a, b)))                                                                   \
-  X(VM_IADD, (uint32_t)(ia + ib))                                                              \
-  X(VM_ISUB, (uint32_t)(ia - ib))                                                              \
-  X(VM_IMUL, (uint32_t)(ia * ib))                                                              \
+  X(VM_IADD, ua + ub)                                                              \
+  X(VM_ISUB, ua - ub)                                                              \
+  X(VM_IMUL, ua * ub)                                                              \
   X(VM_IDIV, ib == 0 ? 0xFFFFFFFFu : ((ia == INT32_MIN && ib == -1) ? (uint32_t)INT32_MIN : (uint32_t)(ia / ib))) \
   X(VM_IMAX, (uint32_t)max(ia, ib))                                                            \
   X(VM_IMIN, (uint32_t)min(ia, ib))                                                            \
