@@ -261,7 +261,12 @@ std::string jit_chain_source(const VmProgram& P, int red_code, const char* famil
     } else if (in.op == VM_MULADD_C) {
       s += "      acc = f2u(__fadd_rn(__fmul_rn(u2f(" + rb + "), u2f(" + rc + ")), u2f(acc)));\n";
     } else if (T.unary[in.op]) {
-      s += "      { const uint32_t ua = acc, imm = " + hex32(in.imm) + "; const float a = u2f(ua), fimm = u2f(imm); const int32_t ia = (int32_t)ua; acc = (" +
+      // A constant that starts a value is read from the program (a kernel parameter), not written as a literal:
+      // with a literal the compiler evaluates tanhf(c), expf(c) ... itself, and its value can differ in the last
+      // bit from the one the device code computes in the interpreter.  Immediates of the exactly rounded ops
+      // (add, multiply, divide, min, max) stay literals.
+      const std::string immv = in.op == VM_CONST ? "P.ins[" + I(k) + "].imm" : hex32(in.imm);
+      s += "      { const uint32_t ua = acc, imm = " + immv + "; const float a = u2f(ua), fimm = u2f(imm); const int32_t ia = (int32_t)ua; acc = (" +
            T.unary[in.op] + "); }\n";
     } else if (T.binary[in.op]) {
       s += "      { const uint32_t ua = acc, ub = " + rb + "; const float a = u2f(ua), b = u2f(ub); const int32_t ia = (int32_t)ua, ib = (int32_t)ub; const int cdir = " +

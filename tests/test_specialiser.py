@@ -120,6 +120,57 @@ def test_specialised_kernels_match_the_interpreter_bit_for_bit():
     np.testing.assert_allclose(outs["specialised"][2], want[2], rtol=tol)
 
 
+# Two chains where a constant written as a literal let the run-time compiler change the result: it evaluated
+# tanh(c) itself (one ulp away from the device's tanhf), and it strength-reduced x * -256 under a signed minimum to
+# the minimum of x * 256.  Constants are therefore read from the program at run time.
+CONST_TANH_MODULE = """
+module {
+  func.func @main(%x: tensor<130x1024xf32>) -> tensor<130x1024xf32> {
+    %k = stablehlo.constant dense<0.7570777535438538> : tensor<130x1024xf32>
+    %t = stablehlo.tanh %k : tensor<130x1024xf32>
+    %0 = stablehlo.add %x, %t : tensor<130x1024xf32>
+    %1 = stablehlo.minimum %t, %0 : tensor<130x1024xf32>
+    return %1 : tensor<130x1024xf32>
+  }
+}
+"""
+CONST_IMUL_MIN_MODULE = """
+module {
+  func.func @main(%x: tensor<128x16x16xi32>) -> tensor<i32> {
+    %k = stablehlo.constant dense<-256> : tensor<128x16x16xi32>
+    %m = stablehlo.multiply %x, %k : tensor<128x16x16xi32>
+    %z = stablehlo.constant dense<2147483647> : tensor<i32>
+    %r = stablehlo.reduce(%m init: %z) applies stablehlo.minimum across dimensions = [0, 1, 2] : (tensor<128x16x16xi32>, tensor<i32>) -> tensor<i32>
+    return %r : tensor<i32>
+  }
+}
+"""
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["tanh_of_constant", "multiply_by_constant_under_min"])
+def test_constants_do_not_let_the_compiler_change_results(name):
+    rng = np.random.default_rng(11)
+    if name == "tanh_of_constant":
+        text, x = CONST_TANH_MODULE, rng.uniform(-1.5, 1.5, size=(130, 1024)).astype(np.float32)
+    else:
+        text = CONST_IMUL_MIN_MODULE
+        x = rng.integers(-60, 60, size=(128, 16, 16)).astype(np.int32)
+        x.ravel()[rng.integers(0, x.size, size=400)] = rng.choice(np.array([65535, -65536, 2**31 - 1, -(2**31), 2**30], dtype=np.int64), size=400).astype(np.int32)
+    outs = []
+    try:
+        for threshold in (-1, 0):
+            rx.chain_specialiser(threshold)
+            r = rx.compile(text)(rx.to_rarray(np.ascontiguousarray(x.T)))
+            outs.append(np.ascontiguousarray(np.asarray(r).T))
+    finally:
+        rx.chain_specialiser(1 << 20)
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    if name != "tanh_of_constant":
+        want = (x.astype(np.int64) * -256 & 0xFFFFFFFF).astype(np.uint32).view(np.int32).min()
+        assert int(outs[1]) == int(want)
+
+
 @pytest.mark.gpu
 def test_default_threshold_keeps_small_launches_on_the_interpreter():
     rx.chain_specialiser(1 << 20)
