@@ -30,6 +30,21 @@ __device__ __forceinline__ float nan_min(float a, float b) {
   return r;
 }
 
+// Signed 32-bit minimum / maximum as the two-input PTX instruction.  Left to the compiler, min(acc, min(-x, t))
+// in a reduction loop became a three-input minimum for sm_100a that returned wrong values (the negation of one
+// operand was lost; reproduced in a stand-alone kernel with CUDA 12.9).  The asm forms keep every min / max a
+// two-input operation.
+__device__ __forceinline__ int32_t smin32(int32_t a, int32_t b) {
+  int32_t r;
+  asm("min.s32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ int32_t smax32(int32_t a, int32_t b) {
+  int32_t r;
+  asm("max.s32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 __device__ __forceinline__ uint32_t red_combine(int code, uint32_t a, uint32_t b) {
   switch (code) {
     case R_FADD: return f2u(u2f(a) + u2f(b));
@@ -37,8 +52,8 @@ __device__ __forceinline__ uint32_t red_combine(int code, uint32_t a, uint32_t b
     case R_FMIN: return f2u(nan_min(u2f(a), u2f(b)));
     case R_FMUL: return f2u(u2f(a) * u2f(b));
     case R_IADD: return a + b;  // two's-complement wrap-around
-    case R_IMAX: return (uint32_t)max((int32_t)a, (int32_t)b);
-    case R_IMIN: return (uint32_t)min((int32_t)a, (int32_t)b);
+    case R_IMAX: return (uint32_t)smax32((int32_t)a, (int32_t)b);
+    case R_IMIN: return (uint32_t)smin32((int32_t)a, (int32_t)b);
     case R_IMUL: return a * b;
     case R_OR: return a | b;
     default: return a & b;

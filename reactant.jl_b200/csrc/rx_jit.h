@@ -9,7 +9,11 @@
 // (src/Compiler.jl:1402-1480 hands the module to XLA.compile, which emits PTX per fusion).
 //
 // Specialisation never changes results: generated code pastes the op expressions of
-// RX_VM_UNARY_OPS / RX_VM_BINARY_OPS (rx_vm.h) that the interpreter itself is built from.
+// RX_VM_UNARY_OPS / RX_VM_BINARY_OPS (rx_vm.h) that the interpreter itself is built from,
+// and a constant that starts a value is read from the program at run time rather than
+// written as a literal, so the compiler cannot evaluate tanhf(c) and the like on its own
+// (its value may differ in the last bit from the device's).  A side effect: chains that
+// differ only in such constants share one compiled kernel.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

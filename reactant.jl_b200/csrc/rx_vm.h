@@ -118,8 +118,8 @@ enum VmOp : uint8_t {
   X(VM_ISUB, ua - ub)                                                              \
   X(VM_IMUL, ua * ub)                                                              \
   X(VM_IDIV, ib == 0 ? 0xFFFFFFFFu : ((ia == INT32_MIN && ib == -1) ? (uint32_t)INT32_MIN : (uint32_t)(ia / ib))) \
-  X(VM_IMAX, (uint32_t)max(ia, ib))                                                            \
-  X(VM_IMIN, (uint32_t)min(ia, ib))                                                            \
+  X(VM_IMAX, (uint32_t)smax32(ia, ib))                                                         \
+  X(VM_IMIN, (uint32_t)smin32(ia, ib))                                                         \
   X(VM_AND, ua & ub)                                                                           \
   X(VM_OR, ua | ub)                                                                            \
   X(VM_XOR, ua ^ ub)                                                                           \

@@ -145,14 +145,31 @@ module {
   }
 }
 """
+# min(acc, min(-x, t)) in a reduction loop: the compiler's own three-input signed minimum lost the negation of
+# one operand; signed min / max are two-input PTX instructions since.
+NEG_UNDER_MIN_MODULE = """
+module {
+  func.func @main(%x: tensor<5x2048xi32>) -> tensor<2048xi32> {
+    %io = stablehlo.iota dim = 1 : tensor<5x2048xi32>
+    %a = stablehlo.abs %io : tensor<5x2048xi32>
+    %n = stablehlo.negate %x : tensor<5x2048xi32>
+    %m = stablehlo.minimum %a, %n : tensor<5x2048xi32>
+    %z = stablehlo.constant dense<2147483647> : tensor<i32>
+    %r = stablehlo.reduce(%m init: %z) applies stablehlo.minimum across dimensions = [0] : (tensor<5x2048xi32>, tensor<i32>) -> tensor<2048xi32>
+    return %r : tensor<2048xi32>
+  }
+}
+"""
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["tanh_of_constant", "multiply_by_constant_under_min"])
-def test_constants_do_not_let_the_compiler_change_results(name):
+@pytest.mark.parametrize("name", ["tanh_of_constant", "multiply_by_constant_under_min", "negation_under_min"])
+def test_constants_and_negations_do_not_let_the_compiler_change_results(name):
     rng = np.random.default_rng(11)
     if name == "tanh_of_constant":
         text, x = CONST_TANH_MODULE, rng.uniform(-1.5, 1.5, size=(130, 1024)).astype(np.float32)
+    elif name == "negation_under_min":
+        text, x = NEG_UNDER_MIN_MODULE, rng.integers(-60, 60, size=(5, 2048)).astype(np.int32)
     else:
         text = CONST_IMUL_MIN_MODULE
         x = rng.integers(-60, 60, size=(128, 16, 16)).astype(np.int32)
@@ -166,9 +183,12 @@ def test_constants_do_not_let_the_compiler_change_results(name):
     finally:
         rx.chain_specialiser(1 << 20)
     assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
-    if name != "tanh_of_constant":
+    if name == "multiply_by_constant_under_min":
         want = (x.astype(np.int64) * -256 & 0xFFFFFFFF).astype(np.uint32).view(np.int32).min()
         assert int(outs[1]) == int(want)
+    if name == "negation_under_min":
+        want = np.minimum(np.arange(2048, dtype=np.int32)[None, :], -x).min(axis=0)
+        assert np.array_equal(outs[1], want)
 
 
 @pytest.mark.gpu
