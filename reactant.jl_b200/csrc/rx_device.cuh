@@ -30,18 +30,31 @@ __device__ __forceinline__ float nan_min(float a, float b) {
   return r;
 }
 
-// Signed 32-bit minimum / maximum as the two-input PTX instruction.  Left to the compiler, min(acc, min(-x, t))
-// in a reduction loop became a three-input minimum for sm_100a that returned wrong values (the negation of one
-// operand was lost; reproduced in a stand-alone kernel with CUDA 12.9).  The asm forms keep every min / max a
-// two-input operation.
+// Signed 32-bit minimum / maximum, computed as an unsigned min / max of sign-biased values inside one asm block.
+// With CUDA 12.9 for sm_100a, a signed integer min / max whose operand or result is negated came out wrong in
+// three shapes (min(acc, x * -256), min(acc, min(-x, t)) in a reduction loop, -max(a, max(a, b))): the negation
+// of one operand was lost, with the C++ min() / max() and with a plain min.s32 / max.s32 alike, so the fault is
+// below PTX.  In the biased form no negation is ever an operand or a user of the min / max instruction.
 __device__ __forceinline__ int32_t smin32(int32_t a, int32_t b) {
   int32_t r;
-  asm("min.s32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  asm("{ .reg .b32 x, y;\n\t"
+      "xor.b32 x, %1, 0x80000000;\n\t"
+      "xor.b32 y, %2, 0x80000000;\n\t"
+      "min.u32 x, x, y;\n\t"
+      "xor.b32 %0, x, 0x80000000; }"
+      : "=r"(r)
+      : "r"(a), "r"(b));
   return r;
 }
 __device__ __forceinline__ int32_t smax32(int32_t a, int32_t b) {
   int32_t r;
-  asm("max.s32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  asm("{ .reg .b32 x, y;\n\t"
+      "xor.b32 x, %1, 0x80000000;\n\t"
+      "xor.b32 y, %2, 0x80000000;\n\t"
+      "max.u32 x, x, y;\n\t"
+      "xor.b32 %0, x, 0x80000000; }"
+      : "=r"(r)
+      : "r"(a), "r"(b));
   return r;
 }
 

@@ -145,8 +145,8 @@ module {
   }
 }
 """
-# min(acc, min(-x, t)) in a reduction loop: the compiler's own three-input signed minimum lost the negation of
-# one operand; signed min / max are two-input PTX instructions since.
+# min(acc, min(-x, t)) in a reduction loop and -max(a, max(a, b)): a signed integer min / max next to a negation
+# lost the negation of one operand; signed min / max are computed on sign-biased unsigned values since.
 NEG_UNDER_MIN_MODULE = """
 module {
   func.func @main(%x: tensor<5x2048xi32>) -> tensor<2048xi32> {
@@ -160,16 +160,33 @@ module {
   }
 }
 """
+NEGATED_MAX_MODULE = """
+module {
+  func.func @main(%x: tensor<2x16x1xi32>) -> tensor<2x16x1xi32> {
+    %k = stablehlo.constant dense<3> : tensor<2x16x1xi32>
+    %v0 = stablehlo.negate %k : tensor<2x16x1xi32>
+    %z0 = stablehlo.subtract %v0, %v0 : tensor<2x16x1xi32>
+    %p = stablehlo.compare NE, %z0, %x : (tensor<2x16x1xi32>, tensor<2x16x1xi32>) -> tensor<2x16x1xi1>
+    %v2 = stablehlo.select %p, %v0, %k : tensor<2x16x1xi1>, tensor<2x16x1xi32>
+    %v3 = stablehlo.maximum %v2, %v0 : tensor<2x16x1xi32>
+    %v6 = stablehlo.maximum %v2, %v3 : tensor<2x16x1xi32>
+    %v9 = stablehlo.negate %v6 : tensor<2x16x1xi32>
+    return %v9 : tensor<2x16x1xi32>
+  }
+}
+"""
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["tanh_of_constant", "multiply_by_constant_under_min", "negation_under_min"])
+@pytest.mark.parametrize("name", ["tanh_of_constant", "multiply_by_constant_under_min", "negation_under_min", "negated_max"])
 def test_constants_and_negations_do_not_let_the_compiler_change_results(name):
     rng = np.random.default_rng(11)
     if name == "tanh_of_constant":
         text, x = CONST_TANH_MODULE, rng.uniform(-1.5, 1.5, size=(130, 1024)).astype(np.float32)
     elif name == "negation_under_min":
         text, x = NEG_UNDER_MIN_MODULE, rng.integers(-60, 60, size=(5, 2048)).astype(np.int32)
+    elif name == "negated_max":
+        text, x = NEGATED_MAX_MODULE, rng.integers(-2, 3, size=(2, 16, 1)).astype(np.int32)
     else:
         text = CONST_IMUL_MIN_MODULE
         x = rng.integers(-60, 60, size=(128, 16, 16)).astype(np.int32)
@@ -186,6 +203,8 @@ def test_constants_and_negations_do_not_let_the_compiler_change_results(name):
     if name == "multiply_by_constant_under_min":
         want = (x.astype(np.int64) * -256 & 0xFFFFFFFF).astype(np.uint32).view(np.int32).min()
         assert int(outs[1]) == int(want)
+    if name == "negated_max":
+        assert np.array_equal(outs[1], np.where(x != 0, 3, -3).astype(np.int32))
     if name == "negation_under_min":
         want = np.minimum(np.arange(2048, dtype=np.int32)[None, :], -x).min(axis=0)
         assert np.array_equal(outs[1], want)
