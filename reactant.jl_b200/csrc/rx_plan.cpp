@@ -1420,6 +1420,8 @@ struct Planner {
       Type xt{X->dt, X->shape};
       ExprP e = round_if_bf16(mkop(vop, xt, {X, konst(xt, init_f, init_i)}));
       emit_map(e, slot, 0, ostr, "reduce over unit dimensions");
+      // a sharded dim whose local extent is one still has to be summed over the mesh
+      if (needs_allreduce) emit_allreduce(slot, rt);
       return leaf(slot, rt);
     } else if (kept_n == 1) {
       st.kind = StepK::ReduceFull;
@@ -1439,17 +1441,18 @@ struct Planner {
       return leaf(slot, rt);
     }
     cur->push_back(std::move(st));
-    if (needs_allreduce) {
-      Step ar;
-      ar.kind = StepK::AllReduce;
-      ar.dst_slot = slot;
-      ar.count = rt.numel();
-      ar.red_dt = rt.dt;
-      ar.note = "all_reduce(sum) over the mesh axis";
-      if (rt.dt != DT::F32) throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type for all_reduce");
-      cur->push_back(std::move(ar));
-    }
+    if (needs_allreduce) emit_allreduce(slot, rt);
     return leaf(slot, rt);
+  }
+  void emit_allreduce(int slot, const Type& rt) {
+    Step ar;
+    ar.kind = StepK::AllReduce;
+    ar.dst_slot = slot;
+    ar.count = rt.numel();
+    ar.red_dt = rt.dt;
+    ar.note = "all_reduce(sum) over the mesh axis";
+    if (rt.dt != DT::F32) throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type for all_reduce");
+    cur->push_back(std::move(ar));
   }
 
   // Rewrite prog dims/strides into exactly three dims [outer][red][inner].

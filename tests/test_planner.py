@@ -189,3 +189,19 @@ module attributes {mhlo.num_partitions = 2 : i64, mhlo.num_replicas = 1 : i64} {
     d = rx.plan_describe(text)
     assert [s["kind"] for s in d["steps"]] == ["map"], d["steps"]
     assert d["steps"][0]["dims"] == [258, 260] or d["steps"][0]["dims"] == [258 * 260], d["steps"]
+
+
+def test_reduce_over_a_sharded_dim_of_local_extent_one_still_crosses_the_mesh(rx):
+    text = """
+module attributes {mhlo.num_partitions = 2 : i64, mhlo.num_replicas = 1 : i64} {
+  sdy.mesh @mesh = <["x"=2]>
+  func.func @main(%arg0: tensor<260x2xf32> {sdy.sharding = #sdy.sharding<@mesh, [{}, {"x"}]>}) -> tensor<260xf32> {
+    %s = stablehlo.sine %arg0 : tensor<260x2xf32>
+    %z = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %red = stablehlo.reduce(%s init: %z) applies stablehlo.add across dimensions = [1] : (tensor<260x2xf32>, tensor<f32>) -> tensor<260xf32>
+    return %red : tensor<260xf32>
+  }
+}
+"""
+    kinds = [s["kind"] for s in rx.plan_describe(text)["steps"]]
+    assert kinds == ["map", "all_reduce"], kinds
