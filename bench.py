@@ -1,4 +1,4 @@
-"""Benchmark of the fused map-reduce hot path on B200.
+"""Benchmark of the fused map-reduce / stencil / dot_general hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
@@ -8,21 +8,32 @@ configuration the metric "fused map-reduce HBM GB/s at 1/2/4/8 B200" is quoted
 on.  At N = 1 it is the whole 2^30 problem on one GPU; at N > 1 (one process per
 GPU under torch.distributed.run) the total problem is fixed (strong scaling):
 each rank reduces its contiguous chunk and the partial sums are all-reduced.
+The global input does not depend on N: it is drawn as 8 fixed chunks, each from
+its own seeded stream, and rank r owns chunks r*8/N .. (r+1)*8/N - 1.
 
-One JSON line is printed by rank 0.  `value` is HBM GB/s over the whole job with
+One JSON line is printed by rank 0.  `value` is the metric over the whole job with
 inputs resident in device memory; `e2e` is the same metric through the public
 API with host buffers (pinned H2D of every step's inputs and D2H of the result
-inside the timed region); `roofline` describes the dominant kernel; and
-`cpu_baseline` is the CPU oracle timed on this host (N = 1 only).
+inside the timed region); `roofline` describes the dominant kernel; `parity`
+compares what the timed steps computed with the CPU oracle on the same inputs
+(the process exits 1 when it does not hold); `cpu_baseline` is the CPU oracle
+timed on this host (N = 1 only).  In the default single-GPU run the other
+single-GPU configurations (c1_sinsum_2p24, c2_logsumexp_32768x8192,
+c3_jacobi2d_8192_100 and its two-half-step spelling, c4_mlp_grad_bf16) are
+measured and checked as well and reported under `configs`.
 
-Other workloads (single GPU): c1_sinsum_2p24, c2_logsumexp_32768x8192,
-c3_jacobi2d_8192_100, c4_mlp_grad_bf16.  Inputs are seeded synthetic data with
-the shapes and distributions of the benchmark configurations.
+`--impl reference` times the CPU implementation of the chosen workload (the
+C/OpenMP or numpy oracle port: the reference's own XLA-CPU path needs Julia and
+its binary artefact, neither of which exists here) on all host cores.
+Inputs are seeded synthetic data with the shapes and distributions of the
+benchmark configurations.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -36,7 +47,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
-GiB = 1 << 30
+N_CHUNKS = 8  # the sharded vectors are drawn as this many independently seeded chunks, whatever the mesh size
 
 
 def measured_peaks():
@@ -46,6 +57,13 @@ def measured_peaks():
             d = json.load(f)
         return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:  # pragma: no cover
+        return os.cpu_count() or 1
 
 
 class ClockSampler:
@@ -85,18 +103,22 @@ class ClockSampler:
         mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+        # the median under load: samples taken while the GPU idled between regions sit at the idle clock
+        busy = [v for v in sm if mx and v >= 0.5 * max(mx)] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
 
 
-def pinned(n, dtype=np.float32):
-    import torch
-    tdt = {np.float32: torch.float32, np.uint16: torch.uint16}[dtype]
-    t = torch.empty(n, dtype=tdt, pin_memory=torch.cuda.is_available())
-    return t, t.numpy()
+def pinned(rx, n, dtype=np.float32):
+    """Page-locked host array from the library's own allocator (pageable numpy memory where no GPU is present)."""
+    if getattr(rx, "PinnedArray", None) is not None:
+        p = rx.PinnedArray(n, dtype)
+        return p, p.array
+    a = np.empty(n, dtype=dtype)
+    return a, a
 
 
 def fill_uniform(dst, seed, lo, hi):
-    """Seeded U[lo,hi) Float32 fill, generated in chunks (keeps host memory bounded)."""
+    """Seeded U[lo,hi) Float32 fill, generated in pieces (keeps host memory bounded)."""
     rng = np.random.default_rng(seed)
     step = 1 << 24
     for i in range(0, dst.size, step):
@@ -104,16 +126,32 @@ def fill_uniform(dst, seed, lo, hi):
         dst[i:j] = rng.random(j - i, dtype=np.float32) * np.float32(hi - lo) + np.float32(lo)
 
 
+def fill_chunks(dst, seed, first_chunk, n_chunks, chunk_len, lo=-np.pi, hi=np.pi):
+    """Chunks first_chunk .. first_chunk + n_chunks - 1 of the global vector, each from its own stream."""
+    for c in range(n_chunks):
+        fill_uniform(dst[c * chunk_len:(c + 1) * chunk_len], seed * 1000 + first_chunk + c, lo, hi)
+
+
+def parity_record(got, want, scale, tol, against, **extra):
+    err = abs(got - want) / scale if scale else abs(got - want)
+    rec = {"got": got, "want": want, "rel_err": err, "tol": tol, "ok": bool(err <= tol), "against": against}
+    rec.update(extra)
+    return rec
+
+
 # ----------------------------------------------------------------------------------------------
-# workloads: each returns dict(thunk, make_args(), read(result), bytes/flops per step, ...)
+# workloads: each returns dict(thunk, upload(), read(result), work per step, check(result), ...)
 # ----------------------------------------------------------------------------------------------
-def setup_sinsum(rx, client, n_total, rank, world, seeds=(11, 12)):
+def setup_sinsum(rx, client, dist, n_total, seeds=(11, 12)):
+    rank, world = dist.rank, dist.world
+    if N_CHUNKS % world or n_total % N_CHUNKS:
+        raise SystemExit(f"the sharded vector is drawn as {N_CHUNKS} chunks: the mesh size must divide it")
+    chunk_len, per_rank = n_total // N_CHUNKS, N_CHUNKS // world
     n_local = n_total // world
-    _, hx = pinned(n_local)
-    _, hy = pinned(n_local)
-    # every rank draws its own chunk from a per-chunk stream so that the global input is fixed for a given world size
-    fill_uniform(hx, seeds[0] * 1000 + rank, -np.pi, np.pi)
-    fill_uniform(hy, seeds[1] * 1000 + rank, -np.pi, np.pi)
+    kx, hx = pinned(rx, n_local)
+    ky, hy = pinned(rx, n_local)
+    fill_chunks(hx, seeds[0], rank * per_rank, per_rank, chunk_len)
+    fill_chunks(hy, seeds[1], rank * per_rank, per_rank, chunk_len)
     text = rx.programs.sinsum_add(n_total, num_partitions=world)
     thunk = rx.compile(text, client)
     if world > 1:
@@ -125,41 +163,102 @@ def setup_sinsum(rx, client, n_total, rank, world, seeds=(11, 12)):
     else:
         def upload():
             return rx.to_rarray(hx, client), rx.to_rarray(hy, client)
-    return dict(thunk=thunk, upload=upload, host=(hx, hy), read=lambda r: float(r),
+
+    def check(result):
+        """float64 sum of this rank's chunks (C oracle, sin in double), summed over the ranks; every rank must
+        hold the same Float32 bits."""
+        ref, cpu = entry.load_oracle()
+        cpu.set_threads(max(1, host_cores() // world))
+        s, q = cpu.sinsum_add_f64(hx, hy)
+        want = dist.reduce(s, "sum")
+        norm = math.sqrt(dist.reduce(q, "sum"))
+        got = float(result)
+        same = dist.reduce(got, "max") == dist.reduce(got, "min")
+        tol = ref.reduction_tolerance(n_total)
+        rec = parity_record(got, want, max(abs(want), norm), tol, "float64 sum of sin(x)+y over the same seeded input (C oracle), error relative to the 2-norm of the terms; tol = 1e-5*sqrt(log2 n)",
+                            same_bits_on_every_rank=bool(same))
+        rec["ok"] = rec["ok"] and bool(same)
+        return rec
+
+    def cpu_run():
+        _, cpu = entry.load_oracle()
+        return cpu.sinsum_add(hx, hy)
+
+    return dict(thunk=thunk, upload=upload, host=(kx, ky, hx, hy), read=lambda r: float(r), check=check, cpu_run=cpu_run,
+                cpu_sample=f"the whole step: sinsum_add over 2^{int(math.log2(n_total))} element pairs ({8 * n_total / 2**30:g} GiB read)",
                 bytes_per_step=8 * n_total, h2d=8 * n_local, d2h=4, unit="GB/s", kind="reduce_full", dtype="f32",
-                bound="hbm", kernel="k_reduce_full_sinadd")
+                bound="hbm", kernel="k_reduce_full_sinadd", shape={"elements": n_total, "chunks": N_CHUNKS, "seeds": list(seeds)})
 
 
-def setup_logsumexp(rx, client, rows=32768, cols=8192):
-    _, hx = pinned(rows * cols)
+def setup_logsumexp(rx, client, dist, rows=32768, cols=8192):
+    keep, hx = pinned(rx, rows * cols)
     rng = np.random.default_rng(3)
     step = 1 << 24
     for i in range(0, hx.size, step):
         hx[i:i + step] = rng.standard_normal(min(step, hx.size - i), dtype=np.float32)
     x = hx.reshape(cols, rows)  # boundary layout
     thunk = rx.compile(rx.programs.logsumexp_dims1(rows, cols), client)
-    return dict(thunk=thunk, upload=lambda: (rx.to_rarray(x.T, client),), host=(x,), read=lambda r: np.asarray(r),
+
+    def check(result):
+        ref, cpu = entry.load_oracle()
+        cpu.set_threads(host_cores())
+        want = cpu.logsumexp_dims1(x).astype(np.float64)
+        got = np.asarray(result, dtype=np.float64).reshape(-1)
+        err = float(np.max(np.abs(got - want) / np.abs(want)))
+        tol = ref.reduction_tolerance(rows)
+        return {"got": float(got[0]), "want": float(want[0]), "rel_err": err, "tol": tol, "ok": bool(err <= tol and got.shape == want.shape),
+                "against": f"C oracle on the same {rows}x{cols} input, max relative error over the {cols} results; tol = 1e-5*sqrt(log2 rows)"}
+
+    def cpu_run():
+        _, cpu = entry.load_oracle()
+        return cpu.logsumexp_dims1(x)
+
+    return dict(thunk=thunk, upload=lambda: (rx.to_rarray(x.T, client),), host=(keep, x), read=lambda r: np.asarray(r), check=check, cpu_run=cpu_run,
+                cpu_sample=f"the whole step: logsumexp over dims=1 of the {rows}x{cols} matrix",
                 bytes_per_step=4 * rows * cols + 4 * cols, h2d=4 * rows * cols, d2h=4 * cols, unit="GB/s", kind="logsumexp", dtype="f32",
-                bound="hbm", kernel="k_logsumexp")
+                bound="hbm", kernel="k_logsumexp", shape={"rows": rows, "cols": cols, "seed": 3})
 
 
-def setup_jacobi(rx, client, n=8192, steps=100):
-    _, ha = pinned(n * n)
-    _, hb = pinned(n * n)
+def setup_jacobi(rx, client, dist, n=8192, steps=100, form="dus"):
+    ka, ha = pinned(rx, n * n)
+    kb, hb = pinned(rx, n * n)
     fill_uniform(ha, 4, 0.0, 1.0)
     fill_uniform(hb, 5, 0.0, 1.0)
     a, b = ha.reshape(n, n), hb.reshape(n, n)
-    thunk = rx.compile(rx.programs.jacobi2d(n, steps), client)
+    sweeps = steps if form != "halfsteps" else 2 * steps
+    order = "polybench" if form == "halfsteps" else "baseline"
+    thunk = rx.compile(rx.programs.jacobi2d(n, steps, form=form), client)
     per_sweep = 4 * n * n + 4 * (n - 2) * (n - 2)
-    return dict(thunk=thunk, upload=lambda: (rx.to_rarray(a.T, client), rx.to_rarray(b.T, client)), host=(a, b),
-                read=lambda r: (np.asarray(r[0]), np.asarray(r[1])), bytes_per_step=per_sweep * steps, h2d=8 * n * n, d2h=8 * n * n,
-                unit="GB/s", kind="stencil_tma", dtype="f32", bound="hbm", kernel="k_stencil", launches_per_step=steps, donates=True)
+
+    def check(_result):
+        """The timed steps keep sweeping the same donated arrays, so parity is taken on a run of its own: fresh
+        upload, one execution (all the sweeps), every element compared with the C oracle's."""
+        _, cpu = entry.load_oracle()
+        cpu.set_threads(host_cores())
+        ra, rb = thunk(rx.to_rarray(a.T, client), rx.to_rarray(b.T, client))
+        ga, gb = np.asarray(ra).T, np.asarray(rb).T
+        wa, wb = cpu.jacobi2d(a, b, sweeps, order)
+        bad = int(np.count_nonzero(ga != wa) + np.count_nonzero(gb != wb))
+        return {"got": float(ga[n // 2, n // 2]), "want": float(wa[n // 2, n // 2]), "rel_err": bad / (2.0 * n * n), "tol": 0.0, "ok": bad == 0,
+                "against": f"C oracle, {sweeps} sweeps of the same {n}x{n} arrays, bit-exact (rel_err = fraction of differing elements)"}
+
+    def cpu_run():
+        _, cpu = entry.load_oracle()
+        return cpu.jacobi2d(a, b, 10, order)
+
+    return dict(thunk=thunk, upload=lambda: (rx.to_rarray(a.T, client), rx.to_rarray(b.T, client)), host=(ka, kb, a, b),
+                read=lambda r: (np.asarray(r[0]), np.asarray(r[1])), check=check, cpu_run=cpu_run, cpu_work=per_sweep * 10,
+                cpu_sample=f"10 of the {sweeps} sweeps of the {n}^2 grid per step",
+                bytes_per_step=per_sweep * sweeps, h2d=8 * n * n, d2h=8 * n * n,
+                unit="GB/s", kind="stencil_tma", dtype="f32", bound="hbm", kernel="k_stencil", launches_per_step=sweeps, donates=True,
+                shape={"n": n, "sweeps": sweeps, "form": form, "seeds": [4, 5]})
 
 
-def setup_mlp(rx, client, rank=0, world=1, F=1024, H=4096, O=1024, B=4096):
+def setup_mlp(rx, client, dist, F=1024, H=4096, O=1024, B=4096):
     """MLP forward + gradients.  With N > 1 ranks the batch is sharded (weak scaling: B rows per GPU, global batch
     B * N), the weights are replicated, and every gradient is all-reduced (NCCL over NVLink) -- data-parallel training."""
     import ml_dtypes
+    rank, world = dist.rank, dist.world
     rng = np.random.default_rng(6)
     bf = lambda a: a.astype(np.float32).astype(ml_dtypes.bfloat16)
     W1 = bf(rng.standard_normal((F, H)) / np.sqrt(F))
@@ -176,7 +275,7 @@ def setup_mlp(rx, client, rank=0, world=1, F=1024, H=4096, O=1024, B=4096):
         transposed view of a C-contiguous buffer, which the upload hands to the library without another host copy."""
         t = np.ascontiguousarray(a)
         raw = np.uint16 if t.dtype == ml_dtypes.bfloat16 else np.float32
-        _keep, buf = pinned(t.size, raw)
+        _keep, buf = pinned(rx, t.size, raw)
         host = buf.view(t.dtype).reshape(t.shape)
         host[...] = t
         host_keep.append(_keep)
@@ -184,9 +283,11 @@ def setup_mlp(rx, client, rank=0, world=1, F=1024, H=4096, O=1024, B=4096):
 
     host_keep = []
     ins_t = [staged(a) for a in ins]
-    thunk = rx.compile(rx.programs.mlp_grad(F, H, O, B * world, num_partitions=world), client)
+    text = rx.programs.mlp_grad(F, H, O, B * world, num_partitions=world)
+    thunk = rx.compile(text, client)
     flops = (2 * B * H * F * 2 + 2 * B * O * H * 3) * world
     nbytes = sum(a.nbytes for a in ins)
+    out_bytes = 2 * F * H + 4 * H + 2 * H * O + 4 * O + 4
     if world > 1:
         mesh = rx.Mesh(client.devices, ("x",))
         rep2, rep1, batch = rx.NamedSharding(mesh, (None, None)), rx.NamedSharding(mesh, (None,)), rx.NamedSharding(mesh, (None, "x"))
@@ -197,36 +298,68 @@ def setup_mlp(rx, client, rank=0, world=1, F=1024, H=4096, O=1024, B=4096):
     else:
         def upload():
             return tuple(rx.to_rarray(a, client) for a in ins_t)
-    # the step's result that travels back is the loss; the gradients stay on the device for the optimiser
-    return dict(thunk=thunk, upload=upload, host=(ins_t, host_keep), read=lambda r: float(r[4]),
-                flops_per_step=flops, h2d=nbytes, d2h=4, unit="TFLOP/s", kind="gemm_tc", dtype="bf16",
-                bound="tensor", kernel="k_gemm", launches_per_step=5)
+
+    def read(r):
+        """The step's results: both weight gradients, both bias gradients and the loss, copied to the host."""
+        return [np.asarray(o.data[0].to_host()) for o in r]
+
+    def check(result):
+        """Every gradient and the loss against the numpy oracle (float64 accumulation) of the same module on the same
+        inputs; each output within 2e-2 of its largest magnitude (the bf16 dot_general bar)."""
+        if world > 1:
+            return None  # the global batch lives on several ranks; the 2-GPU parity tests cover the data-parallel form
+        ref, _ = entry.load_oracle()
+        f32 = lambda a: np.asarray(a, dtype=np.float32)
+        want = ref.run_module(text, [f32(W1), b1, f32(W2), b2, f32(X), Y])
+        worst, names = 0.0, ("dW1", "db1", "dW2", "db2", "loss")
+        detail = {}
+        for name, g, w in zip(names, result, want):
+            g, w = np.asarray(g, dtype=np.float64), np.asarray(w, dtype=np.float64)
+            e = float(np.max(np.abs(g - w)) / max(float(np.max(np.abs(w))), 1e-30))
+            detail[name] = e
+            worst = max(worst, e)
+        return {"got": float(np.asarray(result[4], dtype=np.float64)), "want": float(want[4]), "rel_err": worst, "tol": 2e-2, "ok": bool(worst <= 2e-2), "per_output": detail,
+                "against": "numpy StableHLO oracle (float64 accumulation) on the same inputs; per output max|got - want| / max|want|"}
+
+    def cpu_run():
+        ref, _ = entry.load_oracle()
+        f32 = lambda a: np.asarray(a, dtype=np.float32)
+        return ref.run_module(text, [f32(W1), b1, f32(W2), b2, f32(X), Y])
+
+    return dict(thunk=thunk, upload=upload, host=(ins_t, host_keep), read=read, check=check, cpu_run=cpu_run,
+                cpu_sample="the whole step through the numpy StableHLO oracle (BLAS float64 contractions)",
+                flops_per_step=flops, h2d=nbytes, d2h=out_bytes, unit="TFLOP/s", kind="gemm_tc", dtype="bf16",
+                bound="tensor", kernel="k_gemm", launches_per_step=5,
+                shape={"features": F, "hidden": H, "out": O, "batch_per_gpu": B, "seeds": [6, 600]})
 
 
 WORKLOADS = {
-    "c5_sharded_sinsum_2p30": lambda rx, c, r, w: setup_sinsum(rx, c, 1 << 30, r, w),
-    "c1_sinsum_2p24": lambda rx, c, r, w: setup_sinsum(rx, c, 1 << 24, r, w, seeds=(1, 2)),
-    "c2_logsumexp_32768x8192": lambda rx, c, r, w: setup_logsumexp(rx, c),
-    "c3_jacobi2d_8192_100": lambda rx, c, r, w: setup_jacobi(rx, c),
-    "c4_mlp_grad_bf16": lambda rx, c, r, w: setup_mlp(rx, c, r, w),
+    "c5_sharded_sinsum_2p30": lambda rx, c, d: setup_sinsum(rx, c, d, 1 << 30),
+    "c1_sinsum_2p24": lambda rx, c, d: setup_sinsum(rx, c, d, 1 << 24, seeds=(1, 2)),
+    "c2_logsumexp_32768x8192": lambda rx, c, d: setup_logsumexp(rx, c, d),
+    "c3_jacobi2d_8192_100": lambda rx, c, d: setup_jacobi(rx, c, d),
+    "c3_jacobi2d_8192_50_halfsteps": lambda rx, c, d: setup_jacobi(rx, c, d, 8192, 50, form="halfsteps"),
+    "c4_mlp_grad_bf16": lambda rx, c, d: setup_mlp(rx, c, d),
 }
 # reduced sizes of the same programs for profiler captures (a few hundred MB on the device, still larger than L2)
 WORKLOADS.update({
-    "prof_sinsum_2p27": lambda rx, c, r, w: setup_sinsum(rx, c, 1 << 27, r, w, seeds=(1, 2)),
-    "prof_logsumexp_32768x2048": lambda rx, c, r, w: setup_logsumexp(rx, c, 32768, 2048),
-    "prof_jacobi2d_8192_4": lambda rx, c, r, w: setup_jacobi(rx, c, 8192, 4),
+    "prof_sinsum_2p27": lambda rx, c, d: setup_sinsum(rx, c, d, 1 << 27, seeds=(1, 2)),
+    "prof_logsumexp_32768x2048": lambda rx, c, d: setup_logsumexp(rx, c, d, 32768, 2048),
+    "prof_jacobi2d_8192_4": lambda rx, c, d: setup_jacobi(rx, c, d, 8192, 4),
 })
 SMALL_INPUT = {"c1_sinsum_2p24", "c4_mlp_grad_bf16"}  # working set near or below the 126 MB L2: rotate input copies
+EXTRA_CONFIGS = ["c1_sinsum_2p24", "c2_logsumexp_32768x8192", "c3_jacobi2d_8192_100", "c3_jacobi2d_8192_50_halfsteps", "c4_mlp_grad_bf16"]
+SHARDED = ("c5_sharded_sinsum_2p30", "c1_sinsum_2p24", "c4_mlp_grad_bf16")
 
 
-# DRAM traffic per algorithmic byte of the dominant kernel, from the ncu captures summarised under profiles/
-# (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured launch; traffic grows in
-# proportion to the units processed, so the ratio carries over to the full-size launch).
+# DRAM traffic per algorithmic byte of the dominant kernel, from profiler captures of the reduced-size workloads
+# above (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured launch; traffic
+# grows in proportion to the units processed, so the ratio carries over to the full-size launch).
 TRAFFIC_RATIO = {
-    "reduce_full": (1.073795e9 + 3.84e6) / (8 * (1 << 27)),          # profiles/k_reduce_full_sinadd__sinsum_2p27.md
-    "logsumexp": (268.457728e6 + 3.685e6) / (4 * 32768 * 2048 + 12 * 2048),  # profiles/k_logsumexp__32768x2048.md
-    "stencil_tma": (269.39392e6 + 219.197184e6) / (4 * 8192 * 8192 + 4 * 8190 * 8190),  # profiles/k_stencil_tma__jacobi2d_8192*.md
-    "stencil_tma_loop": (0.930697e9 + 1.023089e9) / 4 / (4 * 8192 * 8192 + 4 * 8190 * 8190),  # profiles/k_stencil_loop__jacobi2d_8192_x4.md
+    "reduce_full": (1.073795e9 + 3.84e6) / (8 * (1 << 27)),
+    "logsumexp": (268.457728e6 + 3.685e6) / (4 * 32768 * 2048 + 12 * 2048),
+    "stencil_tma": (269.39392e6 + 219.197184e6) / (4 * 8192 * 8192 + 4 * 8190 * 8190),
+    "stencil_tma_loop": (0.930697e9 + 1.023089e9) / 4 / (4 * 8192 * 8192 + 4 * 8190 * 8190),
 }
 
 
@@ -236,6 +369,13 @@ def work_per_step(wl):
 
 def to_metric(wl, work, ms):
     return work / (ms * 1e-3) / (1e9 if wl["unit"] == "GB/s" else 1e12)
+
+
+def config_of(name, wl, world):
+    """What both arms of the benchmark print as `config`: the workload, its shape and seeds, the L2 policy."""
+    rotate = 4 if name in SMALL_INPUT else 1
+    return {"workload": name, **wl["shape"], "n_gpus": world,
+            "l2": f"{rotate} rotating resident input sets, together larger than L2" if rotate > 1 else "inputs larger than L2"}
 
 
 def time_resident(rx, client, wl, steps, warmup, rotate, dist, spans=False):
@@ -287,64 +427,118 @@ def time_e2e(rx, client, wl, steps, warmup, dist):
     return ms, out
 
 
-def cpu_baseline(name, seconds_budget=20.0):
-    """The C/OpenMP oracle timed on this host's cores on a bounded sample of the workload."""
+def time_cpu(wl, steps, warmup, seconds_budget=None):
+    """The CPU port of the workload's step on every host core; returns (seconds per step, steps timed)."""
     _, cpu = entry.load_oracle()
-    threads = cpu.threads()
-    rng = np.random.default_rng(99)
-    if "sinsum" in name:
-        n = 1 << 27
-        x = rng.random(n, dtype=np.float32) * np.float32(2 * np.pi) - np.float32(np.pi)
-        y = rng.random(n, dtype=np.float32) * np.float32(2 * np.pi) - np.float32(np.pi)
-        fn, work, unit, sample = (lambda: cpu.sinsum_add(x, y)), 8 * n, "GB/s", f"sinsum_add on 2^27 element pairs (1 GiB read) per repetition"
-    elif "logsumexp" in name:
-        rows, cols = 32768, 1024
-        x = rng.standard_normal((cols, rows), dtype=np.float32)
-        fn, work, unit, sample = (lambda: cpu.logsumexp_dims1(x)), 4 * rows * cols + 4 * cols, "GB/s", f"{cols} of 8192 columns of 32768 rows per repetition"
-    elif "jacobi" in name:
-        n, steps = 8192, 2
-        a, b = rng.random((n, n), dtype=np.float32), rng.random((n, n), dtype=np.float32)
-        fn, work, unit, sample = (lambda: cpu.jacobi2d(a, b, steps)), (4 * n * n + 4 * (n - 2) ** 2) * steps, "GB/s", "2 of 100 sweeps of the 8192^2 grid per repetition"
-    else:
-        return None
-    fn()
-    t0, reps, best = time.perf_counter(), 0, float("inf")
-    while True:
+    cpu.set_threads(host_cores())
+    for _ in range(warmup):
+        wl["cpu_run"]()
+    t0, done, best = time.perf_counter(), 0, float("inf")
+    while done < steps:
         t = time.perf_counter()
-        fn()
+        wl["cpu_run"]()
         best = min(best, time.perf_counter() - t)
-        reps += 1
-        if time.perf_counter() - t0 > seconds_budget or reps >= 10:
+        done += 1
+        if seconds_budget is not None and time.perf_counter() - t0 > seconds_budget:
             break
-    return {"value": work / best / 1e9, "unit": unit, "cores": threads, "kind": "port", "sample": sample + f"; best of {reps}"}
+    return (time.perf_counter() - t0) / done, best, done
+
+
+def cpu_baseline(wl, seconds_budget=15.0):
+    """The oracle port timed on this host's cores, bounded to `seconds_budget` of CPU work."""
+    per_step, best, done = time_cpu(wl, 10, 1, seconds_budget)
+    work = wl.get("cpu_work", work_per_step(wl))
+    return {"value": to_metric(wl, work, best * 1e3), "unit": wl["unit"], "cores": host_cores(), "kind": "port", "sample": wl["cpu_sample"] + f"; best of {done}"}
+
+
+class NoDist:
+    """The reference arm runs on rank 0 alone: no process group."""
+    world, rank, local_rank = 1, 0, 0
+
+    def barrier(self): pass
+    def reduce(self, v, op="max"): return v
+    def close(self): pass
+
+
+class HostOnly:
+    """Stands in for the engine in the reference arm, which needs the workloads' host arrays and module text
+    but never touches a GPU: no pinned memory, no compilation."""
+    PinnedArray = None
+
+    def __init__(self, rx):
+        self.programs = rx.programs
+
+    def compile(self, *a, **k):
+        return None
 
 
 def run_reference(args):
     """Reference arm: the CPU implementation of the path (the oracle port; the reference's own XLA-CPU
-    path cannot be installed here: it needs Julia and the Reactant_jll binary) on all host threads."""
+    path cannot be installed here: it needs Julia and the Reactant_jll binary) on all host threads, on the
+    same workload, shape and seeds as the GPU arm."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    _, cpu = entry.load_oracle()
-    name = args.workload
-    n = 1 << 27
-    rng = np.random.default_rng(11)
-    x = rng.random(n, dtype=np.float32) * np.float32(2 * np.pi) - np.float32(np.pi)
-    y = rng.random(n, dtype=np.float32) * np.float32(2 * np.pi) - np.float32(np.pi)
-    for _ in range(max(1, args.warmup)):
-        cpu.sinsum_add(x, y)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu.sinsum_add(x, y)
-    dt = (time.perf_counter() - t0) / args.steps
-    value = 8 * n / dt / 1e9
-    sample = "each step reduces 2^27 of the 2^30 element pairs (1 GiB read)"
-    line = {"impl": "reference", "metric": "fused map-reduce HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": {"workload": name, "sample": sample},
-            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cpu.threads(), "kind": "port", "sample": sample},
-            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    rx = entry.load_package()
+    host = HostOnly(rx)
+    dist = NoDist()
+    wl = WORKLOADS[args.workload](host, None, dist)
+    per_step, best, done = time_cpu(wl, args.steps, args.warmup, seconds_budget=150.0)  # the whole run ends within a few minutes
+    work = wl.get("cpu_work", work_per_step(wl))
+    value = to_metric(wl, work, per_step * 1e3)
+    cfg = config_of(args.workload, wl, args.gpus)
+    line = {"impl": "reference", "metric": "fused map-reduce HBM GB/s" if wl["unit"] == "GB/s" else "dot_general TFLOP/s", "value": value, "unit": wl["unit"],
+            "n_gpus": args.gpus, "steps": done, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+            "scaling": scaling_of(args.workload, args.gpus), "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic", "config": cfg,
+            "cpu_baseline": {"value": value, "unit": wl["unit"], "cores": host_cores(), "kind": "port", "sample": wl["cpu_sample"]},
+            "e2e": {"value": value, "unit": wl["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def scaling_of(workload, world):
+    return "strong" if "sinsum" in workload and (world > 1 or "c5" in workload) else "weak"
+
+
+def roofline_of(wl, prof, ms, steps, launches, world, dist, peaks):
+    """The dominant kernel: average span of its step kind, measured in the timed region on the launching stream."""
+    kind = wl["kind"]
+    launches_per_step, kernel = wl.get("launches_per_step", 1), wl["kernel"]
+    work = work_per_step(wl)
+    if kind == "stencil_tma" and "stencil_tma_loop" in prof:
+        # the whole counted loop ran as one cooperative launch: a launch processes every sweep of the step
+        kind, launches_per_step, kernel = "stencil_tma_loop", 1, "k_stencil_loop"
+    if kind not in prof or not prof[kind]["launches"]:
+        return None
+    if launches == steps * world:
+        # one launch per step: the timed region itself is that kernel's launches back to back
+        per_launch_ms, timed = ms / steps, "timed region / steps (one launch per step)"
+    else:
+        per_launch_ms, timed = prof[kind]["ms"] / prof[kind]["launches"], "per-launch event pairs, repeat of the timed region"
+    per_launch_ms = dist.reduce(per_launch_ms, "max")
+    per_launch_work = work / launches_per_step
+    achieved = to_metric(wl, per_launch_work, per_launch_ms)
+    peak = (peaks["hbm_gbs"] if wl["bound"] == "hbm" else peaks["bf16_tflops"]) * world
+    traffic = None
+    if kind in TRAFFIC_RATIO:
+        traffic = TRAFFIC_RATIO[kind] * per_launch_work / world  # bytes per launch on one GPU
+    return {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": wl["unit"], "frac": achieved / peak, "traffic": traffic,
+            "kernel": kernel, "peak_source": f"of {peaks['source']}" + (f" x{world} GPUs" if world > 1 else ""),
+            "ms_per_launch": per_launch_ms, "timed_by": timed}
+
+
+def measure(rx, client, dist, name, steps, warmup, peaks):
+    """Device-resident timing, per-kernel spans, roofline and parity of one workload."""
+    wl = WORKLOADS[name](rx, client, dist)
+    rotate = 4 if name in SMALL_INPUT else 1
+    ms, launches, _, result = time_resident(rx, client, wl, steps, warmup, rotate, dist)
+    # per-kernel spans from a repeat of the same K steps, each launch bracketed by its own events
+    _, _, prof, _ = time_resident(rx, client, wl, steps, 1, rotate, dist, spans=True)
+    ms = dist.reduce(ms, "max")
+    launches = int(dist.reduce(launches, "sum"))
+    value = to_metric(wl, work_per_step(wl) * steps, ms)
+    roof = roofline_of(wl, prof, ms, steps, launches, dist.world, dist, peaks)
+    parity = wl["check"](result)
+    return wl, dict(ms=ms, launches=launches, prof=prof, result=result, value=value, roofline=roof, parity=parity)
 
 
 def main():
@@ -352,11 +546,14 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c5_sharded_sinsum_2p30", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the other single-GPU configurations of the default run")
     args = ap.parse_args()
+    default_run = args.workload is None
+    args.workload = args.workload or "c5_sharded_sinsum_2p30"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
@@ -370,64 +567,58 @@ def main():
     client = rx.Client(node_id=dist.rank, num_nodes=world, allowed_devices=[dist.local_rank])
     allreduce = "none"
     if world > 1:
-        if args.workload not in ("c5_sharded_sinsum_2p30", "c1_sinsum_2p24", "c4_mlp_grad_bf16"):
+        if args.workload not in SHARDED:
             raise SystemExit("the sinsum workloads and the data-parallel MLP step shard; the others run as single-GPU configurations")
         default_mode = "mailbox+nccl" if args.workload == "c4_mlp_grad_bf16" else "mailbox"
         allreduce = rx.dist.connect_collectives(rx, client, dist, os.environ.get("RX_ALLREDUCE", default_mode))
-    wl = WORKLOADS[args.workload](rx, client, dist.rank, world)
-    rotate = 4 if args.workload in SMALL_INPUT else 1
     peaks = measured_peaks()
     with ClockSampler(dist.local_rank) as clk:  # sampling covers warm-up and the timed region
-        ms, launches, _, result = time_resident(rx, client, wl, args.steps, args.warmup, rotate, dist)
-        # per-kernel spans from a repeat of the same K steps, each launch bracketed by its own events
-        _, _, prof, _ = time_resident(rx, client, wl, args.steps, 1, rotate, dist, spans=True)
-    ms = dist.reduce(ms, "max")
-    launches = int(dist.reduce(launches, "sum"))
-    work = work_per_step(wl)
-    value = to_metric(wl, work * args.steps, ms)
-    # dominant kernel: average span of its step kind, measured in the timed region on the launching stream
-    kind = wl["kind"]
-    launches_per_step, kernel = wl.get("launches_per_step", 1), wl["kernel"]
-    if kind == "stencil_tma" and "stencil_tma_loop" in prof:
-        # the whole counted loop ran as one cooperative launch: a launch processes every sweep of the step
-        kind, launches_per_step, kernel = "stencil_tma_loop", 1, "k_stencil_loop"
-    roof = None
-    if kind in prof and prof[kind]["launches"]:
-        if launches == args.steps * world:
-            # one launch per step: the timed region itself is that kernel's launches back to back
-            per_launch_ms, timed = ms / args.steps, "timed region / steps (one launch per step)"
-        else:
-            per_launch_ms, timed = prof[kind]["ms"] / prof[kind]["launches"], "per-launch event pairs, repeat of the timed region"
-        per_launch_ms = dist.reduce(per_launch_ms, "max")
-        per_launch_work = work / launches_per_step
-        achieved = to_metric(wl, per_launch_work, per_launch_ms)
-        peak = (peaks["hbm_gbs"] if wl["bound"] == "hbm" else peaks["bf16_tflops"]) * world
-        traffic = None
-        if kind in TRAFFIC_RATIO:
-            traffic = TRAFFIC_RATIO[kind] * per_launch_work / world  # bytes per launch on one GPU
-        roof = {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": wl["unit"], "frac": achieved / peak, "traffic": traffic,
-                "kernel": kernel, "peak_source": f"of {peaks['source']}" + (f" x{world} GPUs" if world > 1 else ""),
-                "ms_per_launch": per_launch_ms, "timed_by": timed}
+        wl, m = measure(rx, client, dist, args.workload, args.steps, args.warmup, peaks)
+    cfg, unit, dtype = config_of(args.workload, wl, world), wl["unit"], wl["dtype"]
     e2e = None
     if not args.no_e2e:
         e_steps = max(2, min(args.steps, 5))
         ems, _ = time_e2e(rx, client, wl, e_steps, args.warmup, dist)
         ems = dist.reduce(ems, "max")
-        e2e = {"value": to_metric(wl, work * e_steps, ems), "unit": wl["unit"], "h2d_bytes_per_step": wl["h2d"] * world, "d2h_bytes_per_step": wl["d2h"] * world,
+        e2e = {"value": to_metric(wl, work_per_step(wl) * e_steps, ems), "unit": unit, "h2d_bytes_per_step": wl["h2d"] * world, "d2h_bytes_per_step": wl["d2h"] * world,
                "steps": e_steps, "ms_per_step": ems / e_steps}
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_baseline(args.workload)
+        cpu = cpu_baseline(wl)
+    ok = m["parity"] is None or m["parity"]["ok"]
+    configs, configs_clocks = None, None
+    if default_run and world == 1 and not args.no_configs:
+        # the other single-GPU configurations, each with the same timing rules (3 warm-up steps, CUDA events on
+        # the launching stream, inputs larger than L2 or rotated), its roofline and its parity check
+        del wl  # frees the headline workload's host and device arrays
+        gc.collect()
+        configs = {}
+        with ClockSampler(dist.local_rank) as cclk:
+            for name in EXTRA_CONFIGS:
+                k = min(args.steps, 20)
+                w, r = measure(rx, client, dist, name, k, 3, peaks)
+                roof = r["roofline"]
+                configs[name] = {"value": r["value"], "unit": w["unit"], "ms_per_step": r["ms"] / k, "steps": k, "warmup": 3, "gpu_launches": r["launches"],
+                                 "roofline": {q: roof[q] for q in ("bound", "achieved", "peak", "frac", "kernel", "ms_per_launch", "peak_source")} if roof else None,
+                                 "parity": r["parity"], "config": config_of(name, w, 1), "profile_ms": r["prof"]}
+                ok = ok and (r["parity"] is None or r["parity"]["ok"])
+                del w, r
+                gc.collect()
+        configs_clocks = cclk.summary()
     if dist.rank == 0:
-        line = {"metric": "fused map-reduce HBM GB/s" if wl["unit"] == "GB/s" else "dot_general TFLOP/s", "value": value, "unit": wl["unit"], "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if "sinsum" in args.workload and (world > 1 or "c5" in args.workload) else "weak",
-                "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-                "config": {"workload": args.workload, "l2": f"{rotate} rotating resident input sets, together larger than L2" if rotate > 1 else "inputs larger than L2", "all_reduce": allreduce,
-                           "result": result if isinstance(result, float) else None},
-                "clocks": clk.summary(), "e2e": e2e, "gpu_launches": launches, "roofline": roof, "cpu_baseline": cpu, "profile_ms": prof}
+        line = {"metric": "fused map-reduce HBM GB/s" if unit == "GB/s" else "dot_general TFLOP/s", "value": m["value"], "unit": unit, "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": m["ms"] / args.steps, "higher_is_better": True, "scaling": scaling_of(args.workload, world),
+                "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+                "config": cfg, "all_reduce": allreduce, "parity": m["parity"],
+                "clocks": clk.summary(), "e2e": e2e, "gpu_launches": m["launches"], "roofline": m["roofline"], "cpu_baseline": cpu, "profile_ms": m["prof"]}
+        if configs is not None:
+            line["configs"] = configs
+            line["configs_clocks"] = configs_clocks
         print(json.dumps(line), flush=True)
     client.close()
     dist.close()
+    if not ok:
+        raise SystemExit(1)
 
 
 if __name__ == "__main__":

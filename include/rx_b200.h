@@ -219,7 +219,22 @@ int RxClientInitCollectives(RxClient* client, const uint8_t* id128);
  * all of them in global device order and passes the table to
  * RxClientOpenMailboxes.  Single-process clients set this up internally. */
 int RxClientMailboxHandle(RxClient* client, int local_device, uint8_t* handle64);
+/* Every wait for a peer inside a kernel is bounded.  This sets the bound for the client's all-reduces, in
+ * milliseconds (1..60000); when it runs out the kernel returns, the rank keeps its own partial value and the
+ * next FutureAwait / BufferToHost reports RX_ERR_PEER_TIMEOUT.  Defaults: 1000 ms when one process drives all
+ * devices, 8000 ms when the ranks are separate processes; the environment variable RX_PEER_WAIT_MS, read when
+ * the client is made, overrides both. */
+int RxClientSetPeerWaitMs(RxClient* client, int64_t milliseconds);
 int RxClientOpenMailboxes(RxClient* client, const uint8_t* handles, int n_global_devices);
+
+/* ---- page-locked host memory (no counterpart in the reference, where XLA stages
+ * pageable host arrays itself inside BufferFromHostBuffer, API.cpp:1093-1095) -----
+ * ArrayFromHostBuffer / BufferToHost move data at the full PCIe rate only from
+ * page-locked memory; a host that wants that rate keeps its arrays in blocks
+ * obtained here.  RxHostAlloc returns NULL and reports an error when the memory
+ * cannot be locked; RxHostFree accepts NULL. */
+void* RxHostAlloc(size_t bytes);
+void RxHostFree(void* ptr);
 
 /* ---- measurement helpers (no counterpart in the reference, which times with
  * the XLA profiler, src/Profiler.jl:109-184) --------------------------------- */

@@ -44,12 +44,35 @@ def lib():
         _lib.rx_oracle_sinsum_add.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
         _lib.rx_oracle_logsumexp_dims1.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
         _lib.rx_oracle_jacobi2d.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]
+        _lib.rx_oracle_jacobi2d_order.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int]
         _lib.rx_oracle_threads.restype = C.c_int
+        _lib.rx_oracle_set_threads.argtypes = [C.c_int]
+        _lib.rx_oracle_sinsum_add_f64.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.POINTER(C.c_double), C.POINTER(C.c_double)]
     return _lib
 
 
 def threads() -> int:
     return int(lib().rx_oracle_threads())
+
+
+def set_threads(n: int | None = None) -> int:
+    """Use `n` OpenMP threads (default: every core this process may run on), whatever OMP_NUM_THREADS says."""
+    if n is None:
+        try:
+            n = len(os.sched_getaffinity(0))
+        except AttributeError:  # pragma: no cover
+            n = os.cpu_count() or 1
+    lib().rx_oracle_set_threads(int(n))
+    return threads()
+
+
+def sinsum_add_f64(x, y):
+    """(sum, sum of squares) of sin(x) + y in float64: the ground truth of the fp32 tolerance checks."""
+    x, px = _f32(x)
+    y, py = _f32(y)
+    s, q = C.c_double(), C.c_double()
+    lib().rx_oracle_sinsum_add_f64(px, py, x.size, C.byref(s), C.byref(q))
+    return s.value, q.value
 
 
 def _f32(a):
@@ -72,8 +95,11 @@ def logsumexp_dims1(x_xla) -> np.ndarray:
     return out
 
 
-def jacobi2d(a_xla, b_xla, steps: int):
+def jacobi2d(a_xla, b_xla, steps: int, order: str = "baseline"):
+    """`steps` sweeps with the roles of the arrays swapping after each.  order="baseline": terms added as centre,
+    i-1, i+1, j-1, j+1 (Julia indices); order="polybench": centre, j-1, j+1, i+1, i-1, the order of
+    benchmark/polybench/stencil.jl:267-287 (one of its iterations is two sweeps)."""
     a = np.array(a_xla, dtype=np.float32, order="C", copy=True)
     b = np.array(b_xla, dtype=np.float32, order="C", copy=True)
-    lib().rx_oracle_jacobi2d(a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), a.shape[0], steps)
+    lib().rx_oracle_jacobi2d_order(a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), a.shape[0], steps, {"baseline": 0, "polybench": 1}[order])
     return a, b

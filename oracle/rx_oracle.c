@@ -39,6 +39,39 @@ int rx_oracle_threads(void) {
 #endif
 }
 
+/* The OpenMP runtime takes its default team size from OMP_NUM_THREADS, which launchers such as
+ * torch.distributed.run set to 1 for every child; callers that want all host cores say so here. */
+void rx_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
+/* Ground truth for the tolerance checks at full size: sum(sin(x) + y) with sin evaluated and everything
+ * accumulated in double (blocks of 4096 summed serially, block sums added in index order by the reduction),
+ * together with the sum of squares of the terms (the scale an ill-conditioned sum is judged against). */
+void rx_oracle_sinsum_add_f64(const float* x, const float* y, int64_t n, double* sum, double* sumsq) {
+  const int64_t BLK = 4096;
+  int64_t nblk = (n + BLK - 1) / BLK;
+  double total = 0.0, sq = 0.0;
+#pragma omp parallel for reduction(+ : total, sq) schedule(static)
+  for (int64_t b = 0; b < nblk; ++b) {
+    int64_t lo = b * BLK, hi = lo + BLK < n ? lo + BLK : n;
+    double s = 0.0, q = 0.0;
+    for (int64_t i = lo; i < hi; ++i) {
+      double t = sin((double)x[i]) + (double)y[i];
+      s += t;
+      q += t * t;
+    }
+    total += s;
+    sq += q;
+  }
+  *sum = total;
+  *sumsq = sq;
+}
+
 float rx_oracle_sinsum_add(const float* x, const float* y, int64_t n) {
   const int64_t BLK = 4096;
   int64_t nblk = (n + BLK - 1) / BLK;
@@ -78,21 +111,34 @@ void rx_oracle_logsumexp_dims1(const float* x, int64_t rows, int64_t cols, float
 }
 
 /* A, B: [n][n]; `steps` sweeps; after each sweep the roles swap.  On return A
- * holds what the program's first result holds and B the second. */
-void rx_oracle_jacobi2d(float* A, float* B, int64_t n, int64_t steps) {
+ * holds what the program's first result holds and B the second.
+ * order 0: the terms are added as centre, minor-1, minor+1, major-1, major+1 (A[c] .+ A[i-1] .+ A[i+1] .+ A[j-1]
+ *          .+ A[j+1] on a column-major Julia array: i is the contiguous index);
+ * order 1: centre, major-1, major+1, minor+1, minor-1 (the order of benchmark/polybench/stencil.jl:267-287, whose
+ *          iteration updates B from A and then A from B: two sweeps of this function). */
+void rx_oracle_jacobi2d_order(float* A, float* B, int64_t n, int64_t steps, int order) {
   float *a = A, *b = B;
   for (int64_t t = 0; t < steps; ++t) {
 #pragma omp parallel for schedule(static)
     for (int64_t i = 1; i < n - 1; ++i) {
       const float* c = a + i * n;
       float* o = b + i * n;
-      for (int64_t j = 1; j < n - 1; ++j) {
-        /* evaluation order of the traced expression: centre, minor-1, minor+1, major-1, major+1 */
-        float s = c[j] + c[j - 1];
-        s = s + c[j + 1];
-        s = s + c[j - n];
-        s = s + c[j + n];
-        o[j] = 0.2f * s;
+      if (order == 0) {
+        for (int64_t j = 1; j < n - 1; ++j) {
+          float s = c[j] + c[j - 1];
+          s = s + c[j + 1];
+          s = s + c[j - n];
+          s = s + c[j + n];
+          o[j] = 0.2f * s;
+        }
+      } else {
+        for (int64_t j = 1; j < n - 1; ++j) {
+          float s = c[j] + c[j - n];
+          s = s + c[j + n];
+          s = s + c[j + 1];
+          s = s + c[j - 1];
+          o[j] = 0.2f * s;
+        }
       }
     }
     float* tmp = a; a = b; b = tmp;
@@ -104,3 +150,5 @@ void rx_oracle_jacobi2d(float* A, float* B, int64_t n, int64_t steps) {
     free(t);
   }
 }
+
+void rx_oracle_jacobi2d(float* A, float* B, int64_t n, int64_t steps) { rx_oracle_jacobi2d_order(A, B, n, steps, 0); }

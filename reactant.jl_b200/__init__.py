@@ -117,7 +117,7 @@ class Event:
 class Client:
     """MakeGPUClient wrapper (src/xla/PJRT/Client.jl, deps/ReactantExtra/API.cpp:528-582)."""
 
-    def __init__(self, node_id=0, num_nodes=1, allowed_devices=None, memory_fraction=0.9):
+    def __init__(self, node_id=0, num_nodes=1, allowed_devices=None, memory_fraction=0.9, peer_wait_ms=None):
         err = C.c_char_p()
         arr, n = None, 0
         if allowed_devices is not None:
@@ -135,6 +135,9 @@ class Client:
         n_addr = lib().ClientNumAddressableDevices(h)
         self.addressable_devices = [Device(self, lib().ClientGetAddressableDevice(h, i)) for i in range(n_addr)]
         self.devices = [Device(self, lib().ClientGetDevice(h, i)) for i in range(lib().ClientNumDevices(h))]
+        if peer_wait_ms is not None:
+            lib().RxClientSetPeerWaitMs(h, int(peer_wait_ms))
+            check()
 
     @property
     def platform_name(self):
@@ -170,6 +173,20 @@ def collectives_unique_id() -> bytes:
     lib().RxCollectivesUniqueId(buf)
     check()
     return bytes(buf)
+
+
+class PinnedArray:
+    """A numpy array over page-locked host memory (RxHostAlloc): uploads from it and downloads into it run at
+    the full PCIe rate.  Keep the object alive as long as `array` is in use; the memory is released with it."""
+
+    def __init__(self, n: int, dtype=np.float32):
+        dt = np.dtype(dtype)
+        self.nbytes = max(1, int(n) * dt.itemsize)
+        self.ptr = lib().RxHostAlloc(self.nbytes)
+        check()
+        self._fin = weakref.finalize(self, lib().RxHostFree, self.ptr)
+        raw = (C.c_uint8 * self.nbytes).from_address(self.ptr)
+        self.array = np.frombuffer(raw, dtype=dt, count=int(n))
 
 
 _default_client = None

@@ -93,7 +93,10 @@ PROTOTYPES = {
     "RxCollectivesUniqueId": (C.c_int, [U8P]),
     "RxClientInitCollectives": (C.c_int, [P, U8P]),
     "RxClientMailboxHandle": (C.c_int, [P, C.c_int, U8P]),
+    "RxClientSetPeerWaitMs": (C.c_int, [P, C.c_int64]),
     "RxClientOpenMailboxes": (C.c_int, [P, U8P, C.c_int]),
+    "RxHostAlloc": (P, [C.c_size_t]),
+    "RxHostFree": (None, [P]),
     "RxEventRecord": (P, [P]),
     "RxEventSynchronize": (None, [P]),
     "RxEventElapsedMs": (C.c_float, [P, P]),

@@ -64,10 +64,9 @@ void cck(cudaError_t e, const char* what) {
   if (e != cudaSuccess) throw Error(RX_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-constexpr long long kSpinLimit = 4000000;  // polls of ~0.25 us: about a second
-
-// One warp; lane r handles rank r.
-__global__ void k_allreduce_mailbox(float* __restrict__ val, MailTable mail, int rank, int n, unsigned epoch, int* status) {
+// One warp; lane r handles rank r.  The wait for a peer's word is bounded by `poll_limit` polls (the same
+// per-client limit the fused form in the reduce kernel uses, RxClient::peer_wait_polls).
+__global__ void k_allreduce_mailbox(float* __restrict__ val, MailTable mail, int rank, int n, unsigned epoch, int* status, long long poll_limit) {
   int lane = threadIdx.x;
   float mine = *val;
   unsigned long long word = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(mine);
@@ -84,8 +83,8 @@ __global__ void k_allreduce_mailbox(float* __restrict__ val, MailTable mail, int
     unsigned long long w = *src;
     long long spins = 0;
     while ((unsigned)(w >> 32) != epoch) {
-      if (++spins > kSpinLimit) { failed = 1; break; }
-      __nanosleep(200);
+      if (++spins > poll_limit) { failed = 1; break; }
+      __nanosleep(kPeerPollNs);
       w = *src;
     }
     got = __uint_as_float((unsigned)w);
@@ -262,6 +261,7 @@ bool prepare_fused_allreduce(RxClient* c, const Step& st, const std::vector<RxDe
     cudaSetDevice(d->ordinal);
     cudaHostGetDevicePointer(&dstatus, d->status, 0);
     ar.status = dstatus;
+    ar.poll_limit = c->peer_wait_polls();
     out->push_back(ar);
   }
   return true;
@@ -291,7 +291,7 @@ void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::funct
       bool prof = d->profiling;
       cudaEvent_t a = nullptr, b = nullptr;
       if (prof) { cudaEventCreate(&a); cudaEventCreate(&b); cudaEventRecord(a, d->stream); }
-      k_allreduce_mailbox<<<1, 32, 0, d->stream>>>((float*)ptr(k), d->mail, d->global_id, world, epoch, dstatus);
+      k_allreduce_mailbox<<<1, 32, 0, d->stream>>>((float*)ptr(k), d->mail, d->global_id, world, epoch, dstatus, c->peer_wait_polls());
       if (prof) { cudaEventRecord(b, d->stream); d->spans.push_back({"all_reduce", a, b}); }
       ++d->launches;
       cck(cudaGetLastError(), "k_allreduce_mailbox");

@@ -338,8 +338,8 @@ __device__ __forceinline__ bool mailbox_allreduce_warp(const FusedAllReduce& ar,
     unsigned long long w = *src;
     long long spins = 0;
     while ((unsigned)(w >> 32) != ar.epoch) {
-      if (++spins > 4000000) { failed = 1; break; }
-      __nanosleep(100);
+      if (++spins > ar.poll_limit) { failed = 1; break; }
+      __nanosleep(kPeerPollNs);
       w = *src;
     }
     got = __uint_as_float((unsigned)w);

@@ -212,10 +212,26 @@ void cache_store(const std::string& src, const std::vector<char>& cubin, const s
 
 }  // namespace
 
+// The generated source includes the embedded device headers by name, so the same text compiles to a different
+// kernel when they change (a struct passed by value grows a field, say).  Their fingerprint is part of the text,
+// and with it of the key of both caches.
+static const std::string& headers_fingerprint() {
+  static const std::string fp = [] {
+    uint64_t h = 1469598103934665603ull;
+    for (int k = 0; k < kEmbedCount; ++k)
+      for (const char* c = kEmbedSrc[k]; *c; ++c) h = (h ^ (unsigned char)*c) * 1099511628211ull;
+    char buf[32];
+    snprintf(buf, sizeof buf, "%016llx", (unsigned long long)h);
+    return std::string(buf);
+  }();
+  return fp;
+}
+
 std::string jit_chain_source(const VmProgram& P, int red_code, const char* family) {
   const OpText& T = op_text();
   std::string s;
   s.reserve(4096);
+  s += "// headers: " + headers_fingerprint() + "\n";
   s += "// family: ";
   s += family;
   s += "\n#define RX_CHAIN_SPECIALISED 1\n#include \"rx_chain_kernels.cuh\"\nnamespace rx {\nstruct SpecChain {\n";

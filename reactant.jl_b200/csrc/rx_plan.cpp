@@ -4,7 +4,7 @@
 //   * elementwise chain -> reduce over one axis   (row / column reductions)
 //   * max -> exp-sum -> log over the same axis     (logsumexp, one HBM read)
 //   * shifted-slice sums written into an interior (stencil updates, in place)
-//   * dot_general with elementwise epilogue       (bf16 GEMM, fp32 accumulate)
+//   * dot_general                                 (bf16 GEMM, fp32 accumulate; operand transposes folded into strides)
 //   * reduce over a mesh-sharded axis             (local reduce + all-reduce)
 // Layout shims (the reversed-dims transposes Reactant inserts at function entry
 // and exit, src/TracedUtils.jl:608-626, 846-883), reshapes, slices and
@@ -313,6 +313,8 @@ struct Planner {
   struct LseInfo { int m_slot, lse_slot; };
   std::map<int, LseInfo> lse_of_sum;  // sumexp slot -> companions
   std::set<int> state_slots_live;     // loop-carried slots (writable in place)
+
+  std::vector<int> remaining;  // per value: uses by ops that have not been planned yet (function and loop results never run out)
 
   Planner(const Module& mod, Plan& p) : m(mod), plan(p), env(mod.values.size()), uses(mod.values.size(), 0), shard(mod.values.size(), -1) {}
 
@@ -843,6 +845,19 @@ struct Planner {
     }
     memo[e.get()] = r;
     return r;
+  }
+  // Is `slot` read by a value that an op after `op` (or the enclosing region's result) still uses?  Values are lazy
+  // expressions, so a value that has been consumed only by ops planned so far no longer matters: whatever it fed
+  // either became a step already emitted or lives on inside another value, which is examined in its own right.
+  bool read_later(int slot, const Op& op) {
+    for (size_t w = 0; w < env.size(); ++w) {
+      if (!env[w]) continue;
+      int left = remaining[w] - (int)std::count(op.in.begin(), op.in.end(), (int)w);
+      if (left <= 0) continue;
+      std::set<const Expr*> seen;
+      if (reads_slot(env[w], slot, seen)) return true;
+    }
+    return false;
   }
   bool reads_slot(const ExprP& e, int slot, std::set<const Expr*>& seen) {
     if (!seen.insert(e.get()).second) return false;
@@ -1398,8 +1413,12 @@ struct Planner {
     st.red = op.red;
     st.red_dt = (dt == DT::S32) ? DT::S32 : (dt == DT::PRED ? DT::PRED : DT::F32);
     if (dt == DT::PRED && op.red == RedK::Add) st.red = RedK::Or;  // i1 addition saturates
-    st.init_f = init_f;
-    st.init_i = init_i;
+    // A reduce over the sharded dim is summed over the mesh afterwards: every device folding the init value into
+    // its local result would count it once per device, so the local reduce starts from the identity and the init
+    // value is added once, after the all-reduce.
+    const bool late_init = needs_allreduce && (init_f != 0.0 || init_i != 0);
+    st.init_f = late_init ? 0.0 : init_f;
+    st.init_i = late_init ? 0 : init_i;
     Lowering L(X->shape);
     int root = L.lower(X, Lowering::identity(X->shape.size()));
     OutSpec os{slot, rt.dt, 0, ostr, root};
@@ -1418,10 +1437,11 @@ struct Planner {
       int vop = st.red_dt == DT::F32 ? (op.red == RedK::Add ? VM_ADD : op.red == RedK::Max ? VM_MAX : op.red == RedK::Min ? VM_MIN : VM_MUL)
                                      : (st.red == RedK::Add ? VM_IADD : st.red == RedK::Max ? VM_IMAX : st.red == RedK::Min ? VM_IMIN : st.red == RedK::Mul ? VM_IMUL : st.red == RedK::Or ? VM_OR : VM_AND);
       Type xt{X->dt, X->shape};
-      ExprP e = round_if_bf16(mkop(vop, xt, {X, konst(xt, init_f, init_i)}));
+      ExprP e = late_init ? X : round_if_bf16(mkop(vop, xt, {X, konst(xt, init_f, init_i)}));
       emit_map(e, slot, 0, ostr, "reduce over unit dimensions");
       // a sharded dim whose local extent is one still has to be summed over the mesh
       if (needs_allreduce) emit_allreduce(slot, rt);
+      if (late_init) emit_late_init(slot, rt, init_f);
       return leaf(slot, rt);
     } else if (kept_n == 1) {
       st.kind = StepK::ReduceFull;
@@ -1442,7 +1462,14 @@ struct Planner {
     }
     cur->push_back(std::move(st));
     if (needs_allreduce) emit_allreduce(slot, rt);
+    if (late_init) emit_late_init(slot, rt, init_f);
     return leaf(slot, rt);
+  }
+  // slot += init, element for element, in place (the all-reduced result of a reduce whose init is not zero)
+  void emit_late_init(int slot, const Type& rt, double init_f) {
+    last_map.where = nullptr;  // must stay behind the all-reduce: never merged into an earlier map
+    emit_map(mkop(VM_ADD, rt, {leaf(slot, rt), konst(rt, init_f, 0)}), slot, 0, canon_strides(rt.shape), "init value added once, after the all-reduce");
+    last_map.where = nullptr;
   }
   void emit_allreduce(int slot, const Type& rt) {
     Step ar;
@@ -1537,7 +1564,10 @@ struct Planner {
       starts.push_back(s);
     }
     int dst = -1;
-    bool in_place = whole_slot(O) && uses[o] == 1 && slot_writable(O->slot);
+    // In place when nothing that is still to be evaluated reads the target's storage: the target itself has no later
+    // use, and every expression that looked at it (the slices of the previous half-step, say) has already been
+    // turned into a step that runs before this one.
+    bool in_place = whole_slot(O) && slot_writable(O->slot) && !read_later(O->slot, op);
     if (in_place) {
       // the update may read the destination only at the position it writes
       std::vector<const Expr*> lv;
@@ -1690,6 +1720,7 @@ struct Planner {
 
   void plan_while(const Op& op) {
     size_t n = op.in.size();
+    for (int v : op.in) --remaining[v];  // the operands are consumed on entry: the loop's storage takes their place
     const Region& cond = op.regions[0];
     const Region& body = op.regions[1];
     for (int x : op.in) if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while carrying sharded tensors");
@@ -1849,6 +1880,8 @@ struct Planner {
         case OpK::While: plan_while(op); break;
         default: throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op " + op.name);
       }
+      if (op.kind != OpK::While)
+        for (int v : op.in) --remaining[v];
     }
   }
 
@@ -1857,6 +1890,7 @@ struct Planner {
     nparts = m.num_partitions;
     plan.num_partitions = nparts;
     count_uses(f.body);
+    remaining = uses;
     int64_t mesh_size = 1;
     for (auto& kv : m.meshes)
       for (auto& ax : kv.second) mesh_size *= ax.second;

@@ -382,12 +382,28 @@ void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<Dev
       }
     }
     if (st.kind == StepK::Loop) {
-      bool whole = true;
-      for (auto& r : runs) whole = try_stencil_loop(st, r) && whole;  // all devices take the same decision: same plan, same shapes
-      if (whole) continue;
+      // Same plan and same shapes on every device, so they normally take the same decision; should one decline after
+      // others ran the whole loop, only the ones that declined go through the step-by-step form below.
+      std::vector<DevRun> rest;
+      std::vector<size_t> rest_index;
+      for (size_t k = 0; k < runs.size(); ++k)
+        if (!try_stencil_loop(st, runs[k])) { rest.push_back(std::move(runs[k])); rest_index.push_back(k); }
+      if (rest.empty()) continue;
+      for (int64_t it = 0; it < st.trip; ++it) {
+        run_steps(ex, st.body, rest);
+        for (auto& r : rest) {
+          join_all_pending(r);
+          rotate_loop_state(st, r);
+        }
+      }
+      for (size_t q = 0; q < rest.size(); ++q) runs[rest_index[q]] = std::move(rest[q]);
+      continue;
       for (int64_t it = 0; it < st.trip; ++it) {
         run_steps(ex, st.body, runs);
-        for (auto& r : runs) rotate_loop_state(st, r);
+        for (auto& r : runs) {
+          join_all_pending(r);  // in-flight all-reduces are tracked by slot, and the rotation moves storages between slots
+          rotate_loop_state(st, r);
+        }
       }
     } else if (st.kind == StepK::AllReduce) {
       // vectors (gradients) go to the communication stream so that the steps after them keep the SMs busy;
@@ -561,6 +577,7 @@ std::shared_ptr<RxDevice> make_device(RxClient* c, int ordinal, int local_id, do
   cudaDeviceProp prop;
   CK(cudaGetDeviceProperties(&prop, ordinal));
   d->sm_count = prop.multiProcessorCount;
+  d->kind = std::string(prop.name) + " (sm_" + std::to_string(prop.major) + std::to_string(prop.minor) + ")";
   d->total_mem = prop.totalGlobalMem;
   d->bytes_limit = (int64_t)((double)prop.totalGlobalMem * (fraction > 0 && fraction <= 1 ? fraction : 0.9));
   CK(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
@@ -634,6 +651,9 @@ RxClient* MakeGPUClient(int node_id, int num_nodes, int64_t* allowed_devices, in
         c->remote.push_back(d);
       }
     }
+    c->peer_wait_ms = c->num_nodes > 1 ? 8000 : 1000;
+    if (const char* w = getenv("RX_PEER_WAIT_MS"))
+      if (atoll(w) > 0) c->peer_wait_ms = std::min<int64_t>(atoll(w), 60000);
     const char* mode = getenv("RX_ALLREDUCE");
     if (mode && !strcmp(mode, "nccl")) c->allreduce_mode = 1;
     if (mode && !strcmp(mode, "mailbox")) c->allreduce_mode = 2;
@@ -703,7 +723,7 @@ RxClient* DeviceToClient(RxDevice* d) { return d ? d->client : nullptr; }
 int64_t PjRtDeviceGetLocalDeviceId(RxDevice* d) { return d->local_id; }
 int64_t PjRtDeviceGetGlobalDeviceId(RxDevice* d) { return d->global_id; }
 int64_t PjRtDeviceGetLocalHardwareId(RxDevice* d) { return d->ordinal; }
-const char* DeviceGetKind(RxDevice*) { return dup_cstr("NVIDIA B200 (sm_100a)"); }
+const char* DeviceGetKind(RxDevice* d) { return dup_cstr(d && !d->kind.empty() ? d->kind : std::string("unknown (not addressable from this process)")); }
 uint8_t pjrt_device_is_addressable(RxDevice* d) { return d && d->addressable; }
 void PjRtDeviceGetAllocatorStats(RxDevice* d, JLAllocatorStats* s) {
   std::lock_guard<std::mutex> lk(d->mu);
@@ -808,6 +828,7 @@ void* UnsafeBufferPointer(RxBuffer* b) {
     CK(cudaSetDevice(b->dev->ordinal));
     b->st->make_ready();
     CK(cudaStreamSynchronize(b->dev->stream));
+    check_device_status(b->dev);
   }
   return b->st->ptr;
   API_END(nullptr)
@@ -830,6 +851,7 @@ RxBuffer* CopyBufferToDevice(RxBuffer* b, RxDevice* dst) {
     CK(cudaMemcpyPeerAsync(o->st->ptr, dst->ordinal, b->st->ptr, b->dev->ordinal, bytes, dst->stream));
     CK(cudaStreamSynchronize(dst->stream));
     cudaEventDestroy(ev);
+    check_device_status(b->dev);
   }
   return o.release();
   API_END(nullptr)
@@ -854,6 +876,7 @@ void CopyFromBuffer(RxClient*, RxBuffer* b, void* data, size_t offset, size_t si
   b->st->make_ready();
   CK(cudaMemcpyAsync(data, (char*)b->st->ptr + offset, size, cudaMemcpyDeviceToHost, b->dev->stream));
   CK(cudaStreamSynchronize(b->dev->stream));
+  check_device_status(b->dev);
   if (bufferP) *bufferP = b;
   API_END_VOID
 }
@@ -870,7 +893,15 @@ void FutureAwait(RxFuture* f) {
   RxDevice* d = f->state->dev;
   CK(cudaSetDevice(d->ordinal));
   CK(cudaEventSynchronize(f->state->ev));
-  check_device_status(d);
+  std::lock_guard<std::mutex> g(f->state->error_mu);
+  if (f->state->error_code) throw Error(f->state->error_code, f->state->error);
+  try {
+    check_device_status(d);
+  } catch (const Error& e) {
+    f->state->error_code = e.code;
+    f->state->error = e.what();
+    throw;
+  }
   API_END_VOID
 }
 
@@ -1004,6 +1035,14 @@ void XLAExecute(RxExecutable* exec, int op_args_len, RxBuffer** op_args, uint8_t
   API_END_VOID
 }
 
+int RxClientSetPeerWaitMs(RxClient* c, int64_t ms) {
+  API_BEGIN
+  if (!c) throw Error(RX_ERR_BAD_HANDLE, "null client");
+  if (ms < 1 || ms > 60000) throw Error(RX_ERR_ARG, "the peer wait must be between 1 and 60000 ms");
+  c->peer_wait_ms = ms;
+  return 0;
+  API_END(g_code)
+}
 int RxCollectivesUniqueId(uint8_t* id128) {
   API_BEGIN
   rx::nccl_unique_id(id128);
@@ -1065,6 +1104,7 @@ void RxDeviceSynchronize(RxDevice* d) {
   CK(cudaSetDevice(d->ordinal));
   CK(cudaStreamSynchronize(d->stream));
   if (d->comm_stream) CK(cudaStreamSynchronize(d->comm_stream));
+  check_device_status(d);
   API_END_VOID
 }
 void RxDeviceJoinStreams(RxDevice* d) {
@@ -1078,6 +1118,21 @@ void RxDeviceJoinStreams(RxDevice* d) {
     cudaEventDestroy(ev);
   }
   API_END_VOID
+}
+void* RxHostAlloc(size_t bytes) {
+  API_BEGIN
+  void* p = nullptr;
+  cudaError_t e = cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocPortable);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    throw Error(RX_ERR_CUDA, std::string("cannot allocate ") + std::to_string(bytes) + " bytes of page-locked host memory: " + cudaGetErrorString(e));
+  }
+  return p;
+  API_END(nullptr)
+}
+void RxHostFree(void* p) {
+  if (p) cudaFreeHost(p);
+  cudaGetLastError();
 }
 uint64_t RxDeviceKernelLaunches(RxDevice* d) { return d->launches; }
 void RxDeviceSetProfiling(RxDevice* d, int on) { d->profiling = on != 0; }

@@ -35,6 +35,7 @@ struct RxDevice : std::enable_shared_from_this<RxDevice> {
   cudaStream_t stream = nullptr;
   cudaStream_t comm_stream = nullptr;  // vector all-reduces run here, ordered against `stream` by events
   int sm_count = 148;
+  std::string kind;   // device name and compute capability, from cudaGetDeviceProperties
   size_t total_mem = 0;
   // One execution at a time enqueues on a device: launches of different host threads must not interleave (they
   // share the reduction scratch in stream order) and the launch-side tables below are not otherwise protected.
@@ -123,6 +124,11 @@ struct RxBuffer {
 };
 
 struct EventState {
+  // A failure found when this execution was awaited (a bounded device-side wait that ran out): kept here so that
+  // every future of the execution reports it, not only the first one to look at the device's status word.
+  std::mutex error_mu;
+  int error_code = 0;
+  std::string error;
   cudaEvent_t ev = nullptr;
   RxDevice* dev = nullptr;
   std::shared_ptr<RxDevice> keep;
@@ -157,5 +163,11 @@ struct RxClient {
   bool peers_enabled = false;
   uint32_t epoch = 0;       // all-reduce sequence number (same on every rank)
   int allreduce_mode = 0;   // 0 auto, 1 nccl, 2 mailbox
+  // How long a kernel waits for a peer's word in an all-reduce mailbox before it gives up and reports
+  // RX_ERR_PEER_TIMEOUT.  Ranks that are separate processes can be far apart in host time (a cold compile cache, a
+  // garbage collection, data loading), so they get several seconds; devices driven by one process are launched
+  // back to back.  RX_PEER_WAIT_MS or RxClientSetPeerWaitMs override the default.
+  int64_t peer_wait_ms = 1000;
+  long long peer_wait_polls() const { return (long long)peer_wait_ms * 4000; }  // one poll is about 0.25 us
   int n_global() const { return (int)devices.size() * num_nodes; }
 };

@@ -95,7 +95,7 @@ enum VmOp : uint8_t {
   X(VM_NOT, ~ua)                                                                               \
   X(VM_LNOT, ua ? 0u : 1u)                                                                     \
   X(VM_I2F, f2u((float)ia))                                                                    \
-  X(VM_F2I, (a != a) ? 0u : (uint32_t)(int32_t)fminf(fmaxf(truncf(a), -2147483648.f), 2147483520.f)) \
+  X(VM_F2I, (a != a) ? 0u : (a >= 2147483648.f ? 0x7FFFFFFFu : (uint32_t)(int32_t)fmaxf(truncf(a), -2147483648.f))) \
   X(VM_P2F, f2u(ua ? 1.f : 0.f))                                                               \
   X(VM_F2P, (uint32_t)(a != 0.f))                                                              \
   X(VM_I2P, (uint32_t)(ia != 0))                                                              \
@@ -196,11 +196,13 @@ struct VmProgram {
 // full reduce (n == 0: no all-reduce).  peer[r] points at rank r's mailbox:
 // 2 x kMailRanks 64-bit slots, indexed [epoch parity][sender rank].
 constexpr int kMailRanks = 32;
+constexpr unsigned kPeerPollNs = 200;  // sleep between two polls of a mailbox word (a poll costs about 0.25 us in all)
 struct FusedAllReduce {
   unsigned long long* peer[kMailRanks];
   int rank, n;
   unsigned epoch;
   int* status;
+  long long poll_limit;  // polls of a peer's word before the wait is given up (RxClient::peer_wait_polls)
 };
 
 }  // namespace rx

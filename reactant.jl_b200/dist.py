@@ -51,7 +51,8 @@ class Dist:
             return v
         dev = "cuda" if self.backend == "nccl" else "cpu"
         t = self.torch.tensor([float(v)], dtype=self.torch.float64, device=dev)
-        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX if op == "max" else self.dist.ReduceOp.SUM)
+        ops = {"max": self.dist.ReduceOp.MAX, "min": self.dist.ReduceOp.MIN, "sum": self.dist.ReduceOp.SUM}
+        self.dist.all_reduce(t, op=ops[op])
         return float(t.item())
 
     def all_gather_bytes(self, b: bytes):

@@ -85,38 +85,52 @@ def logsumexp_dims1(rows: int, cols: int, raw: bool = False) -> str:
 
 
 def jacobi2d(n: int, steps: int, form: str = "dus") -> str:
-    """`steps` sweeps of B[2:end-1,2:end-1] = 0.2f0 .* (A[c] .+ A[n] .+ A[s] .+ A[w] .+ A[e]); A, B = B, A
-    on n x n Float32 arrays (benchmark/polybench/stencil.jl:263-289 spelling).
-    Both arrays are mutated, hence donated and aliased to the two results.
-    form="dus": interior written by dynamic_update_slice; form="pad": the
-    pad + select rewrite that Enzyme-JAX's communication patterns can produce
-    (src/compiler/OptimizationPasses.jl:356-372)."""
+    """Jacobi-2D on n x n Float32 arrays; both arrays are mutated, hence donated and aliased to the two results.
+
+    form="dus" / "pad": `steps` sweeps of
+        B[2:end-1,2:end-1] = 0.2f0 .* (A[c] .+ A[i-1] .+ A[i+1] .+ A[j-1] .+ A[j+1]); A, B = B, A
+    with the interior written by dynamic_update_slice ("dus") or by the pad + select rewrite that Enzyme-JAX's
+    communication patterns can produce ("pad", src/compiler/OptimizationPasses.jl:356-372).
+    form="halfsteps": the spelling of benchmark/polybench/stencil.jl:263-289 -- every one of the `steps`
+    iterations updates B from A and then A from B (two sweeps, no swap), the five terms added in that file's
+    order: centre, j-1, j+1, i+1, i-1."""
     t, ti = _t([n, n]), _t([n - 2, n - 2])
     m = n - 1
     # physical dims are reversed Julia dims: Julia A[i-1, j] is the minor-dim neighbour
-    sl = [f"[1:{m}, 1:{m}]", f"[1:{m}, 0:{n - 2}]", f"[1:{m}, 2:{n}]", f"[0:{n - 2}, 1:{m}]", f"[2:{n}, 1:{m}]"]
-    lines = [f"      %s{k} = stablehlo.slice %iterArg_0 {s} : ({t}) -> {ti}" for k, s in enumerate(sl)]
-    lines += [
-        f"      %a0 = stablehlo.add %s0, %s1 : {ti}",
-        f"      %a1 = stablehlo.add %a0, %s2 : {ti}",
-        f"      %a2 = stablehlo.add %a1, %s3 : {ti}",
-        f"      %a3 = stablehlo.add %a2, %s4 : {ti}",
-        f"      %u = stablehlo.multiply %cst, %a3 : {ti}",
-    ]
-    if form == "dus":
-        lines.append(f"      %nb = stablehlo.dynamic_update_slice %iterArg_1, %u, %c_1, %c_1 : ({t}, {ti}, tensor<i32>, tensor<i32>) -> {t}")
-    else:
-        lines += [
-            f"      %pu = stablehlo.pad %u, %cst_z, low = [1, 1], high = [1, 1], interior = [0, 0] : ({ti}, tensor<f32>) -> {t}",
-            f"      %nb = stablehlo.select %pm, %pu, %iterArg_1 : {_t([n, n], 'i1')}, {t}",
+    centre, i_lo, i_hi, j_lo, j_hi = f"[1:{m}, 1:{m}]", f"[1:{m}, 0:{n - 2}]", f"[1:{m}, 2:{n}]", f"[0:{n - 2}, 1:{m}]", f"[2:{n}, 1:{m}]"
+
+    def sweep(src, tag, order):
+        out = [f"      %s{tag}{k} = stablehlo.slice {src} {sl} : ({t}) -> {ti}" for k, sl in enumerate(order)]
+        out += [
+            f"      %a{tag}0 = stablehlo.add %s{tag}0, %s{tag}1 : {ti}",
+            f"      %a{tag}1 = stablehlo.add %a{tag}0, %s{tag}2 : {ti}",
+            f"      %a{tag}2 = stablehlo.add %a{tag}1, %s{tag}3 : {ti}",
+            f"      %a{tag}3 = stablehlo.add %a{tag}2, %s{tag}4 : {ti}",
+            f"      %u{tag} = stablehlo.multiply %cst, %a{tag}3 : {ti}",
         ]
-    body = "\n".join(lines)
+        return out
+
+    dus = lambda dst, upd, res: f"      {res} = stablehlo.dynamic_update_slice {dst}, {upd}, %c_1, %c_1 : ({t}, {ti}, tensor<i32>, tensor<i32>) -> {t}"
     extra = ""
-    if form != "dus":
-        extra = (f"    %cst_z = stablehlo.constant dense<0.000000e+00> : tensor<f32>\n"
-                 f"    %false = stablehlo.constant dense<false> : tensor<i1>\n"
-                 f"    %ones = stablehlo.constant dense<true> : {_t([n - 2, n - 2], 'i1')}\n"
-                 f"    %pm = stablehlo.pad %ones, %false, low = [1, 1], high = [1, 1], interior = [0, 0] : ({_t([n - 2, n - 2], 'i1')}, tensor<i1>) -> {_t([n, n], 'i1')}\n")
+    if form == "halfsteps":
+        order = [centre, j_lo, j_hi, i_hi, i_lo]
+        lines = sweep("%iterArg_0", "p", order) + [dus("%iterArg_1", "%up", "%nb")] + sweep("%nb", "q", order) + [dus("%iterArg_0", "%uq", "%na")]
+        yields = "%1, %na, %nb"
+    else:
+        lines = sweep("%iterArg_0", "", [centre, i_lo, i_hi, j_lo, j_hi])
+        if form == "dus":
+            lines.append(dus("%iterArg_1", "%u", "%nb"))
+        else:
+            lines += [
+                f"      %pu = stablehlo.pad %u, %cst_z, low = [1, 1], high = [1, 1], interior = [0, 0] : ({ti}, tensor<f32>) -> {t}",
+                f"      %nb = stablehlo.select %pm, %pu, %iterArg_1 : {_t([n, n], 'i1')}, {t}",
+            ]
+            extra = (f"    %cst_z = stablehlo.constant dense<0.000000e+00> : tensor<f32>\n"
+                     f"    %false = stablehlo.constant dense<false> : tensor<i1>\n"
+                     f"    %ones = stablehlo.constant dense<true> : {_t([n - 2, n - 2], 'i1')}\n"
+                     f"    %pm = stablehlo.pad %ones, %false, low = [1, 1], high = [1, 1], interior = [0, 0] : ({_t([n - 2, n - 2], 'i1')}, tensor<i1>) -> {_t([n, n], 'i1')}\n")
+        yields = "%1, %nb, %iterArg_0"
+    body = "\n".join(lines)
     return f"""module @reactant_jacobi2d attributes {{mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64}} {{
   func.func @main(%arg0: {t} {{tf.aliasing_output = 0 : i32}}, %arg1: {t} {{tf.aliasing_output = 1 : i32}}) -> ({t}, {t}) {{
     %c = stablehlo.constant dense<0> : tensor<i64>
@@ -131,7 +145,7 @@ def jacobi2d(n: int, steps: int, form: str = "dus") -> str:
     }} do {{
       %1 = stablehlo.add %iterArg, %c_2 : tensor<i64>
 {body}
-      stablehlo.return %1, %nb, %iterArg_0 : tensor<i64>, {t}, {t}
+      stablehlo.return {yields} : tensor<i64>, {t}, {t}
     }}
     return %0#1, %0#2 : {t}, {t}
   }}

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 def test_all_reduce_wait_runs_out_and_is_reported(rx, ref):
     # rank 0 of a 2-process mesh; both mailbox slots point at this process's own mailbox,
     # so nothing ever writes rank 1's word
-    client = rx.Client(node_id=0, num_nodes=2, allowed_devices=[0])
+    client = rx.Client(node_id=0, num_nodes=2, allowed_devices=[0], peer_wait_ms=500)
     try:
         h = client.mailbox_handles()
         assert len(h) == 64
@@ -27,7 +27,7 @@ def test_all_reduce_wait_runs_out_and_is_reported(rx, ref):
         x = np.ones(n, np.float32)
         X = rx.from_local_shards([x], (2 * n,), sh, client)
         Y = rx.from_local_shards([x], (2 * n,), sh, client)
-        r = f(X, Y)                       # enqueues; the kernel polls for about a second, then gives up
+        r = f(X, Y)                       # enqueues; the kernel polls for half a second (peer_wait_ms), then gives up
         with pytest.raises(rx.ReactantError) as e:
             float(r)
         assert e.value.code == 10 and "all-reduce" in str(e.value)
@@ -42,7 +42,7 @@ def test_all_reduce_wait_runs_out_and_is_reported(rx, ref):
 def test_future_reports_the_same_failure(rx):
     import ctypes as C
     lib = rx._lib.lib()
-    client = rx.Client(node_id=0, num_nodes=2, allowed_devices=[0])
+    client = rx.Client(node_id=0, num_nodes=2, allowed_devices=[0], peer_wait_ms=500)
     try:
         h = client.mailbox_handles()
         client.open_mailboxes(h + h)

@@ -131,3 +131,44 @@ def test_data_parallel_mlp_gradients(rx, ref, transport, monkeypatch):
             assert np.abs(g - w).max() <= 2e-2 * scale, (name, np.abs(g - w).max(), scale)
     finally:
         client.close()
+
+
+def test_sharded_reduce_with_a_nonzero_init_counts_it_once(rx, ref):
+    """reduce(+, x; init = 5) over a sharded vector: the init value must enter the result once, not once per device."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    ndev, n = 2, 1 << 12
+    client = rx.Client(allowed_devices=list(range(ndev)))
+    try:
+        text = rx.programs.sinsum_add(n, num_partitions=ndev).replace("dense<0.000000e+00> : tensor<f32>", "dense<5.000000e+00> : tensor<f32>")
+        rng = np.random.default_rng(3)
+        x = rng.uniform(-1, 1, n).astype(np.float32)
+        y = rng.uniform(-1, 1, n).astype(np.float32)
+        sh = rx.NamedSharding(rx.Mesh(client.devices, ("x",)), ("x",))
+        r = rx.compile(text, client)(rx.to_rarray(x, client, sharding=sh), rx.to_rarray(y, client, sharding=sh))
+        want = float(ref.run_module(text, [x, y])[0])
+        for b in r.data:
+            assert abs(float(b.to_host()) - want) <= 1e-4 * abs(want), (float(b.to_host()), want)
+    finally:
+        client.close()
+
+
+def test_one_process_per_gpu_mesh_matches_the_float64_sum():
+    """The deployment shape the scaling benchmark measures: two processes, one GPU each, mailboxes exchanged as
+    IPC handles, local shards uploaded by their owners.  The benchmark itself compares the all-reduced result with
+    the float64 sum of the same seeded input and exits non-zero when they disagree."""
+    import json
+    import os
+    import subprocess
+    import sys
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", "29617",
+           os.path.join(root, "bench.py"), "--gpus", "2", "--steps", "3", "--warmup", "3", "--workload", "c1_sinsum_2p24", "--no-e2e"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root, env=env)
+    assert r.returncode == 0, (r.stdout[-2000:], r.stderr[-2000:])
+    line = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")][-1]
+    assert line["n_gpus"] == 2 and line["all_reduce"] == "nvlink-mailbox"
+    assert line["parity"]["ok"] and line["parity"]["same_bits_on_every_rank"], line["parity"]

@@ -205,3 +205,41 @@ module attributes {mhlo.num_partitions = 2 : i64, mhlo.num_replicas = 1 : i64} {
 """
     kinds = [s["kind"] for s in rx.plan_describe(text)["steps"]]
     assert kinds == ["map", "all_reduce"], kinds
+
+
+def test_sharded_reduce_applies_a_nonzero_init_once(rx):
+    """sum over the mesh of (local sum + init) would count init once per device: the local reduce must start from
+    the identity and the init value be added after the all-reduce."""
+    text = rx.programs.sinsum_add(1 << 12, num_partitions=4).replace("dense<0.000000e+00> : tensor<f32>", "dense<5.000000e+00> : tensor<f32>")
+    p = rx.plan_describe(text)
+    assert kinds(p) == ["reduce_full", "all_reduce", "map"], p
+    assert "after the all-reduce" in p["steps"][2]["note"]
+    # unsharded: the init value is folded into the reduce itself, no extra step
+    p1 = rx.plan_describe(rx.programs.sinsum_add(1 << 12).replace("dense<0.000000e+00> : tensor<f32>", "dense<5.000000e+00> : tensor<f32>"))
+    assert kinds(p1) == ["reduce_full"]
+
+
+def test_jacobi_two_half_steps_plan_in_place_without_a_copy(rx):
+    """benchmark/polybench/stencil.jl:263-289 updates B from A and then A from B inside one iteration.  When the
+    second update is planned, the slices of A have already been consumed by the first (emitted) step, so A may be
+    written in place: two stencil steps, two slots, no copy."""
+    p = rx.plan_describe(rx.programs.jacobi2d(8192, 50, form="halfsteps"))
+    assert kinds(p) == ["loop"] and p["slots"] == 2
+    body = p["steps"][0]["body"]
+    assert [s["kind"] for s in body] == ["stencil", "stencil"] and all(s["chain"] == "stencil5_mul" for s in body)
+
+
+def test_update_target_that_is_still_read_later_is_copied(rx):
+    """In place only when nothing still to be evaluated reads the target: here the old array is returned too."""
+    t, ti = "tensor<8x8xf32>", "tensor<6x6xf32>"
+    text = f"""module {{
+  func.func @main(%arg0: {t} {{tf.aliasing_output = 0 : i32}}, %arg1: {ti}) -> ({t}, {t}) {{
+    %c = stablehlo.constant dense<1> : tensor<i32>
+    %0 = stablehlo.dynamic_update_slice %arg0, %arg1, %c, %c : ({t}, {ti}, tensor<i32>, tensor<i32>) -> {t}
+    %1 = stablehlo.sine %arg0 : {t}
+    return %0, %1 : {t}, {t}
+  }}
+}}
+"""
+    p = rx.plan_describe(text)
+    assert "copy" in kinds(p), p

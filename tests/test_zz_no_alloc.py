@@ -7,7 +7,9 @@ inputs and the output and the kernel's scratch is a fixed array inside the
 library.  The test calls it through the C ABI on the caller's own buffers, twice
 in a row with different data (the second call meets whatever the first one left
 in the shared scratch array), and compares each result with the regular
-compile-and-execute path on the same buffers.  This file sorts last so that a
+compile-and-execute path on the same buffers.  A larger case gives every CTA several chunks
+of the input, and the free device memory reported by the CUDA runtime is read
+before and after a call to see that none was taken.  This file sorts last so that a
 run that stops at the first failure has already run every other test; it also
 passes on its own in a fresh process.
 """
@@ -24,7 +26,16 @@ def _existing_path(rx, client, n, X, Y):
     return float(f(X, Y))
 
 
-@pytest.mark.parametrize("n", [(1 << 20) + 3, 5, 1 << 16])
+def _free_device_bytes():
+    """Free memory on the current device as the CUDA runtime reports it (a stray cudaMalloc anywhere would move it,
+    which the library's own pool counter would not see)."""
+    rt = C.CDLL("libcudart.so.12")
+    free, total = C.c_size_t(), C.c_size_t()
+    assert rt.cudaMemGetInfo(C.byref(free), C.byref(total)) == 0
+    return free.value
+
+
+@pytest.mark.parametrize("n", [(1 << 20) + 3, 5, 1 << 16, (1 << 27) + 5])
 def test_no_alloc_matches_existing_entry_point_twice_in_a_row(rx, ref, client, n):
     lib = rx._lib.lib()
     dev = client.addressable_devices[0]
@@ -38,10 +49,15 @@ def test_no_alloc_matches_existing_entry_point_twice_in_a_row(rx, ref, client, n
         X, Y = rx.to_rarray(x, client), rx.to_rarray(y, client)
         px = lib.UnsafeBufferPointer(X.data[0].handle)
         py = lib.UnsafeBufferPointer(Y.data[0].handle)
-        before = dev.allocator_stats()["num_allocs"]
+        if call == 0:  # the first call on a device resolves the scratch array's address (and may load the kernel)
+            assert lib.RxSinSumAddNoAlloc(px, py, min(n, 4096), out_ptr, stream) == 0, lib.RxLastError().decode()
+            dev.synchronize()
+        before, free_before = dev.allocator_stats()["num_allocs"], _free_device_bytes()
         rc = lib.RxSinSumAddNoAlloc(px, py, n, out_ptr, stream)
         assert rc == 0, lib.RxLastError().decode()
-        assert dev.allocator_stats()["num_allocs"] == before, "the entry point must not allocate"
+        dev.synchronize()
+        assert dev.allocator_stats()["num_allocs"] == before, "the entry point must not allocate from the library's pool"
+        assert _free_device_bytes() == free_before, "the entry point must not take device memory from the driver either"
         got = float(out.data[0].to_host())  # synchronises the stream
         want = _existing_path(rx, client, n, X, Y)
         terms = np.sin(x.astype(np.float64)) + y.astype(np.float64)
