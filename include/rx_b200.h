@@ -39,6 +39,7 @@ typedef struct RxBuffer RxBuffer;         /* stands in for xla::PjRtBuffer      
 typedef struct RxFuture RxFuture;         /* stands in for xla::Future<>              */
 typedef struct RxExecutable RxExecutable; /* stands in for xla::PjRtLoadedExecutable  */
 typedef struct RxEvent RxEvent;
+typedef struct RxOpSharding RxOpSharding; /* stands in for xla::OpSharding                */
 
 /* ---- errors ------------------------------------------------------------- */
 /* API.cpp:262.  Host-installed callback; NULL by default. */
@@ -88,6 +89,19 @@ typedef struct {
       peak_bytes_reserved, bytes_reservable_limit, largest_free_block_bytes, pool_bytes, peak_pool_bytes;
 } JLAllocatorStats; /* API.cpp:734-746 */
 void PjRtDeviceGetAllocatorStats(RxDevice* device, JLAllocatorStats* stats);
+
+/* CUDA device queries (API.cpp:841-930; callers src/xla/Device.jl:43-60, src/compiler/Compiler.jl:154,336). */
+typedef struct {
+  size_t totalGlobalMem, sharedMemPerBlock;
+  int regsPerBlock, warpSize, maxThreadsPerBlock, maxThreadsDim[3], maxGridSize[3];
+  size_t totalConstMem;
+  int major, minor, multiProcessorCount, canMapHostMemory, l2CacheSize, maxThreadsPerMultiProcessor;
+} RxDeviceProperties; /* layout of DeviceProperties, API.cpp:841-856 */
+void ReactantCudaDeviceGetProperties(RxDeviceProperties* props, int32_t device_id);
+int32_t ReactantCudaDriverGetVersion(void);
+int32_t ReactantCudaDeviceGetComputeCapalilityMajor(void);
+int32_t ReactantCudaDeviceGetComputeCapalilityMinor(void);
+int32_t ReactantCudaDeviceGetWarpSizeInThreads(void);
 
 /* ---- buffers (API.cpp:781-801, 1075-1098, 1162-1177, 1230-1252) ----------- */
 /* H2D upload.  The host memory may be reused as soon as the call returns. */
@@ -140,6 +154,42 @@ int RxExecutableResultShardedDim(RxExecutable* exec, int index);
 /* The `tf.aliasing_output` of parameter `index` (src/compiler/Compiler.jl:1103-1127):
  * the result whose storage may reuse this argument's when it is donated; -1 = none. */
 int RxExecutableParameterAlias(RxExecutable* exec, int index);
+/* The reference's own sharding getters (API.cpp:1538-1583; callers src/xla/PJRT/LoadedExecutable.jl:34-48,
+ * asserted against the traced shardings at src/compiler/Compiler.jl:1416 and src/compiler/Codegen.jl:838,1400).
+ * `num_op_shardings` must equal the number of parameters / results; each out[i] is a fresh object the caller
+ * releases with free_op_sharding.  A replicated value reports type 0 (REPLICATED); a value split along one
+ * tensor dimension over the N devices of the mesh reports type 3 (OTHER) with tile_assignment_dimensions equal to
+ * 1 everywhere except N at that dimension and tile_assignment_devices 0..N-1 -- what XLA reports for the
+ * NamedSharding of a 1-D mesh. */
+void PjRtLoadedExecutableGetParameterShardings(RxExecutable* exec, RxOpSharding** op_shardings, int32_t num_op_shardings);
+void PjRtLoadedExecutableGetOuputShardings(RxExecutable* exec, RxOpSharding** op_shardings, int32_t num_op_shardings);
+/* The OpSharding accessor family (API.cpp:2459-2590; callers src/xla/Sharding.jl:20-120).  The iota, last-tile
+ * and shard-group forms never occur for a 1-D mesh and report "absent". */
+void free_op_sharding(RxOpSharding* op_sharding);
+int32_t op_sharding_to_op_sharding_type(RxOpSharding* op_sharding);
+int32_t op_sharding_to_shard_group_type(RxOpSharding* op_sharding);
+int32_t op_sharding_to_shard_group_id(RxOpSharding* op_sharding);
+uint8_t op_sharding_is_shard_group(RxOpSharding* op_sharding);
+uint8_t op_sharding_replicate_on_last_tile_dim(RxOpSharding* op_sharding);
+uint8_t op_sharding_has_last_tile_dims(RxOpSharding* op_sharding);
+int32_t op_sharding_last_tile_dims_size(RxOpSharding* op_sharding);
+void op_sharding_last_tile_dims(RxOpSharding* op_sharding, int32_t* last_tile_dims);
+uint8_t op_sharding_has_iota_reshape_dims(RxOpSharding* op_sharding);
+int32_t op_sharding_iota_reshape_dims_size(RxOpSharding* op_sharding);
+void op_sharding_iota_reshape_dims(RxOpSharding* op_sharding, int32_t* iota_reshape_dims);
+uint8_t op_sharding_has_iota_transpose_perm(RxOpSharding* op_sharding);
+int32_t op_sharding_iota_transpose_perm_size(RxOpSharding* op_sharding);
+void op_sharding_iota_transpose_perm(RxOpSharding* op_sharding, int32_t* iota_transpose_perm);
+uint8_t op_sharding_has_tile_assignment_dimensions(RxOpSharding* op_sharding);
+int32_t op_sharding_tile_assignment_dimensions_size(RxOpSharding* op_sharding);
+void op_sharding_tile_assignment_dimensions(RxOpSharding* op_sharding, int32_t* tile_assignment_dimensions);
+uint8_t op_sharding_has_tile_assignment_devices(RxOpSharding* op_sharding);
+int32_t op_sharding_tile_assignment_devices_size(RxOpSharding* op_sharding);
+void op_sharding_tile_assignment_devices(RxOpSharding* op_sharding, int32_t* tile_assignment_devices);
+/* API.cpp:2064-2071; called unconditionally after every compile (src/compiler/Compiler.jl:1360,
+ * src/xla/PJRT/LoadedExecutable.jl:50-60).  This engine keeps no HLO: *nmodules is set to 0 and nothing is
+ * written to hlo_modules (RxExecutableDescribe is the way to look at what was built). */
+void PjRtLoadedExecutableGetHloModules(RxExecutable* exec, void** hlo_modules, int32_t* nmodules);
 /* JSON description of the launch plan (fusion groups, chosen kernels); the
  * analogue of dumping the compiled HLO (PjRtLoadedExecutableGetHloModules,
  * src/xla/PJRT/LoadedExecutable.jl:50-60).  Caller frees. */
@@ -188,6 +238,17 @@ void XLAExecuteSharded(RxExecutable* exec, int num_args, RxBuffer** op_args, RxD
  * out [device][arg], op_results [device][result]; is_arg_donatable is per arg. */
 void XLAExecute(RxExecutable* exec, int op_args_len, RxBuffer** op_args, uint8_t* is_arg_donatable,
                 int num_results, RxBuffer** op_results, uint8_t* futures, RxFuture** future_results);
+
+/* ---- living beside another runtime (no counterpart in the reference) ----------
+ * A Julia session that loads this engine still has Reactant's XLA CPU client, and both answer to the same
+ * entry-point names.  RxOwns tells whether `handle` (client, device, buffer, future or executable) was handed
+ * out by this library and has not been freed; the binding routes every call by it.  The two execute entry
+ * points can be reached without passing through the binding (Reactant's generated thunks call them by symbol,
+ * src/xla/PJRT/LoadedExecutable.jl:85-246): once the host has registered the other runtime's functions here, an
+ * executable that is not this library's is passed on to them untouched.  That is routing between two
+ * runtimes, not a fallback: a module this engine cannot run still fails at compile time. */
+uint8_t RxOwns(const void* handle);
+void RxSetForeignExecute(void* xla_execute_sharded, void* xla_execute);
 
 /* ---- allocation-free entry point (no counterpart in the reference) -----------
  * out_dev[0] = sum(sin(x_dev[i]) + y_dev[i], i < n), computed on `stream`

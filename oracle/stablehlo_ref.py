@@ -369,6 +369,19 @@ class Interpreter:
             (shape, et), = _types_after_colon(text)
             idx = np.arange(shape[d]).reshape([-1 if k == d else 1 for k in range(len(shape))])
             return make(np.broadcast_to(idx, shape), et)
+        if name == "enzymexla.math.gelu":
+            # ext/ReactantNNlibExt/Implementations.jl:12-25 -> src/Ops.jl:4153-4175; evaluated in float64 from the
+            # closed forms (the engine expands it into elementwise ops, rounding after each)
+            x = env[re.search(r"%[\w#.$-]+", text[len(name):]).group(0)]
+            (shape, et) = _types_after_colon(text)[-1]
+            v = _wide(x)
+            if "TANH" in text:
+                r = 0.5 * v * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (v + 0.044715 * v ** 3)))
+            elif "SIGMOID" in text:
+                r = v / (1.0 + np.exp(-1.702 * v))
+            else:
+                raise NotImplementedError("enzymexla.math.gelu NONE")
+            return make(r, et)
         if short in _UNARY:
             (x,) = _operands(text, env, len(name))
             (shape, et), = _types_after_colon(text)

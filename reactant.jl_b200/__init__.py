@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import ctypes as C
 import json
+import os
 import weakref
 
 import numpy as np
@@ -119,6 +120,9 @@ class Client:
 
     def __init__(self, node_id=0, num_nodes=1, allowed_devices=None, memory_fraction=0.9, peer_wait_ms=None):
         err = C.c_char_p()
+        if allowed_devices is None and os.environ.get("REACTANT_VISIBLE_GPU_DEVICES"):
+            # the list Reactant reads at start-up and passes to MakeGPUClient as allowed_devices (src/xla/XLA.jl:230-233)
+            allowed_devices = [int(v) for v in os.environ["REACTANT_VISIBLE_GPU_DEVICES"].split(",") if v.strip()]
         arr, n = None, 0
         if allowed_devices is not None:
             n = len(allowed_devices)

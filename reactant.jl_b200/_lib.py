@@ -82,6 +82,35 @@ PROTOTYPES = {
     "RxExecutableResultShardedDim": (C.c_int, [P, C.c_int]),
     "RxExecutableParameterAlias": (C.c_int, [P, C.c_int]),
     "RxExecutableDescribe": (P, [P]),
+    "PjRtLoadedExecutableGetParameterShardings": (None, [P, PP, C.c_int32]),
+    "PjRtLoadedExecutableGetOuputShardings": (None, [P, PP, C.c_int32]),
+    "PjRtLoadedExecutableGetHloModules": (None, [P, PP, C.POINTER(C.c_int32)]),
+    "free_op_sharding": (None, [P]),
+    "op_sharding_to_op_sharding_type": (C.c_int32, [P]),
+    "op_sharding_to_shard_group_type": (C.c_int32, [P]),
+    "op_sharding_to_shard_group_id": (C.c_int32, [P]),
+    "op_sharding_is_shard_group": (C.c_uint8, [P]),
+    "op_sharding_replicate_on_last_tile_dim": (C.c_uint8, [P]),
+    "op_sharding_has_last_tile_dims": (C.c_uint8, [P]),
+    "op_sharding_last_tile_dims_size": (C.c_int32, [P]),
+    "op_sharding_last_tile_dims": (None, [P, C.POINTER(C.c_int32)]),
+    "op_sharding_has_iota_reshape_dims": (C.c_uint8, [P]),
+    "op_sharding_iota_reshape_dims_size": (C.c_int32, [P]),
+    "op_sharding_iota_reshape_dims": (None, [P, C.POINTER(C.c_int32)]),
+    "op_sharding_has_iota_transpose_perm": (C.c_uint8, [P]),
+    "op_sharding_iota_transpose_perm_size": (C.c_int32, [P]),
+    "op_sharding_iota_transpose_perm": (None, [P, C.POINTER(C.c_int32)]),
+    "op_sharding_has_tile_assignment_dimensions": (C.c_uint8, [P]),
+    "op_sharding_tile_assignment_dimensions_size": (C.c_int32, [P]),
+    "op_sharding_tile_assignment_dimensions": (None, [P, C.POINTER(C.c_int32)]),
+    "op_sharding_has_tile_assignment_devices": (C.c_uint8, [P]),
+    "op_sharding_tile_assignment_devices_size": (C.c_int32, [P]),
+    "op_sharding_tile_assignment_devices": (None, [P, C.POINTER(C.c_int32)]),
+    "ReactantCudaDeviceGetProperties": (None, [P, C.c_int32]),
+    "ReactantCudaDriverGetVersion": (C.c_int32, []),
+    "ReactantCudaDeviceGetComputeCapalilityMajor": (C.c_int32, []),
+    "ReactantCudaDeviceGetComputeCapalilityMinor": (C.c_int32, []),
+    "ReactantCudaDeviceGetWarpSizeInThreads": (C.c_int32, []),
     "RxPlanDescribe": (P, [C.c_char_p, C.c_size_t]),
     "RxPlanCacheHits": (C.c_int64, []),
     "RxChainSpecialiser": (None, [C.c_int64]),
@@ -89,6 +118,8 @@ PROTOTYPES = {
     "RxPlanSpecialiseCheck": (P, [C.c_char_p, C.c_size_t]),
     "XLAExecuteSharded": (None, [P, C.c_int, PP, P, U8P, C.c_int, PP, U8P, PP]),
     "XLAExecute": (None, [P, C.c_int, PP, U8P, C.c_int, PP, U8P, PP]),
+    "RxOwns": (C.c_uint8, [P]),
+    "RxSetForeignExecute": (None, [P, P]),
     "RxSinSumAddNoAlloc": (C.c_int, [P, P, C.c_int64, P, P]),
     "RxCollectivesUniqueId": (C.c_int, [U8P]),
     "RxClientInitCollectives": (C.c_int, [P, U8P]),

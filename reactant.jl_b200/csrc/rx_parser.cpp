@@ -519,6 +519,77 @@ struct Parser {
     region.ops.push_back(std::move(op));
   }
 
+  // enzymexla.math.gelu (what NNlib's gelu / gelu_tanh / gelu_sigmoid trace to: ext/ReactantNNlibExt/Implementations.jl:12-25,
+  // src/Ops.jl:4153-4175).  Reactant's own pipeline lowers it to elementwise ops before the runtime sees the module
+  // (`lower-enzymexla-math`, src/compiler/Compiler.jl:417); a module that still carries it is expanded here the same
+  // way, so that it fuses like any other chain:
+  //   TANH     0.5 * x * (1 + tanh(sqrt(2/pi) * (x + 0.044715 * x^3)))
+  //   SIGMOID  x * logistic(1.702 * x)
+  // The exact form (NONE) needs erf, which the chain machine does not have: refused by name.
+  void parse_math_gelu(Region& region, const std::vector<std::string>& res, int line, bool generic) {
+    int x;
+    std::string attrs;
+    if (generic) {
+      expect("(");
+      x = use();
+      expect(")");
+      ws();
+      if (peek("<")) { expect("<"); attrs = balanced_text('{', '}'); expect(">"); }
+      else if (peek("{")) attrs = balanced_text('{', '}');
+    } else {
+      x = use();
+      ws();
+      if (peek("{")) attrs = balanced_text('{', '}');
+    }
+    std::vector<Type> ins, outs;
+    signature(&ins, &outs);
+    if (res.size() != 1 || outs.size() != 1) fail(RX_ERR_PARSE, "enzymexla.math.gelu has one result");
+    const Type t = outs[0];
+    if (!dt_is_float(t.dt)) fail(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type in enzymexla.math.gelu");
+    const bool tanh_form = attrs.find("TANH") != std::string::npos, sigmoid_form = attrs.find("SIGMOID") != std::string::npos;
+    if (!tanh_form && !sigmoid_form) fail(RX_ERR_UNSUPPORTED_OP, "unsupported op enzymexla.math.gelu with gelu_approximation NONE (erf)");
+    int counter = 0;
+    auto fresh = [&]() { return m->new_value(t, res[0] + "$gelu" + std::to_string(counter++)); };
+    auto konst = [&](double v) {
+      Op c;
+      c.kind = OpK::Constant;
+      c.name = "stablehlo.constant";
+      c.line = line;
+      c.splat = true;
+      c.fval = v;
+      c.out.push_back(fresh());
+      region.ops.push_back(c);
+      return c.out[0];
+    };
+    auto emit = [&](OpK kind, const char* name, int vmop, std::vector<int> in, int out = -1) {
+      Op o;
+      o.kind = kind;
+      o.name = name;
+      o.line = line;
+      o.ew = vmop;
+      o.in = std::move(in);
+      o.out.push_back(out >= 0 ? out : fresh());
+      region.ops.push_back(o);
+      return o.out[0];
+    };
+    const int result = define(res[0], t);
+    if (tanh_form) {
+      int x2 = emit(OpK::Binary, "stablehlo.multiply", VM_MUL, {x, x});
+      int x3 = emit(OpK::Binary, "stablehlo.multiply", VM_MUL, {x2, x});
+      int t0 = emit(OpK::Binary, "stablehlo.multiply", VM_MUL, {konst(0.044715), x3});
+      int t1 = emit(OpK::Binary, "stablehlo.add", VM_ADD, {x, t0});
+      int t2 = emit(OpK::Binary, "stablehlo.multiply", VM_MUL, {konst(0.7978845608028654), t1});
+      int th = emit(OpK::Unary, "stablehlo.tanh", VM_TANH, {t2});
+      int t3 = emit(OpK::Binary, "stablehlo.add", VM_ADD, {konst(1.0), th});
+      int t4 = emit(OpK::Binary, "stablehlo.multiply", VM_MUL, {konst(0.5), x});
+      emit(OpK::Binary, "stablehlo.multiply", VM_MUL, {t4, t3}, result);
+    } else {
+      int t0 = emit(OpK::Binary, "stablehlo.multiply", VM_MUL, {konst(1.702), x});
+      int sg = emit(OpK::Unary, "stablehlo.logistic", VM_LOGISTIC, {t0});
+      emit(OpK::Binary, "stablehlo.multiply", VM_MUL, {x, sg}, result);
+    }
+  }
+
   void parse_op(Region& region, bool* saw_return) {
     ws();
     int line = line_at(p);
@@ -539,12 +610,20 @@ struct Parser {
     if (peek("\"")) {
       size_t e = s.find('"', p + 1);
       std::string quoted = s.substr(p, e - p + 1);
-      if (quoted != "\"stablehlo.reduce_window\"") fail(RX_ERR_UNSUPPORTED_OP, "unsupported op (generic form) " + quoted);
       p = e + 1;
+      if (quoted == "\"enzymexla.math.gelu\"") {
+        parse_math_gelu(region, res, line, true);
+        return;
+      }
+      if (quoted != "\"stablehlo.reduce_window\"") fail(RX_ERR_UNSUPPORTED_OP, "unsupported op (generic form) " + quoted);
       parse_reduce_window(region, res, line);
       return;
     }
     std::string name = ident();
+    if (name == "enzymexla.math.gelu") {
+      parse_math_gelu(region, res, line, false);
+      return;
+    }
     Op op;
     op.name = name;
     op.line = line;
@@ -692,6 +771,8 @@ struct Parser {
       }
       expect("contracting_dims"); expect("=");
       op.lcontract = int_list(); expect("x"); op.rcontract = int_list();
+      std::string algorithm;
+      bool has_algorithm = false;
       while (accept(",")) {
         if (accept_kw("precision")) {
           expect("=");
@@ -701,14 +782,32 @@ struct Parser {
         } else if (accept_kw("algorithm")) {
           expect("=");
           std::string al = balanced_text('<', '>');
-          if (al.find("accumulation_type = f32") == std::string::npos)
-            fail(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general with algorithm <" + al + ">");
+          algorithm = al;
+          has_algorithm = true;
         } else {
           fail(RX_ERR_PARSE, "unexpected dot_general attribute near '" + s.substr(p, 24) + "'");
         }
       }
       maybe_attr_dict();
       signature(&ins, &outs);
+      if (has_algorithm) {
+        // What the kernels compute is one pass over the operands in their own element type with float32
+        // accumulation: the presets F32_F32_F32 on f32 operands and BF16_BF16_F32 on bf16 operands
+        // (src/Configuration.jl:216-238, 346-348).  Multi-pass (X3 / X6 / X9), reduced-precision accumulation and
+        // mismatched operand types are refused.
+        auto field = [&](const char* key) {
+          size_t q = algorithm.find(std::string(key) + " = ");
+          if (q == std::string::npos) return std::string();
+          q += strlen(key) + 3;
+          size_t e = algorithm.find_first_of(",>", q);
+          return trim(algorithm.substr(q, e == std::string::npos ? std::string::npos : e - q));
+        };
+        const std::string want = ins.empty() ? "" : dt_name(ins[0].dt);
+        const bool ok = field("accumulation_type") == "f32" && field("lhs_precision_type") == want && field("rhs_precision_type") == want &&
+                        field("lhs_component_count") == "1" && field("rhs_component_count") == "1" && field("num_primitive_operations") == "1" &&
+                        field("allow_imprecise_accumulation") == "false";
+        if (!ok) fail(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general with algorithm <" + algorithm + "> on " + want + " operands");
+      }
       finish(op, res, outs);
     } else if (shortn == "reduce") {
       op.kind = OpK::Reduce;

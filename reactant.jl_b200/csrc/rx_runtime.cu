@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <cmath>
 #include <sstream>
+#include <unordered_set>
 
 #include "../../include/rx_b200.h"
 #include "rx_collective.h"
@@ -46,6 +47,24 @@ struct CudaError : Error {
     cudaError_t e__ = (call);                      \
     if (e__ != cudaSuccess) throw CudaError(e__, #call); \
   } while (0)
+
+// Every handle this library has handed out and not yet been asked to free.  A host that runs this engine next to
+// another runtime behind the same entry-point names (Reactant's XLA CPU client in the same Julia session) asks
+// RxOwns before routing a call.
+std::mutex g_own_mu;
+std::unordered_set<const void*> g_owned;
+template <class T>
+T* own(T* p) {
+  if (p) {
+    std::lock_guard<std::mutex> g(g_own_mu);
+    g_owned.insert(p);
+  }
+  return p;
+}
+void disown(const void* p) {
+  std::lock_guard<std::mutex> g(g_own_mu);
+  g_owned.erase(p);
+}
 
 char* dup_cstr(const std::string& s) {
   char* p = (char*)malloc(s.size() + 1);
@@ -544,14 +563,14 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
     CK(cudaEventRecord(es->ev, d->stream));
     for (int j = 0; j < num_results; ++j) {
       const ResultBinding& rb = p.results[j];
-      auto* b = new RxBuffer();
+      auto* b = own(new RxBuffer());
       b->st = runs[k].table[rb.slot];
       b->dt = rb.type.dt;
       b->dims = rb.type.shape;
       b->dev = d;
       results[k * num_results + j] = b;
       if (future_results) {
-        auto* f = new RxFuture();
+        auto* f = own(new RxFuture());
         auto lt = late[k].find(rb.slot);
         f->state = lt != late[k].end() ? lt->second : es;
         future_results[k * num_results + j] = f;
@@ -657,7 +676,9 @@ RxClient* MakeGPUClient(int node_id, int num_nodes, int64_t* allowed_devices, in
     const char* mode = getenv("RX_ALLREDUCE");
     if (mode && !strcmp(mode, "nccl")) c->allreduce_mode = 1;
     if (mode && !strcmp(mode, "mailbox")) c->allreduce_mode = 2;
-    return c.release();
+    for (auto& d : c->devices) own(d.get());
+    for (auto& d : c->remote) own(d.get());
+    return own(c.release());
   } catch (const Error& e) {
     g_err = e.what();
     g_code = e.code;
@@ -669,6 +690,9 @@ RxClient* MakeGPUClient(int node_id, int num_nodes, int64_t* allowed_devices, in
 void FreeClient(RxClient* client) {
   if (!client) return;
   clear_error();
+  disown(client);
+  for (auto& d : client->devices) disown(d.get());
+  for (auto& d : client->remote) disown(d.get());
   rx::destroy_collectives(client);
   for (auto& d : client->devices) {
     cudaSetDevice(d->ordinal);
@@ -769,7 +793,7 @@ static RxBuffer* new_buffer(RxDevice* d, uint64_t ptype, size_t ndim, const int6
   }
   size_t bytes = b->bytes();
   b->st = std::make_shared<Storage>(d, d->alloc(bytes), bytes);
-  return b.release();
+  return own(b.release());
 }
 
 RxBuffer* ArrayFromHostBuffer(RxClient* client, void* data, uint64_t ptype, size_t ndim, const int64_t* dims, RxDevice* device) {
@@ -794,7 +818,10 @@ RxBuffer* UninitPJRTBuffer(RxClient* client, RxDevice* device, uint64_t ptype, u
   API_END(nullptr)
 }
 
-void PjRtBufferFree(RxBuffer* b) { delete b; }
+void PjRtBufferFree(RxBuffer* b) {
+  disown(b);
+  delete b;
+}
 const int64_t* BufferShape(RxBuffer* b) { return b->dims.data(); }
 int64_t BufferNDimensions(RxBuffer* b) { return (int64_t)b->dims.size(); }
 int BufferPrimitiveType(RxBuffer* b) { return (int)b->dt; }
@@ -881,7 +908,10 @@ void CopyFromBuffer(RxClient*, RxBuffer* b, void* data, size_t offset, size_t si
   API_END_VOID
 }
 
-void FreeFuture(RxFuture* f) { delete f; }
+void FreeFuture(RxFuture* f) {
+  disown(f);
+  delete f;
+}
 uint8_t FutureIsReady(RxFuture* f) {
   if (!f || !f->state) return 1;
   cudaSetDevice(f->state->dev->ordinal);
@@ -947,7 +977,7 @@ RxExecutable* ClientCompileText(RxClient* client, const char* text, size_t len, 
       fclose(f);
     }
   }
-  return ex.release();
+  return own(ex.release());
   API_END(nullptr)
 }
 
@@ -1003,7 +1033,10 @@ void RxChainSpecialiserStats(int64_t* out5) {
   if (out5) rx::jit_stats(out5);
 }
 
-void ExecutableFree(RxExecutable* e) { delete e; }
+void ExecutableFree(RxExecutable* e) {
+  disown(e);
+  delete e;
+}
 RxClient* PjRtLoadedExecutableGetClient(RxExecutable* e) { return e->client; }
 int PjRtLoadedExecutableNumReplicas(RxExecutable*) { return 1; }
 int PjRtLoadedExecutableNumPartitions(RxExecutable* e) { return (int)e->plan->num_partitions; }
@@ -1014,8 +1047,26 @@ int RxExecutableResultShardedDim(RxExecutable* e, int i) { return e->plan->resul
 int RxExecutableParameterAlias(RxExecutable* e, int i) { return e->plan->arg_alias.at(i); }
 const char* RxExecutableDescribe(RxExecutable* e) { return dup_cstr(e->plan->describe()); }
 
+uint8_t RxOwns(const void* handle) {
+  std::lock_guard<std::mutex> g(g_own_mu);
+  return g_owned.count(handle) ? 1 : 0;
+}
+
+typedef void (*ExecShardedFn)(void*, int, void**, void*, uint8_t*, int, void**, uint8_t*, void**);
+typedef void (*ExecFn)(void*, int, void**, uint8_t*, int, void**, uint8_t*, void**);
+static ExecShardedFn g_other_execute_sharded = nullptr;
+static ExecFn g_other_execute = nullptr;
+void RxSetForeignExecute(void* execute_sharded, void* execute) {
+  g_other_execute_sharded = (ExecShardedFn)execute_sharded;
+  g_other_execute = (ExecFn)execute;
+}
+
 void XLAExecuteSharded(RxExecutable* exec, int num_args, RxBuffer** op_args, RxDevice* device, uint8_t* is_arg_donatable, int num_results,
                        RxBuffer** op_results, uint8_t* futures, RxFuture** future_results) {
+  if (g_other_execute_sharded && exec && !RxOwns(exec)) {  // another runtime's executable: not ours to run
+    g_other_execute_sharded(exec, num_args, (void**)op_args, device, is_arg_donatable, num_results, (void**)op_results, futures, (void**)future_results);
+    return;
+  }
   API_BEGIN
   if (!exec || !device) throw Error(RX_ERR_BAD_HANDLE, "null executable or device");
   execute(exec, {device}, op_args, num_args, is_arg_donatable, num_results, op_results, futures, future_results);
@@ -1024,6 +1075,10 @@ void XLAExecuteSharded(RxExecutable* exec, int num_args, RxBuffer** op_args, RxD
 
 void XLAExecute(RxExecutable* exec, int op_args_len, RxBuffer** op_args, uint8_t* is_arg_donatable, int num_results, RxBuffer** op_results,
                 uint8_t* futures, RxFuture** future_results) {
+  if (g_other_execute && exec && !RxOwns(exec)) {
+    g_other_execute(exec, op_args_len, (void**)op_args, is_arg_donatable, num_results, (void**)op_results, futures, (void**)future_results);
+    return;
+  }
   API_BEGIN
   if (!exec) throw Error(RX_ERR_BAD_HANDLE, "null executable");
   std::vector<RxDevice*> devs;

@@ -276,3 +276,108 @@ def scan(xla_dims, xla_axis: int, kind: str = "add", et: str = "f32") -> str:
   }}
 }}
 """
+
+
+class _Body:
+    """Emits the ops of a loop body line by line, naming results %v0, %v1, ..."""
+
+    def __init__(self):
+        self.lines, self.n = [], 0
+
+    def op(self, text, ty):
+        name = f"%v{self.n}"
+        self.n += 1
+        self.lines.append(f"      {name} = {text} : {ty}")
+        return name
+
+    def slice(self, src, ranges, t_in, t_out):
+        name = f"%v{self.n}"
+        self.n += 1
+        spec = ", ".join(f"{a}:{b}" for a, b in ranges)
+        self.lines.append(f"      {name} = stablehlo.slice {src} [{spec}] : ({t_in}) -> {t_out}")
+        return name
+
+    def dus(self, dst, upd, starts, t, tu):
+        name = f"%v{self.n}"
+        self.n += 1
+        idx = ", ".join(starts)
+        types = ", ".join([t, tu] + ["tensor<i32>"] * len(starts))
+        self.lines.append(f"      {name} = stablehlo.dynamic_update_slice {dst}, {upd}, {idx} : ({types}) -> {t}")
+        return name
+
+
+def _two_array_loop(name, shape, steps, consts, body_lines, yield_a, yield_b):
+    t = _t(shape)
+    cs = "\n".join(f"    {n} = stablehlo.constant dense<{v}> : {ty}" for n, v, ty in consts)
+    body = "\n".join(body_lines)
+    return f"""module @reactant_{name} attributes {{mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64}} {{
+  func.func @main(%arg0: {t} {{tf.aliasing_output = 0 : i32}}, %arg1: {t} {{tf.aliasing_output = 1 : i32}}) -> ({t}, {t}) {{
+    %c = stablehlo.constant dense<0> : tensor<i64>
+    %c_0 = stablehlo.constant dense<{steps}> : tensor<i64>
+    %c_2 = stablehlo.constant dense<1> : tensor<i64>
+    %c_1 = stablehlo.constant dense<1> : tensor<i32>
+{cs}
+    %0:3 = stablehlo.while(%iterArg = %c, %iterArg_0 = %arg0, %iterArg_1 = %arg1) : tensor<i64>, {t}, {t} attributes {{enzyme.disable_mincut}}
+     cond {{
+      %1 = stablehlo.compare  LT, %iterArg, %c_0 : (tensor<i64>, tensor<i64>) -> tensor<i1>
+      stablehlo.return %1 : tensor<i1>
+    }} do {{
+      %1 = stablehlo.add %iterArg, %c_2 : tensor<i64>
+{body}
+      stablehlo.return %1, {yield_a}, {yield_b} : tensor<i64>, {t}, {t}
+    }}
+    return %0#1, %0#2 : {t}, {t}
+  }}
+}}
+"""
+
+
+def jacobi1d(n: int, steps: int) -> str:
+    """benchmark/polybench/stencil.jl:201-221 (jacobi_1d_vectorized): per iteration
+    B[2:N-1] = (1/3) .* (A[1:N-2] .+ A[2:N-1] .+ A[3:N]), then the same from B into A."""
+    t, ti = _t([n]), _t([n - 2])
+    b = _Body()
+
+    def half(src, dst):
+        l, c, r = (b.slice(src, [(k, n - 2 + k)], t, ti) for k in range(3))
+        s = b.op(f"stablehlo.add {l}, {c}", ti)
+        s = b.op(f"stablehlo.add {s}, {r}", ti)
+        u = b.op(f"stablehlo.multiply %third, {s}", ti)
+        return b.dus(dst, u, ["%c_1"], t, ti)
+
+    nb = half("%iterArg_0", "%iterArg_1")
+    na = half(nb, "%iterArg_0")
+    third = repr(float(__import__("numpy").float32(1.0 / 3.0)))
+    return _two_array_loop("jacobi1d", [n], steps, [("%third", f"{float(third):.9e}", ti)], b.lines, na, nb)
+
+
+def heat3d(n: int, steps: int) -> str:
+    """benchmark/polybench/stencil.jl:125-169 (heat_3d_vectorized): per iteration the 7-point update
+    0.125*(x[i+1] - 2x + x[i-1]) + 0.125*(x[j+1] - 2x + x[j-1]) + 0.125*(x[k+1] - 2x + x[k-1]) + x of the interior,
+    from A into B and then from B into A.  Julia dim 1 (i) is the contiguous, i.e. last, tensor dim."""
+    t, ti = _t([n, n, n]), _t([n - 2, n - 2, n - 2])
+    b = _Body()
+    m = n - 1
+
+    def sl(src, dk, dj, di):  # offsets along Julia k, j, i = tensor dims 0, 1, 2
+        return b.slice(src, [(1 + dk, m + dk), (1 + dj, m + dj), (1 + di, m + di)], t, ti)
+
+    def half(src, dst):
+        c = sl(src, 0, 0, 0)
+        terms = []
+        for axis in ("i", "j", "k"):
+            d = {"i": (0, 0, 1), "j": (0, 1, 0), "k": (1, 0, 0)}[axis]
+            hi = sl(src, *d)
+            lo = sl(src, *(-x for x in d))
+            two_c = b.op(f"stablehlo.multiply %two, {c}", ti)
+            s = b.op(f"stablehlo.subtract {hi}, {two_c}", ti)
+            s = b.op(f"stablehlo.add {s}, {lo}", ti)
+            terms.append(b.op(f"stablehlo.multiply %eighth, {s}", ti))
+        s = b.op(f"stablehlo.add {terms[0]}, {terms[1]}", ti)
+        s = b.op(f"stablehlo.add {s}, {terms[2]}", ti)
+        s = b.op(f"stablehlo.add {s}, {c}", ti)
+        return b.dus(dst, s, ["%c_1", "%c_1", "%c_1"], t, ti)
+
+    nb = half("%iterArg_0", "%iterArg_1")
+    na = half(nb, "%iterArg_0")
+    return _two_array_loop("heat3d", [n, n, n], steps, [("%two", "2.000000e+00", ti), ("%eighth", "1.250000e-01", ti)], b.lines, na, nb)
