@@ -34,6 +34,18 @@ __device__ __forceinline__ void put4(uint32_t* d, uint32_t x, uint32_t y, uint32
 #endif
 }
 
+// Programmatic dependent launch.  A full reduce is launched with the "programmatic stream serialization"
+// attribute, so its CTAs may start while the kernel in front of it on the stream is still running; everything it
+// shares with that kernel (the partials scratch, the ticket, its output word, a mailbox) is touched only after
+// `pdl_wait`, which returns once the kernel in front has completed and its writes are visible.  With `early`
+// set by the host -- none of this launch's operands is written by the kernel in front -- the operand loads and
+// the arithmetic come before the wait, so the main loop of this launch overlaps the cross-CTA combine and the
+// drain of the previous one.  `pdl_release` lets the kernel behind this one start; it comes after this kernel's own
+// wait, so at most two kernels of such a chain are ever in flight together.  Launched without the attribute
+// both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Second pass of the cross-CTA combine, run by whichever CTA finishes last: it adds
 // the per-CTA partials in index order, so the result does not depend on which CTA
 // that is.  `ticket` counts finished CTAs and is reset for the next launch.
@@ -231,8 +243,12 @@ __global__ void __launch_bounds__(kThreads) k_map_rows(const __grid_constant__ V
 // full reduce over [rows][cols], 4 columns per thread
 template <class C>
 __global__ void __launch_bounds__(kThreads) k_reduce_full_rows(const __grid_constant__ VmProgram P, int64_t rows, int64_t cols, int code_arg, uint32_t* __restrict__ partials,
-                                                               unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar) {
+                                                               unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar, int early) {
   const int code = C::red_code(code_arg);
+  if (!early) {
+    pdl_wait();
+    pdl_release();
+  }
   __shared__ uint32_t sm[kThreads / 32];
   const int64_t c4 = cols >> 2, total = rows * c4;
   const int64_t stride = (int64_t)gridDim.x * kThreads;
@@ -251,6 +267,10 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_rows(const __grid_cons
   }
   uint32_t v = red_combine(code, red_combine(code, acc[0], acc[1]), red_combine(code, acc[2], acc[3]));
   v = block_red<kThreads>(code, v, sm);
+  if (early) {
+    pdl_wait();
+    pdl_release();
+  }
   finish_in_last_block(v, partials, ticket, code, init_bits, C::out(P, 0), sm, ar);
 }
 
@@ -280,8 +300,12 @@ __global__ void __launch_bounds__(kThreads) k_reduce_col_vec(const __grid_consta
 // Generic chain, all operands contiguous: interpreter on 4 lanes.
 template <class C>
 __global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_constant__ VmProgram P, int64_t n, int code_arg, uint32_t* __restrict__ partials,
-                                                                 unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar) {
+                                                                 unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar, int early) {
   const int code = C::red_code(code_arg);
+  if (!early) {
+    pdl_wait();
+    pdl_release();
+  }
   __shared__ uint32_t sm[kThreads / 32];
   int64_t n4 = n >> 2;
   int64_t stride = (int64_t)gridDim.x * kThreads;
@@ -305,14 +329,22 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_co
   }
   uint32_t v = red_combine(code, red_combine(code, acc[0], acc[1]), red_combine(code, acc[2], acc[3]));
   v = block_red<kThreads>(code, v, sm);
+  if (early) {
+    pdl_wait();
+    pdl_release();
+  }
   finish_in_last_block(v, partials, ticket, code, init_bits, C::out(P, 0), sm, ar);
 }
 
 // Generic chain, strided operands.
 template <class C>
 __global__ void __launch_bounds__(kThreads) k_reduce_full_generic(const __grid_constant__ VmProgram P, int64_t n, int code_arg, uint32_t* __restrict__ partials,
-                                                                  unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar) {
+                                                                  unsigned* ticket, uint32_t init_bits, const __grid_constant__ FusedAllReduce ar, int early) {
   const int code = C::red_code(code_arg);
+  if (!early) {
+    pdl_wait();
+    pdl_release();
+  }
   __shared__ uint32_t sm[kThreads / 32];
   int64_t stride = (int64_t)gridDim.x * kThreads;
   uint32_t acc = red_identity(code);
@@ -324,6 +356,10 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_generic(const __grid_c
     acc = red_combine(code, acc, vm_eval_at<C>(P, idx));
   }
   acc = block_red<kThreads>(code, acc, sm);
+  if (early) {
+    pdl_wait();
+    pdl_release();
+  }
   finish_in_last_block(acc, partials, ticket, code, init_bits, C::out(P, 0), sm, ar);
 }
 

@@ -71,6 +71,7 @@ struct Driver {
   CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**) = nullptr;
   CUresult (*Occupancy)(int*, CUfunction, int, size_t) = nullptr;
+  CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;  // optional
   bool ok = false;
 };
 
@@ -89,6 +90,7 @@ const Driver& driver() {
     d.ModuleGetFunction = (decltype(d.ModuleGetFunction))get("cuModuleGetFunction");
     d.LaunchKernel = (decltype(d.LaunchKernel))get("cuLaunchKernel");
     d.Occupancy = (decltype(d.Occupancy))get("cuOccupancyMaxActiveBlocksPerMultiprocessor");
+    d.LaunchKernelEx = (decltype(d.LaunchKernelEx))get("cuLaunchKernelEx");
     d.ok = d.ModuleLoadData && d.ModuleGetFunction && d.LaunchKernel && d.Occupancy;
   });
   return d;
@@ -387,7 +389,20 @@ const JitKernel* jit_chain_kernel(int device, const VmProgram& P, const char* fa
   return &(g_kernels[key] = k);
 }
 
-cudaError_t jit_launch(const JitKernel* k, dim3 grid, dim3 block, void** args, cudaStream_t stream) {
+cudaError_t jit_launch(const JitKernel* k, dim3 grid, dim3 block, void** args, cudaStream_t stream, bool pdl) {
+  if (pdl && driver().LaunchKernelEx) {
+    CUlaunchConfig cfg{};
+    cfg.gridDimX = grid.x; cfg.gridDimY = grid.y; cfg.gridDimZ = grid.z;
+    cfg.blockDimX = block.x; cfg.blockDimY = block.y; cfg.blockDimZ = block.z;
+    cfg.hStream = (CUstream)stream;
+    CUlaunchAttribute at[1];
+    at[0].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    at[0].value.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    CUresult r = driver().LaunchKernelEx(&cfg, (CUfunction)k->fn, args, nullptr);
+    return r == CUDA_SUCCESS ? cudaSuccess : (cudaError_t)r;
+  }
   CUresult r = driver().LaunchKernel((CUfunction)k->fn, grid.x, grid.y, grid.z, block.x, block.y, block.z, 0, (CUstream)stream, args, nullptr);
   return r == CUDA_SUCCESS ? cudaSuccess : (cudaError_t)r;
 }

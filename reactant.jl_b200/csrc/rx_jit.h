@@ -36,7 +36,9 @@ struct JitKernel {
 // library's last-error slot.
 const JitKernel* jit_chain_kernel(int device, const VmProgram& P, const char* family, int red_code, int64_t work_elems, bool* failed);
 
-cudaError_t jit_launch(const JitKernel* k, dim3 grid, dim3 block, void** args, cudaStream_t stream);
+// pdl: launch with the programmatic-stream-serialization attribute (the kernel may start before the one in front of
+// it on the stream has completed; it synchronises with griddepcontrol.wait itself).
+cudaError_t jit_launch(const JitKernel* k, dim3 grid, dim3 block, void** args, cudaStream_t stream, bool pdl = false);
 
 // Threshold in elements per launch (default 2^20); negative switches specialisation off.
 void jit_set_min_elems(int64_t n);

@@ -13,7 +13,9 @@
 #include "rx_kernels.h"
 
 #include <stdio.h>
+#include <stdlib.h>
 #include <algorithm>
+#include <utility>
 
 #include "rx_chain_kernels.cuh"
 #include "rx_jit.h"
@@ -42,8 +44,12 @@ struct InterpChain {
 // ---- full reduce: pass 1 ---------------------------------------------------------
 // FAST_SIN_ADD: sum(sin(x) + y) with x = leaf 0, y = leaf 1, both contiguous f32.
 __global__ void __launch_bounds__(kThreads) k_reduce_full_sinadd(const float* __restrict__ x, const float* __restrict__ y, int64_t n, uint32_t* __restrict__ partials,
-                                                                 unsigned* ticket, uint32_t init_bits, VmOut out, const __grid_constant__ FusedAllReduce ar) {
+                                                                 unsigned* ticket, uint32_t init_bits, VmOut out, const __grid_constant__ FusedAllReduce ar, int early) {
   __shared__ uint32_t sm[kThreads / 32];
+  if (!early) {
+    pdl_wait();
+    pdl_release();
+  }
   const float4* x4 = (const float4*)x;
   const float4* y4 = (const float4*)y;
   int64_t n4 = n >> 2;
@@ -68,6 +74,10 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_sinadd(const float* __
   }
   float v = (a0 + a1) + (a2 + a3);
   uint32_t r = block_red<kThreads>(R_FADD, f2u(v), sm);
+  if (early) {
+    pdl_wait();
+    pdl_release();
+  }
   finish_in_last_block(r, partials, ticket, R_FADD, init_bits, out, sm, ar);
 }
 
@@ -318,7 +328,7 @@ int red_code(RedK k, DT dt) {
 // Launch `family` specialised for P's chain when that is worthwhile and possible; otherwise (*ran == false)
 // the caller launches the interpreter kernel.
 cudaError_t try_specialised(const LaunchCtx& c, const VmProgram& P, const char* family, int code, int64_t work, dim3 grid, void** args, bool* ran,
-                            int* occupancy = nullptr) {
+                            int* occupancy = nullptr, bool pdl = false) {
   *ran = false;
   bool failed = false;
   const JitKernel* k = jit_chain_kernel(c.device, P, family, code, work, &failed);
@@ -329,7 +339,7 @@ cudaError_t try_specialised(const LaunchCtx& c, const VmProgram& P, const char* 
     return cudaSuccess;
   }
   *ran = true;
-  return jit_launch(k, grid, dim3(kThreads), args, c.stream);
+  return jit_launch(k, grid, dim3(kThreads), args, c.stream, pdl);
 }
 
 cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
@@ -381,9 +391,26 @@ int resident_per_sm(K kernel) {
   return n;
 }
 
+// Launch with the programmatic-stream-serialization attribute (see pdl_wait in rx_chain_kernels.cuh).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), int blocks, cudaStream_t stream, bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, const FusedAllReduce* fused) {
   FusedAllReduce ar{};
   if (fused) ar = *fused;
+  static const bool pdl = !(getenv("RX_PDL") && atoi(getenv("RX_PDL")) == 0);
+  int early = pdl && c.operands_settled ? 1 : 0;
   int64_t n = total_of(P);
   static const int occ_sinadd = resident_per_sm(k_reduce_full_sinadd), occ_linear = resident_per_sm(k_reduce_full_linear<InterpChain>),
                    occ_rows = resident_per_sm(k_reduce_full_rows<InterpChain>), occ_generic = resident_per_sm(k_reduce_full_generic<InterpChain>);
@@ -406,20 +433,20 @@ cudaError_t launch_reduce_full(const LaunchCtx& c, const VmProgram& P, int code,
   if (sinadd) {
     const float* x = (const float*)P.leaf[0].ptr + P.leaf[0].offset;
     const float* y = (const float*)P.leaf[1].ptr + P.leaf[1].offset;
-    k_reduce_full_sinadd<<<blocks, kThreads, 0, c.stream>>>(x, y, n, partials, ticket, init_bits, P.out[0], ar);
+    e = launch_pdl(k_reduce_full_sinadd, blocks, c.stream, pdl, x, y, n, partials, ticket, init_bits, P.out[0], ar, early);
   } else if (vec) {
-    void* args[] = {(void*)&P, (void*)&n, (void*)&code, (void*)&partials, (void*)&ticket, (void*)&init_bits, (void*)&ar};
-    e = try_specialised(c, P, family, code, n, dim3(blocks), args, &ran);
-    if (!ran && e == cudaSuccess) k_reduce_full_linear<InterpChain><<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
+    void* args[] = {(void*)&P, (void*)&n, (void*)&code, (void*)&partials, (void*)&ticket, (void*)&init_bits, (void*)&ar, (void*)&early};
+    e = try_specialised(c, P, family, code, n, dim3(blocks), args, &ran, nullptr, pdl);
+    if (!ran && e == cudaSuccess) e = launch_pdl(k_reduce_full_linear<InterpChain>, blocks, c.stream, pdl, P, n, code, partials, ticket, init_bits, ar, early);
   } else if (rows2) {
     int64_t rows = P.dim[0], cols = P.dim[1];
-    void* args[] = {(void*)&P, (void*)&rows, (void*)&cols, (void*)&code, (void*)&partials, (void*)&ticket, (void*)&init_bits, (void*)&ar};
-    e = try_specialised(c, P, family, code, n, dim3(blocks), args, &ran);
-    if (!ran && e == cudaSuccess) k_reduce_full_rows<InterpChain><<<blocks, kThreads, 0, c.stream>>>(P, rows, cols, code, partials, ticket, init_bits, ar);
+    void* args[] = {(void*)&P, (void*)&rows, (void*)&cols, (void*)&code, (void*)&partials, (void*)&ticket, (void*)&init_bits, (void*)&ar, (void*)&early};
+    e = try_specialised(c, P, family, code, n, dim3(blocks), args, &ran, nullptr, pdl);
+    if (!ran && e == cudaSuccess) e = launch_pdl(k_reduce_full_rows<InterpChain>, blocks, c.stream, pdl, P, rows, cols, code, partials, ticket, init_bits, ar, early);
   } else {
-    void* args[] = {(void*)&P, (void*)&n, (void*)&code, (void*)&partials, (void*)&ticket, (void*)&init_bits, (void*)&ar};
-    e = try_specialised(c, P, family, code, n, dim3(blocks), args, &ran);
-    if (!ran && e == cudaSuccess) k_reduce_full_generic<InterpChain><<<blocks, kThreads, 0, c.stream>>>(P, n, code, partials, ticket, init_bits, ar);
+    void* args[] = {(void*)&P, (void*)&n, (void*)&code, (void*)&partials, (void*)&ticket, (void*)&init_bits, (void*)&ar, (void*)&early};
+    e = try_specialised(c, P, family, code, n, dim3(blocks), args, &ran, nullptr, pdl);
+    if (!ran && e == cudaSuccess) e = launch_pdl(k_reduce_full_generic<InterpChain>, blocks, c.stream, pdl, P, n, code, partials, ticket, init_bits, ar, early);
   }
   if (e != cudaSuccess) return e;
   *c.launches += 1;

@@ -15,6 +15,9 @@ struct LaunchCtx {
   uint32_t* scratch = nullptr;   // per-device partials buffer for two-pass reductions
   size_t scratch_words = 0;
   uint64_t* launches = nullptr;  // counts kernels launched through this context
+  // None of the step's operands is written by the kernel launched just before it on this stream: a kernel launched
+  // with programmatic stream serialization may then read them before that kernel has completed.
+  bool operands_settled = false;
 };
 
 int red_code(RedK k, DT dt);

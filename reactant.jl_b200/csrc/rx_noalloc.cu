@@ -163,6 +163,7 @@ extern "C" int RxSinSumAddNoAlloc(const float* x_dev, const float* y_dev, int64_
     long long grid = nchunks < 1 ? 1 : nchunks;
     long long cap = (long long)pd.sm_count * 8;
     if (grid > cap) grid = cap;
+    rx::note_foreign_launch();  // executions queued behind this on the same stream must not read early what it writes
     k_sinsum_noalloc<<<(unsigned)grid, kThreads, 0, s>>>(x_dev, y_dev, (long long)n, out_dev, pd.scratch);
     e = cudaGetLastError();
   }

@@ -151,6 +151,26 @@ void RxDevice::trim() {
     for (void* p : kv.second) cudaFree(p);
 }
 
+cudaEvent_t EventState::event() {
+  std::lock_guard<std::mutex> g(ev_mu);
+  if (ev) return ev;
+  if (!dev || dev->closed.load() || !dev->stream) return nullptr;
+  cudaSetDevice(dev->ordinal);
+  if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+    cudaGetLastError();
+    ev = nullptr;
+    return nullptr;
+  }
+  cudaEventRecord(ev, dev->stream);
+  return ev;
+}
+
+namespace rx {
+static std::atomic<uint64_t> g_foreign_launches{0};
+uint64_t foreign_launches() { return g_foreign_launches.load(); }
+void note_foreign_launch() { g_foreign_launches.fetch_add(1); }
+}  // namespace rx
+
 EventState::~EventState() {
   if (ev) {
     cudaSetDevice(dev->ordinal);
@@ -259,6 +279,7 @@ const char* kind_name(StepK k) {
 }
 
 void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<DevRun>& runs);
+void note_writes(struct DevRun& r, const Step& st);
 
 // End of a loop iteration: carried value j now lives where the body left its next value; the storage it
 // vacated goes to the slots the body writes next time.
@@ -313,8 +334,34 @@ bool try_stencil_loop(const Step& st, DevRun& r) {
     if (!handled) ps.kind = nullptr;
   }
   if (!handled) return false;
+  note_writes(r, st);
   d->last_stencil_tma = true;
   for (int64_t i = 0; i < st.trip % period; ++i) rotate_loop_state(st, r);
+  return true;
+}
+
+// What the launch of `st` writes, for the early-read decision of the launch behind it.
+void note_writes(DevRun& r, const Step& st) {
+  RxDevice* d = r.dev;
+  d->last_writes.clear();
+  d->foreign_seen = rx::foreign_launches();
+  auto add = [&](int slot) {
+    if (slot >= 0 && r.table[slot]) d->last_writes.push_back(r.table[slot]->ptr);
+  };
+  for (int s : st.out_slot) add(s);
+  add(st.dst_slot);
+  add(st.gemm.d_slot);
+  for (int s : st.state_slots) add(s);
+  for (int s : st.yield_slots) add(s);
+}
+bool operands_settled(DevRun& r, const Step& st) {
+  RxDevice* d = r.dev;
+  if (d->foreign_seen != rx::foreign_launches()) return false;
+  for (int s : st.leaf_slot) {
+    const void* p = slot_ptr(r, s);
+    for (const void* w : d->last_writes)
+      if (w == p) return false;
+  }
   return true;
 }
 
@@ -322,6 +369,12 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
   RxDevice* d = r.dev;
   CK(cudaSetDevice(d->ordinal));
   LaunchCtx c = d->ctx();
+  if (st.kind == StepK::ReduceFull) c.operands_settled = operands_settled(r, st);
+  struct NoteAfter {
+    DevRun& r;
+    const Step& st;
+    ~NoteAfter() { note_writes(r, st); }
+  } note_after{r, st};
   static const bool by_note = getenv("RX_PROFILE_NOTES") != nullptr;  // finer spans: one per plan step description
   ProfScope ps(d, by_note ? st.note.c_str() : kind_name(st.kind));
   switch (st.kind) {
@@ -411,19 +464,11 @@ void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<Dev
       for (int64_t it = 0; it < st.trip; ++it) {
         run_steps(ex, st.body, rest);
         for (auto& r : rest) {
-          join_all_pending(r);
-          rotate_loop_state(st, r);
-        }
-      }
-      for (size_t q = 0; q < rest.size(); ++q) runs[rest_index[q]] = std::move(rest[q]);
-      continue;
-      for (int64_t it = 0; it < st.trip; ++it) {
-        run_steps(ex, st.body, runs);
-        for (auto& r : runs) {
           join_all_pending(r);  // in-flight all-reduces are tracked by slot, and the rotation moves storages between slots
           rotate_loop_state(st, r);
         }
       }
+      for (size_t q = 0; q < rest.size(); ++q) runs[rest_index[q]] = std::move(rest[q]);
     } else if (st.kind == StepK::AllReduce) {
       // vectors (gradients) go to the communication stream so that the steps after them keep the SMs busy;
       // single words stay on the compute stream (mailbox kernel, a few microseconds)
@@ -442,6 +487,7 @@ void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<Dev
         }
       }
       rx::run_allreduce(ex->client, st, runs.size(), [&](size_t k) { return runs[k].dev; }, [&](size_t k) { return slot_ptr(runs[k], st.dst_slot); }, side);
+      for (auto& r : runs) note_writes(r, st);
       if (side) {
         for (auto& r : runs) {
           CK(cudaSetDevice(r.dev->ordinal));
@@ -503,6 +549,7 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
           size_t bytes = (size_t)sl.bytes();
           auto st = std::make_shared<Storage>(d, d->alloc(bytes), bytes);
           CK(cudaMemcpyAsync(st->ptr, b->st->ptr, bytes, cudaMemcpyDeviceToDevice, d->stream));
+          d->last_writes.push_back(st->ptr);  // a copy may run as a kernel: its target is not settled yet
           r.table[s] = st;
         } else {
           r.table[s] = b->st;
@@ -559,8 +606,6 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
     auto es = std::make_shared<EventState>();
     es->dev = d;
     es->keep = d->shared_from_this();
-    CK(cudaEventCreateWithFlags(&es->ev, cudaEventDisableTiming));
-    CK(cudaEventRecord(es->ev, d->stream));
     for (int j = 0; j < num_results; ++j) {
       const ResultBinding& rb = p.results[j];
       auto* b = own(new RxBuffer());
@@ -914,15 +959,17 @@ void FreeFuture(RxFuture* f) {
 }
 uint8_t FutureIsReady(RxFuture* f) {
   if (!f || !f->state) return 1;
+  cudaEvent_t ev = f->state->event();
+  if (!ev) return 1;
   cudaSetDevice(f->state->dev->ordinal);
-  return cudaEventQuery(f->state->ev) == cudaSuccess;
+  return cudaEventQuery(ev) == cudaSuccess;
 }
 void FutureAwait(RxFuture* f) {
   API_BEGIN
   if (!f || !f->state) return;
   RxDevice* d = f->state->dev;
   CK(cudaSetDevice(d->ordinal));
-  CK(cudaEventSynchronize(f->state->ev));
+  if (cudaEvent_t ev = f->state->event()) CK(cudaEventSynchronize(ev));
   std::lock_guard<std::mutex> g(f->state->error_mu);
   if (f->state->error_code) throw Error(f->state->error_code, f->state->error);
   try {

@@ -47,6 +47,10 @@ struct RxDevice : std::enable_shared_from_this<RxDevice> {
   uint32_t* scratch = nullptr;
   size_t scratch_words = 0;
   uint64_t launches = 0;
+  // Storage written by the most recent launch on `stream` (and by copies queued since): a kernel launched with
+  // programmatic stream serialization may read its operands early only if none of them is in this list.
+  std::vector<const void*> last_writes;
+  uint64_t foreign_seen = 0;  // value of rx::foreign_launches() when last_writes was last brought up to date
   bool last_gemm_tc = false, last_stencil_tma = false;  // which kernel family the last such step used
   // profiling
   bool profiling = false;
@@ -123,15 +127,29 @@ struct RxBuffer {
   }
 };
 
+namespace rx {
+// Kernels that this library's other entry points launch on caller-supplied streams (RxSinSumAddNoAlloc) are not
+// tracked per device; each bumps this counter, and an execution that sees it moved assumes nothing about what
+// the kernel in front of it wrote.
+uint64_t foreign_launches();
+void note_foreign_launch();
+}  // namespace rx
+
 struct EventState {
   // A failure found when this execution was awaited (a bounded device-side wait that ran out): kept here so that
   // every future of the execution reports it, not only the first one to look at the device's status word.
   std::mutex error_mu;
   int error_code = 0;
   std::string error;
+  // Completion of the execution on the device's compute stream.  The event is recorded only when somebody asks
+  // (FutureIsReady / FutureAwait): most futures are freed unasked, and an event record between two launches would
+  // keep the second from starting under the first (programmatic dependent launch).  Recording late is safe: the
+  // event then also covers whatever was queued after the execution, so "ready" is never reported too early.
+  std::mutex ev_mu;
   cudaEvent_t ev = nullptr;
   RxDevice* dev = nullptr;
   std::shared_ptr<RxDevice> keep;
+  cudaEvent_t event();  // records on first use; nullptr once the device's client has been freed (everything has drained)
   ~EventState();
 };
 

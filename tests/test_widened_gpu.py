@@ -103,7 +103,7 @@ def test_sharding_getters_and_handle_ownership(rx, client):
     assert lib.RxOwns(C.addressof(junk)) == 0
     kind = rx._lib.take_string(lib.DeviceGetKind(dev.handle))
     assert "sm_" in kind and kind != "unknown"
-    props = (C.c_byte * 128)()
+    props = (C.c_ubyte * 128)()
     lib.ReactantCudaDeviceGetProperties(props, 0)
     rx._lib.check()
     assert int.from_bytes(bytes(props[0:8]), "little") > (1 << 30)  # totalGlobalMem
