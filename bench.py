@@ -220,37 +220,62 @@ def setup_logsumexp(rx, client, dist, rows=32768, cols=8192):
 
 
 def setup_jacobi(rx, client, dist, n=8192, steps=100, form="dus"):
-    ka, ha = pinned(rx, n * n)
-    kb, hb = pinned(rx, n * n)
-    fill_uniform(ha, 4, 0.0, 1.0)
-    fill_uniform(hb, 5, 0.0, 1.0)
-    a, b = ha.reshape(n, n), hb.reshape(n, n)
+    """With N > 1 ranks both arrays are split into row blocks of the [n][n] tensors (Julia's second dimension) over the
+    mesh: every sweep each rank updates the rows it owns and the boundary rows travel to the neighbours' halos."""
+    rank, world = dist.rank, dist.world
+    if n % world:
+        raise SystemExit("the mesh size must divide the number of rows")
+    L = n // world
+    fa, fb = np.empty(n * n, np.float32), np.empty(n * n, np.float32)
+    fill_uniform(fa, 4, 0.0, 1.0)
+    fill_uniform(fb, 5, 0.0, 1.0)
+    a, b = fa.reshape(n, n), fb.reshape(n, n)            # the global arrays (the same for every mesh size)
+    ka, ha = pinned(rx, L * n)
+    kb, hb = pinned(rx, L * n)
+    la, lb = ha.reshape(L, n), hb.reshape(L, n)          # this rank's rows, in page-locked memory
+    la[...] = a[rank * L:(rank + 1) * L]
+    lb[...] = b[rank * L:(rank + 1) * L]
     sweeps = steps if form != "halfsteps" else 2 * steps
     order = "polybench" if form == "halfsteps" else "baseline"
-    thunk = rx.compile(rx.programs.jacobi2d(n, steps, form=form), client)
+    thunk = rx.compile(rx.programs.jacobi2d(n, steps, form=form, num_partitions=world), client)
     per_sweep = 4 * n * n + 4 * (n - 2) * (n - 2)
+    if world > 1:
+        sh = rx.NamedSharding(rx.Mesh(client.devices, ("x",)), (None, "x"))
+
+        def upload():
+            return rx.from_local_shards([la.T], (n, n), sh, client), rx.from_local_shards([lb.T], (n, n), sh, client)
+
+        def local(r):
+            return np.asarray(r.data[0].to_host())
+    else:
+        def upload():
+            return rx.to_rarray(la.T, client), rx.to_rarray(lb.T, client)
+
+        def local(r):
+            return np.asarray(r).T
 
     def check(_result):
         """The timed steps keep sweeping the same donated arrays, so parity is taken on a run of its own: fresh
-        upload, one execution (all the sweeps), every element compared with the C oracle's."""
+        upload, one execution (all the sweeps), every element of this rank's rows compared with the C oracle's."""
         _, cpu = entry.load_oracle()
-        cpu.set_threads(host_cores())
-        ra, rb = thunk(rx.to_rarray(a.T, client), rx.to_rarray(b.T, client))
-        ga, gb = np.asarray(ra).T, np.asarray(rb).T
+        cpu.set_threads(max(1, host_cores() // world))
+        ra, rb = thunk(*upload())
+        ga, gb = local(ra), local(rb)
         wa, wb = cpu.jacobi2d(a, b, sweeps, order)
-        bad = int(np.count_nonzero(ga != wa) + np.count_nonzero(gb != wb))
-        return {"got": float(ga[n // 2, n // 2]), "want": float(wa[n // 2, n // 2]), "rel_err": bad / (2.0 * n * n), "tol": 0.0, "ok": bad == 0,
-                "against": f"C oracle, {sweeps} sweeps of the same {n}x{n} arrays, bit-exact (rel_err = fraction of differing elements)"}
+        wa, wb = wa[rank * L:(rank + 1) * L], wb[rank * L:(rank + 1) * L]
+        bad = int(dist.reduce(float(np.count_nonzero(ga != wa) + np.count_nonzero(gb != wb)), "sum"))
+        return {"got": float(ga[L // 2, n // 2]), "want": float(wa[L // 2, n // 2]), "rel_err": bad / (2.0 * n * n), "tol": 0.0, "ok": bad == 0,
+                "against": f"C oracle, {sweeps} sweeps of the same {n}x{n} arrays, bit-exact on every rank's rows (rel_err = fraction of differing elements)"}
 
     def cpu_run():
         _, cpu = entry.load_oracle()
         return cpu.jacobi2d(a, b, 10, order)
 
-    return dict(thunk=thunk, upload=lambda: (rx.to_rarray(a.T, client), rx.to_rarray(b.T, client)), host=(ka, kb, a, b),
-                read=lambda r: (np.asarray(r[0]), np.asarray(r[1])), check=check, cpu_run=cpu_run, cpu_work=per_sweep * 10,
+    return dict(thunk=thunk, upload=upload, host=(ka, kb, a, b),
+                read=lambda r: (local(r[0]), local(r[1])), check=check, cpu_run=cpu_run, cpu_work=per_sweep * 10,
                 cpu_sample=f"10 of the {sweeps} sweeps of the {n}^2 grid per step",
-                bytes_per_step=per_sweep * sweeps, h2d=8 * n * n, d2h=8 * n * n,
-                unit="GB/s", kind="stencil_tma", dtype="f32", bound="hbm", kernel="k_stencil", launches_per_step=sweeps, donates=True,
+                bytes_per_step=per_sweep * sweeps, h2d=8 * n * L, d2h=8 * n * L,
+                unit="GB/s", kind="stencil_tma" if world == 1 else "stencil_rows", dtype="f32", bound="hbm", kernel="k_stencil", launches_per_step=sweeps, donates=True,
                 shape={"n": n, "sweeps": sweeps, "form": form, "seeds": [4, 5]})
 
 
@@ -349,7 +374,7 @@ WORKLOADS.update({
 })
 SMALL_INPUT = {"c1_sinsum_2p24", "c4_mlp_grad_bf16"}  # working set near or below the 126 MB L2: rotate input copies
 EXTRA_CONFIGS = ["c1_sinsum_2p24", "c2_logsumexp_32768x8192", "c3_jacobi2d_8192_100", "c3_jacobi2d_8192_50_halfsteps", "c4_mlp_grad_bf16"]
-SHARDED = ("c5_sharded_sinsum_2p30", "c1_sinsum_2p24", "c4_mlp_grad_bf16")
+SHARDED = ("c5_sharded_sinsum_2p30", "c1_sinsum_2p24", "c4_mlp_grad_bf16", "c3_jacobi2d_8192_100", "c3_jacobi2d_8192_50_halfsteps")
 
 
 # DRAM traffic per algorithmic byte of the dominant kernel, from profiler captures of the reduced-size workloads
@@ -496,7 +521,7 @@ def run_reference(args):
 
 
 def scaling_of(workload, world):
-    return "strong" if "sinsum" in workload and (world > 1 or "c5" in workload) else "weak"
+    return "strong" if ("sinsum" in workload or "jacobi" in workload) and (world > 1 or "c5" in workload) else "weak"
 
 
 def roofline_of(wl, prof, ms, steps, launches, world, dist, peaks):
@@ -507,6 +532,10 @@ def roofline_of(wl, prof, ms, steps, launches, world, dist, peaks):
     if kind == "stencil_tma" and "stencil_tma_loop" in prof:
         # the whole counted loop ran as one cooperative launch: a launch processes every sweep of the step
         kind, launches_per_step, kernel = "stencil_tma_loop", 1, "k_stencil_loop"
+    if kind == "gemm_tc" and "gemm_tc_fused" in prof:
+        # GEMMs with a fused epilogue are the same kernel compiled around a chain: one family for the roofline
+        both = [prof[k] for k in ("gemm_tc", "gemm_tc_fused") if k in prof]
+        prof = dict(prof, gemm_tc={"launches": sum(b["launches"] for b in both), "ms": sum(b["ms"] for b in both)})
     if kind not in prof or not prof[kind]["launches"]:
         return None
     if launches == steps * world:
@@ -517,6 +546,8 @@ def roofline_of(wl, prof, ms, steps, launches, world, dist, peaks):
     per_launch_ms = dist.reduce(per_launch_ms, "max")
     per_launch_work = work / launches_per_step
     achieved = to_metric(wl, per_launch_work, per_launch_ms)
+    if kind == "stencil_rows":
+        per_launch_work = work / launches_per_step  # one launch per sweep on every rank, each over its own rows
     peak = (peaks["hbm_gbs"] if wl["bound"] == "hbm" else peaks["bf16_tflops"]) * world
     traffic = None
     if kind in TRAFFIC_RATIO:
@@ -568,7 +599,7 @@ def main():
     allreduce = "none"
     if world > 1:
         if args.workload not in SHARDED:
-            raise SystemExit("the sinsum workloads and the data-parallel MLP step shard; the others run as single-GPU configurations")
+            raise SystemExit("the sinsum workloads, the Jacobi loops and the data-parallel MLP step shard; logsumexp runs as a single-GPU configuration")
         default_mode = "mailbox+nccl" if args.workload == "c4_mlp_grad_bf16" else "mailbox"
         allreduce = rx.dist.connect_collectives(rx, client, dist, os.environ.get("RX_ALLREDUCE", default_mode))
     peaks = measured_peaks()

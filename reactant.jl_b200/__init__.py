@@ -332,6 +332,10 @@ def to_rarray(x, client: Client | None = None, device: Device | None = None, sha
         return cls([buf], a.shape, a.dtype)
     d = sharding.sharded_dim()
     n = len(sharding.mesh)
+    if d is not None and a.shape[d] % n:
+        # a dimension the mesh does not divide is not split (nor padded): every device holds the whole array, which is
+        # what the compiled module's parameter sharding says too (src/Sharding.jl:582-654 takes the sharding XLA reports)
+        d = None
     bufs = []
     for i, dev in enumerate(sharding.mesh.devices):
         if not dev.addressable:

@@ -42,9 +42,7 @@ __device__ __forceinline__ void put4(uint32_t* d, uint32_t x, uint32_t y, uint32
 // the arithmetic come before the wait, so the main loop of this launch overlaps the cross-CTA combine and the
 // drain of the previous one.  `pdl_release` lets the kernel behind this one start; it comes after this kernel's own
 // wait, so at most two kernels of such a chain are ever in flight together.  Launched without the attribute
-// both instructions do nothing.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// both instructions do nothing.  (pdl_wait / pdl_release: rx_device.cuh)
 
 // Second pass of the cross-CTA combine, run by whichever CTA finishes last: it adds
 // the per-CTA partials in index order, so the result does not depend on which CTA

@@ -24,6 +24,15 @@ void destroy_collectives(RxClient* c);
 void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::function<RxDevice*(size_t)>& dev,
                    const std::function<void*(size_t)>& ptr, bool on_comm_stream = false);
 
+// Halo exchange of a row-sharded array (one launch per device): device g sends the first `down` rows it owns to the
+// lower halo of device g - 1 and the last `up` rows it owns to the upper halo of device g + 1, then waits -- bounded by
+// the client's peer wait -- for the rows its own neighbours send and copies them into its halos.  `block(k)` is local
+// device k's allocation: (rows_local + up + down) rows of `cols` floats, owned rows starting at row `up`.  The rows
+// travel as plain peer stores into a window next to the receiver's all-reduce mailbox (the receiver's own memory, so the
+// stencil kernel's tensor maps never cover peer memory), two windows alternating by sequence number.
+void run_halo_exchange(RxClient* c, size_t n_local, const std::function<RxDevice*(size_t)>& dev, const std::function<float*(size_t)>& block, int64_t rows_local,
+                       int64_t cols, int up, int down);
+
 // If a single-word all-reduce can go through the mailboxes, advance the epoch and fill
 // one FusedAllReduce per local device (to be handed to the producing reduce kernel).
 bool prepare_fused_allreduce(RxClient* c, const Step& ar_step, const std::vector<RxDevice*>& devs, std::vector<FusedAllReduce>* out);

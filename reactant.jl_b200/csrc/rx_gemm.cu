@@ -76,16 +76,18 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const TIn* __restrict__ A, co
 
 }  // namespace
 
-cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* b, void* out, bool* handled);
+cudaError_t run_gemm_tc(RxDevice* d, const Step& st, const void* a, const void* b, void* out, const GemmEpilogueArgs* epilogue, bool* handled);
 
-cudaError_t run_gemm(RxDevice* d, const Step& st, const void* a, const void* b, void* out) {
+cudaError_t run_gemm(RxDevice* d, const Step& st, const void* a, const void* b, void* out, const GemmEpilogueArgs* epilogue) {
   const GemmDesc& g = st.gemm;
   bool handled = false;
-  cudaError_t e = run_gemm_tc(d, st, a, b, out, &handled);
+  cudaError_t e = run_gemm_tc(d, st, a, b, out, epilogue, &handled);
   d->last_gemm_tc = handled;
   if (handled) return e;
+  // a step planned with a fused epilogue exists only in the tensor-core kernel (the planner checked the shape)
+  if (g.has_epilogue) return cudaErrorNotSupported;
   dim3 grid((unsigned)((g.N + TN - 1) / TN), (unsigned)((g.M + TM - 1) / TM), (unsigned)g.batch);
-  int64_t ao = st.prog.leaf[0].offset, bo = st.prog.leaf[1].offset;
+  int64_t ao = g.a_off, bo = g.b_off;
   if (g.in_dt == DT::BF16) {
     auto* A = (const __nv_bfloat16*)a + ao;
     auto* B = (const __nv_bfloat16*)b + bo;
@@ -103,12 +105,6 @@ cudaError_t run_gemm(RxDevice* d, const Step& st, const void* a, const void* b, 
   }
   ++d->launches;
   return cudaGetLastError();
-}
-
-// Tensor-core path: filled in by rx_gemm_tc.cu; this weak default declines.
-__attribute__((weak)) cudaError_t run_gemm_tc(RxDevice*, const Step&, const void*, const void*, void*, bool* handled) {
-  *handled = false;
-  return cudaSuccess;
 }
 
 }  // namespace rx

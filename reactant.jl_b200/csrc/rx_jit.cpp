@@ -72,6 +72,7 @@ struct Driver {
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**) = nullptr;
   CUresult (*Occupancy)(int*, CUfunction, int, size_t) = nullptr;
   CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;  // optional
+  CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;             // optional
   bool ok = false;
 };
 
@@ -91,6 +92,7 @@ const Driver& driver() {
     d.LaunchKernel = (decltype(d.LaunchKernel))get("cuLaunchKernel");
     d.Occupancy = (decltype(d.Occupancy))get("cuOccupancyMaxActiveBlocksPerMultiprocessor");
     d.LaunchKernelEx = (decltype(d.LaunchKernelEx))get("cuLaunchKernelEx");
+    d.FuncSetAttribute = (decltype(d.FuncSetAttribute))get("cuFuncSetAttribute");
     d.ok = d.ModuleLoadData && d.ModuleGetFunction && d.LaunchKernel && d.Occupancy;
   });
   return d;
@@ -138,9 +140,20 @@ bool compile(const std::string& src, const std::string& name_expr, std::vector<c
   n.AddNameExpression(prog, name_expr.c_str());
   // RX_JIT_VERBOSE=1 prints each generated source and ptxas' resource summary to stderr
   static const bool verbose = getenv("RX_JIT_VERBOSE") && atoi(getenv("RX_JIT_VERBOSE")) > 0;
-  const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "--ptxas-options=-v"};
+  // RX_JIT_DEFINES="-DNAME=value -D..." is handed to the compiler as is (tuning experiments)
+  std::vector<std::string> extra;
+  if (const char* defs = getenv("RX_JIT_DEFINES")) {
+    std::string t(defs), cur;
+    for (char c : t + " ") {
+      if (c == ' ') { if (!cur.empty()) extra.push_back(cur); cur.clear(); }
+      else cur += c;
+    }
+  }
+  std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "-std=c++17"};
+  for (auto& e : extra) opts.push_back(e.c_str());
+  if (verbose) opts.push_back("--ptxas-options=-v");
   if (verbose) fprintf(stderr, "---- %s\n%s\n", name_expr.c_str(), src.c_str());
-  int rc = n.CompileProgram(prog, verbose ? 3 : 2, opts);
+  int rc = n.CompileProgram(prog, (int)opts.size(), opts.data());
   size_t ls = 0;
   n.GetProgramLogSize(prog, &ls);
   if (ls > 1) {
@@ -229,14 +242,17 @@ static const std::string& headers_fingerprint() {
   return fp;
 }
 
-std::string jit_chain_source(const VmProgram& P, int red_code, const char* family) {
+std::string jit_chain_source(const VmProgram& P, int red_code, const char* family, const char* extra_members) {
   const OpText& T = op_text();
   std::string s;
   s.reserve(4096);
   s += "// headers: " + headers_fingerprint() + "\n";
   s += "// family: ";
   s += family;
-  s += "\n#define RX_CHAIN_SPECIALISED 1\n#include \"rx_chain_kernels.cuh\"\nnamespace rx {\nstruct SpecChain {\n";
+  s += "\n#define RX_CHAIN_SPECIALISED 1\n#include \"rx_chain_kernels.cuh\"\n";
+  if (!strncmp(family, "k_gemm_pair", 11)) s += "#include \"rx_gemm_pair.cuh\"\n";
+  s += "namespace rx {\nstruct SpecChain {\n";
+  if (extra_members) s += extra_members;
   int max_reg = P.result_reg;
   for (int k = 0; k < P.n_leaves; ++k) max_reg = std::max<int>(max_reg, P.leaf[k].reg);
   for (int k = 0; k < P.n_outs; ++k) max_reg = std::max<int>(max_reg, P.out[k].reg);
@@ -298,14 +314,16 @@ std::string jit_chain_source(const VmProgram& P, int red_code, const char* famil
   return s;
 }
 
-int64_t jit_compile_only(const VmProgram& P, int red_code, const char* family, std::string* log) {
+bool jit_available() { return nvrtc().ok; }
+
+int64_t jit_compile_only(const VmProgram& P, int red_code, const char* family, std::string* log, const char* extra_members) {
   if (!nvrtc().ok) {
     *log = "NVRTC library not found";
     return -1;
   }
   std::vector<char> cubin;
   std::string lowered;
-  if (!compile(jit_chain_source(P, red_code, family), std::string("rx::") + family, &cubin, &lowered, log)) return -1;
+  if (!compile(jit_chain_source(P, red_code, family, extra_members), std::string("rx::") + family, &cubin, &lowered, log)) return -1;
   return (int64_t)cubin.size();
 }
 
@@ -323,14 +341,15 @@ void jit_stats(int64_t out[5]) {
   out[4] = g_disk_hits;
 }
 
-const JitKernel* jit_chain_kernel(int device, const VmProgram& P, const char* family, int red_code, int64_t work_elems, bool* failed) {
+const JitKernel* jit_chain_kernel(int device, const VmProgram& P, const char* family, int red_code, int64_t work_elems, bool* failed,
+                                  const char* extra_members, bool force) {
   *failed = false;
-  {
+  if (!force) {
     std::lock_guard<std::mutex> g(g_mu);
     if (g_min_elems < 0 || work_elems < g_min_elems) return nullptr;
   }
   if (!nvrtc().ok || !driver().ok) return nullptr;
-  const std::string src = jit_chain_source(P, red_code, family);
+  const std::string src = jit_chain_source(P, red_code, family, extra_members);
   auto key = std::make_pair(device, src);
   bool have_cubin = false;
   {
@@ -387,6 +406,36 @@ const JitKernel* jit_chain_kernel(int device, const VmProgram& P, const char* fa
   if (d.Occupancy(&occ, fn, 256, 0) != CUDA_SUCCESS || occ < 1) occ = 4;
   k.occupancy = occ;
   return &(g_kernels[key] = k);
+}
+
+cudaError_t jit_launch_cluster(const JitKernel* k, unsigned grid_x, unsigned block_x, unsigned cluster_x, size_t smem_bytes, void** args, cudaStream_t stream,
+                               bool pdl) {
+  const Driver& d = driver();
+  if (!d.LaunchKernelEx || !d.FuncSetAttribute) return cudaErrorNotSupported;
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    if (k->smem_limit < (int)smem_bytes) {
+      CUresult r = d.FuncSetAttribute((CUfunction)k->fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem_bytes);
+      if (r != CUDA_SUCCESS) return (cudaError_t)r;
+      k->smem_limit = (int)smem_bytes;
+    }
+  }
+  CUlaunchConfig cfg{};
+  cfg.gridDimX = grid_x; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+  cfg.blockDimX = block_x; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+  cfg.sharedMemBytes = (unsigned)smem_bytes;
+  cfg.hStream = (CUstream)stream;
+  CUlaunchAttribute at[2];
+  at[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+  at[0].value.clusterDim.x = cluster_x;
+  at[0].value.clusterDim.y = 1;
+  at[0].value.clusterDim.z = 1;
+  at[1].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+  at[1].value.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl ? 2 : 1;
+  CUresult r = d.LaunchKernelEx(&cfg, (CUfunction)k->fn, args, nullptr);
+  return r == CUDA_SUCCESS ? cudaSuccess : (cudaError_t)r;
 }
 
 cudaError_t jit_launch(const JitKernel* k, dim3 grid, dim3 block, void** args, cudaStream_t stream, bool pdl) {

@@ -262,6 +262,40 @@ __global__ void __launch_bounds__(kThreads) k_scan_row_apply(const uint32_t* __r
   }
 }
 
+// ---- ordered sum of partial rows (second pass of the sums formed in a GEMM epilogue) -----------------------------------
+struct SumJobs {
+  SumPartialsJob j[4];
+};
+__global__ void __launch_bounds__(kThreads) k_sum_partials(const __grid_constant__ SumJobs jobs) {
+  __shared__ uint32_t sm[kThreads / 32];
+  const SumPartialsJob& j = jobs.j[blockIdx.y];
+  if (j.n == 1) {
+    // one value: every thread adds a strided subset of the rows, then the fixed block tree
+    if (blockIdx.x != 0) return;
+    float acc = 0.f;
+    for (int64_t r = threadIdx.x; r < j.rows; r += kThreads) acc += j.src[r];
+    const uint32_t t = block_red<kThreads>(R_FADD, f2u(acc), sm);
+    if (threadIdx.x == 0) j.dst[0] = j.init + u2f(t);
+    return;
+  }
+  // 32 columns per block: warp w adds rows w, w + 8, ... (lane = column, so every load is one 128-byte row piece),
+  // then the eight warp results are added in warp order
+  __shared__ float part[kThreads / 32][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int64_t col = (int64_t)blockIdx.x * 32 + lane;
+  float acc = 0.f;
+  if (col < j.n)
+    for (int64_t r = w; r < j.rows; r += kThreads / 32) acc += __ldg(j.src + r * j.n + col);
+  part[w][lane] = acc;
+  __syncthreads();
+  if (w == 0 && col < j.n) {
+    float t = part[0][lane];
+#pragma unroll
+    for (int q = 1; q < kThreads / 32; ++q) t += part[q][lane];
+    j.dst[col] = j.init + t;
+  }
+}
+
 int grid_for(int64_t work_items, int sm_count, int per_sm) {
   int64_t blocks = (work_items + kThreads - 1) / kThreads;
   int64_t cap = (int64_t)sm_count * per_sm;
@@ -534,6 +568,20 @@ cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code
     ++*c.launches;
   }
   k_scan_row_apply<<<grid, kThreads, 0, c.stream>>>(x, y, partial, code, n, seg, nseg);
+  ++*c.launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_sum_partials(const LaunchCtx& c, const SumPartialsJob* jobs, int n_jobs) {
+  if (n_jobs < 1 || n_jobs > 4) return cudaErrorInvalidValue;
+  SumJobs all{};
+  int64_t widest = 1;
+  for (int q = 0; q < n_jobs; ++q) {
+    all.j[q] = jobs[q];
+    widest = std::max(widest, jobs[q].n);
+  }
+  dim3 grid((unsigned)((widest + 31) / 32), (unsigned)n_jobs);
+  k_sum_partials<<<grid, kThreads, 0, c.stream>>>(all);
   ++*c.launches;
   return cudaGetLastError();
 }

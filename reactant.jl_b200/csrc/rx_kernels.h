@@ -31,6 +31,15 @@ cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, 
                               int64_t inner, uint32_t* partials, int nsplit);
 // inclusive scan along the middle dim of a dense [outer][n][inner] array of 32-bit elements
 cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code, int64_t outer, int64_t n, int64_t inner);
+// dst[c] = init + src[0][c] + src[1][c] + ... (rows added in index order) for up to four jobs in one launch: the
+// second pass of the sums a GEMM epilogue leaves as per-row-block / per-tile partials.
+struct SumPartialsJob {
+  const float* src;
+  float* dst;
+  int64_t rows, n;
+  float init;
+};
+cudaError_t launch_sum_partials(const LaunchCtx& c, const SumPartialsJob* jobs, int n_jobs);
 cudaError_t launch_logsumexp(const LaunchCtx& c, const float* x, int64_t row_stride, int64_t rows, int64_t cols, float* m, float* s, float* lse);
 
 // 2-D stencil step: out window = chain(shifted windows of src), tiles staged through

@@ -15,7 +15,9 @@
 // partitioning of sharded reductions, which XLA performs there
 // (API.cpp:1487-1497), is done here by rule.
 #include "rx_plan.h"
+#include "rx_jit.h"
 
+#include <stdlib.h>
 #include <string.h>
 #include <algorithm>
 #include <cmath>
@@ -458,11 +460,18 @@ struct Planner {
   // Strength-reduce the node list: constants become immediates of their consumer, and a
   // multiply whose only consumer is an add merges into one multiply-add instruction (still
   // two roundings, so results are unchanged).  Returns which nodes are no longer needed.
+  // Set by a caller of assemble() that needs more than the outputs kept in registers to the end of the program
+  // (the values a GEMM epilogue sums): value nodes in, their registers out.  asm_fixed_space keeps the root space
+  // exactly as given (no reordering or merging of dims).
+  std::vector<int> asm_pinned, asm_pinned_regs;
+  bool asm_fixed_space = false;
+
   std::vector<bool> peephole(Lowering& L, const std::vector<OutSpec>& outs, int result_vnode) {
     size_t nn = L.nodes.size();
     std::vector<int> nuses(nn, 0);
     std::vector<bool> pinned(nn, false), dead(nn, false);
     for (auto& o : outs) pinned[o.vnode] = true;
+    for (int v : asm_pinned) pinned[v] = true;
     if (result_vnode >= 0) pinned[result_vnode] = true;
     auto count = [&]() {
       std::fill(nuses.begin(), nuses.end(), 0);
@@ -532,7 +541,7 @@ struct Planner {
       if (span > best) { best = span; dominant = (int)k; }
     }
     for (auto& o : outs) sp.ostride.push_back(o.stride);
-    normalise_space(sp, dominant, by_output, !L.has_iota);
+    if (!asm_fixed_space) normalise_space(sp, dominant, by_output, !L.has_iota);
     if (sp.dim.size() > (size_t)kMaxRank) throw Error(RX_ERR_PLAN, "fusion group iteration space has rank > " + std::to_string(kMaxRank));
     VmProgram& P = st.prog;
     memset(&P, 0, sizeof P);
@@ -551,6 +560,7 @@ struct Planner {
         if (u >= 0) last[u] = (int)k;
     }
     for (auto& o : outs) last[o.vnode] = (int)nn + 1;
+    for (int v : asm_pinned) last[v] = (int)nn + 1;
     if (result_vnode >= 0) last[result_vnode] = (int)nn + 1;
     std::vector<int> reg(nn, -1);
     std::vector<int> free_regs;
@@ -594,6 +604,7 @@ struct Planner {
     }
     std::vector<bool> is_output(nn, false);
     for (auto& o : outs) is_output[o.vnode] = true;
+    for (int v : asm_pinned) is_output[v] = true;
     if (result_vnode >= 0) is_output[result_vnode] = true;
     // ---- emission for the accumulator machine: acc = f(acc, R[b], R[c] | imm) --------------------
     int prev = -1;  // node whose value is in the accumulator
@@ -724,6 +735,8 @@ struct Planner {
       st.out_slot.push_back(outs[k].slot);
     }
     P.result_reg = result_vnode >= 0 ? reg[result_vnode] : 0;
+    asm_pinned_regs.clear();
+    for (int v : asm_pinned) asm_pinned_regs.push_back(reg[v]);
     st.outer = st.red_n = st.inner = 1;
     // reduction classes after normalisation -> [outer][red][inner]
     if (!cls.empty() && std::find(cls.begin(), cls.end(), 1) != cls.end()) {
@@ -867,6 +880,213 @@ struct Planner {
     return false;
   }
 
+  // ---- elementwise and reduction work fused into the epilogue of the GEMM that produces its operand ---------------
+  // After a dot_general has been emitted as a Gemm step, maps and additive reductions over the [M][N] result whose
+  // other operands are per-element ([M][N], any row stride), per-column ([N], broadcast along m) or scalars join
+  // that step: the chain runs on the accumulator while it is still on chip.  What joins must not depend on any
+  // step emitted after the GEMM.  D itself stays a result of the step until the end of planning, when it is dropped
+  // if nothing else reads it.  Only at the top level of @main (steps of a loop body are not revisited), on shapes the
+  // two-CTA tensor-core kernel takes, and when run-time compilation is available (RX_GEMM_EPILOGUE=0 switches it off).
+  struct GemmFusion {
+    std::vector<Step>* where = nullptr;
+    size_t index = 0;
+    int d_slot = -1;
+    DT dt = DT::BF16;
+    int64_t M = 0, N = 0;
+    std::string base_note;
+    struct Out { int slot; ExprP expr; std::string note; };
+    std::vector<Out> outs;
+    struct Sum { int partial_slot; ExprP expr; bool col; std::string note; };
+    std::vector<Sum> sums;
+    int finish_index = -1;
+  };
+  std::vector<GemmFusion> fusions;  // every fused GEMM of the plan; the last one is the one that can still grow
+  bool fusion_open = false;
+
+  static bool epilogue_enabled() {
+    const bool on = !(getenv("RX_GEMM_EPILOGUE") && atoi(getenv("RX_GEMM_EPILOGUE")) == 0) && !getenv("RX_GEMM_SIMT") && !getenv("RX_GEMM_1CTA");
+    return on && jit_available();
+  }
+  GemmFusion* open_fusion() { return fusion_open && !fusions.empty() && fusions.back().where == cur ? &fusions.back() : nullptr; }
+
+  // (Re)build the GEMM step's epilogue program from the fusion record.  false: it does not fit the kernel (too many
+  // operands / results / live values, an operand with a stride the epilogue cannot walk, ...); the step is unchanged.
+  bool lower_fusion(GemmFusion& g, bool keep_d) {
+    Step tmp = (*g.where)[g.index];
+    Lowering L(std::vector<int64_t>{g.M, g.N});
+    const RMap id = Lowering::identity(2);
+    const std::vector<int64_t> dense = {g.N, 1};
+    Type dtype{g.dt, {g.M, g.N}};
+    std::vector<OutSpec> outs;
+    const int acc_v = L.lower(leaf(g.d_slot, dtype), id);
+    if (keep_d) outs.push_back(OutSpec{g.d_slot, g.dt, 0, dense, acc_v});
+    for (auto& o : g.outs) outs.push_back(OutSpec{o.slot, plan.slots[o.slot].type.dt, 0, dense, L.lower(o.expr, id)});
+    std::vector<int> pinned;
+    for (auto& su : g.sums) pinned.push_back(L.lower(su.expr, id));
+    if (L.has_iota || outs.empty() && pinned.empty()) return false;
+    asm_pinned = pinned;
+    asm_fixed_space = true;
+    std::vector<int> regs;
+    try {
+      assemble(tmp, L, outs, -1, std::vector<int>{0, 0}, true);
+      regs = asm_pinned_regs;
+    } catch (const Error& e) {
+      asm_pinned.clear();
+      asm_fixed_space = false;
+      if (e.code != RX_ERR_PLAN) throw;
+      return false;
+    }
+    asm_pinned.clear();
+    asm_fixed_space = false;
+    VmProgram& P = tmp.prog;
+    P.fast_id = FAST_NONE;
+    int acc_leaf = -1;
+    for (int k = 0; k < P.n_leaves; ++k) {
+      const VmLeaf& l = P.leaf[k];
+      if (l.elem != EL_F32 && l.elem != EL_BF16) return false;
+      if (tmp.leaf_slot[k] == g.d_slot) {
+        if (acc_leaf >= 0 || l.offset != 0 || l.stride[0] != g.N || l.stride[1] != 1) return false;  // read other than at (m, n)
+        acc_leaf = k;
+      } else if (l.stride[1] != 0 && l.stride[1] != 1) {
+        return false;
+      }
+    }
+    if (acc_leaf < 0) return false;
+    for (int k = 0; k < P.n_outs; ++k)
+      if (P.out[k].elem != EL_F32 && P.out[k].elem != EL_BF16) return false;
+    GemmDesc& gd = tmp.gemm;
+    gd.has_epilogue = true;
+    gd.acc_leaf = acc_leaf;
+    gd.n_leaves = P.n_leaves;
+    gd.n_col = gd.n_full = 0;
+    for (size_t q = 0; q < g.sums.size(); ++q) {
+      if (g.sums[q].col) {
+        if (gd.n_col == 2) return false;
+        gd.col_reg[gd.n_col] = regs[q];
+        gd.col_slot[gd.n_col++] = g.sums[q].partial_slot;
+      } else {
+        if (gd.n_full == 2) return false;
+        gd.full_reg[gd.n_full] = regs[q];
+        gd.full_slot[gd.n_full++] = g.sums[q].partial_slot;
+      }
+    }
+    std::string note = g.base_note + " + epilogue[";
+    bool first = true;
+    auto add = [&](const std::string& t) { note += (first ? "" : "; ") + t; first = false; };
+    if (keep_d) add("product");
+    for (auto& o : g.outs) add(o.note);
+    for (auto& su : g.sums) add(su.note);
+    tmp.note = note + "]";
+    (*g.where)[g.index] = std::move(tmp);
+    return true;
+  }
+
+  // Slots that steps emitted after the GEMM read or write: nothing that joins the epilogue may touch them.
+  bool touched_after(const GemmFusion& g, const std::set<int>& slots) {
+    for (size_t q = g.index + 1; q < g.where->size(); ++q) {
+      const Step& t = (*g.where)[q];
+      if (t.kind == StepK::Loop) return true;
+      std::vector<int> all = t.leaf_slot;
+      all.insert(all.end(), t.out_slot.begin(), t.out_slot.end());
+      for (int w : {t.src_slot, t.dst_slot, t.gemm.a_slot, t.gemm.b_slot, t.gemm.d_slot}) all.push_back(w);
+      for (auto& j : t.sums) { all.push_back(j.src_slot); all.push_back(j.dst_slot); }
+      for (int w : all)
+        if (w >= 0 && slots.count(w)) {
+          // the partial buffers of this very fusion are written by the GEMM and read by its SumPartials step
+          bool own_partial = false;
+          for (auto& su : g.sums) own_partial = own_partial || su.partial_slot == w;
+          if (!own_partial) return true;
+        }
+    }
+    return false;
+  }
+  bool fusable_expr(GemmFusion& g, const ExprP& e) {
+    if (e->shape != std::vector<int64_t>{g.M, g.N}) return false;
+    std::set<const Expr*> seen;
+    if (!reads_slot(e, g.d_slot, seen)) return false;
+    std::vector<const Expr*> lv;
+    std::set<const Expr*> seen2;
+    collect_leaves(e, lv, seen2);
+    std::set<int> slots;
+    for (auto* l : lv)
+      if (l->slot != g.d_slot) slots.insert(l->slot);
+    return !touched_after(g, slots);
+  }
+  bool try_fuse_map(const ExprP& e, int slot, int64_t offset, const std::vector<int64_t>& ostride, const std::string& note) {
+    GemmFusion* g = open_fusion();
+    if (!g || offset != 0 || !fusable_expr(*g, e)) return false;
+    if (ostride != canon_strides(e->shape) || prod(e->shape) != plan.slots[slot].type.numel() || slot == g->d_slot) return false;
+    for (auto& o : g->outs)
+      if (o.slot == slot) return false;
+    if (touched_after(*g, std::set<int>{slot})) return false;
+    g->outs.push_back({slot, e, note});
+    if (!lower_fusion(*g, true)) {
+      g->outs.pop_back();
+      return false;
+    }
+    return true;
+  }
+  // sum over dim 0 (per column) or over both dims of an [M][N] chain value; returns the slot of the result or -1
+  int try_fuse_sum(const ExprP& X, const std::vector<int64_t>& dims, const Type& rt, double init_f) {
+    GemmFusion* g = open_fusion();
+    if (!g || X->dt != DT::F32 || rt.dt != DT::F32 || !fusable_expr(*g, X)) return -1;
+    const bool col = dims == std::vector<int64_t>{0}, full = dims == std::vector<int64_t>{0, 1};
+    if (!col && !full) return -1;
+    const int64_t tiles = ((g->M + 255) / 256) * ((g->N + 255) / 256);
+    const size_t n_slots = plan.slots.size();
+    Type pt{DT::F32, col ? std::vector<int64_t>{g->M / 32, g->N} : std::vector<int64_t>{tiles * 16}};  // one partial per (tile, CTA, epilogue warp)
+    const int partial = new_slot(pt);
+    g->sums.push_back({partial, X, col, col ? "column sums" : "full sum"});
+    if (!lower_fusion(*g, true)) {
+      g->sums.pop_back();
+      plan.slots.resize(n_slots);
+      return -1;
+    }
+    const int dst = new_slot(rt);
+    SumJob job;
+    job.src_slot = partial;
+    job.dst_slot = dst;
+    job.rows = col ? g->M / 32 : tiles * 16;
+    job.n = col ? g->N : 1;
+    job.init = init_f;
+    if (g->finish_index >= 0 && (size_t)g->finish_index + 1 == g->where->size() && (*g->where)[g->finish_index].sums.size() < 4) {
+      (*g->where)[g->finish_index].sums.push_back(job);
+    } else {
+      Step fin;
+      fin.kind = StepK::SumPartials;
+      fin.note = "ordered sum of the epilogue partials";
+      fin.sums.push_back(job);
+      g->where->push_back(std::move(fin));
+      g->finish_index = (int)g->where->size() - 1;
+    }
+    last_map.where = nullptr;
+    return dst;
+  }
+  // End of planning: a fused GEMM whose product nobody else reads does not store it.
+  void finalize_fusions() {
+    std::function<bool(const std::vector<Step>&, int, const Step*)> reads = [&](const std::vector<Step>& steps, int slot, const Step* self) {
+      for (const Step& t : steps) {
+        if (&t == self) continue;
+        for (int w : t.leaf_slot) if (w == slot) return true;
+        for (int w : {t.src_slot, t.gemm.a_slot, t.gemm.b_slot}) if (w == slot) return true;
+        if (t.kind == StepK::AllReduce && t.dst_slot == slot) return true;
+        for (auto& j : t.sums) if (j.src_slot == slot) return true;
+        for (int w : t.state_slots) if (w == slot) return true;
+        for (int w : t.yield_slots) if (w == slot) return true;
+        if (reads(t.body, slot, self)) return true;
+      }
+      return false;
+    };
+    for (auto& g : fusions) {
+      Step* self = &(*g.where)[g.index];
+      if (!self->gemm.has_epilogue) continue;
+      bool needed = reads(plan.steps, g.d_slot, self);
+      for (auto& rb : plan.results) needed = needed || rb.slot == g.d_slot;
+      if (needed) continue;
+      if (lower_fusion(g, false)) plan.slots[g.d_slot].dead = true;
+    }
+  }
+
   // ---- step emitters -------------------------------------------------------
   // out[shape-indexed] = expr, written at `offset` with `ostride` into `slot`.
   //
@@ -876,6 +1096,10 @@ struct Planner {
   // registers, stored, and used -- it is not written and read back, and the operands the two chains have in common
   // are loaded once.  Results are identical: the register holds exactly the value that is stored.
   void emit_map(const ExprP& e, int slot, int64_t offset, const std::vector<int64_t>& ostride, const std::string& note) {
+    if (try_fuse_map(e, slot, offset, ostride, note)) {
+      last_map.where = nullptr;
+      return;
+    }
     static const bool merge_off = getenv("RX_NO_MAP_MERGE") != nullptr;
     if (!merge_off && last_map.where == cur && last_map.index < cur->size() && (*cur)[last_map.index].kind == StepK::Map &&
         last_map.outs.size() + 1 <= (size_t)kVmMaxOuts && !last_map.outs.empty() && last_map.outs[0].expr->shape == e->shape) {
@@ -1044,8 +1268,15 @@ struct Planner {
     if (nparts > 1 && shard[v] < 0)
       for (size_t d = 0; d < e->shape.size(); ++d)
         if (e->shape[d] > 1 && invariant_along(e, (int)d)) return;
-    if (uses[v] > 1 && e->k != Expr::Leaf && !is_splat(e) && prod(e->shape) > 1024 && e->cost > 12)
+    if (uses[v] > 1 && e->k != Expr::Leaf && !is_splat(e) && prod(e->shape) > 1024 && e->cost > 12) {
+      // a value computed from the result of the GEMM just emitted is evaluated inside that GEMM's epilogue by each of
+      // its consumers that joins it (one evaluation per element there, shared between them) and recomputed by the others
+      if (GemmFusion* g = open_fusion()) {
+        std::set<const Expr*> seen;
+        if (e->shape == std::vector<int64_t>{g->M, g->N} && reads_slot(e, g->d_slot, seen)) return;
+      }
       env[v] = materialised(e, "shared value " + m.values[v].name);
+    }
   }
 
   void plan_elementwise(const Op& op) {
@@ -1398,6 +1629,15 @@ struct Planner {
 
   // chain X -> reduce over `dims` -> a fresh slot of type rt; returns the result as a leaf
   ExprP reduce_core(const Op& op, ExprP X, const std::vector<int64_t>& dims, const Type& rt, double init_f, int64_t init_i, bool needs_allreduce) {
+    if (op.red == RedK::Add) {
+      const bool late = needs_allreduce && init_f != 0.0;
+      const int fused = try_fuse_sum(X, dims, rt, late ? 0.0 : init_f);
+      if (fused >= 0) {
+        if (needs_allreduce) emit_allreduce(fused, rt);
+        if (late) emit_late_init(fused, rt, init_f);
+        return leaf(fused, rt);
+      }
+    }
     const DT dt = X->dt;
     std::vector<int> cls(X->shape.size(), 0);
     for (auto d : dims) cls[d] = 1;
@@ -1692,8 +1932,8 @@ struct Planner {
     g.b_sb = nb ? bv.stride[rb] : 0;
     g.in_dt = A->dt;
     g.out_dt = rt.dt;
-    st.prog.leaf[0].offset = av.off;
-    st.prog.leaf[1].offset = bv.off;
+    g.a_off = av.off;
+    g.b_off = bv.off;
     int dst = new_slot(rt);
     g.d_slot = dst;
     g.d_sb = g.M * g.N;
@@ -1704,6 +1944,25 @@ struct Planner {
          << " A(" << (g.a_sk == 1 ? "k-major" : "m-major") << ") B(" << (g.b_sk == 1 ? "k-major" : "n-major") << ") "
          << dt_name(g.in_dt) << "->" << dt_name(g.out_dt) << " fp32 accumulate";
     st.note = note.str();
+    // can elementwise work on the product join this step?  (what the two-CTA tensor-core kernel with a compiled epilogue takes)
+    const bool majors_ok = (g.a_sk == 1 || g.a_sm == 1) && (g.b_sk == 1 || g.b_sn == 1);
+    const int64_t a_pitch = g.a_sk == 1 ? g.a_sm : g.a_sk, b_pitch = g.b_sk == 1 ? g.b_sn : g.b_sk;
+    const bool fusable = !partial_sum && cur == &plan.steps && epilogue_enabled() && g.in_dt == DT::BF16 && (g.out_dt == DT::BF16 || g.out_dt == DT::F32) &&
+                         g.batch == 1 && g.M >= 256 && g.N >= 256 && g.M % 32 == 0 && g.N % 32 == 0 && g.K >= 1 && majors_ok && a_pitch > 0 && b_pitch > 0 &&
+                         a_pitch % 8 == 0 && b_pitch % 8 == 0 && av.off % 8 == 0 && bv.off % 8 == 0 && g.M < (1LL << 31) && g.N < (1LL << 31) && g.K < (1LL << 31);
+    fusion_open = false;
+    if (fusable) {
+      GemmFusion gf;
+      gf.where = cur;
+      gf.index = cur->size();
+      gf.d_slot = dst;
+      gf.dt = rt.dt;
+      gf.M = g.M;
+      gf.N = g.N;
+      gf.base_note = st.note;
+      fusions.push_back(std::move(gf));
+      fusion_open = true;
+    }
     cur->push_back(std::move(st));
     if (partial_sum) {
       if (rt.dt != DT::F32 && rt.dt != DT::BF16) throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type for all_reduce");
@@ -1723,7 +1982,17 @@ struct Planner {
     for (int v : op.in) --remaining[v];  // the operands are consumed on entry: the loop's storage takes their place
     const Region& cond = op.regions[0];
     const Region& body = op.regions[1];
-    for (int x : op.in) if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while carrying sharded tensors");
+    // Carried arrays split into row blocks over the mesh (tensor dim 0 of 2-D f32 arrays): accepted when the body turns
+    // out to be slice-and-add (stencil) updates only -- what XLA's partitioner turns into collective-permutes of the
+    // boundary rows (test/core/sharding/optimize_comm.jl:48-56).  The body is then planned on the global arrays.
+    bool row_sharded = false;
+    for (int x : op.in) {
+      if (shard[x] < 0) continue;
+      const Type& t = m.values[x].type;
+      if (shard[x] != 0 || t.shape.size() != 2 || t.dt != DT::F32 || cur != &plan.steps)
+        throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while carrying sharded tensors other than 2-D f32 arrays split along their first tensor dimension");
+      row_sharded = true;
+    }
     // ---- trip count: cond is `compare LT|LE, counter, bound`, body steps counter by a constant
     int64_t trip = -1;
     int counter = -1;
@@ -1782,6 +2051,19 @@ struct Planner {
       Type t = m.values[x].type;
       ExprP e = env[x];
       if (t.shape.empty() && !dt_is_float(t.dt)) continue;  // integer scalar bookkeeping stays symbolic
+      if (row_sharded) {
+        if (shard[x] != 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: a row-sharded loop carries a tensor that is not sharded the same way");
+        int s = new_slot(t);  // the global type; allocated per device as its row block plus halos
+        plan.slots[s].row_block = true;
+        Step in;
+        in.kind = StepK::RowsIn;
+        in.src_slot = materialise(e, "row block of a loop-carried array");
+        in.dst_slot = s;
+        in.note = "row block + neighbours' halo rows into loop storage";
+        cur->push_back(std::move(in));
+        state_slot[k] = s;
+        continue;
+      }
       bool reuse = whole_slot(e) && uses[x] == 1 && slot_writable(e->slot);
       if (reuse) {
         state_slot[k] = e->slot;
@@ -1817,7 +2099,15 @@ struct Planner {
       }
     }
     int first_body_slot = (int)plan.slots.size();
-    plan_region(body);
+    const int64_t saved_parts = nparts;
+    if (row_sharded) nparts = 1;  // inside the body the arrays are the global ones (local_type() must not divide them)
+    try {
+      plan_region(body);
+    } catch (...) {
+      nparts = saved_parts;
+      throw;
+    }
+    nparts = saved_parts;
     std::vector<int> yslot(n, -1);
     for (size_t k = 0; k < n; ++k) {
       if (state_slot[k] < 0) continue;
@@ -1842,10 +2132,53 @@ struct Planner {
         loop.yield_slots.push_back(yslot[k]);
       }
     loop.note = "counted loop x" + std::to_string(trip);
+    if (row_sharded) {
+      // every step of the body must be a stencil update from one carried array into another; the rows a device needs
+      // from its neighbours follow from the window offsets
+      int up = 0, down = 0;
+      int64_t rows = 0;
+      for (int x : op.in)
+        if (shard[x] == 0) rows = m.values[x].type.shape[0];
+      for (const Step& b : loop.body) {
+        const bool carried = b.kind == StepK::Stencil && !b.leaf_slot.empty() && b.out_slot.size() == 1 && plan.slots[b.leaf_slot[0]].row_block &&
+                             plan.slots[b.out_slot[0]].row_block && b.st_src_ld == b.st_dst_ld;
+        if (!carried)
+          throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while carrying sharded tensors: the body is not made of slice-and-add updates between the carried arrays only (step: " + b.note + ")");
+        int max_dy = 0;
+        for (int dy : b.st_dy) max_dy = std::max(max_dy, dy);
+        const int64_t row0 = b.st_src_off / b.st_src_ld, drow0 = b.st_dst_off / b.st_dst_ld;
+        up = std::max<int>(up, (int)(drow0 - row0));
+        down = std::max<int>(down, (int)(row0 + max_dy - drow0));
+      }
+      if (up < 0 || down < 0 || up > 2 || down > 2 || rows % saved_parts != 0 || rows / saved_parts < std::max(up, down) || rows / saved_parts < 1)
+        throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while carrying sharded tensors: halo of more than 2 rows, or row blocks smaller than the halo");
+      for (int s : loop.state_slots) {
+        plan.slots[s].halo_up = up;
+        plan.slots[s].halo_down = down;
+      }
+      for (int s : loop.yield_slots) {
+        if (!plan.slots[s].row_block) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while carrying sharded tensors: a carried value leaves the loop's own storage");
+      }
+      loop.row_sharded = true;
+      loop.note += " over row blocks (halo " + std::to_string(up) + " up, " + std::to_string(down) + " down)";
+    }
     cur->push_back(std::move(loop));
     // ---- results
     for (size_t k = 0; k < n; ++k) {
       int r = op.out[k];
+      if (row_sharded && state_slot[k] >= 0) {
+        shard[r] = 0;
+        Type lt = local_type(r);
+        Step out;
+        out.kind = StepK::RowsOut;
+        out.src_slot = state_slot[k];
+        out.dst_slot = new_slot(lt);
+        out.note = "row block out of loop storage";
+        const int dst = out.dst_slot;
+        cur->push_back(std::move(out));
+        env[r] = leaf(dst, lt);
+        continue;
+      }
       if (state_slot[k] >= 0) env[r] = leaf(state_slot[k], m.values[r].type);
       else {
         auto s = std::make_shared<Expr>();  // final scalar values are not consumed by tensor code on the path
@@ -1909,8 +2242,10 @@ struct Planner {
             if (sd >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported: argument sharded along several dimensions");
             sd = (int)d;
           }
-        if (sd >= 0 && m.values[v].type.shape[sd] % nparts != 0)
-          throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported: sharded dimension is not divisible by the mesh size");
+        // A dimension that the mesh does not divide is not padded: Reactant asks XLA for a sharding that fits and
+        // uses that (src/Sharding.jl:582-654, 895-926; the padded form of src/xla/Sharding.jl:236-244 is only a
+        // probe).  Here such an argument is held in full by every device, and reported so by the sharding getters.
+        if (sd >= 0 && m.values[v].type.shape[sd] % nparts != 0) sd = -1;
         shard[v] = sd;
       }
       Type lt = local_type(v);
@@ -1942,6 +2277,7 @@ struct Planner {
       rb.sharded_dim = shard[v];
       plan.results.push_back(rb);
     }
+    finalize_fusions();
     // a temp slot handed out twice would be freed twice: give later duplicates their own copy
     std::set<int> seen;
     for (auto& rb : plan.results) {
@@ -1974,6 +2310,9 @@ const char* step_name(StepK k) {
     case StepK::Loop: return "loop";
     case StepK::AllReduce: return "all_reduce";
     case StepK::Scan: return "scan";
+    case StepK::SumPartials: return "sum_partials";
+    case StepK::RowsIn: return "rows_in";
+    case StepK::RowsOut: return "rows_out";
   }
   return "?";
 }
@@ -2000,6 +2339,10 @@ void describe_steps(std::ostringstream& os, const std::vector<Step>& steps) {
       for (int d = 0; d < s.prog.rank; ++d) os << (d ? "," : "") << s.prog.dim[d];
       os << "]";
     }
+    if (s.kind == StepK::Gemm && s.gemm.has_epilogue)
+      os << ",\"epilogue\":{\"instrs\":" << s.prog.n_instr << ",\"leaves\":" << s.prog.n_leaves << ",\"results\":" << s.prog.n_outs << ",\"column_sums\":" << s.gemm.n_col
+         << ",\"full_sums\":" << s.gemm.n_full << "}";
+    if (s.kind == StepK::SumPartials) os << ",\"jobs\":" << s.sums.size();
     if (s.kind == StepK::Loop) {
       os << ",\"trip\":" << s.trip << ",\"body\":";
       describe_steps(os, s.body);

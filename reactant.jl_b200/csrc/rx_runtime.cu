@@ -207,6 +207,7 @@ void join_pending_of(DevRun& r, const Step& st) {
     if (s >= 0) join_pending(r, s);
   for (int s : st.state_slots) join_pending(r, s);
   for (int s : st.yield_slots) join_pending(r, s);
+  for (auto& j : st.sums) { join_pending(r, j.src_slot); join_pending(r, j.dst_slot); }
   if (st.kind == StepK::Loop) {  // a loop body may touch anything: simplest to drain
     while (!r.pending.empty()) join_pending(r, r.pending.begin()->first);
   }
@@ -274,6 +275,9 @@ const char* kind_name(StepK k) {
     case StepK::Loop: return "loop";
     case StepK::AllReduce: return "all_reduce";
     case StepK::Scan: return "scan";
+    case StepK::SumPartials: return "sum_partials";
+    case StepK::RowsIn: return "rows_in";
+    case StepK::RowsOut: return "rows_out";
   }
   return "?";
 }
@@ -353,6 +357,7 @@ void note_writes(DevRun& r, const Step& st) {
   add(st.gemm.d_slot);
   for (int s : st.state_slots) add(s);
   for (int s : st.yield_slots) add(s);
+  for (auto& j : st.sums) add(j.dst_slot);
 }
 bool operands_settled(DevRun& r, const Step& st) {
   RxDevice* d = r.dev;
@@ -424,8 +429,36 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
       break;
     }
     case StepK::Gemm: {
-      CK(rx::run_gemm(d, st, slot_ptr(r, st.gemm.a_slot), slot_ptr(r, st.gemm.b_slot), slot_ptr(r, st.gemm.d_slot)));
-      ps.kind = d->last_gemm_tc ? "gemm_tc" : "gemm_simt";
+      const GemmDesc& g = st.gemm;
+      void* dptr = r.table[g.d_slot] ? r.table[g.d_slot]->ptr : nullptr;  // absent when the product is consumed in the epilogue only
+      if (g.has_epilogue) {
+        VmProgram P = st.prog;
+        for (int k = 0; k < P.n_leaves; ++k) P.leaf[k].ptr = k == g.acc_leaf ? nullptr : slot_ptr(r, st.leaf_slot[k]);
+        for (int k = 0; k < P.n_outs; ++k) P.out[k].ptr = slot_ptr(r, st.out_slot[k]);
+        GemmEpilogueArgs ea;
+        ea.prog = &P;
+        for (int q = 0; q < g.n_col; ++q) ea.col_partial[q] = (float*)slot_ptr(r, g.col_slot[q]);
+        for (int q = 0; q < g.n_full; ++q) ea.full_partial[q] = (float*)slot_ptr(r, g.full_slot[q]);
+        CK(rx::run_gemm(d, st, slot_ptr(r, g.a_slot), slot_ptr(r, g.b_slot), dptr, &ea));
+        if (!by_note) ps.kind = "gemm_tc_fused";
+      } else {
+        CK(rx::run_gemm(d, st, slot_ptr(r, g.a_slot), slot_ptr(r, g.b_slot), slot_ptr(r, g.d_slot)));
+        if (!by_note) ps.kind = d->last_gemm_tc ? "gemm_tc" : "gemm_simt";
+      }
+      break;
+    }
+    case StepK::SumPartials: {
+      SumPartialsJob jobs[4] = {};
+      int n = 0;
+      for (const SumJob& j : st.sums) {
+        jobs[n].src = (const float*)slot_ptr(r, j.src_slot);
+        jobs[n].dst = (float*)slot_ptr(r, j.dst_slot);
+        jobs[n].rows = j.rows;
+        jobs[n].n = j.n;
+        jobs[n].init = (float)j.init;
+        ++n;
+      }
+      CK(launch_sum_partials(c, jobs, n));
       break;
     }
     case StepK::Copy: {
@@ -434,6 +467,45 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
     }
     default:
       throw Error(RX_ERR_PLAN, std::string("internal: step kind ") + kind_name(st.kind) + " has no single-device launch");
+  }
+}
+
+// A counted loop of stencil updates over arrays split into row blocks.  The body's steps describe the update of the
+// global arrays; device g applies each one to the output rows it owns (reading its halos), then every device sends
+// the boundary rows of the array just written to its neighbours.  Row r of a device's block is global row
+// g * rows_local - halo_up + r.
+void run_row_sharded_loop(RxExecutable* ex, const Step& loop, std::vector<DevRun>& runs) {
+  const Plan& plan = *ex->plan;
+  const int64_t nparts = plan.num_partitions;
+  for (int64_t it = 0; it < loop.trip; ++it) {
+    for (const Step& b : loop.body) {
+      const Slot& blk = plan.slots[b.out_slot[0]];
+      const int64_t ld = b.st_src_ld, rows_local = blk.type.shape[0] / nparts;
+      const int64_t drow0 = b.st_dst_off / ld, row0 = b.st_src_off / ld;
+      for (auto& r : runs) {
+        RxDevice* d = r.dev;
+        CK(cudaSetDevice(d->ordinal));
+        const int64_t g = d->global_id, base = g * rows_local - blk.halo_up;
+        const int64_t o0 = std::max<int64_t>(drow0, g * rows_local), o1 = std::min<int64_t>(drow0 + b.st_rows, (g + 1) * rows_local);
+        if (o1 <= o0) continue;  // none of the updated rows is this device's
+        Step loc = b;
+        const int64_t shift = ((o0 - drow0) - base) * ld;  // global element index -> index in this device's block
+        loc.st_rows = o1 - o0;
+        loc.st_dst_off = b.st_dst_off + shift;
+        loc.st_src_off = b.st_src_off + shift;
+        (void)row0;
+        VmProgram P = bind(loc, r);
+        P.dim[0] = loc.st_rows;
+        for (int k = 0; k < P.n_leaves; ++k) P.leaf[k].offset += shift;
+        P.out[0].offset += shift;
+        ProfScope ps(d, "stencil_rows");
+        CK(rx::run_stencil(d, loc, P));
+        note_writes(r, loc);
+      }
+      rx::run_halo_exchange(ex->client, runs.size(), [&](size_t k) { return runs[k].dev; }, [&](size_t k) { return (float*)slot_ptr(runs[k], b.out_slot[0]); }, rows_local,
+                            blk.type.shape[1], blk.halo_up, blk.halo_down);
+    }
+    for (auto& r : runs) rotate_loop_state(loop, r);
   }
 }
 
@@ -452,6 +524,28 @@ void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<Dev
         ++si;
         continue;
       }
+    }
+    if (st.kind == StepK::RowsIn || st.kind == StepK::RowsOut) {
+      const Plan& plan = *ex->plan;
+      const Slot& blk = plan.slots[st.kind == StepK::RowsIn ? st.dst_slot : st.src_slot];
+      const int64_t cols = blk.type.shape[1], rows_local = blk.type.shape[0] / plan.num_partitions;
+      const size_t bytes = (size_t)rows_local * cols * sizeof(float), skip = (size_t)blk.halo_up * cols * sizeof(float);
+      for (auto& r : runs) {
+        CK(cudaSetDevice(r.dev->ordinal));
+        char* src = (char*)slot_ptr(r, st.src_slot);
+        char* dst = (char*)slot_ptr(r, st.dst_slot);
+        if (st.kind == StepK::RowsIn) CK(cudaMemcpyAsync(dst + skip, src, bytes, cudaMemcpyDeviceToDevice, r.dev->stream));
+        else CK(cudaMemcpyAsync(dst, src + skip, bytes, cudaMemcpyDeviceToDevice, r.dev->stream));
+        note_writes(r, st);
+      }
+      if (st.kind == StepK::RowsIn)
+        rx::run_halo_exchange(ex->client, runs.size(), [&](size_t k) { return runs[k].dev; }, [&](size_t k) { return (float*)slot_ptr(runs[k], st.dst_slot); }, rows_local,
+                              cols, blk.halo_up, blk.halo_down);
+      continue;
+    }
+    if (st.kind == StepK::Loop && st.row_sharded) {
+      run_row_sharded_loop(ex, st, runs);
+      continue;
     }
     if (st.kind == StepK::Loop) {
       // Same plan and same shapes on every device, so they normally take the same decision; should one decline after
@@ -566,7 +660,12 @@ void execute(RxExecutable* ex, const std::vector<RxDevice*>& devs, RxBuffer** ar
           it = cs.emplace((int)s, st).first;
         }
         r.table[s] = it->second;
-      } else {
+      } else if (sl.row_block) {
+        // this device's block of rows plus the halo rows above and below it
+        const int64_t rows_local = sl.type.shape[0] / p.num_partitions;
+        size_t bytes = (size_t)(rows_local + sl.halo_up + sl.halo_down) * (size_t)sl.type.shape[1] * dt_size(sl.type.dt);
+        r.table[s] = std::make_shared<Storage>(d, d->alloc(bytes), bytes);
+      } else if (!sl.dead) {
         size_t bytes = (size_t)sl.bytes();
         r.table[s] = std::make_shared<Storage>(d, d->alloc(bytes), bytes);
       }
@@ -815,7 +914,7 @@ static void check_device_status(RxDevice* d) {
   if (d->status[0]) {
     int s = d->status[0];
     d->status[0] = 0;
-    throw Error(RX_ERR_PEER_TIMEOUT, "a peer did not arrive at an all-reduce within the wait limit (status " + std::to_string(s) + ")");
+    throw Error(RX_ERR_PEER_TIMEOUT, std::string("a peer did not arrive at ") + (s == 2 ? "a halo exchange" : "an all-reduce") + " within the wait limit (status " + std::to_string(s) + ")");
   }
   for (int w = 1; w <= 2; ++w)
     if (d->status[w]) {
@@ -998,9 +1097,15 @@ RxExecutable* ClientCompileText(RxClient* client, const char* text, size_t len, 
   static std::mutex cache_mu;
   static std::map<std::string, std::shared_ptr<const Plan>> cache;
   static int64_t hits = 0;
+  // (the fusion switches are read when the plan is built: a module planned under other settings is another plan)
+  std::string key = s;
+  for (const char* v : {"RX_GEMM_EPILOGUE", "RX_GEMM_SIMT", "RX_GEMM_1CTA", "RX_NO_MAP_MERGE"}) {
+    const char* e = getenv(v);
+    key += std::string("\n") + v + "=" + (e ? e : "");
+  }
   {
     std::lock_guard<std::mutex> g(cache_mu);
-    auto it = cache.find(s);
+    auto it = cache.find(key);
     if (it != cache.end()) {
       ex->plan = it->second;
       ++hits;
@@ -1012,7 +1117,7 @@ RxExecutable* ClientCompileText(RxClient* client, const char* text, size_t len, 
     std::shared_ptr<const Plan> plan(build_plan(*mod).release());
     std::lock_guard<std::mutex> g(cache_mu);
     if (cache.size() >= 256) cache.clear();
-    cache[s] = plan;
+    cache[key] = plan;
     ex->plan = plan;
   }
   if (const char* dir = getenv("RX_DUMP_PLAN")) {
@@ -1041,6 +1146,18 @@ static void specialise_check_steps(const std::vector<Step>& steps, std::string& 
   for (const Step& st : steps) {
     if (st.kind == StepK::Loop) {
       specialise_check_steps(st.body, out, first);
+      continue;
+    }
+    if (st.kind == StepK::Gemm && st.gemm.has_epilogue) {
+      const std::string extra = gemm_epilogue_members(st.gemm);
+      for (bool wide : {true, false}) {
+        std::string log;
+        int64_t bytes = jit_compile_only(st.prog, -1, gemm_epilogue_family(wide), &log, extra.c_str());
+        if (bytes < 0) throw Error(RX_ERR_CUDA, std::string("epilogue of step '") + st.note + "' does not compile: " + log);
+        out += first ? "" : ",";
+        first = false;
+        out += "{\"step\":\"" + st.note + "\",\"kernel\":\"" + gemm_epilogue_family(wide) + "\",\"cubin_bytes\":" + std::to_string(bytes) + "}";
+      }
       continue;
     }
     std::vector<const char*> families;

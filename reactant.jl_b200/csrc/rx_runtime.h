@@ -19,6 +19,15 @@
 struct RxClient;
 
 constexpr int kMaxRanks = 32;
+// Layout of a device's mailbox allocation: 2 x kMaxRanks 64-bit all-reduce slots, then (at kHaloFlagsOffset bytes) the
+// halo-exchange flags [parity][direction] as 32-bit sequence numbers, then (at kHaloWindowOffset bytes) the halo
+// windows [parity][direction][kHaloMaxRows][kHaloMaxCols] of floats.  Direction 0 = rows arriving from the device
+// above (smaller rank), 1 = from the device below.
+constexpr int kHaloMaxRows = 2;
+constexpr int kHaloMaxCols = 16384;
+constexpr size_t kHaloFlagsOffset = sizeof(unsigned long long) * 2 * kMaxRanks;
+constexpr size_t kHaloWindowOffset = kHaloFlagsOffset + 512;
+constexpr size_t kMailboxBytes = kHaloWindowOffset + sizeof(float) * 2 * 2 * kHaloMaxRows * kHaloMaxCols;
 
 // Peer mailboxes for the NVLink all-reduce: slot [parity][rank] of every device.
 struct MailTable {
@@ -180,6 +189,7 @@ struct RxClient {
   bool nccl_ready = false;
   bool peers_enabled = false;
   uint32_t epoch = 0;       // all-reduce sequence number (same on every rank)
+  uint32_t halo_epoch = 0;  // halo-exchange sequence number (same on every rank)
   int allreduce_mode = 0;   // 0 auto, 1 nccl, 2 mailbox
   // How long a kernel waits for a peer's word in an all-reduce mailbox before it gives up and reports
   // RX_ERR_PEER_TIMEOUT.  Ranks that are separate processes can be far apart in host time (a cold compile cache, a

@@ -1,6 +1,6 @@
-// Stencil step.  First path: the generic strided map kernel (neighbouring reads
-// are served by L1/L2).  The TMA-staged shared-memory kernel replaces it for
-// f32 windows when the tensor-map entry point is available.
+// Stencil step: the TMA-staged shared-memory kernel (rx_stencil_tma.cu) takes f32 windows whose row pitch is a
+// multiple of 16 bytes; any other window runs the generic strided map kernel (neighbouring reads are served by
+// L1/L2).  Both are part of the library: a build without rx_stencil_tma.cu does not link.
 #include "rx_stencil.h"
 
 namespace rx {
@@ -13,16 +13,6 @@ cudaError_t run_stencil(RxDevice* d, const Step& st, const VmProgram& P) {
   d->last_stencil_tma = handled;
   if (handled) return e;
   return launch_map(d->ctx(), P);
-}
-
-__attribute__((weak)) cudaError_t run_stencil_loop(RxDevice*, const std::vector<const Step*>&, const std::vector<VmProgram>&, int64_t, bool* handled) {
-  *handled = false;
-  return cudaSuccess;
-}
-
-__attribute__((weak)) cudaError_t run_stencil_tma(RxDevice*, const Step&, const VmProgram&, bool* handled) {
-  *handled = false;
-  return cudaSuccess;
 }
 
 }  // namespace rx

@@ -84,7 +84,7 @@ def logsumexp_dims1(rows: int, cols: int, raw: bool = False) -> str:
             f"  func.func @main(%arg0: {ta}) -> {tr} {{\n{body}\n  }}\n}}\n")
 
 
-def jacobi2d(n: int, steps: int, form: str = "dus") -> str:
+def jacobi2d(n: int, steps: int, form: str = "dus", num_partitions: int = 1) -> str:
     """Jacobi-2D on n x n Float32 arrays; both arrays are mutated, hence donated and aliased to the two results.
 
     form="dus" / "pad": `steps` sweeps of
@@ -93,8 +93,12 @@ def jacobi2d(n: int, steps: int, form: str = "dus") -> str:
     communication patterns can produce ("pad", src/compiler/OptimizationPasses.jl:356-372).
     form="halfsteps": the spelling of benchmark/polybench/stencil.jl:263-289 -- every one of the `steps`
     iterations updates B from A and then A from B (two sweeps, no swap), the five terms added in that file's
-    order: centre, j-1, j+1, i+1, i-1."""
+    order: centre, j-1, j+1, i+1, i-1.
+    With num_partitions > 1 both arrays are split over a 1-D mesh along Julia's second dimension (the first, i.e.
+    row, dimension of the tensors): NamedSharding(mesh, (nothing, :x))."""
     t, ti = _t([n, n]), _t([n - 2, n - 2])
+    shard = ', sdy.sharding = #sdy.sharding<@mesh, [{"x"}, {}]>' if num_partitions > 1 else ""
+    mesh = f'  sdy.mesh @mesh = <["x"={num_partitions}]>\n' if num_partitions > 1 else ""
     m = n - 1
     # physical dims are reversed Julia dims: Julia A[i-1, j] is the minor-dim neighbour
     centre, i_lo, i_hi, j_lo, j_hi = f"[1:{m}, 1:{m}]", f"[1:{m}, 0:{n - 2}]", f"[1:{m}, 2:{n}]", f"[0:{n - 2}, 1:{m}]", f"[2:{n}, 1:{m}]"
@@ -131,8 +135,8 @@ def jacobi2d(n: int, steps: int, form: str = "dus") -> str:
                      f"    %pm = stablehlo.pad %ones, %false, low = [1, 1], high = [1, 1], interior = [0, 0] : ({_t([n - 2, n - 2], 'i1')}, tensor<i1>) -> {_t([n, n], 'i1')}\n")
         yields = "%1, %nb, %iterArg_0"
     body = "\n".join(lines)
-    return f"""module @reactant_jacobi2d attributes {{mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64}} {{
-  func.func @main(%arg0: {t} {{tf.aliasing_output = 0 : i32}}, %arg1: {t} {{tf.aliasing_output = 1 : i32}}) -> ({t}, {t}) {{
+    return f"""module @reactant_jacobi2d attributes {{mhlo.num_partitions = {num_partitions} : i64, mhlo.num_replicas = 1 : i64}} {{
+{mesh}  func.func @main(%arg0: {t} {{tf.aliasing_output = 0 : i32{shard}}}, %arg1: {t} {{tf.aliasing_output = 1 : i32{shard}}}) -> ({t}, {t}) {{
     %c = stablehlo.constant dense<0> : tensor<i64>
     %c_0 = stablehlo.constant dense<{steps}> : tensor<i64>
     %c_2 = stablehlo.constant dense<1> : tensor<i64>

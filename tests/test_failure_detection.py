@@ -82,3 +82,27 @@ def test_handle_misuse_is_an_error_not_a_crash(rx, client):
     with pytest.raises(rx.ReactantError) as e:
         rx._lib.check()
     assert "num_results" in str(e.value)
+
+
+def test_halo_exchange_wait_runs_out_and_is_reported(rx):
+    """Rank 0 of a two-process mesh whose second process does not exist: the rows this rank waits for never arrive, the
+    exchange kernel gives up after the client's peer wait and returns, and the next read reports the timeout."""
+    client = rx.Client(node_id=0, num_nodes=2, allowed_devices=[0], peer_wait_ms=300)
+    try:
+        h = client.mailbox_handles()
+        client.open_mailboxes(h + h)
+        n = 64
+        f = rx.compile(rx.programs.jacobi2d(n, 2, num_partitions=2), client)
+        sh = rx.NamedSharding(rx.Mesh(client.devices, ("x",)), (None, "x"))
+        z = np.zeros((n, n // 2), np.float32)      # this rank's half of the columns (Julia layout)
+        A = rx.from_local_shards([z], (n, n), sh, client)
+        B = rx.from_local_shards([z], (n, n), sh, client)
+        ra, rb = f(A, B)
+        with pytest.raises(rx.ReactantError) as e:
+            ra.data[0].to_host()
+        assert e.value.code == 10 and "halo exchange" in str(e.value)
+        g = rx.compile(rx.programs.sinsum_add(16), client)   # the device is still usable
+        x = rx.to_rarray(np.zeros(16, np.float32), client)
+        assert float(g(x, x)) == 0.0
+    finally:
+        client.close()

@@ -243,3 +243,25 @@ def test_update_target_that_is_still_read_later_is_copied(rx):
 """
     p = rx.plan_describe(text)
     assert "copy" in kinds(p), p
+
+
+def test_row_sharded_jacobi_plans_with_halo_rows(rx):
+    for form, body in (("dus", ["stencil"]), ("halfsteps", ["stencil", "stencil"])):
+        p = rx.plan_describe(rx.programs.jacobi2d(8192, 100, form=form, num_partitions=8))
+        assert kinds(p) == ["rows_in", "rows_in", "loop", "rows_out", "rows_out"]
+        loop = p["steps"][2]
+        assert [s["kind"] for s in loop["body"]] == body and "halo 1 up, 1 down" in loop["note"]
+    # a loop that carries anything else in sharded form is refused by name
+    text = rx.programs.jacobi1d(64, 2).replace("mhlo.num_partitions = 1", "mhlo.num_partitions = 2")
+    text = text.replace("  func.func @main", '  sdy.mesh @mesh = <["x"=2]>\n  func.func @main', 1)
+    text = text.replace("{tf.aliasing_output = 0 : i32}", '{tf.aliasing_output = 0 : i32, sdy.sharding = #sdy.sharding<@mesh, [{"x"}]>}')
+    with pytest.raises(rx.ReactantError) as e:
+        rx.plan_describe(text)
+    assert e.value.code == 2 and "sharded" in str(e.value)
+
+
+def test_a_dimension_the_mesh_does_not_divide_is_replicated(rx):
+    """src/Sharding.jl:582-654: no padding; the argument falls back to a sharding that fits -- here replication, so the
+    reduce needs no all-reduce and every device computes the whole sum."""
+    p = rx.plan_describe(rx.programs.sinsum_add(1001, num_partitions=4))
+    assert kinds(p) == ["reduce_full"] and p["steps"][0]["dims"] == [1001]
