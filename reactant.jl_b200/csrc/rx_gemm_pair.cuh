@@ -247,6 +247,7 @@ struct EpiChain {
 #pragma unroll
       for (int sub = 0; sub < 32; sub += V) load_v(C::leaf(P, k), m, n0 + sub, vec, &L[k][sub]);
     }
+    tmem_ld_wait();  // the accumulators (requested by the caller) and the operands above arrive together
 #pragma unroll
     for (int sub = 0; sub < 32; sub += V) {
       uint32_t R[C::kRegs][V];
@@ -545,9 +546,10 @@ __global__ void __launch_bounds__(64 + 32 * Epi::kWarps, 1) k_gemm_pair(const __
         for (int c = c0; c < c0 + kColsPerWarp; c += 32) {
           uint32_t v[32];
           tmem_ld32(taddr + c, v);
-          tmem_ld_wait();
-          // rows and columns come in whole groups of 32 (the launcher checks M % 32 == 0 and N % 32 == 0)
+          // rows and columns come in whole groups of 32 (the launcher checks M % 32 == 0 and N % 32 == 0); piece()
+          // waits for the accumulators itself, after it has asked for its other operands
           if (row_ok && (long long)tn * 256 + c < p.N) Epi::piece(ts, ep, p, m, (long long)tn * 256 + c, v);
+          else tmem_ld_wait();
         }
         Epi::end_tile(ts, ep, (t * 2 + (int)rank) * Epi::kWarps + (warp - 2), row_ok);
       } else if (p.tma_store) {

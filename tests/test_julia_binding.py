@@ -102,6 +102,13 @@ def test_registration_uses_the_keywords_the_reference_has():
         assert kws <= allowed, f"register_backend called with {kws - allowed}, which src/accelerators/Registration.jl:24-30 does not accept"
 
 
+def test_integration_document_lists_the_committed_file():
+    doc = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    m = re.search(r"```julia\n(.*?)```", doc, flags=re.S)
+    assert m, "INTEGRATION.md holds no julia listing"
+    assert m.group(1) == open(JL).read(), "the listing in INTEGRATION.md is not reactant.jl_b200/julia/B200Backend.jl"
+
+
 def test_ownership_registry_distinguishes_foreign_handles(rx):
     lib = rx._lib.lib()
     junk = ctypes.c_int(0)
