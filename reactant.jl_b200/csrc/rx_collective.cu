@@ -13,6 +13,7 @@
 // In the reference this collective is inserted and executed by XLA's SPMD
 // partitioner and NCCL thunks (deps/ReactantExtra/API.cpp:1487-1497).
 #include "rx_collective.h"
+#include "rx_halo.cuh"
 
 #include <dlfcn.h>
 #include <nccl.h>
@@ -99,69 +100,9 @@ __global__ void k_allreduce_mailbox(float* __restrict__ val, MailTable mail, int
 }
 
 // ---- halo exchange of row-sharded arrays -------------------------------------------------------------------------
-struct HaloArgs {
-  float* block;            // this device's rows: [up halo][owned][down halo], `cols` floats each
-  long long rows_local, cols;
-  int up, down;            // halo heights
-  int rank, n;
-  unsigned epoch;
-  long long poll_limit;
-  int* status;
-};
-__device__ __forceinline__ float* halo_window(unsigned long long* mailbox, int parity, int dir) {
-  return (float*)((char*)mailbox + kHaloWindowOffset) + ((size_t)(parity * 2 + dir) * kHaloMaxRows) * kHaloMaxCols;
-}
-__device__ __forceinline__ volatile unsigned* halo_flag(unsigned long long* mailbox, int parity, int dir) {
-  return (volatile unsigned*)((char*)mailbox + kHaloFlagsOffset) + parity * 2 + dir;
-}
-// One CTA per device.  Rows are whole multiples of 4 floats (checked by the launcher), so everything moves as float4.
-__global__ void __launch_bounds__(1024) k_halo_exchange(const __grid_constant__ HaloArgs a, const __grid_constant__ MailTable mail) {
-  __shared__ int failed;
-  const int parity = a.epoch & 1;
-  const long long c4 = a.cols >> 2;
-  if (threadIdx.x == 0) failed = 0;
-  // send: my first `down` owned rows to the device above (they are its lower halo), my last `up` owned rows to the device below
-  if (a.rank > 0 && a.down > 0) {
-    const float4* src = (const float4*)(a.block + (long long)a.up * a.cols);
-    float4* dst = (float4*)halo_window(mail.peer[a.rank - 1], parity, 1);
-    for (long long i = threadIdx.x; i < a.down * c4; i += blockDim.x) dst[(i / c4) * (kHaloMaxCols / 4) + i % c4] = src[i];
-  }
-  if (a.rank + 1 < a.n && a.up > 0) {
-    const float4* src = (const float4*)(a.block + (a.up + a.rows_local - a.up) * a.cols);
-    float4* dst = (float4*)halo_window(mail.peer[a.rank + 1], parity, 0);
-    for (long long i = threadIdx.x; i < a.up * c4; i += blockDim.x) dst[(i / c4) * (kHaloMaxCols / 4) + i % c4] = src[i];
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    if (a.rank > 0) *halo_flag(mail.peer[a.rank - 1], parity, 1) = a.epoch;
-    if (a.rank + 1 < a.n) *halo_flag(mail.peer[a.rank + 1], parity, 0) = a.epoch;
-    __threadfence_system();
-    // receive: bounded wait for the neighbours' sequence numbers
-    for (int dir = 0; dir < 2; ++dir) {
-      if (dir == 0 ? a.rank == 0 : a.rank + 1 >= a.n) continue;
-      volatile unsigned* f = halo_flag(mail.peer[a.rank], parity, dir);
-      long long spins = 0;
-      while (*f != a.epoch) {
-        if (++spins > a.poll_limit) { failed = 1; break; }
-        __nanosleep(kPeerPollNs);
-      }
-    }
-    if (failed) *a.status = 2;
-  }
-  __syncthreads();
-  if (failed) return;  // the halos keep their old rows; the host reports the timeout
-  __threadfence_system();
-  if (a.rank > 0 && a.up > 0) {
-    const float4* src = (const float4*)halo_window(mail.peer[a.rank], parity, 0);
-    float4* dst = (float4*)a.block;
-    for (long long i = threadIdx.x; i < a.up * c4; i += blockDim.x) dst[i] = __ldcv(&src[(i / c4) * (kHaloMaxCols / 4) + i % c4]);
-  }
-  if (a.rank + 1 < a.n && a.down > 0) {
-    const float4* src = (const float4*)halo_window(mail.peer[a.rank], parity, 1);
-    float4* dst = (float4*)(a.block + (a.up + a.rows_local) * a.cols);
-    for (long long i = threadIdx.x; i < a.down * c4; i += blockDim.x) dst[i] = __ldcv(&src[(i / c4) * (kHaloMaxCols / 4) + i % c4]);
-  }
+// One CTA per device (rx_halo.cuh); a wait that runs out sets status 2 for the host.
+__global__ void __launch_bounds__(1024) k_halo_exchange(const __grid_constant__ HaloArgs a, int* status) {
+  if (!halo_exchange_cta(a) && threadIdx.x == 0) *status = 2;
 }
 
 void ensure_mailbox(RxDevice* d) {
@@ -310,6 +251,34 @@ bool mailboxes_ready_impl(RxClient* c) {
 }
 }  // namespace
 
+bool halo_exchange_possible(RxClient* c, int64_t cols, int up, int down) {
+  if (c->n_global() <= 1) return false;
+  if (cols % 4 || cols > kHaloMaxCols || up > kHaloMaxRows || down > kHaloMaxRows || up < 0 || down < 0) return false;
+  return mailboxes_ready_impl(c);
+}
+
+void halo_fill_args(RxClient* c, RxDevice* d, int64_t rows_local, int64_t cols, int up, int down, HaloArgs* out) {
+  const int world = c->n_global();
+  HaloArgs a{};
+  a.rows_local = rows_local;
+  a.cols = cols;
+  a.up = up;
+  a.down = down;
+  a.rank = d->global_id;
+  a.n = world;
+  a.poll_limit = c->peer_wait_polls();
+  a.mail_self = d->mail.peer[a.rank];
+  a.mail_above = a.rank > 0 ? d->mail.peer[a.rank - 1] : nullptr;
+  a.mail_below = a.rank + 1 < world ? d->mail.peer[a.rank + 1] : nullptr;
+  *out = a;
+}
+
+unsigned halo_reserve_epochs(RxClient* c, unsigned count) {
+  const unsigned first = c->halo_epoch + 1;
+  c->halo_epoch += count;
+  return first;
+}
+
 void run_halo_exchange(RxClient* c, size_t n_local, const std::function<RxDevice*(size_t)>& dev, const std::function<float*(size_t)>& block, int64_t rows_local,
                        int64_t cols, int up, int down) {
   const int world = c->n_global();
@@ -336,12 +305,14 @@ void run_halo_exchange(RxClient* c, size_t n_local, const std::function<RxDevice
     a.n = world;
     a.epoch = epoch;
     a.poll_limit = c->peer_wait_polls();
-    a.status = dstatus;
+    a.mail_self = d->mail.peer[a.rank];
+    a.mail_above = a.rank > 0 ? d->mail.peer[a.rank - 1] : nullptr;
+    a.mail_below = a.rank + 1 < world ? d->mail.peer[a.rank + 1] : nullptr;
     if ((uintptr_t)a.block % 16) throw Error(RX_ERR_PLAN, "internal: row block is not 16-byte aligned");
     bool prof = d->profiling;
     cudaEvent_t ea = nullptr, eb = nullptr;
     if (prof) { cudaEventCreate(&ea); cudaEventCreate(&eb); cudaEventRecord(ea, d->stream); }
-    k_halo_exchange<<<1, 1024, 0, d->stream>>>(a, d->mail);
+    k_halo_exchange<<<1, 1024, 0, d->stream>>>(a, dstatus);
     if (prof) { cudaEventRecord(eb, d->stream); d->spans.push_back({"halo_exchange", ea, eb}); }
     ++d->launches;
     cck(cudaGetLastError(), "k_halo_exchange");

@@ -33,6 +33,14 @@ void run_allreduce(RxClient* c, const Step& st, size_t n_local, const std::funct
 void run_halo_exchange(RxClient* c, size_t n_local, const std::function<RxDevice*(size_t)>& dev, const std::function<float*(size_t)>& block, int64_t rows_local,
                        int64_t cols, int up, int down);
 
+// For kernels that do the exchange themselves (the whole-loop stencil kernel): whether rows of `cols` floats with these
+// halo heights fit the exchange windows and the peer mailboxes are open; the device-independent part of the arguments
+// for local device d; and a run of `count` consecutive sequence numbers (the first is returned).
+bool halo_exchange_possible(RxClient* c, int64_t cols, int up, int down);
+struct HaloArgs;
+void halo_fill_args(RxClient* c, RxDevice* d, int64_t rows_local, int64_t cols, int up, int down, HaloArgs* out);
+unsigned halo_reserve_epochs(RxClient* c, unsigned count);
+
 // If a single-word all-reduce can go through the mailboxes, advance the epoch and fill
 // one FusedAllReduce per local device (to be handed to the producing reduce kernel).
 bool prepare_fused_allreduce(RxClient* c, const Step& ar_step, const std::vector<RxDevice*>& devs, std::vector<FusedAllReduce>* out);

@@ -560,7 +560,7 @@ cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code
   int nseg = (int)std::min<int64_t>(std::min(want, max_seg), 1024);
   int64_t seg = ((n + nseg - 1) / nseg + 1023) / 1024 * 1024;
   nseg = (int)((n + seg - 1) / seg);
-  if ((size_t)(outer * nseg) + 2 > c.scratch_words) return cudaErrorInvalidValue;
+  if ((size_t)(outer * nseg) + 4 > c.scratch_words) return cudaErrorInvalidValue;  // the last four words belong to the stencil loop and the reductions
   uint32_t* partial = c.scratch;
   dim3 grid((unsigned)nseg, (unsigned)outer);
   if (nseg > 1) {

@@ -474,30 +474,113 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
 // global arrays; device g applies each one to the output rows it owns (reading its halos), then every device sends
 // the boundary rows of the array just written to its neighbours.  Row r of a device's block is global row
 // g * rows_local - halo_up + r.
+// The part of stencil step `b` that device r.dev owns, in the coordinates of its row block: the step with shifted
+// offsets and its bound program.  False if none of the updated rows is this device's.
+bool local_stencil_step(const Plan& plan, const Step& b, DevRun& r, Step* loc, VmProgram* P) {
+  const Slot& blk = plan.slots[b.out_slot[0]];
+  const int64_t ld = b.st_src_ld, rows_local = blk.type.shape[0] / plan.num_partitions;
+  const int64_t drow0 = b.st_dst_off / ld;
+  const int64_t g = r.dev->global_id, base = g * rows_local - blk.halo_up;
+  const int64_t o0 = std::max<int64_t>(drow0, g * rows_local), o1 = std::min<int64_t>(drow0 + b.st_rows, (g + 1) * rows_local);
+  if (o1 <= o0) return false;
+  *loc = b;
+  const int64_t shift = ((o0 - drow0) - base) * ld;  // global element index -> index in this device's block
+  loc->st_rows = o1 - o0;
+  loc->st_dst_off = b.st_dst_off + shift;
+  loc->st_src_off = b.st_src_off + shift;
+  *P = bind(*loc, r);
+  P->dim[0] = loc->st_rows;
+  for (int k = 0; k < P->n_leaves; ++k) P->leaf[k].offset += shift;
+  P->out[0].offset += shift;
+  return true;
+}
+
+// The whole row-sharded loop as one cooperative launch per device, boundary rows exchanged inside the kernel between
+// sweeps.  Taken only if every device can take it (they wait for one another's rows).
+bool try_row_sharded_stencil_loop(RxExecutable* ex, const Step& loop, std::vector<DevRun>& runs) {
+  const bool off = getenv("RX_STENCIL_LOOP") && atoi(getenv("RX_STENCIL_LOOP")) == 0;  // read per call: tests compare both forms in one process
+  if (off || loop.trip < 2 || loop.body.empty() || loop.body.size() > 4) return false;
+  const Plan& plan = *ex->plan;
+  const Slot& blk0 = plan.slots[loop.body[0].out_slot[0]];
+  for (const Step& b : loop.body) {
+    const Slot& blk = plan.slots[b.out_slot[0]];
+    if (b.kind != StepK::Stencil || blk.type.shape != blk0.type.shape || blk.halo_up != blk0.halo_up || blk.halo_down != blk0.halo_down) return false;
+  }
+  const int64_t rows_local = blk0.type.shape[0] / plan.num_partitions, cols = blk0.type.shape[1];
+  if (!rx::halo_exchange_possible(ex->client, cols, blk0.halo_up, blk0.halo_down)) return false;
+  if (runs.size() != ex->client->devices.size()) return false;
+  struct PerDev {
+    std::vector<Step> local;
+    std::vector<const Step*> steps;
+    std::vector<VmProgram> bound;
+    rx::StencilLoopHalo halo;
+    int period = 0;
+  };
+  std::vector<PerDev> per(runs.size());
+  const int64_t total = loop.trip * (int64_t)loop.body.size();
+  for (size_t k = 0; k < runs.size(); ++k) {
+    DevRun& r = runs[k];
+    PerDev& pd = per[k];
+    CK(cudaSetDevice(r.dev->ordinal));
+    const auto saved = r.table;
+    pd.local.reserve(8);
+    bool ok = true;
+    for (int p = 1; p <= 4 && !pd.period && ok; ++p) {
+      if (pd.local.size() + loop.body.size() > 4) break;
+      for (const Step& b : loop.body) {
+        Step loc;
+        VmProgram P;
+        if (!local_stencil_step(plan, b, r, &loc, &P)) { ok = false; break; }
+        pd.local.push_back(loc);
+        pd.bound.push_back(P);
+        pd.halo.block.push_back((float*)slot_ptr(r, b.out_slot[0]));
+      }
+      rotate_loop_state(loop, r);
+      if (r.table == saved) pd.period = p;
+    }
+    r.table = saved;
+    if (!ok || !pd.period) return false;
+    for (const Step& s : pd.local) pd.steps.push_back(&s);
+    rx::halo_fill_args(ex->client, r.dev, rows_local, cols, blk0.halo_up, blk0.halo_down, &pd.halo.args);
+    bool would = false;
+    CK(rx::run_stencil_loop(r.dev, pd.steps, pd.bound, total, &would, &pd.halo, true));
+    if (!would) return false;
+  }
+  const unsigned epoch0 = rx::halo_reserve_epochs(ex->client, (unsigned)(total - 1));
+  for (size_t k = 0; k < runs.size(); ++k) {
+    DevRun& r = runs[k];
+    PerDev& pd = per[k];
+    CK(cudaSetDevice(r.dev->ordinal));
+    pd.halo.epoch0 = epoch0;
+    bool handled = false;
+    {
+      ProfScope ps(r.dev, "stencil_rows_loop");
+      CK(rx::run_stencil_loop(r.dev, pd.steps, pd.bound, total, &handled, &pd.halo, false));
+    }
+    // every device passed the dry run with the same arguments; a launch that is refused now leaves the others waiting
+    // until their bounded wait runs out, which the host then reports
+    if (!handled) throw Error(RX_ERR_CUDA, "row-sharded stencil loop: cooperative launch refused after the dry run accepted it");
+    note_writes(r, loop);
+    r.dev->last_stencil_tma = true;
+    for (int64_t i = 0; i < loop.trip % pd.period; ++i) rotate_loop_state(loop, r);
+  }
+  return true;
+}
+
 void run_row_sharded_loop(RxExecutable* ex, const Step& loop, std::vector<DevRun>& runs) {
   const Plan& plan = *ex->plan;
   const int64_t nparts = plan.num_partitions;
+  if (try_row_sharded_stencil_loop(ex, loop, runs)) return;
   for (int64_t it = 0; it < loop.trip; ++it) {
     for (const Step& b : loop.body) {
       const Slot& blk = plan.slots[b.out_slot[0]];
-      const int64_t ld = b.st_src_ld, rows_local = blk.type.shape[0] / nparts;
-      const int64_t drow0 = b.st_dst_off / ld, row0 = b.st_src_off / ld;
+      const int64_t rows_local = blk.type.shape[0] / nparts;
       for (auto& r : runs) {
         RxDevice* d = r.dev;
         CK(cudaSetDevice(d->ordinal));
-        const int64_t g = d->global_id, base = g * rows_local - blk.halo_up;
-        const int64_t o0 = std::max<int64_t>(drow0, g * rows_local), o1 = std::min<int64_t>(drow0 + b.st_rows, (g + 1) * rows_local);
-        if (o1 <= o0) continue;  // none of the updated rows is this device's
-        Step loc = b;
-        const int64_t shift = ((o0 - drow0) - base) * ld;  // global element index -> index in this device's block
-        loc.st_rows = o1 - o0;
-        loc.st_dst_off = b.st_dst_off + shift;
-        loc.st_src_off = b.st_src_off + shift;
-        (void)row0;
-        VmProgram P = bind(loc, r);
-        P.dim[0] = loc.st_rows;
-        for (int k = 0; k < P.n_leaves; ++k) P.leaf[k].offset += shift;
-        P.out[0].offset += shift;
+        Step loc;
+        VmProgram P;
+        if (!local_stencil_step(plan, b, r, &loc, &P)) continue;  // none of the updated rows is this device's
         ProfScope ps(d, "stencil_rows");
         CK(rx::run_stencil(d, loc, P));
         note_writes(r, loc);

@@ -18,6 +18,7 @@
 // down to a multiple of 4 floats and the box is widened); no multicast is used.
 #include "rx_device.cuh"
 #include "rx_stencil.h"
+#include "rx_halo.cuh"
 #include "rx_tma.h"
 
 namespace rx {
@@ -48,28 +49,40 @@ struct StencilParams {
 // stage is drained.  Returns false if a load did not arrive within the wait limit.
 // `reverse` walks the tile list from its far end: consecutive sweeps of one launch alternate direction, so that a
 // sweep starts on the part of the arrays the previous sweep touched last, which is still in L2.
+// `cta` of `ncta` CTAs share the tile list.  With `edge_rows` the tiles of the first and last tile row come first
+// (they hold the rows a row-sharded array's neighbours are waiting for), each counted in *edge_counter once its
+// rows are written, and only the remaining tiles alternate direction.
 template <bool FAST5, int TH>
 __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const StencilParams& p, const VmProgram* P, float fast_c, float* const* tile, uint64_t* bars,
-                                              int& it, bool reverse = false) {
+                                              int& it, bool reverse = false, int cta = blockIdx.x, int ncta = gridDim.x, bool edge_rows = false,
+                                              unsigned* edge_counter = nullptr) {
   const uint32_t bytes = (uint32_t)(BOX_W * p.box_h * sizeof(float));
   const int ntiles = p.tiles_x * p.tiles_y;
+  const int n_edge = edge_rows ? (p.tiles_y >= 2 ? 2 : 1) * p.tiles_x : 0;
+  // position in this sweep's order -> tile
+  auto tile_of = [&](int t) {
+    if (t < n_edge) return t < p.tiles_x ? t : (p.tiles_y - 1) * p.tiles_x + (t - p.tiles_x);
+    if (!edge_rows) return reverse ? ntiles - 1 - t : t;
+    const int u = t - n_edge, n_int = ntiles - n_edge;
+    return p.tiles_x + (reverse ? n_int - 1 - u : u);
+  };
   auto issue = [&](int t, int s) {
-    if (reverse) t = ntiles - 1 - t;
+    t = tile_of(t);
     int ty = t / p.tiles_x, tx = t - ty * p.tiles_x;
     mbar_expect_tx(&bars[s], bytes);
     tma_load_2d(tile[s], tmap, p.x_base + tx * p.tw, p.y_base + ty * TH, &bars[s]);
   };
-  int first = blockIdx.x;
+  int first = cta;
   if (threadIdx.x == 0)
     for (int q = 0; q < STAGES - 1; ++q)
-      if (first + q * (int)gridDim.x < ntiles) issue(first + q * (int)gridDim.x, (it + q) % STAGES);
-  for (int t = first; t < ntiles; t += gridDim.x, ++it) {
+      if (first + q * ncta < ntiles) issue(first + q * ncta, (it + q) % STAGES);
+  for (int t = first; t < ntiles; t += ncta, ++it) {
     int s = it % STAGES;
     uint32_t parity = (it / STAGES) & 1;
-    int next = t + (STAGES - 1) * (int)gridDim.x;
+    int next = t + (STAGES - 1) * ncta;
     if (threadIdx.x == 0 && next < ntiles) issue(next, (it + STAGES - 1) % STAGES);  // that stage was drained before the last barrier
     if (!mbar_wait(&bars[s], parity, kWaitLimit)) return false;
-    const int tt = reverse ? ntiles - 1 - t : t;
+    const int tt = tile_of(t);
     int ty = tt / p.tiles_x, tx = tt - ty * p.tiles_x;
     int64_t c = (int64_t)tx * p.tw + threadIdx.x;
     int64_t r0 = (int64_t)ty * TH;
@@ -115,6 +128,10 @@ __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const Ste
       }
     }
     __syncthreads();  // every thread is done with stage s before it is refilled
+    if (t < n_edge && threadIdx.x == 0) {
+      __threadfence();  // the tile's rows, written by all threads before the barrier, precede the count
+      atomicAdd(edge_counter, 1u);
+    }
   }
   return true;
 }
@@ -165,6 +182,16 @@ struct LoopParams {
   int total;          // sweeps to run = loop trip count x stencil steps per iteration
   int alternate;      // odd sweeps walk the tiles backwards
   unsigned* counter;  // zero at launch
+  // Row-sharded arrays (the device owns a block of rows of each array and keeps copies of its neighbours' boundary
+  // rows): between two sweeps CTA 0 exchanges the boundary rows of the array just written with the neighbouring
+  // devices, and the other CTAs are released into the next sweep only when the received rows are in place.
+  int halo;           // 1: CTA 0 exchanges after every sweep but the last, the other CTAs share the tiles
+  unsigned* edge;     // zero at launch: finished first- and last-row tiles, over all sweeps
+  int* peer_status;   // the device's status word for waits on peers
+  HaloArgs hx;        // .block and .epoch are filled per sweep: block = halo_block[phase], epoch = halo_epoch0 + sweep
+  float* halo_block[kMaxPhases];
+  unsigned halo_epoch0;
+  unsigned* release;  // zero at launch; sweep + 1 once the exchange after `sweep` is done, 0xFFFFFFFF if it failed
 };
 
 template <int TH>
@@ -181,23 +208,67 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
     mbar_fence_init();
   }
   __syncthreads();
+
+  if (lp.halo && blockIdx.x == 0) {
+    // The exchange CTA.  As soon as the tiles holding the first and last owned rows of sweep s are written (the
+    // workers take them first), it trades those rows with the neighbouring devices -- while the workers are busy
+    // with the rest of the sweep -- and publishes `release = s + 1`; the workers need that before sweep s + 1.
+    for (int sweep = 0; sweep + 1 < lp.total; ++sweep) {
+      const int ph = sweep % lp.n_phases;
+      const unsigned n_edge = (unsigned)((lp.ph[ph].tiles_y >= 2 ? 2 : 1) * lp.ph[ph].tiles_x);
+      int ok = 1;
+      if (threadIdx.x == 0) {
+        // edge tiles are counted per phase geometry; all phases of a loop share it (checked by the launcher)
+        const unsigned target = (unsigned)(sweep + 1) * n_edge;
+        long long spins = 0;
+        for (;;) {
+          unsigned v;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(lp.edge) : "memory");
+          if (v >= target) break;
+          if (++spins > kWaitLimit) { ok = 0; break; }
+          if (spins > 64) __nanosleep(100);
+        }
+      }
+      ok = __syncthreads_and(ok);
+      bool got = false;
+      if (ok) {
+        HaloArgs hx = lp.hx;
+        hx.block = lp.halo_block[ph];
+        hx.epoch = lp.halo_epoch0 + (unsigned)sweep;
+        got = halo_exchange_cta(hx);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");  // the received rows are read by the next sweep's bulk loads
+        if (!ok) *lp.ph[0].status = 3;
+        else if (!got) *lp.peer_status = 2;  // what the stand-alone exchange kernel reports
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(lp.release), "r"(got ? (unsigned)(sweep + 1) : 0xFFFFFFFFu) : "memory");
+      }
+      if (!got) return;
+    }
+    return;
+  }
+
+  const int cta = lp.halo ? (int)blockIdx.x - 1 : (int)blockIdx.x;
+  const int ncta = lp.halo ? (int)gridDim.x - 1 : (int)gridDim.x;
   int it = 0;
   for (int sweep = 0; sweep < lp.total; ++sweep) {
     const int ph = sweep % lp.n_phases;
-    if (!stencil_sweep<true, TH>(&maps.m[ph], lp.ph[ph], nullptr, lp.k[ph], tile, bars, it, lp.alternate && (sweep & 1))) {
+    if (!stencil_sweep<true, TH>(&maps.m[ph], lp.ph[ph], nullptr, lp.k[ph], tile, bars, it, lp.alternate && (sweep & 1), cta, ncta, lp.halo != 0, lp.edge)) {
       if (threadIdx.x == 0) *lp.ph[0].status = 2;
       stencil_drain(bars);
       return;
     }
     if (sweep + 1 == lp.total) break;
-    // grid-wide barrier between sweeps
+    // grid-wide barrier between sweeps (over the worker CTAs); with an exchange, its rows must be in place too
     __syncthreads();
     int ok = 1;
     if (threadIdx.x == 0) {
       __threadfence();
       asm volatile("fence.proxy.async;" ::: "memory");
       atomicAdd(lp.counter, 1u);
-      const unsigned target = (unsigned)(sweep + 1) * gridDim.x;
+      const unsigned target = (unsigned)(sweep + 1) * (unsigned)ncta;
       long long spins = 0;
       for (;;) {
         unsigned v;
@@ -205,13 +276,22 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
         if (v >= target) break;
         if (++spins > kWaitLimit) { ok = 0; break; }
       }
+      if (ok && lp.halo) {
+        spins = 0;
+        for (;;) {
+          unsigned v;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(lp.release) : "memory");
+          if (v == 0xFFFFFFFFu) { ok = -1; break; }  // the exchange CTA gave up and has reported why
+          if (v >= (unsigned)(sweep + 1)) break;
+          if (++spins > kWaitLimit + lp.hx.poll_limit) { ok = 0; break; }
+          if (spins > 64) __nanosleep(100);
+        }
+      }
       asm volatile("fence.proxy.async;" ::: "memory");
+      if (ok == 0) *lp.ph[0].status = 3;
     }
-    ok = __syncthreads_and(ok);
-    if (!ok) {
-      if (threadIdx.x == 0) *lp.ph[0].status = 3;
-      return;  // nothing of this CTA is in flight: the sweep above drained its ring
-    }
+    ok = __syncthreads_and(ok == 1);
+    if (!ok) return;  // nothing of this CTA is in flight: the sweep above drained its ring
   }
 }
 
@@ -344,7 +424,8 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
 
 // `total` sweeps cycling through the given stencil steps (already bound to their buffers) in one cooperative
 // launch.  Declines (handled = false) unless every step is the 5-point fast chain on the same tile geometry.
-cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps, const std::vector<VmProgram>& bound, int64_t total, bool* handled) {
+cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps, const std::vector<VmProgram>& bound, int64_t total, bool* handled,
+                             const StencilLoopHalo* halo, bool dry_run) {
   *handled = false;
   const int n = (int)steps.size();
   if (n < 1 || n > kMaxPhases || total < 2 || total > INT32_MAX) return cudaSuccess;
@@ -363,7 +444,17 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
   lp.n_phases = n;
   lp.total = (int)total;
   lp.alternate = getenv("RX_STENCIL_ONE_WAY") ? 0 : 1;
-  lp.counter = (unsigned*)(d->scratch + d->scratch_words - 2);  // the word before the reductions' ticket
+  lp.edge = (unsigned*)(d->scratch + d->scratch_words - 4);  // the three words before the reductions' ticket
+  lp.release = lp.edge + 1;
+  lp.counter = lp.edge + 2;
+  if (halo) {
+    if ((int)halo->block.size() != n) return cudaSuccess;
+    lp.halo = 1;
+    lp.peer_status = lp.ph[0].status - 1;  // word 0 of the device's status block; the stencil's own is word 1
+    lp.hx = halo->args;
+    for (int i = 0; i < n; ++i) lp.halo_block[i] = halo->block[i];
+    lp.halo_epoch0 = halo->epoch0;
+  }
   auto kern = k_stencil_loop<32>;
   static size_t attr_set[64] = {};
   static int resident[64] = {};
@@ -385,7 +476,18 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
   int ntiles = 0;
   for (int i = 0; i < n; ++i) ntiles = std::max(ntiles, lp.ph[i].tiles_x * lp.ph[i].tiles_y);
   int grid = std::min(ntiles, d->sm_count * std::min(occ, 2));
-  cudaError_t e = cudaMemsetAsync(lp.counter, 0, sizeof(unsigned), d->stream);
+  if (halo) {
+    // one more CTA, which only exchanges; every sweep must count the same number of edge tiles
+    for (int i = 1; i < n; ++i)
+      if (lp.ph[i].tiles_x != lp.ph[0].tiles_x || lp.ph[i].tiles_y != lp.ph[0].tiles_y) return cudaSuccess;
+    grid = std::min(ntiles, d->sm_count * std::min(occ, 2) - 1) + 1;
+    if (grid < 2) return cudaSuccess;
+  }
+  if (dry_run) {
+    *handled = true;
+    return cudaSuccess;
+  }
+  cudaError_t e = cudaMemsetAsync(lp.edge, 0, 3 * sizeof(unsigned), d->stream);
   if (e != cudaSuccess) return e;
   void* args[] = {(void*)&maps, (void*)&lp};
   e = cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(256), args, smem, d->stream);

@@ -174,15 +174,22 @@ def test_one_process_per_gpu_mesh_matches_the_float64_sum():
     assert line["parity"]["ok"] and line["parity"]["same_bits_on_every_rank"], line["parity"]
 
 
+@pytest.mark.parametrize("whole_loop", [True, False])
 @pytest.mark.parametrize("ndev", [2, 4])
 @pytest.mark.parametrize("n,steps,form", [(64, 3, "dus"), (516, 5, "dus"), (1028, 4, "halfsteps"), (260, 7, "halfsteps")])
-def test_row_sharded_jacobi_with_halo_exchange_is_bit_exact(rx, ref, ndev, n, steps, form):
+def test_row_sharded_jacobi_with_halo_exchange_is_bit_exact(rx, ref, ndev, n, steps, form, whole_loop, monkeypatch):
     """Both arrays split into row blocks over the mesh (Julia's second dimension); every sweep each device updates the
-    rows it owns and sends its boundary rows to its neighbours' halos.  Same bits as the unsharded program."""
+    rows it owns and sends its boundary rows to its neighbours' halos.  Same bits as the unsharded program, whether
+    the loop runs as one cooperative launch per device with the exchange between the sweeps inside the kernel, or
+    (RX_STENCIL_LOOP=0) as one stencil launch and one exchange launch per sweep."""
     if _ngpu() < ndev:
         pytest.skip(f"needs {ndev} GPUs")
     if n % ndev:
         pytest.skip("rows do not divide")
+    if whole_loop:
+        monkeypatch.delenv("RX_STENCIL_LOOP", raising=False)
+    else:
+        monkeypatch.setenv("RX_STENCIL_LOOP", "0")
     client = rx.Client(allowed_devices=list(range(ndev)))
     try:
         rng = np.random.default_rng(n + steps)
@@ -194,7 +201,12 @@ def test_row_sharded_jacobi_with_halo_exchange_is_bit_exact(rx, ref, ndev, n, st
         f = rx.compile(rx.programs.jacobi2d(n, steps, form=form, num_partitions=ndev), client)
         kinds = [s["kind"] for s in f.describe()["steps"]]
         assert kinds == ["rows_in", "rows_in", "loop", "rows_out", "rows_out"], kinds
+        before = [d.kernel_launches() for d in client.addressable_devices]
         ra, rb = f(A, B)
+        launched = [d.kernel_launches() - b0 for d, b0 in zip(client.addressable_devices, before)]
+        sweeps = steps * (2 if form == "halfsteps" else 1)
+        # two exchange launches for the arrays' first halos, then one launch for the whole loop or two per sweep
+        assert all(l == (3 if whole_loop else 2 + 2 * sweeps) for l in launched), launched
         wa, wb = ref.run_module(rx.programs.jacobi2d(n, steps, form=form), [a, b])
         assert np.array_equal(np.asarray(ra).T, wa) and np.array_equal(np.asarray(rb).T, wb)
         # a second execution (later sequence numbers of the exchange) continues from the results
