@@ -1858,18 +1858,107 @@ struct Planner {
     env[v] = leaf(dst, t);
   }
 
+  // ---- concatenate --------------------------------------------------------------------------------------------
+  // Reactant's pad / communication patterns may rewrite a dynamic_update_slice into concatenates of the untouched
+  // borders of the target around the update (src/CompileOptions.jl:22-41, OptimizationPasses.jl:356-372), usually
+  // nested: columns first, then rows.  A concatenate whose only user is another concatenate is not materialised;
+  // the outer one places all pieces at their N-d offsets.  Pieces that are the target's own contents at the position
+  // they already occupy are not copied: when every such piece comes from one writable array that nothing reads
+  // later, the rest is written into that array in place -- the same plan the dynamic_update_slice form gets.
+  struct ConcatPiece { ExprP e; std::vector<int64_t> at; };
+  std::map<int, const Op*> deferred_concat;
+  const Region* cur_region = nullptr;
+
+  const Op* sole_user_if_concat(int v) const {
+    if (uses[v] != 1 || !cur_region) return nullptr;
+    for (auto& op : cur_region->ops)
+      for (int x : op.in)
+        if (x == v) return op.kind == OpK::Concatenate ? &op : nullptr;
+    return nullptr;  // a result of the region, or used inside a nested one
+  }
+  void concat_pieces(const Op& op, const std::vector<int64_t>& base, std::vector<ConcatPiece>& out, std::vector<const Op*>& inner) {
+    const int d = (int)op.dims[0];
+    int64_t pos = 0;
+    for (int x : op.in) {
+      std::vector<int64_t> at = base;
+      at[d] += pos;
+      auto it = deferred_concat.find(x);
+      if (it != deferred_concat.end()) {
+        inner.push_back(it->second);
+        concat_pieces(*it->second, at, out, inner);
+      } else {
+        out.push_back({env[x], at});
+      }
+      pos += m.values[x].type.shape[d];
+    }
+  }
+
   void plan_concat(const Op& op) {
     int v = op.out[0];
     Type t = m.values[v].type;
     check_dt(op, t.dt);
-    int dst = new_slot(t);
-    std::vector<int64_t> cs = canon_strides(t.shape);
-    int64_t pos = 0;
-    int d = (int)op.dims[0];
-    for (int x : op.in) {
+    for (int x : op.in)
       if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.concatenate of a sharded tensor");
-      emit_map(env[x], dst, pos * cs[d], cs, "concatenate piece");
-      pos += env[x]->shape[d];
+    if (sole_user_if_concat(v)) {
+      deferred_concat[v] = &op;
+      for (int x : op.in) ++remaining[x];  // still needed: consumed when the outer concatenate is planned
+      return;
+    }
+    std::vector<ConcatPiece> pieces;
+    std::vector<const Op*> inner;
+    concat_pieces(op, std::vector<int64_t>(t.shape.size(), 0), pieces, inner);
+    const std::vector<int64_t> cs = canon_strides(t.shape);
+    auto offset_of = [&](const ConcatPiece& p) {
+      int64_t off = 0;
+      for (size_t d = 0; d < cs.size(); ++d) off += p.at[d] * cs[d];
+      return off;
+    };
+    // which pieces already sit where they belong, and in which array
+    int target = -1;
+    std::vector<bool> in_place_piece(pieces.size(), false);
+    for (size_t k = 0; k < pieces.size(); ++k) {
+      MatView mv;
+      if (!as_strided_leaf(pieces[k].e, &mv)) continue;
+      if (target >= 0 && mv.slot != target) continue;
+      const Slot& sl = plan.slots[mv.slot];
+      if (sl.type.dt != t.dt || sl.type.shape != t.shape || mv.off != offset_of(pieces[k])) continue;
+      bool same_layout = true;
+      for (size_t d = 0; d < cs.size(); ++d)
+        if (pieces[k].e->shape[d] != 1 && mv.stride[d] != cs[d]) same_layout = false;
+      if (!same_layout) continue;
+      target = mv.slot;
+      in_place_piece[k] = true;
+    }
+    bool in_place = target >= 0 && slot_writable(target);
+    if (in_place) {
+      // nothing still to be evaluated may read the target, apart from the operands consumed here
+      std::vector<int> consumed(op.in.begin(), op.in.end());
+      for (const Op* q : inner) consumed.insert(consumed.end(), q->in.begin(), q->in.end());
+      for (size_t w = 0; w < env.size() && in_place; ++w) {
+        if (!env[w]) continue;
+        int left = remaining[w] - (int)std::count(consumed.begin(), consumed.end(), (int)w);
+        if (left <= 0) continue;
+        std::set<const Expr*> seen;
+        if (reads_slot(env[w], target, seen)) in_place = false;
+      }
+      // and the pieces that are written may not read it at all (they would see rows already replaced)
+      for (size_t k = 0; k < pieces.size() && in_place; ++k) {
+        if (in_place_piece[k]) continue;
+        std::vector<const Expr*> lv;
+        std::set<const Expr*> seen;
+        collect_leaves(pieces[k].e, lv, seen);
+        for (auto* l : lv)
+          if (l->slot == target) in_place = false;
+      }
+    }
+    int dst = in_place ? target : new_slot(t);
+    for (size_t k = 0; k < pieces.size(); ++k) {
+      if (in_place && in_place_piece[k]) continue;
+      emit_map(pieces[k].e, dst, offset_of(pieces[k]), cs, in_place ? "concatenate piece, written in place" : "concatenate piece");
+    }
+    for (const Op* q : inner) {
+      for (int x : q->in) --remaining[x];
+      deferred_concat.erase(q->out[0]);
     }
     env[v] = leaf(dst, t);
   }
@@ -2196,6 +2285,8 @@ struct Planner {
   }
 
   void plan_region(const Region& r) {
+    const Region* outer_region = cur_region;
+    cur_region = &r;
     for (auto& op : r.ops) {
       switch (op.kind) {
         case OpK::Constant: plan_constant(op); break;
@@ -2216,6 +2307,7 @@ struct Planner {
       if (op.kind != OpK::While)
         for (int v : op.in) --remaining[v];
     }
+    cur_region = outer_region;
   }
 
   void run() {

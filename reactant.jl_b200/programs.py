@@ -91,6 +91,9 @@ def jacobi2d(n: int, steps: int, form: str = "dus", num_partitions: int = 1) -> 
         B[2:end-1,2:end-1] = 0.2f0 .* (A[c] .+ A[i-1] .+ A[i+1] .+ A[j-1] .+ A[j+1]); A, B = B, A
     with the interior written by dynamic_update_slice ("dus") or by the pad + select rewrite that Enzyme-JAX's
     communication patterns can produce ("pad", src/compiler/OptimizationPasses.jl:356-372).
+    form="concat": the same update with the interior placed by two nested concatenates -- the borders of B's rows
+    around the new interior, then B's first and last row around that -- which is what the rewrite of a
+    dynamic_update_slice into concatenates leaves (src/CompileOptions.jl:22-41).
     form="halfsteps": the spelling of benchmark/polybench/stencil.jl:263-289 -- every one of the `steps`
     iterations updates B from A and then A from B (two sweeps, no swap), the five terms added in that file's
     order: centre, j-1, j+1, i+1, i-1.
@@ -124,6 +127,16 @@ def jacobi2d(n: int, steps: int, form: str = "dus", num_partitions: int = 1) -> 
         lines = sweep("%iterArg_0", "", [centre, i_lo, i_hi, j_lo, j_hi])
         if form == "dus":
             lines.append(dus("%iterArg_1", "%u", "%nb"))
+        elif form == "concat":
+            tc, tr, tm = _t([n - 2, 1]), _t([1, n]), _t([n - 2, n])
+            lines += [
+                f"      %left = stablehlo.slice %iterArg_1 [1:{m}, 0:1] : ({t}) -> {tc}",
+                f"      %right = stablehlo.slice %iterArg_1 [1:{m}, {m}:{n}] : ({t}) -> {tc}",
+                f"      %mid = stablehlo.concatenate %left, %u, %right, dim = 1 : ({tc}, {ti}, {tc}) -> {tm}",
+                f"      %top = stablehlo.slice %iterArg_1 [0:1, 0:{n}] : ({t}) -> {tr}",
+                f"      %bot = stablehlo.slice %iterArg_1 [{m}:{n}, 0:{n}] : ({t}) -> {tr}",
+                f"      %nb = stablehlo.concatenate %top, %mid, %bot, dim = 0 : ({tr}, {tm}, {tr}) -> {t}",
+            ]
         else:
             lines += [
                 f"      %pu = stablehlo.pad %u, %cst_z, low = [1, 1], high = [1, 1], interior = [0, 0] : ({ti}, tensor<f32>) -> {t}",

@@ -169,7 +169,7 @@ def test_logsumexp_full_size_against_c_oracle(rx, ref, cpu, client):
 
 # ---------------------------------------------------------------- Jacobi-2D (C3)
 @pytest.mark.parametrize("n,steps", [(3, 1), (4, 3), (8, 2), (33, 5), (130, 4), (515, 3), (1030, 2)])
-@pytest.mark.parametrize("form", ["dus", "pad"])
+@pytest.mark.parametrize("form", ["dus", "pad", "concat"])
 def test_jacobi2d_bit_exact(rx, ref, client, n, steps, form):
     rng = np.random.default_rng(n)
     a = rng.random((n, n), dtype=np.float32)

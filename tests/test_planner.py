@@ -229,6 +229,34 @@ def test_jacobi_two_half_steps_plan_in_place_without_a_copy(rx):
     assert [s["kind"] for s in body] == ["stencil", "stencil"] and all(s["chain"] == "stencil5_mul" for s in body)
 
 
+def test_nested_concatenates_around_an_update_plan_as_the_update_in_place(rx):
+    """The concatenate spelling of a window update (borders of B's rows around the new interior, then B's first and
+    last row around that) plans exactly like the dynamic_update_slice it was rewritten from: the inner concatenate is
+    not materialised, the border pieces already sit where they belong, and the interior is written into B."""
+    p = rx.plan_describe(rx.programs.jacobi2d(8192, 100, form="concat"))
+    q = rx.plan_describe(rx.programs.jacobi2d(8192, 100, form="dus"))
+    assert kinds(p) == ["loop"] and p["slots"] == q["slots"] == 2
+    body = p["steps"][0]["body"]
+    assert [s["kind"] for s in body] == ["stencil"] and body[0]["chain"] == "stencil5_mul", body
+    # when the old array is still read afterwards the pieces are written into a fresh array instead
+    t = "tensor<8x8xf32>"
+    text = f"""module {{
+  func.func @main(%arg0: {t} {{tf.aliasing_output = 0 : i32}}, %arg1: tensor<6x8xf32>) -> ({t}, {t}) {{
+    %top = stablehlo.slice %arg0 [0:1, 0:8] : ({t}) -> tensor<1x8xf32>
+    %bot = stablehlo.slice %arg0 [7:8, 0:8] : ({t}) -> tensor<1x8xf32>
+    %0 = stablehlo.concatenate %top, %arg1, %bot, dim = 0 : (tensor<1x8xf32>, tensor<6x8xf32>, tensor<1x8xf32>) -> {t}
+    %1 = stablehlo.sine %arg0 : {t}
+    return %0, %1 : {t}, {t}
+  }}
+}}
+"""
+    k = kinds(rx.plan_describe(text))
+    assert k.count("map") == 4, k   # three pieces into a new array + the sine
+    # a piece taken from somewhere else in the target is not "in place"
+    text2 = text.replace("[7:8, 0:8]", "[6:7, 0:8]").replace("    %1 = stablehlo.sine %arg0 : " + t + "\n", "").replace("return %0, %1 : " + t + ", " + t, "return %0 : " + t).replace(f"-> ({t}, {t})", f"-> {t}")
+    assert kinds(rx.plan_describe(text2)).count("map") == 3
+
+
 def test_update_target_that_is_still_read_later_is_copied(rx):
     """In place only when nothing still to be evaluated reads the target: here the old array is returned too."""
     t, ti = "tensor<8x8xf32>", "tensor<6x6xf32>"
