@@ -550,35 +550,45 @@ class Interpreter:
         return make(np.asarray(r).reshape(shape), et)
 
     def _reduce_window(self, op, env):
-        """Cumulative form only (Reactant's scan_impl!, src/TracedRArray.jl:1049-1107): the window spans one whole
-        dimension, padded low by its extent minus one, unit strides and dilations -- an inclusive scan."""
+        """stablehlo.reduce_window with a single-op combiner, base dilations of 1.  The cumulative form (Reactant's
+        scan_impl!, src/TracedRArray.jl:1049-1107: the window spans one whole dimension, padded low by its extent minus
+        one) is an inclusive scan; anything else (pooling windows) is evaluated position by position over the operand
+        padded with the init value, in the wide type."""
         text = op.text
         names = re.findall(r"%[\w#.$-]+", text[text.index("("):text.index(")")])
         x, init = env[names[0]], env[names[1]]
         win = [int(v) for v in re.search(r"window_dimensions\s*=\s*array<i64:\s*([^>]*)>", text).group(1).split(",")]
-        pm = re.search(r"padding\s*=\s*dense<(.*?)>\s*:\s*tensor<(\d+)x2xi64>", text)
-        nums = [int(v) for v in re.findall(r"-?\d+", pm.group(1))]
         rank = len(win)
+        pm = re.search(r"padding\s*=\s*dense<(.*?)>\s*:\s*tensor<(\d+)x2xi64>", text)
+        nums = [int(v) for v in re.findall(r"-?\d+", pm.group(1))] if pm else [0]
         pad = [(nums[2 * d], nums[2 * d + 1]) for d in range(rank)] if len(nums) == 2 * rank else [(nums[0], nums[0])] * rank
-        for attr in ("window_strides", "base_dilations", "window_dilations"):
+
+        def ints(attr):
             m = re.search(attr + r"\s*=\s*array<i64:\s*([^>]*)>", text)
-            assert m is None or all(int(v) == 1 for v in m.group(1).split(",")), f"oracle: {attr} other than 1"
+            return [int(v) for v in m.group(1).split(",")] if m else [1] * rank
+
+        strides, wdil = ints("window_strides"), ints("window_dilations")
+        assert all(v == 1 for v in ints("base_dilations")), "oracle: base_dilations other than 1"
         shape = list(x.a.shape)
-        axes = [d for d in range(rank) if win[d] != 1 or pad[d] != (0, 0)]
-        assert len(axes) <= 1, "oracle: only cumulative windows along one dimension"
         kinds = [o.name.split(".", 1)[1] for o in op.regions[0] if o.name != "stablehlo.return"]
         assert len(kinds) == 1, "only single-op reducers are on the path"
         kind = kinds[0]
         X, i0 = _wide(x), _wide(init)
         ufunc = {"add": np.add, "maximum": np.maximum, "minimum": np.minimum, "multiply": np.multiply}[kind]
-        if axes:
-            d = axes[0]
-            assert win[d] == shape[d] and pad[d] == (shape[d] - 1, 0), "oracle: only cumulative windows"
-            r = ufunc.accumulate(X, axis=d)
-        else:
-            r = X
-        r = ufunc(r, i0)
         (oshape, et), = _types_after_colon(text)[-1:]
+        axes = [d for d in range(rank) if win[d] != 1 or pad[d] != (0, 0) or strides[d] != 1]
+        if not axes:
+            return make(np.asarray(ufunc(X, i0)).reshape(oshape), et)
+        if len(axes) == 1 and win[axes[0]] == shape[axes[0]] and pad[axes[0]] == (shape[axes[0]] - 1, 0) and strides[axes[0]] == 1 and wdil[axes[0]] == 1:
+            r = ufunc(ufunc.accumulate(X, axis=axes[0]), i0)
+            return make(np.asarray(r).reshape(oshape), et)
+        P = np.pad(X, pad, mode="constant", constant_values=i0.item())
+        r = None
+        for k in np.ndindex(*win):
+            sl = tuple(slice(k[d] * wdil[d], k[d] * wdil[d] + (oshape[d] - 1) * strides[d] + 1, strides[d]) for d in range(rank))
+            piece = P[sl]
+            assert list(piece.shape) == list(oshape), (piece.shape, oshape)
+            r = piece if r is None else ufunc(r, piece)
         return make(np.asarray(r).reshape(oshape), et)
 
     def _while(self, op, env):

@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "librx_b200.so")
+# RX_B200_LIB selects another build of the library (the bounds-checked one, say); the default is the in-tree build
+LIB_PATH = os.environ.get("RX_B200_LIB") or os.path.join(HERE, "librx_b200.so")
 
 
 class ReactantError(RuntimeError):

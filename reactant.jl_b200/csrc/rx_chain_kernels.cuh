@@ -78,7 +78,7 @@ __device__ __forceinline__ void finish_in_last_block(uint32_t mine, uint32_t* pa
       x = f2u(total);
     }
     if (lane == 0) {
-      store_elem(out.ptr, out.offset, out.elem, x);
+      out_store(out, out.offset, x);
       *ticket = 0;
     }
   }
@@ -87,8 +87,12 @@ __device__ __forceinline__ void finish_in_last_block(uint32_t mine, uint32_t* pa
 // ---- vector leaf access (4 consecutive elements, 4-element aligned) ----------
 __device__ __forceinline__ void load4(const VmLeaf& l, int64_t i, uint32_t* d) {
   if (l.linear == 2) {
-    uint32_t u = load_elem(l.ptr, l.offset, l.elem);
+    uint32_t u = leaf_load(l, l.offset);
     put4(d, u, u, u, u);
+    return;
+  }
+  if (!RX_LEAF_OK(l, l.offset + i, 4)) {
+    put4(d, 0u, 0u, 0u, 0u);
     return;
   }
   switch (l.elem) {
@@ -112,6 +116,7 @@ __device__ __forceinline__ void load4(const VmLeaf& l, int64_t i, uint32_t* d) {
 }
 
 __device__ __forceinline__ void store4(const VmOut& o, int64_t i, const uint32_t* s) {
+  if (!RX_OUT_OK(o, o.offset + i, 4)) return;
   switch (o.elem) {
     case EL_F32:
     case EL_I32:
@@ -136,7 +141,7 @@ __device__ __forceinline__ uint32_t vm_eval_at(const VmProgram& P, const int64_t
   __align__(16) uint32_t R[C::kRegs][1];
   RX_CHAIN_UNROLL for (int k = 0; k < C::n_leaves(P); ++k) {
     const auto& l = C::leaf(P, k);
-    R[C::leaf_reg(P, k)][0] = load_elem(l.ptr, leaf_offset(l, idx, P.rank), l.elem);
+    R[C::leaf_reg(P, k)][0] = leaf_load(l, leaf_offset(l, idx, P.rank));
   }
   C::template exec<1>(P, R, idx);
   return R[C::result_reg(P)][0];
@@ -159,9 +164,9 @@ __global__ void __launch_bounds__(kThreads) k_map_linear(const __grid_constant__
     int64_t i = n4 * 4 + threadIdx.x;
     __align__(16) uint32_t R[C::kRegs][1];
     RX_CHAIN_UNROLL for (int k = 0; k < C::n_leaves(P); ++k)
-      R[C::leaf_reg(P, k)][0] = load_elem(C::leaf(P, k).ptr, C::leaf(P, k).offset + (C::leaf(P, k).linear == 2 ? 0 : i), C::leaf(P, k).elem);
+      R[C::leaf_reg(P, k)][0] = leaf_load(C::leaf(P, k), C::leaf(P, k).offset + (C::leaf(P, k).linear == 2 ? 0 : i));
     C::template exec<1>(P, R, idx0);
-    RX_CHAIN_UNROLL for (int k = 0; k < C::n_outs(P); ++k) store_elem(C::out(P, k).ptr, C::out(P, k).offset + i, C::out(P, k).elem, R[C::out_reg(P, k)][0]);
+    RX_CHAIN_UNROLL for (int k = 0; k < C::n_outs(P); ++k) out_store(C::out(P, k), C::out(P, k).offset + i, R[C::out_reg(P, k)][0]);
   }
 }
 
@@ -173,9 +178,9 @@ __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant_
     if (SMALL) unravel32(P, (uint32_t)i, idx);
     else unravel(P, i, idx);
     __align__(16) uint32_t R[C::kRegs][1];
-    RX_CHAIN_UNROLL for (int k = 0; k < C::n_leaves(P); ++k) R[C::leaf_reg(P, k)][0] = load_elem(C::leaf(P, k).ptr, leaf_offset(C::leaf(P, k), idx, P.rank), C::leaf(P, k).elem);
+    RX_CHAIN_UNROLL for (int k = 0; k < C::n_leaves(P); ++k) R[C::leaf_reg(P, k)][0] = leaf_load(C::leaf(P, k), leaf_offset(C::leaf(P, k), idx, P.rank));
     C::template exec<1>(P, R, idx);
-    RX_CHAIN_UNROLL for (int k = 0; k < C::n_outs(P); ++k) store_elem(C::out(P, k).ptr, out_offset(C::out(P, k), idx, P.rank), C::out(P, k).elem, R[C::out_reg(P, k)][0]);
+    RX_CHAIN_UNROLL for (int k = 0; k < C::n_outs(P); ++k) out_store(C::out(P, k), out_offset(C::out(P, k), idx, P.rank), R[C::out_reg(P, k)][0]);
   }
 }
 
@@ -185,11 +190,15 @@ __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant_
 __device__ __forceinline__ void load4_rowvec(const VmLeaf& l, int64_t row, int64_t col, int drow, int dcol, uint32_t* d) {
   int64_t off = l.offset + row * l.stride[drow];
   if (l.stride[dcol] == 0) {
-    uint32_t u = load_elem(l.ptr, off, l.elem);
+    uint32_t u = leaf_load(l, off);
     put4(d, u, u, u, u);
     return;
   }
   off += col;
+  if (!RX_LEAF_OK(l, off, 4)) {
+    put4(d, 0u, 0u, 0u, 0u);
+    return;
+  }
   switch (l.elem) {
     case EL_F32:
     case EL_I32: {
@@ -321,7 +330,7 @@ __global__ void __launch_bounds__(kThreads) k_reduce_full_linear(const __grid_co
     int64_t i = n4 * 4 + threadIdx.x;
     __align__(16) uint32_t R[C::kRegs][1];
     RX_CHAIN_UNROLL for (int k = 0; k < C::n_leaves(P); ++k)
-      R[C::leaf_reg(P, k)][0] = load_elem(C::leaf(P, k).ptr, C::leaf(P, k).offset + (C::leaf(P, k).linear == 2 ? 0 : i), C::leaf(P, k).elem);
+      R[C::leaf_reg(P, k)][0] = leaf_load(C::leaf(P, k), C::leaf(P, k).offset + (C::leaf(P, k).linear == 2 ? 0 : i));
     C::template exec<1>(P, R, idx0);
     acc[0] = red_combine(code, acc[0], R[C::result_reg(P)][0]);
   }
@@ -379,7 +388,7 @@ __global__ void __launch_bounds__(kThreads) k_reduce_row(const __grid_constant__
   }
   if (TPR == kThreads) acc = block_red<kThreads>(code, acc, sm);
   else if (TPR == 32) acc = warp_red(code, acc);
-  if (lane == 0 && row < outer) store_elem(C::out(P, 0).ptr, C::out(P, 0).offset + row * C::out(P, 0).stride[0], C::out(P, 0).elem, red_combine(code, init_bits, acc));
+  if (lane == 0 && row < outer) out_store(C::out(P, 0), C::out(P, 0).offset + row * C::out(P, 0).stride[0], red_combine(code, init_bits, acc));
 }
 
 // ---- reduce along a strided axis: [outer][red][inner], threads along inner -----------

@@ -140,6 +140,42 @@ __device__ __forceinline__ void store_elem(void* p, int64_t i, int elem, uint32_
   }
 }
 
+// ---- bounds-checked build ---------------------------------------------------------------------------------
+// With -DRX_BOUNDS=1 (build.py --bounds; the run-time compiler is given the same definition) every element access a
+// chain kernel makes through an operand or result descriptor is checked against the extent of the buffer behind it.
+// A miss is recorded once per execution in the device's status block -- {what, index low / high word, extent} -- and
+// the access is skipped (loads give 0): nothing traps, the host reports the record at its next synchronising call.
+// It stands in for compute-sanitizer's memcheck, which is not available where this engine is developed: an access
+// that strays inside mapped memory changes no test result but does show up here.
+#ifndef RX_BOUNDS
+#define RX_BOUNDS 0
+#endif
+#if RX_BOUNDS
+static __device__ __noinline__ void rx_bounds_miss(int* rec, int64_t extent, int64_t first, int what) {
+  if (rec && atomicCAS(rec, 0, what) == 0) {
+    rec[1] = (int)(first & 0xFFFFFFFFll);
+    rec[2] = (int)(first >> 32);
+    rec[3] = (int)(extent > 0x7FFFFFFF ? 0x7FFFFFFF : extent);
+    __threadfence_system();
+  }
+}
+__device__ __forceinline__ bool rx_in_bounds(int* rec, int64_t extent, int64_t first, int count, int what) {
+  if (first >= 0 && first + count <= extent) return true;
+  rx_bounds_miss(rec, extent, first, what);
+  return false;
+}
+#define RX_LEAF_OK(l, first, count) rx_in_bounds((l).bounds, (l).extent, (first), (count), 100 + (l).reg)
+#define RX_OUT_OK(o, first, count) rx_in_bounds((o).bounds, (o).extent, (first), (count), 200 + (o).reg)
+#else
+#define RX_LEAF_OK(l, first, count) true
+#define RX_OUT_OK(o, first, count) true
+#endif
+// one element of an operand / result at element index i of its buffer
+__device__ __forceinline__ uint32_t leaf_load(const VmLeaf& l, int64_t i) { return RX_LEAF_OK(l, i, 1) ? load_elem(l.ptr, i, l.elem) : 0u; }
+__device__ __forceinline__ void out_store(const VmOut& o, int64_t i, uint32_t v) {
+  if (RX_OUT_OK(o, i, 1)) store_elem(o.ptr, i, o.elem, v);
+}
+
 
 __device__ __forceinline__ uint32_t vm_cmp_f(int dir, float a, float b) {
   switch (dir) {

@@ -179,9 +179,14 @@ struct EpiChain {
   static __device__ __forceinline__ void load_v(const VmLeaf& l, long long m, long long n, bool vec, uint32_t* d) {
     const long long base = l.offset + m * l.stride[0];
     if (l.stride[1] == 0) {
-      const uint32_t u = load_elem(l.ptr, base, l.elem);
+      const uint32_t u = leaf_load(l, base);
 #pragma unroll
       for (int j = 0; j < V; ++j) d[j] = u;
+      return;
+    }
+    if (!RX_LEAF_OK(l, base + n, V)) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) d[j] = 0u;
       return;
     }
     if (vec && l.elem == EL_F32) {
@@ -207,6 +212,7 @@ struct EpiChain {
   }
   static __device__ __forceinline__ void store_v(const VmOut& o, long long m, long long n, bool vec, const uint32_t* s) {
     const long long at = o.offset + m * o.stride[0] + n;
+    if (!RX_OUT_OK(o, at, V)) return;
     if (vec && o.elem == EL_F32) {
       uint4* q = (uint4*)((uint32_t*)o.ptr + at);
 #pragma unroll

@@ -64,7 +64,8 @@ struct Op {
   int ew = 0;                 // VmOp for Unary/Binary; VmCmp for Compare
   std::vector<int> in, out;   // value ids
   std::vector<int64_t> dims;  // broadcast dims / permutation / reduce dims / concat dim / iota dim
-  std::vector<int64_t> start, limit, stride;  // slice; pad: low/high/interior; reduce_window: padding low/high (dims = window)
+  std::vector<int64_t> start, limit, stride;  // slice; pad: low/high/interior; reduce_window: padding low/high, window strides (dims = window)
+  std::vector<int64_t> dilation;              // reduce_window: window dilations
   // constant payload
   bool splat = true;
   double fval = 0;            // splat value as double (floats)

@@ -150,6 +150,9 @@ bool compile(const std::string& src, const std::string& name_expr, std::vector<c
     }
   }
   std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "-std=c++17"};
+#if defined(RX_BOUNDS) && RX_BOUNDS
+  opts.push_back("-DRX_BOUNDS=1");  // the bounds-checked library compiles bounds-checked chains
+#endif
   for (auto& e : extra) opts.push_back(e.c_str());
   if (verbose) opts.push_back("--ptxas-options=-v");
   if (verbose) fprintf(stderr, "---- %s\n%s\n", name_expr.c_str(), src.c_str());
@@ -247,6 +250,12 @@ std::string jit_chain_source(const VmProgram& P, int red_code, const char* famil
   std::string s;
   s.reserve(4096);
   s += "// headers: " + headers_fingerprint() + "\n";
+  // what the compiler is told besides the source is part of the text too, so that the caches never hand a kernel
+  // built one way to a library that asks for the other
+#if defined(RX_BOUNDS) && RX_BOUNDS
+  s += "// options: -DRX_BOUNDS=1\n";
+#endif
+  if (const char* defs = getenv("RX_JIT_DEFINES")) s += std::string("// options: ") + defs + "\n";
   s += "// family: ";
   s += family;
   s += "\n#define RX_CHAIN_SPECIALISED 1\n#include \"rx_chain_kernels.cuh\"\n";

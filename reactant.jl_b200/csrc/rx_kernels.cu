@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(kThreads) k_reduce_col_finish(const uint32_t* 
     uint32_t t = sm[0][lane];
 #pragma unroll
     for (int q = 1; q < kThreads / 32; ++q) t = red_combine(code, t, sm[q][lane]);
-    store_elem(out.ptr, out.offset + o * out.stride[0] + b * out.stride[2], out.elem, red_combine(code, init_bits, t));
+    out_store(out, out.offset + o * out.stride[0] + b * out.stride[2], red_combine(code, init_bits, t));
   }
 }
 

@@ -481,9 +481,15 @@ struct Parser {
       op.start.push_back(pad[2 * d]);
       op.limit.push_back(pad[2 * d + 1]);
     }
-    for (const char* key : {"window_strides", "base_dilations", "window_dilations"})
-      for (int64_t v : ints_after(key, false))
-        if (v != 1) fail(RX_ERR_UNSUPPORTED_OP, std::string("unsupported op stablehlo.reduce_window with ") + key + " other than 1");
+    op.stride = ints_after("window_strides", false);
+    op.dilation = ints_after("window_dilations", false);
+    if (op.stride.empty()) op.stride.assign(rank, 1);
+    if (op.dilation.empty()) op.dilation.assign(rank, 1);
+    if (op.stride.size() != rank || op.dilation.size() != rank) fail(RX_ERR_PARSE, "stablehlo.reduce_window: strides or dilations do not match the window rank");
+    for (size_t d = 0; d < rank; ++d)
+      if (op.stride[d] < 1 || op.dilation[d] < 1 || op.dims[d] < 1) fail(RX_ERR_PARSE, "stablehlo.reduce_window: non-positive window size, stride or dilation");
+    for (int64_t v : ints_after("base_dilations", false))
+      if (v != 1) fail(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window with base_dilations other than 1");
     expect("(");
     expect("{");
     scopes.emplace_back();

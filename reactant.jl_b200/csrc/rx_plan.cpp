@@ -1530,6 +1530,68 @@ struct Planner {
   // stablehlo.reduce_window in the cumulative form Reactant's accumulate / cumsum / cumprod emit
   // (src/TracedRArray.jl:1049-1107): the window covers one whole dimension, padded low by its extent minus one,
   // unit strides and dilations -- an inclusive scan along that dimension, combined with the init value.
+  // Windows that are not scans (pooling: ext/ReactantNNlibExt/Implementations.jl, src/TracedRArray.jl:981-1047): the
+  // result is the combiner applied to one strided view of the (padded) operand per window position,
+  //   out[i] = x'[i * stride + k * dilation]  combined over k,
+  // so it needs no kernel of its own: the views are leaves of an ordinary fused chain (the strided map kernels read
+  // them in place), materialised every few positions to stay inside a chain's operand budget.  Padding is written
+  // once, with the combiner's identity.  Positions are combined in row-major window order.
+  void plan_general_window(const Op& op) {
+    int v = op.out[0], x = op.in[0];
+    ExprP X = env[x], init = env[op.in[1]];
+    if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window over a sharded tensor (other than a scan along an unsharded dimension)");
+    const int rank = (int)X->shape.size();
+    const Type t = m.values[v].type;
+    const bool flt = X->dt == DT::F32;
+    int64_t volume = 1;
+    bool padded = false;
+    std::vector<int64_t> pshape = X->shape;
+    for (int d = 0; d < rank; ++d) {
+      volume *= op.dims[d];
+      if (op.start[d] < 0 || op.limit[d] < 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window with negative padding");
+      padded = padded || op.start[d] || op.limit[d];
+      pshape[d] += op.start[d] + op.limit[d];
+      // the shape rule of the op, checked because the views below rely on it
+      const int64_t span = (op.dims[d] - 1) * op.dilation[d] + 1;
+      const int64_t expect = pshape[d] < span ? 0 : (pshape[d] - span) / op.stride[d] + 1;
+      if (t.shape[d] != expect) throw Error(RX_ERR_SHAPE, "stablehlo.reduce_window: result extent " + std::to_string(t.shape[d]) + " in dimension " + std::to_string(d) + ", the window gives " + std::to_string(expect));
+    }
+    if (volume > 64) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window with a window of " + std::to_string(volume) + " elements (more than 64) that is not a scan");
+    ExprP base;
+    if (padded) {
+      Type pt{X->dt, pshape};
+      const int dst = new_slot(pt);
+      const std::vector<int64_t> cs = canon_strides(pshape);
+      emit_map(konst(pt, init->f, init->i), dst, 0, cs, "window padding");
+      int64_t off = 0;
+      for (int d = 0; d < rank; ++d) off += op.start[d] * cs[d];
+      emit_map(X, dst, off, cs, "window operand inside its padding");
+      base = leaf(dst, pt);
+    } else {
+      base = materialised(X, "window operand");
+    }
+    const int vop = flt ? (op.red == RedK::Add ? VM_ADD : op.red == RedK::Max ? VM_MAX : op.red == RedK::Min ? VM_MIN : VM_MUL)
+                        : (op.red == RedK::Add ? VM_IADD : op.red == RedK::Max ? VM_IMAX : op.red == RedK::Min ? VM_IMIN : VM_IMUL);
+    ExprP acc;
+    std::vector<int64_t> k(rank, 0);
+    int in_chain = 0;
+    for (int64_t pos = 0; pos < volume; ++pos) {
+      RMap mp(rank);
+      for (int d = 0; d < rank; ++d) mp[d] = {d, op.stride[d], k[d] * op.dilation[d]};
+      ExprP piece = simplify(view(base, t, mp));
+      acc = acc ? mkop(vop, t, {acc, piece}) : piece;
+      if (++in_chain == 6 && pos + 1 < volume) {  // keep every chain within its operand budget
+        acc = materialised(acc, "window partial");
+        in_chain = 1;
+      }
+      for (int d = rank - 1; d >= 0; --d) {
+        if (++k[d] < op.dims[d]) break;
+        k[d] = 0;
+      }
+    }
+    env[v] = acc;
+  }
+
   void plan_reduce_window(const Op& op) {
     int v = op.out[0], x = op.in[0];
     ExprP X = env[x], init = env[op.in[1]];
@@ -1552,14 +1614,18 @@ struct Planner {
     }
     const int rank = (int)X->shape.size();
     int axis = -1;
+    bool cumulative = true;
     for (int d = 0; d < rank; ++d) {
-      const bool trivial = op.dims[d] == 1 && op.start[d] == 0 && op.limit[d] == 0;
+      const bool trivial = op.dims[d] == 1 && op.start[d] == 0 && op.limit[d] == 0 && op.stride[d] == 1;
       if (trivial) continue;
       // the window and padding are written for the global shape
       const int64_t extent = m.values[x].type.shape[d];
-      if (axis >= 0 || op.dims[d] != extent || op.start[d] != extent - 1 || op.limit[d] != 0)
-        throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window: only cumulative windows along one dimension (scans) are supported");
+      if (axis >= 0 || op.dims[d] != extent || op.start[d] != extent - 1 || op.limit[d] != 0 || op.stride[d] != 1 || op.dilation[d] != 1) cumulative = false;
       axis = d;
+    }
+    if (!cumulative) {
+      plan_general_window(op);
+      return;
     }
     if (axis >= 0 && shard[x] == axis) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window scanning along a sharded dimension");
     shard[v] = shard[x];

@@ -221,10 +221,37 @@ void* slot_ptr(DevRun& r, int slot) {
   return r.table[slot]->ptr;
 }
 
+// Elements of the given type in the storage behind a slot (for the bounds-checked build).
+int64_t slot_extent(DevRun& r, int slot, int elem) {
+  const auto& st = r.table[slot];
+  const size_t es = elem == EL_BF16 ? 2 : (elem == EL_F32 || elem == EL_I32) ? 4 : 1;
+  int64_t n = st ? (int64_t)(st->bytes / es) : 0;
+#if RX_BOUNDS
+  // RX_BOUNDS_SELFTEST=1 understates every extent by one element, so that a correct program trips the check on the
+  // last element of a buffer (the access is skipped, nothing is out of bounds): the way the reporting path is tested.
+  static const bool selftest = getenv("RX_BOUNDS_SELFTEST") != nullptr;
+  if (selftest && n > 0) --n;
+#endif
+  return n;
+}
+
 VmProgram bind(const Step& st, DevRun& r) {
   VmProgram P = st.prog;
-  for (int k = 0; k < P.n_leaves; ++k) P.leaf[k].ptr = slot_ptr(r, st.leaf_slot[k]);
-  for (int k = 0; k < P.n_outs; ++k) P.out[k].ptr = slot_ptr(r, st.out_slot[k]);
+  int* rec = nullptr;
+#if RX_BOUNDS
+  cudaHostGetDevicePointer(&rec, r.dev->status, 0);
+  rec += 4;  // words 4..7 of the status block: {what, index low, index high, extent}
+#endif
+  for (int k = 0; k < P.n_leaves; ++k) {
+    P.leaf[k].ptr = slot_ptr(r, st.leaf_slot[k]);
+    P.leaf[k].extent = slot_extent(r, st.leaf_slot[k], P.leaf[k].elem);
+    P.leaf[k].bounds = rec;
+  }
+  for (int k = 0; k < P.n_outs; ++k) {
+    P.out[k].ptr = slot_ptr(r, st.out_slot[k]);
+    P.out[k].extent = slot_extent(r, st.out_slot[k], P.out[k].elem);
+    P.out[k].bounds = rec;
+  }
   return P;
 }
 
@@ -998,6 +1025,14 @@ static void check_device_status(RxDevice* d) {
     int s = d->status[0];
     d->status[0] = 0;
     throw Error(RX_ERR_PEER_TIMEOUT, std::string("a peer did not arrive at ") + (s == 2 ? "a halo exchange" : "an all-reduce") + " within the wait limit (status " + std::to_string(s) + ")");
+  }
+  if (d->status[4]) {
+    const int what = d->status[4];
+    const long long at = ((long long)d->status[6] << 32) | (unsigned)d->status[5];
+    const int extent = d->status[7];
+    d->status[4] = d->status[5] = d->status[6] = d->status[7] = 0;
+    throw Error(RX_ERR_CUDA, std::string("bounds check: ") + (what >= 200 ? "a result" : "an operand") + " (register " + std::to_string(what % 100) + ") was accessed at element " +
+                                 std::to_string(at) + " of a buffer of " + std::to_string(extent) + " elements; the access was skipped");
   }
   for (int w = 1; w <= 2; ++w)
     if (d->status[w]) {

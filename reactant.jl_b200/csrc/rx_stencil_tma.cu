@@ -42,6 +42,8 @@ struct StencilParams {
   int dy[kMaxTaps], dx[kMaxTaps];
   int tiles_x, tiles_y;
   int* status;
+  long long dst_extent;  // bounds-checked builds: elements in the destination buffer, and where a miss is recorded
+  int* bounds;
 };
 
 // One sweep of this CTA's tiles.  `it` counts the tiles this CTA has processed since the kernel started: it
@@ -90,6 +92,12 @@ __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const Ste
     if ((int)threadIdx.x < p.tw && c < p.cols) {
       float* out = p.dst + p.dst_off + r0 * p.dst_ld + c;
       int rmax = (int)min((int64_t)TH, p.rows - r0);
+#if RX_BOUNDS
+      // this thread writes one element per row of the tile: first and last must lie inside the destination
+      if (rmax > 0 && !(rx_in_bounds(p.bounds, p.dst_extent, p.dst_off + r0 * p.dst_ld + c, 1, 299) &&
+                        rx_in_bounds(p.bounds, p.dst_extent, p.dst_off + (r0 + rmax - 1) * p.dst_ld + c, 1, 299)))
+        rmax = 0;
+#endif
       if (FAST5) {
         const float k = fast_c;
         if (p.cross) {
@@ -387,6 +395,8 @@ bool prepare_stencil(RxDevice* d, const Step& st, const VmProgram& P, Prepared* 
   int* dstatus = nullptr;
   cudaHostGetDevicePointer(&dstatus, d->status, 0);
   sp.status = dstatus + 1;
+  sp.dst_extent = P.out[0].extent;
+  sp.bounds = P.out[0].bounds;
   out->smem = (size_t)STAGES * BOX_W * box_h * sizeof(float) + 128;  // 2 x 34 KiB for a radius-1 stencil; two CTAs per SM measured fastest
   out->fast = P.fast_id == FAST_STENCIL5_MUL && sp.n_taps == 5;
   return true;

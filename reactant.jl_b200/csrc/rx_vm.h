@@ -173,6 +173,9 @@ struct VmLeaf {
   uint8_t reg;                // destination register
   uint8_t linear;             // 1: contiguous in the root linear index; 2: scalar broadcast
   uint8_t pad[5];
+  // Bounds-checked builds (RX_BOUNDS): elements in the buffer behind `ptr`, and where a miss is recorded.
+  int64_t extent;
+  int* bounds;
 };
 
 struct VmOut {
@@ -183,6 +186,8 @@ struct VmOut {
   uint8_t reg;                // register holding the value
   uint8_t linear;
   uint8_t pad[5];
+  int64_t extent;             // as in VmLeaf
+  int* bounds;
 };
 
 struct VmProgram {
