@@ -160,7 +160,7 @@ static __device__ __noinline__ void rx_bounds_miss(int* rec, int64_t extent, int
   }
 }
 __device__ __forceinline__ bool rx_in_bounds(int* rec, int64_t extent, int64_t first, int count, int what) {
-  if (first >= 0 && first + count <= extent) return true;
+  if (!rec || (first >= 0 && first + count <= extent)) return true;  // no record word: the descriptor was not bound for checking
   rx_bounds_miss(rec, extent, first, what);
   return false;
 }

@@ -235,7 +235,9 @@ int64_t slot_extent(DevRun& r, int slot, int elem) {
   return n;
 }
 
-VmProgram bind(const Step& st, DevRun& r) {
+// The step's program with its operand and result descriptors pointed at this run's buffers.  `skip_leaf`: an operand
+// that is not read from memory (the accumulator of a fused GEMM epilogue).
+VmProgram bind(const Step& st, DevRun& r, int skip_leaf = -1) {
   VmProgram P = st.prog;
   int* rec = nullptr;
 #if RX_BOUNDS
@@ -243,6 +245,10 @@ VmProgram bind(const Step& st, DevRun& r) {
   rec += 4;  // words 4..7 of the status block: {what, index low, index high, extent}
 #endif
   for (int k = 0; k < P.n_leaves; ++k) {
+    if (k == skip_leaf) {
+      P.leaf[k].ptr = nullptr;
+      continue;
+    }
     P.leaf[k].ptr = slot_ptr(r, st.leaf_slot[k]);
     P.leaf[k].extent = slot_extent(r, st.leaf_slot[k], P.leaf[k].elem);
     P.leaf[k].bounds = rec;
@@ -459,9 +465,7 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
       const GemmDesc& g = st.gemm;
       void* dptr = r.table[g.d_slot] ? r.table[g.d_slot]->ptr : nullptr;  // absent when the product is consumed in the epilogue only
       if (g.has_epilogue) {
-        VmProgram P = st.prog;
-        for (int k = 0; k < P.n_leaves; ++k) P.leaf[k].ptr = k == g.acc_leaf ? nullptr : slot_ptr(r, st.leaf_slot[k]);
-        for (int k = 0; k < P.n_outs; ++k) P.out[k].ptr = slot_ptr(r, st.out_slot[k]);
+        VmProgram P = bind(st, r, g.acc_leaf);
         GemmEpilogueArgs ea;
         ea.prog = &P;
         for (int q = 0; q < g.n_col; ++q) ea.col_partial[q] = (float*)slot_ptr(r, g.col_slot[q]);

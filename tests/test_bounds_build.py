@@ -43,9 +43,10 @@ try:
         got = run(text, [x, y])[0]; want = ref.run_module(text, [x, y])[0]
         assert abs(float(got) - float(want)) <= 1e-4 * max(1.0, abs(float(want)) + np.sqrt(n)), (got, want)
     # strided maps and axis reductions
-    a = rng.standard_normal((37, 53)).astype(np.float32)
+    a = rng.standard_normal((37, 53)).astype(np.float32)   # Julia layout: the module takes the reversed dims
     text = rx.programs.logsumexp_dims1(37, 53)
-    got = run(text, [a])[0]; want = ref.run_module(text, [a])[0]
+    got = np.asarray(rx.compile(text, client)(rx.to_rarray(a, client)))
+    want = ref.run_module(text, [ref.julia_to_xla(a)])[0].T
     np.testing.assert_allclose(got, want, rtol=1e-5)
     # stencil: TMA path (row pitch a multiple of 16 bytes) and the strided map path
     for n in (36, 33):
