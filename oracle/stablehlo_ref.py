@@ -453,6 +453,16 @@ class Interpreter:
                 st = int(np.clip(int(s.a), 0, x.shape[d] - n))
                 sl.append(slice(st, st + n))
             return T(np.ascontiguousarray(x.a[tuple(sl)]), x.et)
+        if short == "dynamic_slice":
+            # %r = stablehlo.dynamic_slice %x, %i0, ..., sizes = [..]: start indices clamped so that the slice fits
+            vals = _operands(text[:text.index("sizes")], env, len(name))
+            x, starts = vals[0], vals[1:]
+            sizes = [int(v) for v in re.search(r"sizes\s*=\s*\[([^\]]*)\]", text).group(1).split(",") if v.strip()]
+            sl = []
+            for d, st in enumerate(starts):
+                b = int(np.clip(int(st.a), 0, x.shape[d] - sizes[d]))
+                sl.append(slice(b, b + sizes[d]))
+            return T(np.ascontiguousarray(x.a[tuple(sl)]), x.et)
         if short == "dynamic_update_slice":
             vals = _operands(text, env, len(name))
             x, u, starts = vals[0], vals[1], vals[2:]

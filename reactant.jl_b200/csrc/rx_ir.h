@@ -45,7 +45,7 @@ struct Type {
 
 enum class OpK {
   Constant, Iota, Unary, Binary, Convert, Compare, Select, Clamp,
-  BroadcastInDim, Transpose, Reshape, Slice, DynamicUpdateSlice, Pad, Concatenate,
+  BroadcastInDim, Transpose, Reshape, Slice, DynamicSlice, DynamicUpdateSlice, Pad, Concatenate,
   DotGeneral, Reduce, ReduceWindow, While, AllReduce, Return
 };
 

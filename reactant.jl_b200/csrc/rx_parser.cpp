@@ -740,6 +740,19 @@ struct Parser {
       maybe_attr_dict();
       signature(&ins, &outs);
       finish(op, res, outs);
+    } else if (shortn == "dynamic_slice") {
+      // %r = stablehlo.dynamic_slice %x, %i0, %i1, sizes = [1, 4] : (tensor<..>, tensor<i32>, tensor<i32>) -> tensor<..>
+      op.kind = OpK::DynamicSlice;
+      for (;;) {
+        op.in.push_back(use());
+        expect(",");
+        if (accept_kw("sizes")) break;
+      }
+      expect("=");
+      op.dims = int_list();
+      maybe_attr_dict();
+      signature(&ins, &outs);
+      finish(op, res, outs);
     } else if (shortn == "dynamic_update_slice") {
       op.kind = OpK::DynamicUpdateSlice;
       do op.in.push_back(use()); while (accept(","));

@@ -59,6 +59,10 @@ struct Expr {
   RMap map;  // View: one entry per kid dim
   int cost = 0;
   bool heavy = false;
+  // Sym: the counter of an enclosing counted loop, value = sym_a * it + sym_b in 0-based iteration `it` of the loop at
+  // nesting depth sym_depth (0: not a counter, nothing is known about the value)
+  int sym_depth = 0;
+  int64_t sym_a = 0, sym_b = 0;
 };
 
 std::vector<int64_t> canon_strides(const std::vector<int64_t>& shape) {
@@ -417,6 +421,36 @@ struct Planner {
   }
 
   // host evaluation of scalar integer expressions (loop bounds, update offsets)
+  // Integer scalar bookkeeping that is affine in a loop counter: value = a * it + b (depth: which loop; 0 = constant).
+  static bool affine_int(const ExprP& e, int64_t* a, int64_t* b, int* depth) {
+    switch (e->k) {
+      case Expr::Const: *a = 0; *b = dt_is_float(e->dt) ? (int64_t)e->f : e->i; *depth = 0; return true;
+      case Expr::Sym:
+        if (e->sym_depth <= 0) return false;
+        *a = e->sym_a; *b = e->sym_b; *depth = e->sym_depth;
+        return true;
+      case Expr::View: return affine_int(e->kids[0], a, b, depth);
+      case Expr::Op: {
+        int64_t a0 = 0, b0 = 0, a1 = 0, b1 = 0;
+        int d0 = 0, d1 = 0;
+        if (e->kids.size() >= 1 && !affine_int(e->kids[0], &a0, &b0, &d0)) return false;
+        if (e->kids.size() >= 2 && !affine_int(e->kids[1], &a1, &b1, &d1)) return false;
+        if (d0 && d1 && d0 != d1) return false;  // counters of two different loops
+        *depth = d0 ? d0 : d1;
+        switch (e->vmop) {
+          case VM_IADD: *a = a0 + a1; *b = b0 + b1; return true;
+          case VM_ISUB: *a = a0 - a1; *b = b0 - b1; return true;
+          case VM_IMUL:
+            if (a0 && a1) return false;
+            *a = a0 * b1 + a1 * b0; *b = b0 * b1;
+            return true;
+          case VM_MOV: *a = a0; *b = b0; return true;
+          default: return false;
+        }
+      }
+      default: return false;
+    }
+  }
   static bool const_int(const ExprP& e, int64_t* out) {
     switch (e->k) {
       case Expr::Const: *out = dt_is_float(e->dt) ? (int64_t)e->f : e->i; return true;
@@ -1856,6 +1890,63 @@ struct Planner {
     return false;
   }
 
+  int loop_depth = 0;
+
+  // stablehlo.dynamic_slice (src/Ops.jl:3680-3696; scalar indexing `a[i]` with a traced index, src/Indexing.jl:25-31).
+  // Constant start indices make it a slice.  Start indices that are affine in the counter of the enclosing counted
+  // loop (`fict[t]` in benchmark/polybench/stencil.jl:49) become a DynSlice step: the host knows the iteration it is
+  // enqueueing, so the slice is a small device-to-device copy from a computed offset into a temporary, and everything
+  // downstream sees an ordinary array.  The slice must be contiguous in the operand (a scalar, a row, whole trailing
+  // dims); anything else is refused by name.
+  void plan_dynamic_slice(const Op& op) {
+    int v = op.out[0], x = op.in[0];
+    if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dynamic_slice of a sharded tensor");
+    const Type& tin = m.values[x].type;
+    const Type t = m.values[v].type;
+    const int rank = (int)tin.shape.size();
+    if ((int)op.in.size() != 1 + rank || (int)op.dims.size() != rank) throw Error(RX_ERR_PARSE, "stablehlo.dynamic_slice: start indices or sizes do not match the operand rank");
+    std::vector<int64_t> a(rank), b(rank);
+    int depth = 0;
+    for (int d = 0; d < rank; ++d) {
+      int dd = 0;
+      if (!affine_int(env[op.in[1 + d]], &a[d], &b[d], &dd))
+        throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dynamic_slice with a start index that is not affine in a loop counter");
+      if (dd && depth && dd != depth) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dynamic_slice indexed by the counters of two loops");
+      if (dd) depth = dd;
+      if (op.dims[d] < 0 || op.dims[d] > tin.shape[d]) throw Error(RX_ERR_SHAPE, "stablehlo.dynamic_slice: slice size exceeds the operand");
+    }
+    if (depth == 0) {  // all constant: an ordinary slice, clamped as the op specifies
+      RMap mp(rank);
+      for (int d = 0; d < rank; ++d) mp[d] = {d, 1, std::max<int64_t>(0, std::min<int64_t>(b[d], tin.shape[d] - op.dims[d]))};
+      env[v] = simplify(view(env[x], t, mp));
+      return;
+    }
+    if (depth != loop_depth) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dynamic_slice indexed by the counter of an outer loop");
+    // contiguous: sizes are 1 up to some dim, then one partial dim, then whole dims
+    int first = 0;
+    while (first < rank && op.dims[first] == 1) ++first;
+    for (int d = first + 1; d < rank; ++d)
+      if (op.dims[d] != tin.shape[d]) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dynamic_slice with loop-variant start indices whose slice is not contiguous in the operand");
+    check_dt(op, t.dt);
+    Step st;
+    st.kind = StepK::DynSlice;
+    st.src_slot = materialise(env[x], "dynamic_slice operand");
+    st.dst_slot = new_slot(t);
+    st.dyn_elem_bytes = (int64_t)dt_size(t.dt);
+    st.bytes = t.numel() * st.dyn_elem_bytes;
+    const std::vector<int64_t> cs = canon_strides(tin.shape);
+    for (int d = 0; d < rank; ++d) {
+      st.dyn_a.push_back(a[d]);
+      st.dyn_b.push_back(b[d]);
+      st.dyn_hi.push_back(tin.shape[d] - op.dims[d]);
+      st.dyn_stride.push_back(cs[d]);
+    }
+    st.note = "dynamic slice at an offset that follows the loop counter (" + std::to_string(st.bytes) + " bytes per iteration)";
+    const int dst = st.dst_slot;
+    cur->push_back(std::move(st));
+    env[v] = leaf(dst, t);
+  }
+
   void plan_dus(const Op& op) {
     int v = op.out[0], o = op.in[0], u = op.in[1];
     for (int x : op.in) if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dynamic_update_slice of a sharded tensor");
@@ -1874,13 +1965,22 @@ struct Planner {
     // use, and every expression that looked at it (the slices of the previous half-step, say) has already been
     // turned into a step that runs before this one.
     bool in_place = whole_slot(O) && slot_writable(O->slot) && !read_later(O->slot, op);
+    std::vector<int64_t> cs = canon_strides(t.shape);
+    int64_t off = 0;
+    for (size_t d = 0; d < starts.size(); ++d) off += starts[d] * cs[d];
     if (in_place) {
-      // the update may read the destination only at the position it writes
-      std::vector<const Expr*> lv;
-      std::set<const Expr*> seen;
-      collect_leaves(U, lv, seen);
-      for (auto* l : lv)
-        if (l->slot == O->slot) in_place = false;
+      // the update may read the destination only at the very position it writes (A[w] = A[w] - ..., the in-place
+      // field updates of fdtd_2d, benchmark/polybench/stencil.jl:52-66): every element then depends on its own old
+      // value only, whatever order the kernel takes them in
+      Lowering L(U->shape);
+      L.lower(U, Lowering::identity(U->shape.size()));
+      for (auto& lf : L.leaves) {
+        if (lf.slot != O->slot) continue;
+        bool same = lf.offset == off;
+        for (size_t d = 0; d < cs.size() && same; ++d)
+          if (U->shape[d] != 1 && lf.stride[d] != cs[d]) same = false;
+        if (!same) in_place = false;
+      }
     }
     if (in_place) {
       dst = O->slot;
@@ -1898,9 +1998,6 @@ struct Planner {
         emit_map(O, dst, 0, canon_strides(t.shape), "materialise update target");
       }
     }
-    std::vector<int64_t> cs = canon_strides(t.shape);
-    int64_t off = 0;
-    for (size_t d = 0; d < starts.size(); ++d) off += starts[d] * cs[d];
     emit_map(U, dst, off, cs, "update window at offset " + std::to_string(off));
     env[v] = leaf(dst, t);
   }
@@ -2151,6 +2248,7 @@ struct Planner {
     // ---- trip count: cond is `compare LT|LE, counter, bound`, body steps counter by a constant
     int64_t trip = -1;
     int counter = -1;
+    int64_t counter_init = 0, counter_step = 0;
     {
       if (cond.ops.empty() || cond.yields.size() != 1) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: condition is not a comparison");
       // bind cond args symbolically
@@ -2194,6 +2292,8 @@ struct Planner {
       if (step <= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while: counter is not advanced by a positive constant");
       if (cmp->ew == CMP_LE) bound += 1;
       trip = bound <= init ? 0 : (bound - init + step - 1) / step;
+      counter_init = init;
+      counter_step = step;
     }
     // ---- loop-carried tensors live in slots
     Step loop;
@@ -2241,6 +2341,7 @@ struct Planner {
     // ---- body
     std::vector<Step>* saved = cur;
     cur = &loop.body;
+    ++loop_depth;
     for (size_t k = 0; k < n; ++k) {
       int arg = body.args[k];
       if (state_slot[k] >= 0) {
@@ -2250,6 +2351,11 @@ struct Planner {
         s->k = Expr::Sym;
         s->dt = m.values[arg].type.dt;
         s->shape = m.values[arg].type.shape;
+        if ((int)k == counter) {  // its value in iteration `it` is known: init + it * step
+          s->sym_depth = loop_depth;
+          s->sym_a = counter_step;
+          s->sym_b = counter_init;
+        }
         env[arg] = s;
       }
     }
@@ -2260,9 +2366,11 @@ struct Planner {
       plan_region(body);
     } catch (...) {
       nparts = saved_parts;
+      --loop_depth;
       throw;
     }
     nparts = saved_parts;
+    --loop_depth;
     std::vector<int> yslot(n, -1);
     for (size_t k = 0; k < n; ++k) {
       if (state_slot[k] < 0) continue;
@@ -2363,6 +2471,7 @@ struct Planner {
         case OpK::Reshape: plan_reshape(op); break;
         case OpK::Reduce: plan_reduce(op); break;
         case OpK::ReduceWindow: plan_reduce_window(op); break;
+        case OpK::DynamicSlice: plan_dynamic_slice(op); break;
         case OpK::DynamicUpdateSlice: plan_dus(op); break;
         case OpK::Pad: plan_pad(op); break;
         case OpK::Concatenate: plan_concat(op); break;
@@ -2471,6 +2580,7 @@ const char* step_name(StepK k) {
     case StepK::SumPartials: return "sum_partials";
     case StepK::RowsIn: return "rows_in";
     case StepK::RowsOut: return "rows_out";
+    case StepK::DynSlice: return "dyn_slice";
   }
   return "?";
 }

@@ -29,7 +29,7 @@ struct Slot {
   int64_t bytes() const { return type.numel() * (int64_t)dt_size(type.dt); }
 };
 
-enum class StepK { Map, ReduceFull, ReduceRow, ReduceCol, LogSumExp, Stencil, Gemm, Copy, Fill, Loop, AllReduce, Scan, SumPartials, RowsIn, RowsOut };
+enum class StepK { Map, ReduceFull, ReduceRow, ReduceCol, LogSumExp, Stencil, Gemm, Copy, Fill, Loop, AllReduce, Scan, SumPartials, RowsIn, RowsOut, DynSlice };
 
 struct GemmDesc {
   // D[m][n] = sum_k A(m,k) * B(k,n); strides in elements of the operand slots.
@@ -97,6 +97,12 @@ struct Step {
   int64_t count = 0;
   // SumPartials
   std::vector<SumJob> sums;
+  // DynSlice: `bytes` contiguous bytes of src_slot copied to dst_slot, starting at element
+  //   sum_d clamp(dyn_a[d] * it + dyn_b[d], 0, dyn_hi[d]) * dyn_stride[d]
+  // where `it` is the current iteration (0-based) of the innermost enclosing loop: a stablehlo.dynamic_slice whose
+  // start indices are affine in the loop counter (fict[t] in benchmark/polybench/stencil.jl:49).
+  std::vector<int64_t> dyn_a, dyn_b, dyn_hi, dyn_stride;
+  int64_t dyn_elem_bytes = 4;
 };
 
 struct ResultBinding {

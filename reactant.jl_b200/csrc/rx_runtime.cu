@@ -188,6 +188,7 @@ struct DevRun {
   std::vector<std::shared_ptr<Storage>> table;  // per slot
   // slots with an all-reduce still running on the device's communication stream, and the event that ends it
   std::map<int, cudaEvent_t> pending;
+  int64_t iter = 0;  // 0-based iteration of the innermost counted loop whose body is being enqueued
 };
 
 // Before a step touches a slot whose all-reduce is still in flight on the communication stream, the compute
@@ -311,6 +312,7 @@ const char* kind_name(StepK k) {
     case StepK::SumPartials: return "sum_partials";
     case StepK::RowsIn: return "rows_in";
     case StepK::RowsOut: return "rows_out";
+    case StepK::DynSlice: return "dyn_slice";
   }
   return "?";
 }
@@ -496,6 +498,16 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
       CK(cudaMemcpyAsync(slot_ptr(r, st.dst_slot), slot_ptr(r, st.src_slot), (size_t)st.bytes, cudaMemcpyDeviceToDevice, d->stream));
       break;
     }
+    case StepK::DynSlice: {
+      // the start indices follow the loop counter; each is clamped so that the slice stays inside the operand
+      int64_t off = 0;
+      for (size_t k = 0; k < st.dyn_a.size(); ++k) {
+        const int64_t start = std::max<int64_t>(0, std::min<int64_t>(st.dyn_a[k] * r.iter + st.dyn_b[k], st.dyn_hi[k]));
+        off += start * st.dyn_stride[k];
+      }
+      CK(cudaMemcpyAsync(slot_ptr(r, st.dst_slot), (const char*)slot_ptr(r, st.src_slot) + off * st.dyn_elem_bytes, (size_t)st.bytes, cudaMemcpyDeviceToDevice, d->stream));
+      break;
+    }
     default:
       throw Error(RX_ERR_PLAN, std::string("internal: step kind ") + kind_name(st.kind) + " has no single-device launch");
   }
@@ -669,13 +681,17 @@ void run_steps(RxExecutable* ex, const std::vector<Step>& steps, std::vector<Dev
       for (size_t k = 0; k < runs.size(); ++k)
         if (!try_stencil_loop(st, runs[k])) { rest.push_back(std::move(runs[k])); rest_index.push_back(k); }
       if (rest.empty()) continue;
+      std::vector<int64_t> outer_iter;
+      for (auto& r : rest) outer_iter.push_back(r.iter);
       for (int64_t it = 0; it < st.trip; ++it) {
+        for (auto& r : rest) r.iter = it;
         run_steps(ex, st.body, rest);
         for (auto& r : rest) {
           join_all_pending(r);  // in-flight all-reduces are tracked by slot, and the rotation moves storages between slots
           rotate_loop_state(st, r);
         }
       }
+      for (size_t q = 0; q < rest.size(); ++q) rest[q].iter = outer_iter[q];
       for (size_t q = 0; q < rest.size(); ++q) runs[rest_index[q]] = std::move(rest[q]);
     } else if (st.kind == StepK::AllReduce) {
       // vectors (gradients) go to the communication stream so that the steps after them keep the SMs busy;

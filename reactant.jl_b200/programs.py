@@ -349,6 +349,92 @@ def _two_array_loop(name, shape, steps, consts, body_lines, yield_a, yield_b):
 """
 
 
+def fdtd2d(nx: int, ny: int, tmax: int) -> str:
+    """benchmark/polybench/stencil.jl:42-72 (fdtd_2d_vectorized): per time step t
+        EY[1, :] .= fict[t]
+        EY[2:NX, :]       .-= 0.5 .* (HZ[2:NX, :] .- HZ[1:NX-1, :])
+        EX[:, 2:NY]       .-= 0.5 .* (HZ[:, 2:NY] .- HZ[:, 1:NY-1])
+        HZ[1:NX-1,1:NY-1] .-= 0.7 .* (EX[1:NX-1,2:NY] .- EX[1:NX-1,1:NY-1] .+ EY[2:NX,1:NY-1] .- EY[1:NX-1,1:NY-1])
+    on NX x NY Float32 arrays (tensors [NY][NX]).  `fict[t]` is a scalar read at the traced loop variable: the
+    induction value start + i * step of the counter (src/ControlFlow / ReactantCore `@trace for`), converted to Int32 and
+    made 0-based (src/Ops.jl:3624-3646), a dynamic_slice of one element (src/Indexing.jl:25-31) reshaped to a scalar and
+    broadcast into the first row.  All three arrays are mutated, hence donated and returned."""
+    t, tf = _t([ny, nx]), _t([tmax])
+    b = _Body()
+    ti = b.op("stablehlo.multiply %iterArg, %c_2", "tensor<i64>")
+    ti = b.op(f"stablehlo.add {ti}, %c_2", "tensor<i64>")
+    t32 = f"%v{b.n}"
+    b.n += 1
+    b.lines.append(f"      {t32} = stablehlo.convert {ti} : (tensor<i64>) -> tensor<i32>")
+    idx = b.op(f"stablehlo.subtract {t32}, %c_1", "tensor<i32>")
+    fs = f"%v{b.n}"
+    b.n += 1
+    b.lines.append(f"      {fs} = stablehlo.dynamic_slice %arg3, {idx}, sizes = [1] : ({tf}, tensor<i32>) -> tensor<1xf32>")
+    f0 = f"%v{b.n}"
+    b.n += 1
+    b.lines.append(f"      {f0} = stablehlo.reshape {fs} : (tensor<1xf32>) -> tensor<f32>")
+    tcol = _t([ny, 1])
+    row = f"%v{b.n}"
+    b.n += 1
+    b.lines.append(f"      {row} = stablehlo.broadcast_in_dim {f0}, dims = [] : (tensor<f32>) -> {tcol}")
+    ey1 = b.dus("%iterArg_1", row, ["%c_z", "%c_z"], t, tcol)
+    # EY[2:NX, :]: tensor columns 1..NX-1
+    te = _t([ny, nx - 1])
+    a = b.slice(ey1, [(0, ny), (1, nx)], t, te)
+    h1 = b.slice("%iterArg_2", [(0, ny), (1, nx)], t, te)
+    h0 = b.slice("%iterArg_2", [(0, ny), (0, nx - 1)], t, te)
+    d = b.op(f"stablehlo.subtract {h1}, {h0}", te)
+    mm = b.op(f"stablehlo.multiply %half_e, {d}", te)
+    u = b.op(f"stablehlo.subtract {a}, {mm}", te)
+    ey2 = b.dus(ey1, u, ["%c_z", "%c_1"], t, te)
+    # EX[:, 2:NY]: tensor rows 1..NY-1
+    tx = _t([ny - 1, nx])
+    a = b.slice("%iterArg_0", [(1, ny), (0, nx)], t, tx)
+    h1 = b.slice("%iterArg_2", [(1, ny), (0, nx)], t, tx)
+    h0 = b.slice("%iterArg_2", [(0, ny - 1), (0, nx)], t, tx)
+    d = b.op(f"stablehlo.subtract {h1}, {h0}", tx)
+    mm = b.op(f"stablehlo.multiply %half_x, {d}", tx)
+    u = b.op(f"stablehlo.subtract {a}, {mm}", tx)
+    ex2 = b.dus("%iterArg_0", u, ["%c_1", "%c_z"], t, tx)
+    # HZ[1:NX-1, 1:NY-1]
+    th = _t([ny - 1, nx - 1])
+    hz = b.slice("%iterArg_2", [(0, ny - 1), (0, nx - 1)], t, th)
+    x1 = b.slice(ex2, [(1, ny), (0, nx - 1)], t, th)
+    x0 = b.slice(ex2, [(0, ny - 1), (0, nx - 1)], t, th)
+    y1 = b.slice(ey2, [(0, ny - 1), (1, nx)], t, th)
+    y0 = b.slice(ey2, [(0, ny - 1), (0, nx - 1)], t, th)
+    s1 = b.op(f"stablehlo.subtract {x1}, {x0}", th)
+    s2 = b.op(f"stablehlo.add {s1}, {y1}", th)
+    s3 = b.op(f"stablehlo.subtract {s2}, {y0}", th)
+    mm = b.op(f"stablehlo.multiply %seven, {s3}", th)
+    u = b.op(f"stablehlo.subtract {hz}, {mm}", th)
+    hz2 = b.dus("%iterArg_2", u, ["%c_z", "%c_z"], t, th)
+    body = "\n".join(b.lines)
+    return f"""module @reactant_fdtd2d attributes {{mhlo.num_partitions = 1 : i64, mhlo.num_replicas = 1 : i64}} {{
+  func.func @main(%arg0: {t} {{tf.aliasing_output = 0 : i32}}, %arg1: {t} {{tf.aliasing_output = 1 : i32}}, %arg2: {t} {{tf.aliasing_output = 2 : i32}}, %arg3: {tf}) -> ({t}, {t}, {t}) {{
+    %c = stablehlo.constant dense<0> : tensor<i64>
+    %c_0 = stablehlo.constant dense<{tmax}> : tensor<i64>
+    %c_2 = stablehlo.constant dense<1> : tensor<i64>
+    %c_1 = stablehlo.constant dense<1> : tensor<i32>
+    %c_z = stablehlo.constant dense<0> : tensor<i32>
+    %half_e = stablehlo.constant dense<5.000000e-01> : {te}
+    %half_x = stablehlo.constant dense<5.000000e-01> : {tx}
+    %seven = stablehlo.constant dense<0.699999988> : {th}
+    %0:4 = stablehlo.while(%iterArg = %c, %iterArg_0 = %arg0, %iterArg_1 = %arg1, %iterArg_2 = %arg2) : tensor<i64>, {t}, {t}, {t} attributes {{enzyme.disable_mincut}}
+     cond {{
+      %1 = stablehlo.compare  LT, %iterArg, %c_0 : (tensor<i64>, tensor<i64>) -> tensor<i1>
+      stablehlo.return %1 : tensor<i1>
+    }} do {{
+      %1 = stablehlo.add %iterArg, %c_2 : tensor<i64>
+{body}
+      stablehlo.return %1, {ex2}, {ey2}, {hz2} : tensor<i64>, {t}, {t}, {t}
+    }}
+    return %0#1, %0#2, %0#3 : {t}, {t}, {t}
+  }}
+}}
+"""
+
+
 def jacobi1d(n: int, steps: int) -> str:
     """benchmark/polybench/stencil.jl:201-221 (jacobi_1d_vectorized): per iteration
     B[2:N-1] = (1/3) .* (A[1:N-2] .+ A[2:N-1] .+ A[3:N]), then the same from B into A."""
