@@ -332,7 +332,7 @@ def setup_mlp(rx, client, dist, F=1024, H=4096, O=1024, B=4096):
         """Every gradient and the loss against the numpy oracle (float64 accumulation) of the same module on the same
         inputs; each output within 2e-2 of its largest magnitude (the bf16 dot_general bar)."""
         if world > 1:
-            return None  # the global batch lives on several ranks; the 2-GPU parity tests cover the data-parallel form
+            return check_data_parallel(result)
         ref, _ = entry.load_oracle()
         f32 = lambda a: np.asarray(a, dtype=np.float32)
         want = ref.run_module(text, [f32(W1), b1, f32(W2), b2, f32(X), Y])
@@ -345,6 +345,29 @@ def setup_mlp(rx, client, dist, F=1024, H=4096, O=1024, B=4096):
             worst = max(worst, e)
         return {"got": float(np.asarray(result[4], dtype=np.float64)), "want": float(want[4]), "rel_err": worst, "tol": 2e-2, "ok": bool(worst <= 2e-2), "per_output": detail,
                 "against": "numpy StableHLO oracle (float64 accumulation) on the same inputs; per output max|got - want| / max|want|"}
+
+    def check_data_parallel(result):
+        """N > 1: the global batch lives on several ranks, so the all-reduced gradients are checked by decomposition.
+        Every rank runs the unsharded step on its own rows (the program whose results the N = 1 run checks against the
+        oracle); the ranks' gradients and losses are gathered, and their mean -- what the data-parallel step must
+        produce, every rank holding the same number of rows -- is compared with this rank's result.  Independent of the
+        all-reduce path: the local programs contain no collective."""
+        local = rx.compile(rx.programs.mlp_grad(F, H, O, B), client)
+        lres = local(*[rx.to_rarray(a, client) for a in ins_t])
+        mine = [np.asarray(o.data[0].to_host()).astype(np.float32) for o in lres]
+        worst, names, detail = 0.0, ("dW1", "db1", "dW2", "db2", "loss"), {}
+        for name, g, m in zip(names, result, mine):
+            parts = dist.all_gather_bytes(np.ascontiguousarray(m).tobytes())
+            mean = sum(np.frombuffer(p, dtype=np.float32).astype(np.float64) for p in parts) / world
+            g = np.asarray(g).astype(np.float64).reshape(-1)
+            e = float(np.max(np.abs(g - mean)) / max(float(np.max(np.abs(mean))), 1e-30))
+            detail[name] = e
+            worst = max(worst, e)
+        worst = dist.reduce(worst, "max")
+        loss = float(np.asarray(result[4], dtype=np.float64))
+        same = dist.reduce(loss, "max") == dist.reduce(loss, "min")
+        return {"got": loss, "want": None, "rel_err": worst, "tol": 2e-2, "ok": bool(worst <= 2e-2 and same), "per_output": detail, "same_bits_on_every_rank": bool(same),
+                "against": "mean over the ranks of the unsharded step's results on each rank's own rows (that program is checked against the numpy oracle at N = 1); per output max|got - want| / max|want|"}
 
     def cpu_run():
         ref, _ = entry.load_oracle()
