@@ -348,7 +348,7 @@ int64_t total_of(const VmProgram& P) {
 }  // namespace
 
 int red_code(RedK k, DT dt) {
-  bool f = dt == DT::F32 || dt == DT::BF16;
+  bool f = dt == DT::F32 || dt == DT::BF16 || dt == DT::F64;
   switch (k) {
     case RedK::Add: return f ? R_FADD : R_IADD;
     case RedK::Max: return f ? R_FMAX : R_IMAX;

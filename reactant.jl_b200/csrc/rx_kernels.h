@@ -29,6 +29,14 @@ cudaError_t launch_reduce_row(const LaunchCtx& c, const VmProgram& P, int code, 
 int reduce_col_splits(int64_t outer, int64_t red_n, int64_t inner, int sm_count);
 cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, uint32_t init_bits, int64_t outer, int64_t red_n,
                               int64_t inner, uint32_t* partials, int nsplit);
+// f64 programs (VmProgram::wide, rx_wide.cu): 64-bit-register interpreter kernels.  shape: 0 = everything to one
+// value, 1 = [outer][red], 2 = [outer][red][inner]; code: the reduction kind as for f32 (R_FADD ...) with f64 = true
+// when the reduced values are doubles, else the 32-bit integer / predicate code; init: raw bits of the init value.
+cudaError_t launch_wide_map(const LaunchCtx& c, const VmProgram& P);
+cudaError_t launch_wide_reduce(const LaunchCtx& c, const VmProgram& P, int shape, int code, bool f64, uint64_t init, int64_t outer, int64_t red_n, int64_t inner);
+cudaError_t launch_wide_scan(const LaunchCtx& c, const void* src, void* dst, int code, int64_t outer, int64_t n, int64_t inner);
+cudaError_t launch_wide_gemm(const LaunchCtx& c, const void* a, const void* b, void* d, int64_t M, int64_t N, int64_t K, int64_t batch, int64_t a_sm, int64_t a_sk, int64_t b_sk,
+                             int64_t b_sn, int64_t a_sb, int64_t b_sb, int64_t d_sb);
 // inclusive scan along the middle dim of a dense [outer][n][inner] array of 32-bit elements
 cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code, int64_t outer, int64_t n, int64_t inner);
 // dst[c] = init + src[0][c] + src[1][c] + ... (rows added in index order) for up to four jobs in one launch: the

@@ -87,6 +87,7 @@ VmElem elem_of(DT dt) {
     case DT::BF16: return EL_BF16;
     case DT::S32: case DT::U32: return EL_I32;
     case DT::PRED: return EL_PRED;
+    case DT::F64: return EL_F64;
     default: throw Error(RX_ERR_UNSUPPORTED_TYPE, std::string("unsupported element type ") + dt_name(dt) + " in a fused computation");
   }
 }
@@ -122,6 +123,19 @@ struct Lowering {
   std::vector<LeafRef> leaves;
   std::map<std::pair<const Expr*, RMap>, int> memo;
   bool has_iota = false;
+  // f64 anywhere in the group makes the program "wide" (64-bit registers, rx_wide.cu): its floating-point constants
+  // live in a table (VNode.imm = index, VNode.cmp = 64); f32 constants are marked (cmp = 32) so that assemble() can
+  // move them there too once it knows the program is wide
+  bool wide = false;
+  std::vector<uint64_t> wconsts;
+  int wconst(double v) {
+    uint64_t bits;
+    memcpy(&bits, &v, 8);
+    for (size_t k = 0; k < wconsts.size(); ++k)
+      if (wconsts[k] == bits) return (int)k;
+    wconsts.push_back(bits);
+    return (int)wconsts.size() - 1;
+  }
 
   explicit Lowering(const std::vector<int64_t>& root_shape) : root(root_shape) {}
 
@@ -152,13 +166,23 @@ struct Lowering {
   }
   int konst(DT dt, double f, int64_t i) {
     uint32_t bits;
-    if (dt == DT::F32 || dt == DT::BF16) {
-      float v = (float)f;
-      memcpy(&bits, &v, 4);
-      if (dt == DT::BF16) bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16;
-    } else {
-      bits = (uint32_t)(int32_t)i;
+    if (dt == DT::F64) {
+      wide = true;
+      VNode n{VM_CONST};
+      n.imm = (uint32_t)wconst(f);
+      n.cmp = 64;
+      return add(n);
     }
+    if (dt == DT::F32 || dt == DT::BF16) {
+      float v32 = (float)f;
+      memcpy(&bits, &v32, 4);
+      if (dt == DT::BF16) bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16;
+      VNode n{VM_CONST};
+      n.imm = bits;
+      n.cmp = 32;
+      return add(n);
+    }
+    bits = (uint32_t)(int32_t)i;
     return konst_bits(bits);
   }
 
@@ -169,6 +193,7 @@ struct Lowering {
     int r = -1;
     switch (e->k) {
       case Expr::Leaf: {
+        if (e->dt == DT::F64) wide = true;
         LeafRef lr{e->slot, e->dt, e->loffset, std::vector<int64_t>(root.size(), 0)};
         for (size_t d = 0; d < e->lstride.size(); ++d) {
           lr.offset += e->lstride[d] * rmap[d].off;
@@ -211,6 +236,7 @@ struct Lowering {
         break;
       }
       case Expr::Op: {
+        if (e->dt == DT::F64) wide = true;
         if (e->vmop == VM_MOV && e->kids.size() == 1) {  // widening converts and identities cost nothing
           r = lower(e->kids[0], rmap);
           break;
@@ -530,7 +556,7 @@ struct Planner {
         case VM_DIV: imm_op = VM_DIVI; rimm_op = VM_RDIVI; break;
         default: break;
       }
-      if (imm_op < 0) continue;
+      if (imm_op < 0 || L.wide) continue;  // a wide program's constants are table entries, not immediates
       if (is_const(n.b)) { n.imm = L.nodes[n.b].imm; n.op = imm_op; n.b = -1; }
       else if (is_const(n.a)) { n.imm = L.nodes[n.a].imm; n.op = rimm_op; n.a = n.b; n.b = -1; }
     }
@@ -694,6 +720,14 @@ struct Planner {
         } else if (op == VM_CONST) {
           VmInstr& in = push(VM_CONST);
           in.imm = n.imm;
+          if (L.wide && n.cmp == 32) {  // an f32 constant inside a wide program: same value, as a double
+            float f32v;
+            memcpy(&f32v, &n.imm, 4);
+            in.imm = (uint32_t)L.wconst((double)f32v);
+            in.c = 1;
+          } else if (n.cmp == 64) {
+            in.c = 1;
+          }
         } else if (op == VM_SELECT) {
           load_acc(n.a);
           uint8_t rb = rg(n.b), rc = rg(n.c);
@@ -789,6 +823,13 @@ struct Planner {
     }
     L.nodes = original_nodes;
     detect_fast(st, L, result_vnode >= 0 ? result_vnode : (outs.empty() ? -1 : outs[0].vnode));
+    if (L.wide) {
+      if (L.wconsts.size() > (size_t)kVmMaxWideConsts) throw Error(RX_ERR_PLAN, "fusion group uses more than " + std::to_string(kVmMaxWideConsts) + " distinct f64 constants");
+      P.wide = 1;
+      P.n_wconst = (int)L.wconsts.size();
+      for (size_t k = 0; k < L.wconsts.size(); ++k) P.wconst[k] = L.wconsts[k];
+      P.fast_id = FAST_NONE;  // the hand-fused kernels are f32
+    }
     cls_after = sp.cls;
   }
   std::vector<int> cls_after;
@@ -1129,6 +1170,15 @@ struct Planner {
   // backward pass need), the two become ONE launch with both outputs: the shared value is computed once in
   // registers, stored, and used -- it is not written and read back, and the operands the two chains have in common
   // are loaded once.  Results are identical: the register holds exactly the value that is stored.
+  // does any value of the expression have type f64?  (Such a group is lowered as a wide program.)
+  static bool expr_wide(const ExprP& e, std::set<const Expr*>& seen) {
+    if (!seen.insert(e.get()).second) return false;
+    if (e->dt == DT::F64) return true;
+    for (auto& k : e->kids)
+      if (expr_wide(k, seen)) return true;
+    return false;
+  }
+
   void emit_map(const ExprP& e, int slot, int64_t offset, const std::vector<int64_t>& ostride, const std::string& note) {
     if (try_fuse_map(e, slot, offset, ostride, note)) {
       last_map.where = nullptr;
@@ -1139,6 +1189,12 @@ struct Planner {
         last_map.outs.size() + 1 <= (size_t)kVmMaxOuts && !last_map.outs.empty() && last_map.outs[0].expr->shape == e->shape) {
       ExprP merged = e;
       bool found = false, blocked = false;
+      {
+        // an f64 group and a 32-bit group stay two launches: merged, the narrow one's floats would be computed as doubles
+        std::set<const Expr*> seen;
+        const bool wide_here = expr_wide(e, seen) || plan.slots[slot].type.dt == DT::F64;
+        blocked = wide_here != ((*cur)[last_map.index].prog.wide != 0);
+      }
       for (auto& o : last_map.outs) {
         std::map<const Expr*, ExprP> memo;
         merged = subst_slot(merged, o.slot, o.expr, memo, &found, &blocked);
@@ -1283,7 +1339,7 @@ struct Planner {
     return VM_MOV;  // pred->int, int->int of the same width
   }
   void check_dt(const Op& op, DT dt) {
-    if (dt == DT::F32 || dt == DT::BF16 || dt == DT::S32 || dt == DT::PRED) return;
+    if (dt == DT::F32 || dt == DT::BF16 || dt == DT::S32 || dt == DT::PRED || dt == DT::F64) return;
     throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type " + std::string(dt_name(dt)) + " in " + op.name);
   }
   // bf16 arithmetic is evaluated in f32 and rounded once per op, as XLA's CPU backend does
@@ -1372,7 +1428,13 @@ struct Planner {
       case OpK::Convert: {
         if (scalar_int) { e = mkop(VM_MOV, t, k); break; }
         check_dt(op, idt);
+        // f64 and narrower floats never share a fusion group (a wide program computes every float as a double):
+        // a value that is widened is materialised in its own type first and read as an operand, a value that is
+        // narrowed is stored (rounded once, which is the conversion) and read back by whatever follows
+        const bool from_wide = idt == DT::F64, to_wide = t.dt == DT::F64;
+        if (to_wide && !from_wide && dt_is_float(idt)) k[0] = materialised(k[0], "value widened to f64");
         e = mkop(convert_op(idt, t.dt), t, k);
+        if (from_wide && !to_wide && dt_is_float(t.dt)) e = materialised(e, "f64 value rounded to " + std::string(dt_name(t.dt)));
         break;
       }
       case OpK::Compare: {
@@ -1576,7 +1638,7 @@ struct Planner {
     if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window over a sharded tensor (other than a scan along an unsharded dimension)");
     const int rank = (int)X->shape.size();
     const Type t = m.values[v].type;
-    const bool flt = X->dt == DT::F32;
+    const bool flt = dt_is_float(X->dt);
     int64_t volume = 1;
     bool padded = false;
     std::vector<int64_t> pshape = X->shape;
@@ -1630,12 +1692,12 @@ struct Planner {
     int v = op.out[0], x = op.in[0];
     ExprP X = env[x], init = env[op.in[1]];
     if (init->k != Expr::Const) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window with a non-constant init value");
-    if (X->dt != DT::F32 && X->dt != DT::S32)
+    if (X->dt != DT::F32 && X->dt != DT::S32 && X->dt != DT::F64)
       throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type " + std::string(dt_name(X->dt)) + " in " + op.name);
     {
       // the padding is filled with the init value, so anything but the combiner's identity would be counted once
       // per padded position; Reactant passes the identity (src/TracedRArray.jl:1063-1070)
-      const bool f = X->dt == DT::F32;
+      const bool f = dt_is_float(X->dt);
       bool identity = false;
       switch (op.red) {
         case RedK::Add: identity = f ? init->f == 0.0 : init->i == 0; break;
@@ -1664,7 +1726,7 @@ struct Planner {
     if (axis >= 0 && shard[x] == axis) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.reduce_window scanning along a sharded dimension");
     shard[v] = shard[x];
     Type t = local_type(v);
-    const bool flt = X->dt == DT::F32;
+    const bool flt = dt_is_float(X->dt);
     if (axis < 0) {  // windows of one element: out = x (op) init
       int vop = flt ? (op.red == RedK::Add ? VM_ADD : op.red == RedK::Max ? VM_MAX : op.red == RedK::Min ? VM_MIN : VM_MUL)
                     : (op.red == RedK::Add ? VM_IADD : op.red == RedK::Max ? VM_IMAX : op.red == RedK::Min ? VM_IMIN : VM_IMUL);
@@ -1676,7 +1738,7 @@ struct Planner {
     st.src_slot = materialise(X, "scan operand");
     st.dst_slot = new_slot(t);
     st.red = op.red;
-    st.red_dt = flt ? DT::F32 : DT::S32;
+    st.red_dt = X->dt == DT::F64 ? DT::F64 : flt ? DT::F32 : DT::S32;
     st.init_f = init->f;
     st.init_i = init->i;
     st.outer = st.inner = 1;
@@ -1751,7 +1813,7 @@ struct Planner {
     int slot = new_slot(rt);
     Step st;
     st.red = op.red;
-    st.red_dt = (dt == DT::S32) ? DT::S32 : (dt == DT::PRED ? DT::PRED : DT::F32);
+    st.red_dt = (dt == DT::S32) ? DT::S32 : (dt == DT::PRED ? DT::PRED : dt == DT::F64 ? DT::F64 : DT::F32);
     if (dt == DT::PRED && op.red == RedK::Add) st.red = RedK::Or;  // i1 addition saturates
     // A reduce over the sharded dim is summed over the mesh afterwards: every device folding the init value into
     // its local result would count it once per device, so the local reduce starts from the identity and the init
@@ -1774,7 +1836,7 @@ struct Planner {
     note << "reduce(" << (op.red == RedK::Add ? "add" : op.red == RedK::Max ? "max" : op.red == RedK::Min ? "min" : op.red == RedK::Mul ? "mul" : op.red == RedK::Or ? "or" : "and") << ")";
     if (nred == 0) {
       // only unit dims are reduced: out = x (op) init, a plain map
-      int vop = st.red_dt == DT::F32 ? (op.red == RedK::Add ? VM_ADD : op.red == RedK::Max ? VM_MAX : op.red == RedK::Min ? VM_MIN : VM_MUL)
+      int vop = dt_is_float(st.red_dt) ? (op.red == RedK::Add ? VM_ADD : op.red == RedK::Max ? VM_MAX : op.red == RedK::Min ? VM_MIN : VM_MUL)
                                      : (st.red == RedK::Add ? VM_IADD : st.red == RedK::Max ? VM_IMAX : st.red == RedK::Min ? VM_IMIN : st.red == RedK::Mul ? VM_IMUL : st.red == RedK::Or ? VM_OR : VM_AND);
       Type xt{X->dt, X->shape};
       ExprP e = late_init ? X : round_if_bf16(mkop(vop, xt, {X, konst(xt, init_f, init_i)}));
@@ -2145,7 +2207,7 @@ struct Planner {
       else shard[v] = (int)A->shape.size() - 1;
     }
     Type rt = local_type(v);
-    if (!(A->dt == B->dt && (A->dt == DT::BF16 || A->dt == DT::F32)))
+    if (!(A->dt == B->dt && (A->dt == DT::BF16 || A->dt == DT::F32 || (A->dt == DT::F64 && rt.dt == DT::F64))))
       throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element types for stablehlo.dot_general: " + std::string(dt_name(A->dt)) + " x " + dt_name(B->dt));
     if (op.lcontract.size() != 1 || op.lbatch.size() > 1)
       throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dot_general with several contracting or batching dimensions");
@@ -2194,7 +2256,7 @@ struct Planner {
     std::ostringstream note;
     note << "gemm M=" << g.M << " N=" << g.N << " K=" << g.K << (g.batch > 1 ? " batch=" + std::to_string(g.batch) : "")
          << " A(" << (g.a_sk == 1 ? "k-major" : "m-major") << ") B(" << (g.b_sk == 1 ? "k-major" : "n-major") << ") "
-         << dt_name(g.in_dt) << "->" << dt_name(g.out_dt) << " fp32 accumulate";
+         << dt_name(g.in_dt) << "->" << dt_name(g.out_dt) << (g.in_dt == DT::F64 ? " fp64 accumulate" : " fp32 accumulate");
     st.note = note.str();
     // can elementwise work on the product join this step?  (what the two-CTA tensor-core kernel with a compiled epilogue takes)
     const bool majors_ok = (g.a_sk == 1 || g.a_sm == 1) && (g.b_sk == 1 || g.b_sn == 1);
@@ -2606,6 +2668,7 @@ void describe_steps(std::ostringstream& os, const std::vector<Step>& steps) {
          << ",\"linear\":" << s.prog.all_linear << ",\"rank\":" << s.prog.rank << ",\"dims\":[";
       for (int d = 0; d < s.prog.rank; ++d) os << (d ? "," : "") << s.prog.dim[d];
       os << "]";
+      if (s.prog.wide) os << ",\"wide\":1";
     }
     if (s.kind == StepK::Gemm && s.gemm.has_epilogue)
       os << ",\"epilogue\":{\"instrs\":" << s.prog.n_instr << ",\"leaves\":" << s.prog.n_leaves << ",\"results\":" << s.prog.n_outs << ",\"column_sums\":" << s.gemm.n_col

@@ -262,6 +262,17 @@ VmProgram bind(const Step& st, DevRun& r, int skip_leaf = -1) {
   return P;
 }
 
+// the init value of a reduction in a wide program: a double's bits, or the 32-bit value in the low word
+uint64_t wide_init_bits(const Step& st) {
+  if (st.red_dt == DT::F64) {
+    uint64_t u;
+    memcpy(&u, &st.init_f, 8);
+    return u;
+  }
+  if (st.red_dt == DT::PRED) return st.init_i ? 1u : 0u;
+  return (uint64_t)(uint32_t)(int32_t)st.init_i;
+}
+
 uint32_t init_bits(const Step& st) {
   if (st.red_dt == DT::F32) {
     float f = (float)st.init_f;
@@ -420,6 +431,11 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
   switch (st.kind) {
     case StepK::Map: {
       VmProgram P = bind(st, r);
+      if (P.wide) {
+        CK(launch_wide_map(c, P));
+        if (!by_note) ps.kind = "map_f64";
+        break;
+      }
       CK(launch_map(c, P));
       break;
     }
@@ -431,16 +447,32 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
     }
     case StepK::ReduceFull: {
       VmProgram P = bind(st, r);
+      if (P.wide) {
+        if (fused) throw Error(RX_ERR_UNSUPPORTED_TYPE, "unsupported element type f64 in a sharded reduction");
+        CK(launch_wide_reduce(c, P, 0, red_code(st.red, st.red_dt), st.red_dt == DT::F64, wide_init_bits(st), 1, st.red_n, 1));
+        if (!by_note) ps.kind = "reduce_f64";
+        break;
+      }
       CK(launch_reduce_full(c, P, red_code(st.red, st.red_dt), init_bits(st), fused));
       break;
     }
     case StepK::ReduceRow: {
       VmProgram P = bind(st, r);
+      if (P.wide) {
+        CK(launch_wide_reduce(c, P, 1, red_code(st.red, st.red_dt), st.red_dt == DT::F64, wide_init_bits(st), st.outer, st.red_n, 1));
+        if (!by_note) ps.kind = "reduce_f64";
+        break;
+      }
       CK(launch_reduce_row(c, P, red_code(st.red, st.red_dt), init_bits(st), st.outer, st.red_n));
       break;
     }
     case StepK::ReduceCol: {
       VmProgram P = bind(st, r);
+      if (P.wide) {
+        CK(launch_wide_reduce(c, P, 2, red_code(st.red, st.red_dt), st.red_dt == DT::F64, wide_init_bits(st), st.outer, st.red_n, st.inner));
+        if (!by_note) ps.kind = "reduce_f64";
+        break;
+      }
       int ns = reduce_col_splits(st.outer, st.red_n, st.inner, d->sm_count);
       size_t words = (size_t)st.outer * ns * st.inner;
       std::shared_ptr<Storage> tmp;
@@ -460,6 +492,10 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
       break;
     }
     case StepK::Scan: {
+      if (st.red_dt == DT::F64) {
+        CK(launch_wide_scan(c, slot_ptr(r, st.src_slot), slot_ptr(r, st.dst_slot), red_code(st.red, st.red_dt), st.outer, st.red_n, st.inner));
+        break;
+      }
       CK(launch_scan(c, slot_ptr(r, st.src_slot), slot_ptr(r, st.dst_slot), red_code(st.red, st.red_dt), st.outer, st.red_n, st.inner));
       break;
     }
@@ -474,6 +510,10 @@ void run_one(RxExecutable* ex, const Step& st, DevRun& r, const FusedAllReduce* 
         for (int q = 0; q < g.n_full; ++q) ea.full_partial[q] = (float*)slot_ptr(r, g.full_slot[q]);
         CK(rx::run_gemm(d, st, slot_ptr(r, g.a_slot), slot_ptr(r, g.b_slot), dptr, &ea));
         if (!by_note) ps.kind = "gemm_tc_fused";
+      } else if (g.in_dt == DT::F64) {
+        CK(launch_wide_gemm(c, (const double*)slot_ptr(r, g.a_slot) + g.a_off, (const double*)slot_ptr(r, g.b_slot) + g.b_off, slot_ptr(r, g.d_slot), g.M, g.N, g.K, g.batch, g.a_sm,
+                            g.a_sk, g.b_sk, g.b_sn, g.a_sb, g.b_sb, g.d_sb));
+        if (!by_note) ps.kind = "gemm_f64";
       } else {
         CK(rx::run_gemm(d, st, slot_ptr(r, g.a_slot), slot_ptr(r, g.b_slot), slot_ptr(r, g.d_slot)));
         if (!by_note) ps.kind = d->last_gemm_tc ? "gemm_tc" : "gemm_simt";
@@ -1298,6 +1338,7 @@ static void specialise_check_steps(const std::vector<Step>& steps, std::string& 
       }
       continue;
     }
+    if (st.prog.wide) continue;  // f64 programs run on the interpreter kernels only
     std::vector<const char*> families;
     int code = -1;
     if (st.kind == StepK::Map) families = {"k_map_linear<rx::SpecChain>", "k_map_rows<rx::SpecChain, 2>", "k_map_generic<rx::SpecChain, true>"};

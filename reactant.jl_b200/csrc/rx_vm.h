@@ -155,6 +155,7 @@ constexpr int kVmMaxRegs = 24;
 constexpr int kVmMaxLeaves = 8;
 constexpr int kVmMaxOuts = 4;
 constexpr int kMaxRank = 4;
+constexpr int kVmMaxWideConsts = 8;
 
 // Known chains with compile-time-fused implementations.
 enum FastId : int32_t {
@@ -200,6 +201,13 @@ struct VmProgram {
   VmLeaf leaf[kVmMaxLeaves];
   VmOut out[kVmMaxOuts];
   VmInstr ins[kVmMaxInstr];
+  // Wide programs: every floating-point value of the chain is an f64 (f32 / bf16 operands are widened when loaded,
+  // f32 results rounded when stored), registers are 64 bits, integers and predicates keep their 32-bit semantics in
+  // the low word.  Constants do not fit an instruction's 32-bit immediate: VM_CONST with c == 1 reads wconst[imm].
+  // Such programs run on the interpreter kernels of rx_wide.cu only.
+  int32_t wide;
+  int32_t n_wconst;
+  uint64_t wconst[kVmMaxWideConsts];
 };
 
 // Arguments of the NVLink mailbox all-reduce when it is fused into the tail of a

@@ -64,12 +64,7 @@ def test_golden_modules_all_plan(rx):
     with open(os.path.join(HERE, "golden", "reactant_fixtures.json")) as f:
         cases = json.load(f)["cases"]
     for c in cases:
-        if c["element_type"] == "f64":
-            with pytest.raises(rx.ReactantError) as e:
-                rx.plan_describe(c["module"])
-            assert "f64" in str(e.value)
-        else:
-            rx.plan_describe(c["module"])
+        rx.plan_describe(c["module"])   # f64 fixtures included: they plan as wide programs (tests/test_f64.py)
 
 
 UNSUPPORTED = {
