@@ -158,3 +158,32 @@ def test_random_fusion_groups(seed):
         if kind == "add":
             tol = tol * n + oracle.reduction_tolerance(max(n, 2)) * scale * n
         np.testing.assert_allclose(got, w, rtol=0, atol=tol, err_msg=text)
+
+
+def to_f64(text, inputs):
+    """The same random program on Float64 arrays (bf16 operands stay bf16 and are widened by their convert)."""
+    t = text.replace("xf32>", "xf64>").replace("tensor<f32>", "tensor<f64>").replace("0xFF800000", "0xFFF0000000000000")
+    ins = [a if a.dtype == rx.bfloat16 else a.astype(np.float64) for a in inputs]
+    return t, ins
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(int(os.environ.get("RX_FUZZ_FIRST", "0")), int(os.environ.get("RX_FUZZ_FIRST", "0")) + int(os.environ.get("RX_FUZZ_CASES", "60"))))
+def test_random_fusion_groups_in_float64(seed):
+    """Wide programs (64-bit registers, the interpreter kernels of rx_wide.cu) against the oracle, which evaluates
+    f64 modules in float64: a few ulp of double per op."""
+    oracle, _ = entry.load_oracle()
+    text, inputs, kinds, scale, n_ops = gen_case(seed)
+    text, inputs = to_f64(text, inputs)
+    want = oracle.run_module(text, inputs)
+    f = rx.compile(text)
+    r = f(*[rx.to_rarray(np.ascontiguousarray(a.T)) for a in inputs])
+    r = r if isinstance(r, tuple) else (r,)
+    outs = [np.ascontiguousarray(np.asarray(t).T) for t in r]
+    for got, w, (kind, n) in zip(outs, want, kinds):
+        assert got.dtype == np.float64
+        w = np.asarray(w, dtype=np.float64).reshape(got.shape)
+        tol = 1e-15 * (n_ops + 4) * scale * 4
+        if kind == "add":
+            tol = tol * n + 1e-15 * scale * n * np.sqrt(max(n, 2))
+        np.testing.assert_allclose(got, w, rtol=0, atol=tol, err_msg=text)
