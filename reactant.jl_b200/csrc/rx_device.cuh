@@ -88,27 +88,6 @@ __host__ __device__ __forceinline__ uint32_t red_identity(int code) {
   }
 }
 
-// tanh as a clamped odd rational function x * P(x^2) / Q(x^2) (degree 13 / 6): no branches, so that the
-// independent elements a thread works on interleave freely.  The published minimax form used by Eigen's and XLA's
-// float tanh; within 4e-7 of the exact value relative to it over the whole range.
-__device__ __forceinline__ float tanh_rational(float x) {
-  x = fminf(fmaxf(x, -7.90531110763549805f), 7.90531110763549805f);  // NaN passes through both
-  const float x2 = x * x;
-  float p = -2.76076847742355e-16f;
-  p = fmaf(p, x2, 2.00018790482477e-13f);
-  p = fmaf(p, x2, -8.60467152213735e-11f);
-  p = fmaf(p, x2, 5.12229709037114e-08f);
-  p = fmaf(p, x2, 1.48572235717979e-05f);
-  p = fmaf(p, x2, 6.37261928875436e-04f);
-  p = fmaf(p, x2, 4.89352455891786e-03f);
-  p = p * x;
-  float q = 1.19825839466702e-06f;
-  q = fmaf(q, x2, 1.18534705686654e-04f);
-  q = fmaf(q, x2, 2.26843463243900e-03f);
-  q = fmaf(q, x2, 4.89352518554385e-03f);
-  return __fdividef(p, q);
-}
-
 // f32 -> bf16, round to nearest even (cvt.rn), as a 16-bit pattern; two at once packed lo | hi << 16
 __device__ __forceinline__ uint16_t bf16_bits(float x) {
   uint16_t r;

@@ -62,11 +62,6 @@ enum VmOp : uint8_t {
 // Names available to an expression: ua / a / ia = the accumulator as raw bits / f32 / i32,
 // ub / b / ib = the register operand, imm / fimm = the immediate as raw bits / f32,
 // cdir = comparison direction.
-#ifdef RX_TANH_RATIONAL
-#define RX_TANH tanh_rational
-#else
-#define RX_TANH tanhf
-#endif
 #define RX_VM_UNARY_OPS(X)                                                                     \
   X(VM_CONST, imm)                                                                             \
   X(VM_MOV, ua)                                                                                \
@@ -75,7 +70,7 @@ enum VmOp : uint8_t {
   X(VM_COS, f2u(cosf(a)))                                                                      \
   X(VM_EXP, f2u(expf(a)))                                                                      \
   X(VM_LOG, f2u(logf(a)))                                                                      \
-  X(VM_TANH, f2u(RX_TANH(a)))                                                                  \
+  X(VM_TANH, f2u(tanhf(a)))                                                                    \
   X(VM_SQRT, f2u(sqrtf(a)))                                                                    \
   X(VM_RSQRT, f2u(1.0f / sqrtf(a)))                                                            \
   X(VM_ABS, f2u(fabsf(a)))                                                                     \
