@@ -394,6 +394,7 @@ WORKLOADS.update({
     "prof_sinsum_2p27": lambda rx, c, d: setup_sinsum(rx, c, d, 1 << 27, seeds=(1, 2)),
     "prof_logsumexp_32768x2048": lambda rx, c, d: setup_logsumexp(rx, c, d, 32768, 2048),
     "prof_jacobi2d_8192_4": lambda rx, c, d: setup_jacobi(rx, c, d, 8192, 4),
+    "prof_jacobi2d_8192_12": lambda rx, c, d: setup_jacobi(rx, c, d, 8192, 12),
 })
 SMALL_INPUT = {"c1_sinsum_2p24", "c4_mlp_grad_bf16"}  # working set near or below the 126 MB L2: rotate input copies
 EXTRA_CONFIGS = ["c1_sinsum_2p24", "c2_logsumexp_32768x8192", "c3_jacobi2d_8192_100", "c3_jacobi2d_8192_50_halfsteps", "c4_mlp_grad_bf16"]
@@ -407,8 +408,18 @@ TRAFFIC_RATIO = {
     "reduce_full": (1.073795e9 + 3.84e6) / (8 * (1 << 27)),
     "logsumexp": (268.457728e6 + 3.685e6) / (4 * 32768 * 2048 + 12 * 2048),
     "stencil_tma": (269.39392e6 + 219.197184e6) / (4 * 8192 * 8192 + 4 * 8190 * 8190),
-    "stencil_tma_loop": (0.930697e9 + 1.023089e9) / 4 / (4 * 8192 * 8192 + 4 * 8190 * 8190),
 }
+
+
+def stencil_loop_traffic(n, sweeps):
+    """DRAM bytes of one whole-loop launch over n x n arrays.  The loop kernel does two sweeps per pass over memory
+    for all but its last two (three, for an odd count) sweeps.  Per pass, from profiler captures of 4 and 12 sweeps at
+    n = 8192 (1481.3 MB and 3445.9 MB: 1 resp. 5 double passes + 2 single sweeps): 491.2 MB per double pass, 495.0 MB per
+    single sweep (less than the arrays' 536.7 MB because a sweep starts on what the previous one left in L2); both grow
+    with the number of points."""
+    tail = min(sweeps, 2 + sweeps % 2) if sweeps >= 4 else sweeps
+    double = (sweeps - tail) // 2
+    return (double * 491.2e6 + tail * 495.0e6) * (n * n) / (8192.0 * 8192.0)
 
 
 def work_per_step(wl):
@@ -575,6 +586,8 @@ def roofline_of(wl, prof, ms, steps, launches, world, dist, peaks):
     traffic = None
     if kind in TRAFFIC_RATIO:
         traffic = TRAFFIC_RATIO[kind] * per_launch_work / world  # bytes per launch on one GPU
+    elif kind == "stencil_tma_loop" and world == 1:
+        traffic = stencil_loop_traffic(wl["shape"]["n"], wl["shape"]["sweeps"])
     return {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": wl["unit"], "frac": achieved / peak, "traffic": traffic,
             "kernel": kernel, "peak_source": f"of {peaks['source']}" + (f" x{world} GPUs" if world > 1 else ""),
             "ms_per_launch": per_launch_ms, "timed_by": timed}
@@ -653,7 +666,7 @@ def main():
                 w, r = measure(rx, client, dist, name, k, 3, peaks)
                 roof = r["roofline"]
                 configs[name] = {"value": r["value"], "unit": w["unit"], "ms_per_step": r["ms"] / k, "steps": k, "warmup": 3, "gpu_launches": r["launches"],
-                                 "roofline": {q: roof[q] for q in ("bound", "achieved", "peak", "frac", "kernel", "ms_per_launch", "peak_source")} if roof else None,
+                                 "roofline": {q: roof[q] for q in ("bound", "achieved", "peak", "frac", "traffic", "kernel", "ms_per_launch", "peak_source")} if roof else None,
                                  "parity": r["parity"], "config": config_of(name, w, 1), "profile_ms": r["prof"]}
                 ok = ok and (r["parity"] is None or r["parity"]["ok"])
                 del w, r

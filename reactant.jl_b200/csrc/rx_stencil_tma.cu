@@ -173,6 +173,131 @@ __global__ void __launch_bounds__(256) k_stencil_tma(const __grid_constant__ CUt
   }
 }
 
+// ---- two sweeps per pass over memory (temporal blocking) ----------------------------------------------------
+// A Jacobi-style loop alternates between two arrays: sweep s reads X[s % 2] and writes the update window of
+// X[(s + 1) % 2]; outside the window each array keeps its own values for ever.  Two consecutive sweeps can therefore
+// be done on one tile while it is on chip: load the tile of state s with a halo of two (one bulk copy), compute
+// state s + 1 on the tile plus a halo of one into shared memory -- taking the points outside the window from the
+// other array, whose values there never change -- then state s + 2 on the tile itself, and store only that.  Every
+// point is computed by the same operations in the same order as in two separate sweeps, so the result is the same
+// bits; the arrays cross HBM once per two sweeps instead of twice (plus 7 % redundant work on the halos).
+// State s + 2 belongs in the array state s sits in, which other CTAs are still reading: the fused passes ping-pong
+// between that array and a scratch array with the same border, and the last two (three, for an odd count) sweeps of
+// the loop run one at a time, so that both carried arrays end with exactly the contents the unfused loop leaves.
+struct FuseParams {
+  int n_fused;              // fused double sweeps before the remaining single sweeps (0: none)
+  float* buf[2];            // [0]: the array the first sweep reads; [1]: scratch array of the same shape and border
+  const float* other;       // the other carried array
+  long long ld, rows_total;
+  long long r0, r1, c0, c1; // update window [r0, r1) x [c0, c1), the same for both directions
+  int order;                // in which order the five values of the cross are added (cross_sum)
+  int xs;                   // columns skipped at the left of a box so that the copy starts on a 16-byte boundary
+  int tw2, tiles_x2, tiles_y2;
+  float k;
+  int* status;
+  long long extent;         // bounds-checked builds
+  int* bounds;
+};
+struct alignas(64) FuseMaps { CUtensorMap m[3]; };  // buf[0] and buf[1] with (TH + 4)-row boxes; buf[1] with the single-sweep box
+
+// the five values of a radius-1 cross, added in the order the traced program adds them
+//   ORDER 0: centre, left, right, up, down      (the swap spelling, and the pad / concatenate spellings)
+//   ORDER 1: centre, up, down, right, left      (benchmark/polybench/stencil.jl:263-289 after the layout fold)
+template <int ORDER>
+__device__ __forceinline__ float cross_sum(float c, float l, float r, float u, float d) {
+  if (ORDER == 0) return __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(c, l), r), u), d);
+  return __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(c, u), d), r), l);
+}
+
+template <int TH, int ORDER>
+__device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const FuseParams& f, float* dst, float* const* tile, float* mid, uint64_t* bars, int& it,
+                                               bool reverse, int cta, int ncta) {
+  constexpr int BH = TH + 4;
+  const uint32_t bytes = (uint32_t)(BOX_W * BH * sizeof(float));
+  const int ntiles = f.tiles_x2 * f.tiles_y2;
+  const float k = f.k;
+  auto issue = [&](int t, int s) {
+    if (reverse) t = ntiles - 1 - t;
+    const int ty = t / f.tiles_x2, tx = t - ty * f.tiles_x2;
+    mbar_expect_tx(&bars[s], bytes);
+    // the box starts two points up and to the left of the tile (minus the alignment columns); negative coordinates
+    // read the fill value, which is never used: those positions come from the other array
+    tma_load_2d(tile[s], tmap, (int)(f.c0 + (long long)tx * f.tw2 - 2 - f.xs), (int)(f.r0 + (long long)ty * TH - 2), &bars[s]);
+  };
+  if (threadIdx.x == 0)
+    for (int q = 0; q < STAGES - 1; ++q)
+      if (cta + q * ncta < ntiles) issue(cta + q * ncta, (it + q) % STAGES);
+  for (int t = cta; t < ntiles; t += ncta, ++it) {
+    const int s = it % STAGES;
+    const uint32_t parity = (it / STAGES) & 1;
+    const int next = t + (STAGES - 1) * ncta;
+    if (threadIdx.x == 0 && next < ntiles) issue(next, (it + STAGES - 1) % STAGES);
+    if (!mbar_wait(&bars[s], parity, kWaitLimit)) return false;
+    const int tt = reverse ? ntiles - 1 - t : t;
+    const int ty = tt / f.tiles_x2, tx = tt - ty * f.tiles_x2;
+    const long long Y0 = f.r0 + (long long)ty * TH, X0 = f.c0 + (long long)tx * f.tw2;  // first point of the tile
+    const float* sm = tile[s];
+    // state s + 1 on the tile and a halo of one: thread x' owns a column of the intermediate tile, rows
+    // [lo, hi) of it lie inside the update window (computed, with a three-row window sliding down the column), the
+    // rest is the other array's own
+    {
+      const int xp = threadIdx.x;
+      const long long X = X0 - 1 + xp;
+      if (xp < f.tw2 + 2) {
+        const bool col_in = X >= f.c0 && X < f.c1, col_ok = X >= 0 && X < f.ld;
+        const int lo = col_in ? (int)max(0ll, f.r0 - (Y0 - 1)) : TH + 2;
+        const int hi = col_in ? (int)min((long long)(TH + 2), f.r1 - (Y0 - 1)) : TH + 2;
+        const float* other = f.other + (Y0 - 1) * f.ld + X;
+        for (int yp = 0; yp < min(lo, TH + 2); ++yp) {
+          const long long Y = Y0 - 1 + yp;
+          mid[yp * BOX_W + xp] = (col_ok && Y >= 0 && Y < f.rows_total) ? __ldg(other + (long long)yp * f.ld) : 0.f;
+        }
+        if (lo < hi) {
+          const float* q = sm + (lo + 1) * BOX_W + (f.xs + xp + 1);  // the point itself in the source box
+          float up = q[-BOX_W], c = q[0];
+#pragma unroll 4
+          for (int yp = lo; yp < hi; ++yp) {
+            const float l = q[-1], r = q[1], dn = q[BOX_W];
+            mid[yp * BOX_W + xp] = __fmul_rn(k, cross_sum<ORDER>(c, l, r, up, dn));
+            up = c;
+            c = dn;
+            q += BOX_W;
+          }
+        }
+        for (int yp = max(hi, 0); yp < TH + 2; ++yp) {
+          const long long Y = Y0 - 1 + yp;
+          mid[yp * BOX_W + xp] = (col_ok && Y >= 0 && Y < f.rows_total) ? __ldg(other + (long long)yp * f.ld) : 0.f;
+        }
+      }
+    }
+    __syncthreads();
+    // state s + 2 on the tile
+    {
+      const int cx = threadIdx.x;
+      const long long X = X0 + cx;
+      if (cx < f.tw2 && X < f.c1) {
+        int rmax = (int)min((long long)TH, f.r1 - Y0);
+#if RX_BOUNDS
+        if (rmax > 0 && !(rx_in_bounds(f.bounds, f.extent, Y0 * f.ld + X, 1, 299) && rx_in_bounds(f.bounds, f.extent, (Y0 + rmax - 1) * f.ld + X, 1, 299))) rmax = 0;
+#endif
+        float* out = dst + Y0 * f.ld + X;
+        const float* q = mid + BOX_W + (cx + 1);
+        float up = q[-BOX_W], c = q[0];
+#pragma unroll 4
+        for (int r = 0; r < rmax; ++r) {
+          const float l = q[-1], rr = q[1], dn = q[BOX_W];
+          out[(long long)r * f.ld] = __fmul_rn(k, cross_sum<ORDER>(c, l, rr, up, dn));
+          up = c;
+          c = dn;
+          q += BOX_W;
+        }
+      }
+    }
+    __syncthreads();  // stage s and the intermediate tile are free again
+  }
+  return true;
+}
+
 // ---- whole counted loop in one launch ------------------------------------------------------------------
 // A `stablehlo.while` whose body is nothing but 5-point stencil updates (Jacobi: A -> B, B -> A, ...) runs as ONE
 // cooperative launch: every CTA keeps its tile list and its shared-memory ring, sweeps follow each other
@@ -190,6 +315,7 @@ struct LoopParams {
   int total;          // sweeps to run = loop trip count x stencil steps per iteration
   int alternate;      // odd sweeps walk the tiles backwards
   unsigned* counter;  // zero at launch
+  FuseParams fuse;    // double sweeps that come first (n_fused = 0: none); `total` then counts the single sweeps after them
   // Row-sharded arrays (the device owns a block of rows of each array and keeps copies of its neighbours' boundary
   // rows): between two sweeps CTA 0 exchanges the boundary rows of the array just written with the neighbouring
   // devices, and the other CTAs are released into the next sweep only when the received rows are in place.
@@ -203,14 +329,17 @@ struct LoopParams {
 };
 
 template <int TH>
-__global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ PhaseMaps maps, const __grid_constant__ LoopParams lp) {
+__global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ PhaseMaps maps, const __grid_constant__ LoopParams lp, const __grid_constant__ FuseMaps fm) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[STAGES];
   float* tile[STAGES];
-  const int stage_floats = BOX_W * lp.ph[0].box_h;  // all phases share the ring geometry
+  // all phases share the ring geometry; with double sweeps the stages hold their taller boxes and a third region
+  // the intermediate tile
+  const int stage_floats = BOX_W * (lp.fuse.n_fused > 0 ? TH + 4 : lp.ph[0].box_h);
   uintptr_t base = ((uintptr_t)smem_raw + 127) & ~(uintptr_t)127;
 #pragma unroll
   for (int s = 0; s < STAGES; ++s) tile[s] = (float*)base + (size_t)s * stage_floats;
+  float* mid = (float*)base + (size_t)STAGES * stage_floats;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
     mbar_fence_init();
@@ -261,22 +390,16 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
   const int cta = lp.halo ? (int)blockIdx.x - 1 : (int)blockIdx.x;
   const int ncta = lp.halo ? (int)gridDim.x - 1 : (int)gridDim.x;
   int it = 0;
-  for (int sweep = 0; sweep < lp.total; ++sweep) {
-    const int ph = sweep % lp.n_phases;
-    if (!stencil_sweep<true, TH>(&maps.m[ph], lp.ph[ph], nullptr, lp.k[ph], tile, bars, it, lp.alternate && (sweep & 1), cta, ncta, lp.halo != 0, lp.edge)) {
-      if (threadIdx.x == 0) *lp.ph[0].status = 2;
-      stencil_drain(bars);
-      return;
-    }
-    if (sweep + 1 == lp.total) break;
-    // grid-wide barrier between sweeps (over the worker CTAs); with an exchange, its rows must be in place too
+  int epoch = 0;  // grid barriers passed
+  // grid-wide barrier between sweeps (over the worker CTAs); with an exchange, its rows must be in place too
+  auto sweep_barrier = [&]() -> bool {
     __syncthreads();
     int ok = 1;
     if (threadIdx.x == 0) {
       __threadfence();
       asm volatile("fence.proxy.async;" ::: "memory");
       atomicAdd(lp.counter, 1u);
-      const unsigned target = (unsigned)(sweep + 1) * (unsigned)ncta;
+      const unsigned target = (unsigned)(epoch + 1) * (unsigned)ncta;
       long long spins = 0;
       for (;;) {
         unsigned v;
@@ -290,7 +413,7 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
           unsigned v;
           asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(lp.release) : "memory");
           if (v == 0xFFFFFFFFu) { ok = -1; break; }  // the exchange CTA gave up and has reported why
-          if (v >= (unsigned)(sweep + 1)) break;
+          if (v >= (unsigned)(epoch + 1)) break;
           if (++spins > kWaitLimit + lp.hx.poll_limit) { ok = 0; break; }
           if (spins > 64) __nanosleep(100);
         }
@@ -299,7 +422,31 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
       if (ok == 0) *lp.ph[0].status = 3;
     }
     ok = __syncthreads_and(ok == 1);
-    if (!ok) return;  // nothing of this CTA is in flight: the sweep above drained its ring
+    ++epoch;
+    return ok != 0;  // false: nothing of this CTA is in flight (the sweep before drained its ring)
+  };
+  // double sweeps first: state 2q -> state 2q + 2, ping-ponging between the first array and the scratch array
+  for (int q = 0; q < lp.fuse.n_fused; ++q) {
+    const bool done = lp.fuse.order == 0 ? stencil_sweep2<TH, 0>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta)
+                                         : stencil_sweep2<TH, 1>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta);
+    if (!done) {
+      if (threadIdx.x == 0) *lp.ph[0].status = 2;
+      stencil_drain(bars);
+      return;
+    }
+    if (!sweep_barrier()) return;
+  }
+  for (int sweep = 0; sweep < lp.total; ++sweep) {
+    const int ph = sweep % lp.n_phases;
+    // after an odd number of double sweeps the current state sits in the scratch array: the first single sweep reads it there
+    const CUtensorMap* src_map = (sweep == 0 && (lp.fuse.n_fused & 1)) ? &fm.m[2] : &maps.m[ph];
+    if (!stencil_sweep<true, TH>(src_map, lp.ph[ph], nullptr, lp.k[ph], tile, bars, it, lp.alternate && ((sweep + lp.fuse.n_fused) & 1), cta, ncta, lp.halo != 0, lp.edge)) {
+      if (threadIdx.x == 0) *lp.ph[0].status = 2;
+      stencil_drain(bars);
+      return;
+    }
+    if (sweep + 1 == lp.total) break;
+    if (!sweep_barrier()) return;
   }
 }
 
@@ -314,6 +461,18 @@ struct Prepared {
   bool fast = false;
   bool empty = false;
 };
+
+// Tensor map over a dense [rows][ld] f32 array with boxes of BOX_W x box_h.
+bool make_array_map(const float* base, int64_t ld, int64_t rows, int box_h, CUtensorMap* out) {
+  EncodeTiledFn enc = tma_encode_fn();
+  if (!enc) return false;
+  cuuint64_t gdim[2] = {(cuuint64_t)ld, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)ld * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)BOX_W, (cuuint32_t)box_h};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 // Tile geometry, tensor map and parameters of one stencil step; false = this path declines the step.
 bool prepare_stencil(RxDevice* d, const Step& st, const VmProgram& P, Prepared* out) {
@@ -465,6 +624,80 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
     for (int i = 0; i < n; ++i) lp.halo_block[i] = halo->block[i];
     lp.halo_epoch0 = halo->epoch0;
   }
+  // ---- two sweeps per pass over memory, when the loop simply alternates between two arrays -----------------------
+  FuseMaps fmaps{};
+  float* scratch_array = nullptr;
+  size_t scratch_bytes = 0;
+  const bool fuse_off = getenv("RX_STENCIL_FUSE2") && atoi(getenv("RX_STENCIL_FUSE2")) == 0;  // read per call
+  if (!halo && !fuse_off && n == 2 && total >= 4) {
+    const Step &s0 = *steps[0], &s1 = *steps[1];
+    const VmProgram &p0 = bound[0], &p1 = bound[1];
+    const float* x0 = (const float*)p0.leaf[0].ptr;
+    const float* x1 = (const float*)p1.leaf[0].ptr;
+    const int64_t ld = s0.st_src_ld;
+    bool same = x0 != x1 && p0.out[0].ptr == (void*)x1 && p1.out[0].ptr == (void*)x0 && s0.st_dst_ld == ld && s1.st_src_ld == ld && s1.st_dst_ld == ld &&
+                s0.st_src_off == s1.st_src_off && s0.st_dst_off == s1.st_dst_off && s0.st_rows == s1.st_rows && s0.st_cols == s1.st_cols && s0.st_dy == s1.st_dy &&
+                s0.st_dx == s1.st_dx && p0.fast_c == p1.fast_c && s0.st_dy.size() == 5 && p0.leaf[0].extent == p1.leaf[0].extent && p0.leaf[0].extent % ld == 0;
+    const int64_t rows_total = same ? p0.leaf[0].extent / ld : 0;
+    const int64_t r0 = s0.st_dst_off / ld, c0 = s0.st_dst_off % ld, row0 = s0.st_src_off / ld, col0 = s0.st_src_off % ld;
+    FuseParams f{};
+    if (same) {
+      // tap offsets relative to the updated point, in evaluation order: (dy, dx)
+      int oy[5], ox[5];
+      for (int k = 0; k < 5; ++k) {
+        oy[k] = (int)(row0 + s0.st_dy[k] - r0);
+        ox[k] = (int)(col0 + s0.st_dx[k] - c0);
+      }
+      auto is = [&](int k, int y, int x) { return oy[k] == y && ox[k] == x; };
+      if (is(0, 0, 0) && is(1, 0, -1) && is(2, 0, 1) && is(3, -1, 0) && is(4, 1, 0)) f.order = 0;
+      else if (is(0, 0, 0) && is(1, -1, 0) && is(2, 1, 0) && is(3, 0, 1) && is(4, 0, -1)) f.order = 1;
+      else same = false;
+    }
+    // the window must leave room for the taps inside the array, and box starts must fall on 16-byte boundaries
+    same = same && r0 >= 1 && c0 >= 1 && r0 + s0.st_rows + 1 <= rows_total && c0 + s0.st_cols + 1 <= ld && rows_total >= 4;
+    if (same) {
+      const int tail = 2 + (int)(total & 1);
+      f.n_fused = (int)((total - tail) / 2);
+      f.xs = (int)(((c0 - 2) % 4 + 4) % 4);
+      f.tw2 = (BOX_W - 4 - f.xs) & ~3;
+      f.tiles_x2 = (int)((s0.st_cols + f.tw2 - 1) / f.tw2);
+      f.tiles_y2 = (int)((s0.st_rows + 32 - 1) / 32);
+      f.ld = ld;
+      f.rows_total = rows_total;
+      f.r0 = r0;
+      f.r1 = r0 + s0.st_rows;
+      f.c0 = c0;
+      f.c1 = c0 + s0.st_cols;
+      f.k = p0.fast_c;
+      f.status = lp.ph[0].status;
+      f.other = x1;
+      f.extent = p0.leaf[0].extent;
+      f.bounds = p0.out[0].bounds;
+      scratch_bytes = (size_t)p0.leaf[0].extent * sizeof(float);
+      if (f.n_fused >= 1 && !dry_run) {
+        scratch_array = (float*)d->alloc(scratch_bytes);
+        f.buf[0] = const_cast<float*>(x0);
+        f.buf[1] = scratch_array;
+        if (!make_array_map(x0, ld, rows_total, 32 + 4, &fmaps.m[0]) || !make_array_map(scratch_array, ld, rows_total, 32 + 4, &fmaps.m[1]) ||
+            !make_array_map(scratch_array, ld, rows_total, lp.ph[0].box_h, &fmaps.m[2])) {
+          d->release(scratch_array, scratch_bytes);
+          scratch_array = nullptr;
+          f.n_fused = 0;
+        }
+      }
+      if (f.n_fused >= 1) {
+        lp.fuse = f;
+        lp.total = tail;
+        smem = (size_t)STAGES * BOX_W * (32 + 4) * sizeof(float) + (size_t)BOX_W * (32 + 2) * sizeof(float) + 128;
+      }
+    }
+  }
+  struct ScratchGuard {  // the pool hands the block out again in stream order, so it can go back right after the launch
+    RxDevice* d;
+    float*& p;
+    size_t bytes;
+    ~ScratchGuard() { if (p) d->release(p, bytes); }
+  } scratch_guard{d, scratch_array, scratch_bytes};
   auto kern = k_stencil_loop<32>;
   static size_t attr_set[64] = {};
   static int resident[64] = {};
@@ -485,6 +718,7 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
   }
   int ntiles = 0;
   for (int i = 0; i < n; ++i) ntiles = std::max(ntiles, lp.ph[i].tiles_x * lp.ph[i].tiles_y);
+  if (lp.fuse.n_fused > 0) ntiles = std::max(ntiles, lp.fuse.tiles_x2 * lp.fuse.tiles_y2);
   int grid = std::min(ntiles, d->sm_count * std::min(occ, 2));
   if (halo) {
     // one more CTA, which only exchanges; every sweep must count the same number of edge tiles
@@ -499,7 +733,24 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
   }
   cudaError_t e = cudaMemsetAsync(lp.edge, 0, 3 * sizeof(unsigned), d->stream);
   if (e != cudaSuccess) return e;
-  void* args[] = {(void*)&maps, (void*)&lp};
+  if (lp.fuse.n_fused > 0) {
+    // the scratch array needs the first array's values outside the update window (they are never written): the rows
+    // above and below it, and the columns left and right of it
+    const FuseParams& f = lp.fuse;
+    const size_t pitch = (size_t)f.ld * sizeof(float);
+    const float* x0 = f.buf[0];
+    float* z = f.buf[1];
+    if (f.r0 > 0) e = cudaMemcpyAsync(z, x0, (size_t)f.r0 * pitch, cudaMemcpyDeviceToDevice, d->stream);
+    if (e == cudaSuccess && f.r1 < f.rows_total)
+      e = cudaMemcpyAsync(z + f.r1 * f.ld, x0 + f.r1 * f.ld, (size_t)(f.rows_total - f.r1) * pitch, cudaMemcpyDeviceToDevice, d->stream);
+    if (e == cudaSuccess && f.c0 > 0)
+      e = cudaMemcpy2DAsync(z + f.r0 * f.ld, pitch, x0 + f.r0 * f.ld, pitch, (size_t)f.c0 * sizeof(float), (size_t)(f.r1 - f.r0), cudaMemcpyDeviceToDevice, d->stream);
+    if (e == cudaSuccess && f.c1 < f.ld)
+      e = cudaMemcpy2DAsync(z + f.r0 * f.ld + f.c1, pitch, x0 + f.r0 * f.ld + f.c1, pitch, (size_t)(f.ld - f.c1) * sizeof(float), (size_t)(f.r1 - f.r0), cudaMemcpyDeviceToDevice,
+                            d->stream);
+    if (e != cudaSuccess) return e;
+  }
+  void* args[] = {(void*)&maps, (void*)&lp, (void*)&fmaps};
   e = cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(256), args, smem, d->stream);
   if (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorNotSupported) {
     cudaGetLastError();

@@ -180,12 +180,14 @@ def test_jacobi2d_bit_exact(rx, ref, client, n, steps, form):
     assert np.array_equal(ga, wa) and np.array_equal(gb, wb)
 
 
-@pytest.mark.parametrize("steps", [2, 3, 7])
-def test_counted_stencil_loop_is_one_launch_and_bit_exact(rx, ref, client, steps):
+@pytest.mark.parametrize("n", [1028, 516, 2052])
+@pytest.mark.parametrize("steps", [2, 3, 4, 5, 7, 12])
+def test_counted_stencil_loop_is_one_launch_and_bit_exact(rx, ref, client, steps, n):
     """A loop whose body is only 5-point updates runs as one cooperative launch with grid barriers between the
-    sweeps; an odd trip count leaves the arrays swapped exactly as sweep-by-sweep execution does.  (The row pitch
-    must be a multiple of 16 bytes for the TMA path; other sizes run the strided map kernel sweep by sweep.)"""
-    n = 1028
+    sweeps; an odd trip count leaves the arrays swapped exactly as sweep-by-sweep execution does.  From four sweeps
+    on, all but the last two (three, for an odd count) are done two per pass over memory, through a scratch array:
+    same bits, and both carried arrays end with what the one-sweep-at-a-time loop leaves.  (The row pitch must be a
+    multiple of 16 bytes for the TMA path; other sizes run the strided map kernel sweep by sweep.)"""
     rng = np.random.default_rng(steps)
     a = rng.random((n, n), dtype=np.float32)
     b = rng.random((n, n), dtype=np.float32)
@@ -199,6 +201,28 @@ def test_counted_stencil_loop_is_one_launch_and_bit_exact(rx, ref, client, steps
     ga, gb = [np.asarray(o).T for o in out]
     wa, wb = ref.run_module(text, [a, b])
     assert np.array_equal(ga, wa) and np.array_equal(gb, wb)
+
+
+@pytest.mark.parametrize("steps", [1, 2, 3, 6])
+def test_two_half_step_loop_is_one_launch_and_bit_exact(rx, ref, client, steps, monkeypatch):
+    """The reference's own spelling (two updates per iteration, no swap; a different order of the additions): also one
+    launch, also two sweeps per pass from four sweeps on, and the same bits with that turned off."""
+    n = 1028
+    rng = np.random.default_rng(steps)
+    a = rng.random((n, n), dtype=np.float32)
+    b = rng.random((n, n), dtype=np.float32)
+    text = rx.programs.jacobi2d(n, steps, form="halfsteps")
+    dev = client.addressable_devices[0]
+    f = rx.compile(text, client)
+    before = dev.kernel_launches()
+    out = f(rx.to_rarray(a.T, client), rx.to_rarray(b.T, client))
+    assert dev.kernel_launches() - before == (1 if steps >= 2 else 2)   # a single iteration is not worth a cooperative launch
+    ga, gb = [np.asarray(o).T for o in out]
+    wa, wb = ref.run_module(text, [a, b])
+    assert np.array_equal(ga, wa) and np.array_equal(gb, wb)
+    monkeypatch.setenv("RX_STENCIL_FUSE2", "0")
+    out = f(rx.to_rarray(a.T, client), rx.to_rarray(b.T, client))
+    assert all(np.array_equal(np.asarray(o).T, w) for o, w in zip(out, (wa, wb)))
 
 
 def test_jacobi2d_full_size_against_c_oracle(rx, cpu, client):
