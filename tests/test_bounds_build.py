@@ -49,9 +49,9 @@ try:
     want = ref.run_module(text, [ref.julia_to_xla(a)])[0].T
     np.testing.assert_allclose(got, want, rtol=1e-5)
     # stencil: TMA path (row pitch a multiple of 16 bytes) and the strided map path
-    for n in (36, 33):
+    for n, sweeps in ((36, 3), (33, 3), (516, 7)):   # the last one runs two sweeps per pass over memory
         A = rng.random((n, n), dtype=np.float32); B = rng.random((n, n), dtype=np.float32)
-        text = rx.programs.jacobi2d(n, 3)
+        text = rx.programs.jacobi2d(n, sweeps)
         ga, gb = run(text, [A, B]); wa, wb = ref.run_module(text, [A, B])
         assert np.array_equal(ga, wa) and np.array_equal(gb, wb)
     # GEMM with a fused epilogue (direct operand loads, staged and direct stores, column sums)
