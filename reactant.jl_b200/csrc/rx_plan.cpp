@@ -2475,6 +2475,8 @@ struct Planner {
         up = std::max<int>(up, (int)(drow0 - row0));
         down = std::max<int>(down, (int)(row0 + max_dy - drow0));
       }
+      // a radius-1 loop gets two halo rows on each side, so that the executor may do two sweeps per pass over memory
+      if (up == 1 && down == 1 && rows / saved_parts >= 2) up = down = 2;
       if (up < 0 || down < 0 || up > 2 || down > 2 || rows % saved_parts != 0 || rows / saved_parts < std::max(up, down) || rows / saved_parts < 1)
         throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.while carrying sharded tensors: halo of more than 2 rows, or row blocks smaller than the halo");
       for (int s : loop.state_slots) {

@@ -601,6 +601,7 @@ bool try_row_sharded_stencil_loop(RxExecutable* ex, const Step& loop, std::vecto
   };
   std::vector<PerDev> per(runs.size());
   const int64_t total = loop.trip * (int64_t)loop.body.size();
+  int passes = 0;
   for (size_t k = 0; k < runs.size(); ++k) {
     DevRun& r = runs[k];
     PerDev& pd = per[k];
@@ -625,11 +626,21 @@ bool try_row_sharded_stencil_loop(RxExecutable* ex, const Step& loop, std::vecto
     if (!ok || !pd.period) return false;
     for (const Step& s : pd.local) pd.steps.push_back(&s);
     rx::halo_fill_args(ex->client, r.dev, rows_local, cols, blk0.halo_up, blk0.halo_down, &pd.halo.args);
+    {
+      // does the update window continue into the rows above / below this device's?
+      const Step& b0 = loop.body[0];
+      const int64_t ld = b0.st_src_ld, drow0 = b0.st_dst_off / ld, g = r.dev->global_id;
+      pd.halo.window_above = g * rows_local > drow0;
+      pd.halo.window_below = (g + 1) * rows_local < drow0 + b0.st_rows;
+    }
     bool would = false;
-    CK(rx::run_stencil_loop(r.dev, pd.steps, pd.bound, total, &would, &pd.halo, true));
+    int dev_passes = 0;
+    CK(rx::run_stencil_loop(r.dev, pd.steps, pd.bound, total, &would, &pd.halo, true, &dev_passes));
     if (!would) return false;
+    if (k == 0) passes = dev_passes;
+    else if (dev_passes != passes) return false;  // the devices must run the same sequence of passes
   }
-  const unsigned epoch0 = rx::halo_reserve_epochs(ex->client, (unsigned)(total - 1));
+  const unsigned epoch0 = rx::halo_reserve_epochs(ex->client, (unsigned)(passes - 1));
   for (size_t k = 0; k < runs.size(); ++k) {
     DevRun& r = runs[k];
     PerDev& pd = per[k];

@@ -190,6 +190,9 @@ struct FuseParams {
   const float* other;       // the other carried array
   long long ld, rows_total;
   long long r0, r1, c0, c1; // update window [r0, r1) x [c0, c1), the same for both directions
+  long long m0, m1;         // rows on which the intermediate state is computed: [r0, r1), or one more row on a side where a
+                            // row-sharded device's rows border a neighbour's (those rows are the neighbour's to write, but
+                            // their intermediate values are needed here)
   int order;                // in which order the five values of the cross are added (cross_sum)
   int xs;                   // columns skipped at the left of a box so that the copy starts on a 16-byte boundary
   int tw2, tiles_x2, tiles_y2;
@@ -211,13 +214,21 @@ __device__ __forceinline__ float cross_sum(float c, float l, float r, float u, f
 
 template <int TH, int ORDER>
 __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const FuseParams& f, float* dst, float* const* tile, float* mid, uint64_t* bars, int& it,
-                                               bool reverse, int cta, int ncta) {
+                                               bool reverse, int cta, int ncta, bool edge_rows = false, unsigned* edge_counter = nullptr) {
   constexpr int BH = TH + 4;
   const uint32_t bytes = (uint32_t)(BOX_W * BH * sizeof(float));
   const int ntiles = f.tiles_x2 * f.tiles_y2;
   const float k = f.k;
+  const int n_edge = edge_rows ? (f.tiles_y2 >= 2 ? 2 : 1) * f.tiles_x2 : 0;
+  // position in this pass's order -> tile (first and last tile row first when the rows are traded with neighbours)
+  auto tile_of = [&](int t) {
+    if (t < n_edge) return t < f.tiles_x2 ? t : (f.tiles_y2 - 1) * f.tiles_x2 + (t - f.tiles_x2);
+    if (!edge_rows) return reverse ? ntiles - 1 - t : t;
+    const int u = t - n_edge, n_int = ntiles - n_edge;
+    return f.tiles_x2 + (reverse ? n_int - 1 - u : u);
+  };
   auto issue = [&](int t, int s) {
-    if (reverse) t = ntiles - 1 - t;
+    t = tile_of(t);
     const int ty = t / f.tiles_x2, tx = t - ty * f.tiles_x2;
     mbar_expect_tx(&bars[s], bytes);
     // the box starts two points up and to the left of the tile (minus the alignment columns); negative coordinates
@@ -233,7 +244,7 @@ __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const Fu
     const int next = t + (STAGES - 1) * ncta;
     if (threadIdx.x == 0 && next < ntiles) issue(next, (it + STAGES - 1) % STAGES);
     if (!mbar_wait(&bars[s], parity, kWaitLimit)) return false;
-    const int tt = reverse ? ntiles - 1 - t : t;
+    const int tt = tile_of(t);
     const int ty = tt / f.tiles_x2, tx = tt - ty * f.tiles_x2;
     const long long Y0 = f.r0 + (long long)ty * TH, X0 = f.c0 + (long long)tx * f.tw2;  // first point of the tile
     const float* sm = tile[s];
@@ -245,8 +256,8 @@ __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const Fu
       const long long X = X0 - 1 + xp;
       if (xp < f.tw2 + 2) {
         const bool col_in = X >= f.c0 && X < f.c1, col_ok = X >= 0 && X < f.ld;
-        const int lo = col_in ? (int)max(0ll, f.r0 - (Y0 - 1)) : TH + 2;
-        const int hi = col_in ? (int)min((long long)(TH + 2), f.r1 - (Y0 - 1)) : TH + 2;
+        const int lo = col_in ? (int)max(0ll, f.m0 - (Y0 - 1)) : TH + 2;
+        const int hi = col_in ? (int)min((long long)(TH + 2), f.m1 - (Y0 - 1)) : TH + 2;
         const float* other = f.other + (Y0 - 1) * f.ld + X;
         for (int yp = 0; yp < min(lo, TH + 2); ++yp) {
           const long long Y = Y0 - 1 + yp;
@@ -294,6 +305,10 @@ __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const Fu
       }
     }
     __syncthreads();  // stage s and the intermediate tile are free again
+    if (t < n_edge && threadIdx.x == 0) {
+      __threadfence();  // the tile's rows, written by all threads before the barrier, precede the count
+      atomicAdd(edge_counter, 1u);
+    }
   }
   return true;
 }
@@ -347,21 +362,25 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
   __syncthreads();
 
   if (lp.halo && blockIdx.x == 0) {
-    // The exchange CTA.  As soon as the tiles holding the first and last owned rows of sweep s are written (the
-    // workers take them first), it trades those rows with the neighbouring devices -- while the workers are busy
-    // with the rest of the sweep -- and publishes `release = s + 1`; the workers need that before sweep s + 1.
-    for (int sweep = 0; sweep + 1 < lp.total; ++sweep) {
-      const int ph = sweep % lp.n_phases;
-      const unsigned n_edge = (unsigned)((lp.ph[ph].tiles_y >= 2 ? 2 : 1) * lp.ph[ph].tiles_x);
+    // The exchange CTA.  As soon as the tiles holding the first and last owned rows of a pass (a double sweep or a
+    // single one) are written -- the workers take them first -- it trades those rows with the neighbouring devices
+    // while the workers are busy with the rest of the pass, and publishes `release = pass + 1`, which the workers
+    // need before the next pass.
+    const int n_pass = lp.fuse.n_fused + lp.total;
+    unsigned edge_target = 0;
+    for (int pass = 0; pass + 1 < n_pass; ++pass) {
+      const bool dbl = pass < lp.fuse.n_fused;
+      const int ph = dbl ? 0 : (pass - lp.fuse.n_fused) % lp.n_phases;
+      // the array this pass writes, and how many of its tiles hold rows the neighbours wait for
+      float* block = dbl ? lp.fuse.buf[(pass + 1) & 1] : lp.halo_block[ph];
+      edge_target += dbl ? (unsigned)((lp.fuse.tiles_y2 >= 2 ? 2 : 1) * lp.fuse.tiles_x2) : (unsigned)((lp.ph[ph].tiles_y >= 2 ? 2 : 1) * lp.ph[ph].tiles_x);
       int ok = 1;
       if (threadIdx.x == 0) {
-        // edge tiles are counted per phase geometry; all phases of a loop share it (checked by the launcher)
-        const unsigned target = (unsigned)(sweep + 1) * n_edge;
         long long spins = 0;
         for (;;) {
           unsigned v;
           asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(lp.edge) : "memory");
-          if (v >= target) break;
+          if (v >= edge_target) break;
           if (++spins > kWaitLimit) { ok = 0; break; }
           if (spins > 64) __nanosleep(100);
         }
@@ -370,17 +389,17 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
       bool got = false;
       if (ok) {
         HaloArgs hx = lp.hx;
-        hx.block = lp.halo_block[ph];
-        hx.epoch = lp.halo_epoch0 + (unsigned)sweep;
+        hx.block = block;
+        hx.epoch = lp.halo_epoch0 + (unsigned)pass;
         got = halo_exchange_cta(hx);
       }
       __syncthreads();
       if (threadIdx.x == 0) {
         __threadfence();
-        asm volatile("fence.proxy.async;" ::: "memory");  // the received rows are read by the next sweep's bulk loads
+        asm volatile("fence.proxy.async;" ::: "memory");  // the received rows are read by the next pass's bulk loads
         if (!ok) *lp.ph[0].status = 3;
         else if (!got) *lp.peer_status = 2;  // what the stand-alone exchange kernel reports
-        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(lp.release), "r"(got ? (unsigned)(sweep + 1) : 0xFFFFFFFFu) : "memory");
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(lp.release), "r"(got ? (unsigned)(pass + 1) : 0xFFFFFFFFu) : "memory");
       }
       if (!got) return;
     }
@@ -427,8 +446,9 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
   };
   // double sweeps first: state 2q -> state 2q + 2, ping-ponging between the first array and the scratch array
   for (int q = 0; q < lp.fuse.n_fused; ++q) {
-    const bool done = lp.fuse.order == 0 ? stencil_sweep2<TH, 0>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta)
-                                         : stencil_sweep2<TH, 1>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta);
+    const bool done = lp.fuse.order == 0
+                          ? stencil_sweep2<TH, 0>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta, lp.halo != 0, lp.edge)
+                          : stencil_sweep2<TH, 1>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta, lp.halo != 0, lp.edge);
     if (!done) {
       if (threadIdx.x == 0) *lp.ph[0].status = 2;
       stencil_drain(bars);
@@ -594,8 +614,9 @@ cudaError_t run_stencil_tma(RxDevice* d, const Step& st, const VmProgram& P, boo
 // `total` sweeps cycling through the given stencil steps (already bound to their buffers) in one cooperative
 // launch.  Declines (handled = false) unless every step is the 5-point fast chain on the same tile geometry.
 cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps, const std::vector<VmProgram>& bound, int64_t total, bool* handled,
-                             const StencilLoopHalo* halo, bool dry_run) {
+                             const StencilLoopHalo* halo, bool dry_run, int* passes) {
   *handled = false;
+  if (passes) *passes = (int)total;
   const int n = (int)steps.size();
   if (n < 1 || n > kMaxPhases || total < 2 || total > INT32_MAX) return cudaSuccess;
   PhaseMaps maps{};
@@ -629,7 +650,8 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
   float* scratch_array = nullptr;
   size_t scratch_bytes = 0;
   const bool fuse_off = getenv("RX_STENCIL_FUSE2") && atoi(getenv("RX_STENCIL_FUSE2")) == 0;  // read per call
-  if (!halo && !fuse_off && n == 2 && total >= 4) {
+  // (a row-sharded loop needs two halo rows for it: the planner gives stencil loops of radius 1 that much)
+  if ((!halo || (halo->args.up == 2 && halo->args.down == 2)) && !fuse_off && n == 2 && total >= 4) {
     const Step &s0 = *steps[0], &s1 = *steps[1];
     const VmProgram &p0 = bound[0], &p1 = bound[1];
     const float* x0 = (const float*)p0.leaf[0].ptr;
@@ -666,6 +688,8 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
       f.rows_total = rows_total;
       f.r0 = r0;
       f.r1 = r0 + s0.st_rows;
+      f.m0 = f.r0 - ((halo && halo->window_above) ? 1 : 0);
+      f.m1 = f.r1 + ((halo && halo->window_below) ? 1 : 0);
       f.c0 = c0;
       f.c1 = c0 + s0.st_cols;
       f.k = p0.fast_c;
@@ -682,12 +706,14 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
             !make_array_map(scratch_array, ld, rows_total, lp.ph[0].box_h, &fmaps.m[2])) {
           d->release(scratch_array, scratch_bytes);
           scratch_array = nullptr;
+          if (halo) return cudaErrorUnknown;  // the other devices of the mesh have decided for double sweeps: do not run a different loop here
           f.n_fused = 0;
         }
       }
       if (f.n_fused >= 1) {
         lp.fuse = f;
         lp.total = tail;
+        if (passes) *passes = f.n_fused + tail;
         smem = (size_t)STAGES * BOX_W * (32 + 4) * sizeof(float) + (size_t)BOX_W * (32 + 2) * sizeof(float) + 128;
       }
     }
@@ -740,12 +766,18 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
     const size_t pitch = (size_t)f.ld * sizeof(float);
     const float* x0 = f.buf[0];
     float* z = f.buf[1];
-    if (f.r0 > 0) e = cudaMemcpyAsync(z, x0, (size_t)f.r0 * pitch, cudaMemcpyDeviceToDevice, d->stream);
-    if (e == cudaSuccess && f.r1 < f.rows_total)
+    if (lp.halo) {
+      // a row block: its halo rows and the rows of neighbouring windows included
+      e = cudaMemcpyAsync(z, x0, (size_t)f.rows_total * pitch, cudaMemcpyDeviceToDevice, d->stream);
+    } else if (f.r0 > 0) {
+      e = cudaMemcpyAsync(z, x0, (size_t)f.r0 * pitch, cudaMemcpyDeviceToDevice, d->stream);
+    }
+    if (lp.halo) {
+    } else if (e == cudaSuccess && f.r1 < f.rows_total)
       e = cudaMemcpyAsync(z + f.r1 * f.ld, x0 + f.r1 * f.ld, (size_t)(f.rows_total - f.r1) * pitch, cudaMemcpyDeviceToDevice, d->stream);
-    if (e == cudaSuccess && f.c0 > 0)
+    if (!lp.halo && e == cudaSuccess && f.c0 > 0)
       e = cudaMemcpy2DAsync(z + f.r0 * f.ld, pitch, x0 + f.r0 * f.ld, pitch, (size_t)f.c0 * sizeof(float), (size_t)(f.r1 - f.r0), cudaMemcpyDeviceToDevice, d->stream);
-    if (e == cudaSuccess && f.c1 < f.ld)
+    if (!lp.halo && e == cudaSuccess && f.c1 < f.ld)
       e = cudaMemcpy2DAsync(z + f.r0 * f.ld + f.c1, pitch, x0 + f.r0 * f.ld + f.c1, pitch, (size_t)(f.ld - f.c1) * sizeof(float), (size_t)(f.r1 - f.r0), cudaMemcpyDeviceToDevice,
                             d->stream);
     if (e != cudaSuccess) return e;

@@ -176,7 +176,7 @@ def test_one_process_per_gpu_mesh_matches_the_float64_sum():
 
 @pytest.mark.parametrize("whole_loop", [True, False])
 @pytest.mark.parametrize("ndev", [2, 4])
-@pytest.mark.parametrize("n,steps,form", [(64, 3, "dus"), (516, 5, "dus"), (1028, 4, "halfsteps"), (260, 7, "halfsteps")])
+@pytest.mark.parametrize("n,steps,form", [(64, 3, "dus"), (516, 5, "dus"), (1028, 12, "dus"), (64, 6, "dus"), (1028, 4, "halfsteps"), (260, 7, "halfsteps")])
 def test_row_sharded_jacobi_with_halo_exchange_is_bit_exact(rx, ref, ndev, n, steps, form, whole_loop, monkeypatch):
     """Both arrays split into row blocks over the mesh (Julia's second dimension); every sweep each device updates the
     rows it owns and sends its boundary rows to its neighbours' halos.  Same bits as the unsharded program, whether

@@ -273,7 +273,7 @@ def test_row_sharded_jacobi_plans_with_halo_rows(rx):
         p = rx.plan_describe(rx.programs.jacobi2d(8192, 100, form=form, num_partitions=8))
         assert kinds(p) == ["rows_in", "rows_in", "loop", "rows_out", "rows_out"]
         loop = p["steps"][2]
-        assert [s["kind"] for s in loop["body"]] == body and "halo 1 up, 1 down" in loop["note"]
+        assert [s["kind"] for s in loop["body"]] == body and "halo 2 up, 2 down" in loop["note"]
     # a loop that carries anything else in sharded form is refused by name
     text = rx.programs.jacobi1d(64, 2).replace("mhlo.num_partitions = 1", "mhlo.num_partitions = 2")
     text = text.replace("  func.func @main", '  sdy.mesh @mesh = <["x"=2]>\n  func.func @main', 1)
