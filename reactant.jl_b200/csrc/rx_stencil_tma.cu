@@ -203,6 +203,16 @@ struct FuseParams {
 };
 struct alignas(64) FuseMaps { CUtensorMap m[3]; };  // buf[0] and buf[1] with (TH + 4)-row boxes; buf[1] with the single-sweep box
 
+// Shared-memory accesses by 32-bit shared address: the tile pointers reach the sweep functions as generic pointers,
+// and generic loads are slower than ld.shared and wait on the long scoreboard.  Volatile, so that they stay behind
+// the mbarrier wait and the CTA barriers they follow in program order.
+__device__ __forceinline__ float lds(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v)); }
+
 // the five values of a radius-1 cross, added in the order the traced program adds them
 //   ORDER 0: centre, left, right, up, down      (the swap spelling, and the pad / concatenate spellings)
 //   ORDER 1: centre, up, down, right, left      (benchmark/polybench/stencil.jl:263-289 after the layout fold)
@@ -264,15 +274,33 @@ __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const Fu
           mid[yp * BOX_W + xp] = (col_ok && Y >= 0 && Y < f.rows_total) ? __ldg(other + (long long)yp * f.ld) : 0.f;
         }
         if (lo < hi) {
-          const float* q = sm + (lo + 1) * BOX_W + (f.xs + xp + 1);  // the point itself in the source box
-          float up = q[-BOX_W], c = q[0];
-#pragma unroll 4
-          for (int yp = lo; yp < hi; ++yp) {
-            const float l = q[-1], r = q[1], dn = q[BOX_W];
-            mid[yp * BOX_W + xp] = __fmul_rn(k, cross_sum<ORDER>(c, l, r, up, dn));
+          constexpr uint32_t R = BOX_W * sizeof(float);  // one row
+          uint32_t qa = smem_u32(sm) + (uint32_t)(((lo + 1) * BOX_W + (f.xs + xp + 1)) * sizeof(float));  // the point itself in the source box
+          uint32_t ma = smem_u32(mid) + (uint32_t)((lo * BOX_W + xp) * sizeof(float));
+          float up = lds(qa - R), c = lds(qa);
+          int yp = lo;
+          // four rows at a time: their twelve loads are issued together, then the arithmetic
+          for (; yp + 4 <= hi; yp += 4) {
+            const float l0 = lds(qa - 4), r0 = lds(qa + 4), d0 = lds(qa + R);
+            const float l1 = lds(qa + R - 4), r1 = lds(qa + R + 4), d1 = lds(qa + 2 * R);
+            const float l2 = lds(qa + 2 * R - 4), r2 = lds(qa + 2 * R + 4), d2 = lds(qa + 3 * R);
+            const float l3 = lds(qa + 3 * R - 4), r3 = lds(qa + 3 * R + 4), d3 = lds(qa + 4 * R);
+            sts(ma, __fmul_rn(k, cross_sum<ORDER>(c, l0, r0, up, d0)));
+            sts(ma + R, __fmul_rn(k, cross_sum<ORDER>(d0, l1, r1, c, d1)));
+            sts(ma + 2 * R, __fmul_rn(k, cross_sum<ORDER>(d1, l2, r2, d0, d2)));
+            sts(ma + 3 * R, __fmul_rn(k, cross_sum<ORDER>(d2, l3, r3, d1, d3)));
+            up = d2;
+            c = d3;
+            qa += 4 * R;
+            ma += 4 * R;
+          }
+          for (; yp < hi; ++yp) {
+            const float l = lds(qa - 4), r = lds(qa + 4), dn = lds(qa + R);
+            sts(ma, __fmul_rn(k, cross_sum<ORDER>(c, l, r, up, dn)));
             up = c;
             c = dn;
-            q += BOX_W;
+            qa += R;
+            ma += R;
           }
         }
         for (int yp = max(hi, 0); yp < TH + 2; ++yp) {
@@ -292,15 +320,31 @@ __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const Fu
         if (rmax > 0 && !(rx_in_bounds(f.bounds, f.extent, Y0 * f.ld + X, 1, 299) && rx_in_bounds(f.bounds, f.extent, (Y0 + rmax - 1) * f.ld + X, 1, 299))) rmax = 0;
 #endif
         float* out = dst + Y0 * f.ld + X;
-        const float* q = mid + BOX_W + (cx + 1);
-        float up = q[-BOX_W], c = q[0];
-#pragma unroll 4
-        for (int r = 0; r < rmax; ++r) {
-          const float l = q[-1], rr = q[1], dn = q[BOX_W];
-          out[(long long)r * f.ld] = __fmul_rn(k, cross_sum<ORDER>(c, l, rr, up, dn));
+        constexpr uint32_t R = BOX_W * sizeof(float);
+        uint32_t qa = smem_u32(mid) + (uint32_t)((BOX_W + (cx + 1)) * sizeof(float));
+        float up = lds(qa - R), c = lds(qa);
+        int r = 0;
+        for (; r + 4 <= rmax; r += 4) {
+          const float l0 = lds(qa - 4), r0 = lds(qa + 4), d0 = lds(qa + R);
+          const float l1 = lds(qa + R - 4), r1 = lds(qa + R + 4), d1 = lds(qa + 2 * R);
+          const float l2 = lds(qa + 2 * R - 4), r2 = lds(qa + 2 * R + 4), d2 = lds(qa + 3 * R);
+          const float l3 = lds(qa + 3 * R - 4), r3 = lds(qa + 3 * R + 4), d3 = lds(qa + 4 * R);
+          out[0] = __fmul_rn(k, cross_sum<ORDER>(c, l0, r0, up, d0));
+          out[f.ld] = __fmul_rn(k, cross_sum<ORDER>(d0, l1, r1, c, d1));
+          out[2 * f.ld] = __fmul_rn(k, cross_sum<ORDER>(d1, l2, r2, d0, d2));
+          out[3 * f.ld] = __fmul_rn(k, cross_sum<ORDER>(d2, l3, r3, d1, d3));
+          up = d2;
+          c = d3;
+          qa += 4 * R;
+          out += 4 * f.ld;
+        }
+        for (; r < rmax; ++r) {
+          const float l = lds(qa - 4), rr = lds(qa + 4), dn = lds(qa + R);
+          out[0] = __fmul_rn(k, cross_sum<ORDER>(c, l, rr, up, dn));
           up = c;
           c = dn;
-          q += BOX_W;
+          qa += R;
+          out += f.ld;
         }
       }
     }
