@@ -398,7 +398,8 @@ WORKLOADS.update({
 })
 SMALL_INPUT = {"c1_sinsum_2p24", "c4_mlp_grad_bf16"}  # working set near or below the 126 MB L2: rotate input copies
 EXTRA_CONFIGS = ["c1_sinsum_2p24", "c2_logsumexp_32768x8192", "c3_jacobi2d_8192_100", "c3_jacobi2d_8192_50_halfsteps", "c4_mlp_grad_bf16"]
-SHARDED = ("c5_sharded_sinsum_2p30", "c1_sinsum_2p24", "c4_mlp_grad_bf16", "c3_jacobi2d_8192_100", "c3_jacobi2d_8192_50_halfsteps")
+SHARDED = ("c5_sharded_sinsum_2p30", "c1_sinsum_2p24", "c4_mlp_grad_bf16", "c3_jacobi2d_8192_100", "c3_jacobi2d_8192_50_halfsteps",
+           "prof_jacobi2d_8192_4", "prof_jacobi2d_8192_12")
 
 
 # DRAM traffic per algorithmic byte of the dominant kernel, from profiler captures of the reduced-size workloads

@@ -31,6 +31,7 @@ constexpr int STAGES = 2;                   // a deeper ring measured slower (mo
 constexpr int kMaxTaps = 8;
 constexpr long long kWaitLimit = 2000000;  // bounded mbarrier polling
 
+
 struct StencilParams {
   float* dst;
   int64_t rows, cols, dst_ld, dst_off;
@@ -46,6 +47,75 @@ struct StencilParams {
   int* bounds;
 };
 
+// Row-sharded arrays: the tile rows that hold rows the neighbouring devices wait for (up to two at either end of the
+// window) come first in a sweep's order: the first tile row, and the last one -- or the last two, when the last holds
+// a single row.  edge_tail() is how many tile rows at the end, edge_tiles() how many tiles in all.
+__device__ __forceinline__ int edge_tail(long long rows, int tiles_y, int th) {
+  if (tiles_y < 2) return 0;
+  return (rows - (long long)(tiles_y - 1) * th >= 2 || tiles_y < 3) ? 1 : 2;
+}
+__device__ __forceinline__ int edge_tiles(long long rows, int tiles_x, int tiles_y, int th) { return (1 + edge_tail(rows, tiles_y, th)) * tiles_x; }
+
+// Shared-memory accesses by 32-bit shared address: the tile pointers reach the sweep functions as generic pointers,
+// and generic loads are slower than ld.shared and wait on the long scoreboard.  Volatile, so that they stay behind
+// the mbarrier wait and the CTA barriers they follow in program order.
+__device__ __forceinline__ float lds(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v)); }
+
+// the five values of a radius-1 cross, added in the order the traced program adds them
+//   ORDER 0: centre, left, right, up, down      (the swap spelling, and the pad / concatenate spellings)
+//   ORDER 1: centre, up, down, right, left      (benchmark/polybench/stencil.jl:263-289 after the layout fold)
+template <int ORDER>
+__device__ __forceinline__ float cross_sum(float c, float l, float r, float u, float d) {
+  if (ORDER == 0) return __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(c, l), r), u), d);
+  return __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(c, u), d), r), l);
+}
+
+// B consecutive rows of one column of a radius-1 cross over a tile in shared memory.  `qa` is the shared address of
+// the first row's centre; `up` and `c` hold the two values above the row after it and are carried on.  All 3 B loads
+// are issued before the arithmetic, so that B independent chains of adds are in flight.
+constexpr int kRowBatch = 8;
+template <int B, int ORDER, class Store>
+__device__ __forceinline__ void cross_rows(uint32_t qa, float& up, float& c, float k, Store&& store) {
+  constexpr uint32_t R = BOX_W * sizeof(float);
+  float v[B + 2], l[B], r[B];
+  v[0] = up;
+  v[1] = c;
+#pragma unroll
+  for (int j = 0; j < B; ++j) {
+    l[j] = lds(qa + j * R - 4);
+    r[j] = lds(qa + j * R + 4);
+    v[j + 2] = lds(qa + (j + 1) * R);
+  }
+#pragma unroll
+  for (int j = 0; j < B; ++j) store(j, __fmul_rn(k, cross_sum<ORDER>(v[j + 1], l[j], r[j], v[j], v[j + 2])));
+  up = v[B];
+  c = v[B + 1];
+}
+
+// rows [0, n) of a column: batches of kRowBatch, then pairs, then one
+template <int ORDER, class Store, class Advance>
+__device__ __forceinline__ void cross_column(uint32_t qa, int n, float k, Store&& store, Advance&& advance) {
+  constexpr uint32_t R = BOX_W * sizeof(float);
+  float up = lds(qa - R), c = lds(qa);
+  int r = 0;
+  for (; r + kRowBatch <= n; r += kRowBatch) {
+    cross_rows<kRowBatch, ORDER>(qa, up, c, k, store);
+    qa += kRowBatch * R;
+    advance(kRowBatch);
+  }
+  for (; r + 2 <= n; r += 2) {
+    cross_rows<2, ORDER>(qa, up, c, k, store);
+    qa += 2 * R;
+    advance(2);
+  }
+  if (r < n) cross_rows<1, ORDER>(qa, up, c, k, store);
+}
+
 // One sweep of this CTA's tiles.  `it` counts the tiles this CTA has processed since the kernel started: it
 // selects the ring stage and the mbarrier parity, so that several sweeps can share one ring.  On entry every
 // stage is drained.  Returns false if a load did not arrive within the wait limit.
@@ -54,16 +124,22 @@ struct StencilParams {
 // `cta` of `ncta` CTAs share the tile list.  With `edge_rows` the tiles of the first and last tile row come first
 // (they hold the rows a row-sharded array's neighbours are waiting for), each counted in *edge_counter once its
 // rows are written, and only the remaining tiles alternate direction.
+// With `queue` (a counter in device memory, zero when the sweep starts) the CTAs take the positions of the sweep's
+// order one by one as they become free instead of every ncta-th one: CTAs do not run at the same speed (by 20 %
+// between the first and the last to finish a pass of 30 tiles each), and what the slowest one needs is what the
+// grid barrier after the sweep waits for.  A position is claimed one step before its load is issued, so the
+// atomic's latency is off the issuing thread's path.
 template <bool FAST5, int TH>
 __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const StencilParams& p, const VmProgram* P, float fast_c, float* const* tile, uint64_t* bars,
                                               int& it, bool reverse = false, int cta = blockIdx.x, int ncta = gridDim.x, bool edge_rows = false,
-                                              unsigned* edge_counter = nullptr) {
+                                              unsigned* edge_counter = nullptr, unsigned* queue = nullptr) {
+  __shared__ int claimed[STAGES];  // position in the sweep's order of the tile in (or on its way into) each stage; >= ntiles: none
   const uint32_t bytes = (uint32_t)(BOX_W * p.box_h * sizeof(float));
   const int ntiles = p.tiles_x * p.tiles_y;
-  const int n_edge = edge_rows ? (p.tiles_y >= 2 ? 2 : 1) * p.tiles_x : 0;
+  const int n_edge = edge_rows ? edge_tiles(p.rows, p.tiles_x, p.tiles_y, TH) : 0;
   // position in this sweep's order -> tile
   auto tile_of = [&](int t) {
-    if (t < n_edge) return t < p.tiles_x ? t : (p.tiles_y - 1) * p.tiles_x + (t - p.tiles_x);
+    if (t < n_edge) return t < p.tiles_x ? t : ntiles - n_edge + t;  // the first tile row, then the last ones
     if (!edge_rows) return reverse ? ntiles - 1 - t : t;
     const int u = t - n_edge, n_int = ntiles - n_edge;
     return p.tiles_x + (reverse ? n_int - 1 - u : u);
@@ -74,15 +150,30 @@ __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const Ste
     mbar_expect_tx(&bars[s], bytes);
     tma_load_2d(tile[s], tmap, p.x_base + tx * p.tw, p.y_base + ty * TH, &bars[s]);
   };
-  int first = cta;
-  if (threadIdx.x == 0)
-    for (int q = 0; q < STAGES - 1; ++q)
-      if (first + q * ncta < ntiles) issue(first + q * ncta, (it + q) % STAGES);
-  for (int t = first; t < ntiles; t += ncta, ++it) {
+  // thread 0: claims made; the position claimed but not yet issued (its value is first looked at one step later, so
+  // the warp does not wait for the atomic)
+  unsigned n_claims = 0, pending = 0;
+  auto claim = [&]() { return queue ? atomicAdd(queue, 1u) : (unsigned)cta + (n_claims++) * (unsigned)ncta; };
+  if (threadIdx.x == 0) {
+    for (int q = 0; q < STAGES - 1; ++q) {
+      const int t = (int)min(claim(), (unsigned)ntiles);
+      claimed[(it + q) % STAGES] = t;
+      if (t < ntiles) issue(t, (it + q) % STAGES);
+    }
+    pending = claim();
+  }
+  __syncthreads();
+  for (;; ++it) {
     int s = it % STAGES;
     uint32_t parity = (it / STAGES) & 1;
-    int next = t + (STAGES - 1) * ncta;
-    if (threadIdx.x == 0 && next < ntiles) issue(next, (it + STAGES - 1) % STAGES);  // that stage was drained before the last barrier
+    const int t = claimed[s];
+    if (t >= ntiles) break;
+    if (threadIdx.x == 0) {  // the other stage was drained before the last barrier, and its position read before that
+      const int sn = (it + STAGES - 1) % STAGES, tn = (int)min(pending, (unsigned)ntiles);
+      claimed[sn] = tn;
+      if (tn < ntiles) issue(tn, sn);
+      pending = claim();
+    }
     if (!mbar_wait(&bars[s], parity, kWaitLimit)) return false;
     const int tt = tile_of(t);
     int ty = tt / p.tiles_x, tx = tt - ty * p.tiles_x;
@@ -103,17 +194,9 @@ __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const Ste
         if (p.cross) {
           // taps are centre, left, right, up, down in that evaluation order: slide a three-row window
           // down the column so that each output costs three shared-memory reads instead of five
-          const float* q = sm + p.dx[0];  // column of the centre tap
-          float up = q[(p.dy[3]) * BOX_W], mid = q[p.dy[0] * BOX_W];
-#pragma unroll 4
-          for (int r = 0; r < rmax; ++r) {
-            const float* row = q + (r + p.dy[0]) * BOX_W;
-            const float left = row[-1], right = row[1], down = row[BOX_W];
-            float v = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(mid, left), right), up), down);
-            out[(int64_t)r * p.dst_ld] = __fmul_rn(k, v);
-            up = mid;
-            mid = down;
-          }
+          const uint32_t qa = smem_u32(sm + p.dx[0] + p.dy[0] * BOX_W);  // the centre tap of the first row
+          const int64_t ld = p.dst_ld;
+          cross_column<0>(qa, rmax, k, [&](int j, float v) { out[j * ld] = v; }, [&](int n) { out += n * ld; });
         } else {
           const int o0 = p.dy[0] * BOX_W + p.dx[0], o1 = p.dy[1] * BOX_W + p.dx[1], o2 = p.dy[2] * BOX_W + p.dx[2], o3 = p.dy[3] * BOX_W + p.dx[3],
                     o4 = p.dy[4] * BOX_W + p.dx[4];
@@ -203,36 +286,18 @@ struct FuseParams {
 };
 struct alignas(64) FuseMaps { CUtensorMap m[3]; };  // buf[0] and buf[1] with (TH + 4)-row boxes; buf[1] with the single-sweep box
 
-// Shared-memory accesses by 32-bit shared address: the tile pointers reach the sweep functions as generic pointers,
-// and generic loads are slower than ld.shared and wait on the long scoreboard.  Volatile, so that they stay behind
-// the mbarrier wait and the CTA barriers they follow in program order.
-__device__ __forceinline__ float lds(uint32_t a) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ void sts(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v)); }
-
-// the five values of a radius-1 cross, added in the order the traced program adds them
-//   ORDER 0: centre, left, right, up, down      (the swap spelling, and the pad / concatenate spellings)
-//   ORDER 1: centre, up, down, right, left      (benchmark/polybench/stencil.jl:263-289 after the layout fold)
-template <int ORDER>
-__device__ __forceinline__ float cross_sum(float c, float l, float r, float u, float d) {
-  if (ORDER == 0) return __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(c, l), r), u), d);
-  return __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(c, u), d), r), l);
-}
-
 template <int TH, int ORDER>
 __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const FuseParams& f, float* dst, float* const* tile, float* mid, uint64_t* bars, int& it,
-                                               bool reverse, int cta, int ncta, bool edge_rows = false, unsigned* edge_counter = nullptr) {
+                                               bool reverse, int cta, int ncta, bool edge_rows = false, unsigned* edge_counter = nullptr, unsigned* queue = nullptr) {
+  __shared__ int claimed[STAGES];
   constexpr int BH = TH + 4;
   const uint32_t bytes = (uint32_t)(BOX_W * BH * sizeof(float));
   const int ntiles = f.tiles_x2 * f.tiles_y2;
   const float k = f.k;
-  const int n_edge = edge_rows ? (f.tiles_y2 >= 2 ? 2 : 1) * f.tiles_x2 : 0;
-  // position in this pass's order -> tile (first and last tile row first when the rows are traded with neighbours)
+  const int n_edge = edge_rows ? edge_tiles(f.r1 - f.r0, f.tiles_x2, f.tiles_y2, TH) : 0;
+  // position in this pass's order -> tile (first and last tile rows first when the rows are traded with neighbours)
   auto tile_of = [&](int t) {
-    if (t < n_edge) return t < f.tiles_x2 ? t : (f.tiles_y2 - 1) * f.tiles_x2 + (t - f.tiles_x2);
+    if (t < n_edge) return t < f.tiles_x2 ? t : ntiles - n_edge + t;
     if (!edge_rows) return reverse ? ntiles - 1 - t : t;
     const int u = t - n_edge, n_int = ntiles - n_edge;
     return f.tiles_x2 + (reverse ? n_int - 1 - u : u);
@@ -245,14 +310,25 @@ __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const Fu
     // read the fill value, which is never used: those positions come from the other array
     tma_load_2d(tile[s], tmap, (int)(f.c0 + (long long)tx * f.tw2 - 2 - f.xs), (int)(f.r0 + (long long)ty * TH - 2), &bars[s]);
   };
-  if (threadIdx.x == 0)
-    for (int q = 0; q < STAGES - 1; ++q)
-      if (cta + q * ncta < ntiles) issue(cta + q * ncta, (it + q) % STAGES);
-  for (int t = cta; t < ntiles; t += ncta, ++it) {
+  // Only the first of the two steps on a tile reads the ring stage, so the stage is refilled as soon as that step is
+  // over: the whole ring is in flight at the start, and the load of the CTA's next tile but one overlaps the second
+  // step on this tile and everything on the next.  Positions come from `queue` as in stencil_sweep.
+  unsigned n_claims = 0, pending = 0;
+  auto claim = [&]() { return queue ? atomicAdd(queue, 1u) : (unsigned)cta + (n_claims++) * (unsigned)ncta; };
+  if (threadIdx.x == 0) {
+    for (int q = 0; q < STAGES; ++q) {
+      const int t = (int)min(claim(), (unsigned)ntiles);
+      claimed[(it + q) % STAGES] = t;
+      if (t < ntiles) issue(t, (it + q) % STAGES);
+    }
+    pending = claim();
+  }
+  __syncthreads();
+  for (;; ++it) {
     const int s = it % STAGES;
     const uint32_t parity = (it / STAGES) & 1;
-    const int next = t + (STAGES - 1) * ncta;
-    if (threadIdx.x == 0 && next < ntiles) issue(next, (it + STAGES - 1) % STAGES);
+    const int t = claimed[s];
+    if (t >= ntiles) break;
     if (!mbar_wait(&bars[s], parity, kWaitLimit)) return false;
     const int tt = tile_of(t);
     const int ty = tt / f.tiles_x2, tx = tt - ty * f.tiles_x2;
@@ -269,47 +345,41 @@ __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const Fu
         const int lo = col_in ? (int)max(0ll, f.m0 - (Y0 - 1)) : TH + 2;
         const int hi = col_in ? (int)min((long long)(TH + 2), f.m1 - (Y0 - 1)) : TH + 2;
         const float* other = f.other + (Y0 - 1) * f.ld + X;
-        for (int yp = 0; yp < min(lo, TH + 2); ++yp) {
+        if (!col_in) {
+          // a column left or right of the window: all of it is the other array's.  The loads are issued together --
+          // one after the other they cost the whole CTA, which waits at the barrier below, 34 memory round trips
+          float v[TH + 2];
+#pragma unroll
+          for (int yp = 0; yp < TH + 2; ++yp) {
+            const long long Y = Y0 - 1 + yp;
+            v[yp] = (col_ok && Y >= 0 && Y < f.rows_total) ? __ldg(other + (long long)yp * f.ld) : 0.f;
+          }
+#pragma unroll
+          for (int yp = 0; yp < TH + 2; ++yp) mid[yp * BOX_W + xp] = v[yp];
+        }
+        for (int yp = 0; yp < min(lo, TH + 2) && col_in; ++yp) {
           const long long Y = Y0 - 1 + yp;
           mid[yp * BOX_W + xp] = (col_ok && Y >= 0 && Y < f.rows_total) ? __ldg(other + (long long)yp * f.ld) : 0.f;
         }
         if (lo < hi) {
           constexpr uint32_t R = BOX_W * sizeof(float);  // one row
-          uint32_t qa = smem_u32(sm) + (uint32_t)(((lo + 1) * BOX_W + (f.xs + xp + 1)) * sizeof(float));  // the point itself in the source box
+          const uint32_t qa = smem_u32(sm) + (uint32_t)(((lo + 1) * BOX_W + (f.xs + xp + 1)) * sizeof(float));  // the point itself in the source box
           uint32_t ma = smem_u32(mid) + (uint32_t)((lo * BOX_W + xp) * sizeof(float));
-          float up = lds(qa - R), c = lds(qa);
-          int yp = lo;
-          // four rows at a time: their twelve loads are issued together, then the arithmetic
-          for (; yp + 4 <= hi; yp += 4) {
-            const float l0 = lds(qa - 4), r0 = lds(qa + 4), d0 = lds(qa + R);
-            const float l1 = lds(qa + R - 4), r1 = lds(qa + R + 4), d1 = lds(qa + 2 * R);
-            const float l2 = lds(qa + 2 * R - 4), r2 = lds(qa + 2 * R + 4), d2 = lds(qa + 3 * R);
-            const float l3 = lds(qa + 3 * R - 4), r3 = lds(qa + 3 * R + 4), d3 = lds(qa + 4 * R);
-            sts(ma, __fmul_rn(k, cross_sum<ORDER>(c, l0, r0, up, d0)));
-            sts(ma + R, __fmul_rn(k, cross_sum<ORDER>(d0, l1, r1, c, d1)));
-            sts(ma + 2 * R, __fmul_rn(k, cross_sum<ORDER>(d1, l2, r2, d0, d2)));
-            sts(ma + 3 * R, __fmul_rn(k, cross_sum<ORDER>(d2, l3, r3, d1, d3)));
-            up = d2;
-            c = d3;
-            qa += 4 * R;
-            ma += 4 * R;
-          }
-          for (; yp < hi; ++yp) {
-            const float l = lds(qa - 4), r = lds(qa + 4), dn = lds(qa + R);
-            sts(ma, __fmul_rn(k, cross_sum<ORDER>(c, l, r, up, dn)));
-            up = c;
-            c = dn;
-            qa += R;
-            ma += R;
-          }
+          cross_column<ORDER>(qa, hi - lo, k, [&](int j, float v) { sts(ma + j * R, v); }, [&](int n) { ma += n * R; });
         }
-        for (int yp = max(hi, 0); yp < TH + 2; ++yp) {
+        for (int yp = max(hi, 0); yp < TH + 2 && col_in; ++yp) {
           const long long Y = Y0 - 1 + yp;
           mid[yp * BOX_W + xp] = (col_ok && Y >= 0 && Y < f.rows_total) ? __ldg(other + (long long)yp * f.ld) : 0.f;
         }
       }
     }
     __syncthreads();
+    if (threadIdx.x == 0) {  // every thread is done with stage s, and has read its position
+      const int tn = (int)min(pending, (unsigned)ntiles);
+      claimed[s] = tn;
+      if (tn < ntiles) issue(tn, s);
+      pending = claim();
+    }
     // state s + 2 on the tile
     {
       const int cx = threadIdx.x;
@@ -320,32 +390,9 @@ __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const Fu
         if (rmax > 0 && !(rx_in_bounds(f.bounds, f.extent, Y0 * f.ld + X, 1, 299) && rx_in_bounds(f.bounds, f.extent, (Y0 + rmax - 1) * f.ld + X, 1, 299))) rmax = 0;
 #endif
         float* out = dst + Y0 * f.ld + X;
-        constexpr uint32_t R = BOX_W * sizeof(float);
-        uint32_t qa = smem_u32(mid) + (uint32_t)((BOX_W + (cx + 1)) * sizeof(float));
-        float up = lds(qa - R), c = lds(qa);
-        int r = 0;
-        for (; r + 4 <= rmax; r += 4) {
-          const float l0 = lds(qa - 4), r0 = lds(qa + 4), d0 = lds(qa + R);
-          const float l1 = lds(qa + R - 4), r1 = lds(qa + R + 4), d1 = lds(qa + 2 * R);
-          const float l2 = lds(qa + 2 * R - 4), r2 = lds(qa + 2 * R + 4), d2 = lds(qa + 3 * R);
-          const float l3 = lds(qa + 3 * R - 4), r3 = lds(qa + 3 * R + 4), d3 = lds(qa + 4 * R);
-          out[0] = __fmul_rn(k, cross_sum<ORDER>(c, l0, r0, up, d0));
-          out[f.ld] = __fmul_rn(k, cross_sum<ORDER>(d0, l1, r1, c, d1));
-          out[2 * f.ld] = __fmul_rn(k, cross_sum<ORDER>(d1, l2, r2, d0, d2));
-          out[3 * f.ld] = __fmul_rn(k, cross_sum<ORDER>(d2, l3, r3, d1, d3));
-          up = d2;
-          c = d3;
-          qa += 4 * R;
-          out += 4 * f.ld;
-        }
-        for (; r < rmax; ++r) {
-          const float l = lds(qa - 4), rr = lds(qa + 4), dn = lds(qa + R);
-          out[0] = __fmul_rn(k, cross_sum<ORDER>(c, l, rr, up, dn));
-          up = c;
-          c = dn;
-          qa += R;
-          out += f.ld;
-        }
+        const long long ld = f.ld;
+        const uint32_t qa = smem_u32(mid) + (uint32_t)((BOX_W + (cx + 1)) * sizeof(float));
+        cross_column<ORDER>(qa, rmax, k, [&](int j, float v) { out[j * ld] = v; }, [&](int n) { out += n * ld; });
       }
     }
     __syncthreads();  // stage s and the intermediate tile are free again
@@ -374,6 +421,7 @@ struct LoopParams {
   int total;          // sweeps to run = loop trip count x stencil steps per iteration
   int alternate;      // odd sweeps walk the tiles backwards
   unsigned* counter;  // zero at launch
+  unsigned* queue;    // two words, zero at launch: the tile queues of even and odd passes (see stencil_sweep)
   FuseParams fuse;    // double sweeps that come first (n_fused = 0: none); `total` then counts the single sweeps after them
   // Row-sharded arrays (the device owns a block of rows of each array and keeps copies of its neighbours' boundary
   // rows): between two sweeps CTA 0 exchanges the boundary rows of the array just written with the neighbouring
@@ -388,7 +436,7 @@ struct LoopParams {
 };
 
 template <int TH>
-__global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ PhaseMaps maps, const __grid_constant__ LoopParams lp, const __grid_constant__ FuseMaps fm) {
+__global__ void __launch_bounds__(256, 2) k_stencil_loop(const __grid_constant__ PhaseMaps maps, const __grid_constant__ LoopParams lp, const __grid_constant__ FuseMaps fm) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[STAGES];
   float* tile[STAGES];
@@ -417,7 +465,8 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
       const int ph = dbl ? 0 : (pass - lp.fuse.n_fused) % lp.n_phases;
       // the array this pass writes, and how many of its tiles hold rows the neighbours wait for
       float* block = dbl ? lp.fuse.buf[(pass + 1) & 1] : lp.halo_block[ph];
-      edge_target += dbl ? (unsigned)((lp.fuse.tiles_y2 >= 2 ? 2 : 1) * lp.fuse.tiles_x2) : (unsigned)((lp.ph[ph].tiles_y >= 2 ? 2 : 1) * lp.ph[ph].tiles_x);
+      edge_target += dbl ? (unsigned)edge_tiles(lp.fuse.r1 - lp.fuse.r0, lp.fuse.tiles_x2, lp.fuse.tiles_y2, TH)
+                         : (unsigned)edge_tiles(lp.ph[ph].rows, lp.ph[ph].tiles_x, lp.ph[ph].tiles_y, TH);
       int ok = 1;
       if (threadIdx.x == 0) {
         long long spins = 0;
@@ -489,10 +538,19 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
     return ok != 0;  // false: nothing of this CTA is in flight (the sweep before drained its ring)
   };
   // double sweeps first: state 2q -> state 2q + 2, ping-ponging between the first array and the scratch array
+  // The queue of pass p is word p & 1; the worker CTA 0 clears the other word, which every CTA stopped using before
+  // the barrier that ended pass p - 1 and which is next used after the barrier that ends pass p.
+  auto pass_queue = [&](int pass) -> unsigned* {
+    if (!lp.queue) return nullptr;  // every ncta-th position
+    if (cta == 0 && threadIdx.x == 0) lp.queue[(pass + 1) & 1] = 0;
+    return lp.queue + (pass & 1);
+  };
   for (int q = 0; q < lp.fuse.n_fused; ++q) {
-    const bool done = lp.fuse.order == 0
-                          ? stencil_sweep2<TH, 0>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta, lp.halo != 0, lp.edge)
-                          : stencil_sweep2<TH, 1>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta, lp.halo != 0, lp.edge);
+    unsigned* queue = pass_queue(q);
+    const bool done =
+        lp.fuse.order == 0
+            ? stencil_sweep2<TH, 0>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta, lp.halo != 0, lp.edge, queue)
+            : stencil_sweep2<TH, 1>(&fm.m[q & 1], lp.fuse, lp.fuse.buf[(q + 1) & 1], tile, mid, bars, it, lp.alternate && (q & 1), cta, ncta, lp.halo != 0, lp.edge, queue);
     if (!done) {
       if (threadIdx.x == 0) *lp.ph[0].status = 2;
       stencil_drain(bars);
@@ -504,7 +562,8 @@ __global__ void __launch_bounds__(256) k_stencil_loop(const __grid_constant__ Ph
     const int ph = sweep % lp.n_phases;
     // after an odd number of double sweeps the current state sits in the scratch array: the first single sweep reads it there
     const CUtensorMap* src_map = (sweep == 0 && (lp.fuse.n_fused & 1)) ? &fm.m[2] : &maps.m[ph];
-    if (!stencil_sweep<true, TH>(src_map, lp.ph[ph], nullptr, lp.k[ph], tile, bars, it, lp.alternate && ((sweep + lp.fuse.n_fused) & 1), cta, ncta, lp.halo != 0, lp.edge)) {
+    if (!stencil_sweep<true, TH>(src_map, lp.ph[ph], nullptr, lp.k[ph], tile, bars, it, lp.alternate && ((sweep + lp.fuse.n_fused) & 1), cta, ncta, lp.halo != 0, lp.edge,
+                                 pass_queue(lp.fuse.n_fused + sweep))) {
       if (threadIdx.x == 0) *lp.ph[0].status = 2;
       stencil_drain(bars);
       return;
@@ -678,7 +737,10 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
   lp.n_phases = n;
   lp.total = (int)total;
   lp.alternate = getenv("RX_STENCIL_ONE_WAY") ? 0 : 1;
-  lp.edge = (unsigned*)(d->scratch + d->scratch_words - 4);  // the three words before the reductions' ticket
+  unsigned* const words = (unsigned*)(d->scratch + d->scratch_words - 6);  // the five words before the reductions' ticket
+  const char* qenv = getenv("RX_STENCIL_QUEUE");  // 0: every CTA takes every ncta-th tile instead (read per call)
+  lp.queue = (qenv && atoi(qenv) == 0) ? nullptr : words;
+  lp.edge = words + 2;
   lp.release = lp.edge + 1;
   lp.counter = lp.edge + 2;
   if (halo) {
@@ -801,7 +863,7 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
     *handled = true;
     return cudaSuccess;
   }
-  cudaError_t e = cudaMemsetAsync(lp.edge, 0, 3 * sizeof(unsigned), d->stream);
+  cudaError_t e = cudaMemsetAsync(words, 0, 5 * sizeof(unsigned), d->stream);
   if (e != cudaSuccess) return e;
   if (lp.fuse.n_fused > 0) {
     // the scratch array needs the first array's values outside the update window (they are never written): the rows
@@ -810,18 +872,14 @@ cudaError_t run_stencil_loop(RxDevice* d, const std::vector<const Step*>& steps,
     const size_t pitch = (size_t)f.ld * sizeof(float);
     const float* x0 = f.buf[0];
     float* z = f.buf[1];
-    if (lp.halo) {
-      // a row block: its halo rows and the rows of neighbouring windows included
-      e = cudaMemcpyAsync(z, x0, (size_t)f.rows_total * pitch, cudaMemcpyDeviceToDevice, d->stream);
-    } else if (f.r0 > 0) {
-      e = cudaMemcpyAsync(z, x0, (size_t)f.r0 * pitch, cudaMemcpyDeviceToDevice, d->stream);
-    }
-    if (lp.halo) {
-    } else if (e == cudaSuccess && f.r1 < f.rows_total)
+    // (of a row block too: its halo rows are written by the exchange after the first pass, before anything reads them
+    // there, and arrive with their border columns)
+    if (f.r0 > 0) e = cudaMemcpyAsync(z, x0, (size_t)f.r0 * pitch, cudaMemcpyDeviceToDevice, d->stream);
+    if (e == cudaSuccess && f.r1 < f.rows_total)
       e = cudaMemcpyAsync(z + f.r1 * f.ld, x0 + f.r1 * f.ld, (size_t)(f.rows_total - f.r1) * pitch, cudaMemcpyDeviceToDevice, d->stream);
-    if (!lp.halo && e == cudaSuccess && f.c0 > 0)
+    if (e == cudaSuccess && f.c0 > 0)
       e = cudaMemcpy2DAsync(z + f.r0 * f.ld, pitch, x0 + f.r0 * f.ld, pitch, (size_t)f.c0 * sizeof(float), (size_t)(f.r1 - f.r0), cudaMemcpyDeviceToDevice, d->stream);
-    if (!lp.halo && e == cudaSuccess && f.c1 < f.ld)
+    if (e == cudaSuccess && f.c1 < f.ld)
       e = cudaMemcpy2DAsync(z + f.r0 * f.ld + f.c1, pitch, x0 + f.r0 * f.ld + f.c1, pitch, (size_t)(f.ld - f.c1) * sizeof(float), (size_t)(f.r1 - f.r0), cudaMemcpyDeviceToDevice,
                             d->stream);
     if (e != cudaSuccess) return e;

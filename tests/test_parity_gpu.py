@@ -223,6 +223,13 @@ def test_two_half_step_loop_is_one_launch_and_bit_exact(rx, ref, client, steps, 
     monkeypatch.setenv("RX_STENCIL_FUSE2", "0")
     out = f(rx.to_rarray(a.T, client), rx.to_rarray(b.T, client))
     assert all(np.array_equal(np.asarray(o).T, w) for o, w in zip(out, (wa, wb)))
+    # tiles handed out in a fixed pattern instead of from the per-pass queue: with and without double sweeps
+    monkeypatch.setenv("RX_STENCIL_QUEUE", "0")
+    out = f(rx.to_rarray(a.T, client), rx.to_rarray(b.T, client))
+    assert all(np.array_equal(np.asarray(o).T, w) for o, w in zip(out, (wa, wb)))
+    monkeypatch.delenv("RX_STENCIL_FUSE2")
+    out = f(rx.to_rarray(a.T, client), rx.to_rarray(b.T, client))
+    assert all(np.array_equal(np.asarray(o).T, w) for o, w in zip(out, (wa, wb)))
 
 
 def test_jacobi2d_full_size_against_c_oracle(rx, cpu, client):
