@@ -415,12 +415,12 @@ TRAFFIC_RATIO = {
 def stencil_loop_traffic(n, sweeps):
     """DRAM bytes of one whole-loop launch over n x n arrays.  The loop kernel does two sweeps per pass over memory
     for all but its last two (three, for an odd count) sweeps.  Per pass, from profiler captures of 4 and 12 sweeps at
-    n = 8192 (1481.3 MB and 3445.9 MB: 1 resp. 5 double passes + 2 single sweeps): 491.2 MB per double pass, 495.0 MB per
+    n = 8192 (1476.3 MB and 3425.4 MB: 1 resp. 5 double passes + 2 single sweeps): 487.3 MB per double pass, 494.5 MB per
     single sweep (less than the arrays' 536.7 MB because a sweep starts on what the previous one left in L2); both grow
     with the number of points."""
     tail = min(sweeps, 2 + sweeps % 2) if sweeps >= 4 else sweeps
     double = (sweeps - tail) // 2
-    return (double * 491.2e6 + tail * 495.0e6) * (n * n) / (8192.0 * 8192.0)
+    return (double * 487.3e6 + tail * 494.5e6) * (n * n) / (8192.0 * 8192.0)
 
 
 def work_per_step(wl):
