@@ -128,7 +128,9 @@ __device__ __forceinline__ void cross_column(uint32_t qa, int n, float k, Store&
 // order one by one as they become free instead of every ncta-th one: CTAs do not run at the same speed (by 20 %
 // between the first and the last to finish a pass of 30 tiles each), and what the slowest one needs is what the
 // grid barrier after the sweep waits for.  A position is claimed one step before its load is issued, so the
-// atomic's latency is off the issuing thread's path.
+// atomic's latency is off the issuing thread's path.  Every CTA's first position is its own number, the queue hands
+// out the ones from ncta on: the tiles at the front of the order (the edge tiles of a row-sharded array, which the
+// exchange waits for) are then all worked on at once instead of two or three in a row by the CTAs that start first.
 template <bool FAST5, int TH>
 __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const StencilParams& p, const VmProgram* P, float fast_c, float* const* tile, uint64_t* bars,
                                               int& it, bool reverse = false, int cta = blockIdx.x, int ncta = gridDim.x, bool edge_rows = false,
@@ -153,7 +155,11 @@ __device__ __forceinline__ bool stencil_sweep(const CUtensorMap* tmap, const Ste
   // thread 0: claims made; the position claimed but not yet issued (its value is first looked at one step later, so
   // the warp does not wait for the atomic)
   unsigned n_claims = 0, pending = 0;
-  auto claim = [&]() { return queue ? atomicAdd(queue, 1u) : (unsigned)cta + (n_claims++) * (unsigned)ncta; };
+  auto claim = [&]() -> unsigned {
+    const unsigned k = n_claims++;
+    if (!queue) return (unsigned)cta + k * (unsigned)ncta;
+    return k == 0 ? (unsigned)cta : (unsigned)ncta + atomicAdd(queue, 1u);  // the first ncta positions go one to each CTA
+  };
   if (threadIdx.x == 0) {
     for (int q = 0; q < STAGES - 1; ++q) {
       const int t = (int)min(claim(), (unsigned)ntiles);
@@ -314,7 +320,11 @@ __device__ __forceinline__ bool stencil_sweep2(const CUtensorMap* tmap, const Fu
   // over: the whole ring is in flight at the start, and the load of the CTA's next tile but one overlaps the second
   // step on this tile and everything on the next.  Positions come from `queue` as in stencil_sweep.
   unsigned n_claims = 0, pending = 0;
-  auto claim = [&]() { return queue ? atomicAdd(queue, 1u) : (unsigned)cta + (n_claims++) * (unsigned)ncta; };
+  auto claim = [&]() -> unsigned {
+    const unsigned k = n_claims++;
+    if (!queue) return (unsigned)cta + k * (unsigned)ncta;
+    return k == 0 ? (unsigned)cta : (unsigned)ncta + atomicAdd(queue, 1u);  // the first ncta positions go one to each CTA
+  };
   if (threadIdx.x == 0) {
     for (int q = 0; q < STAGES; ++q) {
       const int t = (int)min(claim(), (unsigned)ntiles);
