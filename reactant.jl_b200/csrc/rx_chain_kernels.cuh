@@ -184,6 +184,64 @@ __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant_
   }
 }
 
+// Any strides, no alignment: the space is [rows][inner] (rows = all dims but the last, flattened), and a thread takes
+// four elements of one row that lie W apart, W lanes side by side on the row (W: a power of two between 32 and 256
+// picked by the launcher from the row length; a CTA covers 256 / W rows' chunks at once).  The index arithmetic --
+// unravelling the row, one offset per operand -- is done once per four elements, a warp's accesses stay consecutive
+// whatever the operands' offsets (shifted windows of one array are never 16-byte aligned all at once), and four
+// independent chains are in flight.  Not for programs that read the index (iota): element v is not at inner + v.
+template <class C>
+__global__ void __launch_bounds__(kThreads) k_map_runs(const __grid_constant__ VmProgram P, int64_t rows, int64_t inner, int log2w, int64_t chunks_per_row) {
+  constexpr int V = 4;
+  const int W = 1 << log2w, last = P.rank - 1;
+  const int sub = (int)threadIdx.x >> log2w, lane = (int)threadIdx.x & (W - 1), per_cta = kThreads >> log2w;
+  const int64_t total = rows * chunks_per_row;
+  const bool small = total < ((int64_t)1 << 31) && rows < ((int64_t)1 << 31);
+  int64_t idx0[kMaxRank] = {0, 0, 0, 0};
+  for (int64_t g = (int64_t)blockIdx.x * per_cta + sub; g < total; g += (int64_t)gridDim.x * per_cta) {
+    int64_t row, cc;
+    if (small) { const uint32_t r = (uint32_t)g / (uint32_t)chunks_per_row; row = r; cc = (uint32_t)g - r * (uint32_t)chunks_per_row; }
+    else { row = g / chunks_per_row; cc = g - row * chunks_per_row; }
+    const int64_t col = cc * (V * W) + lane;
+    int64_t idx[kMaxRank] = {0, 0, 0, 0};
+    {
+      int64_t lin = row;
+#pragma unroll
+      for (int d = kMaxRank - 2; d >= 0; --d) {
+        if (d < last) {
+          if (small) { const uint32_t dm = (uint32_t)P.dim[d], q = (uint32_t)lin / dm; idx[d] = (uint32_t)lin - q * dm; lin = q; }
+          else { const int64_t q = lin / P.dim[d]; idx[d] = lin - q * P.dim[d]; lin = q; }
+        }
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < kMaxRank; ++d)
+      if (d == last) idx[d] = col;
+    __align__(16) uint32_t R[C::kRegs][V];
+    RX_CHAIN_UNROLL for (int k = 0; k < C::n_leaves(P); ++k) {
+      const VmLeaf l = C::leaf(P, k);
+      const int64_t off = leaf_offset(l, idx, P.rank);
+      int64_t st = 0;
+#pragma unroll
+      for (int d = 0; d < kMaxRank; ++d)
+        if (d == last) st = l.stride[d] * W;
+#pragma unroll
+      for (int v = 0; v < V; ++v) R[C::leaf_reg(P, k)][v] = col + v * W < inner ? leaf_load(l, off + v * st) : 0u;
+    }
+    C::template exec<V>(P, R, idx0);
+    RX_CHAIN_UNROLL for (int k = 0; k < C::n_outs(P); ++k) {
+      const VmOut o = C::out(P, k);
+      const int64_t off = out_offset(o, idx, P.rank);
+      int64_t st = 0;
+#pragma unroll
+      for (int d = 0; d < kMaxRank; ++d)
+        if (d == last) st = o.stride[d] * W;
+#pragma unroll
+      for (int v = 0; v < V; ++v)
+        if (col + v * W < inner) out_store(o, off + v * st, R[C::out_reg(P, k)][v]);
+    }
+  }
+}
 
 // ---- 2-D "row-vector" access: 4 consecutive elements of the innermost dim, operands either
 // contiguous along it (stride 1) or broadcast along it (stride 0); any stride along the row dim.

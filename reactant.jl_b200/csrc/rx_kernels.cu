@@ -376,6 +376,13 @@ cudaError_t try_specialised(const LaunchCtx& c, const VmProgram& P, const char* 
   return jit_launch(k, grid, dim3(kThreads), args, c.stream, pdl);
 }
 
+// does the chain read the element's index (stablehlo.iota)?
+static bool reads_index(const VmProgram& P) {
+  for (int k = 0; k < P.n_instr; ++k)
+    if (P.ins[k].op == VM_IOTA) return true;
+  return false;
+}
+
 cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
   int64_t n = total_of(P);
   if (n == 0) return cudaSuccess;
@@ -398,6 +405,16 @@ cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
       e = try_specialised(c, P, "k_map_rows<rx::SpecChain, 1>", -1, n, grid, args, &ran);
       if (!ran && e == cudaSuccess) k_map_rows<InterpChain, 1><<<grid, kThreads, 0, c.stream>>>(P, rows, cols);
     }
+  } else if (P.rank >= 1 && !reads_index(P) && !(getenv("RX_MAP_RUNS") && atoi(getenv("RX_MAP_RUNS")) == 0)) {
+    // four elements per thread along the last dim, W lanes apart (k_map_runs)
+    int64_t inner = P.dim[P.rank - 1], rows = n / inner;
+    int log2w = 5;
+    while (log2w < 8 && ((int64_t)4 << log2w) < inner) ++log2w;
+    int64_t chunks_per_row = (inner + ((int64_t)4 << log2w) - 1) / ((int64_t)4 << log2w);
+    dim3 grid(grid_for(rows * chunks_per_row << log2w, c.sm_count, 8));
+    void* args[] = {(void*)&P, (void*)&rows, (void*)&inner, (void*)&log2w, (void*)&chunks_per_row};
+    e = try_specialised(c, P, "k_map_runs<rx::SpecChain>", -1, n, grid, args, &ran);
+    if (!ran && e == cudaSuccess) k_map_runs<InterpChain><<<grid, kThreads, 0, c.stream>>>(P, rows, inner, log2w, chunks_per_row);
   } else {
     dim3 grid(grid_for(n, c.sm_count, 8));
     void* args[] = {(void*)&P, (void*)&n};

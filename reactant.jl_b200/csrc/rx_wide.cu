@@ -210,17 +210,39 @@ __global__ void __launch_bounds__(kWideThreads) k_wide_map(const __grid_constant
   }
 }
 
-// whole space -> one value: one CTA, strided partials per thread, fixed tree
-__global__ void __launch_bounds__(kWideThreads) k_wide_reduce_full(const __grid_constant__ VmProgram P, int64_t n, int code, int f64, uint64_t init) {
+// whole space -> one value: every CTA folds a strided share of the elements (strided partials per thread, fixed tree),
+// the CTA that finishes last folds the CTAs' values in index order.  The grid depends only on the element count and
+// the device, so the order of combination, and with it the result, is the same from run to run.
+__global__ void __launch_bounds__(kWideThreads) k_wide_reduce_full(const __grid_constant__ VmProgram P, int64_t n, int code, int f64, uint64_t init, uint64_t* partials,
+                                                                   unsigned* ticket) {
   __shared__ uint64_t sm[kWideThreads];
+  __shared__ int last_cta;
   uint64_t acc = wide_identity(code, f64);
-  for (int64_t i = threadIdx.x; i < n; i += kWideThreads) {
+  for (int64_t i = (int64_t)blockIdx.x * kWideThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kWideThreads) {
     int64_t idx[kMaxRank];
     unravel(P, i, idx);
     acc = wide_combine(code, f64, acc, wide_eval_at(P, idx));
   }
   acc = wide_block_red(code, f64, acc, sm);
-  if (threadIdx.x == 0) wide_store(P.out[0], P.out[0].offset, wide_combine(code, f64, init, acc));
+  if (gridDim.x == 1) {
+    if (threadIdx.x == 0) wide_store(P.out[0], P.out[0].offset, wide_combine(code, f64, init, acc));
+    return;
+  }
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = acc;
+    __threadfence();
+    last_cta = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!last_cta) return;
+  __threadfence();
+  acc = wide_identity(code, f64);
+  for (int j = threadIdx.x; j < (int)gridDim.x; j += kWideThreads) acc = wide_combine(code, f64, acc, __ldcg(partials + j));
+  acc = wide_block_red(code, f64, acc, sm);
+  if (threadIdx.x == 0) {
+    wide_store(P.out[0], P.out[0].offset, wide_combine(code, f64, init, acc));
+    *ticket = 0;  // for the next launch that counts finished CTAs in it
+  }
 }
 
 // [outer][red]: one CTA per row
@@ -302,7 +324,11 @@ cudaError_t launch_wide_reduce(const LaunchCtx& c, const VmProgram& P, int shape
   if (shape == 0) {
     int64_t n = 1;
     for (int d = 0; d < P.rank; ++d) n *= P.dim[d];
-    k_wide_reduce_full<<<1, kWideThreads, 0, c.stream>>>(P, n, code, f64 ? 1 : 0, init);
+    // at least 8 elements per thread; the partials sit at the start of the device's scratch words, the ticket in the
+    // last one (shared, in stream order, with the 32-bit reductions)
+    int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((n + 8 * kWideThreads - 1) / (8 * kWideThreads), (int64_t)c.sm_count * 8));
+    if ((size_t)blocks * 2 + 8 > c.scratch_words) blocks = 1;
+    k_wide_reduce_full<<<blocks, kWideThreads, 0, c.stream>>>(P, n, code, f64 ? 1 : 0, init, (uint64_t*)c.scratch, (unsigned*)(c.scratch + c.scratch_words - 1));
   } else if (shape == 1) {
     if (outer == 0) return cudaSuccess;
     k_wide_reduce_row<<<(int)std::min<int64_t>(outer, (int64_t)c.sm_count * 8), kWideThreads, 0, c.stream>>>(P, outer, red_n, code, f64 ? 1 : 0, init);
