@@ -195,7 +195,19 @@ __global__ void __launch_bounds__(kThreads) k_scan_lines(const uint32_t* __restr
   const int64_t o = line / inner, i = line - o * inner;
   const int64_t base = o * n * inner + i;
   uint32_t acc = red_identity(code);
-  for (int64_t r = 0; r < n; ++r) {
+  int64_t r = 0;
+  // eight steps at a time: their loads do not depend on the running value and are issued together
+  for (; r + 8 <= n; r += 8) {
+    uint32_t v[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) v[q] = __ldg(x + base + (r + q) * inner);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      acc = red_combine(code, acc, v[q]);
+      y[base + (r + q) * inner] = acc;
+    }
+  }
+  for (; r < n; ++r) {
     acc = red_combine(code, acc, __ldg(x + base + r * inner));
     y[base + r * inner] = acc;
   }
@@ -224,18 +236,27 @@ __global__ void __launch_bounds__(kThreads) k_scan_row_apply(const uint32_t* __r
   const uint32_t* xr = x + row * n;
   uint32_t* yr = y + row * n;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  if (threadIdx.x == 0) {
+  {
+    // the segments before this one, folded in a fixed order: a strided share per thread, then the block tree
     uint32_t c = red_identity(code);
-    for (int q = 0; q < (int)blockIdx.x; ++q) c = red_combine(code, c, partial[row * nseg + q]);
-    carry_s = c;
+    for (int q = threadIdx.x; q < (int)blockIdx.x; q += kThreads) c = red_combine(code, c, partial[row * nseg + q]);
+    c = block_red<kThreads>(code, c, warp_tot);
+    if (threadIdx.x == 0) carry_s = c;
   }
   __syncthreads();
   uint32_t carry = carry_s;
+  const uint32_t ident = red_identity(code);
+  auto fetch = [&](int64_t c0, uint32_t* v) {
+    const int64_t c = c0 + 4 * threadIdx.x;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) v[q] = (c + q < s1) ? __ldg(xr + c + q) : ident;
+  };
+  uint32_t nv[4];
+  fetch(s0, nv);
   for (int64_t c0 = s0; c0 < s1; c0 += 4 * kThreads) {
     const int64_t c = c0 + 4 * threadIdx.x;
-    uint32_t v[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) v[q] = (c + q < s1) ? __ldg(xr + c + q) : red_identity(code);
+    uint32_t v[4] = {nv[0], nv[1], nv[2], nv[3]};
+    if (c0 + 4 * kThreads < s1) fetch(c0 + 4 * kThreads, nv);  // the next chunk is on its way during the work on this one
     v[1] = red_combine(code, v[0], v[1]);
     v[2] = red_combine(code, v[1], v[2]);
     v[3] = red_combine(code, v[2], v[3]);
@@ -572,12 +593,12 @@ cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code
   }
   if (outer > 65535) return cudaErrorInvalidValue;
   // enough CTAs to fill the GPU, at least four 1024-element chunks per segment
-  int64_t want = std::max<int64_t>(1, (4 * (int64_t)c.sm_count + outer - 1) / outer);
+  int64_t want = std::max<int64_t>(1, (8 * (int64_t)c.sm_count + outer - 1) / outer);
   int64_t max_seg = std::max<int64_t>(1, n / 4096);
-  int nseg = (int)std::min<int64_t>(std::min(want, max_seg), 1024);
+  int nseg = (int)std::min<int64_t>(std::min(want, max_seg), 4096);
   int64_t seg = ((n + nseg - 1) / nseg + 1023) / 1024 * 1024;
   nseg = (int)((n + seg - 1) / seg);
-  if ((size_t)(outer * nseg) + 4 > c.scratch_words) return cudaErrorInvalidValue;  // the last four words belong to the stencil loop and the reductions
+  if ((size_t)(outer * nseg) + 6 > c.scratch_words) return cudaErrorInvalidValue;  // the last six words belong to the stencil loop and the reductions
   uint32_t* partial = c.scratch;
   dim3 grid((unsigned)nseg, (unsigned)outer);
   if (nseg > 1) {

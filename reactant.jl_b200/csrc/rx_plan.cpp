@@ -2012,7 +2012,7 @@ struct Planner {
   void plan_dus(const Op& op) {
     int v = op.out[0], o = op.in[0], u = op.in[1];
     for (int x : op.in) if (shard[x] >= 0) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.dynamic_update_slice of a sharded tensor");
-    ExprP O = env[o], U = env[u];
+    ExprP U = env[u];
     Type t = m.values[v].type;
     std::vector<int64_t> starts;
     for (size_t k = 2; k < op.in.size(); ++k) {
@@ -2022,6 +2022,13 @@ struct Planner {
       s = std::max<int64_t>(0, std::min<int64_t>(s, t.shape[d] - U->shape[d]));  // clamped, as the op specifies
       starts.push_back(s);
     }
+    plan_update_window(op, v, env[o], U, starts);
+  }
+
+  // value v = the array O with the window at `starts` replaced by U (`op` is the op being planned: a
+  // dynamic_update_slice, or the select of the pad + select spelling)
+  void plan_update_window(const Op& op, int v, ExprP O, ExprP U, const std::vector<int64_t>& starts) {
+    Type t = m.values[v].type;
     int dst = -1;
     // In place when nothing that is still to be evaluated reads the target's storage: the target itself has no later
     // use, and every expression that looked at it (the slices of the previous half-step, say) has already been
@@ -2074,6 +2081,20 @@ struct Planner {
     if (pv->k != Expr::Const) throw Error(RX_ERR_UNSUPPORTED_OP, "unsupported op stablehlo.pad with a non-constant padding value");
     Type t = m.values[v].type;
     check_dt(op, t.dt);
+    {
+      // `true` padded with `false`: the mask of a window (see plan_masked_update)
+      int64_t inside = 0, outside = 1;
+      if (t.dt == DT::PRED && const_int(X, &inside) && inside != 0 && const_int(pv, &outside) && outside == 0) window_mask[v] = {op.start, op.limit};
+    }
+    if (const Op* sel = sole_user_if(v, OpK::Select)) {
+      auto it = window_mask.find(sel->in[0]);
+      if (sel->in[1] == v && sel->in[2] != v && sel->in[0] != v && it != window_mask.end() && it->second.first == op.start && it->second.second == op.limit &&
+          shard[sel->in[2]] < 0) {
+        deferred_pad[v] = &op;
+        for (int x : op.in) ++remaining[x];  // still needed: consumed when the select is planned
+        return;
+      }
+    }
     int dst = new_slot(t);
     emit_map(konst(t, pv->f, pv->i), dst, 0, canon_strides(t.shape), "pad fill");
     std::vector<int64_t> cs = canon_strides(t.shape);
@@ -2094,12 +2115,31 @@ struct Planner {
   std::map<int, const Op*> deferred_concat;
   const Region* cur_region = nullptr;
 
-  const Op* sole_user_if_concat(int v) const {
+  const Op* sole_user_if(int v, OpK kind) const {
     if (uses[v] != 1 || !cur_region) return nullptr;
     for (auto& op : cur_region->ops)
       for (int x : op.in)
-        if (x == v) return op.kind == OpK::Concatenate ? &op : nullptr;
+        if (x == v) return op.kind == kind ? &op : nullptr;
     return nullptr;  // a result of the region, or used inside a nested one
+  }
+  const Op* sole_user_if_concat(int v) const { return sole_user_if(v, OpK::Concatenate); }
+
+  // ---- pad + select ---------------------------------------------------------------------------------------------
+  // The other spelling the communication patterns leave of a dynamic_update_slice (src/compiler/OptimizationPasses.jl:
+  // 356-372): select(mask, pad(update), target), where mask is `true` padded with `false` by the same amounts (a
+  // constant, usually hoisted out of the loop).  The padded update is not materialised; the select is planned as the
+  // window update it is, in place under the same conditions as a dynamic_update_slice.
+  std::map<int, std::pair<std::vector<int64_t>, std::vector<int64_t>>> window_mask;  // value -> (low, high) padding
+  std::map<int, const Op*> deferred_pad;
+
+  bool plan_masked_update(const Op& op) {
+    auto it = deferred_pad.find(op.in[1]);
+    if (it == deferred_pad.end()) return false;
+    const Op* pad = it->second;
+    deferred_pad.erase(it);
+    plan_update_window(op, op.out[0], env[op.in[2]], env[pad->in[0]], pad->start);
+    for (int x : pad->in) --remaining[x];
+    return true;
   }
   void concat_pieces(const Op& op, const std::vector<int64_t>& base, std::vector<ConcatPiece>& out, std::vector<const Op*>& inner) {
     const int d = (int)op.dims[0];
@@ -2529,7 +2569,10 @@ struct Planner {
       switch (op.kind) {
         case OpK::Constant: plan_constant(op); break;
         case OpK::Iota: plan_iota(op); break;
-        case OpK::Unary: case OpK::Binary: case OpK::Convert: case OpK::Compare: case OpK::Select: case OpK::Clamp:
+        case OpK::Select:
+          if (plan_masked_update(op)) break;
+          plan_elementwise(op); break;
+        case OpK::Unary: case OpK::Binary: case OpK::Convert: case OpK::Compare: case OpK::Clamp:
           plan_elementwise(op); break;
         case OpK::BroadcastInDim: case OpK::Transpose: case OpK::Slice: plan_view(op); break;
         case OpK::Reshape: plan_reshape(op); break;

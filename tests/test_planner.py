@@ -3,6 +3,7 @@ programs and the hard-error contract for anything outside the supported set."""
 import json
 import os
 
+import numpy as np
 import pytest
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -250,6 +251,41 @@ def test_nested_concatenates_around_an_update_plan_as_the_update_in_place(rx):
     # a piece taken from somewhere else in the target is not "in place"
     text2 = text.replace("[7:8, 0:8]", "[6:7, 0:8]").replace("    %1 = stablehlo.sine %arg0 : " + t + "\n", "").replace("return %0, %1 : " + t + ", " + t, "return %0 : " + t).replace(f"-> ({t}, {t})", f"-> {t}")
     assert kinds(rx.plan_describe(text2)).count("map") == 3
+
+
+def test_pad_and_select_around_an_update_plan_as_the_update_in_place(rx, ref):
+    """The pad + select spelling of a window update -- select(mask, pad(update), target) with mask = `true` padded
+    with `false` by the same amounts -- plans like the dynamic_update_slice it was rewritten from: the padded update
+    is not materialised and the loop body is the one stencil step.  A mask that does not match the padding, or a
+    padded update that something else reads too, keeps the general plan (pad into a new array, select as a map)."""
+    p = rx.plan_describe(rx.programs.jacobi2d(8192, 100, form="pad"))
+    loop = [s for s in p["steps"] if s["kind"] == "loop"]
+    assert len(loop) == 1 and [s["kind"] for s in loop[0]["body"]] == ["stencil"], p["steps"]
+    assert loop[0]["body"][0]["chain"] == "stencil5_mul"
+    t, ti, tm = "tensor<8x8xf32>", "tensor<6x6xf32>", "tensor<8x8xi1>"
+    text = f"""module {{
+  func.func @main(%arg0: {t} {{tf.aliasing_output = 0 : i32}}, %arg1: {ti}) -> {t} {{
+    %z = stablehlo.constant dense<0.000000e+00> : tensor<f32>
+    %false = stablehlo.constant dense<false> : tensor<i1>
+    %ones = stablehlo.constant dense<true> : tensor<6x6xi1>
+    %pm = stablehlo.pad %ones, %false, low = [1, 1], high = [1, 1], interior = [0, 0] : (tensor<6x6xi1>, tensor<i1>) -> {tm}
+    %pu = stablehlo.pad %arg1, %z, low = [1, 1], high = [1, 1], interior = [0, 0] : ({ti}, tensor<f32>) -> {t}
+    %0 = stablehlo.select %pm, %pu, %arg0 : {tm}, {t}
+    return %0 : {t}
+  }}
+}}
+"""
+    notes = [s.get("note", "") for s in rx.plan_describe(text)["steps"]]
+    assert any("update window at offset 9" in n for n in notes) and not any("pad interior" in n and "f32" in n for n in notes[2:]), notes
+    x = np.arange(64, dtype=np.float32).reshape(8, 8)
+    u = -np.arange(36, dtype=np.float32).reshape(6, 6)
+    want = x.copy()
+    want[1:7, 1:7] = u
+    assert np.array_equal(ref.run_module(text, [x, u])[0], want)
+    # the update padded differently from the mask: not a window update
+    other = text.replace("%pu = stablehlo.pad %arg1, %z, low = [1, 1], high = [1, 1]", "%pu = stablehlo.pad %arg1, %z, low = [2, 1], high = [0, 1]")
+    notes = [s.get("note", "") for s in rx.plan_describe(other)["steps"]]
+    assert not any("update window" in n for n in notes), notes
 
 
 def test_update_target_that_is_still_read_later_is_copied(rx):
