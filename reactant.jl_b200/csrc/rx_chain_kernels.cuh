@@ -185,14 +185,14 @@ __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant_
 }
 
 // Any strides, no alignment: the space is [rows][inner] (rows = all dims but the last, flattened), and a thread takes
-// four elements of one row that lie W apart, W lanes side by side on the row (W: a power of two between 32 and 256
+// V elements of one row that lie W apart, W lanes side by side on the row (W: a power of two between 32 and 256
 // picked by the launcher from the row length; a CTA covers 256 / W rows' chunks at once).  The index arithmetic --
-// unravelling the row, one offset per operand -- is done once per four elements, a warp's accesses stay consecutive
-// whatever the operands' offsets (shifted windows of one array are never 16-byte aligned all at once), and four
-// independent chains are in flight.  Not for programs that read the index (iota): element v is not at inner + v.
-template <class C>
+// unravelling the row, one offset per operand -- is done once per V elements, a warp's accesses stay consecutive
+// whatever the operands' offsets (shifted windows of one array are never 16-byte aligned all at once), and V
+// independent chains and V loads per operand are in flight (V = 4, or 8 for chains with few registers).  Not for
+// programs that read the index (iota): element v is not at inner + v.
+template <class C, int V>
 __global__ void __launch_bounds__(kThreads) k_map_runs(const __grid_constant__ VmProgram P, int64_t rows, int64_t inner, int log2w, int64_t chunks_per_row) {
-  constexpr int V = 4;
   const int W = 1 << log2w, last = P.rank - 1;
   const int sub = (int)threadIdx.x >> log2w, lane = (int)threadIdx.x & (W - 1), per_cta = kThreads >> log2w;
   const int64_t total = rows * chunks_per_row;
@@ -217,28 +217,31 @@ __global__ void __launch_bounds__(kThreads) k_map_runs(const __grid_constant__ V
 #pragma unroll
     for (int d = 0; d < kMaxRank; ++d)
       if (d == last) idx[d] = col;
+    // what is left of the row from this thread's first element on, and the steps between a thread's elements, as
+    // 32-bit numbers (the launcher checks that V steps fit): per element only one widening add is left
+    const int rem = (int)min(inner - col, (int64_t)0x7FFFFFFF);
     __align__(16) uint32_t R[C::kRegs][V];
     RX_CHAIN_UNROLL for (int k = 0; k < C::n_leaves(P); ++k) {
       const VmLeaf l = C::leaf(P, k);
       const int64_t off = leaf_offset(l, idx, P.rank);
-      int64_t st = 0;
+      int st = 0;
 #pragma unroll
       for (int d = 0; d < kMaxRank; ++d)
-        if (d == last) st = l.stride[d] * W;
+        if (d == last) st = (int)l.stride[d] * W;
 #pragma unroll
-      for (int v = 0; v < V; ++v) R[C::leaf_reg(P, k)][v] = col + v * W < inner ? leaf_load(l, off + v * st) : 0u;
+      for (int v = 0; v < V; ++v) R[C::leaf_reg(P, k)][v] = v * W < rem ? leaf_load(l, off + v * st) : 0u;
     }
     C::template exec<V>(P, R, idx0);
     RX_CHAIN_UNROLL for (int k = 0; k < C::n_outs(P); ++k) {
       const VmOut o = C::out(P, k);
       const int64_t off = out_offset(o, idx, P.rank);
-      int64_t st = 0;
+      int st = 0;
 #pragma unroll
       for (int d = 0; d < kMaxRank; ++d)
-        if (d == last) st = o.stride[d] * W;
+        if (d == last) st = (int)o.stride[d] * W;
 #pragma unroll
       for (int v = 0; v < V; ++v)
-        if (col + v * W < inner) out_store(o, off + v * st, R[C::out_reg(P, k)][v]);
+        if (v * W < rem) out_store(o, off + v * st, R[C::out_reg(P, k)][v]);
     }
   }
 }

@@ -10,6 +10,7 @@
 //
 // All of them are HBM-bound streaming kernels: 128-bit coalesced loads, several
 // independent loads in flight per thread, grids sized in multiples of the SM count.
+#include <cstdlib>
 #include "rx_kernels.h"
 
 #include <stdio.h>
@@ -397,6 +398,27 @@ cudaError_t try_specialised(const LaunchCtx& c, const VmProgram& P, const char* 
   return jit_launch(k, grid, dim3(kThreads), args, c.stream, pdl);
 }
 
+// registers of the chain's virtual machine that the program uses
+static int chain_regs(const VmProgram& P) {
+  int r = P.result_reg;
+  for (int k = 0; k < P.n_leaves; ++k) r = std::max<int>(r, P.leaf[k].reg);
+  for (int k = 0; k < P.n_outs; ++k) r = std::max<int>(r, P.out[k].reg);
+  for (int k = 0; k < P.n_instr; ++k)
+    if (P.ins[k].flags & VMF_STORE) r = std::max<int>(r, P.ins[k].dst);
+  return r + 1;
+}
+
+// k_map_runs steps along the last dim in 32-bit arithmetic: 8 steps of 256 elements must fit for every operand (with room to spare)
+static bool runs_steps_fit(const VmProgram& P) {
+  const int last = P.rank - 1;
+  const int64_t lim = ((int64_t)1 << 31) / (16 * 256);
+  for (int k = 0; k < P.n_leaves; ++k)
+    if (std::llabs(P.leaf[k].stride[last]) >= lim) return false;
+  for (int k = 0; k < P.n_outs; ++k)
+    if (std::llabs(P.out[k].stride[last]) >= lim) return false;
+  return true;
+}
+
 // does the chain read the element's index (stablehlo.iota)?
 static bool reads_index(const VmProgram& P) {
   for (int k = 0; k < P.n_instr; ++k)
@@ -426,16 +448,32 @@ cudaError_t launch_map(const LaunchCtx& c, const VmProgram& P) {
       e = try_specialised(c, P, "k_map_rows<rx::SpecChain, 1>", -1, n, grid, args, &ran);
       if (!ran && e == cudaSuccess) k_map_rows<InterpChain, 1><<<grid, kThreads, 0, c.stream>>>(P, rows, cols);
     }
-  } else if (P.rank >= 1 && !reads_index(P) && !(getenv("RX_MAP_RUNS") && atoi(getenv("RX_MAP_RUNS")) == 0)) {
-    // four elements per thread along the last dim, W lanes apart (k_map_runs)
+  } else if (P.rank >= 1 && P.dim[P.rank - 1] >= 64 && !reads_index(P) && runs_steps_fit(P) && !(getenv("RX_MAP_RUNS") && atoi(getenv("RX_MAP_RUNS")) == 0)) {
+    // V elements per thread along the last dim, W lanes apart (k_map_runs); rows shorter than two warps' worth
+    // would leave most lanes idle and stay with one element per thread.  V = 4 in the interpreter; a specialised
+    // chain with few registers takes 8 when the rows are long enough.
     int64_t inner = P.dim[P.rank - 1], rows = n / inner;
-    int log2w = 5;
-    while (log2w < 8 && ((int64_t)4 << log2w) < inner) ++log2w;
-    int64_t chunks_per_row = (inner + ((int64_t)4 << log2w) - 1) / ((int64_t)4 << log2w);
-    dim3 grid(grid_for(rows * chunks_per_row << log2w, c.sm_count, 8));
+    auto geometry = [&](int v, int* log2w, int64_t* chunks_per_row) {
+      *log2w = 5;
+      while (*log2w < 8 && ((int64_t)v << *log2w) < inner) ++*log2w;
+      *chunks_per_row = (inner + ((int64_t)v << *log2w) - 1) / ((int64_t)v << *log2w);
+      return dim3(grid_for(rows * *chunks_per_row << *log2w, c.sm_count, 8));
+    };
+    const int regs = chain_regs(P);
+    int v = (regs <= 8 && inner >= 8 * 256) ? 8 : 4;  // measured: 16 per thread is slower for every chain tried (registers)
+    if (const char* ev = getenv("RX_MAP_RUNS_V")) {  // A/B measurements
+      const int w = atoi(ev);
+      if (w == 4 || w == 8) v = w;
+    }
+    int log2w;
+    int64_t chunks_per_row;
     void* args[] = {(void*)&P, (void*)&rows, (void*)&inner, (void*)&log2w, (void*)&chunks_per_row};
-    e = try_specialised(c, P, "k_map_runs<rx::SpecChain>", -1, n, grid, args, &ran);
-    if (!ran && e == cudaSuccess) k_map_runs<InterpChain><<<grid, kThreads, 0, c.stream>>>(P, rows, inner, log2w, chunks_per_row);
+    dim3 grid = geometry(v, &log2w, &chunks_per_row);
+    e = try_specialised(c, P, v == 8 ? "k_map_runs<rx::SpecChain, 8>" : "k_map_runs<rx::SpecChain, 4>", -1, n, grid, args, &ran);
+    if (!ran && e == cudaSuccess) {
+      grid = geometry(4, &log2w, &chunks_per_row);
+      k_map_runs<InterpChain, 4><<<grid, kThreads, 0, c.stream>>>(P, rows, inner, log2w, chunks_per_row);
+    }
   } else {
     dim3 grid(grid_for(n, c.sm_count, 8));
     void* args[] = {(void*)&P, (void*)&n};

@@ -1352,7 +1352,7 @@ static void specialise_check_steps(const std::vector<Step>& steps, std::string& 
     if (st.prog.wide) continue;  // f64 programs run on the interpreter kernels only
     std::vector<const char*> families;
     int code = -1;
-    if (st.kind == StepK::Map) families = {"k_map_linear<rx::SpecChain>", "k_map_rows<rx::SpecChain, 2>", "k_map_runs<rx::SpecChain>", "k_map_generic<rx::SpecChain, true>"};
+    if (st.kind == StepK::Map) families = {"k_map_linear<rx::SpecChain>", "k_map_rows<rx::SpecChain, 2>", "k_map_runs<rx::SpecChain, 4>", "k_map_runs<rx::SpecChain, 8>", "k_map_generic<rx::SpecChain, true>"};
     else if (st.kind == StepK::ReduceFull) families = {"k_reduce_full_linear<rx::SpecChain>", "k_reduce_full_rows<rx::SpecChain>", "k_reduce_full_generic<rx::SpecChain>"};
     else if (st.kind == StepK::ReduceRow) families = {"k_reduce_row<rx::SpecChain, 256>", "k_reduce_row<rx::SpecChain, 32>"};
     else if (st.kind == StepK::ReduceCol) families = {"k_reduce_col_vec<rx::SpecChain>", "k_reduce_col<rx::SpecChain>"};
