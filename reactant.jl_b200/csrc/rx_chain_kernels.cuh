@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(kThreads) k_map_generic(const __grid_constant_
 // programs that read the index (iota): element v is not at inner + v.
 template <class C, int V>
 __global__ void __launch_bounds__(kThreads) k_map_runs(const __grid_constant__ VmProgram P, int64_t rows, int64_t inner, int log2w, int64_t chunks_per_row) {
-  const int W = 1 << log2w, last = P.rank - 1;
+  const int W = 1 << log2w, rank = C::rank(P), last = rank - 1;
   const int sub = (int)threadIdx.x >> log2w, lane = (int)threadIdx.x & (W - 1), per_cta = kThreads >> log2w;
   const int64_t total = rows * chunks_per_row;
   const bool small = total < ((int64_t)1 << 31) && rows < ((int64_t)1 << 31);
@@ -209,8 +209,8 @@ __global__ void __launch_bounds__(kThreads) k_map_runs(const __grid_constant__ V
 #pragma unroll
       for (int d = kMaxRank - 2; d >= 0; --d) {
         if (d < last) {
-          if (small) { const uint32_t dm = (uint32_t)P.dim[d], q = (uint32_t)lin / dm; idx[d] = (uint32_t)lin - q * dm; lin = q; }
-          else { const int64_t q = lin / P.dim[d]; idx[d] = lin - q * P.dim[d]; lin = q; }
+          if (small) { const uint32_t dm = (uint32_t)C::dim(P, d), q = (uint32_t)lin / dm; idx[d] = (uint32_t)lin - q * dm; lin = q; }
+          else { const int64_t q = lin / C::dim(P, d); idx[d] = lin - q * C::dim(P, d); lin = q; }
         }
       }
     }
@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(kThreads) k_map_runs(const __grid_constant__ V
     __align__(16) uint32_t R[C::kRegs][V];
     RX_CHAIN_UNROLL for (int k = 0; k < C::n_leaves(P); ++k) {
       const VmLeaf l = C::leaf(P, k);
-      const int64_t off = leaf_offset(l, idx, P.rank);
+      const int64_t off = leaf_offset(l, idx, rank);
       int st = 0;
 #pragma unroll
       for (int d = 0; d < kMaxRank; ++d)
@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(kThreads) k_map_runs(const __grid_constant__ V
     C::template exec<V>(P, R, idx0);
     RX_CHAIN_UNROLL for (int k = 0; k < C::n_outs(P); ++k) {
       const VmOut o = C::out(P, k);
-      const int64_t off = out_offset(o, idx, P.rank);
+      const int64_t off = out_offset(o, idx, rank);
       int st = 0;
 #pragma unroll
       for (int d = 0; d < kMaxRank; ++d)

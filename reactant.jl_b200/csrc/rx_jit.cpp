@@ -270,7 +270,22 @@ std::string jit_chain_source(const VmProgram& P, int red_code, const char* famil
     if (in.flags & VMF_STORE) max_reg = std::max<int>(max_reg, in.dst);
   }
   auto I = [](int v) { return std::to_string(v); };
+  auto L = [](int64_t v) { return std::to_string((long long)v) + "LL"; };
+  // The general map kernel spends most of its instructions on index arithmetic (unravelling the row, one offset per
+  // operand from 64-bit strides): for it the rank, the dims and every stride are written into the source, so that
+  // the loops over dims fold, divisions are by constants and operands with equal strides share their products.
+  // (One compilation per shape; the other families stay shape-independent.)
+  const bool shaped = !strncmp(family, "k_map_runs", 10);
   s += "  static constexpr int kRegs = " + I(max_reg + 1) + ";\n";
+  s += "  static __device__ __forceinline__ int rank(const VmProgram& P) { return " + (shaped ? I(P.rank) : std::string("P.rank")) + "; }\n";
+  s += "  static __device__ __forceinline__ int64_t dim(const VmProgram& P, int d) {\n";
+  if (shaped) {
+    s += "    switch (d) {\n";
+    for (int d = 0; d < P.rank; ++d) s += "      case " + I(d) + ": return " + L(P.dim[d]) + ";\n";
+    s += "    }\n    return 1;\n  }\n";
+  } else {
+    s += "    return P.dim[d];\n  }\n";
+  }
   s += "  static __device__ __forceinline__ int n_leaves(const VmProgram&) { return " + I(P.n_leaves) + "; }\n";
   s += "  static __device__ __forceinline__ int n_outs(const VmProgram&) { return " + I(P.n_outs) + "; }\n";
   s += "  static __device__ __forceinline__ int result_reg(const VmProgram&) { return " + I(P.result_reg) + "; }\n";
@@ -282,11 +297,20 @@ std::string jit_chain_source(const VmProgram& P, int red_code, const char* famil
   for (int k = 0; k < P.n_outs; ++k) s += "      case " + I(k) + ": return " + I(P.out[k].reg) + ";\n";
   s += "    }\n    return 0;\n  }\n";
   s += "  static __device__ __forceinline__ VmLeaf leaf(const VmProgram& P, int k) {\n    VmLeaf l = P.leaf[k];\n    switch (k) {\n";
-  for (int k = 0; k < P.n_leaves; ++k)
-    s += "      case " + I(k) + ": l.elem = " + I(P.leaf[k].elem) + "; l.linear = " + I(P.leaf[k].linear) + "; break;\n";
+  for (int k = 0; k < P.n_leaves; ++k) {
+    s += "      case " + I(k) + ": l.elem = " + I(P.leaf[k].elem) + "; l.linear = " + I(P.leaf[k].linear) + ";";
+    if (shaped)
+      for (int d = 0; d < kMaxRank; ++d) s += " l.stride[" + I(d) + "] = " + L(d < P.rank ? P.leaf[k].stride[d] : 0) + ";";
+    s += " break;\n";
+  }
   s += "    }\n    return l;\n  }\n";
   s += "  static __device__ __forceinline__ VmOut out(const VmProgram& P, int k) {\n    VmOut o = P.out[k];\n    switch (k) {\n";
-  for (int k = 0; k < P.n_outs; ++k) s += "      case " + I(k) + ": o.elem = " + I(P.out[k].elem) + "; break;\n";
+  for (int k = 0; k < P.n_outs; ++k) {
+    s += "      case " + I(k) + ": o.elem = " + I(P.out[k].elem) + ";";
+    if (shaped)
+      for (int d = 0; d < kMaxRank; ++d) s += " o.stride[" + I(d) + "] = " + L(d < P.rank ? P.out[k].stride[d] : 0) + ";";
+    s += " break;\n";
+  }
   s += "    }\n    return o;\n  }\n";
   s += "  template <int V>\n  static __device__ __forceinline__ void exec(const VmProgram& P, uint32_t (*R)[V], const int64_t* idx) {\n";
   s += "#pragma unroll\n    for (int v = 0; v < V; ++v) {\n      uint32_t acc = 0;\n";

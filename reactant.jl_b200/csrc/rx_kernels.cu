@@ -32,6 +32,8 @@ struct InterpChain {
   static __device__ __forceinline__ int n_outs(const VmProgram& P) { return P.n_outs; }
   static __device__ __forceinline__ int result_reg(const VmProgram& P) { return P.result_reg; }
   static __device__ __forceinline__ int red_code(int c) { return c; }
+  static __device__ __forceinline__ int rank(const VmProgram& P) { return P.rank; }
+  static __device__ __forceinline__ int64_t dim(const VmProgram& P, int d) { return P.dim[d]; }
   static __device__ __forceinline__ int leaf_reg(const VmProgram& P, int k) { return P.leaf[k].reg; }
   static __device__ __forceinline__ int out_reg(const VmProgram& P, int k) { return P.out[k].reg; }
   static __device__ __forceinline__ const VmLeaf& leaf(const VmProgram& P, int k) { return P.leaf[k]; }
