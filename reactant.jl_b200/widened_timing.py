@@ -58,11 +58,11 @@ def main(argv):
     rng = np.random.default_rng(0)
     up = lambda x: rx.to_rarray(x, client)
     if "jacobi1d" in which:
-        n, steps = (1 << 23) if small else (1 << 26), 10
+        n, steps = (1 << 25) if small else (1 << 26), 10
         f = rx.compile(P.jacobi1d(n, steps), client)
         timeit(dev, f"jacobi_1d n={n} x{steps} iterations", f, [up(rng.random(n, dtype=np.float32)), up(rng.random(n, dtype=np.float32))], 2 * steps * 8.0 * n)
     if "heat3d" in which:
-        n, steps = 256 if small else 512, 5
+        n, steps = 320 if small else 512, 5
         f = rx.compile(P.heat3d(n, steps), client)
         timeit(dev, f"heat_3d n={n} x{steps} iterations", f, [up(rng.random((n, n, n), dtype=np.float32)), up(rng.random((n, n, n), dtype=np.float32))], 2 * steps * 8.0 * n ** 3)
     if "fdtd2d" in which:
