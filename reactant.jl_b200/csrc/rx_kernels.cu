@@ -192,7 +192,11 @@ __global__ void __launch_bounds__(kThreads) k_logsumexp(const float* __restrict_
 
 // ---- inclusive scan along the middle dim of [outer][n][inner] (stablehlo.reduce_window in its cumulative form) ------
 // Lines that are strided in memory (inner > 1): one thread per line, sequential along n, coalesced across lines.
-__global__ void __launch_bounds__(kThreads) k_scan_lines(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, int code, int64_t outer, int64_t n, int64_t inner) {
+// (The combiner is a template parameter of the scan kernels: red_combine() is a switch over ten cases, and a scan
+// calls it several times per element.)
+template <int CODE>
+__global__ void __launch_bounds__(kThreads) k_scan_lines(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, int64_t outer, int64_t n, int64_t inner) {
+  constexpr int code = CODE;
   const int64_t line = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   if (line >= outer * inner) return;
   const int64_t o = line / inner, i = line - o * inner;
@@ -216,12 +220,46 @@ __global__ void __launch_bounds__(kThreads) k_scan_lines(const uint32_t* __restr
   }
 }
 
+// Few long strided lines do not fill the GPU with a thread per line: the lines are cut into `nseg` segments of `seg`
+// steps (blockIdx.y).  Pass 1 leaves every (segment, line) total in partial[segment][line]; pass 2 folds the totals
+// of the segments before its own, in order, and scans its segment from there.
+template <int CODE, bool APPLY>
+__global__ void __launch_bounds__(kThreads) k_scan_lines_seg(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, uint32_t* __restrict__ partial, int64_t outer, int64_t n,
+                                                            int64_t inner, int64_t seg) {
+  constexpr int code = CODE;
+  const int64_t lines = outer * inner, line = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (line >= lines) return;
+  const int64_t o = line / inner, i = line - o * inner;
+  const int64_t base = o * n * inner + i;
+  const int64_t r0 = (int64_t)blockIdx.y * seg, r1 = min(n, r0 + seg);
+  uint32_t acc = red_identity(code);
+  if (APPLY)
+    for (int q = 0; q < (int)blockIdx.y; ++q) acc = red_combine(code, acc, partial[q * lines + line]);
+  int64_t r = r0;
+  for (; r + 8 <= r1; r += 8) {
+    uint32_t v[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) v[q] = __ldg(x + base + (r + q) * inner);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      acc = red_combine(code, acc, v[q]);
+      if (APPLY) y[base + (r + q) * inner] = acc;
+    }
+  }
+  for (; r < r1; ++r) {
+    acc = red_combine(code, acc, __ldg(x + base + r * inner));
+    if (APPLY) y[base + r * inner] = acc;
+  }
+  if (!APPLY) partial[(int64_t)blockIdx.y * lines + line] = acc;
+}
+
 // Contiguous rows (inner == 1), each row cut into `nseg` segments of `seg` elements (a multiple of 1024).
 // Pass 1: the combined value of every segment.  Pass 2: every CTA folds the values of the segments before its own
 // (in order), then scans its segment 1024 elements at a time: four per thread, warp shuffles, one shared-memory hop
 // across the eight warps, and a running carry.  The order of combination is fixed, so results are deterministic.
-__global__ void __launch_bounds__(kThreads) k_scan_row_partials(const uint32_t* __restrict__ x, uint32_t* __restrict__ partial, int code, int64_t n, int64_t seg,
-                                                               int nseg) {
+template <int CODE>
+__global__ void __launch_bounds__(kThreads) k_scan_row_partials(const uint32_t* __restrict__ x, uint32_t* __restrict__ partial, int64_t n, int64_t seg, int nseg) {
+  constexpr int code = CODE;
   __shared__ uint32_t sm[kThreads / 32];
   const int64_t row = blockIdx.y, s0 = (int64_t)blockIdx.x * seg, s1 = min(n, s0 + seg);
   const uint32_t* xr = x + row * n;
@@ -231,8 +269,10 @@ __global__ void __launch_bounds__(kThreads) k_scan_row_partials(const uint32_t* 
   if (threadIdx.x == 0) partial[row * nseg + blockIdx.x] = acc;
 }
 
-__global__ void __launch_bounds__(kThreads) k_scan_row_apply(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, const uint32_t* __restrict__ partial, int code, int64_t n,
-                                                            int64_t seg, int nseg) {
+template <int CODE>
+__global__ void __launch_bounds__(kThreads) k_scan_row_apply(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, const uint32_t* __restrict__ partial, int64_t n, int64_t seg,
+                                                            int nseg) {
+  constexpr int code = CODE;
   __shared__ uint32_t warp_tot[kThreads / 32];
   __shared__ uint32_t carry_s;
   const int64_t row = blockIdx.y, s0 = (int64_t)blockIdx.x * seg, s1 = min(n, s0 + seg);
@@ -620,14 +660,29 @@ cudaError_t launch_reduce_col(const LaunchCtx& c, const VmProgram& P, int code, 
 }
 
 
-cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code, int64_t outer, int64_t n, int64_t inner) {
+template <int CODE>
+static cudaError_t launch_scan_with(const LaunchCtx& c, const void* src, void* dst, int64_t outer, int64_t n, int64_t inner) {
   if (outer * n * inner == 0) return cudaSuccess;
   const uint32_t* x = (const uint32_t*)src;
   uint32_t* y = (uint32_t*)dst;
   if (inner > 1 || n <= 32) {
     // (for very short contiguous rows a thread per row is as good as anything)
     const int64_t lines = outer * inner;
-    k_scan_lines<<<(unsigned)((lines + kThreads - 1) / kThreads), kThreads, 0, c.stream>>>(x, y, code, outer, n, inner);
+    const unsigned blocks = (unsigned)((lines + kThreads - 1) / kThreads);
+    // fewer lines than half the threads the GPU holds, and long ones: cut them into segments (two launches)
+    const int64_t want_threads = (int64_t)c.sm_count * 1024;
+    int64_t nseg = std::min<int64_t>((want_threads + lines - 1) / lines, n / 64);
+    nseg = std::min<int64_t>(nseg, 64);
+    if (nseg >= 2 && (size_t)(nseg * lines) + 6 <= c.scratch_words) {
+      const int64_t seg = ((n + nseg - 1) / nseg + 7) / 8 * 8;
+      nseg = (n + seg - 1) / seg;
+      dim3 grid(blocks, (unsigned)nseg);
+      k_scan_lines_seg<CODE, false><<<grid, kThreads, 0, c.stream>>>(x, y, c.scratch, outer, n, inner, seg);
+      k_scan_lines_seg<CODE, true><<<grid, kThreads, 0, c.stream>>>(x, y, c.scratch, outer, n, inner, seg);
+      *c.launches += 2;
+      return cudaGetLastError();
+    }
+    k_scan_lines<CODE><<<blocks, kThreads, 0, c.stream>>>(x, y, outer, n, inner);
     ++*c.launches;
     return cudaGetLastError();
   }
@@ -642,12 +697,28 @@ cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code
   uint32_t* partial = c.scratch;
   dim3 grid((unsigned)nseg, (unsigned)outer);
   if (nseg > 1) {
-    k_scan_row_partials<<<grid, kThreads, 0, c.stream>>>(x, partial, code, n, seg, nseg);
+    k_scan_row_partials<CODE><<<grid, kThreads, 0, c.stream>>>(x, partial, n, seg, nseg);
     ++*c.launches;
   }
-  k_scan_row_apply<<<grid, kThreads, 0, c.stream>>>(x, y, partial, code, n, seg, nseg);
+  k_scan_row_apply<CODE><<<grid, kThreads, 0, c.stream>>>(x, y, partial, n, seg, nseg);
   ++*c.launches;
   return cudaGetLastError();
+}
+
+cudaError_t launch_scan(const LaunchCtx& c, const void* src, void* dst, int code, int64_t outer, int64_t n, int64_t inner) {
+  switch (code) {
+    case R_FADD: return launch_scan_with<R_FADD>(c, src, dst, outer, n, inner);
+    case R_FMAX: return launch_scan_with<R_FMAX>(c, src, dst, outer, n, inner);
+    case R_FMIN: return launch_scan_with<R_FMIN>(c, src, dst, outer, n, inner);
+    case R_FMUL: return launch_scan_with<R_FMUL>(c, src, dst, outer, n, inner);
+    case R_IADD: return launch_scan_with<R_IADD>(c, src, dst, outer, n, inner);
+    case R_IMAX: return launch_scan_with<R_IMAX>(c, src, dst, outer, n, inner);
+    case R_IMIN: return launch_scan_with<R_IMIN>(c, src, dst, outer, n, inner);
+    case R_IMUL: return launch_scan_with<R_IMUL>(c, src, dst, outer, n, inner);
+    case R_OR: return launch_scan_with<R_OR>(c, src, dst, outer, n, inner);
+    case R_AND: return launch_scan_with<R_AND>(c, src, dst, outer, n, inner);
+  }
+  return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_sum_partials(const LaunchCtx& c, const SumPartialsJob* jobs, int n_jobs) {

@@ -62,7 +62,7 @@ def test_constant_start_indices_are_a_clamped_slice(rx, ref):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("nx,ny,tmax", [(12, 10, 5), (64, 96, 7), (260, 132, 9), (1024, 512, 4)])
+@pytest.mark.parametrize("nx,ny,tmax", [(12, 10, 5), (64, 96, 7), (260, 132, 9), (1024, 512, 4), (2308, 516, 3)])
 def test_fdtd2d_bit_exact(rx, ref, client, nx, ny, tmax):
     EX, EY, HZ, fict = fields(nx, ny, tmax, seed=nx)
     text = rx.programs.fdtd2d(nx, ny, tmax)

@@ -101,3 +101,15 @@ def test_random_view_chains(seed):
     if len(got) > 1:
         tol = oracle.reduction_tolerance(max(n, 2)) * (np.abs(np.asarray(want[0], dtype=np.float64)).sum() + 1e-30)
         np.testing.assert_allclose(got[1], np.asarray(want[1], dtype=np.float64).reshape(got[1].shape), rtol=0, atol=tol, err_msg=text)
+    if seed % 3 == 0:
+        # the same program with every chain compiled at run time (the general map kernel then has the operands' strides
+        # and the dims written into its source): the same bits as the interpreter kernels gave
+        try:
+            rx.chain_specialiser(0)
+            r2 = rx.compile(text)(*[rx.to_rarray(np.ascontiguousarray(a.T)) for a in inputs])
+        finally:
+            rx.chain_specialiser(1 << 20)
+        r2 = r2 if isinstance(r2, tuple) else (r2,)
+        assert rx.chain_specialiser_stats()["failed"] == 0
+        for a, b in zip(r, r2):
+            assert np.asarray(a).tobytes() == np.asarray(b).tobytes(), text
