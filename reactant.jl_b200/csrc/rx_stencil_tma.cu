@@ -7,7 +7,8 @@
 // (src/Indexing.jl:552-627 getindex -> stablehlo.slice, :350-446 setindex! ->
 // dynamic_update_slice; benchmark/polybench/stencil.jl:263-289).
 //
-// Each CTA walks a strided list of 32 x 252 (or 248) output tiles.  One elected thread
+// Each CTA works through 32 x 252 (or 248) output tiles: every n-th one in the single-launch
+// kernel, the next free one of a per-pass queue in the whole-loop kernel.  One elected thread
 // issues a cp.async.bulk.tensor.2d (TMA) load of the tile plus its halo into a
 // two-stage shared-memory ring, signalled through mbarriers; the other threads
 // compute the previous tile meanwhile.  Halo rows/columns are re-read from L2,
